@@ -1,0 +1,154 @@
+"""Builds and loads the CUDA kernel modules.
+
+Every ``<module>.cu`` in this folder becomes one shared library with a C interface, built
+with nvcc for sm_100a and loaded with ctypes.  A module is built the first time something
+asks for it (or all at once by ``build_all``), into ``_build/`` beside the sources when that
+folder can be written, else into a per-user folder under the system's temporary folder.  A
+library is reused when the hash of its sources, the shared header and the flags is the one
+it was built from; time stamps are not trusted.  While nvcc runs, a line is printed to
+standard error now and then.  There is no fallback: without nvcc, or when a build fails, the
+caller gets an error with the compiler's output.
+"""
+from __future__ import annotations
+
+import ctypes
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from concurrent.futures import ThreadPoolExecutor
+from typing import Dict, Iterable, List
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
+NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-shared",
+              "-Xcompiler", "-fvisibility=default"]
+MODULES = ["embedding", "rmsnorm", "qk_rope_store", "attention_generic", "gemm_simt", "swiglu", "sampling"]
+
+_loaded: Dict[str, ctypes.CDLL] = {}
+_lock = threading.Lock()
+
+
+class KernelBuildError(RuntimeError):
+    pass
+
+
+def _nvcc() -> str:
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and os.path.isfile(cand) and os.access(cand, os.X_OK):
+            return cand
+    raise KernelBuildError("nvcc was not found (looked at $NVCC, PATH and /usr/local/cuda/bin): the CUDA kernels cannot be built, "
+                           "and this engine has no other path")
+
+
+def _build_dir() -> str:
+    local = os.path.join(HERE, "_build")
+    try:
+        os.makedirs(local, exist_ok=True)
+        probe = os.path.join(local, f".probe{os.getpid()}")
+        with open(probe, "w"):
+            pass
+        os.remove(probe)
+        return local
+    except OSError:
+        d = os.path.join(tempfile.gettempdir(), f"spyinfer_b200_build_{os.getuid()}")
+        os.makedirs(d, exist_ok=True)
+        return d
+
+
+def _source_hash(module: str) -> str:
+    h = hashlib.sha256()
+    h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS).encode())
+    for name in sorted(os.listdir(HERE)):
+        if name.endswith(".cuh") or name == module + ".cu":
+            with open(os.path.join(HERE, name), "rb") as f:
+                h.update(name.encode())
+                h.update(f.read())
+    return h.hexdigest()
+
+
+def library_path(module: str) -> str:
+    return os.path.join(_build_dir(), f"libspy_{module}.so")
+
+
+def _is_current(module: str) -> bool:
+    so = library_path(module)
+    stamp = so + ".hash"
+    if not (os.path.isfile(so) and os.path.isfile(stamp)):
+        return False
+    with open(stamp) as f:
+        return f.read().strip() == _source_hash(module)
+
+
+def _compile(module: str) -> None:
+    src = os.path.join(HERE, module + ".cu")
+    if not os.path.isfile(src):
+        raise KernelBuildError(f"no kernel module {module!r} ({src} does not exist)")
+    so = library_path(module)
+    tmp = f"{so}.{os.getpid()}.tmp"
+    cmd = [_nvcc()] + ARCH_FLAGS + NVCC_FLAGS + ["-I", HERE, "-o", tmp, src]
+    env = dict(os.environ)
+    env.setdefault("TMPDIR", tempfile.gettempdir())
+    t0 = time.time()
+    proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=env)
+    done = threading.Event()
+
+    def ticker():
+        while not done.wait(15.0):
+            print(f"[spyinfer_b200] still compiling {module}.cu ({time.time() - t0:.0f} s)", file=sys.stderr, flush=True)
+
+    th = threading.Thread(target=ticker, daemon=True)
+    th.start()
+    out, _ = proc.communicate()
+    done.set()
+    if proc.returncode != 0:
+        if os.path.exists(tmp):
+            os.remove(tmp)
+        raise KernelBuildError(f"nvcc failed on {module}.cu:\n$ {' '.join(cmd)}\n{out}")
+    os.replace(tmp, so)
+    with open(so + ".hash", "w") as f:
+        f.write(_source_hash(module))
+    print(f"[spyinfer_b200] compiled {module}.cu in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
+
+
+def ensure_built(modules: Iterable[str]) -> None:
+    """Builds, in parallel, those of ``modules`` whose library is missing or out of date."""
+    todo = [m for m in dict.fromkeys(modules) if not _is_current(m)]
+    if not todo:
+        return
+    print(f"[spyinfer_b200] compiling {len(todo)} CUDA kernel module(s) for sm_100a: {', '.join(todo)}", file=sys.stderr, flush=True)
+    with ThreadPoolExecutor(max_workers=min(len(todo), os.cpu_count() or 1)) as pool:
+        for f in [pool.submit(_compile, m) for m in todo]:
+            f.result()
+
+
+def build_all() -> List[str]:
+    ensure_built(MODULES)
+    return [library_path(m) for m in MODULES]
+
+
+def load(module: str) -> ctypes.CDLL:
+    """The loaded library of one module, built first if need be."""
+    lib = _loaded.get(module)
+    if lib is not None:
+        return lib
+    with _lock:
+        lib = _loaded.get(module)
+        if lib is None:
+            ensure_built([module])
+            try:
+                lib = ctypes.CDLL(library_path(module))
+            except OSError as e:
+                raise KernelBuildError(f"cannot load {library_path(module)}: {e}") from None
+            err = getattr(lib, f"spy_{module}_last_error")
+            err.restype = ctypes.c_char_p
+            _loaded[module] = lib
+    return lib
+
+
+def last_error(module: str) -> str:
+    return getattr(load(module), f"spy_{module}_last_error")().decode(errors="replace")

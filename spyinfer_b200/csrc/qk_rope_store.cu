@@ -1,0 +1,153 @@
+// Per-head q/k RMSNorm + rotary position encoding + store of keys and values into the paged
+// cache, one kernel over the fused qkv activation.  Replaces five launches of the reference
+// (spymaster2h/spyinfer src/models/qwen3.hpp:161-194 and the cache store in
+// src/backends/cuda/native/attention.cu:25-47).
+//
+//   qkv  [T, (nh + 2*nkv) * hd]   q heads, then k heads, then v heads
+//   q    normed and rotated in place
+//   k    normed and rotated, written to the page of its position (not in place)
+//   v    copied to the page of its position
+//
+// Norm (optional): x * (1/sqrt(mean(x^2) + eps)) * w over head_dim, 32-bit.
+// Rotation (optional): pairs (j, j + rot_half) for j < rot_half, angles from a table of
+// (cos, sin) [positions, rot_half] built in 32-bit by spy_build_rope_table; elements from
+// 2*rot_half on pass through.  Formula: src/backends/cpu/cpu_operator.cpp:397-408,
+// table: src/utils/constant_table.hpp:28-41.
+//
+// Pages of one cache: [num_pages][2 (K, V)][nkv][page_size][hd].  A token at position p of
+// sequence s lies in page block_table[s, p / page_size] at slot p % page_size.
+#include "common.cuh"
+
+SPY_MODULE(spy_qk_rope_store)
+
+__global__ void rope_table_kernel(float2* __restrict__ table, const float* __restrict__ inv_freq, int rows, int rot_half)
+{
+    const long long total = (long long)rows * rot_half;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int pos = (int)(i / rot_half), j = (int)(i % rot_half);
+        const float angle = (float)pos * inv_freq[j];
+        table[i] = make_float2(cosf(angle), sinf(angle));
+    }
+}
+
+extern "C" int spy_build_rope_table(float* table, const float* inv_freq, int rows, int rot_half, cudaStream_t stream)
+{
+    if (rows <= 0 || rot_half <= 0) SPY_FAIL("rope table: rows %d and rot_half %d must be positive", rows, rot_half);
+    const long long total = (long long)rows * rot_half;
+    long long blocks = (total + 255) / 256;
+    if (blocks > 4096) blocks = 4096;
+    rope_table_kernel<<<(int)blocks, 256, 0, stream>>>((float2*)table, inv_freq, rows, rot_half);
+    SPY_CHECK_LAUNCH("rope table");
+    return 0;
+}
+
+constexpr int WARPS_PER_BLOCK = 4;
+
+template <typename TA, typename TC, typename TW>
+__global__ void qk_rope_store_kernel(TA* qkv, int tokens, int nh, int nkv, int hd, const TW* __restrict__ q_w,
+                                     const TW* __restrict__ k_w, float eps, const float2* __restrict__ cos_sin, int rot_half,
+                                     int table_rows, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                                     const int* __restrict__ block_table, int table_width, TC* pages, int page_size, int num_pages,
+                                     int store, int* status)
+{
+    extern __shared__ float head_buf[];  // WARPS_PER_BLOCK * hd
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int heads = store ? nh + 2 * nkv : nh;
+    const long long item = (long long)blockIdx.x * WARPS_PER_BLOCK + warp;
+    if (item >= (long long)tokens * heads) return;
+    const int t = (int)(item / heads), head = (int)(item % heads);
+    const int kind = head < nh ? 0 : (head < nh + nkv ? 1 : 2);  // q, k, v
+    float* buf = head_buf + warp * hd;
+    TA* src = qkv + (size_t)t * (nh + 2 * nkv) * hd + (size_t)head * hd;
+    const int pos = positions[t];
+
+    TC* dst_page = nullptr;
+    if (kind != 0) {
+        const int seq = seq_of_token[t];
+        const bool in_table = pos >= 0 && pos / page_size < table_width;
+        const int page = in_table ? block_table[(size_t)seq * table_width + pos / page_size] : -1;
+        if (page < 0 || page >= num_pages) {
+            if (lane == 0) report_status(status, SPY_STATUS_BAD_PAGE, t);
+            return;
+        }
+        const int kv_head = kind == 1 ? head - nh : head - nh - nkv;
+        dst_page = pages + ((((size_t)page * 2 + (kind - 1)) * nkv + kv_head) * page_size + pos % page_size) * hd;
+    }
+
+    if (kind == 2) {
+        for (int d = lane; d < hd; d += 32) dst_page[d] = from_f32<TC>(to_f32(src[d]));
+        return;
+    }
+
+    const TW* w = kind == 0 ? q_w : k_w;
+    float ss = 0.f;
+    for (int d = lane; d < hd; d += 32) {
+        const float v = to_f32(src[d]);
+        buf[d] = v;
+        ss += v * v;
+    }
+    if (w != nullptr) {
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)hd + eps);
+        for (int d = lane; d < hd; d += 32) buf[d] = (inv * buf[d]) * to_f32(w[d]);
+    }
+    __syncwarp();
+    const bool rotate = cos_sin != nullptr;
+    if (rotate && (pos < 0 || pos >= table_rows)) {
+        if (lane == 0) report_status(status, SPY_STATUS_BAD_POSITION, t);
+        return;
+    }
+    for (int d = lane; d < hd; d += 32) {
+        float v = buf[d];
+        if (rotate && d < 2 * rot_half) {
+            const int j = d < rot_half ? d : d - rot_half;
+            const float2 cs = cos_sin[(size_t)pos * rot_half + j];
+            const float lo = buf[j], hi = buf[j + rot_half];
+            v = d < rot_half ? lo * cs.x - hi * cs.y : lo * cs.y + hi * cs.x;
+        }
+        if (kind == 0) src[d] = from_f32<TA>(v);
+        else dst_page[d] = from_f32<TC>(v);
+    }
+}
+
+template <typename TA, typename TC, typename TW>
+static int launch(void* qkv, int tokens, int nh, int nkv, int hd, const void* q_w, const void* k_w, float eps, const float* cos_sin,
+                  int rot_half, int table_rows, const int* positions, const int* seq_of_token, const int* block_table, int table_width,
+                  void* pages, int page_size, int num_pages, int store, int* status, cudaStream_t stream)
+{
+    const int heads = store ? nh + 2 * nkv : nh;
+    const long long items = (long long)tokens * heads;
+    const long long blocks = (items + WARPS_PER_BLOCK - 1) / WARPS_PER_BLOCK;
+    if (blocks > 0x7fffffffLL) SPY_FAIL("qk_rope_store: %lld work items exceed the grid limit", items);
+    const size_t smem = (size_t)WARPS_PER_BLOCK * hd * sizeof(float);
+    if (smem > 48 * 1024) SPY_FAIL("qk_rope_store: head_dim %d is too large (limit %d)", hd, 48 * 1024 / 4 / WARPS_PER_BLOCK);
+    qk_rope_store_kernel<TA, TC, TW><<<(int)blocks, WARPS_PER_BLOCK * 32, smem, stream>>>(
+        (TA*)qkv, tokens, nh, nkv, hd, (const TW*)q_w, (const TW*)k_w, eps, (const float2*)cos_sin, rot_half, table_rows, positions,
+        seq_of_token, block_table, table_width, (TC*)pages, page_size, num_pages, store, status);
+    SPY_CHECK_LAUNCH("qk_rope_store");
+    return 0;
+}
+
+// q_w / k_w: null for no norm (both or neither).  cos_sin: null for no rotation.
+// store == 0: only the q heads are processed (a layer that reads another layer's cache).
+extern "C" int spy_qk_rope_store(void* qkv, int act_dtype, int tokens, int nh, int nkv, int hd, const void* q_w, const void* k_w,
+                                 int w_dtype, float eps, const float* cos_sin, int rot_half, int table_rows, const int* positions,
+                                 const int* seq_of_token, const int* block_table, int table_width, void* pages, int cache_dtype,
+                                 int page_size, int num_pages, int store, int* status, cudaStream_t stream)
+{
+    if (tokens <= 0) return 0;
+    if (nh <= 0 || nkv <= 0 || hd <= 0) SPY_FAIL("qk_rope_store: heads %d/%d and head_dim %d must be positive", nh, nkv, hd);
+    if ((q_w == nullptr) != (k_w == nullptr)) SPY_FAIL("qk_rope_store: q and k norm weights must both be given or both be null");
+    if (cos_sin && (rot_half <= 0 || 2 * rot_half > hd)) SPY_FAIL("qk_rope_store: rotary width %d does not fit head_dim %d", 2 * rot_half, hd);
+    if (store && (page_size <= 0 || num_pages <= 0 || table_width <= 0 || !pages || !block_table))
+        SPY_FAIL("qk_rope_store: storing needs pages, a block table and positive page_size/num_pages/table_width");
+    SPY_DISPATCH_DTYPE(act_dtype, TA, {
+        SPY_DISPATCH_DTYPE(cache_dtype, TC, {
+            SPY_DISPATCH_DTYPE(w_dtype, TW, {
+                return launch<TA, TC, TW>(qkv, tokens, nh, nkv, hd, q_w, k_w, eps, cos_sin, rot_half, table_rows, positions, seq_of_token,
+                                          block_table, table_width, pages, page_size, num_pages, store, status, stream);
+            })
+        })
+    })
+    return 0;
+}

@@ -1,0 +1,236 @@
+"""Python faces of the CUDA kernels: argument checks, then one C call on the current stream.
+
+Every function takes CUDA tensors, checks device, dtype, shape and contiguity (a kernel
+never sees a tensor it cannot index), and raises ``KernelError`` with the module's message
+if the C side refuses the sizes.  Nothing here falls back to a library or to the CPU.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .csrc import build
+
+F32, BF16 = 0, 1
+_CODES = {torch.float32: F32, torch.bfloat16: BF16}
+
+STATUS_MESSAGES = {
+    1: "a token id outside the vocabulary (batch token index {detail})",
+    2: "a position beyond the position table (batch token index {detail})",
+    3: "a block-table entry that is no page of the pool (batch token index {detail})",
+    4: "a wait inside a kernel ran out of its iteration limit (code {detail})",
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def require_cuda() -> None:
+    if not torch.cuda.is_available():
+        raise KernelError("no CUDA device is visible: this engine runs its kernels on the GPU only and has no CPU path")
+
+
+def _code(t: torch.Tensor, what: str) -> int:
+    if t.dtype not in _CODES:
+        raise KernelError(f"{what}: dtype {t.dtype} is not supported (float32 or bfloat16)")
+    return _CODES[t.dtype]
+
+
+def _check(t: torch.Tensor, what: str, dtype=None, ndim=None) -> None:
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise KernelError(f"{what}: expected a CUDA tensor")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{what}: expected {dtype}, found {t.dtype}")
+    if ndim is not None and t.dim() != ndim:
+        raise KernelError(f"{what}: expected {ndim} dimensions, found shape {tuple(t.shape)}")
+    if not t.is_contiguous():
+        raise KernelError(f"{what}: expected a contiguous tensor, found strides {t.stride()} for shape {tuple(t.shape)}")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _call(module: str, fn: str, *args) -> None:
+    lib = build.load(module)
+    f = getattr(lib, fn)
+    f.restype = ctypes.c_int
+    if f(*args) != 0:
+        raise KernelError(build.last_error(module))
+
+
+def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[t] = table[ids[t]]`` widened to float32.  table [V, H]; ids [T] int32; out [T, H] float32."""
+    _check(table, "embedding table", ndim=2)
+    _check(ids, "token ids", torch.int32, 1)
+    _check(out, "embedding output", torch.float32, 2)
+    T, (V, H) = ids.shape[0], table.shape
+    if tuple(out.shape) != (T, H):
+        raise KernelError(f"embedding output: expected shape {(T, H)}, found {tuple(out.shape)}")
+    _call("embedding", "spy_embedding", _ptr(table), _code(table, "embedding table"), _ptr(ids), _ptr(out), T, H, V, _ptr(status), _stream())
+    return out
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, delta: Optional[torch.Tensor] = None,
+            rows: Optional[torch.Tensor] = None, write_back: bool = False) -> torch.Tensor:
+    """``out = rmsnorm(x [+ delta]) * weight`` row by row; with ``write_back`` the sum is stored
+    into ``x`` (the residual stream); ``rows`` gathers rows of x (and delta) into out."""
+    _check(x, "rmsnorm input", ndim=2)
+    _check(weight, "rmsnorm weight", ndim=1)
+    _check(out, "rmsnorm output", ndim=2)
+    H = x.shape[1]
+    if weight.shape[0] != H or out.shape[1] != H:
+        raise KernelError(f"rmsnorm: row lengths differ: input {H}, weight {weight.shape[0]}, output {out.shape[1]}")
+    if delta is not None:
+        _check(delta, "rmsnorm delta", ndim=2)
+        if tuple(delta.shape) != tuple(x.shape):
+            raise KernelError(f"rmsnorm: delta shape {tuple(delta.shape)} differs from input shape {tuple(x.shape)}")
+    if rows is not None:
+        _check(rows, "rmsnorm rows", torch.int32, 1)
+        n = rows.shape[0]
+    else:
+        n = x.shape[0]
+    if out.shape[0] != n:
+        raise KernelError(f"rmsnorm: output has {out.shape[0]} rows, expected {n}")
+    _call("rmsnorm", "spy_rmsnorm", _ptr(x), _code(x, "rmsnorm input"), _ptr(delta), _code(delta, "rmsnorm delta") if delta is not None else 0,
+          _ptr(rows), _ptr(weight), _code(weight, "rmsnorm weight"), _ptr(out), _code(out, "rmsnorm output"), n, H,
+          ctypes.c_float(eps), int(bool(write_back)), _stream())
+    return out
+
+
+def build_rope_table(inv_freq: torch.Tensor, rows: int) -> torch.Tensor:
+    """(cos, sin) of ``position * inv_freq[j]`` as float32 ``[rows, len(inv_freq), 2]``."""
+    _check(inv_freq, "inverse frequencies", torch.float32, 1)
+    table = torch.empty((rows, inv_freq.shape[0], 2), dtype=torch.float32, device=inv_freq.device)
+    _call("qk_rope_store", "spy_build_rope_table", _ptr(table), _ptr(inv_freq), rows, inv_freq.shape[0], _stream())
+    return table
+
+
+def qk_rope_store(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, q_weight: Optional[torch.Tensor],
+                  k_weight: Optional[torch.Tensor], eps: float, rope_table: Optional[torch.Tensor], positions: torch.Tensor,
+                  seq_of_token: torch.Tensor, block_table: Optional[torch.Tensor], pages: Optional[torch.Tensor], store: bool = True,
+                  status: Optional[torch.Tensor] = None) -> None:
+    """In place on the q heads of ``qkv [T, (nh + 2 nkv) hd]``: per-head RMSNorm (if weights are
+    given) and rotation (if a table is given).  With ``store`` the k heads (normed, rotated)
+    and the v heads go to ``pages [num_pages, 2, nkv, page_size, hd]`` through ``block_table
+    [S, width]``."""
+    _check(qkv, "qkv", ndim=2)
+    T = qkv.shape[0]
+    if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
+        raise KernelError(f"qkv: expected {(num_heads + 2 * num_kv_heads) * head_dim} columns, found {qkv.shape[1]}")
+    _check(positions, "positions", torch.int32, 1)
+    _check(seq_of_token, "seq_of_token", torch.int32, 1)
+    if positions.shape[0] != T or seq_of_token.shape[0] != T:
+        raise KernelError("qk_rope_store: positions and seq_of_token must have one entry per token")
+    w_code = 0
+    if (q_weight is None) != (k_weight is None):
+        raise KernelError("qk_rope_store: q and k norm weights must both be given or both be None")
+    if q_weight is not None:
+        _check(q_weight, "q norm weight", ndim=1)
+        _check(k_weight, "k norm weight", q_weight.dtype, 1)
+        if q_weight.shape[0] != head_dim or k_weight.shape[0] != head_dim:
+            raise KernelError(f"qk_rope_store: norm weights must have head_dim={head_dim} elements")
+        w_code = _code(q_weight, "q norm weight")
+    rot_half = table_rows = 0
+    if rope_table is not None:
+        _check(rope_table, "rope table", torch.float32, 3)
+        table_rows, rot_half = rope_table.shape[0], rope_table.shape[1]
+    page_size = num_pages = width = cache_code = 0
+    if store:
+        if pages is None or block_table is None:
+            raise KernelError("qk_rope_store: storing needs pages and a block table")
+        _check(pages, "cache pages", ndim=5)
+        _check(block_table, "block table", torch.int32, 2)
+        num_pages, two, nkv, page_size, hd = pages.shape
+        if two != 2 or nkv != num_kv_heads or hd != head_dim:
+            raise KernelError(f"cache pages: expected [pages, 2, {num_kv_heads}, page_size, {head_dim}], found {tuple(pages.shape)}")
+        width = block_table.shape[1]
+        cache_code = _code(pages, "cache pages")
+    _call("qk_rope_store", "spy_qk_rope_store", _ptr(qkv), _code(qkv, "qkv"), T, num_heads, num_kv_heads, head_dim, _ptr(q_weight),
+          _ptr(k_weight), w_code, ctypes.c_float(eps), _ptr(rope_table), rot_half, table_rows, _ptr(positions), _ptr(seq_of_token),
+          _ptr(block_table if store else None), width, _ptr(pages if store else None), cache_code, page_size, num_pages,
+          int(bool(store)), _ptr(status), _stream())
+
+
+def attention_generic(q: torch.Tensor, num_heads: int, head_dim: int, out: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor,
+                      positions: torch.Tensor, seq_of_token: torch.Tensor, scale: float, window: Optional[int] = None,
+                      status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Attention of every token of the batch over its sequence's pages (any mix of prompt
+    portions and single tokens).  ``q [T, >= nh*hd]`` (only the first nh*hd columns are read),
+    ``out [T, nh*hd]``."""
+    _check(q, "attention queries", ndim=2)
+    _check(out, "attention output", q.dtype, 2)
+    _check(pages, "cache pages", ndim=5)
+    _check(block_table, "block table", torch.int32, 2)
+    _check(positions, "positions", torch.int32, 1)
+    _check(seq_of_token, "seq_of_token", torch.int32, 1)
+    T = q.shape[0]
+    num_pages, two, nkv, page_size, hd = pages.shape
+    if two != 2 or hd != head_dim:
+        raise KernelError(f"cache pages: expected [pages, 2, nkv, page_size, {head_dim}], found {tuple(pages.shape)}")
+    if q.shape[1] < num_heads * head_dim or tuple(out.shape) != (T, num_heads * head_dim):
+        raise KernelError(f"attention: q {tuple(q.shape)} / out {tuple(out.shape)} do not fit {num_heads} heads of {head_dim}")
+    if positions.shape[0] != T or seq_of_token.shape[0] != T:
+        raise KernelError("attention: positions and seq_of_token must have one entry per token")
+    _call("attention_generic", "spy_attention_generic", _ptr(q), ctypes.c_longlong(q.shape[1]), _ptr(out), _code(q, "attention queries"),
+          _ptr(pages), _code(pages, "cache pages"), _ptr(block_table), block_table.shape[1], page_size, num_pages, num_heads, nkv, head_dim,
+          _ptr(positions), _ptr(seq_of_token), T, int(window or 0), ctypes.c_float(scale), _ptr(status), _stream())
+    return out
+
+
+def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out[M, N] = a[M, K] @ w[N, K]^T`` on the CUDA cores in 32-bit, any sizes and dtypes."""
+    _check(a, "gemm input", ndim=2)
+    _check(w, "gemm weight", ndim=2)
+    _check(out, "gemm output", ndim=2)
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or tuple(out.shape) != (M, N):
+        raise KernelError(f"gemm: shapes do not fit: input {tuple(a.shape)}, weight {tuple(w.shape)}, output {tuple(out.shape)}")
+    _call("gemm_simt", "spy_gemm_simt", _ptr(a), _code(a, "gemm input"), ctypes.c_longlong(K), _ptr(w), _code(w, "gemm weight"),
+          ctypes.c_longlong(K), _ptr(out), _code(out, "gemm output"), ctypes.c_longlong(N), M, N, K, _stream())
+    return out
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]``; gate_up [T, 2I], out [T, I]."""
+    _check(gate_up, "swiglu input", ndim=2)
+    _check(out, "swiglu output", gate_up.dtype, 2)
+    T, two_i = gate_up.shape
+    if two_i % 2 != 0 or tuple(out.shape) != (T, two_i // 2):
+        raise KernelError(f"swiglu: input {tuple(gate_up.shape)} and output {tuple(out.shape)} do not fit")
+    _call("swiglu", "spy_swiglu", _ptr(gate_up), _ptr(out), _code(gate_up, "swiglu input"), T, two_i // 2, _stream())
+    return out
+
+
+def sample(logits: torch.Tensor, tokens: torch.Tensor, temperature: Optional[torch.Tensor] = None, seed: Optional[torch.Tensor] = None,
+           draw: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One token per row of ``logits [R, V]`` float32 into ``tokens [R]`` int32: argmax where the
+    row's temperature is 0 (or no temperatures are given), else a seeded draw from
+    ``softmax(logits / temperature)``."""
+    _check(logits, "logits", torch.float32, 2)
+    _check(tokens, "sampled tokens", torch.int32, 1)
+    R, V = logits.shape
+    if tokens.shape[0] != R:
+        raise KernelError("sample: one output token per row of logits is needed")
+    if temperature is not None:
+        _check(temperature, "temperatures", torch.float32, 1)
+        _check(seed, "seeds", torch.int64, 1)
+        _check(draw, "draw counters", torch.int64, 1)
+        if not (temperature.shape[0] == seed.shape[0] == draw.shape[0] == R):
+            raise KernelError("sample: temperature, seed and draw need one entry per row")
+    _call("sampling", "spy_sample", _ptr(logits), ctypes.c_longlong(V), R, V, _ptr(temperature), _ptr(seed), _ptr(draw), _ptr(tokens), _stream())
+    return tokens
+
+
+def tensor_core_gemm_takes(out_features: int, in_features: int) -> bool:
+    """Whether the tcgen05 kernel takes a weight of this shape (its rows must be 16-byte
+    aligned for TMA: ``in_features`` a multiple of 8)."""
+    return False

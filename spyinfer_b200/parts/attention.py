@@ -1,0 +1,89 @@
+"""Grouped-query softmax attention over the paged cache, with optional per-head q/k RMSNorm,
+a position encoding of its own, and an optional window.
+
+Order of operations (spymaster2h/spyinfer src/models/qwen3.hpp:136-213): q, k, v projections
+(fused into one matrix here), RMSNorm over head_dim on q and k with one shared weight each,
+position encoding on q and k, keys and values stored into the cache, attention, output
+projection.  kv head = head * nkv / nh, score = q.k / sqrt(head_dim), causal on absolute
+positions (src/backends/cpu/cpu_attention.cpp:59, :96, :100-110).  A windowed layer sees
+the last ``window`` keys, the query's own included.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .. import kernels
+from ..config.spec import PagedCacheNeed
+from ..weights.loader import WeightDecl
+from .base import Mixer
+from .linear import Linear
+from .registry import build_part, register_part
+
+
+@register_part("attention")
+class Attention(Mixer):
+    """params: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``, ``qk_norm_eps``
+    (None: no q/k norm), ``position`` (a PartSpec or None), ``window`` (None: all keys),
+    ``scale`` (None: 1/sqrt(head_dim)), ``prefix``."""
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.hidden = int(params["hidden_size"])
+        self.nh, self.nkv, self.hd = int(params["num_heads"]), int(params["num_kv_heads"]), int(params["head_dim"])
+        if self.nh % self.nkv:
+            raise ValueError(f"attention: {self.nh} heads do not group over {self.nkv} key/value heads")
+        if self.hd % 4 or self.hd > 512:
+            raise ValueError(f"attention: head_dim {self.hd} must be a multiple of 4 and at most 512")
+        self.qk_norm_eps = params.get("qk_norm_eps")
+        self.window = params.get("window")
+        if self.window is not None and int(self.window) <= 0:
+            raise ValueError(f"attention: window {self.window} must be positive")
+        self.scale = float(params["scale"]) if params.get("scale") is not None else 1.0 / math.sqrt(float(self.hd))
+        self.prefix = params.get("prefix", "")
+        pos = params.get("position")
+        self.position = build_part(pos, ctx) if pos is not None else None
+        self.qkv = self.o = self.q_norm = self.k_norm = self.rope_table = None
+
+    def weight_decls(self):
+        p, nh, nkv, hd, H = self.prefix, self.nh, self.nkv, self.hd, self.hidden
+        decls = [WeightDecl(p + "q_proj.weight", (nh * hd, H)), WeightDecl(p + "k_proj.weight", (nkv * hd, H)),
+                 WeightDecl(p + "v_proj.weight", (nkv * hd, H)), WeightDecl(p + "o_proj.weight", (H, nh * hd))]
+        if self.qk_norm_eps is not None:
+            decls += [WeightDecl(p + "q_norm.weight", (hd,), init="one_plus_normal"),
+                      WeightDecl(p + "k_norm.weight", (hd,), init="one_plus_normal")]
+        return decls
+
+    def bind(self, tensors):
+        p = self.prefix
+        qkv = [tensors[p + n] for n in ("q_proj.weight", "k_proj.weight", "v_proj.weight")]
+        if len({t.dtype for t in qkv}) > 1:
+            qkv = [t.float() for t in qkv]
+        self.qkv = Linear(torch.cat(qkv, dim=0).contiguous(), self.ctx.dtype)
+        self.o = Linear(tensors[p + "o_proj.weight"], self.ctx.dtype)
+        if self.qk_norm_eps is not None:
+            self.q_norm, self.k_norm = tensors[p + "q_norm.weight"], tensors[p + "k_norm.weight"]
+            if self.q_norm.dtype != self.k_norm.dtype:
+                self.q_norm, self.k_norm = self.q_norm.float(), self.k_norm.float()
+        if self.position is not None:
+            self.rope_table = self.position.rotation_table()
+
+    def modules(self):
+        mods = ["qk_rope_store", "attention_generic"] + self.qkv.modules() + self.o.modules()
+        if self.position is not None:
+            mods += self.position.modules()
+        return mods
+
+    def cache_need(self):
+        return PagedCacheNeed(self.nkv, self.hd, int(self.window) if self.window is not None else None)
+
+    def forward(self, x, batch, cache):
+        qkv = self.qkv(x)
+        kernels.qk_rope_store(qkv, self.nh, self.nkv, self.hd, self.q_norm, self.k_norm, float(self.qk_norm_eps or 0.0),
+                              self.rope_table, batch.positions, batch.seq_of_token, cache.block_table, cache.pages,
+                              store=cache.writes, status=batch.status)
+        out = torch.empty((x.shape[0], self.nh * self.hd), dtype=x.dtype, device=x.device)
+        kernels.attention_generic(qkv, self.nh, self.hd, out, cache.pages, cache.block_table, batch.positions, batch.seq_of_token,
+                                  self.scale, window=self.window, status=batch.status)
+        return self.o(out)

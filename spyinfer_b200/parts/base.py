@@ -1,0 +1,97 @@
+"""Interfaces of the parts a model is put together from.
+
+A part is built from its own sizes and constants (``params``) and a ``BuildContext``; it
+declares the tensors it needs by names relative to its layer's prefix, gets them bound, and
+then only computes.  No part knows which model it is in, which layer it is, or what other
+parts the model has.
+
+* ``Norm``: ``forward(x)`` and ``forward_add(residual, delta)`` (residual sum fused in).
+* ``PositionEncoding``: owned by a mixer; hands out what the mixer's kernel needs.
+* ``Mixer``: ``forward(x, batch, cache)``; declares what it keeps between steps through
+  ``cache_need()`` (pages of keys and values, a fixed-size state per request, or nothing).
+* ``FeedForward``: ``forward(x)``.
+* ``Block``: the arrangement of two norms, a mixer and a feed-forward around the residual
+  stream: ``forward(hidden, delta, batch, cache) -> (hidden, delta)``.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Dict, List, Optional, Sequence
+
+import torch
+
+from ..weights.loader import WeightDecl
+
+
+@dataclass
+class BuildContext:
+    """What every part is built with.  ``dtype`` is the storage type of activations and of
+    the cache: bfloat16 (the serving path) or float32 (everything in true 32-bit)."""
+
+    dtype: torch.dtype
+    device: torch.device
+    max_model_len: int
+
+
+class Part:
+    kind: str = ""
+    #: kernel modules (``csrc/<name>.cu``) this part launches; built before the first step
+    kernel_modules: Sequence[str] = ()
+
+    def __init__(self, params: Dict[str, Any], ctx: BuildContext):
+        self.params = params
+        self.ctx = ctx
+
+    def weight_decls(self) -> List[WeightDecl]:
+        """Tensors this part needs, named relative to its layer's prefix."""
+        return []
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        """Receives the declared tensors (same relative names), already on the device."""
+
+    def modules(self) -> List[str]:
+        return list(self.kernel_modules)
+
+
+class Norm(Part):
+    def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        raise NotImplementedError
+
+    def forward_add(self, residual: torch.Tensor, delta: Optional[torch.Tensor], rows: Optional[torch.Tensor] = None,
+                    out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """``residual += delta`` (32-bit, in place, skipped when ``delta`` is None), then the
+        norm of the sum.  With ``rows`` only those rows are normed and nothing is written back."""
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    def rotation_table(self) -> Optional[torch.Tensor]:
+        """For encodings that rotate pairs ``(j, j + r)`` of each head: float32 ``[positions, r, 2]``
+        of (cos, sin), which the fused q/k kernel applies; None for no rotation."""
+        return None
+
+
+class Mixer(Part):
+    def cache_need(self):
+        """A ``PagedCacheNeed``, a ``StateCacheNeed`` or None."""
+        return None
+
+    def forward(self, x: torch.Tensor, batch, cache) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Block:
+    kind: str = ""
+
+    def __init__(self, mixer_norm: Norm, mixer: Mixer, ffn_norm: Norm, feed_forward: FeedForward):
+        self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward = mixer_norm, mixer, ffn_norm, feed_forward
+
+    def forward(self, hidden: torch.Tensor, delta: Optional[torch.Tensor], batch, cache):
+        """``hidden`` is the 32-bit residual stream; ``delta`` the previous block's output
+        that is still to be added to it (None for the first).  Returns the same pair."""
+        raise NotImplementedError

@@ -1,0 +1,51 @@
+"""Dense gated feed-forward: ``down(act(gate(x)) * up(x))``, no biases.
+
+spymaster2h/spyinfer src/models/qwen3.hpp:233-263 with SiLU as the activation (SwiGLU:
+src/backends/cpu/x64/kernels.cpp:242-247).  The gate and up projections are fused into one
+matrix at load, so one product feeds the activation kernel.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from ..weights.loader import WeightDecl
+from .base import FeedForward
+from .linear import Linear
+from .registry import register_part
+
+
+@register_part("gated_mlp")
+class GatedMLP(FeedForward):
+    """params: ``hidden_size``, ``intermediate_size``, ``activation`` ("silu"), ``prefix``."""
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.hidden, self.inter = int(params["hidden_size"]), int(params["intermediate_size"])
+        if params.get("activation", "silu") != "silu":
+            raise ValueError(f"gated_mlp: activation {params['activation']!r} is not implemented (only \"silu\")")
+        self.prefix = params.get("prefix", "")
+        self.gate_up = self.down = None
+
+    def weight_decls(self):
+        p = self.prefix
+        return [WeightDecl(p + "gate_proj.weight", (self.inter, self.hidden)),
+                WeightDecl(p + "up_proj.weight", (self.inter, self.hidden)),
+                WeightDecl(p + "down_proj.weight", (self.hidden, self.inter))]
+
+    def bind(self, tensors):
+        p = self.prefix
+        gate, up = tensors[p + "gate_proj.weight"], tensors[p + "up_proj.weight"]
+        if gate.dtype != up.dtype:
+            gate, up = gate.float(), up.float()
+        self.gate_up = Linear(torch.cat([gate, up], dim=0).contiguous(), self.ctx.dtype)
+        self.down = Linear(tensors[p + "down_proj.weight"], self.ctx.dtype)
+
+    def modules(self):
+        return ["swiglu"] + self.gate_up.modules() + self.down.modules()
+
+    def forward(self, x):
+        gu = self.gate_up(x)
+        z = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
+        kernels.swiglu(gu, z)
+        return self.down(z)

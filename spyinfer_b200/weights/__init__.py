@@ -1,0 +1,7 @@
+"""Weights: the safetensors container, binding by tensor name, and seeded random models."""
+from .loader import WeightDecl, WeightError, load_checkpoint
+from .random_init import random_tensor, random_tensors, write_model_folder
+from .safetensors_io import SafetensorsError, SafetensorsFile, shard_paths, write_safetensors
+
+__all__ = ["WeightDecl", "WeightError", "load_checkpoint", "random_tensor", "random_tensors", "write_model_folder",
+           "SafetensorsError", "SafetensorsFile", "shard_paths", "write_safetensors"]

@@ -1,0 +1,152 @@
+"""The cache manager on the host: pages, block tables, groups, windows, state slots."""
+import random
+
+import pytest
+
+from spyinfer_b200.cache import CacheManager, NoFreeSlot, OutOfPages, PagePool
+from spyinfer_b200.config import PagedCacheNeed, StateCacheNeed
+
+FULL = PagedCacheNeed(2, 16, None)
+WIN = PagedCacheNeed(2, 16, 10)
+
+
+def manager(needs=(FULL, FULL), page_size=4, num_pages=12, max_num_seqs=4, max_model_len=64, cache_of=None):
+    return CacheManager(list(needs), page_size, num_pages, max_num_seqs, max_model_len, device=None, cache_of=cache_of)
+
+
+def test_page_pool_is_lifo_and_refuses_double_free():
+    p = PagePool(3)
+    a, b = p.allocate(), p.allocate()
+    assert (a, b) == (0, 1)
+    p.free(a)
+    assert p.allocate() == a            # the page just given back is the next one handed out
+    p.free(b)
+    with pytest.raises(ValueError):
+        p.free(b)
+    with pytest.raises(ValueError):
+        p.free(7)
+    p.allocate(), p.allocate()
+    with pytest.raises(OutOfPages):
+        p.allocate()
+
+
+def test_equal_needs_share_a_group_and_different_needs_do_not():
+    m = manager(needs=(WIN, FULL, WIN, FULL, None, StateCacheNeed((3, 5))))
+    assert m.num_groups() == 2
+    assert [m.view(i).group for i in range(4)] == [0, 1, 0, 1]
+    assert m.view(0).window == 10 and m.view(1).window is None
+    assert m.view(4).kind == "none" and m.view(5).kind == "state"
+
+
+def test_reserve_commit_free_and_block_table():
+    m = manager()
+    m.add_request("a")
+    m.reserve("a", 9)                    # 3 pages of 4
+    assert list(m.block_table("a")[:4]) == [0, 1, 2, -1] and m.num_free_pages() == 9
+    m.commit("a", 9)
+    m.reserve("a", 12)                   # still 3 pages
+    assert m.num_free_pages() == 9
+    m.reserve("a", 13)
+    assert m.block_table("a")[3] == 3
+    m.commit("a", 13)
+    with pytest.raises(ValueError):
+        m.commit("a", 20)                # more than has pages
+    m.check_invariants()
+    m.free_request("a")
+    assert m.num_free_pages() == 12 and not m.has_request("a")
+    m.check_invariants()
+    m.add_request("b")
+    m.reserve("b", 4)
+    assert m.block_table("b")[0] == 3    # the page freed last is used again first
+
+
+def test_reserve_is_all_or_nothing():
+    m = manager(num_pages=3)
+    m.add_request("a")
+    m.reserve("a", 8)
+    m.add_request("b")
+    assert not m.can_reserve("b", 8) and m.can_reserve("b", 4)
+    with pytest.raises(OutOfPages):
+        m.reserve("b", 8)
+    assert m.num_free_pages() == 1 and list(m.block_table("b")[:2]) == [-1, -1]
+    with pytest.raises(ValueError):
+        m.reserve("a", 65)               # beyond max_model_len
+    m.check_invariants()
+
+
+def test_window_gives_pages_back_as_it_passes_them():
+    m = manager(needs=(WIN, FULL), num_pages=16)
+    m.add_request("a")
+    m.reserve("a", 30)
+    m.commit("a", 30)
+    win_table, full_table = m.block_table("a", 0), m.block_table("a", 1)
+    # a query at position 30 sees keys 21..30: pages 0..4 (positions 0..19) are behind the window
+    assert [int(x >= 0) for x in win_table[:8]] == [0, 0, 0, 0, 0, 1, 1, 1]
+    assert all(x >= 0 for x in full_table[:8])
+    assert m.num_free_pages(0) == 16 - 3 and m.num_free_pages(1) == 16 - 8
+    m.check_invariants()
+    for n in range(31, 45):
+        m.reserve("a", n)
+        m.commit("a", n)
+        lo_page = max(0, n - 10 + 1) // 4
+        assert all(x < 0 for x in win_table[:lo_page]) and all(x >= 0 for x in win_table[lo_page:(n + 3) // 4])
+    m.check_invariants()
+    m.free_request("a")
+    assert m.num_free_pages(0) == 16 and m.num_free_pages(1) == 16
+
+
+def test_state_slots():
+    m = manager(max_num_seqs=2)
+    s0, s1 = m.add_request("a"), m.add_request("b")
+    assert {s0, s1} == {0, 1}
+    with pytest.raises(NoFreeSlot):
+        m.add_request("c")
+    with pytest.raises(ValueError):
+        m.add_request("a")
+    m.free_request("a")
+    assert m.add_request("c") == s0
+    m.check_invariants()
+
+
+def test_entry_reading_another_entrys_cache():
+    m = manager(needs=(FULL, FULL, FULL), cache_of=[None, None, 0])
+    assert m.num_groups() == 1 and len(m.groups[0].entries) == 2
+    assert m.view(2).writes is False and m.view(2).group == m.view(0).group and m.view(0).writes
+
+
+@pytest.mark.parametrize("seed", range(5))
+def test_random_orders_lose_no_page(seed):
+    rng = random.Random(seed)
+    m = manager(needs=(WIN, FULL, WIN), page_size=4, num_pages=20, max_num_seqs=5, max_model_len=60)
+    lengths = {}
+    for it in range(600):
+        op = rng.random()
+        if op < 0.25 and len(lengths) < 5:
+            rid = f"r{it}"
+            m.add_request(rid)
+            lengths[rid] = 0
+        elif op < 0.85 and lengths:
+            rid = rng.choice(list(lengths))
+            n = lengths[rid] + rng.choice([1, 1, 1, 2, 5, 9])
+            if n <= 60 and m.can_reserve(rid, n):
+                m.reserve(rid, n)
+                if rng.random() < 0.9:
+                    m.commit(rid, n)
+                    lengths[rid] = n
+            elif n <= 60:
+                with pytest.raises(OutOfPages):
+                    m.reserve(rid, n)
+        elif lengths:
+            rid = rng.choice(list(lengths))
+            m.free_request(rid)
+            del lengths[rid]
+            with pytest.raises(KeyError):
+                m.free_request(rid)      # freeing twice is an error, not a silent double free
+        m.check_invariants()
+        for rid, n in lengths.items():
+            assert m.length(rid) == n
+            full = m.block_table(rid, 1)
+            assert all(full[i] >= 0 for i in range((n + 3) // 4))
+    for rid in list(lengths):
+        m.free_request(rid)
+    assert m.num_free_pages(0) == 20 and m.num_free_pages(1) == 20 and m.num_free_slots() == 5

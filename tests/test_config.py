@@ -1,0 +1,100 @@
+"""Typed configuration and the architecture registry."""
+import copy
+import json
+
+import pytest
+
+from conftest import TINY
+from spyinfer_b200.config import (ConfigError, EngineConfig, Qwen3Config, config_from_json, known_architectures, load_model_config)
+
+
+def test_registry_maps_name_to_config():
+    assert "Qwen3ForCausalLM" in known_architectures()
+    cfg = config_from_json(TINY["b"]["config"])
+    assert isinstance(cfg, Qwen3Config)
+    assert (cfg.hidden_size, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim) == (96, 8, 2, 32)
+    assert cfg.rms_norm_eps == 1e-5 and cfg.rope_theta == 1e6 and cfg.tie_word_embeddings is False
+
+
+def test_unknown_architecture_lists_known_ones():
+    data = dict(TINY["a"]["config"], architectures=["LlamaForCausalLM"])
+    with pytest.raises(ConfigError) as e:
+        config_from_json(data)
+    assert "LlamaForCausalLM" in str(e.value) and "Qwen3ForCausalLM" in str(e.value)
+    with pytest.raises(ConfigError):
+        config_from_json({k: v for k, v in data.items() if k != "architectures"})
+
+
+def test_defaults_follow_the_reference():
+    data = {k: v for k, v in TINY["a"]["config"].items() if k not in ("head_dim", "rope_theta", "rms_norm_eps", "tie_word_embeddings",
+                                                                     "max_position_embeddings")}
+    cfg = config_from_json(data)
+    assert cfg.head_dim == 64 // 4 and cfg.rope_theta == 1e6 and cfg.rms_norm_eps == 1e-6
+    assert cfg.tie_word_embeddings is False and cfg.max_position_embeddings == 16384
+
+
+@pytest.mark.parametrize("key", ["model_type", "hidden_act", "hidden_size", "intermediate_size", "num_hidden_layers",
+                                 "num_attention_heads", "num_key_value_heads", "vocab_size"])
+def test_missing_keys_are_named(key):
+    data = {k: v for k, v in TINY["a"]["config"].items() if k != key}
+    with pytest.raises(ConfigError) as e:
+        config_from_json(data)
+    assert key in str(e.value)
+
+
+@pytest.mark.parametrize("patch", [{"num_key_value_heads": 3}, {"hidden_act": "gelu"}, {"rope_scaling": {"type": "yarn"}},
+                                   {"attention_bias": True}, {"head_dim": 15}, {"vocab_size": -1},
+                                   {"use_sliding_window": True, "sliding_window": None},
+                                   {"use_sliding_window": True, "sliding_window": 8, "layer_types": ["full_attention"]}])
+def test_values_the_engine_cannot_run_are_refused(patch):
+    with pytest.raises(ConfigError):
+        config_from_json(dict(TINY["a"]["config"], **patch))
+
+
+def test_spec_is_data_layer_by_layer():
+    spec = config_from_json(TINY["c"]["config"]).to_spec()
+    assert len(spec.layers) == 4 and [e.layer for e in spec.run_order] == [0, 1, 2, 3]
+    windows = [l.mixer.params["window"] for l in spec.layers]
+    assert windows == [40, None, 40, None]
+    m = spec.layers[0].mixer.params
+    assert (m["num_heads"], m["num_kv_heads"], m["head_dim"], m["qk_norm_eps"]) == (6, 3, 48, 3e-6)
+    assert m["position"].kind == "rotary_half" and m["position"].params == {"theta": 50000.0, "rotary_dim": 48}
+    assert spec.layers[1].feed_forward.params["intermediate_size"] == 200
+    assert spec.head.params["tied"] is False and spec.vocab_size == 517
+    # a window key without use_sliding_window changes nothing
+    plain = dict(TINY["c"]["config"], use_sliding_window=False)
+    assert [l.mixer.params["window"] for l in config_from_json(plain).to_spec().layers] == [None] * 4
+
+
+def test_config_round_trips_through_json(tmp_path):
+    cfg = config_from_json(TINY["c"]["config"])
+    with open(tmp_path / "config.json", "w") as f:
+        json.dump(cfg.to_json(), f)
+    again = load_model_config(str(tmp_path))
+    assert again.to_json() == cfg.to_json()
+    with pytest.raises(ConfigError):
+        load_model_config(str(tmp_path / "nowhere"))
+
+
+def test_run_order_is_checked():
+    from spyinfer_b200.config import RunEntry
+    spec = config_from_json(TINY["a"]["config"]).to_spec()
+    spec.run_order = [RunEntry(0), RunEntry(1), RunEntry(1, cache_of=1), RunEntry(0)]
+    spec.validate()
+    bad = copy.copy(spec)
+    bad.run_order = [RunEntry(0, cache_of=0)]
+    with pytest.raises(ValueError):
+        bad.validate()
+    bad.run_order = [RunEntry(5)]
+    with pytest.raises(ValueError):
+        bad.validate()
+
+
+def test_engine_config_names_and_checks():
+    c = EngineConfig(max_num_batched_tokens=64, max_num_seqs=4, max_model_len=100, kvcache_block_size=8, num_kvcache_blocks=10, dtype="fp32")
+    assert c.dtype == "float32"
+    c.clamp_to_model(50)
+    assert c.max_model_len == 50
+    for bad in (dict(dtype="float16"), dict(kvcache_block_size=0), dict(num_kvcache_blocks=0), dict(gpu_memory_utilization=0.0)):
+        with pytest.raises(ValueError):
+            EngineConfig(**bad)
