@@ -1,0 +1,283 @@
+#!/usr/bin/env python3
+"""Benchmark of the engine's decode step and prefill on one GPU.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--batch B] [--context C] [--impl ours|reference]
+
+The model has the layer sizes of Qwen3-8B (36 layers, hidden 4096, 32 query heads, 8 key/value
+heads, head size 128, intermediate 12288, vocabulary 151936, untied head) with seeded random
+weights in bfloat16.  A "step" is one decode step of a batch of 8 requests at a context of
+8192 tokens: the step function on the live batch plus device-side sampling.  The requests'
+caches are filled with random keys and values of that length (the step's work does not depend
+on their content), so no prefill is timed.  One JSON line is printed:
+
+* ``value``: decoded tokens a second, timed with CUDA events around K steps after W warm-up
+  steps; between steps the inputs (weights + cache, > 20 GB) are far larger than L2;
+* ``e2e``: the same through the Python entry point ``LLMEngine.step()``: every step copies
+  that step's batch arrays from pinned host memory and reads the sampled tokens back;
+* ``prefill``: one step of 2048 prompt tokens of one request; ``frac`` = flops / time / peak;
+* ``roofline``: bytes the decode step has to read (every weight it uses once, and the cache
+  of the live requests) / its time, against the measured copy bandwidth;
+* ``points``: decoding at batch 1 and 64 (same context), and at the context of about 640
+  tokens that the reference workload "prompts of 512, 256 generated tokens" averages;
+* ``clocks``: SM clocks and throttle reasons sampled with nvidia-smi during the timed region.
+
+Peaks come from MEASURED_PEAKS.json beside this file when it exists, else 6.65 TB/s and
+1.59 PFLOP/s.  ``--gpus N`` with N > 1 prints one line saying that this engine is
+single-GPU and exits with 2.  ``--impl reference`` prints why the reference cannot run here.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+QWEN3_8B = {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "hidden_act": "silu", "num_hidden_layers": 36,
+            "hidden_size": 4096, "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 12288,
+            "vocab_size": 151936, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": False,
+            "max_position_embeddings": 40960, "eos_token_id": 151645}
+REFERENCE_UNAVAILABLE = ("spymaster2h/spyinfer is a C++/xmake project without a Python package: pip cannot install it offline "
+                         "(no setup.py or pyproject.toml), xmake is not in the image, and its CUDA path cannot hold a step of 100 or "
+                         "more tokens or a cache of more than 400 tokens")
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    hbm, flops, src = 6650.0, 1590.0, "fallback"
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                d = json.load(f)
+            hbm = float(d.get("hbm_gbs", hbm))
+            flops = float(d.get("bf16_tflops", flops))
+            src = "measured"
+        except (ValueError, OSError):
+            pass
+    return hbm, flops, src
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int = 0):
+        self.samples, self.proc, self.index = [], None, index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) == 6:
+                self.samples.append(parts)
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm = sorted(int(s[0]) for s in self.samples if s[0].isdigit())
+        mx = [int(s[1]) for s in self.samples if s[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for s in self.samples for n, v in zip(names, s[2:]) if v.lower().startswith("active")})
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
+                "samples": len(self.samples)}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the model has (both numbers are reported)")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=8192)
+    ap.add_argument("--prefill-tokens", type=int, default=2048)
+    ap.add_argument("--no-points", action="store_true", help="skip the batch 1/64 and short-context points")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
+        return 0
+    if args.gpus != 1:
+        print(json.dumps({"error": f"this engine runs on one GPU; --gpus {args.gpus} is not supported", "n_gpus": args.gpus}))
+        return 2
+    warmup = max(3, args.warmup)
+
+    import torch
+
+    from spyinfer_b200 import SamplingParams, config_from_json, kernels
+    from spyinfer_b200.engine import LLMEngine, StepEntry
+
+    hbm_gbs, bf16_tflops, peak_src = peaks()
+    cfg_json = dict(QWEN3_8B)
+    full_layers = cfg_json["num_hidden_layers"]
+    layers = args.layers or full_layers
+    cfg_json["num_hidden_layers"] = layers
+    model_config = config_from_json(cfg_json)
+    page = 16
+    max_batch = max(args.batch, 1 if args.no_points else 64)
+    ctx = args.context
+    total_steps = warmup + args.steps + 8
+    pages_per_req = (ctx + page - 1) // page + 1
+    num_pages = max_batch * pages_per_req + (args.prefill_tokens + page - 1) // page + 8
+    torch.cuda.set_device(0)
+    engine = LLMEngine(model_config=model_config, seed=0, dtype="bfloat16", max_num_seqs=max_batch, max_model_len=ctx + 16,
+                       kvcache_block_size=page, num_kvcache_blocks=num_pages, max_num_batched_tokens=max(args.prefill_tokens, max_batch))
+    runner, cache = engine.runner, engine.runner.cache
+    for g in cache.groups:                      # random cache contents: the decode step's work does not depend on them
+        g.pages.normal_(0.0, 1.0)
+    c = model_config
+    H, I, V, nh, nkv, hd = c.hidden_size, c.intermediate_size, c.vocab_size, c.num_attention_heads, c.num_key_value_heads, c.head_dim
+    layer_params = H * (nh + 2 * nkv) * hd + nh * hd * H + 3 * H * I
+    weight_bytes = 2 * (layers * layer_params + V * H)
+    kv_bytes_per_token = 2 * 2 * nkv * hd * layers
+    vocab = V
+
+    def fake_requests(batch, context, tag):
+        """Live requests whose caches hold ``context`` tokens (random content)."""
+        rids = [f"{tag}{i}" for i in range(batch)]
+        for r in rids:
+            cache.add_request(r)
+            cache.reserve(r, context)
+            cache.commit(r, context)
+        return rids
+
+    def release(rids):
+        for r in rids:
+            runner.finish(r)
+
+    def decode_device(batch, context, steps, warm):
+        """Tokens a second of `steps` decode steps timed on the device."""
+        start_ctx = context - (steps + warm) - 1
+        rids = fake_requests(batch, start_ctx, "d")
+        g = torch.Generator().manual_seed(batch)
+        toks = torch.randint(0, vocab, (steps + warm, batch), generator=g).tolist()
+        sp = [SamplingParams()] * batch
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        launches0 = 0
+        for i in range(steps + warm):
+            if i == warm:
+                torch.cuda.synchronize()
+                launches0 = kernels.launch_count()
+                e0.record()
+            logits = runner.step([StepEntry(r, [toks[i][j]], [0]) for j, r in enumerate(rids)])
+            engine.sampler.sample(logits, sp, [i] * batch)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        runner.check_status()
+        release(rids)
+        return batch * steps / (ms / 1e3), ms / steps, kernels.launch_count() - launches0
+
+    def decode_e2e(batch, context, steps, warm):
+        """The same through LLMEngine.step(): host tokens in, host tokens out, every step."""
+        start_ctx = context - (steps + warm) - 2
+        g = torch.Generator().manual_seed(1000 + batch)
+        sp = SamplingParams(max_new_tokens=steps + warm + 1, ignore_eos=True)
+        ids = []
+        for j in range(batch):
+            # the request's cache is filled directly; the engine sees a request whose prompt is already computed but for its last token
+            prompt = torch.randint(0, vocab, (start_ctx + 1,), generator=g).tolist()
+            rid = engine.add_request(prompt, sp)
+            seq = engine.scheduler.waiting.pop()
+            cache.add_request(rid)
+            cache.reserve(rid, start_ctx)
+            cache.commit(rid, start_ctx)
+            seq.num_computed = start_ctx
+            seq.status = type(seq.status).RUNNING
+            engine.scheduler.running.append(seq)
+            ids.append(rid)
+        n_out = 0
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for i in range(steps + warm):
+            if i == warm:
+                torch.cuda.synchronize()
+                e0.record()
+                n_out = 0
+            n_out += len(engine.step())
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        for r in ids:
+            engine.remove_request(r)
+        assert n_out == batch * steps, (n_out, batch, steps)
+        h2d = 4 * (4 * batch + 3 * batch + 1 + batch * cache.width)
+        return n_out / (ms / 1e3), h2d, 4 * batch
+
+    def prefill(tokens):
+        g = torch.Generator().manual_seed(7)
+        toks = torch.randint(0, vocab, (tokens,), generator=g).tolist()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        times = []
+        for i in range(3):                       # the first run is a warm-up
+            torch.cuda.synchronize()
+            e0.record()
+            runner.step([StepEntry(f"p{i}", toks, [tokens - 1])])
+            e1.record()
+            torch.cuda.synchronize()
+            runner.finish(f"p{i}")
+            times.append(e0.elapsed_time(e1))
+        best = min(times[1:])
+        runner.check_status()
+        flops = 2.0 * tokens * layers * layer_params + 2.0 * V * H + layers * 4.0 * nh * hd * tokens * (tokens + 1) / 2
+        return {"value": round(tokens / (best / 1e3), 1), "tokens": tokens, "ms": round(best, 3),
+                "frac": round(flops / (best / 1e3) / (bf16_tflops * 1e12), 4)}
+
+    with ClockSampler() as clocks:
+        value, ms_per_step, launches = decode_device(args.batch, ctx, args.steps, warmup)
+    clock_summary = clocks.summary()
+    step_bytes = weight_bytes + kv_bytes_per_token * (ctx - args.steps // 2) * args.batch
+    achieved = step_bytes / (ms_per_step / 1e3) / 1e9
+    out = {
+        "metric": "decode tokens/s (Qwen3-8B shape, bf16, batch 8, context 8192)", "value": round(value, 1), "unit": "tokens/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: seeded random weights, random token ids, random cache contents of the stated context length",
+        "config": {"model": "Qwen3-8B shape", "num_layers": layers, "num_layers_full": full_layers, "hidden_size": H,
+                   "num_attention_heads": nh, "num_key_value_heads": nkv, "head_dim": hd, "intermediate_size": I, "vocab_size": V,
+                   "global_batch": args.batch, "seq_len": ctx, "page_size": page, "parallelism": "single GPU",
+                   "l2": "inputs (weights and cache) exceed L2 many times", "peaks": peak_src},
+        "gpu_launches": launches,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_gbs, "unit": "GB/s", "frac": round(achieved / hbm_gbs, 4)},
+        "clocks": clock_summary,
+    }
+    out["prefill"] = prefill(args.prefill_tokens)
+    if not args.no_e2e:
+        e2e, h2d, d2h = decode_e2e(args.batch, ctx, args.steps, warmup)
+        out["e2e"] = {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+    if not args.no_points:
+        points = {}
+        for b in (1, 64):
+            points[f"decode_b{b}"] = round(decode_device(b, ctx, args.steps, warmup)[0], 1)
+        for b in (1, 8, 64):
+            points[f"decode_b{b}_ctx640"] = round(decode_device(b, 640 + (args.steps + warmup) // 2, args.steps, warmup)[0], 1)
+        out["points"] = points
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -58,7 +58,23 @@ def _stream():
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """How many kernel launches this process has made through this module (a replayed CUDA
+    graph counts the launches it holds)."""
+    return _launches
+
+
+def count_launches(n: int) -> None:
+    global _launches
+    _launches += n
+
+
 def _call(module: str, fn: str, *args) -> None:
+    global _launches
+    _launches += 1
     lib = build.load(module)
     f = getattr(lib, fn)
     f.restype = ctypes.c_int

@@ -1,0 +1,140 @@
+"""Generation through the Python entry point against the plain implementation: greedy
+tokens, long decoding, the first tokens of a sequence, continuous batching with a pool so
+small that requests are preempted and recomputed, and seeded temperature sampling."""
+import numpy as np
+import pytest
+import torch
+
+import plain_model
+
+pytestmark = pytest.mark.gpu
+
+
+def engine_for(folder, dtype, **kw):
+    from spyinfer_b200 import LLMEngine
+    opts = dict(dtype=dtype, max_num_seqs=4, max_model_len=512, kvcache_block_size=16, num_kvcache_blocks=64, max_num_batched_tokens=64)
+    opts.update(kw)
+    return LLMEngine(folder, **opts)
+
+
+def check_greedy(weights, cfg, prompt, out, dtype):
+    """Every generated token is the plain implementation's argmax given the same history, or
+    a token whose plain logit is within the dtype's reach of the best one."""
+    seq = list(prompt)
+    for i, tok in enumerate(out):
+        logits = plain_model.forward_logits(weights, cfg, seq)[-1]
+        best = logits.max().item()
+        limit = 1e-4 * max(1.0, logits.abs().max().item()) if dtype == "float32" else 0.05 * logits.abs().max().item()
+        assert logits[tok].item() >= best - limit, f"token {i}: engine chose {tok}, plain argmax {int(logits.argmax())}"
+        seq.append(tok)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["a", "b", "c"])
+def test_greedy_generation_matches_plain(name, dtype, tiny_models):
+    from spyinfer_b200 import SamplingParams
+    folder, cfg, weights = tiny_models[name]
+    rng = np.random.default_rng(5)
+    prompts = [rng.integers(0, cfg["vocab_size"], n).tolist() for n in (1, 5, 9, 13, 31)]
+    engine = engine_for(folder, dtype)
+    outs = engine.generate(prompts, SamplingParams(max_new_tokens=12, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        assert len(o) == 12
+        check_greedy(weights, cfg, p, o, dtype)
+    assert engine.runner.cache.min_free_pages() == 64 and engine.runner.cache.num_free_slots() == 4
+    engine.runner.cache.check_invariants()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_first_tokens_and_long_decoding(dtype, tiny_models):
+    """A one-token prompt (the very first positions of a sequence), decoded for 200 tokens:
+    across many pages and, in model c, far past its window of 40."""
+    from spyinfer_b200 import SamplingParams
+    folder, cfg, weights = tiny_models["c"]
+    engine = engine_for(folder, dtype)
+    out = engine.generate([[7]], SamplingParams(max_new_tokens=200, ignore_eos=True))[0]
+    assert len(out) == 200
+    # checking all 200 steps with the plain implementation is quadratic; check the first 24 and every 16th after
+    seq = [7]
+    for i, tok in enumerate(out):
+        if i < 24 or i % 16 == 0 or i == 199:
+            check_greedy(weights, cfg, seq, [tok], dtype)
+        seq.append(tok)
+
+
+def test_small_pool_preempts_and_still_gives_the_same_tokens(tiny_models):
+    from spyinfer_b200 import SamplingParams
+    folder, cfg, weights = tiny_models["b"]
+    rng = np.random.default_rng(9)
+    prompts = [rng.integers(0, cfg["vocab_size"], n).tolist() for n in (20, 33, 7, 40, 12, 25)]
+    sp = SamplingParams(max_new_tokens=30, ignore_eos=True)
+    roomy = engine_for(folder, "float32", num_kvcache_blocks=64)
+    want = roomy.generate(prompts, sp)
+    del roomy
+    tight = engine_for(folder, "float32", num_kvcache_blocks=9, max_num_batched_tokens=24)   # 144 tokens of cache for 6 requests of up to 70
+    got = tight.generate(prompts, sp)
+    assert tight.scheduler.num_preemptions > 0, "the pool was meant to be too small"
+    assert got == want
+    tight.runner.cache.check_invariants()
+    assert tight.runner.cache.min_free_pages() == 9
+
+
+def test_eos_and_max_model_len_finish_requests(tiny_models):
+    from spyinfer_b200 import SamplingParams
+    folder, cfg, weights = tiny_models["a"]
+    engine = engine_for(folder, "float32", max_model_len=24)
+    prompt = [3, 9, 27, 81]
+    free_run = engine.generate([prompt], SamplingParams(max_new_tokens=10, ignore_eos=True))[0]
+    # make the third generated token the end-of-sequence token
+    engine.eos_token_id = free_run[2]
+    rid = engine.add_request(prompt, SamplingParams(max_new_tokens=10))
+    while not engine.is_request_finished(rid):
+        engine.step()
+    first_eos = free_run.index(free_run[2])
+    assert engine.get_generated_tokens(rid) == free_run[:first_eos + 1] and engine.finish_reason(rid) == "eos"
+    assert engine.get_output_tokens(rid) == prompt + free_run[:first_eos + 1]
+    engine.remove_request(rid)
+    engine.eos_token_id = -1
+    rid = engine.add_request(prompt, SamplingParams(ignore_eos=True))
+    while engine.has_unfinished_requests():
+        engine.step()
+    assert engine.finish_reason(rid) == "max_model_len" and len(engine.get_output_tokens(rid)) == 24
+    with pytest.raises(ValueError):
+        engine.add_request(list(range(24)))          # no room to generate
+    with pytest.raises(ValueError):
+        engine.add_request([cfg["vocab_size"]])      # outside the vocabulary
+
+
+def test_temperature_sampling_is_seeded_and_follows_the_distribution(tiny_models):
+    from spyinfer_b200 import SamplingParams
+    folder, cfg, weights = tiny_models["a"]
+    engine = engine_for(folder, "float32", max_num_seqs=64, num_kvcache_blocks=128, max_num_batched_tokens=512)
+    prompt = [11, 22, 33]
+    a = engine.generate([prompt] * 3, [SamplingParams(temperature=0.9, seed=s, max_new_tokens=8, ignore_eos=True) for s in (1, 1, 2)])
+    assert a[0] == a[1] and a[0] != a[2]
+    # the first generated token over many seeds follows softmax(logits / T) of the plain implementation
+    n, temp = 4000, 1.5
+    firsts = []
+    for lo in range(0, n, 50):
+        outs = engine.generate([prompt] * 50, [SamplingParams(temperature=temp, seed=s, max_new_tokens=1, ignore_eos=True) for s in range(lo, lo + 50)])
+        firsts += [o[0] for o in outs]
+    p = plain_model.softmax_probabilities(plain_model.forward_logits(weights, cfg, prompt)[-1], temp).numpy()
+    freq = np.bincount(firsts, minlength=cfg["vocab_size"]) / n
+    assert np.abs(freq - p).max() < 4 * np.sqrt(p.max() / n) + 2e-3
+
+
+def test_command_line_generates(tiny_models):
+    import os, subprocess, sys
+    folder, cfg, weights = tiny_models["a"]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, os.path.join(root, "bin", "spyinfer"), "-m", folder, "--dtype", "float32", "--prompt-tokens", "5,6,7",
+           "--max-new-tokens", "5", "--ignore-eos", "--max-model-len", "64", "--num-kvcache-blocks", "8", "--stats"]
+    proc = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    lines = proc.stdout.strip().splitlines()
+    tokens = [int(t) for t in lines[1].split()]
+    assert len(tokens) == 5
+    check_greedy(weights, cfg, [5, 6, 7], tokens, "float32")
+    assert "steps" in lines[-1]
+    bad = subprocess.run([sys.executable, os.path.join(root, "bin", "spyinfer"), "-m", folder, "-b", "cpu"], capture_output=True, text=True)
+    assert bad.returncode == 1 and "Invalid backend type" in bad.stderr

@@ -1,0 +1,263 @@
+"""Each CUDA kernel alone against a plain PyTorch float32 statement of the same operation,
+at sizes other than the engine's tiny models (odd widths, head sizes in steps of 16, several
+group sizes, vocabularies that are no power of two)."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def tol(dtype):
+    return dict(rtol=2e-2, atol=2e-2) if dtype == torch.bfloat16 else dict(rtol=2e-5, atol=2e-5)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,H,V", [(1, 16, 7), (37, 200, 1001), (5, 4096, 333)])
+def test_embedding(dtype, T, H, V):
+    from spyinfer_b200 import kernels
+    table = torch.randn(V, H, device=DEV).to(dtype)
+    ids = torch.randint(0, V, (T,), device=DEV, dtype=torch.int32)
+    out = torch.empty(T, H, device=DEV)
+    status = torch.zeros(2, dtype=torch.int32, device=DEV)
+    kernels.embedding(table, ids, out, status)
+    assert torch.equal(out, table.float()[ids.long()]) and status[0].item() == 0
+    ids[T // 2] = V  # outside the vocabulary: reported, not read
+    kernels.embedding(table, ids, out, status)
+    assert status.tolist() == [1, T // 2]
+
+
+@pytest.mark.parametrize("xd,dd,wd,od", [(torch.float32, torch.float32, torch.float32, torch.float32),
+                                         (torch.float32, torch.bfloat16, torch.bfloat16, torch.bfloat16),
+                                         (torch.bfloat16, torch.bfloat16, torch.float32, torch.float32)])
+@pytest.mark.parametrize("n,H,eps", [(1, 64, 1e-6), (19, 1000, 1e-5), (3, 5120, 1e-6), (2, 15000, 1e-3)])
+def test_rmsnorm_with_residual_and_gather(xd, dd, wd, od, n, H, eps):
+    from spyinfer_b200 import kernels
+    x = (torch.randn(n, H, device=DEV) * 3).to(xd)
+    delta = torch.randn(n, H, device=DEV).to(dd)
+    w = (1 + 0.1 * torch.randn(H, device=DEV)).to(wd)
+
+    def ref(v):
+        return v * torch.rsqrt((v * v).mean(-1, keepdim=True) + eps) * w.float()
+
+    out = torch.empty(n, H, device=DEV, dtype=od)
+    kernels.rmsnorm(x, w, eps, out)
+    torch.testing.assert_close(out.float(), ref(x.float()).to(od).float(), **tol(od))
+    x2 = x.clone()
+    kernels.rmsnorm(x2, w, eps, out, delta=delta, write_back=True)
+    s = x.float() + delta.float()
+    torch.testing.assert_close(out.float(), ref(s).to(od).float(), **tol(od))
+    torch.testing.assert_close(x2.float(), s.to(xd).float(), rtol=0, atol=0)       # the residual sum is exact in 32-bit
+    rows = torch.tensor([n - 1, 0, n - 1], device=DEV, dtype=torch.int32)
+    out3 = torch.empty(3, H, device=DEV, dtype=od)
+    x3 = x.clone()
+    kernels.rmsnorm(x3, w, eps, out3, delta=delta, rows=rows)
+    torch.testing.assert_close(out3.float(), ref(s)[rows.long()].to(od).float(), **tol(od))
+    assert torch.equal(x3, x)                                                      # a gather writes nothing back
+
+
+@pytest.mark.parametrize("dtypes", [(torch.float32, torch.float32, torch.float32), (torch.float32, torch.bfloat16, torch.float32),
+                                    (torch.bfloat16, torch.bfloat16, torch.bfloat16), (torch.bfloat16, torch.bfloat16, torch.float32),
+                                    (torch.bfloat16, torch.float32, torch.bfloat16)])
+@pytest.mark.parametrize("M,N,K", [(1, 1, 1), (3, 70, 50), (65, 129, 257), (130, 64, 1024), (2, 1187, 96)])
+def test_gemm_simt(dtypes, M, N, K):
+    from spyinfer_b200 import kernels
+    ad, wd, cd = dtypes
+    a = torch.randn(M, K, device=DEV).to(ad)
+    w = (torch.randn(N, K, device=DEV) / math.sqrt(K)).to(wd)
+    out = torch.empty(M, N, device=DEV, dtype=cd)
+    kernels.gemm_simt(a, w, out)
+    ref = (a.double() @ w.double().t()).float()
+    torch.testing.assert_close(out.float(), ref.to(cd).float(), **tol(cd))
+    # a row's result does not depend on the other rows of the batch
+    if M > 1:
+        one = torch.empty(1, N, device=DEV, dtype=cd)
+        kernels.gemm_simt(a[M - 1:M].contiguous(), w, one)
+        assert torch.equal(one[0], out[M - 1])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,I", [(1, 8), (7, 224), (33, 1000)])
+def test_swiglu(dtype, T, I):
+    from spyinfer_b200 import kernels
+    gu = (torch.randn(T, 2 * I, device=DEV) * 4).to(dtype)
+    out = torch.empty(T, I, device=DEV, dtype=dtype)
+    kernels.swiglu(gu, out)
+    g, u = gu.float()[:, :I], gu.float()[:, I:]
+    torch.testing.assert_close(out.float(), ((g / (1 + torch.exp(-g))) * u).to(dtype).float(), **tol(dtype))
+
+
+def paged_setup(S, lens, nkv, hd, page_size, dtype, shuffle=True):
+    """Random keys and values of S sequences scattered over shuffled pages."""
+    width = max((l + page_size - 1) // page_size for l in lens)
+    num_pages = S * width + 3
+    perm = torch.randperm(num_pages) if shuffle else torch.arange(num_pages)
+    bt = torch.full((S, width), -1, dtype=torch.int32)
+    nxt = 0
+    for s, l in enumerate(lens):
+        for lp in range((l + page_size - 1) // page_size):
+            bt[s, lp] = perm[nxt]
+            nxt += 1
+    pages = torch.zeros(num_pages, 2, nkv, page_size, hd, device=DEV, dtype=dtype)
+    ks = [torch.randn(l, nkv, hd, device=DEV).to(dtype) for l in lens]
+    vs = [torch.randn(l, nkv, hd, device=DEV).to(dtype) for l in lens]
+    for s, l in enumerate(lens):
+        for p in range(l):
+            page = int(bt[s, p // page_size])
+            pages[page, 0, :, p % page_size] = ks[s][p]
+            pages[page, 1, :, p % page_size] = vs[s][p]
+    return pages, bt.to(DEV), ks, vs
+
+
+def ref_attention(q, k, v, pos, scale, window):
+    """q [nh, hd] at position pos over k, v [L, nkv, hd] in float64."""
+    nh, nkv = q.shape[0], k.shape[1]
+    lo = 0 if not window else max(0, pos - window + 1)
+    out = torch.zeros_like(q, dtype=torch.float64)
+    for h in range(nh):
+        kvh = h // (nh // nkv)
+        s = (k[lo:pos + 1, kvh].double() @ q[h].double()) * scale
+        p = torch.softmax(s, dim=0)
+        out[h] = p @ v[lo:pos + 1, kvh].double()
+    return out
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,page_size,window", [(4, 2, 16, 4, None), (6, 1, 48, 8, 20), (8, 8, 80, 16, None), (5, 5, 128, 16, 130),
+                                                        (16, 2, 256, 32, None)])
+def test_attention_generic_mixed_batch(dtype, nh, nkv, hd, page_size, window):
+    from spyinfer_b200 import kernels
+    torch.manual_seed(hd)
+    lens = [1, 37, 300, 129]
+    pages, bt, ks, vs = paged_setup(4, lens, nkv, hd, page_size, dtype)
+    # a batch of: seq0 its only token; seq1 a portion of 5 in the middle; seq2 its last token; seq3 two tokens across a chunk edge
+    toks = [(0, 0)] + [(1, p) for p in range(20, 25)] + [(2, 299)] + [(3, 127), (3, 128)]
+    T = len(toks)
+    q = torch.randn(T, nh * hd + 8, device=DEV).to(dtype)      # wider rows than nh*hd: only the first nh*hd columns are queries
+    positions = torch.tensor([p for _, p in toks], dtype=torch.int32, device=DEV)
+    seq_of = torch.tensor([s for s, _ in toks], dtype=torch.int32, device=DEV)
+    out = torch.empty(T, nh * hd, device=DEV, dtype=dtype)
+    status = torch.zeros(2, dtype=torch.int32, device=DEV)
+    scale = 1 / math.sqrt(hd)
+    kernels.attention_generic(q, nh, hd, out, pages, bt, positions, seq_of, scale, window=window, status=status)
+    assert status[0].item() == 0
+    for i, (s, p) in enumerate(toks):
+        ref = ref_attention(q[i, :nh * hd].view(nh, hd), ks[s], vs[s], p, scale, window)
+        torch.testing.assert_close(out[i].view(nh, hd).double(), ref, **(dict(rtol=2e-2, atol=2e-2) if dtype == torch.bfloat16
+                                                                         else dict(rtol=1e-4, atol=1e-5)))
+
+
+def test_attention_generic_finds_one_far_key():
+    """One key among hundreds is made to stand out (its score is far above the rest): the
+    output must be that key's value row, wherever it lies: first slot of a page, last slot,
+    the first key of all, the key just inside a window, and never the one just outside."""
+    from spyinfer_b200 import kernels
+    nh, nkv, hd, page_size, L = 2, 1, 32, 16, 700
+    pages, bt, ks, vs = paged_setup(1, [L], nkv, hd, page_size, torch.float32)
+    q = torch.randn(1, nh * hd, device=DEV)
+    pos = torch.tensor([L - 1], dtype=torch.int32, device=DEV)
+    seq = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.empty(1, nh * hd, device=DEV)
+    for window, far in [(None, 0), (None, 15), (None, 16), (None, 127), (None, 128), (None, 511), (300, L - 300), (300, L - 301)]:
+        pg = pages.clone()
+        page, slot = int(bt[0, far // page_size]), far % page_size
+        pg[page, 0, 0, slot] = 40.0 * q[0, :hd] / q[0, :hd].norm()     # aligned with head 0's query, large
+        kernels.attention_generic(q, nh, hd, out, pg, bt, pos, seq, 1.0, window=window)
+        hit = torch.allclose(out[0, :hd], vs[0][far, 0], atol=1e-3)
+        inside = window is None or far > L - 1 - window
+        assert hit == inside, f"window {window}, far key {far}: expected {'a hit' if inside else 'no hit'}"
+
+
+@pytest.mark.parametrize("adtype,cdtype,wdtype", [(torch.float32, torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16, torch.bfloat16),
+                                                  (torch.float32, torch.float32, torch.bfloat16)])
+@pytest.mark.parametrize("nh,nkv,hd,rot,page_size", [(4, 2, 16, 16, 4), (3, 3, 48, 32, 8), (8, 2, 128, 128, 16), (2, 1, 80, 80, 5)])
+def test_qk_norm_rope_store(adtype, cdtype, wdtype, nh, nkv, hd, rot, page_size):
+    from spyinfer_b200 import kernels
+    torch.manual_seed(nh * hd)
+    S, lens = 3, [9, 1, 30]
+    starts = [4, 0, 27]                                   # this step brings positions [start, len) of each sequence
+    width = 8
+    perm = torch.randperm(S * width)
+    bt = perm.view(S, width).to(torch.int32).to(DEV)
+    pages = torch.zeros(S * width, 2, nkv, page_size, hd, device=DEV, dtype=cdtype)
+    toks = [(s, p) for s in range(S) for p in range(starts[s], lens[s])]
+    T = len(toks)
+    qkv = torch.randn(T, (nh + 2 * nkv) * hd, device=DEV).to(adtype)
+    qw = (1 + 0.2 * torch.randn(hd, device=DEV)).to(wdtype)
+    kw = (1 + 0.2 * torch.randn(hd, device=DEV)).to(wdtype)
+    eps, theta = 1e-5, 10000.0
+    inv = torch.pow(torch.tensor(theta), -torch.arange(rot // 2, dtype=torch.float32) / (rot // 2)).to(DEV)
+    table = kernels.build_rope_table(inv, 64)
+    pos_f = torch.arange(64, dtype=torch.float32, device=DEV)[:, None] * inv[None, :]
+    torch.testing.assert_close(table[..., 0], torch.cos(pos_f), rtol=0, atol=2e-6)
+    torch.testing.assert_close(table[..., 1], torch.sin(pos_f), rtol=0, atol=2e-6)
+    positions = torch.tensor([p for _, p in toks], dtype=torch.int32, device=DEV)
+    seq_of = torch.tensor([s for s, _ in toks], dtype=torch.int32, device=DEV)
+    before = qkv.clone().float()
+    status = torch.zeros(2, dtype=torch.int32, device=DEV)
+    kernels.qk_rope_store(qkv, nh, nkv, hd, qw, kw, eps, table, positions, seq_of, bt, pages, store=True, status=status)
+    assert status[0].item() == 0
+
+    def norm_rope(x, w):                                    # x [T, heads, hd] float32
+        x = x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * w.float()
+        c, s = torch.cos(pos_f[positions.long()])[:, None, :], torch.sin(pos_f[positions.long()])[:, None, :]
+        lo, hi, rest = x[..., :rot // 2], x[..., rot // 2:rot], x[..., rot:]
+        return torch.cat([lo * c - hi * s, lo * s + hi * c, rest], dim=-1)
+
+    q_ref = norm_rope(before[:, :nh * hd].view(T, nh, hd), qw)
+    k_ref = norm_rope(before[:, nh * hd:(nh + nkv) * hd].view(T, nkv, hd), kw)
+    v_ref = before[:, (nh + nkv) * hd:].view(T, nkv, hd)
+    t = tol(adtype)
+    torch.testing.assert_close(qkv[:, :nh * hd].float().view(T, nh, hd), q_ref.to(adtype).float(), **t)
+    assert torch.equal(qkv[:, nh * hd:].float(), before[:, nh * hd:])       # k and v columns are left as they were
+    for i, (s, p) in enumerate(toks):
+        page = int(bt[s, p // page_size])
+        torch.testing.assert_close(pages[page, 0, :, p % page_size].float(), k_ref[i].to(cdtype).float(), **tol(cdtype))
+        torch.testing.assert_close(pages[page, 1, :, p % page_size].float(), v_ref[i].to(cdtype).float(), rtol=0, atol=0)
+    written = torch.zeros(S * width, page_size, dtype=torch.bool)
+    for s, p in toks:
+        written[int(bt[s, p // page_size]), p % page_size] = True
+    assert (pages.float().abs().sum(dim=(1, 2, 4)).cpu()[~written] == 0).all()   # no other slot of any page was touched
+    # store=False touches no page and still norms and rotates q
+    qkv2 = before.to(adtype)
+    pages2 = torch.zeros_like(pages)
+    kernels.qk_rope_store(qkv2, nh, nkv, hd, qw, kw, eps, table, positions, seq_of, None, None, store=False)
+    assert torch.equal(qkv2[:, :nh * hd], qkv[:, :nh * hd]) and pages2.abs().sum() == 0
+    # a block-table entry that is no page is reported and skipped
+    bad = bt.clone()
+    bad[0, starts[0] // page_size] = S * width
+    kernels.qk_rope_store(before.to(adtype), nh, nkv, hd, qw, kw, eps, table, positions, seq_of, bad, pages, store=True, status=status)
+    assert status[0].item() == 3
+
+
+def test_sampling_greedy_and_distribution():
+    from spyinfer_b200 import kernels
+    V = 1187
+    logits = torch.randn(6, V, device=DEV)
+    logits[2, 5] = logits[2, 900] = 50.0             # a tie: the lowest index wins
+    tokens = torch.empty(6, dtype=torch.int32, device=DEV)
+    kernels.sample(logits, tokens)
+    want = logits.argmax(dim=-1)
+    want[2] = 5
+    assert tokens.tolist() == want.tolist()
+    # temperature: frequencies of many seeded draws follow softmax(logits / T)
+    V2, n, temp = 23, 20000, 0.7
+    row = torch.randn(V2, device=DEV) * 2
+    lg = row.expand(n, V2).contiguous()
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    t = torch.full((n,), temp, device=DEV)
+    seed = torch.full((n,), 99, dtype=torch.int64, device=DEV)
+    draw = torch.arange(n, dtype=torch.int64, device=DEV)
+    kernels.sample(lg, out, t, seed, draw)
+    freq = torch.bincount(out.long(), minlength=V2).double() / n
+    p = torch.softmax(row.double() / temp, dim=0)
+    assert (freq - p).abs().max() < 4 * math.sqrt(0.25 / n) + 1e-3
+    again = torch.empty_like(out)
+    kernels.sample(lg, again, t, seed, draw)
+    assert torch.equal(out, again)                   # same seed and draw number: same token
+    t0 = torch.zeros(n, device=DEV)                  # temperature 0 is greedy
+    kernels.sample(lg, again, t0, seed, draw)
+    assert (again == int(row.argmax())).all()

@@ -1,0 +1,304 @@
+"""Each part alone against the plain implementation's function for it, at sizes other than
+the tiny models'; then arrangements that only a description can express: a run order that
+names a layer twice and lets an entry read another entry's cache, and a toy mixer with a
+state of its own that is defined here, registered, built and stepped without any change to
+the package."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_model
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def ctx_for(dtype, max_len=512):
+    from spyinfer_b200.parts import BuildContext
+    return BuildContext(dtype=dtype, device=torch.device(DEV), max_model_len=max_len)
+
+
+def bound(part, std=0.05, seed=0):
+    """Binds seeded random weights to a part; returns them by relative name (on the CPU)."""
+    g = torch.Generator().manual_seed(seed)
+    w = {}
+    for d in part.weight_decls():
+        x = torch.randn(d.shape, generator=g)
+        x = 1 + 0.1 * x if d.init == "one_plus_normal" else x * std
+        w[d.name] = x.to(torch.bfloat16)
+    part.bind({k: v.to(DEV) for k, v in w.items()})
+    return w
+
+
+def close(got, want, dtype):
+    if dtype == torch.float32:
+        torch.testing.assert_close(got.float().cpu(), want, rtol=1e-4, atol=1e-5 * max(1.0, want.abs().max().item()))
+    else:
+        err = (got.float().cpu() - want).abs().max().item()
+        assert err <= 4e-2 * max(want.abs().max().item(), 1e-3), f"max error {err} against a largest value of {want.abs().max().item()}"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rms_norm_part(dtype):
+    from spyinfer_b200.config import PartSpec
+    from spyinfer_b200.parts import build_part
+    part = build_part(PartSpec("rms_norm", {"size": 200, "eps": 1e-4, "weight": "n.weight"}), ctx_for(dtype))
+    w = bound(part)
+    x = torch.randn(9, 200)
+    delta = torch.randn(9, 200).to(dtype)
+    want = plain_model.rms_norm(x, w["n.weight"], 1e-4)
+    close(part.forward(x.to(DEV)), want, dtype)
+    res = x.to(DEV).clone()
+    got = part.forward_add(res, delta.to(DEV))
+    close(got, plain_model.rms_norm(x + delta.float(), w["n.weight"], 1e-4), dtype)
+    torch.testing.assert_close(res.cpu(), x + delta.float())      # the residual stream holds the 32-bit sum
+
+
+def test_rotary_half_table():
+    from spyinfer_b200.config import PartSpec
+    from spyinfer_b200.parts import build_part
+    part = build_part(PartSpec("rotary_half", {"theta": 1e6, "rotary_dim": 48}), ctx_for(torch.float32, 300))
+    table = part.rotation_table().cpu()
+    cos, sin = plain_model.rotary_angles(range(300), 48, 1e6)
+    torch.testing.assert_close(table[..., 0], cos, rtol=0, atol=3e-6)
+    torch.testing.assert_close(table[..., 1], sin, rtol=0, atol=3e-6)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gated_mlp_part(dtype):
+    from spyinfer_b200.config import PartSpec
+    from spyinfer_b200.parts import build_part
+    part = build_part(PartSpec("gated_mlp", {"hidden_size": 72, "intermediate_size": 200, "activation": "silu", "prefix": "mlp."}), ctx_for(dtype))
+    w = bound(part, std=0.2)
+    x = torch.randn(11, 72).to(dtype)
+    want = plain_model.feed_forward(x.float(), w, "")
+    close(part.forward(x.to(DEV)), want, dtype)
+
+
+def one_step_batch(cache, lens, device):
+    """A batch that brings every sequence whole (positions 0..len-1)."""
+    from spyinfer_b200.engine.batch import BatchStager
+    stager = BatchStager(device, 1024, 8, cache.width, max(1, cache.num_groups()))
+    tok, pos, seq, qs, cl, slots = [], [], [], [0], [], []
+    for s, n in enumerate(lens):
+        rid = f"s{s}"
+        cache.add_request(rid)
+        cache.reserve(rid, n)
+        tok += [0] * n
+        pos += range(n)
+        seq += [s] * n
+        qs.append(qs[-1] + n)
+        cl.append(n)
+        slots.append(cache.slot(rid))
+    i32 = lambda a: np.asarray(a, dtype=np.int32)
+    tables = [cache.gather_block_tables([f"s{s}" for s in range(len(lens))], g) for g in range(cache.num_groups())]
+    return stager.stage(i32(tok), i32(pos), i32(seq), i32(qs), i32(cl), i32(slots), i32([]), tables)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,window,rot", [(6, 2, 32, None, 32), (4, 4, 80, 9, 80), (8, 1, 64, None, 32)])
+def test_attention_part(dtype, nh, nkv, hd, window, rot):
+    from spyinfer_b200.cache import CacheManager
+    from spyinfer_b200.config import PartSpec
+    from spyinfer_b200.parts import build_part
+    H, eps, theta = 88, 1e-5, 5000.0
+    spec = PartSpec("attention", {"hidden_size": H, "num_heads": nh, "num_kv_heads": nkv, "head_dim": hd, "qk_norm_eps": eps,
+                                  "position": PartSpec("rotary_half", {"theta": theta, "rotary_dim": rot}), "window": window,
+                                  "scale": None, "prefix": "self_attn."})
+    part = build_part(spec, ctx_for(dtype))
+    w = bound(part, std=0.15)
+    lens = [23, 1, 40]
+    cache = CacheManager([part.cache_need()], 8, 32, 4, 512, dtype=dtype, device=torch.device(DEV))
+    batch = one_step_batch(cache, lens, torch.device(DEV))
+    view = cache.view(0)
+    view.block_table = batch.block_tables[0]
+    x = torch.randn(sum(lens), H).to(dtype)
+    got = part.forward(x.to(DEV), batch, view).float().cpu()
+    assert batch.status[0].item() == 0
+    cfg = {"num_attention_heads": nh, "num_key_value_heads": nkv, "head_dim": hd, "rms_norm_eps": eps, "rope_theta": theta}
+    off = 0
+    for n in lens:
+        xs = x[off:off + n].float()
+        if rot == hd:
+            want = plain_model.attention_mixer(xs, w, "", cfg, list(range(n)), window=window)
+        else:   # partial rotation: only the first `rot` elements of each head are rotated
+            q = plain_model.rms_norm(plain_model.linear(xs, w["self_attn.q_proj.weight"]).reshape(n, nh, hd), w["self_attn.q_norm.weight"], eps)
+            k = plain_model.rms_norm(plain_model.linear(xs, w["self_attn.k_proj.weight"]).reshape(n, nkv, hd), w["self_attn.k_norm.weight"], eps)
+            v = plain_model.linear(xs, w["self_attn.v_proj.weight"]).reshape(n, nkv, hd)
+            cos, sin = plain_model.rotary_angles(range(n), rot, theta)
+            q = torch.cat([plain_model.rotate_half(q[..., :rot], cos, sin), q[..., rot:]], dim=-1)
+            k = torch.cat([plain_model.rotate_half(k[..., :rot], cos, sin), k[..., rot:]], dim=-1)
+            o = plain_model.causal_attention(q, k, v, range(n), window=window)
+            want = plain_model.linear(o.reshape(n, nh * hd), w["self_attn.o_proj.weight"])
+        close(got[off:off + n], want, dtype)
+        off += n
+
+
+TOY_DECAY = 0.75
+
+
+def register_toy_parts():
+    """A mixer with a state of its own (a decaying sum of its inputs, one vector per request)
+    and the cache need that goes with it.  Defined here, in the test, through the public
+    registry only."""
+    from spyinfer_b200.config import StateCacheNeed
+    from spyinfer_b200.parts import Mixer, register_part
+    from spyinfer_b200.weights import WeightDecl
+
+    @register_part("toy_decay_mixer")
+    class ToyDecayMixer(Mixer):
+        def __init__(self, params, ctx):
+            super().__init__(params, ctx)
+            self.hidden = params["hidden_size"]
+            self.weight = None
+
+        def weight_decls(self):
+            return [WeightDecl("toy.weight", (self.hidden, self.hidden))]
+
+        def bind(self, tensors):
+            self.weight = tensors["toy.weight"].float()
+
+        def cache_need(self):
+            return StateCacheNeed((self.hidden,), "float32")
+
+        def forward(self, x, batch, cache):
+            out = torch.empty_like(x)
+            for s in range(batch.num_seqs):
+                slot = int(batch.host_state_slot[s])
+                state = cache.state[slot].clone()
+                for t in range(int(batch.host_q_start[s]), int(batch.host_q_start[s + 1])):
+                    state = TOY_DECAY * state + x[t].float()
+                    out[t] = (self.weight @ state).to(x.dtype)
+                cache.state[slot] = state
+            return out
+
+    return ToyDecayMixer
+
+
+def toy_spec():
+    from spyinfer_b200.config import LayerSpec, ModelSpec, PartSpec, RunEntry
+    H, V = 48, 97
+    norm = lambda name: PartSpec("rms_norm", {"size": H, "eps": 1e-6, "weight": name})
+    ffn = PartSpec("gated_mlp", {"hidden_size": H, "intermediate_size": 80, "activation": "silu", "prefix": "mlp."})
+    attn = PartSpec("attention", {"hidden_size": H, "num_heads": 3, "num_kv_heads": 1, "head_dim": 16, "qk_norm_eps": 1e-6,
+                                  "position": PartSpec("rotary_half", {"theta": 10000.0, "rotary_dim": 16}), "window": None, "scale": None,
+                                  "prefix": "self_attn."})
+    toy = PartSpec("toy_decay_mixer", {"hidden_size": H})
+    layers = [LayerSpec("pre_norm", norm("input_layernorm.weight"), m, norm("post_attention_layernorm.weight"), ffn, f"model.layers.{i}.")
+              for i, m in enumerate([toy, attn, toy])]
+    return ModelSpec(architecture="toy", hidden_size=H, vocab_size=V,
+                     embedding=PartSpec("token_embedding", {"vocab_size": V, "hidden_size": H, "weight": "model.embed_tokens.weight"}),
+                     layers=layers, run_order=[RunEntry(0), RunEntry(1), RunEntry(2)], final_norm=norm("model.norm.weight"),
+                     head=PartSpec("lm_head", {"vocab_size": V, "hidden_size": H, "tied": True, "weight": "lm_head.weight",
+                                               "tied_to": "model.embed_tokens.weight"}), max_position=256)
+
+
+def plain_toy_logits(w, tokens):
+    cfg = {"num_attention_heads": 3, "num_key_value_heads": 1, "head_dim": 16, "rms_norm_eps": 1e-6, "rope_theta": 10000.0}
+    h = plain_model.embed_tokens(w["model.embed_tokens.weight"], tokens)
+    pos = list(range(len(tokens)))
+    for i in range(3):
+        p = f"model.layers.{i}."
+        n = plain_model.rms_norm(h, w[p + "input_layernorm.weight"], 1e-6)
+        if i == 1:
+            a = plain_model.attention_mixer(n, w, p, cfg, pos)
+        else:
+            state, rows = torch.zeros(48), []
+            for t in range(len(tokens)):
+                state = TOY_DECAY * state + n[t]
+                rows.append(w[p + "toy.weight"].float() @ state)
+            a = torch.stack(rows)
+        h = h + a
+        n = plain_model.rms_norm(h, w[p + "post_attention_layernorm.weight"], 1e-6)
+        h = h + plain_model.feed_forward(n, w, p)
+    h = plain_model.rms_norm(h, w["model.norm.weight"], 1e-6)
+    return plain_model.linear(h, w["model.embed_tokens.weight"])
+
+
+def test_toy_mixer_with_state_is_registered_built_and_stepped():
+    from spyinfer_b200.config import EngineConfig
+    from spyinfer_b200.engine import Model, ModelRunner, StepEntry
+    from spyinfer_b200.weights import random_tensors
+    register_toy_parts()
+    spec = toy_spec()
+    cfg = EngineConfig(dtype="float32", max_num_seqs=3, max_model_len=128, kvcache_block_size=8, num_kvcache_blocks=24, max_num_batched_tokens=128)
+    model = Model(spec, torch.float32, cfg.device, cfg.max_model_len)
+    w = dict(random_tensors(model.weight_decls(), seed=4, std=0.1, norm_std=0.1))
+    model.bind({k: v.to(DEV) for k, v in w.items()})
+    runner = ModelRunner(model, cfg)
+    assert [runner.cache.view(i).kind for i in range(3)] == ["state", "paged", "state"]
+    rng = np.random.default_rng(0)
+    seqs = {r: rng.integers(0, 97, n).tolist() for r, n in (("x", 19), ("y", 30), ("z", 5))}
+    want = {r: plain_toy_logits(w, t) for r, t in seqs.items()}
+    # x whole; y in portions beside z's single tokens; then a new request in x's old slot must start from a zero state
+    got = runner.step([StepEntry("x", seqs["x"], range(19))]).cpu()
+    torch.testing.assert_close(got, want["x"], rtol=1e-4, atol=1e-5)
+    runner.finish("x")
+    done = {"y": 0, "z": 0}
+    sizes = [7, 2, 9, 5, 4, 3]
+    rows = {"y": [], "z": []}
+    for n in sizes:
+        entries = [StepEntry("y", seqs["y"][done["y"]:done["y"] + n], range(n))]
+        done["y"] += n
+        if done["z"] < 5:
+            entries.insert(0, StepEntry("z", seqs["z"][done["z"]:done["z"] + 1], [0]))
+            done["z"] += 1
+        out = runner.step(entries).cpu()
+        off = 0
+        for e in entries:
+            rows[e.request].append(out[off:off + len(e.tokens)])
+            off += len(e.tokens)
+    runner.check_status()
+    torch.testing.assert_close(torch.cat(rows["y"]), want["y"], rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(torch.cat(rows["z"]), want["z"], rtol=1e-4, atol=1e-5)
+    runner.finish("y"), runner.finish("z")
+    got = runner.step([StepEntry("x2", seqs["x"], range(19))]).cpu()
+    torch.testing.assert_close(got, want["x"], rtol=1e-4, atol=1e-5)
+    runner.cache.check_invariants()
+
+
+def test_run_order_names_a_layer_twice_and_reads_another_entrys_cache(tiny_models):
+    """Run order [0, 1, 1 reading entry 1's cache, 0]: layer 1 runs twice with the same
+    weights; its second run attends to the keys and values its first run stored.  Layer 0
+    runs twice with a cache for each run."""
+    from spyinfer_b200.config import EngineConfig, RunEntry, config_from_json
+    from spyinfer_b200.engine import Model, ModelRunner, StepEntry
+    folder, cfg, w = tiny_models["a"]
+    spec = config_from_json(cfg).to_spec()
+    spec.run_order = [RunEntry(0), RunEntry(1), RunEntry(1, cache_of=1), RunEntry(0)]
+    ecfg = EngineConfig(dtype="float32", max_num_seqs=2, max_model_len=64, kvcache_block_size=4, num_kvcache_blocks=40, max_num_batched_tokens=64)
+    model = Model(spec, torch.float32, ecfg.device, ecfg.max_model_len)
+    model.load(folder)
+    runner = ModelRunner(model, ecfg)
+    assert len(runner.cache.groups[0].entries) == 3      # entries 0, 1 and 3 own a cache; entry 2 borrows
+    tokens = np.random.default_rng(3).integers(0, cfg["vocab_size"], 21).tolist()
+    # plain statement of the same run order
+    T, pos = len(tokens), list(range(len(tokens)))
+    nh, nkv, hd, eps = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"], cfg["rms_norm_eps"]
+    h = plain_model.embed_tokens(w["model.embed_tokens.weight"], tokens)
+    kept = {}
+    for idx, (layer, reads) in enumerate([(0, None), (1, None), (1, 1), (0, None)]):
+        p = f"model.layers.{layer}."
+        n = plain_model.rms_norm(h, w[p + "input_layernorm.weight"], eps)
+        cos, sin = plain_model.rotary_angles(pos, hd, cfg["rope_theta"])
+        q = plain_model.rotate_half(plain_model.rms_norm(plain_model.linear(n, w[p + "self_attn.q_proj.weight"]).reshape(T, nh, hd),
+                                                         w[p + "self_attn.q_norm.weight"], eps), cos, sin)
+        if reads is None:
+            k = plain_model.rotate_half(plain_model.rms_norm(plain_model.linear(n, w[p + "self_attn.k_proj.weight"]).reshape(T, nkv, hd),
+                                                             w[p + "self_attn.k_norm.weight"], eps), cos, sin)
+            v = plain_model.linear(n, w[p + "self_attn.v_proj.weight"]).reshape(T, nkv, hd)
+            kept[idx] = (k, v)
+        else:
+            k, v = kept[reads]
+        o = plain_model.causal_attention(q, k, v, pos)
+        h = h + plain_model.linear(o.reshape(T, nh * hd), w[p + "self_attn.o_proj.weight"])
+        n = plain_model.rms_norm(h, w[p + "post_attention_layernorm.weight"], eps)
+        h = h + plain_model.feed_forward(n, w, p)
+    want = plain_model.linear(plain_model.rms_norm(h, w["model.norm.weight"], eps), w["model.embed_tokens.weight"])
+    whole = runner.step([StepEntry("w", tokens, range(T))]).cpu()
+    torch.testing.assert_close(whole, want, rtol=1e-4, atol=1e-5)
+    cut = torch.cat([runner.step([StepEntry("c", tokens[a:b], range(b - a))]).cpu() for a, b in [(0, 9), (9, 11), (11, 12), (12, 21)]])
+    torch.testing.assert_close(cut, want, rtol=1e-4, atol=1e-5)
+    runner.check_status()
