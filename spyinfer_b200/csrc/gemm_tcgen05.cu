@@ -1,0 +1,472 @@
+// bfloat16 matrix product on the 5th-generation tensor cores:  C[M, N] = A[M, K] . W[N, K]^T
+// with 32-bit accumulation in tensor memory.  Both operands are K-major; TMA brings
+// 128-byte-swizzled tiles into a ring of shared-memory stages, one elected thread issues
+// tcgen05.mma (128 x BN x 16 per instruction), four warps read the accumulator back with
+// tcgen05.ld and store bfloat16 or float32.
+//
+// One block computes one 128 x BN tile of "X . Y^T" over a range of K:
+//   normal mode: X = activations (128 tokens), Y = weights (BN = 128 or 256 outputs);
+//   swapped mode (few tokens): X = weights (128 outputs fill the instruction's M slot),
+//     Y = activations (BN = 16, 32 or 64 tokens); the tile is stored transposed.
+// With split-K every split stores its 32-bit partial tile into scratch memory and a second
+// kernel sums the splits in a fixed order; the number of splits depends only on the shape
+// class, so a token's result does not depend on the batch beyond rounding.
+// Tails: rows beyond M or N and the end of K are zero-filled by TMA; stores are predicated.
+// K must be a multiple of 8 (16-byte rows for TMA).  No cluster multicast is used.
+//
+// The reference's products are cuBLAS half-precision GEMMs and a SIMT GEMV
+// (spymaster2h/spyinfer src/backends/cuda/cublas/sgemm.cu:37-55,
+// src/backends/cuda/native/sgemm.cu:130-206); it has no tensor-core kernel of its own.
+#include <cuda.h>
+
+#include "common.cuh"
+
+SPY_MODULE(spy_gemm_tcgen05)
+
+namespace {
+
+constexpr int BM = 128;            // rows of X per tile = UMMA M
+constexpr int BK = 64;             // 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int NUM_THREADS = 192;   // warp 0: TMA, warp 1: MMA + TMEM, warps 2..5: epilogue
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ unsigned long long global_timer()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded wait: gives up after WAIT_LIMIT_NS (or at once when another role has given up),
+// raises the block's abort flag and returns false.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_timer();
+    uint32_t spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if ((++spins & 0x3ff) == 0) {
+            if (*abort_flag) return false;
+            if (global_timer() - t0 > WAIT_LIMIT_NS) {
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+
+__device__ __forceinline__ uint64_t make_smem_desc(const void* tile)
+{
+    // K-major, 128-byte swizzle: 8 rows of 128 bytes form one 1024-byte group
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_u32(tile) & 0x3FFFF) >> 4);   // start address
+    d |= (uint64_t)1 << 16;                             // leading byte offset (unused with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;                   // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                             // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;                             // SWIZZLE_128B
+    return d;
+}
+
+__device__ __forceinline__ uint32_t make_instr_desc(int n)
+{
+    uint32_t d = 0;
+    d |= 1u << 4;                    // accumulator F32
+    d |= 1u << 7;                    // A BF16
+    d |= 1u << 10;                   // B BF16
+    d |= (uint32_t)(n >> 3) << 17;   // N
+    d |= (uint32_t)(BM >> 4) << 24;  // M
+    return d;                        // both operands K-major, no negation
+}
+
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint64_t* bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t (&r)[32])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+
+__device__ __forceinline__ void tmem_load_16(uint32_t taddr, uint32_t (&r)[32])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+}
+
+template <int BN> struct Tile {
+    static constexpr int X_BYTES = BM * BK * 2;
+    static constexpr int Y_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = X_BYTES + Y_BYTES;
+    // few-token tiles keep about 100 KB so that two blocks share an SM; large tiles take the SM
+    static constexpr int STAGES = BN <= 64 ? (100 * 1024) / STAGE_BYTES : (200 * 1024) / STAGE_BYTES;
+    static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+    static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+};
+
+template <typename TC> __device__ __forceinline__ void store_elem(TC* p, float v) { *p = from_f32<TC>(v); }
+
+// Stores 32 consecutive columns of one row, vectorised when the row allows it.
+template <typename TC>
+__device__ __forceinline__ void store_row32(TC* dst, const uint32_t (&r)[32], int valid, bool aligned)
+{
+    if (valid >= 32 && aligned) {
+        if constexpr (sizeof(TC) == 4) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                reinterpret_cast<float4*>(dst)[i] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
+                                                                __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                uint4 v;
+                __nv_bfloat162 t;
+                t = __floats2bfloat162_rn(__uint_as_float(r[8 * i]), __uint_as_float(r[8 * i + 1])); v.x = *reinterpret_cast<uint32_t*>(&t);
+                t = __floats2bfloat162_rn(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3])); v.y = *reinterpret_cast<uint32_t*>(&t);
+                t = __floats2bfloat162_rn(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5])); v.z = *reinterpret_cast<uint32_t*>(&t);
+                t = __floats2bfloat162_rn(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7])); v.w = *reinterpret_cast<uint32_t*>(&t);
+                reinterpret_cast<uint4*>(dst)[i] = v;
+            }
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+            if (i < valid) store_elem(dst + i, __uint_as_float(r[i]));
+    }
+}
+
+// X: [x_rows, K] in the instruction's M slot; Y: [y_rows, K] in its N slot.
+// SWAP == false: out[x, y] (row stride ld);  SWAP == true: out[y, x].
+// splits > 1: out is the float scratch [splits][rows][ld] and TC is float.
+template <int BN, typename TC, bool SWAP>
+__global__ void __launch_bounds__(NUM_THREADS, BN <= 64 ? 2 : 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, TC* __restrict__ out,
+                    long long ld, long long split_stride, int x_rows, int y_rows, int k_blocks, int k_blocks_per_split, int* status)
+{
+    using T = Tile<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* tiles = smem;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)T::STAGES * T::STAGE_BYTES);
+    uint64_t* empty_bar = full_bar + T::STAGES;
+    uint64_t* accum_bar = empty_bar + T::STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int x0 = blockIdx.x * BM, y0 = blockIdx.y * BN;
+    const int kb0 = blockIdx.z * k_blocks_per_split;
+    const int kb1 = min(k_blocks, kb0 + k_blocks_per_split);
+    const int num_kb = kb1 - kb0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < T::STAGES; ++s) {
+            mbar_init(full_bar + s, 1);
+            mbar_init(empty_bar + s, 1);
+        }
+        mbar_init(accum_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)T::TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int i = 0; i < num_kb; ++i) {
+                const int s = i % T::STAGES;
+                const uint32_t phase = (i / T::STAGES) & 1;
+                if (i >= T::STAGES && !mbar_wait(empty_bar + s, phase ^ 1, abort_flag)) break;
+                uint8_t* xs = tiles + (size_t)s * T::STAGE_BYTES;
+                uint8_t* ys = xs + T::X_BYTES;
+                mbar_expect_tx(full_bar + s, T::STAGE_BYTES);
+                tma_load_2d(xs, &map_x, (kb0 + i) * BK, x0, full_bar + s);
+                tma_load_2d(ys, &map_y, (kb0 + i) * BK, y0, full_bar + s);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = make_instr_desc(BN);
+            bool ok = true;
+            for (int i = 0; i < num_kb && ok; ++i) {
+                const int s = i % T::STAGES;
+                const uint32_t phase = (i / T::STAGES) & 1;
+                ok = mbar_wait(full_bar + s, phase, abort_flag);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint8_t* xs = tiles + (size_t)s * T::STAGE_BYTES;
+                const uint64_t dx = make_smem_desc(xs), dy = make_smem_desc(xs + T::X_BYTES);
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k) {
+                    const uint64_t adv = (uint64_t)((k * UMMA_K * 2) >> 4);
+                    umma(tmem_base, dx + adv, dy + adv, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                }
+                umma_commit(empty_bar + s);   // the stage is free again when these MMAs have read it
+            }
+            umma_commit(accum_bar);           // the accumulator is complete when every MMA has finished
+        }
+    } else {
+        // epilogue: warp w reads TMEM lanes 32*(w%4) .. +31, i.e. tile rows of X
+        const int quarter = warp & 3;
+        const bool ok = mbar_wait(accum_bar, 0, abort_flag);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int x = x0 + quarter * 32 + lane;
+        TC* base = out + (size_t)blockIdx.z * split_stride;
+        if (ok && num_kb > 0) {
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                uint32_t r[32];
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c;
+                if constexpr (BN >= 32) tmem_load_32(taddr, r);
+                else tmem_load_16(taddr, r);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                const int cols = BN >= 32 ? 32 : BN;
+                const int y = y0 + c;
+                if constexpr (!SWAP) {
+                    if (x < x_rows && y < y_rows) {
+                        TC* dst = base + (size_t)x * ld + y;
+                        const bool aligned = (reinterpret_cast<uintptr_t>(dst) & 15) == 0;
+                        store_row32<TC>(dst, r, min(cols, y_rows - y), aligned && cols == 32);
+                    }
+                } else {
+                    if (x < x_rows) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (j < cols && y + j < y_rows) store_elem(base + (size_t)(y + j) * ld + x, __uint_as_float(r[j]));
+                    }
+                }
+            }
+        } else if (num_kb <= 0) {
+            // an empty K range contributes zeros (only possible for a trailing split)
+            for (int c = 0; c < BN; ++c) {
+                const int y = y0 + c;
+                if (x < x_rows && y < y_rows) {
+                    if constexpr (!SWAP) store_elem(base + (size_t)x * ld + y, 0.f);
+                    else store_elem(base + (size_t)y * ld + x, 0.f);
+                }
+            }
+        }
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (*abort_flag) {
+        // a wait ran out: give copies that may still be in flight time to land before the
+        // shared memory is released, then report
+        if (threadIdx.x == 0) {
+            const unsigned long long t0 = global_timer();
+            while (global_timer() - t0 < 2000000ull) { }
+            report_status(status, SPY_STATUS_WAIT_TIMEOUT, (int)(blockIdx.x + blockIdx.y * gridDim.x));
+        }
+        __syncthreads();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)T::TMEM_COLS) : "memory");
+    }
+}
+
+// Sums the splits of a scratch buffer in ascending order and stores the output type.
+template <typename TC>
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, TC* __restrict__ out, long long elems, int splits)
+{
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < elems; i += (long long)gridDim.x * blockDim.x) {
+        float acc = partial[i];
+        for (int s = 1; s < splits; ++s) acc += partial[(size_t)s * elems + i];
+        out[i] = from_f32<TC>(acc);
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// A [rows, K] bfloat16 matrix with K contiguous; box = 64 columns x box_rows rows, 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* ptr, long long rows, long long K, long long ld, int box_rows)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) SPY_FAIL("gemm_tcgen05: cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) SPY_FAIL("gemm_tcgen05: cuTensorMapEncodeTiled failed with code %d (rows %lld, K %lld, ld %lld)", (int)r, rows, K, ld);
+    return 0;
+}
+
+template <int BN, typename TC, bool SWAP>
+static int launch(const CUtensorMap& mx, const CUtensorMap& my, void* out, long long ld, long long split_stride, int x_rows, int y_rows,
+                  int k_blocks, int splits, int* status, cudaStream_t stream)
+{
+    using T = Tile<BN>;
+    auto kernel = gemm_tcgen05_kernel<BN, TC, SWAP>;
+    static bool configured = false;
+    if (!configured) {
+        SPY_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)T::SMEM));
+        configured = true;
+    }
+    const int per_split = (k_blocks + splits - 1) / splits;
+    dim3 grid((x_rows + BM - 1) / BM, (y_rows + BN - 1) / BN, splits);
+    if (grid.y > 65535 || grid.z > 65535) SPY_FAIL("gemm_tcgen05: the grid %u x %u x %u exceeds the launch limits", grid.x, grid.y, grid.z);
+    kernel<<<grid, NUM_THREADS, T::SMEM, stream>>>(mx, my, (TC*)out, ld, split_stride, x_rows, y_rows, k_blocks, per_split, status);
+    SPY_CHECK_LAUNCH("gemm_tcgen05");
+    return 0;
+}
+
+}  // namespace
+
+// How many splits of K a product of this shape uses, and the floats of scratch it needs.
+// The choice depends on M only through its class (<= 64 rows or more), never on M itself
+// within the class beyond the number of row tiles.  A plan that would need more than
+// scratch_limit floats falls back to one pass over K.
+extern "C" int spy_gemm_tcgen05_plan(int M, int N, int K, long long scratch_limit, int* splits_out, long long* scratch_floats_out)
+{
+    const int k_blocks = (K + BK - 1) / BK;
+    int tiles;
+    if (M <= 64) tiles = (N + BM - 1) / BM;
+    else tiles = ((M + BM - 1) / BM) * ((N + 255) / 256);
+    int splits = 1;
+    if (tiles < 148) {
+        splits = (296 + tiles - 1) / tiles;
+        const int most = k_blocks / 4 > 0 ? k_blocks / 4 : 1;   // at least four K blocks per split
+        if (splits > most) splits = most;
+        if (splits > 16) splits = 16;
+    }
+    // no empty trailing split
+    const int per = (k_blocks + splits - 1) / splits;
+    splits = (k_blocks + per - 1) / per;
+    *splits_out = splits;
+    *scratch_floats_out = splits > 1 ? (long long)splits * M * N : 0;
+    if (*scratch_floats_out > scratch_limit) {   // not enough scratch: one pass over K
+        *splits_out = 1;
+        *scratch_floats_out = 0;
+    }
+    return 0;
+}
+
+// A [M, K] and W [N, K] bfloat16, rows lda/ldw elements apart; C [M, N] of c_dtype, rows ldc
+// apart.  scratch: float buffer of at least the plan's size (may be null when it is 0).
+extern "C" int spy_gemm_tcgen05(const void* A, long long lda, const void* W, long long ldw, void* C, int c_dtype, long long ldc, int M, int N,
+                                int K, float* scratch, long long scratch_floats, int* status, cudaStream_t stream)
+{
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 != 0) SPY_FAIL("gemm_tcgen05: K %d must be a positive multiple of 8 (16-byte rows for TMA)", K);
+    if (lda % 8 != 0 || ldw % 8 != 0) SPY_FAIL("gemm_tcgen05: row strides %lld/%lld must be multiples of 8 elements", lda, ldw);
+    if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15)) SPY_FAIL("gemm_tcgen05: operands must be 16-byte aligned");
+    if (c_dtype != SPY_F32 && c_dtype != SPY_BF16) SPY_FAIL("gemm_tcgen05: unknown output dtype code %d", c_dtype);
+    int splits;
+    long long need;
+    spy_gemm_tcgen05_plan(M, N, K, scratch ? scratch_floats : 0, &splits, &need);
+    const int k_blocks = (K + BK - 1) / BK;
+    const bool swap = M <= 64;
+    const int bn = swap ? (M <= 16 ? 16 : (M <= 32 ? 32 : 64)) : 256;
+    CUtensorMap mx, my;
+    if (swap) {
+        if (make_map(&mx, W, N, K, ldw, BM) || make_map(&my, A, M, K, lda, bn)) return 1;
+    } else {
+        if (make_map(&mx, A, M, K, lda, BM) || make_map(&my, W, N, K, ldw, bn)) return 1;
+    }
+    const int x_rows = swap ? N : M, y_rows = swap ? M : N;
+    void* out = splits > 1 ? (void*)scratch : C;
+    const long long ld = splits > 1 ? N : ldc;
+    const long long split_stride = splits > 1 ? (long long)M * N : 0;
+    const bool f32_out = splits > 1 || c_dtype == SPY_F32;
+    int rc;
+#define SPY_LAUNCH(BN_, SWAP_)                                                                                              \
+    rc = f32_out ? launch<BN_, float, SWAP_>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, status, stream) \
+                 : launch<BN_, bf16, SWAP_>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, status, stream)
+    if (!swap) SPY_LAUNCH(256, false);
+    else if (bn == 16) SPY_LAUNCH(16, true);
+    else if (bn == 32) SPY_LAUNCH(32, true);
+    else SPY_LAUNCH(64, true);
+#undef SPY_LAUNCH
+    if (rc) return rc;
+    if (splits > 1) {
+        const long long elems = (long long)M * N;
+        if (ldc != N) SPY_FAIL("gemm_tcgen05: split-K needs a contiguous output (ldc %lld, N %d)", ldc, N);
+        long long blocks = (elems + 255) / 256;
+        if (blocks > 148 * 8) blocks = 148 * 8;
+        if (c_dtype == SPY_F32) splitk_reduce_kernel<float><<<(int)blocks, 256, 0, stream>>>(scratch, (float*)C, elems, splits);
+        else splitk_reduce_kernel<bf16><<<(int)blocks, 256, 0, stream>>>(scratch, (bf16*)C, elems, splits);
+        SPY_CHECK_LAUNCH("gemm_tcgen05 split-K reduce");
+    }
+    return 0;
+}

@@ -24,6 +24,8 @@ from typing import Dict, List, Optional, Sequence
 import numpy as np
 import torch
 
+from .. import kernels
+
 
 @dataclass
 class StepEntry:
@@ -69,7 +71,7 @@ class BatchStager:
         self.host = torch.empty(n, dtype=torch.int32, pin_memory=True)
         self.host_np = self.host.numpy()
         self.dev = torch.empty(n, dtype=torch.int32, device=device)
-        self.status = torch.zeros(2, dtype=torch.int32, device=device)
+        self.status = kernels.status_word(device)
         self._copied = torch.cuda.Event()
         self._copy_pending = False
 

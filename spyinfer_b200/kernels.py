@@ -247,6 +247,50 @@ def sample(logits: torch.Tensor, tokens: torch.Tensor, temperature: Optional[tor
 
 
 def tensor_core_gemm_takes(out_features: int, in_features: int) -> bool:
-    """Whether the tcgen05 kernel takes a weight of this shape (its rows must be 16-byte
-    aligned for TMA: ``in_features`` a multiple of 8)."""
-    return False
+    """Whether the tcgen05 kernel takes a weight of this shape: its rows must be 16 bytes
+    aligned for TMA, so ``in_features`` must be a multiple of 8.  Any ``out_features``."""
+    return in_features % 8 == 0 and in_features > 0
+
+
+_status_words = {}
+
+
+def status_word(device) -> torch.Tensor:
+    """The device's status word: two int32 (code, detail), zero while all is well.  Kernels
+    that meet an index outside their buffers, or whose bounded waits run out, store a code
+    here and skip the access; the engine reads it after a step."""
+    key = str(torch.device(device))
+    if key not in _status_words:
+        _status_words[key] = torch.zeros(2, dtype=torch.int32, device=device)
+    return _status_words[key]
+
+
+GEMM_SCRATCH_FLOATS = 16 * 1024 * 1024
+_gemm_scratch = {}
+
+
+def _scratch(device) -> torch.Tensor:
+    """The split-K scratch of a device: one fixed buffer (64 MB), made at first use, so that
+    captured graphs keep pointing at live memory.  Products on one stream use it in turn."""
+    key = str(device)
+    if key not in _gemm_scratch:
+        _gemm_scratch[key] = torch.empty(GEMM_SCRATCH_FLOATS, dtype=torch.float32, device=device)
+    return _gemm_scratch[key]
+
+
+def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[M, N] = a[M, K] @ w[N, K]^T`` on the tensor cores: bfloat16 operands, 32-bit
+    accumulation, bfloat16 or float32 output.  K must be a multiple of 8."""
+    _check(a, "gemm input", torch.bfloat16, 2)
+    _check(w, "gemm weight", torch.bfloat16, 2)
+    _check(out, "gemm output", ndim=2)
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or tuple(out.shape) != (M, N):
+        raise KernelError(f"gemm: shapes do not fit: input {tuple(a.shape)}, weight {tuple(w.shape)}, output {tuple(out.shape)}")
+    scratch = _scratch(a.device)
+    if status is None:
+        status = status_word(a.device)
+    _call("gemm_tcgen05", "spy_gemm_tcgen05", _ptr(a), ctypes.c_longlong(K), _ptr(w), ctypes.c_longlong(K), _ptr(out), _code(out, "gemm output"),
+          ctypes.c_longlong(N), M, N, K, _ptr(scratch), ctypes.c_longlong(scratch.numel()), _ptr(status), _stream())
+    return out

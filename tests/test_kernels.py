@@ -261,3 +261,55 @@ def test_sampling_greedy_and_distribution():
     t0 = torch.zeros(n, device=DEV)                  # temperature 0 is greedy
     kernels.sample(lg, again, t0, seed, draw)
     assert (again == int(row.argmax())).all()
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M,N,K", [(1, 128, 64), (5, 200, 96), (16, 4096, 4096), (17, 1000, 520), (33, 136, 72), (64, 6144, 512),
+                                   (65, 300, 136), (128, 256, 64), (129, 1187, 1032), (300, 512, 4096), (1000, 24, 200), (2048, 1024, 12288)])
+def test_gemm_tcgen05(out_dtype, M, N, K):
+    """Tensor-core product at sizes that exercise every tile class (16/32/64 tokens swapped,
+    128 x 256 tiles), tails in M, N and K, and split-K."""
+    from spyinfer_b200 import kernels
+    torch.manual_seed(M * 7 + N)
+    a = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
+    out = torch.full((M, N), float("nan"), device=DEV, dtype=out_dtype)
+    status = kernels.status_word(DEV)
+    kernels.gemm_tcgen05(a, w, out)
+    torch.cuda.synchronize()
+    assert status[0].item() == 0
+    ref = a.float() @ w.float().t()
+    assert torch.isfinite(out.float()).all()
+    if out_dtype == torch.float32:
+        torch.testing.assert_close(out, ref, rtol=1e-4, atol=2e-4)
+    else:
+        torch.testing.assert_close(out.float(), ref.to(torch.bfloat16).float(), rtol=1.6e-2, atol=2e-3)
+    if 1 < M <= 16:
+        one = torch.empty(1, N, device=DEV, dtype=out_dtype)
+        kernels.gemm_tcgen05(a[M - 1:M].contiguous(), w, one)
+        assert torch.equal(one[0], out[M - 1])      # within a tile class a row does not depend on the batch
+
+
+def test_gemm_tcgen05_finds_one_large_product():
+    """One input element and one weight element are made large: exactly one output element
+    must stand out, wherever in K the pair lies (start of a 64-block, its end, the K tail)."""
+    from spyinfer_b200 import kernels
+    M, N, K = 70, 260, 328
+    for k in (0, 63, 64, 127, 320, 327):
+        a = torch.zeros(M, K, device=DEV, dtype=torch.bfloat16)
+        w = torch.zeros(N, K, device=DEV, dtype=torch.bfloat16)
+        a[69, k], w[259, k] = 3.0, 5.0
+        out = torch.empty(M, N, device=DEV, dtype=torch.float32)
+        kernels.gemm_tcgen05(a, w, out)
+        want = torch.zeros(M, N, device=DEV)
+        want[69, 259] = 15.0
+        assert torch.equal(out, want), f"k = {k}"
+
+
+def test_gemm_tcgen05_refuses_unaligned_k():
+    from spyinfer_b200 import kernels
+    a = torch.zeros(4, 60, device=DEV, dtype=torch.bfloat16)
+    w = torch.zeros(8, 60, device=DEV, dtype=torch.bfloat16)
+    with pytest.raises(kernels.KernelError):
+        kernels.gemm_tcgen05(a, w, torch.empty(4, 8, device=DEV, dtype=torch.bfloat16))
+    assert not kernels.tensor_core_gemm_takes(8, 60) and kernels.tensor_core_gemm_takes(8, 64)
