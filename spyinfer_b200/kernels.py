@@ -201,6 +201,64 @@ def attention_generic(q: torch.Tensor, num_heads: int, head_dim: int, out: torch
     return out
 
 
+_attn_scratch = {}
+
+
+def attention_scratch(device, floats: int) -> torch.Tensor:
+    """A float32 buffer of at least ``floats`` for the split attention kernel's partial
+    results.  Buffers are kept for the life of the process (captured graphs point at them);
+    a larger request makes a new one."""
+    key = str(torch.device(device))
+    buf = _attn_scratch.get(key)
+    if buf is None or buf[-1].numel() < floats:
+        size = max(floats, 1 << 20)
+        _attn_scratch.setdefault(key, []).append(torch.empty(size, dtype=torch.float32, device=device))
+        buf = _attn_scratch[key]
+    return buf[-1]
+
+
+def attention_mma_takes(num_heads: int, num_kv_heads: int, head_dim: int, dtype: torch.dtype) -> bool:
+    """Whether the tensor-core attention kernel takes these sizes: bfloat16, head size 64 or
+    128, at most 16 query heads per key/value head."""
+    return dtype == torch.bfloat16 and head_dim in (64, 128) and num_heads % num_kv_heads == 0 and num_heads // num_kv_heads <= 16
+
+
+def attention_mma(q: torch.Tensor, num_heads: int, head_dim: int, out: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor,
+                  positions: torch.Tensor, q_start: torch.Tensor, num_seqs: int, scale: float, window: Optional[int] = None,
+                  split_keys: int = 0, max_splits: int = 0, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Tensor-core attention of a batch over its pages.  ``split_keys == 0``: tiles mode, any
+    mix of portions and single tokens.  ``split_keys > 0``: every sequence brings one token
+    and its keys are cut into splits of ``split_keys`` (a multiple of 64), at most
+    ``max_splits`` of them, merged through scratch memory."""
+    _check(q, "attention queries", torch.bfloat16, 2)
+    _check(out, "attention output", torch.bfloat16, 2)
+    _check(pages, "cache pages", torch.bfloat16, 5)
+    _check(block_table, "block table", torch.int32, 2)
+    _check(positions, "positions", torch.int32, 1)
+    _check(q_start, "q_start", torch.int32, 1)
+    T = q.shape[0]
+    num_pages, two, nkv, page_size, hd = pages.shape
+    if two != 2 or hd != head_dim:
+        raise KernelError(f"cache pages: expected [pages, 2, nkv, page_size, {head_dim}], found {tuple(pages.shape)}")
+    if q.shape[1] < num_heads * head_dim or tuple(out.shape) != (T, num_heads * head_dim):
+        raise KernelError(f"attention: q {tuple(q.shape)} / out {tuple(out.shape)} do not fit {num_heads} heads of {head_dim}")
+    if positions.shape[0] != T or q_start.shape[0] != num_seqs + 1 or block_table.shape[0] < num_seqs:
+        raise KernelError("attention: positions need one entry per token, q_start one per sequence plus one, the block table a row per sequence")
+    mode = 1 if split_keys > 0 else 0
+    scratch, floats = None, 0
+    if mode == 1 and max_splits > 1:
+        floats = num_seqs * num_heads * max_splits * (head_dim + 2)
+        scratch = attention_scratch(q.device, floats)
+        floats = scratch.numel()
+    if status is None:
+        status = status_word(q.device)
+    _call("attention_mma", "spy_attention_mma", _ptr(q), ctypes.c_longlong(q.shape[1]), _ptr(out), _ptr(pages), _ptr(block_table),
+          block_table.shape[1], page_size, num_pages, num_heads, nkv, head_dim, _ptr(positions), _ptr(q_start), T, num_seqs,
+          int(window or 0), ctypes.c_float(scale), mode, int(split_keys), int(max_splits), _ptr(scratch), ctypes.c_longlong(floats),
+          _ptr(status), _stream())
+    return out
+
+
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """``out[M, N] = a[M, K] @ w[N, K]^T`` on the CUDA cores in 32-bit, any sizes and dtypes."""
     _check(a, "gemm input", ndim=2)

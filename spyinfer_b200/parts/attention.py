@@ -45,6 +45,12 @@ class Attention(Mixer):
         pos = params.get("position")
         self.position = build_part(pos, ctx) if pos is not None else None
         self.qkv = self.o = self.q_norm = self.k_norm = self.rope_table = None
+        self.fast = kernels.attention_mma_takes(self.nh, self.nkv, self.hd, ctx.dtype)
+        # decoding splits every sequence's keys into at most 16 ranges; the range length is
+        # fixed by the longest sequence the engine allows, so a row's arithmetic does not
+        # depend on the batch it decodes in
+        self.split_keys = max(256, (ctx.max_model_len // 16 + 63) // 64 * 64)
+        self.max_splits = (ctx.max_model_len + self.split_keys - 1) // self.split_keys
 
     def weight_decls(self):
         p, nh, nkv, hd, H = self.prefix, self.nh, self.nkv, self.hd, self.hidden
@@ -70,7 +76,7 @@ class Attention(Mixer):
             self.rope_table = self.position.rotation_table()
 
     def modules(self):
-        mods = ["qk_rope_store", "attention_generic"] + self.qkv.modules() + self.o.modules()
+        mods = ["qk_rope_store", "attention_mma" if self.fast else "attention_generic"] + self.qkv.modules() + self.o.modules()
         if self.position is not None:
             mods += self.position.modules()
         return mods
@@ -84,6 +90,15 @@ class Attention(Mixer):
                               self.rope_table, batch.positions, batch.seq_of_token, cache.block_table, cache.pages,
                               store=cache.writes, status=batch.status)
         out = torch.empty((x.shape[0], self.nh * self.hd), dtype=x.dtype, device=x.device)
-        kernels.attention_generic(qkv, self.nh, self.hd, out, cache.pages, cache.block_table, batch.positions, batch.seq_of_token,
-                                  self.scale, window=self.window, status=batch.status)
+        if not self.fast:
+            kernels.attention_generic(qkv, self.nh, self.hd, out, cache.pages, cache.block_table, batch.positions, batch.seq_of_token,
+                                      self.scale, window=self.window, status=batch.status)
+        elif batch.num_tokens == batch.num_seqs:
+            # every request brings one token: decoding, keys split across blocks
+            kernels.attention_mma(qkv, self.nh, self.hd, out, cache.pages, cache.block_table, batch.positions, batch.q_start,
+                                  batch.num_seqs, self.scale, window=self.window, split_keys=self.split_keys,
+                                  max_splits=self.max_splits, status=batch.status)
+        else:
+            kernels.attention_mma(qkv, self.nh, self.hd, out, cache.pages, cache.block_table, batch.positions, batch.q_start,
+                                  batch.num_seqs, self.scale, window=self.window, status=batch.status)
         return self.o(out)

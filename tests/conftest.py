@@ -31,7 +31,9 @@ def pytest_collection_modifyitems(config, items):
 
 
 # Tiny configurations that differ in every size and option.  A and B have the sizes of the
-# two tiny reference workloads; C adds windows on some layers and a head size of 48.
+# two tiny reference workloads; C adds windows on some layers and a head size of 48; D has
+# the head size (64) and group size (5 query heads per key/value head, no power of two) that
+# put the bfloat16 path on its tensor-core attention kernel, a window, and a tied head.
 TINY = {
     "a": dict(
         config={"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "hidden_act": "silu", "num_hidden_layers": 2,
@@ -52,6 +54,13 @@ TINY = {
                 "max_position_embeddings": 4096, "bos_token_id": 3, "eos_token_id": 4, "use_sliding_window": True,
                 "sliding_window": 40, "layer_types": ["sliding_attention", "full_attention", "sliding_attention", "full_attention"]},
         seed=33, std=0.05, norm_std=0.2),
+    "d": dict(
+        config={"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "hidden_act": "silu", "num_hidden_layers": 2,
+                "hidden_size": 200, "num_attention_heads": 10, "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 328,
+                "vocab_size": 1187, "rope_theta": 300000.0, "rms_norm_eps": 2e-6, "tie_word_embeddings": True,
+                "max_position_embeddings": 8192, "bos_token_id": 7, "eos_token_id": 8, "use_sliding_window": True,
+                "sliding_window": 100, "layer_types": ["full_attention", "sliding_attention"]},
+        seed=44, std=0.04, norm_std=0.1),
 }
 
 

@@ -313,3 +313,73 @@ def test_gemm_tcgen05_refuses_unaligned_k():
     with pytest.raises(kernels.KernelError):
         kernels.gemm_tcgen05(a, w, torch.empty(4, 8, device=DEV, dtype=torch.bfloat16))
     assert not kernels.tensor_core_gemm_takes(8, 60) and kernels.tensor_core_gemm_takes(8, 64)
+
+
+@pytest.mark.parametrize("nh,nkv,hd,page_size,window", [(8, 2, 128, 16, None), (10, 2, 64, 16, 150), (4, 4, 128, 8, None), (16, 1, 64, 32, None),
+                                                        (6, 2, 128, 5, 33)])
+def test_attention_mma_tiles_mixed_batch(nh, nkv, hd, page_size, window):
+    """Tensor-core attention, tiles mode: portions, single tokens and a one-token sequence in
+    one batch, group sizes 1, 3, 4, 5 and 16, page sizes that are no power of two."""
+    from spyinfer_b200 import kernels
+    torch.manual_seed(nh * hd)
+    lens = [1, 70, 333, 129, 40]
+    pages, bt, ks, vs = paged_setup(5, lens, nkv, hd, page_size, torch.bfloat16)
+    # seq0 its only token; seq1 a portion of 23 tokens in the middle; seq2 its last token; seq3 two tokens across key 128; seq4 whole
+    toks = [(0, 0)] + [(1, p) for p in range(30, 53)] + [(2, 332)] + [(3, 127), (3, 128)] + [(4, p) for p in range(40)]
+    T = len(toks)
+    q = torch.randn(T, (nh + 2 * nkv) * hd, device=DEV).to(torch.bfloat16)
+    positions = torch.tensor([p for _, p in toks], dtype=torch.int32, device=DEV)
+    q_start = torch.tensor([0, 1, 24, 25, 27, 67], dtype=torch.int32, device=DEV)
+    out = torch.full((T, nh * hd), float("nan"), device=DEV, dtype=torch.bfloat16)
+    scale = 1 / math.sqrt(hd)
+    kernels.attention_mma(q, nh, hd, out, pages, bt, positions, q_start, 5, scale, window=window)
+    torch.cuda.synchronize()
+    assert kernels.status_word(DEV)[0].item() == 0
+    for i, (s, p) in enumerate(toks):
+        ref = ref_attention(q[i, :nh * hd].view(nh, hd), ks[s], vs[s], p, scale, window)
+        torch.testing.assert_close(out[i].view(nh, hd).double(), ref, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("nh,nkv,hd,page_size,window,split_keys", [(32, 8, 128, 16, None, 256), (10, 2, 64, 16, 300, 64), (8, 8, 128, 8, None, 128),
+                                                                   (12, 4, 64, 16, None, 512)])
+def test_attention_mma_split_decode(nh, nkv, hd, page_size, window, split_keys):
+    """Tensor-core attention, split mode: one token per sequence, contexts from 1 to 1500 keys
+    so that rows fall into one split, two splits and many, with and without a window."""
+    from spyinfer_b200 import kernels
+    torch.manual_seed(nh + hd)
+    lens = [1, 17, split_keys, split_keys + 1, 700, 1500]
+    S = len(lens)
+    pages, bt, ks, vs = paged_setup(S, lens, nkv, hd, page_size, torch.bfloat16)
+    q = torch.randn(S, (nh + 2 * nkv) * hd, device=DEV).to(torch.bfloat16)
+    positions = torch.tensor([l - 1 for l in lens], dtype=torch.int32, device=DEV)
+    q_start = torch.arange(S + 1, dtype=torch.int32, device=DEV)
+    out = torch.full((S, nh * hd), float("nan"), device=DEV, dtype=torch.bfloat16)
+    scale = 1 / math.sqrt(hd)
+    max_splits = (1500 + split_keys - 1) // split_keys
+    kernels.attention_mma(q, nh, hd, out, pages, bt, positions, q_start, S, scale, window=window, split_keys=split_keys, max_splits=max_splits)
+    torch.cuda.synchronize()
+    assert kernels.status_word(DEV)[0].item() == 0
+    for i, l in enumerate(lens):
+        ref = ref_attention(q[i, :nh * hd].view(nh, hd), ks[i], vs[i], l - 1, scale, window)
+        torch.testing.assert_close(out[i].view(nh, hd).double(), ref, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("split_keys", [0, 128])
+def test_attention_mma_finds_one_far_key(split_keys):
+    """As for the plain kernel: one key among hundreds stands out and the output must be its
+    value row, at page and split edges and at a window's edge, in both launch modes."""
+    from spyinfer_b200 import kernels
+    nh, nkv, hd, page_size, L = 4, 1, 64, 16, 700
+    pages, bt, ks, vs = paged_setup(1, [L], nkv, hd, page_size, torch.bfloat16)
+    q = torch.randn(1, nh * hd, device=DEV).to(torch.bfloat16)
+    pos = torch.tensor([L - 1], dtype=torch.int32, device=DEV)
+    q_start = torch.tensor([0, 1], dtype=torch.int32, device=DEV)
+    out = torch.empty(1, nh * hd, device=DEV, dtype=torch.bfloat16)
+    for window, far in [(None, 0), (None, 15), (None, 16), (None, 127), (None, 128), (None, 511), (None, 699), (300, L - 300), (300, L - 301)]:
+        pg = pages.clone()
+        page, slot = int(bt[0, far // page_size]), far % page_size
+        pg[page, 0, 0, slot] = (60.0 * q[0, :hd].float() / q[0, :hd].float().norm()).to(torch.bfloat16)
+        kernels.attention_mma(q, nh, hd, out, pg, bt, pos, q_start, 1, 1.0, window=window, split_keys=split_keys, max_splits=6 if split_keys else 0)
+        hit = torch.allclose(out[0, :hd].float(), vs[0][far, 0].float(), atol=2e-2)
+        inside = window is None or far > L - 1 - window
+        assert hit == inside, f"window {window}, far key {far}: expected {'a hit' if inside else 'no hit'}"

@@ -94,14 +94,14 @@ MODES = {"whole": "w_", "tail_one_by_one": "t_", "portions": "p_", "mixed": "m_"
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["a", "b", "c"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d"])
 @pytest.mark.parametrize("mode", list(MODES))
 def test_replay_matches_plain(mode, name, dtype, replayed, tiny_models, plain_logits_cache):
     rows, tokens_of = replayed(name, dtype)
     compare(rows, tokens_of, MODES[mode], name, tiny_models, plain_logits_cache, TOL[dtype])
 
 
-@pytest.mark.parametrize("name", ["a", "b", "c"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d"])
 def test_float32_does_not_depend_on_the_cut(name, replayed):
     """In 32-bit every token's arithmetic is arranged to be independent of the batch: the
     same request gives the same logits, to the last bit or nearly so, however it was cut."""
