@@ -117,7 +117,9 @@ class CacheManager:
         if device is not None:
             for g in self.groups:
                 n = g.need
-                g.pages = torch.zeros((len(g.entries), num_pages, 2, n.num_kv_heads, page_size, n.head_dim), dtype=dtype, device=device)
+                # one page more than the pool hands out: the spare page (id num_pages) takes the
+                # writes of the padding rows of a fixed-size (captured) decode batch
+                g.pages = torch.zeros((len(g.entries), num_pages + 1, 2, n.num_kv_heads, page_size, n.head_dim), dtype=dtype, device=device)
         for i, v in enumerate(self._views):
             if v.kind == "paged" and self.groups[v.group].pages is not None:
                 v.pages = self.groups[v.group].pages[self._entry_slot_in_group[i]]
@@ -232,6 +234,11 @@ class CacheManager:
                 g.pool.free(int(row[lp]))
             row[:] = -1
         self._free_slots.append(r.slot)
+
+    @property
+    def spare_page(self) -> int:
+        """Id of the page that no request ever holds (see the pages tensor's allocation)."""
+        return self.num_pages
 
     def block_table(self, rid, group: int = 0) -> np.ndarray:
         return self.groups[group].tables[self._requests[rid].slot]

@@ -85,6 +85,9 @@ class Model:
             mods += part.modules()
         return list(dict.fromkeys(mods))
 
+    def graph_safe(self) -> bool:
+        return all(l.mixer.graph_safe for l in self.layers)
+
     # ---- cache needs -------------------------------------------------------------------------
     def cache_needs(self):
         """Per run-order entry: its mixer's need, and the entry whose cache it reads instead."""

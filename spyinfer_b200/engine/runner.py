@@ -39,10 +39,13 @@ class ModelRunner:
             cache = CacheManager(needs, config.kvcache_block_size, num_pages, config.max_num_seqs, config.max_model_len,
                                  dtype=model.ctx.dtype, device=self.device, cache_of=cache_of)
         self.cache = cache
-        self.stager = BatchStager(self.device, config.max_num_batched_tokens, config.max_num_seqs, cache.width, max(1, cache.num_groups()))
+        self.stager = BatchStager(self.device, max(config.max_num_batched_tokens, config.max_num_seqs), config.max_num_seqs, cache.width, max(1, cache.num_groups()))
         self.vocab_size = model.spec.vocab_size
         self.steps = 0
         self.tokens_run = 0
+        self.graph_steps = 0
+        self._graphs = {}          # decode batch size (padded) -> (graph, logits, kernel launches it holds)
+        self._use_graphs = bool(config.use_cuda_graphs) and model.graph_safe()
 
     def _pages_from_free_memory(self, needs) -> int:
         per_page = CacheManager.bytes_per_page(needs, self.config.kvcache_block_size, self.model.ctx.dtype)
@@ -101,12 +104,85 @@ class ModelRunner:
         for e in entries:
             self.cache.commit(e.request, self.cache.length(e.request) + len(e.tokens))
 
+    # ---- decoding through a captured graph -----------------------------------------------------
+    def _decode_bucket(self, n: int) -> int:
+        b = 1
+        while b < n:
+            b *= 2
+        return min(b, self.config.max_num_seqs)
+
+    def _build_decode_batch(self, entries: Sequence[StepEntry], bucket: int) -> StepBatch:
+        """A batch of ``bucket`` one-token rows at fixed device offsets: the entries first, then
+        padding rows that read and write only the cache's spare page."""
+        cache, S = self.cache, len(entries)
+        token_ids = np.zeros(bucket, np.int32)
+        positions = np.zeros(bucket, np.int32)
+        ctx_len = np.ones(bucket, np.int32)
+        slots = np.zeros(bucket, np.int32)
+        for s, e in enumerate(entries):
+            if not cache.has_request(e.request):
+                cache.add_request(e.request)
+            start = cache.length(e.request)
+            cache.reserve(e.request, start + 1)
+            t = int(e.tokens[0])
+            if not 0 <= t < self.vocab_size:
+                raise StepError(f"request {e.request!r}: token id {t} is outside the vocabulary of {self.vocab_size}")
+            token_ids[s], positions[s], ctx_len[s], slots[s] = t, start, start + 1, cache.slot(e.request)
+        rids = [e.request for e in entries]
+        tables = []
+        for g in range(cache.num_groups()):
+            t = np.full((bucket, cache.width), -1, np.int32)
+            t[:S] = cache.gather_block_tables(rids, g)
+            t[S:, 0] = cache.spare_page
+            tables.append(t)
+        ar = np.arange(bucket + 1, dtype=np.int32)
+        return self.stager.stage(token_ids, positions, ar[:bucket], ar, ctx_len, slots, ar[:bucket], tables, bucket, bucket)
+
+    def _step_graph(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        S = len(entries)
+        bucket = self._decode_bucket(S)
+        batch = self._build_decode_batch(entries, bucket)
+        held = self._graphs.get(bucket)
+        if held is None:
+            # the first step of this size runs eagerly (it also makes every lazy allocation);
+            # the graph is captured from the second on
+            self._graphs[bucket] = "warm"
+            logits = self.model.forward(batch, self.cache)
+        elif held == "warm":
+            torch.cuda.synchronize()
+            before = kernels.launch_count()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                static_logits = self.model.forward(batch, self.cache)
+            self._graphs[bucket] = (graph, static_logits, kernels.launch_count() - before)
+            kernels.count_launches(-(kernels.launch_count() - before))   # captured, not run
+            graph.replay()
+            kernels.count_launches(self._graphs[bucket][2])
+            logits = static_logits
+            self.graph_steps += 1
+        else:
+            graph, static_logits, launches = held
+            graph.replay()
+            kernels.count_launches(launches)
+            logits = static_logits
+            self.graph_steps += 1
+        self.commit(entries)
+        self.steps += 1
+        self.tokens_run += S
+        return logits[:S]
+
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Runs the entries as one batch.  Returns float32 logits ``[wanted, vocab]`` on the
         device, rows in the order of the entries and of each entry's ``want``; None when
-        nothing is wanted."""
+        nothing is wanted.  A batch in which every request brings one token and wants its
+        logits (a decode step) is replayed from a CUDA graph captured for its size; the
+        returned tensor is then the graph's own output buffer, valid until the next step."""
         if not entries:
             return None
+        if self._use_graphs and all(len(e.tokens) == 1 and len(e.want) == 1 and int(e.want[0]) == 0 for e in entries):
+            if len({e.request for e in entries}) != len(entries):
+                raise StepError("a request appears twice in one step")
+            return self._step_graph(entries)
         batch = self.build_batch(entries)
         logits = self.model.forward(batch, self.cache)
         self.commit(entries)

@@ -28,6 +28,8 @@ class Attention(Mixer):
     (None: no q/k norm), ``position`` (a PartSpec or None), ``window`` (None: all keys),
     ``scale`` (None: 1/sqrt(head_dim)), ``prefix``."""
 
+    graph_safe = True
+
     def __init__(self, params, ctx):
         super().__init__(params, ctx)
         self.hidden = int(params["hidden_size"])

@@ -72,6 +72,11 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    #: True when ``forward`` launches the same kernels with the same arguments for every
+    #: batch of one size whose requests bring one token each (no host-side look at the
+    #: batch's content), so that a decode step can be captured in a CUDA graph
+    graph_safe: bool = False
+
     def cache_need(self):
         """A ``PagedCacheNeed``, a ``StateCacheNeed`` or None."""
         return None
