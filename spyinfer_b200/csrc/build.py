@@ -64,7 +64,7 @@ def _source_hash(module: str) -> str:
     h = hashlib.sha256()
     h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS).encode())
     for name in sorted(os.listdir(HERE)):
-        if name.endswith(".cuh") or name == module + ".cu":
+        if name.endswith(".cuh") or name.endswith(".h") or name == module + ".cu":
             with open(os.path.join(HERE, name), "rb") as f:
                 h.update(name.encode())
                 h.update(f.read())

@@ -470,3 +470,55 @@ extern "C" int spy_gemm_tcgen05(const void* A, long long lda, const void* W, lon
     }
     return 0;
 }
+
+// ---------------------------------------------------------------------------------------------
+// The same product for callers that cannot allocate device memory (declared in
+// gemm_tcgen05_static.h; it has no counterpart in the reference).
+//
+// Some callers must not call cudaMalloc or anything that might: code that runs while a CUDA
+// graph is being captured or inside a latency-critical serving loop where an allocation would
+// synchronise the device, plug-ins loaded into a host process that owns all device memory and
+// hands out none, and callers whose memory budget is fixed before the library is loaded.  For
+// them the split-K scratch lives in the library image itself: a file-scope device array that
+// every GPU which loads this library holds from load until the process exits.
+//
+// Limit: SPY_GEMM_STATIC_SCRATCH_FLOATS floats (16 MiB).  A product whose split-K plan needs
+// more is refused with an error; it is not silently run another way.
+//
+// Set-up: the array's name is only a host-side handle; the device address comes from
+// cudaGetSymbolAddress, asked once per device with that device current.  The first call on a
+// device does this, so make that first call before any stream capture begins.
+//
+// Sharing: every call on a device uses the same array and leaves its partial sums there.
+// Nothing has to be cleared between calls, because every element the reduction reads is
+// written earlier in the same call.  Two calls that overlap on the GPU (different streams
+// without an ordering between them) race on the array; order them.
+#include "gemm_tcgen05_static.h"
+
+static __device__ __align__(256) float g_gemm_static_scratch[SPY_GEMM_STATIC_SCRATCH_FLOATS];
+
+extern "C" int spy_gemm_tcgen05_static_scratch(const void* A, long long lda, const void* W, long long ldw, void* C, int c_dtype, long long ldc,
+                                               int M, int N, int K, int* status, cudaStream_t stream)
+{
+    constexpr int MAX_DEVICES = 64;
+    static float* scratch_of_device[MAX_DEVICES] = {nullptr};
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 != 0) SPY_FAIL("gemm_tcgen05_static_scratch: K %d must be a positive multiple of 8", K);
+    int splits;
+    long long need;
+    spy_gemm_tcgen05_plan(M, N, K, 0x7fffffffffffffffLL, &splits, &need);
+    if (need > (long long)SPY_GEMM_STATIC_SCRATCH_FLOATS)
+        SPY_FAIL("gemm_tcgen05_static_scratch: M=%d N=%d K=%d splits K %d ways and needs %lld floats of scratch; the built-in scratch holds %lld",
+                 M, N, K, splits, need, (long long)SPY_GEMM_STATIC_SCRATCH_FLOATS);
+    int device = -1;
+    SPY_CUDA(cudaGetDevice(&device));
+    if (device < 0 || device >= MAX_DEVICES) SPY_FAIL("gemm_tcgen05_static_scratch: device index %d is out of range", device);
+    if (scratch_of_device[device] == nullptr) {
+        float* ptr = nullptr;
+        SPY_CUDA(cudaGetSymbolAddress((void**)&ptr, g_gemm_static_scratch));
+        if (ptr == nullptr) SPY_FAIL("gemm_tcgen05_static_scratch: the built-in scratch has no address on device %d", device);
+        scratch_of_device[device] = ptr;
+    }
+    return spy_gemm_tcgen05(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, scratch_of_device[device], (long long)SPY_GEMM_STATIC_SCRATCH_FLOATS, status,
+                            stream);
+}

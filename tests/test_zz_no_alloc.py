@@ -1,0 +1,64 @@
+"""The allocation-free entry point of the tensor-core matrix product, called the way its
+users call it: through the exported C symbol of the shared library, with raw device pointers.
+
+Who needs it: callers that may not allocate device memory, because they run while a graph
+is being captured, sit in a loop where an allocation would stall the device, or live in a
+host process that owns all device memory.  The split-K scratch is a fixed array inside the
+library; this test checks that two calls in a row give what the ordinary entry point gives
+(the second call finds the first call's partial sums in the array and must not be disturbed
+by them), and that a size beyond the array is refused."""
+import ctypes
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def static_entry():
+    from spyinfer_b200.csrc import build
+    lib = build.load("gemm_tcgen05")
+    fn = lib.spy_gemm_tcgen05_static_scratch
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.c_void_p, ctypes.c_longlong, ctypes.c_void_p, ctypes.c_longlong, ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong,
+                   ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]
+    err = lib.spy_gemm_tcgen05_last_error
+    err.restype = ctypes.c_char_p
+    return fn, err
+
+
+def test_static_scratch_entry_matches_the_ordinary_one_twice_in_a_row():
+    from spyinfer_b200 import kernels
+    fn, err = static_entry()
+    status = kernels.status_word(DEV)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    # both shapes split K (few output tiles); the second is smaller, so stale partial sums of
+    # the first call lie around and beyond the region the second call uses
+    for seed, (M, N, K) in enumerate([(24, 1024, 4096), (5, 384, 2048)]):
+        torch.manual_seed(seed)
+        a = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+        w = (torch.randn(N, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
+        want = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+        kernels.gemm_tcgen05(a, w, want)
+        got = torch.full((M, N), float("nan"), device=DEV, dtype=torch.bfloat16)
+        rc = fn(a.data_ptr(), K, w.data_ptr(), K, got.data_ptr(), 1, N, M, N, K, status.data_ptr(), stream)
+        assert rc == 0, err().decode()
+        torch.cuda.synchronize()
+        assert status[0].item() == 0
+        torch.testing.assert_close(got.float(), want.float(), rtol=1.6e-2, atol=2e-3)
+        ref = (a.float() @ w.float().t()).to(torch.bfloat16).float()
+        torch.testing.assert_close(got.float(), ref, rtol=1.6e-2, atol=2e-3)
+
+
+def test_static_scratch_entry_refuses_what_does_not_fit():
+    fn, err = static_entry()
+    M, N, K = 1024, 4096, 8192           # 128 output tiles split 3 ways: 3 * 1024 * 4096 floats > 4 Mi
+    a = torch.zeros(M, K, device=DEV, dtype=torch.bfloat16)
+    w = torch.zeros(N, K, device=DEV, dtype=torch.bfloat16)
+    out = torch.zeros(M, N, device=DEV, dtype=torch.bfloat16)
+    rc = fn(a.data_ptr(), K, w.data_ptr(), K, out.data_ptr(), 1, N, M, N, K, None, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc != 0
+    msg = err().decode()
+    assert "scratch" in msg and "4194304" in msg
