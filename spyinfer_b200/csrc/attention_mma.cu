@@ -1,6 +1,7 @@
 // bfloat16 attention over the paged cache on the tensor cores (mma.sync m16n8k16), keys and
-// values streamed straight from the pages into the instruction's operand registers with
-// 16-byte loads: no shared-memory staging.  One warp owns a tile of 16 rows = the G query
+// values streamed from the pages in exactly the order of the instruction's operand registers:
+// every thread copies its own 16-byte pieces with cp.async into a private ring in shared
+// memory (an asynchronous extension of its registers) and never reads another thread's.  One warp owns a tile of 16 rows = the G query
 // heads of one key/value head for 16 / Gp consecutive tokens of one sequence (Gp = G rounded
 // up to a power of two), so every key and value row is read once for all G heads.
 //
@@ -66,85 +67,194 @@ struct Params {
     float scale_log2;
 };
 
-// Row of the K (kv = 0) or V (kv = 1) plane that holds key j of this sequence, or null when
-// the block table names no page of the pool for it.
-__device__ __forceinline__ const bf16* kv_row(const Params& p, const int* bt, int kvh, int j, int kv, int HD, int tok_for_status)
-{
-    const int lp = j / p.page_size;
-    const int page = lp < p.table_width ? bt[lp] : -1;
-    if (page < 0 || page >= p.num_pages) {
-        report_status(p.status, SPY_STATUS_BAD_PAGE, tok_for_status);
-        return nullptr;
-    }
-    return p.pages + ((((size_t)page * 2 + kv) * p.nkv + kvh) * p.page_size + (j - lp * p.page_size)) * HD;
-}
-
 // State of one warp's 16-row tile while it walks a range of keys.
 template <int HD> struct TileState {
     float o[HD / 64][8][4];   // output accumulators: [d set of 64][n-tile][c0..c3]
     float m[2], l[2];         // running max (log2 domain) and this thread's share of the sum, rows g and g + 8
 };
 
+constexpr int RING = 3;   // stages of the per-thread copy ring
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* src, bool valid)
+{
+    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    const int bytes = valid ? 16 : 0;   // 0 source bytes: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Looks a key's page up: in `bt_s` (shared copy of the block table from logical page
+// `bt_first` on) when it is given, else in the global table.
+__device__ __forceinline__ int page_of(const Params& p, const int* bt, const int* bt_s, int bt_first, int lp)
+{
+    if (bt_s != nullptr) return bt_s[lp - bt_first];
+    return lp < p.table_width ? bt[lp] : -1;
+}
+
 // Walks keys [key_lo, key_hi] (inclusive, absolute positions) for one tile.
 // row_pos / row_lo: last and first visible key of rows g and g + 8 (row_pos < 0: row unused).
-template <int HD>
-__device__ __forceinline__ void walk_keys(const Params& p, const int* bt, int kvh, const uint4 (&qf)[2][HD / 32], const int (&row_pos)[2],
-                                          const int (&row_lo)[2], int key_lo, int key_hi, TileState<HD>& st, int tok_for_status)
+// Every thread copies exactly the 16-byte pieces it will use itself (its operand fragments
+// of 16 keys: 8 pieces of K, 8 of V for head_dim 128) into its own slots of a ring in shared
+// memory with cp.async, RING - 1 groups of 16 keys ahead of the one it computes on; no
+// thread reads another thread's slots, so the ring needs no barrier.
+// ring: [RING][2 * HD / 16 pieces][blockDim.x] of 16 bytes.
+// PAGE16: the page size is a multiple of 16, so the 16 keys of a group share one page and
+// one block-table lookup serves the whole group.
+// Groups whose 16 keys are visible to every row of the tile skip the masking, and the
+// running output is rescaled only in iterations in which some row's maximum grew.
+template <int HD, bool PAGE16>
+__device__ __forceinline__ void walk_keys(const Params& p, const int* bt, const int* bt_s, int bt_first, int kvh, const uint4 (&qf)[2][HD / 32],
+                                          const int (&row_pos)[2], const int (&row_lo)[2], int key_lo, int key_hi, TileState<HD>& st,
+                                          uint4* ring, int tok_for_status)
 {
     const int lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
     constexpr int KC = HD / 32;   // 32-element chunks of head_dim
     constexpr int DS = HD / 64;   // sets of 64 output columns
-    for (int kb = key_lo & ~15; kb <= key_hi; kb += 16) {
-        // ---- loads: K rows of keys kb + g and kb + 8 + g; V rows of keys kb + {2t4, 2t4+1, 2t4+8, 2t4+9}
-        uint4 kf[2][KC];
+    constexpr int PIECES = 2 * KC + 4 * DS;
+    const int nthreads = blockDim.x;
+    const int kb_first = key_lo & ~15;
+    const int n_iter = (key_hi - kb_first) / 16 + 1;
+    const size_t plane = (size_t)p.nkv * p.page_size * HD;   // elements from a page's K plane to its V plane
+    // keys every used row of the tile can see: [all_lo, all_hi]
+    int all_lo = key_lo, all_hi = key_hi;
 #pragma unroll
-        for (int tile = 0; tile < 2; ++tile) {
-            const int j = kb + tile * 8 + g;
-            const bf16* row = (j >= key_lo && j <= key_hi) ? kv_row(p, bt, kvh, j, 0, HD, tok_for_status) : nullptr;
-#pragma unroll
-            for (int c = 0; c < KC; ++c) kf[tile][c] = row ? load16(row + c * 32 + t4 * 8) : make_uint4(0, 0, 0, 0);
+    for (int r = 0; r < 2; ++r)
+        if (row_pos[r] >= 0) {
+            all_lo = max(all_lo, row_lo[r]);
+            all_hi = min(all_hi, row_pos[r]);
         }
-        uint4 vf[4][DS];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int j = kb + 2 * t4 + (i & 1) + (i >> 1) * 8;
-            const bf16* row = (j >= key_lo && j <= key_hi) ? kv_row(p, bt, kvh, j, 1, HD, tok_for_status) : nullptr;
-#pragma unroll
-            for (int ds = 0; ds < DS; ++ds) vf[i][ds] = row ? load16(row + ds * 64 + g * 8) : make_uint4(0, 0, 0, 0);
+    all_lo = __reduce_max_sync(0xffffffffu, all_lo);
+    all_hi = __reduce_min_sync(0xffffffffu, all_hi);
+
+    auto page_base = [&](int lp) -> const bf16* {   // K plane of this kv head in logical page lp, or null
+        const int page = page_of(p, bt, bt_s, bt_first, lp);
+        if (page < 0 || page >= p.num_pages) {
+            report_status(p.status, SPY_STATUS_BAD_PAGE, tok_for_status);
+            return nullptr;
         }
+        return p.pages + (((size_t)page * 2) * p.nkv + kvh) * p.page_size * HD;
+    };
+
+    auto issue = [&](int it) {
+        if (it < n_iter) {
+            const int kb = kb_first + it * 16;
+            uint4* slot = ring + ((size_t)(it % RING) * PIECES) * nthreads + threadIdx.x;
+            const bf16* group_base = nullptr;
+            int group_slot = 0;
+            if constexpr (PAGE16) {
+                const int lp = kb / p.page_size;
+                group_base = page_base(lp);
+                group_slot = kb - lp * p.page_size;
+            }
+#pragma unroll
+            for (int tile = 0; tile < 2; ++tile) {
+                const int j = kb + tile * 8 + g;
+                bool ok = j >= key_lo && j <= key_hi;
+                const bf16* row = p.pages;
+                if constexpr (PAGE16) {
+                    ok = ok && group_base != nullptr;
+                    if (ok) row = group_base + (size_t)(group_slot + tile * 8 + g) * HD;
+                } else if (ok) {
+                    const int lp = j / p.page_size;
+                    const bf16* base = page_base(lp);
+                    ok = base != nullptr;
+                    if (ok) row = base + (size_t)(j - lp * p.page_size) * HD;
+                }
+#pragma unroll
+                for (int c = 0; c < KC; ++c) cp_async16(slot + (size_t)(tile * KC + c) * nthreads, row + c * 32 + t4 * 8, ok);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int off = 2 * t4 + (i & 1) + (i >> 1) * 8;
+                const int j = kb + off;
+                bool ok = j >= key_lo && j <= key_hi;
+                const bf16* row = p.pages;
+                if constexpr (PAGE16) {
+                    ok = ok && group_base != nullptr;
+                    if (ok) row = group_base + plane + (size_t)(group_slot + off) * HD;
+                } else if (ok) {
+                    const int lp = j / p.page_size;
+                    const bf16* base = page_base(lp);
+                    ok = base != nullptr;
+                    if (ok) row = base + plane + (size_t)(j - lp * p.page_size) * HD;
+                }
+#pragma unroll
+                for (int ds = 0; ds < DS; ++ds) cp_async16(slot + (size_t)(2 * KC + i * DS + ds) * nthreads, row + ds * 64 + g * 8, ok);
+            }
+        }
+        cp_async_commit();   // an empty group keeps the count of groups in step with the iterations
+    };
+
+#pragma unroll
+    for (int s = 0; s < RING - 1; ++s) issue(s);
+    for (int it = 0; it < n_iter; ++it) {
+        issue(it + RING - 1);
+        cp_async_wait<RING - 1>();
+        const int kb = kb_first + it * 16;
+        const uint4* slot = ring + ((size_t)(it % RING) * PIECES) * nthreads + threadIdx.x;
         // ---- scores of 16 rows x 16 keys
         float s[2][4];
 #pragma unroll
-        for (int tile = 0; tile < 2; ++tile) {
-            s[tile][0] = s[tile][1] = s[tile][2] = s[tile][3] = 0.f;
+        for (int tile = 0; tile < 2; ++tile) s[tile][0] = s[tile][1] = s[tile][2] = s[tile][3] = 0.f;
 #pragma unroll
-            for (int c = 0; c < KC; ++c) {
-                mma_bf16(s[tile], qf[0][c].x, qf[1][c].x, qf[0][c].y, qf[1][c].y, kf[tile][c].x, kf[tile][c].y);
-                mma_bf16(s[tile], qf[0][c].z, qf[1][c].z, qf[0][c].w, qf[1][c].w, kf[tile][c].z, kf[tile][c].w);
-            }
+        for (int c = 0; c < KC; ++c) {
+            const uint4 k0 = slot[(size_t)c * nthreads], k1 = slot[(size_t)(KC + c) * nthreads];
+            mma_bf16(s[0], qf[0][c].x, qf[1][c].x, qf[0][c].y, qf[1][c].y, k0.x, k0.y);
+            mma_bf16(s[1], qf[0][c].x, qf[1][c].x, qf[0][c].y, qf[1][c].y, k1.x, k1.y);
+            mma_bf16(s[0], qf[0][c].z, qf[1][c].z, qf[0][c].w, qf[1][c].w, k0.z, k0.w);
+            mma_bf16(s[1], qf[0][c].z, qf[1][c].z, qf[0][c].w, qf[1][c].w, k1.z, k1.w);
         }
-        // ---- mask, running max
+        // ---- scale, mask (only in groups that some row cannot see whole), running max
+        const bool whole = kb >= all_lo && kb + 15 <= all_hi;   // uniform over the warp
         float mx[2] = {-INFINITY, -INFINITY};
+        if (whole) {
 #pragma unroll
-        for (int tile = 0; tile < 2; ++tile)
+            for (int tile = 0; tile < 2; ++tile)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int r = e >> 1;                              // c0, c1: row g; c2, c3: row g + 8
-                const int j = kb + tile * 8 + 2 * t4 + (e & 1);
-                const bool ok = j <= row_pos[r] && j >= row_lo[r] && j >= key_lo && j <= key_hi;
-                const float v = ok ? s[tile][e] * p.scale_log2 : -INFINITY;
-                s[tile][e] = v;
-                mx[r] = fmaxf(mx[r], v);
-            }
-        float alpha[2];
+                for (int e = 0; e < 4; ++e) {
+                    s[tile][e] *= p.scale_log2;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], s[tile][e]);
+                }
+        } else {
+#pragma unroll
+            for (int tile = 0; tile < 2; ++tile)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int r = e >> 1;                              // c0, c1: row g; c2, c3: row g + 8
+                    const int j = kb + tile * 8 + 2 * t4 + (e & 1);
+                    const bool ok = j <= row_pos[r] && j >= row_lo[r] && j >= key_lo && j <= key_hi;
+                    const float v = ok ? s[tile][e] * p.scale_log2 : -INFINITY;
+                    s[tile][e] = v;
+                    mx[r] = fmaxf(mx[r], v);
+                }
+        }
+        bool grew = false;
+        float m_new[2];
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
             mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
             mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-            const float m_new = fmaxf(st.m[r], mx[r]);
-            alpha[r] = m_new == -INFINITY ? 1.f : exp2f(st.m[r] - m_new);   // st.m = -inf gives 0
-            st.m[r] = m_new;
-            st.l[r] *= alpha[r];
+            m_new[r] = fmaxf(st.m[r], mx[r]);
+            grew = grew || m_new[r] != st.m[r];
+        }
+        if (__any_sync(0xffffffffu, grew)) {
+            float alpha[2];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                alpha[r] = m_new[r] == -INFINITY ? 1.f : exp2f(st.m[r] - m_new[r]);   // st.m = -inf gives 0
+                st.m[r] = m_new[r];
+                st.l[r] *= alpha[r];
+            }
+#pragma unroll
+            for (int ds = 0; ds < DS; ++ds)
+#pragma unroll
+                for (int jt = 0; jt < 8; ++jt) {
+                    st.o[ds][jt][0] *= alpha[0];
+                    st.o[ds][jt][1] *= alpha[0];
+                    st.o[ds][jt][2] *= alpha[1];
+                    st.o[ds][jt][3] *= alpha[1];
+                }
         }
         // ---- probabilities
         uint32_t pa[4];   // A fragment of P: a0 (row g, keys 2t4..), a1 (row g+8), a2 (row g, keys 8+2t4..), a3 (row g+8)
@@ -164,21 +274,22 @@ __device__ __forceinline__ void walk_keys(const Params& p, const int* bt, int kv
             pa[2] = pack_bf16(pr[1][0], pr[1][1]);
             pa[3] = pack_bf16(pr[1][2], pr[1][3]);
         }
-        // ---- O = O * alpha + P V
+        // ---- O += P V
 #pragma unroll
-        for (int ds = 0; ds < DS; ++ds)
+        for (int ds = 0; ds < DS; ++ds) {
+            uint4 vf[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) vf[i] = slot[(size_t)(2 * KC + i * DS + ds) * nthreads];
 #pragma unroll
             for (int jt = 0; jt < 8; ++jt) {
-                st.o[ds][jt][0] *= alpha[0];
-                st.o[ds][jt][1] *= alpha[0];
-                st.o[ds][jt][2] *= alpha[1];
-                st.o[ds][jt][3] *= alpha[1];
                 const uint32_t sel = (jt & 1) ? 0x7632u : 0x5410u;   // upper or lower halves of the two words
-                const uint32_t b0 = __byte_perm(word(vf[0][ds], jt >> 1), word(vf[1][ds], jt >> 1), sel);
-                const uint32_t b1 = __byte_perm(word(vf[2][ds], jt >> 1), word(vf[3][ds], jt >> 1), sel);
+                const uint32_t b0 = __byte_perm(word(vf[0], jt >> 1), word(vf[1], jt >> 1), sel);
+                const uint32_t b1 = __byte_perm(word(vf[2], jt >> 1), word(vf[3], jt >> 1), sel);
                 mma_bf16(st.o[ds][jt], pa[0], pa[1], pa[2], pa[3], b0, b1);
             }
+        }
     }
+    cp_async_wait<0>();
 }
 
 template <int HD> __device__ __forceinline__ void init_state(TileState<HD>& st)
@@ -245,6 +356,7 @@ __device__ __forceinline__ void store_rows(const Params& p, const TileState<HD>&
 template <int HD>
 __global__ void __launch_bounds__(WARPS * 32, 2) attention_tiles_kernel(const Params p)
 {
+    extern __shared__ uint4 ring_smem[];
     __shared__ int s_seq, s_tok0;
     const int tokens_per_tile = 16 / p.Gp, tokens_per_block = WARPS * tokens_per_tile;
     if (threadIdx.x == 0) {
@@ -283,7 +395,8 @@ __global__ void __launch_bounds__(WARPS * 32, 2) attention_tiles_kernel(const Pa
     const int key_lo = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
     TileState<HD> st;
     init_state<HD>(st);
-    walk_keys<HD>(p, bt, kvh, qf, row_pos, row_lo, key_lo, last_pos, st, tok0);
+    if (p.page_size % 16 == 0) walk_keys<HD, true>(p, bt, nullptr, 0, kvh, qf, row_pos, row_lo, key_lo, last_pos, st, ring_smem, tok0);
+    else walk_keys<HD, false>(p, bt, nullptr, 0, kvh, qf, row_pos, row_lo, key_lo, last_pos, st, ring_smem, tok0);
     store_rows<HD>(p, st, row_tok, row_head);
 }
 
@@ -291,9 +404,13 @@ __global__ void __launch_bounds__(WARPS * 32, 2) attention_tiles_kernel(const Pa
 template <int HD>
 __global__ void __launch_bounds__(WARPS * 32, 2) attention_split_kernel(const Params p)
 {
-    extern __shared__ float smem[];   // [WARPS][16][HD] outputs, then [WARPS][16][2] (m, l)
-    float* s_o = smem;
-    float* s_ml = smem + WARPS * 16 * HD;
+    // shared memory: the copy ring, then this split's slice of the block table; after the walk
+    // the ring's space is reused for the merge: [WARPS][16][HD] outputs, then [WARPS][16][2] (m, l)
+    extern __shared__ uint4 ring_smem[];
+    constexpr int PIECES = 2 * (HD / 32) + 4 * (HD / 64);
+    float* s_o = reinterpret_cast<float*>(ring_smem);
+    float* s_ml = s_o + WARPS * 16 * HD;
+    int* bt_s = reinterpret_cast<int*>(ring_smem + (size_t)RING * PIECES * WARPS * 32);
     const int seq = blockIdx.x, kvh = blockIdx.y, z = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
     const int tok = p.q_start[seq];
@@ -303,6 +420,8 @@ __global__ void __launch_bounds__(WARPS * 32, 2) attention_split_kernel(const Pa
     if (z < z_first || z > z_last) return;
     const int key_lo = max(lo, z * p.split_keys), key_hi = min(pos, (z + 1) * p.split_keys - 1);
     const int* bt = p.block_table + (size_t)seq * p.table_width;
+    const int bt_first = key_lo / p.page_size, bt_last = key_hi / p.page_size;
+    for (int i = bt_first + threadIdx.x; i <= bt_last; i += WARPS * 32) bt_s[i - bt_first] = i < p.table_width ? bt[i] : -1;
 
     uint4 qf[2][HD / 32];
     int row_tok[2], row_head[2], row_pos[2], row_lo[2];
@@ -312,12 +431,17 @@ __global__ void __launch_bounds__(WARPS * 32, 2) attention_split_kernel(const Pa
         row_pos[r] = row_tok[r] >= 0 ? pos : -1;
         row_lo[r] = lo;
     }
+    __syncthreads();   // the block table slice is in shared memory
     // the four warps share the split: warp w takes its w-th quarter
     const int sub = p.split_keys / WARPS;
     const int w_lo = max(key_lo, z * p.split_keys + warp * sub), w_hi = min(key_hi, z * p.split_keys + (warp + 1) * sub - 1);
     TileState<HD> st;
     init_state<HD>(st);
-    if (w_lo <= w_hi) walk_keys<HD>(p, bt, kvh, qf, row_pos, row_lo, w_lo, w_hi, st, tok);
+    if (w_lo <= w_hi) {
+        if (p.page_size % 16 == 0) walk_keys<HD, true>(p, bt, bt_s, bt_first, kvh, qf, row_pos, row_lo, w_lo, w_hi, st, ring_smem, tok);
+        else walk_keys<HD, false>(p, bt, bt_s, bt_first, kvh, qf, row_pos, row_lo, w_lo, w_hi, st, ring_smem, tok);
+    }
+    __syncthreads();   // every warp is done with the ring before it is reused
 
     // ---- merge the four warps in shared memory
 #pragma unroll
@@ -431,8 +555,15 @@ extern "C" int spy_attention_mma(const void* q, long long q_row_stride, void* ou
         const long long blocks = (tokens + tokens_per_block - 1) / tokens_per_block + seqs;
         if (blocks > 0x7fffffffLL || nkv > 65535) SPY_FAIL("attention_mma: the batch exceeds the grid limits");
         dim3 grid((unsigned)blocks, nkv);
-        if (hd == 64) attention_tiles_kernel<64><<<grid, WARPS * 32, 0, stream>>>(p);
-        else attention_tiles_kernel<128><<<grid, WARPS * 32, 0, stream>>>(p);
+        const size_t ring_bytes = (size_t)RING * (2 * (hd / 32) + 4 * (hd / 64)) * WARPS * 32 * sizeof(uint4);
+        static bool tiles_configured = false;
+        if (!tiles_configured) {
+            SPY_CUDA(cudaFuncSetAttribute(attention_tiles_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+            SPY_CUDA(cudaFuncSetAttribute(attention_tiles_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+            tiles_configured = true;
+        }
+        if (hd == 64) attention_tiles_kernel<64><<<grid, WARPS * 32, ring_bytes, stream>>>(p);
+        else attention_tiles_kernel<128><<<grid, WARPS * 32, ring_bytes, stream>>>(p);
         SPY_CHECK_LAUNCH("attention_mma (tiles)");
         return 0;
     }
@@ -446,17 +577,19 @@ extern "C" int spy_attention_mma(const void* q, long long q_row_stride, void* ou
     p.part_ml = scratch ? scratch + (size_t)seqs * nh * max_splits * hd : nullptr;
     if (seqs > 0x7fffffff || nkv > 65535) SPY_FAIL("attention_mma: the batch exceeds the grid limits");
     dim3 grid(seqs, nkv, max_splits);
-    const size_t smem = (size_t)WARPS * 16 * (hd + 2) * sizeof(float);
-    if (hd == 64) {
-        attention_split_kernel<64><<<grid, WARPS * 32, smem, stream>>>(p);
-    } else {
-        static bool configured = false;
-        if (!configured) {
-            SPY_CUDA(cudaFuncSetAttribute(attention_split_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            configured = true;
-        }
-        attention_split_kernel<128><<<grid, WARPS * 32, smem, stream>>>(p);
+    const size_t ring_bytes = (size_t)RING * (2 * (hd / 32) + 4 * (hd / 64)) * WARPS * 32 * sizeof(uint4);
+    const size_t merge_bytes = (size_t)WARPS * 16 * (hd + 2) * sizeof(float);
+    const size_t table_bytes = (size_t)(split_keys + 2) * sizeof(int);   // page_size 1 is the worst case
+    const size_t smem = (ring_bytes > merge_bytes ? ring_bytes : merge_bytes) + table_bytes;
+    if (smem > 110 * 1024) SPY_FAIL("attention_mma: split_keys %d needs %zu bytes of shared memory (limit %d)", split_keys, smem, 110 * 1024);
+    static bool configured = false;
+    if (!configured) {
+        SPY_CUDA(cudaFuncSetAttribute(attention_split_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024));
+        SPY_CUDA(cudaFuncSetAttribute(attention_split_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024));
+        configured = true;
     }
+    if (hd == 64) attention_split_kernel<64><<<grid, WARPS * 32, smem, stream>>>(p);
+    else attention_split_kernel<128><<<grid, WARPS * 32, smem, stream>>>(p);
     SPY_CHECK_LAUNCH("attention_mma (split)");
     if (max_splits > 1) {
         dim3 mgrid(seqs, nh);

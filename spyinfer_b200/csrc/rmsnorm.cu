@@ -1,72 +1,135 @@
 // RMSNorm, optionally fused with the residual sum and with a row gather.
-//   v   = x[row] (+ delta[row])                   32-bit sum
+//   v   = x[row] (+ delta[row], itself possibly a sum of split-K partial products)   32-bit sums
 //   x[row] = v                                    when write_back (the residual stream)
 //   out = v * (1 / sqrt(mean(v^2) + eps)) * w     32-bit statistics, plain weight
 // Formula of the reference: spymaster2h/spyinfer src/backends/cpu/x64/kernels.cpp:168-180
 // (its CUDA twin: src/backends/cuda/native/common.cuh:57-188, which needs len % 8 == 0 and
-// launches a separate add kernel for the residual).  Any row length works here.
+// launches a separate add kernel for the residual).  Any row length works here; rows whose
+// length is a multiple of 4 take 16- and 8-byte accesses.
 #include "common.cuh"
 
 SPY_MODULE(spy_rmsnorm)
 
-template <typename TX, typename TD, typename TW, typename TO>
-__global__ void rmsnorm_kernel(TX* x, const TD* __restrict__ delta, const int* __restrict__ rows, const TW* __restrict__ w,
-                               TO* __restrict__ out, int len, float eps, int write_back)
+template <typename T> struct Quad;
+template <> struct Quad<float> {
+    static __device__ __forceinline__ void load(const float* p, float (&v)[4])
+    {
+        const float4 x = *reinterpret_cast<const float4*>(p);
+        v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float (&v)[4]) { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+};
+template <> struct Quad<bf16> {
+    static __device__ __forceinline__ void load(const bf16* p, float (&v)[4])
+    {
+        const uint2 x = *reinterpret_cast<const uint2*>(p);
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&x.x), b = *reinterpret_cast<const __nv_bfloat162*>(&x.y);
+        v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
+    }
+    static __device__ __forceinline__ void store(bf16* p, const float (&v)[4])
+    {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+        uint2 x;
+        x.x = *reinterpret_cast<uint32_t*>(&a);
+        x.y = *reinterpret_cast<uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(p) = x;
+    }
+};
+
+template <typename TX, typename TD, typename TW, typename TO, bool VEC>
+__global__ void rmsnorm_kernel(TX* x, const TD* __restrict__ delta, int delta_splits, long long delta_split_stride, const int* __restrict__ rows,
+                               const TW* __restrict__ w, TO* __restrict__ out, int len, float eps, int write_back)
 {
     extern __shared__ float row_buf[];  // len floats, then 33 of scratch
     float* scratch = row_buf + len;
     const int src_row = rows ? rows[blockIdx.x] : blockIdx.x;
     TX* xr = x + (size_t)src_row * len;
     const TD* dr = delta ? delta + (size_t)src_row * len : nullptr;
+    TO* orow = out + (size_t)blockIdx.x * len;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < len; i += blockDim.x) {
-        float v = to_f32(xr[i]);
-        if (dr) v += to_f32(dr[i]);
-        row_buf[i] = v;
-        ss += v * v;
+    if constexpr (VEC) {
+        for (int i = threadIdx.x * 4; i < len; i += blockDim.x * 4) {
+            float v[4];
+            Quad<TX>::load(xr + i, v);
+            if (dr) {
+                for (int s = 0; s < delta_splits; ++s) {
+                    float d[4];
+                    Quad<TD>::load(dr + (size_t)s * delta_split_stride + i, d);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) v[e] += d[e];
+                }
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                row_buf[i + e] = v[e];
+                ss += v[e] * v[e];
+            }
+            if (write_back) Quad<TX>::store(xr + i, v);
+        }
+    } else {
+        for (int i = threadIdx.x; i < len; i += blockDim.x) {
+            float v = to_f32(xr[i]);
+            if (dr)
+                for (int s = 0; s < delta_splits; ++s) v += to_f32(dr[(size_t)s * delta_split_stride + i]);
+            row_buf[i] = v;
+            ss += v * v;
+            if (write_back) xr[i] = from_f32<TX>(v);
+        }
     }
     ss = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(ss / (float)len + eps);
-    TO* orow = out + (size_t)blockIdx.x * len;
-    for (int i = threadIdx.x; i < len; i += blockDim.x) {
-        const float v = row_buf[i];
-        if (write_back) xr[i] = from_f32<TX>(v);
-        orow[i] = from_f32<TO>((inv * v) * to_f32(w[i]));
+    if constexpr (VEC) {
+        for (int i = threadIdx.x * 4; i < len; i += blockDim.x * 4) {
+            float wv[4], o[4];
+            Quad<TW>::load(w + i, wv);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o[e] = (inv * row_buf[i + e]) * wv[e];
+            Quad<TO>::store(orow + i, o);
+        }
+    } else {
+        for (int i = threadIdx.x; i < len; i += blockDim.x) orow[i] = from_f32<TO>((inv * row_buf[i]) * to_f32(w[i]));
     }
 }
 
 template <typename TX, typename TD, typename TW, typename TO>
-static int launch(void* x, const void* delta, const int* rows, const void* w, void* out, int n, int len, float eps, int write_back,
-                  cudaStream_t stream)
+static int launch(void* x, const void* delta, int delta_splits, long long delta_split_stride, const int* rows, const void* w, void* out, int n,
+                  int len, float eps, int write_back, cudaStream_t stream)
 {
     const size_t smem = (size_t)(len + 33) * sizeof(float);
-    auto kernel = rmsnorm_kernel<TX, TD, TW, TO>;
+    const bool vec = len % 4 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(delta) | reinterpret_cast<uintptr_t>(w) |
+                                       reinterpret_cast<uintptr_t>(out)) & 15) == 0 && delta_split_stride % 4 == 0;
+    auto kernel = vec ? rmsnorm_kernel<TX, TD, TW, TO, true> : rmsnorm_kernel<TX, TD, TW, TO, false>;
     if (smem > 48 * 1024) {
         if (smem > 227 * 1024) SPY_FAIL("rmsnorm: a row of %d elements does not fit in shared memory (limit %d)", len, (227 * 1024) / 4 - 33);
         SPY_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     }
-    const int threads = len >= 2048 ? 512 : (len >= 512 ? 256 : 128);
-    kernel<<<n, threads, smem, stream>>>((TX*)x, (const TD*)delta, rows, (const TW*)w, (TO*)out, len, eps, write_back);
+    int threads = vec ? (len / 4 + 31) / 32 * 32 : len;
+    threads = threads < 64 ? 64 : (threads > 1024 ? 1024 : (threads + 31) / 32 * 32);
+    kernel<<<n, threads, smem, stream>>>((TX*)x, (const TD*)delta, delta_splits, delta_split_stride, rows, (const TW*)w, (TO*)out, len, eps,
+                                         write_back);
     SPY_CHECK_LAUNCH("rmsnorm");
     return 0;
 }
 
-// x: [*, len] of x_dtype; delta: null or [*, len] of delta_dtype, added to x; rows: null or
-// n row indices (gather); w: [len] of w_dtype; out: [n, len] of out_dtype.  write_back
-// stores the sum into x and needs rows == null.
-extern "C" int spy_rmsnorm(void* x, int x_dtype, const void* delta, int delta_dtype, const int* rows, const void* w, int w_dtype,
-                           void* out, int out_dtype, int n, int len, float eps, int write_back, cudaStream_t stream)
+// x: [*, len] of x_dtype; delta: null or delta_splits stacked [*, len] arrays of delta_dtype
+// (delta_split_stride elements apart), all added to x in order; rows: null or n row indices
+// (gather); w: [len] of w_dtype; out: [n, len] of out_dtype.  write_back stores the sum into
+// x and needs rows == null.
+extern "C" int spy_rmsnorm(void* x, int x_dtype, const void* delta, int delta_dtype, int delta_splits, long long delta_split_stride,
+                           const int* rows, const void* w, int w_dtype, void* out, int out_dtype, int n, int len, float eps, int write_back,
+                           cudaStream_t stream)
 {
     if (n <= 0) return 0;
     if (len <= 0) SPY_FAIL("rmsnorm: row length %d must be positive", len);
     if (write_back && rows) SPY_FAIL("rmsnorm: write_back with a row gather is not defined");
+    if (delta && delta_splits <= 0) SPY_FAIL("rmsnorm: delta_splits %d must be positive", delta_splits);
     if (write_back && !delta) write_back = 0;
-    if (!delta) delta_dtype = x_dtype;
+    if (!delta) { delta_dtype = x_dtype; delta_splits = 0; delta_split_stride = 0; }
     SPY_DISPATCH_DTYPE(x_dtype, TX, {
         SPY_DISPATCH_DTYPE(delta_dtype, TD, {
             SPY_DISPATCH_DTYPE(w_dtype, TW, {
                 SPY_DISPATCH_DTYPE(out_dtype, TO, {
-                    return launch<TX, TD, TW, TO>(x, delta, rows, w, out, n, len, eps, write_back, stream);
+                    return launch<TX, TD, TW, TO>(x, delta, delta_splits, delta_split_stride, rows, w, out, n, len, eps, write_back, stream);
                 })
             })
         })

@@ -1,10 +1,12 @@
-// Next-token choice from 32-bit logits, one block per row.
+// Next-token choice from 32-bit logits.
 //   temperature == 0: argmax, lowest index on ties (the reference's only sampler:
 //     spymaster2h/spyinfer src/engine/model_runner.cpp:120-134, std::max_element on the host).
 //   temperature  > 0: a draw from softmax(logits / temperature) by the Gumbel-max rule:
 //     argmax_i (logits[i] / temperature - log(-log(u_i))), u_i uniform in (0, 1) from a
 //     counter-based generator keyed by (seed, draw, i).  A row's token depends only on its
 //     logits, seed and draw number, never on the rest of the batch.
+// Two stages so that a row of a large vocabulary is read by many blocks: every block finds
+// the best of its slice of the row, then one block per row picks among the slices' bests.
 #include "common.cuh"
 
 SPY_MODULE(spy_sampling)
@@ -17,58 +19,87 @@ __device__ __forceinline__ uint64_t mix64(uint64_t z)
     return z ^ (z >> 31);
 }
 
-__device__ __forceinline__ float uniform_open(uint64_t seed, uint64_t draw, uint32_t index)
+__device__ __forceinline__ float uniform_open(uint64_t key, uint32_t index)
 {
-    const uint64_t r = mix64(mix64(seed ^ mix64(draw)) + index);
+    const uint64_t r = mix64(key + index);
     return ((float)(uint32_t)(r >> 40) + 0.5f) * (1.0f / 16777216.0f);  // 24 bits, never 0 or 1
 }
 
-__global__ void sample_kernel(const float* __restrict__ logits, long long row_stride, int vocab, const float* __restrict__ temperature,
-                              const long long* __restrict__ seed, const long long* __restrict__ draw, int* __restrict__ tokens)
+constexpr int NONE = 0x7fffffff;
+
+__device__ __forceinline__ void take_better(float& bv, int& bi, float ov, int oi)
+{
+    if (oi != NONE && (bi == NONE || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
+}
+
+// Reduces (value, index) over the block; thread 0 gets the result.
+__device__ __forceinline__ void block_best(float& bv, int& bi)
 {
     __shared__ float best_v[32];
     __shared__ int best_i[32];
-    const int r = blockIdx.x;
-    const float* row = logits + (size_t)r * row_stride;
-    const float temp = temperature ? temperature[r] : 0.f;
-    const uint64_t sd = seed ? (uint64_t)seed[r] : 0, dr = draw ? (uint64_t)draw[r] : 0;
-    float bv = -INFINITY;
-    int bi = 0x7fffffff;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-        float v = row[i];
-        if (temp > 0.f) v = v / temp - logf(-logf(uniform_open(sd, dr, (uint32_t)i)));
-        if (v > bv || (v == bv && i < bi) || bi == 0x7fffffff) { bv = v; bi = i; }
-    }
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
-    }
+    for (int o = 16; o > 0; o >>= 1) take_better(bv, bi, __shfl_xor_sync(0xffffffffu, bv, o), __shfl_xor_sync(0xffffffffu, bi, o));
     if (lane == 0) { best_v[warp] = bv; best_i[warp] = bi; }
     __syncthreads();
     if (warp == 0) {
         bv = lane < nwarps ? best_v[lane] : -INFINITY;
-        bi = lane < nwarps ? best_i[lane] : 0x7fffffff;
+        bi = lane < nwarps ? best_i[lane] : NONE;
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
-        }
-        if (lane == 0) tokens[r] = bi == 0x7fffffff ? 0 : bi;
+        for (int o = 16; o > 0; o >>= 1) take_better(bv, bi, __shfl_xor_sync(0xffffffffu, bv, o), __shfl_xor_sync(0xffffffffu, bi, o));
     }
 }
 
+__global__ void sample_slices_kernel(const float* __restrict__ logits, long long row_stride, int vocab, int slice, const float* __restrict__ temperature,
+                                     const long long* __restrict__ seed, const long long* __restrict__ draw, float* __restrict__ slice_v,
+                                     int* __restrict__ slice_i)
+{
+    const int r = blockIdx.y, lo = blockIdx.x * slice, hi = min(vocab, lo + slice);
+    const float* row = logits + (size_t)r * row_stride;
+    const float temp = temperature ? temperature[r] : 0.f;
+    const uint64_t key = mix64((seed ? (uint64_t)seed[r] : 0) ^ mix64(draw ? (uint64_t)draw[r] : 0));
+    float bv = -INFINITY;
+    int bi = NONE;
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        float v = row[i];
+        if (temp > 0.f) v = v / temp - logf(-logf(uniform_open(key, (uint32_t)i)));
+        if (bi == NONE || v > bv) { bv = v; bi = i; }   // ascending i: the lowest index is kept on ties
+    }
+    block_best(bv, bi);
+    if (threadIdx.x == 0) {
+        slice_v[(size_t)r * gridDim.x + blockIdx.x] = bv;
+        slice_i[(size_t)r * gridDim.x + blockIdx.x] = bi;
+    }
+}
+
+__global__ void sample_pick_kernel(const float* __restrict__ slice_v, const int* __restrict__ slice_i, int slices, int* __restrict__ tokens)
+{
+    const int r = blockIdx.x;
+    float bv = -INFINITY;
+    int bi = NONE;
+    for (int s = threadIdx.x; s < slices; s += blockDim.x) take_better(bv, bi, slice_v[(size_t)r * slices + s], slice_i[(size_t)r * slices + s]);
+    block_best(bv, bi);
+    if (threadIdx.x == 0) tokens[r] = bi == NONE ? 0 : bi;
+}
+
+// How many slices a row of `vocab` logits is cut into.
+extern "C" int spy_sample_slices(int vocab) { return vocab <= 4096 ? 1 : (vocab + 4095) / 4096; }
+
 // logits: [rows, vocab] floats, rows row_stride apart.  temperature/seed/draw: per row, or
-// null for greedy.  tokens: [rows] int32 out.
+// null for greedy.  tokens: [rows] int32 out.  slice_v / slice_i: rows * spy_sample_slices(vocab)
+// floats / ints of scratch.
 extern "C" int spy_sample(const float* logits, long long row_stride, int rows, int vocab, const float* temperature, const long long* seed,
-                          const long long* draw, int* tokens, cudaStream_t stream)
+                          const long long* draw, int* tokens, float* slice_v, int* slice_i, cudaStream_t stream)
 {
     if (rows <= 0) return 0;
     if (vocab <= 0 || row_stride < vocab) SPY_FAIL("sample: vocab %d must be positive and fit the row stride %lld", vocab, row_stride);
-    sample_kernel<<<rows, 1024, 0, stream>>>(logits, row_stride, vocab, temperature, seed, draw, tokens);
-    SPY_CHECK_LAUNCH("sample");
+    if (rows > 65535) SPY_FAIL("sample: %d rows exceed the grid limit", rows);
+    const int slices = spy_sample_slices(vocab);
+    const int slice = (vocab + slices - 1) / slices;
+    dim3 grid(slices, rows);
+    sample_slices_kernel<<<grid, 256, 0, stream>>>(logits, row_stride, vocab, slice, temperature, seed, draw, slice_v, slice_i);
+    SPY_CHECK_LAUNCH("sample (slices)");
+    sample_pick_kernel<<<rows, 64, 0, stream>>>(slice_v, slice_i, slices, tokens);
+    SPY_CHECK_LAUNCH("sample (pick)");
     return 0;
 }

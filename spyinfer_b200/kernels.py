@@ -97,17 +97,27 @@ def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, status:
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, delta: Optional[torch.Tensor] = None,
             rows: Optional[torch.Tensor] = None, write_back: bool = False) -> torch.Tensor:
     """``out = rmsnorm(x [+ delta]) * weight`` row by row; with ``write_back`` the sum is stored
-    into ``x`` (the residual stream); ``rows`` gathers rows of x (and delta) into out."""
+    into ``x`` (the residual stream); ``rows`` gathers rows of x (and delta) into out.
+    ``delta`` has x's shape, or is a stack ``[splits, rows, len]`` of partial sums (the
+    unreduced output of a split-K product) that are added in order."""
     _check(x, "rmsnorm input", ndim=2)
     _check(weight, "rmsnorm weight", ndim=1)
     _check(out, "rmsnorm output", ndim=2)
     H = x.shape[1]
     if weight.shape[0] != H or out.shape[1] != H:
         raise KernelError(f"rmsnorm: row lengths differ: input {H}, weight {weight.shape[0]}, output {out.shape[1]}")
+    splits, split_stride = 0, 0
     if delta is not None:
-        _check(delta, "rmsnorm delta", ndim=2)
-        if tuple(delta.shape) != tuple(x.shape):
-            raise KernelError(f"rmsnorm: delta shape {tuple(delta.shape)} differs from input shape {tuple(x.shape)}")
+        if delta.dim() == 3:
+            _check(delta, "rmsnorm delta", ndim=3)
+            splits, split_stride = delta.shape[0], delta.shape[1] * delta.shape[2]
+            if tuple(delta.shape[1:]) != tuple(x.shape):
+                raise KernelError(f"rmsnorm: stacked delta shape {tuple(delta.shape)} does not fit input shape {tuple(x.shape)}")
+        else:
+            _check(delta, "rmsnorm delta", ndim=2)
+            splits = 1
+            if tuple(delta.shape) != tuple(x.shape):
+                raise KernelError(f"rmsnorm: delta shape {tuple(delta.shape)} differs from input shape {tuple(x.shape)}")
     if rows is not None:
         _check(rows, "rmsnorm rows", torch.int32, 1)
         n = rows.shape[0]
@@ -116,8 +126,8 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
     if out.shape[0] != n:
         raise KernelError(f"rmsnorm: output has {out.shape[0]} rows, expected {n}")
     _call("rmsnorm", "spy_rmsnorm", _ptr(x), _code(x, "rmsnorm input"), _ptr(delta), _code(delta, "rmsnorm delta") if delta is not None else 0,
-          _ptr(rows), _ptr(weight), _code(weight, "rmsnorm weight"), _ptr(out), _code(out, "rmsnorm output"), n, H,
-          ctypes.c_float(eps), int(bool(write_back)), _stream())
+          splits, ctypes.c_longlong(split_stride), _ptr(rows), _ptr(weight), _code(weight, "rmsnorm weight"), _ptr(out),
+          _code(out, "rmsnorm output"), n, H, ctypes.c_float(eps), int(bool(write_back)), _stream())
     return out
 
 
@@ -300,7 +310,12 @@ def sample(logits: torch.Tensor, tokens: torch.Tensor, temperature: Optional[tor
         _check(draw, "draw counters", torch.int64, 1)
         if not (temperature.shape[0] == seed.shape[0] == draw.shape[0] == R):
             raise KernelError("sample: temperature, seed and draw need one entry per row")
-    _call("sampling", "spy_sample", _ptr(logits), ctypes.c_longlong(V), R, V, _ptr(temperature), _ptr(seed), _ptr(draw), _ptr(tokens), _stream())
+    lib = build.load("sampling")
+    slices = lib.spy_sample_slices(V)
+    slice_v = torch.empty(R * slices, dtype=torch.float32, device=logits.device)
+    slice_i = torch.empty(R * slices, dtype=torch.int32, device=logits.device)
+    _call("sampling", "spy_sample", _ptr(logits), ctypes.c_longlong(V), R, V, _ptr(temperature), _ptr(seed), _ptr(draw), _ptr(tokens),
+          _ptr(slice_v), _ptr(slice_i), _stream())
     return tokens
 
 

@@ -1,0 +1,98 @@
+"""Timings of single kernels at chosen sizes, for profiling and for the summaries under profiles/.
+
+    python -m spyinfer_b200.microbench gemm --m 2048 --n 24576 --k 4096 [--out-dtype float32] [--iters 20]
+    python -m spyinfer_b200.microbench attention --batch 8 --context 8192 [--q-len 1] [--split-keys 576] [--iters 10]
+
+Defaults are Qwen3-8B's sizes (32 query heads, 8 key/value heads, head size 128, pages of 16).
+Timing is by CUDA events around ``iters`` launches after a warm-up; the product cycles through
+enough weight copies to exceed L2, the attention's cache does so by itself at the default sizes.
+"""
+from __future__ import annotations
+
+import argparse
+import math
+import sys
+
+import torch
+
+from . import kernels
+
+DEV = "cuda:0"
+
+
+def bench_gemm(M: int, N: int, K: int, out_dtype=torch.bfloat16, iters: int = 20) -> dict:
+    a = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    copies = max(1, int(300e6 // (N * K * 2)) + 1)
+    ws = [(torch.randn(N, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16) for _ in range(copies)]
+    out = torch.empty(M, N, device=DEV, dtype=out_dtype)
+    for w in ws[:2]:
+        kernels.gemm_tcgen05(a, w, out)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(iters):
+        kernels.gemm_tcgen05(a, ws[i % copies], out)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / iters
+    return {"us": ms * 1e3, "tflops": 2.0 * M * N * K / ms / 1e9, "gbs": (N * K * 2 + M * K * 2 + M * N * out.element_size()) / ms / 1e6}
+
+
+def bench_attention(batch: int, context: int, q_len: int = 1, split_keys: int = 0, nh: int = 32, nkv: int = 8, hd: int = 128,
+                    page_size: int = 16, iters: int = 10) -> dict:
+    width = (context + page_size - 1) // page_size
+    pages = torch.randn(batch * width + 1, 2, nkv, page_size, hd, device=DEV).to(torch.bfloat16)
+    bt = torch.randperm(batch * width, device=DEV).view(batch, width).to(torch.int32)
+    T = batch * q_len
+    q = torch.randn(T, (nh + 2 * nkv) * hd, device=DEV).to(torch.bfloat16)
+    pos = torch.cat([torch.arange(context - q_len, context, dtype=torch.int32) for _ in range(batch)]).to(DEV)
+    q_start = (torch.arange(batch + 1, dtype=torch.int32) * q_len).to(DEV)
+    out = torch.empty(T, nh * hd, device=DEV, dtype=torch.bfloat16)
+    max_splits = (context + split_keys - 1) // split_keys if split_keys else 0
+
+    def run():
+        kernels.attention_mma(q, nh, hd, out, pages, bt, pos, q_start, batch, 1 / math.sqrt(hd), split_keys=split_keys, max_splits=max_splits)
+
+    run()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / iters
+    kv_bytes = batch * context * 2 * nkv * hd * 2
+    flops = 4.0 * nh * hd * batch * (q_len * (context - q_len) + q_len * (q_len + 1) / 2)
+    return {"us": ms * 1e3, "kv_gbs": kv_bytes / ms / 1e6, "tflops": flops / ms / 1e9}
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    sub = ap.add_subparsers(dest="what", required=True)
+    g = sub.add_parser("gemm")
+    g.add_argument("--m", type=int, required=True)
+    g.add_argument("--n", type=int, required=True)
+    g.add_argument("--k", type=int, required=True)
+    g.add_argument("--out-dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    g.add_argument("--iters", type=int, default=20)
+    a = sub.add_parser("attention")
+    a.add_argument("--batch", type=int, required=True)
+    a.add_argument("--context", type=int, required=True)
+    a.add_argument("--q-len", type=int, default=1)
+    a.add_argument("--split-keys", type=int, default=0, help="0: tiles mode; else split mode with this range length")
+    a.add_argument("--iters", type=int, default=10)
+    args = ap.parse_args(argv)
+    kernels.require_cuda()
+    if args.what == "gemm":
+        r = bench_gemm(args.m, args.n, args.k, getattr(torch, args.out_dtype), args.iters)
+        print(f"gemm M={args.m} N={args.n} K={args.k}: {r['us']:.1f} us, {r['tflops']:.1f} TFLOP/s, {r['gbs']:.1f} GB/s")
+    else:
+        r = bench_attention(args.batch, args.context, args.q_len, args.split_keys, iters=args.iters)
+        print(f"attention batch={args.batch} context={args.context} q_len={args.q_len} split_keys={args.split_keys}: {r['us']:.1f} us, "
+              f"cache read at {r['kv_gbs']:.1f} GB/s, {r['tflops']:.1f} TFLOP/s")
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
