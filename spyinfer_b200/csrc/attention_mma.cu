@@ -1,13 +1,14 @@
 // bfloat16 attention over the paged cache on the tensor cores (mma.sync m16n8k16), keys and
-// values streamed from the pages in exactly the order of the instruction's operand registers:
-// every thread copies its own 16-byte pieces with cp.async into a private ring in shared
-// memory (an asynchronous extension of its registers) and never reads another thread's.  One warp owns a tile of 16 rows = the G query
+// values streamed from the pages with cp.async in the order of the instruction's operand
+// registers (in split mode every thread copies its own 16-byte pieces into a private ring in
+// shared memory, an asynchronous extension of its registers).  One warp owns a tile of 16 rows = the G query
 // heads of one key/value head for 16 / Gp consecutive tokens of one sequence (Gp = G rounded
 // up to a power of two), so every key and value row is read once for all G heads.
 //
 // Two launch modes:
-//   tiles  (any batch): a block's four warps take four consecutive token tiles of a sequence;
-//          each warp walks all keys its rows can see and writes its output rows directly.
+//   tiles  (any batch): a block's eight warps take eight consecutive token tiles of a sequence
+//          and share the keys and values, which go through tiles of 64 keys in shared memory;
+//          each warp writes its output rows directly.
 //   split  (every sequence brings exactly one token: decoding): grid (sequence, kv head,
 //          split); split z covers keys [z * split_keys, (z + 1) * split_keys); the four warps
 //          share that range and merge in shared memory; when a row's keys span more than one
@@ -46,6 +47,13 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi)
 {
     __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&t);
+}
+
+__device__ __forceinline__ float fast_exp2(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));   // exp2(-inf) = 0
+    return y;
 }
 
 __device__ __forceinline__ uint4 load16(const bf16* p) { return *reinterpret_cast<const uint4*>(p); }
@@ -92,6 +100,138 @@ __device__ __forceinline__ int page_of(const Params& p, const int* bt, const int
     return lp < p.table_width ? bt[lp] : -1;
 }
 
+// The arithmetic on one group of 16 keys [kb, kb + 16) for one 16-row tile: scores, mask, online
+// softmax, output update.  ld_k(tile, c) returns this thread's 16 bytes of K for key
+// kb + 8 tile + g, chunk c; ld_v(i, ds) its 16 bytes of V for key kb + 2 t4 + (i & 1) + 8 (i >> 1),
+// column set ds.  Groups that every used row sees whole ([all_lo, all_hi]) skip the masking;
+// the running output is rescaled only when some row's maximum grew.
+template <int HD, typename LoadK, typename LoadV>
+__device__ __forceinline__ void process_group(const Params& p, const uint4 (&qf)[2][HD / 32], const int (&row_pos)[2], const int (&row_lo)[2],
+                                              int key_lo, int key_hi, int all_lo, int all_hi, int kb, TileState<HD>& st, LoadK ld_k, LoadV ld_v)
+{
+    const int lane = threadIdx.x & 31, t4 = lane & 3;
+    constexpr int KC = HD / 32;   // 32-element chunks of head_dim
+    constexpr int DS = HD / 64;   // sets of 64 output columns
+    // ---- scores of 16 rows x 16 keys (two accumulators per key tile keep four chains in flight)
+    float s[2][4], s2[2][4];
+#pragma unroll
+    for (int tile = 0; tile < 2; ++tile)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[tile][e] = s2[tile][e] = 0.f;
+#pragma unroll
+    for (int c = 0; c < KC; ++c) {
+        const uint4 k0 = ld_k(0, c), k1 = ld_k(1, c);
+        mma_bf16(s[0], qf[0][c].x, qf[1][c].x, qf[0][c].y, qf[1][c].y, k0.x, k0.y);
+        mma_bf16(s[1], qf[0][c].x, qf[1][c].x, qf[0][c].y, qf[1][c].y, k1.x, k1.y);
+        mma_bf16(s2[0], qf[0][c].z, qf[1][c].z, qf[0][c].w, qf[1][c].w, k0.z, k0.w);
+        mma_bf16(s2[1], qf[0][c].z, qf[1][c].z, qf[0][c].w, qf[1][c].w, k1.z, k1.w);
+    }
+#pragma unroll
+    for (int tile = 0; tile < 2; ++tile)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[tile][e] += s2[tile][e];
+    // ---- scale, mask (only in groups that some row cannot see whole), running max
+    const bool whole = kb >= all_lo && kb + 15 <= all_hi;   // uniform over the warp
+    float mx[2] = {-INFINITY, -INFINITY};
+    if (whole) {
+#pragma unroll
+        for (int tile = 0; tile < 2; ++tile)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                s[tile][e] *= p.scale_log2;
+                mx[e >> 1] = fmaxf(mx[e >> 1], s[tile][e]);
+            }
+    } else {
+#pragma unroll
+        for (int tile = 0; tile < 2; ++tile)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int r = e >> 1;                              // c0, c1: row g; c2, c3: row g + 8
+                const int j = kb + tile * 8 + 2 * t4 + (e & 1);
+                const bool ok = j <= row_pos[r] && j >= row_lo[r] && j >= key_lo && j <= key_hi;
+                const float v = ok ? s[tile][e] * p.scale_log2 : -INFINITY;
+                s[tile][e] = v;
+                mx[r] = fmaxf(mx[r], v);
+            }
+    }
+    bool grew = false;
+    float m_new[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        m_new[r] = fmaxf(st.m[r], mx[r]);
+        grew = grew || m_new[r] != st.m[r];
+    }
+    if (__any_sync(0xffffffffu, grew)) {
+        float alpha[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            alpha[r] = m_new[r] == -INFINITY ? 1.f : fast_exp2(st.m[r] - m_new[r]);   // st.m = -inf gives 0
+            st.m[r] = m_new[r];
+            st.l[r] *= alpha[r];
+        }
+#pragma unroll
+        for (int ds = 0; ds < DS; ++ds)
+#pragma unroll
+            for (int jt = 0; jt < 8; ++jt) {
+                st.o[ds][jt][0] *= alpha[0];
+                st.o[ds][jt][1] *= alpha[0];
+                st.o[ds][jt][2] *= alpha[1];
+                st.o[ds][jt][3] *= alpha[1];
+            }
+    }
+    // ---- probabilities
+    uint32_t pa[4];   // A fragment of P: a0 (row g, keys 2t4..), a1 (row g+8), a2 (row g, keys 8+2t4..), a3 (row g+8)
+    {
+        float pr[2][4];
+        // a row that has seen no key yet has max -inf: its scores are -inf too and must give 0, not NaN
+        const float m0 = st.m[0] == -INFINITY ? 0.f : st.m[0], m1 = st.m[1] == -INFINITY ? 0.f : st.m[1];
+#pragma unroll
+        for (int tile = 0; tile < 2; ++tile)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int r = e >> 1;
+                const float v = fast_exp2(s[tile][e] - (r == 0 ? m0 : m1));
+                pr[tile][e] = v;
+                st.l[r] += v;
+            }
+        pa[0] = pack_bf16(pr[0][0], pr[0][1]);
+        pa[1] = pack_bf16(pr[0][2], pr[0][3]);
+        pa[2] = pack_bf16(pr[1][0], pr[1][1]);
+        pa[3] = pack_bf16(pr[1][2], pr[1][3]);
+    }
+    // ---- O += P V
+#pragma unroll
+    for (int ds = 0; ds < DS; ++ds) {
+        uint4 vf[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) vf[i] = ld_v(i, ds);
+#pragma unroll
+        for (int jt = 0; jt < 8; ++jt) {
+            const uint32_t sel = (jt & 1) ? 0x7632u : 0x5410u;   // upper or lower halves of the two words
+            const uint32_t b0 = __byte_perm(word(vf[0], jt >> 1), word(vf[1], jt >> 1), sel);
+            const uint32_t b1 = __byte_perm(word(vf[2], jt >> 1), word(vf[3], jt >> 1), sel);
+            mma_bf16(st.o[ds][jt], pa[0], pa[1], pa[2], pa[3], b0, b1);
+        }
+    }
+}
+
+// The keys every used row of a warp's tile can see, as one range (uniform over the warp).
+__device__ __forceinline__ void common_range(const int (&row_pos)[2], const int (&row_lo)[2], int key_lo, int key_hi, int& all_lo, int& all_hi)
+{
+    all_lo = key_lo;
+    all_hi = key_hi;
+#pragma unroll
+    for (int r = 0; r < 2; ++r)
+        if (row_pos[r] >= 0) {
+            all_lo = max(all_lo, row_lo[r]);
+            all_hi = min(all_hi, row_pos[r]);
+        }
+    all_lo = __reduce_max_sync(0xffffffffu, all_lo);
+    all_hi = __reduce_min_sync(0xffffffffu, all_hi);
+}
+
 // Walks keys [key_lo, key_hi] (inclusive, absolute positions) for one tile.
 // row_pos / row_lo: last and first visible key of rows g and g + 8 (row_pos < 0: row unused).
 // Every thread copies exactly the 16-byte pieces it will use itself (its operand fragments
@@ -101,8 +241,6 @@ __device__ __forceinline__ int page_of(const Params& p, const int* bt, const int
 // ring: [RING][2 * HD / 16 pieces][blockDim.x] of 16 bytes.
 // PAGE16: the page size is a multiple of 16, so the 16 keys of a group share one page and
 // one block-table lookup serves the whole group.
-// Groups whose 16 keys are visible to every row of the tile skip the masking, and the
-// running output is rescaled only in iterations in which some row's maximum grew.
 template <int HD, bool PAGE16>
 __device__ __forceinline__ void walk_keys(const Params& p, const int* bt, const int* bt_s, int bt_first, int kvh, const uint4 (&qf)[2][HD / 32],
                                           const int (&row_pos)[2], const int (&row_lo)[2], int key_lo, int key_hi, TileState<HD>& st,
@@ -116,16 +254,8 @@ __device__ __forceinline__ void walk_keys(const Params& p, const int* bt, const 
     const int kb_first = key_lo & ~15;
     const int n_iter = (key_hi - kb_first) / 16 + 1;
     const size_t plane = (size_t)p.nkv * p.page_size * HD;   // elements from a page's K plane to its V plane
-    // keys every used row of the tile can see: [all_lo, all_hi]
-    int all_lo = key_lo, all_hi = key_hi;
-#pragma unroll
-    for (int r = 0; r < 2; ++r)
-        if (row_pos[r] >= 0) {
-            all_lo = max(all_lo, row_lo[r]);
-            all_hi = min(all_hi, row_pos[r]);
-        }
-    all_lo = __reduce_max_sync(0xffffffffu, all_lo);
-    all_hi = __reduce_min_sync(0xffffffffu, all_hi);
+    int all_lo, all_hi;
+    common_range(row_pos, row_lo, key_lo, key_hi, all_lo, all_hi);
 
     auto page_base = [&](int lp) -> const bf16* {   // K plane of this kv head in logical page lp, or null
         const int page = page_of(p, bt, bt_s, bt_first, lp);
@@ -193,101 +323,9 @@ __device__ __forceinline__ void walk_keys(const Params& p, const int* bt, const 
         cp_async_wait<RING - 1>();
         const int kb = kb_first + it * 16;
         const uint4* slot = ring + ((size_t)(it % RING) * PIECES) * nthreads + threadIdx.x;
-        // ---- scores of 16 rows x 16 keys
-        float s[2][4];
-#pragma unroll
-        for (int tile = 0; tile < 2; ++tile) s[tile][0] = s[tile][1] = s[tile][2] = s[tile][3] = 0.f;
-#pragma unroll
-        for (int c = 0; c < KC; ++c) {
-            const uint4 k0 = slot[(size_t)c * nthreads], k1 = slot[(size_t)(KC + c) * nthreads];
-            mma_bf16(s[0], qf[0][c].x, qf[1][c].x, qf[0][c].y, qf[1][c].y, k0.x, k0.y);
-            mma_bf16(s[1], qf[0][c].x, qf[1][c].x, qf[0][c].y, qf[1][c].y, k1.x, k1.y);
-            mma_bf16(s[0], qf[0][c].z, qf[1][c].z, qf[0][c].w, qf[1][c].w, k0.z, k0.w);
-            mma_bf16(s[1], qf[0][c].z, qf[1][c].z, qf[0][c].w, qf[1][c].w, k1.z, k1.w);
-        }
-        // ---- scale, mask (only in groups that some row cannot see whole), running max
-        const bool whole = kb >= all_lo && kb + 15 <= all_hi;   // uniform over the warp
-        float mx[2] = {-INFINITY, -INFINITY};
-        if (whole) {
-#pragma unroll
-            for (int tile = 0; tile < 2; ++tile)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    s[tile][e] *= p.scale_log2;
-                    mx[e >> 1] = fmaxf(mx[e >> 1], s[tile][e]);
-                }
-        } else {
-#pragma unroll
-            for (int tile = 0; tile < 2; ++tile)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int r = e >> 1;                              // c0, c1: row g; c2, c3: row g + 8
-                    const int j = kb + tile * 8 + 2 * t4 + (e & 1);
-                    const bool ok = j <= row_pos[r] && j >= row_lo[r] && j >= key_lo && j <= key_hi;
-                    const float v = ok ? s[tile][e] * p.scale_log2 : -INFINITY;
-                    s[tile][e] = v;
-                    mx[r] = fmaxf(mx[r], v);
-                }
-        }
-        bool grew = false;
-        float m_new[2];
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-            m_new[r] = fmaxf(st.m[r], mx[r]);
-            grew = grew || m_new[r] != st.m[r];
-        }
-        if (__any_sync(0xffffffffu, grew)) {
-            float alpha[2];
-#pragma unroll
-            for (int r = 0; r < 2; ++r) {
-                alpha[r] = m_new[r] == -INFINITY ? 1.f : exp2f(st.m[r] - m_new[r]);   // st.m = -inf gives 0
-                st.m[r] = m_new[r];
-                st.l[r] *= alpha[r];
-            }
-#pragma unroll
-            for (int ds = 0; ds < DS; ++ds)
-#pragma unroll
-                for (int jt = 0; jt < 8; ++jt) {
-                    st.o[ds][jt][0] *= alpha[0];
-                    st.o[ds][jt][1] *= alpha[0];
-                    st.o[ds][jt][2] *= alpha[1];
-                    st.o[ds][jt][3] *= alpha[1];
-                }
-        }
-        // ---- probabilities
-        uint32_t pa[4];   // A fragment of P: a0 (row g, keys 2t4..), a1 (row g+8), a2 (row g, keys 8+2t4..), a3 (row g+8)
-        {
-            float pr[2][4];
-#pragma unroll
-            for (int tile = 0; tile < 2; ++tile)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int r = e >> 1;
-                    const float v = st.m[r] == -INFINITY ? 0.f : exp2f(s[tile][e] - st.m[r]);
-                    pr[tile][e] = v;
-                    st.l[r] += v;
-                }
-            pa[0] = pack_bf16(pr[0][0], pr[0][1]);
-            pa[1] = pack_bf16(pr[0][2], pr[0][3]);
-            pa[2] = pack_bf16(pr[1][0], pr[1][1]);
-            pa[3] = pack_bf16(pr[1][2], pr[1][3]);
-        }
-        // ---- O += P V
-#pragma unroll
-        for (int ds = 0; ds < DS; ++ds) {
-            uint4 vf[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) vf[i] = slot[(size_t)(2 * KC + i * DS + ds) * nthreads];
-#pragma unroll
-            for (int jt = 0; jt < 8; ++jt) {
-                const uint32_t sel = (jt & 1) ? 0x7632u : 0x5410u;   // upper or lower halves of the two words
-                const uint32_t b0 = __byte_perm(word(vf[0], jt >> 1), word(vf[1], jt >> 1), sel);
-                const uint32_t b1 = __byte_perm(word(vf[2], jt >> 1), word(vf[3], jt >> 1), sel);
-                mma_bf16(st.o[ds][jt], pa[0], pa[1], pa[2], pa[3], b0, b1);
-            }
-        }
+        process_group<HD>(p, qf, row_pos, row_lo, key_lo, key_hi, all_lo, all_hi, kb, st,
+                          [&](int tile, int c) { return slot[(size_t)(tile * KC + c) * nthreads]; },
+                          [&](int i, int ds) { return slot[(size_t)(2 * KC + i * DS + ds) * nthreads]; });
     }
     cp_async_wait<0>();
 }
@@ -353,12 +391,26 @@ __device__ __forceinline__ void store_rows(const Params& p, const TileState<HD>&
 }
 
 // ---- tiles mode ------------------------------------------------------------------------------
-template <int HD>
-__global__ void __launch_bounds__(WARPS * 32, 2) attention_tiles_kernel(const Params p)
+// A block's warps take consecutive token tiles of one sequence and walk the keys together:
+// tiles of 64 keys go through a three-stage ring in shared memory (cp.async by all threads,
+// one barrier per tile) and every warp reads its operand fragments from them.  Rows of the
+// shared tiles are 16-byte-chunk swizzled so that those reads hit distinct banks:
+//   K rows: chunk ^ (((row & 1) << 2) | ((row >> 1) & 3))   (a warp reads 8 consecutive rows x 4 chunks)
+//   V rows: chunk ^ (row & 7)                               (a warp reads rows 2 apart x 8 chunks)
+constexpr int TILE_KEYS = 64;
+constexpr int TILE_STAGES = 3;
+
+__device__ __forceinline__ int swz_k(int row) { return ((row & 1) << 2) | ((row >> 1) & 3); }
+__device__ __forceinline__ int swz_v(int row) { return row & 7; }
+
+template <int HD, int NWARPS>
+__global__ void __launch_bounds__(NWARPS * 32, NWARPS <= 4 ? 2 : 1) attention_tiles_kernel(const Params p)
 {
-    extern __shared__ uint4 ring_smem[];
+    extern __shared__ uint4 tile_smem[];   // [TILE_STAGES][2 (K, V)][TILE_KEYS][HD / 8] chunks of 16 bytes
     __shared__ int s_seq, s_tok0;
-    const int tokens_per_tile = 16 / p.Gp, tokens_per_block = WARPS * tokens_per_tile;
+    constexpr int CPR = HD / 8;                        // 16-byte chunks per row
+    constexpr int STAGE_CHUNKS = 2 * TILE_KEYS * CPR;
+    const int tokens_per_tile = 16 / p.Gp, tokens_per_block = NWARPS * tokens_per_tile;
     if (threadIdx.x == 0) {
         // block b of the grid -> (sequence, token block within it)
         int b = blockIdx.x, seq = -1, tok0 = 0;
@@ -374,30 +426,102 @@ __global__ void __launch_bounds__(WARPS * 32, 2) attention_tiles_kernel(const Pa
     __syncthreads();
     const int seq = s_seq;
     if (seq < 0) return;
-    const int warp = threadIdx.x >> 5, kvh = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3, kvh = blockIdx.y;
     const int tok_end = p.q_start[seq + 1];
-    const int tok0 = s_tok0 + warp * tokens_per_tile;
-    if (tok0 >= tok_end) return;
+    const int block_tok0 = s_tok0;
     const int* bt = p.block_table + (size_t)seq * p.table_width;
+    const size_t plane = (size_t)p.nkv * p.page_size * HD;
 
+    // the block's key range: its tokens are consecutive positions of one sequence
+    const int block_first_pos = p.positions[block_tok0];
+    const int block_last_pos = p.positions[min(tok_end, block_tok0 + tokens_per_block) - 1];
+    const int block_lo = p.window > 0 ? max(0, block_first_pos - p.window + 1) : 0;
+    const int tile_first = block_lo / TILE_KEYS;
+    const int n_tiles = block_last_pos / TILE_KEYS - tile_first + 1;
+
+    // this warp's tile
+    const int tok0 = block_tok0 + warp * tokens_per_tile;
+    const bool active = tok0 < tok_end;
     uint4 qf[2][HD / 32];
-    int row_tok[2], row_head[2], row_pos[2], row_lo[2];
-    load_q<HD>(p, kvh, tok0, tok_end, qf, row_tok, row_head);
+    int row_tok[2] = {-1, -1}, row_head[2] = {0, 0}, row_pos[2] = {-1, -1}, row_lo[2] = {0, 0};
+    int key_lo = 0, key_hi = -1, all_lo = 0, all_hi = -1;
+    if (active) {
+        load_q<HD>(p, kvh, tok0, tok_end, qf, row_tok, row_head);
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        row_pos[r] = row_tok[r] >= 0 ? p.positions[row_tok[r]] : -1;
-        row_lo[r] = (row_tok[r] >= 0 && p.window > 0) ? max(0, row_pos[r] - p.window + 1) : 0;
+        for (int r = 0; r < 2; ++r) {
+            row_pos[r] = row_tok[r] >= 0 ? p.positions[row_tok[r]] : -1;
+            row_lo[r] = (row_tok[r] >= 0 && p.window > 0) ? max(0, row_pos[r] - p.window + 1) : 0;
+        }
+        key_lo = p.window > 0 ? max(0, p.positions[tok0] - p.window + 1) : 0;
+        key_hi = p.positions[min(tok_end, tok0 + tokens_per_tile) - 1];
+        common_range(row_pos, row_lo, key_lo, key_hi, all_lo, all_hi);
     }
-    // the tile's key range: tokens of a tile are consecutive positions of one sequence
-    const int first_pos = p.positions[tok0];
-    const int last_tok = min(tok_end, tok0 + tokens_per_tile) - 1;
-    const int last_pos = p.positions[last_tok];
-    const int key_lo = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
     TileState<HD> st;
     init_state<HD>(st);
-    if (p.page_size % 16 == 0) walk_keys<HD, true>(p, bt, nullptr, 0, kvh, qf, row_pos, row_lo, key_lo, last_pos, st, ring_smem, tok0);
-    else walk_keys<HD, false>(p, bt, nullptr, 0, kvh, qf, row_pos, row_lo, key_lo, last_pos, st, ring_smem, tok0);
-    store_rows<HD>(p, st, row_tok, row_head);
+
+    auto issue = [&](int t) {
+        if (t < n_tiles) {
+            uint4* stage = tile_smem + (size_t)(t % TILE_STAGES) * STAGE_CHUNKS;
+            const int key0 = (tile_first + t) * TILE_KEYS;
+            for (int idx = threadIdx.x; idx < STAGE_CHUNKS; idx += NWARPS * 32) {
+                const int kv = idx / (TILE_KEYS * CPR);
+                const int row = (idx / CPR) % TILE_KEYS, chunk = idx % CPR;
+                const int j = key0 + row;
+                bool ok = j >= block_lo && j <= block_last_pos;
+                const bf16* src = p.pages;
+                if (ok) {
+                    const int lp = j / p.page_size;
+                    const int page = lp < p.table_width ? bt[lp] : -1;
+                    if (page < 0 || page >= p.num_pages) {
+                        report_status(p.status, SPY_STATUS_BAD_PAGE, block_tok0);
+                        ok = false;
+                    } else {
+                        src = p.pages + (((size_t)page * 2) * p.nkv + kvh) * p.page_size * HD + kv * plane + (size_t)(j - lp * p.page_size) * HD +
+                              chunk * 8;
+                    }
+                }
+                const int phys = chunk ^ (kv == 0 ? swz_k(row) : swz_v(row));
+                cp_async16(stage + (size_t)kv * TILE_KEYS * CPR + (size_t)row * CPR + phys, src, ok);
+            }
+        }
+        cp_async_commit();
+    };
+
+    // this thread's fragment addresses inside a group of 16 keys: K row g (+ 8 tile), chunk
+    // 4 c + t4; V row 2 t4 + (i & 1) (+ 8 (i >> 1)), chunk 8 ds + g; the swizzle of a row depends
+    // only on its low three bits, which the group's and the tile's offsets (multiples of 8) leave alone
+    const int k_off = g * CPR, v_off = 2 * t4 * CPR;
+    int k_chunk[HD / 32], v_chunk[2][HD / 64];
+#pragma unroll
+    for (int c = 0; c < HD / 32; ++c) k_chunk[c] = (c * 4 + t4) ^ swz_k(g);
+#pragma unroll
+    for (int o = 0; o < 2; ++o)
+#pragma unroll
+        for (int ds = 0; ds < HD / 64; ++ds) v_chunk[o][ds] = (ds * 8 + g) ^ swz_v(2 * t4 + o);
+
+    issue(0);
+    issue(1);
+    for (int t = 0; t < n_tiles; ++t) {
+        cp_async_wait<1>();      // tile t has landed (tile t + 1 may still be in flight)
+        __syncthreads();         // ... for every thread; and every warp is done with tile t - 1
+        issue(t + 2);            // into the stage that held tile t - 1
+        if (!active) continue;
+        const uint4* ks = tile_smem + (size_t)(t % TILE_STAGES) * STAGE_CHUNKS + k_off;
+        const uint4* vs = tile_smem + (size_t)(t % TILE_STAGES) * STAGE_CHUNKS + TILE_KEYS * CPR + v_off;
+        const int key0 = (tile_first + t) * TILE_KEYS;
+#pragma unroll 1
+        for (int kk = 0; kk < TILE_KEYS / 16; ++kk) {
+            const int kb = key0 + kk * 16;
+            if (kb > key_hi || kb + 15 < key_lo) continue;   // no row of this warp sees the group
+            const uint4* kg = ks + kk * 16 * CPR;
+            const uint4* vg = vs + kk * 16 * CPR;
+            process_group<HD>(p, qf, row_pos, row_lo, key_lo, key_hi, all_lo, all_hi, kb, st,
+                              [&](int tile, int c) { return kg[tile * 8 * CPR + k_chunk[c]]; },
+                              [&](int i, int ds) { return vg[((i & 1) + (i >> 1) * 8) * CPR + v_chunk[i & 1][ds]]; });
+        }
+    }
+    cp_async_wait<0>();
+    if (active) store_rows<HD>(p, st, row_tok, row_head);
 }
 
 // ---- split mode -------------------------------------------------------------------------------
@@ -550,20 +674,24 @@ extern "C" int spy_attention_mma(const void* q, long long q_row_stride, void* ou
     p.table_width = table_width; p.page_size = page_size; p.num_pages = num_pages; p.nh = nh; p.nkv = nkv; p.G = G; p.Gp = Gp; p.S = seqs;
     p.window = window; p.split_keys = split_keys; p.max_splits = max_splits; p.scale_log2 = scale * LOG2E;
     if (mode == 0) {
-        const int tokens_per_block = WARPS * (16 / Gp);
+#ifndef SPY_TILES_WARPS
+#define SPY_TILES_WARPS 8
+#endif
+        constexpr int TW = SPY_TILES_WARPS;   // warps of a tiles-mode block
+        const int tokens_per_block = TW * (16 / Gp);
         // every sequence rounds up to whole blocks: an upper bound that needs no host copy of q_start
         const long long blocks = (tokens + tokens_per_block - 1) / tokens_per_block + seqs;
         if (blocks > 0x7fffffffLL || nkv > 65535) SPY_FAIL("attention_mma: the batch exceeds the grid limits");
         dim3 grid((unsigned)blocks, nkv);
-        const size_t ring_bytes = (size_t)RING * (2 * (hd / 32) + 4 * (hd / 64)) * WARPS * 32 * sizeof(uint4);
+        const size_t tile_bytes = (size_t)TILE_STAGES * 2 * TILE_KEYS * (hd / 8) * sizeof(uint4);
         static bool tiles_configured = false;
         if (!tiles_configured) {
-            SPY_CUDA(cudaFuncSetAttribute(attention_tiles_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
-            SPY_CUDA(cudaFuncSetAttribute(attention_tiles_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+            SPY_CUDA(cudaFuncSetAttribute(attention_tiles_kernel<64, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+            SPY_CUDA(cudaFuncSetAttribute(attention_tiles_kernel<128, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
             tiles_configured = true;
         }
-        if (hd == 64) attention_tiles_kernel<64><<<grid, WARPS * 32, ring_bytes, stream>>>(p);
-        else attention_tiles_kernel<128><<<grid, WARPS * 32, ring_bytes, stream>>>(p);
+        if (hd == 64) attention_tiles_kernel<64, TW><<<grid, TW * 32, tile_bytes, stream>>>(p);
+        else attention_tiles_kernel<128, TW><<<grid, TW * 32, tile_bytes, stream>>>(p);
         SPY_CHECK_LAUNCH("attention_mma (tiles)");
         return 0;
     }

@@ -48,10 +48,10 @@ class Attention(Mixer):
         self.position = build_part(pos, ctx) if pos is not None else None
         self.qkv = self.o = self.q_norm = self.k_norm = self.rope_table = None
         self.fast = kernels.attention_mma_takes(self.nh, self.nkv, self.hd, ctx.dtype)
-        # decoding splits every sequence's keys into at most 16 ranges; the range length is
+        # decoding splits every sequence's keys into at most 8 ranges; the range length is
         # fixed by the longest sequence the engine allows, so a row's arithmetic does not
         # depend on the batch it decodes in
-        self.split_keys = max(256, (ctx.max_model_len // 16 + 63) // 64 * 64)
+        self.split_keys = max(256, ((ctx.max_model_len + 7) // 8 + 63) // 64 * 64)
         self.max_splits = (ctx.max_model_len + self.split_keys - 1) // self.split_keys
 
     def weight_decls(self):
