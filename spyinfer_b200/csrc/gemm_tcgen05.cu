@@ -192,10 +192,14 @@ __device__ __forceinline__ void store_row32(TC* dst, const uint32_t (&r)[32], in
     }
 }
 
+__device__ __forceinline__ float silu_mul(float g, float u) { return (g / (1.0f + expf(-g))) * u; }
+
 // X: [x_rows, K] in the instruction's M slot; Y: [y_rows, K] in its N slot.
 // SWAP == false: out[x, y] (row stride ld);  SWAP == true: out[y, x].
 // splits > 1: out is the float scratch [splits][rows][ld] and TC is float.
-template <int BN, typename TC, bool SWAP>
+// EPI == 1 (SwiGLU): the weight's rows alternate gate, up, gate, up, ...; the kernel stores
+// silu(gate) * up, half as many output columns (ld counts those); one pass over K only.
+template <int BN, typename TC, bool SWAP, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, BN <= 64 ? 2 : 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, TC* __restrict__ out,
                     long long ld, long long split_stride, int x_rows, int y_rows, int k_blocks, int k_blocks_per_split, int* status)
@@ -286,7 +290,42 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 const int cols = BN >= 32 ? 32 : BN;
                 const int y = y0 + c;
-                if constexpr (!SWAP) {
+                if constexpr (EPI == 1 && !SWAP) {
+                    // this thread holds 16 (gate, up) pairs of row x: outputs y / 2 .. y / 2 + 15
+                    if (x < x_rows && y < y_rows) {
+                        uint32_t o[32];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(silu_mul(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1])));
+                        TC* dst = base + (size_t)x * ld + y / 2;
+                        const int valid = min(16, (y_rows - y) / 2);
+                        if (valid >= 16 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0 && sizeof(TC) == 2) {
+#pragma unroll
+                            for (int i = 0; i < 2; ++i) {
+                                uint4 v;
+                                __nv_bfloat162 t;
+                                t = __floats2bfloat162_rn(__uint_as_float(o[8 * i]), __uint_as_float(o[8 * i + 1])); v.x = *reinterpret_cast<uint32_t*>(&t);
+                                t = __floats2bfloat162_rn(__uint_as_float(o[8 * i + 2]), __uint_as_float(o[8 * i + 3])); v.y = *reinterpret_cast<uint32_t*>(&t);
+                                t = __floats2bfloat162_rn(__uint_as_float(o[8 * i + 4]), __uint_as_float(o[8 * i + 5])); v.z = *reinterpret_cast<uint32_t*>(&t);
+                                t = __floats2bfloat162_rn(__uint_as_float(o[8 * i + 6]), __uint_as_float(o[8 * i + 7])); v.w = *reinterpret_cast<uint32_t*>(&t);
+                                reinterpret_cast<uint4*>(dst)[i] = v;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j)
+                                if (j < valid) store_elem(dst + j, __uint_as_float(o[j]));
+                        }
+                    }
+                } else if constexpr (EPI == 1 && SWAP) {
+                    // lanes 2i and 2i + 1 hold gate row and up row of output x / 2 for every token
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        if (j < cols) {
+                            const float mine = __uint_as_float(r[j]);
+                            const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
+                            if ((lane & 1) == 0 && x < x_rows && y + j < y_rows) store_elem(base + (size_t)(y + j) * ld + x / 2, silu_mul(mine, other));
+                        }
+                    }
+                } else if constexpr (!SWAP) {
                     if (x < x_rows && y < y_rows) {
                         TC* dst = base + (size_t)x * ld + y;
                         const bool aligned = (reinterpret_cast<uintptr_t>(dst) & 15) == 0;
@@ -372,12 +411,12 @@ static int make_map(CUtensorMap* map, const void* ptr, long long rows, long long
     return 0;
 }
 
-template <int BN, typename TC, bool SWAP>
+template <int BN, typename TC, bool SWAP, int EPI>
 static int launch(const CUtensorMap& mx, const CUtensorMap& my, void* out, long long ld, long long split_stride, int x_rows, int y_rows,
                   int k_blocks, int splits, int* status, cudaStream_t stream)
 {
     using T = Tile<BN>;
-    auto kernel = gemm_tcgen05_kernel<BN, TC, SWAP>;
+    auto kernel = gemm_tcgen05_kernel<BN, TC, SWAP, EPI>;
     static bool configured = false;
     if (!configured) {
         SPY_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)T::SMEM));
@@ -424,17 +463,25 @@ extern "C" int spy_gemm_tcgen05_plan(int M, int N, int K, long long scratch_limi
 
 // A [M, K] and W [N, K] bfloat16, rows lda/ldw elements apart; C [M, N] of c_dtype, rows ldc
 // apart.  scratch: float buffer of at least the plan's size (may be null when it is 0).
-extern "C" int spy_gemm_tcgen05(const void* A, long long lda, const void* W, long long ldw, void* C, int c_dtype, long long ldc, int M, int N,
-                                int K, float* scratch, long long scratch_floats, int* status, cudaStream_t stream)
+// epilogue 1 (SwiGLU): W's rows alternate gate and up rows, C is [M, N / 2], K is not split.
+// defer_reduce: when the plan splits K, the partial products stay in scratch as
+// [splits][M][N] floats for the consumer to sum (C is not written); *splits_used tells.
+extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, long long ldw, void* C, int c_dtype, long long ldc, int M, int N,
+                                   int K, float* scratch, long long scratch_floats, int epilogue, int defer_reduce, int* splits_used,
+                                   int* status, cudaStream_t stream)
 {
+    if (splits_used) *splits_used = 1;
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 != 0) SPY_FAIL("gemm_tcgen05: K %d must be a positive multiple of 8 (16-byte rows for TMA)", K);
     if (lda % 8 != 0 || ldw % 8 != 0) SPY_FAIL("gemm_tcgen05: row strides %lld/%lld must be multiples of 8 elements", lda, ldw);
     if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15)) SPY_FAIL("gemm_tcgen05: operands must be 16-byte aligned");
     if (c_dtype != SPY_F32 && c_dtype != SPY_BF16) SPY_FAIL("gemm_tcgen05: unknown output dtype code %d", c_dtype);
-    int splits;
-    long long need;
-    spy_gemm_tcgen05_plan(M, N, K, scratch ? scratch_floats : 0, &splits, &need);
+    if (epilogue != 0 && epilogue != 1) SPY_FAIL("gemm_tcgen05: unknown epilogue %d", epilogue);
+    if (epilogue == 1 && (N % 2 != 0 || c_dtype != SPY_BF16)) SPY_FAIL("gemm_tcgen05: the SwiGLU epilogue needs an even N and bfloat16 output");
+    int splits = 1;
+    long long need = 0;
+    if (epilogue == 0) spy_gemm_tcgen05_plan(M, N, K, scratch ? scratch_floats : 0, &splits, &need);
+    if (splits_used) *splits_used = splits;
     const int k_blocks = (K + BK - 1) / BK;
     const bool swap = M <= 64;
     const int bn = swap ? (M <= 16 ? 16 : (M <= 32 ? 32 : 64)) : 256;
@@ -450,16 +497,17 @@ extern "C" int spy_gemm_tcgen05(const void* A, long long lda, const void* W, lon
     const long long split_stride = splits > 1 ? (long long)M * N : 0;
     const bool f32_out = splits > 1 || c_dtype == SPY_F32;
     int rc;
-#define SPY_LAUNCH(BN_, SWAP_)                                                                                              \
-    rc = f32_out ? launch<BN_, float, SWAP_>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, status, stream) \
-                 : launch<BN_, bf16, SWAP_>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, status, stream)
+#define SPY_LAUNCH(BN_, SWAP_)                                                                                                          \
+    rc = epilogue == 1 ? launch<BN_, bf16, SWAP_, 1>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, status, stream)       \
+         : f32_out     ? launch<BN_, float, SWAP_, 0>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, status, stream)      \
+                       : launch<BN_, bf16, SWAP_, 0>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, status, stream)
     if (!swap) SPY_LAUNCH(256, false);
     else if (bn == 16) SPY_LAUNCH(16, true);
     else if (bn == 32) SPY_LAUNCH(32, true);
     else SPY_LAUNCH(64, true);
 #undef SPY_LAUNCH
     if (rc) return rc;
-    if (splits > 1) {
+    if (splits > 1 && !defer_reduce) {
         const long long elems = (long long)M * N;
         if (ldc != N) SPY_FAIL("gemm_tcgen05: split-K needs a contiguous output (ldc %lld, N %d)", ldc, N);
         long long blocks = (elems + 255) / 256;
@@ -469,6 +517,13 @@ extern "C" int spy_gemm_tcgen05(const void* A, long long lda, const void* W, lon
         SPY_CHECK_LAUNCH("gemm_tcgen05 split-K reduce");
     }
     return 0;
+}
+
+// The plain product: no epilogue, partial products summed before it returns.
+extern "C" int spy_gemm_tcgen05(const void* A, long long lda, const void* W, long long ldw, void* C, int c_dtype, long long ldc, int M, int N,
+                                int K, float* scratch, long long scratch_floats, int* status, cudaStream_t stream)
+{
+    return spy_gemm_tcgen05_ex(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, scratch, scratch_floats, 0, 0, nullptr, status, stream);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -3,8 +3,9 @@
 // (spymaster2h/spyinfer src/models/qwen3.hpp:161-194 and the cache store in
 // src/backends/cuda/native/attention.cu:25-47).
 //
-//   qkv  [T, (nh + 2*nkv) * hd]   q heads, then k heads, then v heads
-//   q    normed and rotated in place
+//   qkv  [T, (nh + 2*nkv) * hd]   q heads, then k heads, then v heads; either one array, or
+//        a stack of split-K partial products [splits][T][...] in float that is summed here
+//   q    normed and rotated, written to q_out (which may be qkv itself: in place)
 //   k    normed and rotated, written to the page of its position (not in place)
 //   v    copied to the page of its position
 //
@@ -43,12 +44,12 @@ extern "C" int spy_build_rope_table(float* table, const float* inv_freq, int row
 
 constexpr int WARPS_PER_BLOCK = 4;
 
-template <typename TA, typename TC, typename TW>
-__global__ void qk_rope_store_kernel(TA* qkv, int tokens, int nh, int nkv, int hd, const TW* __restrict__ q_w,
-                                     const TW* __restrict__ k_w, float eps, const float2* __restrict__ cos_sin, int rot_half,
-                                     int table_rows, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
-                                     const int* __restrict__ block_table, int table_width, TC* pages, int page_size, int num_pages,
-                                     int store, int* status)
+template <typename TS, typename TQ, typename TC, typename TW>
+__global__ void qk_rope_store_kernel(const TS* src, int src_splits, long long src_split_stride, TQ* q_out, long long q_out_stride, int tokens,
+                                     int nh, int nkv, int hd, const TW* __restrict__ q_w, const TW* __restrict__ k_w, float eps,
+                                     const float2* __restrict__ cos_sin, int rot_half, int table_rows, const int* __restrict__ positions,
+                                     const int* __restrict__ seq_of_token, const int* __restrict__ block_table, int table_width, TC* pages,
+                                     int page_size, int num_pages, int store, int* status)
 {
     extern __shared__ float head_buf[];  // WARPS_PER_BLOCK * hd
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -58,7 +59,7 @@ __global__ void qk_rope_store_kernel(TA* qkv, int tokens, int nh, int nkv, int h
     const int t = (int)(item / heads), head = (int)(item % heads);
     const int kind = head < nh ? 0 : (head < nh + nkv ? 1 : 2);  // q, k, v
     float* buf = head_buf + warp * hd;
-    TA* src = qkv + (size_t)t * (nh + 2 * nkv) * hd + (size_t)head * hd;
+    const TS* in = src + (size_t)t * (nh + 2 * nkv) * hd + (size_t)head * hd;
     const int pos = positions[t];
 
     TC* dst_page = nullptr;
@@ -74,15 +75,21 @@ __global__ void qk_rope_store_kernel(TA* qkv, int tokens, int nh, int nkv, int h
         dst_page = pages + ((((size_t)page * 2 + (kind - 1)) * nkv + kv_head) * page_size + pos % page_size) * hd;
     }
 
+    auto read = [&](int d) {
+        float v = to_f32(in[d]);
+        for (int s = 1; s < src_splits; ++s) v += to_f32(in[(size_t)s * src_split_stride + d]);
+        return v;
+    };
+
     if (kind == 2) {
-        for (int d = lane; d < hd; d += 32) dst_page[d] = from_f32<TC>(to_f32(src[d]));
+        for (int d = lane; d < hd; d += 32) dst_page[d] = from_f32<TC>(read(d));
         return;
     }
 
     const TW* w = kind == 0 ? q_w : k_w;
     float ss = 0.f;
     for (int d = lane; d < hd; d += 32) {
-        const float v = to_f32(src[d]);
+        const float v = read(d);
         buf[d] = v;
         ss += v * v;
     }
@@ -97,6 +104,7 @@ __global__ void qk_rope_store_kernel(TA* qkv, int tokens, int nh, int nkv, int h
         if (lane == 0) report_status(status, SPY_STATUS_BAD_POSITION, t);
         return;
     }
+    TQ* q_dst = q_out + (size_t)t * q_out_stride + (size_t)head * hd;
     for (int d = lane; d < hd; d += 32) {
         float v = buf[d];
         if (rotate && d < 2 * rot_half) {
@@ -105,15 +113,16 @@ __global__ void qk_rope_store_kernel(TA* qkv, int tokens, int nh, int nkv, int h
             const float lo = buf[j], hi = buf[j + rot_half];
             v = d < rot_half ? lo * cs.x - hi * cs.y : lo * cs.y + hi * cs.x;
         }
-        if (kind == 0) src[d] = from_f32<TA>(v);
+        if (kind == 0) q_dst[d] = from_f32<TQ>(v);
         else dst_page[d] = from_f32<TC>(v);
     }
 }
 
-template <typename TA, typename TC, typename TW>
-static int launch(void* qkv, int tokens, int nh, int nkv, int hd, const void* q_w, const void* k_w, float eps, const float* cos_sin,
-                  int rot_half, int table_rows, const int* positions, const int* seq_of_token, const int* block_table, int table_width,
-                  void* pages, int page_size, int num_pages, int store, int* status, cudaStream_t stream)
+template <typename TS, typename TQ, typename TC, typename TW>
+static int launch(const void* src, int src_splits, long long src_split_stride, void* q_out, long long q_out_stride, int tokens, int nh, int nkv,
+                  int hd, const void* q_w, const void* k_w, float eps, const float* cos_sin, int rot_half, int table_rows, const int* positions,
+                  const int* seq_of_token, const int* block_table, int table_width, void* pages, int page_size, int num_pages, int store,
+                  int* status, cudaStream_t stream)
 {
     const int heads = store ? nh + 2 * nkv : nh;
     const long long items = (long long)tokens * heads;
@@ -121,31 +130,41 @@ static int launch(void* qkv, int tokens, int nh, int nkv, int hd, const void* q_
     if (blocks > 0x7fffffffLL) SPY_FAIL("qk_rope_store: %lld work items exceed the grid limit", items);
     const size_t smem = (size_t)WARPS_PER_BLOCK * hd * sizeof(float);
     if (smem > 48 * 1024) SPY_FAIL("qk_rope_store: head_dim %d is too large (limit %d)", hd, 48 * 1024 / 4 / WARPS_PER_BLOCK);
-    qk_rope_store_kernel<TA, TC, TW><<<(int)blocks, WARPS_PER_BLOCK * 32, smem, stream>>>(
-        (TA*)qkv, tokens, nh, nkv, hd, (const TW*)q_w, (const TW*)k_w, eps, (const float2*)cos_sin, rot_half, table_rows, positions,
-        seq_of_token, block_table, table_width, (TC*)pages, page_size, num_pages, store, status);
+    qk_rope_store_kernel<TS, TQ, TC, TW><<<(int)blocks, WARPS_PER_BLOCK * 32, smem, stream>>>(
+        (const TS*)src, src_splits, src_split_stride, (TQ*)q_out, q_out_stride, tokens, nh, nkv, hd, (const TW*)q_w, (const TW*)k_w, eps,
+        (const float2*)cos_sin, rot_half, table_rows, positions, seq_of_token, block_table, table_width, (TC*)pages, page_size, num_pages, store,
+        status);
     SPY_CHECK_LAUNCH("qk_rope_store");
     return 0;
 }
 
+// src: qkv of src_dtype, src_splits arrays src_split_stride elements apart that are summed
+// (1 for a plain array).  q_out: [T, ...] rows q_out_stride elements apart, of q_dtype; it may
+// be src itself (same dtype, one split, stride (nh + 2 nkv) hd).
 // q_w / k_w: null for no norm (both or neither).  cos_sin: null for no rotation.
 // store == 0: only the q heads are processed (a layer that reads another layer's cache).
-extern "C" int spy_qk_rope_store(void* qkv, int act_dtype, int tokens, int nh, int nkv, int hd, const void* q_w, const void* k_w,
-                                 int w_dtype, float eps, const float* cos_sin, int rot_half, int table_rows, const int* positions,
-                                 const int* seq_of_token, const int* block_table, int table_width, void* pages, int cache_dtype,
-                                 int page_size, int num_pages, int store, int* status, cudaStream_t stream)
+extern "C" int spy_qk_rope_store(const void* src, int src_dtype, int src_splits, long long src_split_stride, void* q_out, int q_dtype,
+                                 long long q_out_stride, int tokens, int nh, int nkv, int hd, const void* q_w, const void* k_w, int w_dtype,
+                                 float eps, const float* cos_sin, int rot_half, int table_rows, const int* positions, const int* seq_of_token,
+                                 const int* block_table, int table_width, void* pages, int cache_dtype, int page_size, int num_pages, int store,
+                                 int* status, cudaStream_t stream)
 {
     if (tokens <= 0) return 0;
     if (nh <= 0 || nkv <= 0 || hd <= 0) SPY_FAIL("qk_rope_store: heads %d/%d and head_dim %d must be positive", nh, nkv, hd);
+    if (src_splits <= 0) SPY_FAIL("qk_rope_store: src_splits %d must be positive", src_splits);
+    if (q_out_stride < (long long)nh * hd) SPY_FAIL("qk_rope_store: q_out rows of %lld elements cannot hold %d heads of %d", q_out_stride, nh, hd);
     if ((q_w == nullptr) != (k_w == nullptr)) SPY_FAIL("qk_rope_store: q and k norm weights must both be given or both be null");
     if (cos_sin && (rot_half <= 0 || 2 * rot_half > hd)) SPY_FAIL("qk_rope_store: rotary width %d does not fit head_dim %d", 2 * rot_half, hd);
     if (store && (page_size <= 0 || num_pages <= 0 || table_width <= 0 || !pages || !block_table))
         SPY_FAIL("qk_rope_store: storing needs pages, a block table and positive page_size/num_pages/table_width");
-    SPY_DISPATCH_DTYPE(act_dtype, TA, {
-        SPY_DISPATCH_DTYPE(cache_dtype, TC, {
-            SPY_DISPATCH_DTYPE(w_dtype, TW, {
-                return launch<TA, TC, TW>(qkv, tokens, nh, nkv, hd, q_w, k_w, eps, cos_sin, rot_half, table_rows, positions, seq_of_token,
-                                          block_table, table_width, pages, page_size, num_pages, store, status, stream);
+    SPY_DISPATCH_DTYPE(src_dtype, TS, {
+        SPY_DISPATCH_DTYPE(q_dtype, TQ, {
+            SPY_DISPATCH_DTYPE(cache_dtype, TC, {
+                SPY_DISPATCH_DTYPE(w_dtype, TW, {
+                    return launch<TS, TQ, TC, TW>(src, src_splits, src_split_stride, q_out, q_out_stride, tokens, nh, nkv, hd, q_w, k_w, eps,
+                                                  cos_sin, rot_half, table_rows, positions, seq_of_token, block_table, table_width, pages,
+                                                  page_size, num_pages, store, status, stream);
+                })
             })
         })
     })

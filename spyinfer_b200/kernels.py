@@ -142,15 +142,31 @@ def build_rope_table(inv_freq: torch.Tensor, rows: int) -> torch.Tensor:
 def qk_rope_store(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, q_weight: Optional[torch.Tensor],
                   k_weight: Optional[torch.Tensor], eps: float, rope_table: Optional[torch.Tensor], positions: torch.Tensor,
                   seq_of_token: torch.Tensor, block_table: Optional[torch.Tensor], pages: Optional[torch.Tensor], store: bool = True,
-                  status: Optional[torch.Tensor] = None) -> None:
-    """In place on the q heads of ``qkv [T, (nh + 2 nkv) hd]``: per-head RMSNorm (if weights are
-    given) and rotation (if a table is given).  With ``store`` the k heads (normed, rotated)
-    and the v heads go to ``pages [num_pages, 2, nkv, page_size, hd]`` through ``block_table
-    [S, width]``."""
-    _check(qkv, "qkv", ndim=2)
-    T = qkv.shape[0]
-    if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
-        raise KernelError(f"qkv: expected {(num_heads + 2 * num_kv_heads) * head_dim} columns, found {qkv.shape[1]}")
+                  status: Optional[torch.Tensor] = None, q_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Per-head RMSNorm (if weights are given) and rotation (if a table is given) of the q and k
+    heads of ``qkv [T, (nh + 2 nkv) hd]``, or of a stack ``[splits, T, ...]`` of float32 partial
+    products that is summed on the way.  q goes to ``q_out [T, nh hd]`` (default: in place,
+    which a stack does not allow).  With ``store`` the k heads (normed, rotated) and the v heads
+    go to ``pages [num_pages, 2, nkv, page_size, hd]`` through ``block_table [S, width]``.
+    Returns the tensor that holds q (rows may be wider than ``nh hd``)."""
+    width = (num_heads + 2 * num_kv_heads) * head_dim
+    if qkv.dim() == 3:
+        _check(qkv, "qkv partial products", torch.float32, 3)
+        splits, T = qkv.shape[0], qkv.shape[1]
+        split_stride = qkv.shape[1] * qkv.shape[2]
+        if q_out is None:
+            raise KernelError("qk_rope_store: a stack of partial products needs q_out")
+    else:
+        _check(qkv, "qkv", ndim=2)
+        splits, T, split_stride = 1, qkv.shape[0], 0
+    if qkv.shape[-1] != width:
+        raise KernelError(f"qkv: expected {width} columns, found {qkv.shape[-1]}")
+    if q_out is None:
+        q_out = qkv
+    else:
+        _check(q_out, "q output", ndim=2)
+        if q_out.shape[0] != T or q_out.shape[1] < num_heads * head_dim:
+            raise KernelError(f"q output: expected [{T}, >= {num_heads * head_dim}], found {tuple(q_out.shape)}")
     _check(positions, "positions", torch.int32, 1)
     _check(seq_of_token, "seq_of_token", torch.int32, 1)
     if positions.shape[0] != T or seq_of_token.shape[0] != T:
@@ -168,7 +184,7 @@ def qk_rope_store(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim
     if rope_table is not None:
         _check(rope_table, "rope table", torch.float32, 3)
         table_rows, rot_half = rope_table.shape[0], rope_table.shape[1]
-    page_size = num_pages = width = cache_code = 0
+    page_size = num_pages = table_width = cache_code = 0
     if store:
         if pages is None or block_table is None:
             raise KernelError("qk_rope_store: storing needs pages and a block table")
@@ -177,12 +193,14 @@ def qk_rope_store(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim
         num_pages, two, nkv, page_size, hd = pages.shape
         if two != 2 or nkv != num_kv_heads or hd != head_dim:
             raise KernelError(f"cache pages: expected [pages, 2, {num_kv_heads}, page_size, {head_dim}], found {tuple(pages.shape)}")
-        width = block_table.shape[1]
+        table_width = block_table.shape[1]
         cache_code = _code(pages, "cache pages")
-    _call("qk_rope_store", "spy_qk_rope_store", _ptr(qkv), _code(qkv, "qkv"), T, num_heads, num_kv_heads, head_dim, _ptr(q_weight),
-          _ptr(k_weight), w_code, ctypes.c_float(eps), _ptr(rope_table), rot_half, table_rows, _ptr(positions), _ptr(seq_of_token),
-          _ptr(block_table if store else None), width, _ptr(pages if store else None), cache_code, page_size, num_pages,
+    _call("qk_rope_store", "spy_qk_rope_store", _ptr(qkv), _code(qkv, "qkv"), splits, ctypes.c_longlong(split_stride), _ptr(q_out),
+          _code(q_out, "q output"), ctypes.c_longlong(q_out.shape[1]), T, num_heads, num_kv_heads, head_dim, _ptr(q_weight), _ptr(k_weight),
+          w_code, ctypes.c_float(eps), _ptr(rope_table), rot_half, table_rows, _ptr(positions), _ptr(seq_of_token),
+          _ptr(block_table if store else None), table_width, _ptr(pages if store else None), cache_code, page_size, num_pages,
           int(bool(store)), _ptr(status), _stream())
+    return q_out
 
 
 def attention_generic(q: torch.Tensor, num_heads: int, head_dim: int, out: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor,
@@ -351,19 +369,47 @@ def _scratch(device) -> torch.Tensor:
     return _gemm_scratch[key]
 
 
-def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``out[M, N] = a[M, K] @ w[N, K]^T`` on the tensor cores: bfloat16 operands, 32-bit
-    accumulation, bfloat16 or float32 output.  K must be a multiple of 8."""
+def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None,
+                 out_dtype: Optional[torch.dtype] = None, epilogue: Optional[str] = None, defer: bool = False) -> torch.Tensor:
+    """``a[M, K] @ w[N, K]^T`` on the tensor cores: bfloat16 operands, 32-bit accumulation,
+    bfloat16 or float32 output.  K must be a multiple of 8.
+
+    ``epilogue="swiglu"``: ``w``'s rows alternate gate and up rows and the result is
+    ``silu(gate) * up``, ``[M, N / 2]``.  ``defer=True``: when the kernel splits K, the float32
+    partial products are returned unsummed as ``[splits, M, N]`` for a consumer that adds them
+    (``rmsnorm``'s delta, ``qk_rope_store``'s input); otherwise the result is ``[M, N]``."""
     _check(a, "gemm input", torch.bfloat16, 2)
     _check(w, "gemm weight", torch.bfloat16, 2)
-    _check(out, "gemm output", ndim=2)
     M, K = a.shape
     N = w.shape[0]
-    if w.shape[1] != K or tuple(out.shape) != (M, N):
-        raise KernelError(f"gemm: shapes do not fit: input {tuple(a.shape)}, weight {tuple(w.shape)}, output {tuple(out.shape)}")
-    scratch = _scratch(a.device)
+    if w.shape[1] != K:
+        raise KernelError(f"gemm: shapes do not fit: input {tuple(a.shape)}, weight {tuple(w.shape)}")
+    if epilogue not in (None, "swiglu"):
+        raise KernelError(f"gemm: unknown epilogue {epilogue!r}")
+    n_out = N // 2 if epilogue == "swiglu" else N
     if status is None:
         status = status_word(a.device)
-    _call("gemm_tcgen05", "spy_gemm_tcgen05", _ptr(a), ctypes.c_longlong(K), _ptr(w), ctypes.c_longlong(K), _ptr(out), _code(out, "gemm output"),
-          ctypes.c_longlong(N), M, N, K, _ptr(scratch), ctypes.c_longlong(scratch.numel()), _ptr(status), _stream())
+    lib = build.load("gemm_tcgen05")
+    if defer and epilogue is None and out is None:
+        splits, need = ctypes.c_int(1), ctypes.c_longlong(0)
+        lib.spy_gemm_tcgen05_plan(M, N, K, ctypes.c_longlong(1 << 40), ctypes.byref(splits), ctypes.byref(need))
+        if splits.value > 1:
+            stack = torch.empty((splits.value, M, N), dtype=torch.float32, device=a.device)
+            used = ctypes.c_int(0)
+            _call("gemm_tcgen05", "spy_gemm_tcgen05_ex", _ptr(a), ctypes.c_longlong(K), _ptr(w), ctypes.c_longlong(K), None, BF16,
+                  ctypes.c_longlong(N), M, N, K, _ptr(stack), ctypes.c_longlong(stack.numel()), 0, 1, ctypes.byref(used), _ptr(status),
+                  _stream())
+            if used.value != splits.value:
+                raise KernelError(f"gemm: planned {splits.value} splits, the kernel used {used.value}")
+            return stack
+    if out is None:
+        out = torch.empty((M, n_out), dtype=out_dtype or torch.bfloat16, device=a.device)
+    else:
+        _check(out, "gemm output", ndim=2)
+        if tuple(out.shape) != (M, n_out):
+            raise KernelError(f"gemm: output {tuple(out.shape)} does not fit [{M}, {n_out}]")
+    scratch = _scratch(a.device)
+    _call("gemm_tcgen05", "spy_gemm_tcgen05_ex", _ptr(a), ctypes.c_longlong(K), _ptr(w), ctypes.c_longlong(K), _ptr(out),
+          _code(out, "gemm output"), ctypes.c_longlong(n_out), M, N, K, _ptr(scratch), ctypes.c_longlong(scratch.numel()),
+          1 if epilogue == "swiglu" else 0, 0, None, _ptr(status), _stream())
     return out

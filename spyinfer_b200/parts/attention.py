@@ -87,20 +87,23 @@ class Attention(Mixer):
         return PagedCacheNeed(self.nkv, self.hd, int(self.window) if self.window is not None else None)
 
     def forward(self, x, batch, cache):
-        qkv = self.qkv(x)
-        kernels.qk_rope_store(qkv, self.nh, self.nkv, self.hd, self.q_norm, self.k_norm, float(self.qk_norm_eps or 0.0),
-                              self.rope_table, batch.positions, batch.seq_of_token, cache.block_table, cache.pages,
-                              store=cache.writes, status=batch.status)
+        qkv = self.qkv(x, defer=True)
+        q = None
+        if qkv.dim() == 3:   # split-K partial products: summed inside the next kernel, q gets a buffer of its own
+            q = torch.empty((x.shape[0], self.nh * self.hd), dtype=x.dtype, device=x.device)
+        q = kernels.qk_rope_store(qkv, self.nh, self.nkv, self.hd, self.q_norm, self.k_norm, float(self.qk_norm_eps or 0.0),
+                                  self.rope_table, batch.positions, batch.seq_of_token, cache.block_table, cache.pages,
+                                  store=cache.writes, status=batch.status, q_out=q)
         out = torch.empty((x.shape[0], self.nh * self.hd), dtype=x.dtype, device=x.device)
         if not self.fast:
-            kernels.attention_generic(qkv, self.nh, self.hd, out, cache.pages, cache.block_table, batch.positions, batch.seq_of_token,
+            kernels.attention_generic(q, self.nh, self.hd, out, cache.pages, cache.block_table, batch.positions, batch.seq_of_token,
                                       self.scale, window=self.window, status=batch.status)
         elif batch.num_tokens == batch.num_seqs:
             # every request brings one token: decoding, keys split across blocks
-            kernels.attention_mma(qkv, self.nh, self.hd, out, cache.pages, cache.block_table, batch.positions, batch.q_start,
+            kernels.attention_mma(q, self.nh, self.hd, out, cache.pages, cache.block_table, batch.positions, batch.q_start,
                                   batch.num_seqs, self.scale, window=self.window, split_keys=self.split_keys,
                                   max_splits=self.max_splits, status=batch.status)
         else:
-            kernels.attention_mma(qkv, self.nh, self.hd, out, cache.pages, cache.block_table, batch.positions, batch.q_start,
+            kernels.attention_mma(q, self.nh, self.hd, out, cache.pages, cache.block_table, batch.positions, batch.q_start,
                                   batch.num_seqs, self.scale, window=self.window, status=batch.status)
-        return self.o(out)
+        return self.o(out, defer=True)

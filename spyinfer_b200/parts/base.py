@@ -60,7 +60,9 @@ class Norm(Part):
     def forward_add(self, residual: torch.Tensor, delta: Optional[torch.Tensor], rows: Optional[torch.Tensor] = None,
                     out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         """``residual += delta`` (32-bit, in place, skipped when ``delta`` is None), then the
-        norm of the sum.  With ``rows`` only those rows are normed and nothing is written back."""
+        norm of the sum.  With ``rows`` only those rows are normed and nothing is written back.
+        ``delta`` is ``[rows, size]``, or a stack ``[splits, rows, size]`` of float32 partial
+        products (a mixer or feed-forward may hand its last product over unsummed); all are added."""
         raise NotImplementedError
 
 

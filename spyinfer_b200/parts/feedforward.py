@@ -2,7 +2,9 @@
 
 spymaster2h/spyinfer src/models/qwen3.hpp:233-263 with SiLU as the activation (SwiGLU:
 src/backends/cpu/x64/kernels.cpp:242-247).  The gate and up projections are fused into one
-matrix at load, so one product feeds the activation kernel.
+matrix at load; on the bfloat16 path their rows are interleaved and the activation runs in
+the product's epilogue, so the gate and up activations never reach memory.  The output may
+come back as a stack of split-K partial products, which the next norm adds to the residual.
 """
 from __future__ import annotations
 
@@ -26,6 +28,7 @@ class GatedMLP(FeedForward):
             raise ValueError(f"gated_mlp: activation {params['activation']!r} is not implemented (only \"silu\")")
         self.prefix = params.get("prefix", "")
         self.gate_up = self.down = None
+        self.fused = False
 
     def weight_decls(self):
         p = self.prefix
@@ -38,13 +41,21 @@ class GatedMLP(FeedForward):
         gate, up = tensors[p + "gate_proj.weight"], tensors[p + "up_proj.weight"]
         if gate.dtype != up.dtype:
             gate, up = gate.float(), up.float()
-        self.gate_up = Linear(torch.cat([gate, up], dim=0).contiguous(), self.ctx.dtype)
+        self.fused = (self.ctx.dtype == torch.bfloat16 and gate.dtype == torch.bfloat16
+                      and kernels.tensor_core_gemm_takes(2 * self.inter, self.hidden))
+        if self.fused:
+            # rows alternate gate_i, up_i: the tensor-core product applies SwiGLU in its epilogue
+            self.gate_up = Linear(torch.stack([gate, up], dim=1).reshape(2 * self.inter, self.hidden).contiguous(), self.ctx.dtype)
+        else:
+            self.gate_up = Linear(torch.cat([gate, up], dim=0).contiguous(), self.ctx.dtype)
         self.down = Linear(tensors[p + "down_proj.weight"], self.ctx.dtype)
 
     def modules(self):
-        return ["swiglu"] + self.gate_up.modules() + self.down.modules()
+        return ([] if self.fused else ["swiglu"]) + self.gate_up.modules() + self.down.modules()
 
     def forward(self, x):
+        if self.fused:
+            return self.down(self.gate_up(x, epilogue="swiglu"), defer=True)
         gu = self.gate_up(x)
         z = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
         kernels.swiglu(gu, z)

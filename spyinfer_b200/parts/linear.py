@@ -27,8 +27,13 @@ class Linear:
     def modules(self) -> List[str]:
         return ["gemm_tcgen05"] if self.fast else ["gemm_simt"]
 
-    def __call__(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-        out = torch.empty((x.shape[0], self.out_features), dtype=out_dtype or x.dtype, device=x.device)
+    def __call__(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None, epilogue: Optional[str] = None, defer: bool = False) -> torch.Tensor:
+        """``epilogue="swiglu"`` (tensor-core kernel only; the weight's rows must alternate gate
+        and up rows) returns ``silu(gate) * up``.  ``defer=True`` allows the result to come back
+        as a stack ``[splits, rows, out]`` of float32 partial products that the consumer sums."""
         if self.fast:
-            return kernels.gemm_tcgen05(x, self.weight, out)
+            return kernels.gemm_tcgen05(x, self.weight, out_dtype=out_dtype or x.dtype, epilogue=epilogue, defer=defer)
+        if epilogue is not None:
+            raise ValueError("only the tensor-core product has fused epilogues")
+        out = torch.empty((x.shape[0], self.out_features), dtype=out_dtype or x.dtype, device=x.device)
         return kernels.gemm_simt(x, self.weight, out)

@@ -383,3 +383,69 @@ def test_attention_mma_finds_one_far_key(split_keys):
         hit = torch.allclose(out[0, :hd].float(), vs[0][far, 0].float(), atol=2e-2)
         inside = window is None or far > L - 1 - window
         assert hit == inside, f"window {window}, far key {far}: expected {'a hit' if inside else 'no hit'}"
+
+
+@pytest.mark.parametrize("M,I,K", [(3, 100, 64), (16, 328, 200), (40, 1000, 136), (64, 6144, 512), (130, 520, 264), (300, 12288, 1024)])
+def test_gemm_tcgen05_swiglu_epilogue(M, I, K):
+    """Gate and up rows interleaved in the weight; the product's epilogue applies SwiGLU."""
+    from spyinfer_b200 import kernels
+    torch.manual_seed(M + I)
+    a = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    gate = (torch.randn(I, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
+    up = (torch.randn(I, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
+    w = torch.stack([gate, up], dim=1).reshape(2 * I, K).contiguous()
+    out = kernels.gemm_tcgen05(a, w, epilogue="swiglu")
+    assert out.shape == (M, I) and out.dtype == torch.bfloat16
+    g, u = a.float() @ gate.float().t(), a.float() @ up.float().t()
+    ref = (g / (1 + torch.exp(-g))) * u
+    torch.testing.assert_close(out.float(), ref.to(torch.bfloat16).float(), rtol=1.6e-2, atol=2e-3)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (24, 1024, 2048), (64, 384, 12288), (200, 512, 4096)])
+def test_gemm_tcgen05_deferred_reduction(M, N, K):
+    """With defer=True a split-K product hands back its partial products; their sum is the product."""
+    from spyinfer_b200 import kernels
+    a = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
+    stack = kernels.gemm_tcgen05(a, w, defer=True)
+    assert stack.dim() == 3 and stack.shape[1:] == (M, N) and stack.dtype == torch.float32 and stack.shape[0] > 1
+    direct = kernels.gemm_tcgen05(a, w, out_dtype=torch.float32)
+    acc = stack[0].clone()
+    for s in range(1, stack.shape[0]):
+        acc += stack[s]
+    assert torch.equal(acc, direct)          # the reduce kernel adds the splits in the same order
+    torch.testing.assert_close(direct, a.float() @ w.float().t(), rtol=1e-4, atol=2e-4)
+    # the fused consumers: rmsnorm adds the stack to the residual, qk_rope_store sums it on the way
+    x = torch.randn(M, N, device=DEV)
+    wn = torch.ones(N, device=DEV, dtype=torch.bfloat16)
+    out1, out2 = torch.empty(M, N, device=DEV, dtype=torch.bfloat16), torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    x1, x2 = x.clone(), x.clone()
+    kernels.rmsnorm(x1, wn, 1e-6, out1, delta=stack, write_back=True)
+    kernels.rmsnorm(x2, wn, 1e-6, out2, delta=direct, write_back=True)
+    torch.testing.assert_close(x1, x2, rtol=2e-6, atol=2e-6)     # x + (s0 + s1 + ...) against ((x + s0) + s1) + ...: one rounding apart
+    torch.testing.assert_close(out1.float(), out2.float(), rtol=1e-2, atol=1e-2)
+
+
+def test_qk_rope_store_sums_a_stack_of_partial_products():
+    from spyinfer_b200 import kernels
+    nh, nkv, hd, page_size, T = 4, 2, 64, 16, 9
+    width = (nh + 2 * nkv) * hd
+    stack = torch.randn(3, T, width, device=DEV)
+    total = (stack[0] + stack[1]) + stack[2]
+    qw = (1 + 0.1 * torch.randn(hd, device=DEV)).to(torch.bfloat16)
+    kw = (1 + 0.1 * torch.randn(hd, device=DEV)).to(torch.bfloat16)
+    inv = torch.pow(torch.tensor(10000.0), -torch.arange(hd // 2, dtype=torch.float32) / (hd // 2)).to(DEV)
+    table = kernels.build_rope_table(inv, 64)
+    positions = torch.arange(5, 5 + T, dtype=torch.int32, device=DEV)
+    seq_of = torch.zeros(T, dtype=torch.int32, device=DEV)
+    bt = torch.tensor([[2, 0, 1]], dtype=torch.int32, device=DEV)
+    pages_a = torch.zeros(3, 2, nkv, page_size, hd, device=DEV, dtype=torch.bfloat16)
+    pages_b = torch.zeros_like(pages_a)
+    q_a = torch.empty(T, nh * hd, device=DEV, dtype=torch.bfloat16)
+    kernels.qk_rope_store(stack, nh, nkv, hd, qw, kw, 1e-6, table, positions, seq_of, bt, pages_a, q_out=q_a)
+    plain = total.clone()                                            # float32 in place
+    kernels.qk_rope_store(plain, nh, nkv, hd, qw, kw, 1e-6, table, positions, seq_of, bt, pages_b)
+    torch.testing.assert_close(q_a.float(), plain[:, :nh * hd].to(torch.bfloat16).float(), rtol=0, atol=0)
+    assert torch.equal(pages_a, pages_b)
+    with pytest.raises(kernels.KernelError):
+        kernels.qk_rope_store(stack, nh, nkv, hd, qw, kw, 1e-6, table, positions, seq_of, bt, pages_a)    # a stack cannot be rotated in place
