@@ -41,6 +41,7 @@ attention_generic_kernel(const TA* __restrict__ q, long long q_row_stride, TA* _
                          const int* __restrict__ positions, const int* __restrict__ seq_of_token, int window, float scale, int* status)
 {
     extern __shared__ float smem[];
+    pdl_enter();
     float* q_s = smem;                       // hd
     float* p_s = q_s + hd;                   // CHUNK
     long long* row_s = (long long*)(p_s + CHUNK);  // CHUNK offsets of K rows (elements); 8-byte aligned: hd % 4 == 0, CHUNK even
@@ -136,7 +137,7 @@ extern "C" int spy_attention_generic(const void* q, long long q_row_stride, void
     dim3 grid(tokens, nh);
     SPY_DISPATCH_DTYPE(act_dtype, TA, {
         SPY_DISPATCH_DTYPE(cache_dtype, TC, {
-            attention_generic_kernel<TA, TC><<<grid, CHUNK, smem, stream>>>(
+            spy_launch(attention_generic_kernel<TA, TC>, grid, dim3(CHUNK), smem, stream,
                 (const TA*)q, q_row_stride, (TA*)out, (const TC*)pages, block_table, table_width, page_size, num_pages, nh, nkv, hd,
                 positions, seq_of_token, window, scale, status);
         })

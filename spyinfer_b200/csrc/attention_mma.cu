@@ -408,6 +408,7 @@ __global__ void __launch_bounds__(NWARPS * 32, NWARPS <= 4 ? 2 : 1) attention_ti
 {
     extern __shared__ uint4 tile_smem[];   // [TILE_STAGES][2 (K, V)][TILE_KEYS][HD / 8] chunks of 16 bytes
     __shared__ int s_seq, s_tok0;
+    pdl_enter();
     constexpr int CPR = HD / 8;                        // 16-byte chunks per row
     constexpr int STAGE_CHUNKS = 2 * TILE_KEYS * CPR;
     const int tokens_per_tile = 16 / p.Gp, tokens_per_block = NWARPS * tokens_per_tile;
@@ -531,6 +532,7 @@ __global__ void __launch_bounds__(WARPS * 32, 2) attention_split_kernel(const Pa
     // shared memory: the copy ring, then this split's slice of the block table; after the walk
     // the ring's space is reused for the merge: [WARPS][16][HD] outputs, then [WARPS][16][2] (m, l)
     extern __shared__ uint4 ring_smem[];
+    pdl_enter();
     constexpr int PIECES = 2 * (HD / 32) + 4 * (HD / 64);
     float* s_o = reinterpret_cast<float*>(ring_smem);
     float* s_ml = s_o + WARPS * 16 * HD;
@@ -621,6 +623,7 @@ __global__ void __launch_bounds__(WARPS * 32, 2) attention_split_kernel(const Pa
 template <int HD>
 __global__ void attention_merge_kernel(const Params p)
 {
+    pdl_enter();
     const int seq = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
     const int tok = p.q_start[seq];
     const int pos = p.positions[tok];
@@ -690,8 +693,8 @@ extern "C" int spy_attention_mma(const void* q, long long q_row_stride, void* ou
             SPY_CUDA(cudaFuncSetAttribute(attention_tiles_kernel<128, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
             tiles_configured = true;
         }
-        if (hd == 64) attention_tiles_kernel<64, TW><<<grid, TW * 32, tile_bytes, stream>>>(p);
-        else attention_tiles_kernel<128, TW><<<grid, TW * 32, tile_bytes, stream>>>(p);
+        if (hd == 64) spy_launch(attention_tiles_kernel<64, TW>, grid, dim3(TW * 32), tile_bytes, stream, p);
+        else spy_launch(attention_tiles_kernel<128, TW>, grid, dim3(TW * 32), tile_bytes, stream, p);
         SPY_CHECK_LAUNCH("attention_mma (tiles)");
         return 0;
     }
@@ -716,13 +719,13 @@ extern "C" int spy_attention_mma(const void* q, long long q_row_stride, void* ou
         SPY_CUDA(cudaFuncSetAttribute(attention_split_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024));
         configured = true;
     }
-    if (hd == 64) attention_split_kernel<64><<<grid, WARPS * 32, smem, stream>>>(p);
-    else attention_split_kernel<128><<<grid, WARPS * 32, smem, stream>>>(p);
+    if (hd == 64) spy_launch(attention_split_kernel<64>, grid, dim3(WARPS * 32), smem, stream, p);
+    else spy_launch(attention_split_kernel<128>, grid, dim3(WARPS * 32), smem, stream, p);
     SPY_CHECK_LAUNCH("attention_mma (split)");
     if (max_splits > 1) {
         dim3 mgrid(seqs, nh);
-        if (hd == 64) attention_merge_kernel<64><<<mgrid, 64, 0, stream>>>(p);
-        else attention_merge_kernel<128><<<mgrid, 128, 0, stream>>>(p);
+        if (hd == 64) spy_launch(attention_merge_kernel<64>, mgrid, dim3(64), 0, stream, p);
+        else spy_launch(attention_merge_kernel<128>, mgrid, dim3(128), 0, stream, p);
         SPY_CHECK_LAUNCH("attention_mma (merge)");
     }
     return 0;

@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 typedef __nv_bfloat16 bf16;
 
@@ -34,7 +35,7 @@ enum {
 
 #define SPY_CHECK_LAUNCH(what)                                                             \
     do {                                                                                   \
-        cudaError_t e_ = cudaGetLastError();                                               \
+        cudaError_t e_ = spy_take_launch_error();                                          \
         if (e_ != cudaSuccess) SPY_FAIL("%s: launch failed: %s", what, cudaGetErrorString(e_)); \
     } while (0)
 
@@ -43,6 +44,61 @@ enum {
         cudaError_t e_ = (call);                                                           \
         if (e_ != cudaSuccess) SPY_FAIL("%s: %s", #call, cudaGetErrorString(e_));          \
     } while (0)
+
+// ---- launches with programmatic dependent launch --------------------------------------------
+// Every kernel of this library is launched with the programmatic-stream-serialization
+// attribute: it may begin while the kernel before it in the stream is still finishing.  In
+// return every kernel calls pdl_wait() before it reads or writes anything another kernel
+// touches (the wait returns when all earlier kernels are complete and their memory is visible),
+// and pdl_launch_dependents() as early as it can, which lets the next kernel start its
+// prologue.  A kernel may do work that depends on no other kernel before its wait: the
+// tensor-core product uses that to prefetch weights.  SPYINFER_PDL=0 in the environment
+// turns the attribute off (the two instructions are then no-ops).
+static thread_local cudaError_t g_spy_launch_error = cudaSuccess;
+
+static inline bool spy_pdl_enabled()
+{
+    static int enabled = -1;
+    if (enabled < 0) {
+        const char* e = getenv("SPYINFER_PDL");
+        enabled = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    return enabled == 1;
+}
+
+static inline cudaError_t spy_take_launch_error()
+{
+    cudaError_t e = g_spy_launch_error;
+    g_spy_launch_error = cudaSuccess;
+    if (e == cudaSuccess) e = cudaGetLastError();
+    return e;
+}
+
+template <typename... KArgs, typename... Args>
+static inline void spy_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = spy_pdl_enabled() ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+    if (e != cudaSuccess) g_spy_launch_error = e;
+}
+
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// the usual opening of a kernel that has nothing to do before its inputs are ready
+__device__ __forceinline__ void pdl_enter()
+{
+    pdl_launch_dependents();
+    pdl_wait();
+}
 
 __device__ __forceinline__ float to_f32(float x) { return x; }
 __device__ __forceinline__ float to_f32(bf16 x) { return __bfloat162float(x); }

@@ -9,6 +9,7 @@ template <typename TW>
 __global__ void embedding_kernel(const TW* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
                                  int hidden, int vocab, int* status)
 {
+    pdl_enter();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* dst = out + (size_t)t * hidden;
@@ -27,7 +28,7 @@ extern "C" int spy_embedding(const void* table, int table_dtype, const int* ids,
     if (tokens <= 0) return 0;
     if (hidden <= 0 || vocab <= 0) SPY_FAIL("embedding: hidden %d and vocab %d must be positive", hidden, vocab);
     SPY_DISPATCH_DTYPE(table_dtype, TW, {
-        embedding_kernel<TW><<<tokens, 256, 0, stream>>>((const TW*)table, ids, out, hidden, vocab, status);
+        spy_launch(embedding_kernel<TW>, dim3(tokens), dim3(256), 0, stream, (const TW*)table, ids, out, hidden, vocab, status);
     })
     SPY_CHECK_LAUNCH("embedding");
     return 0;

@@ -19,6 +19,7 @@ gemm_simt_kernel(const TA* __restrict__ A, long long lda, const TW* __restrict__
 {
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
+    pdl_enter();
     const int tid = threadIdx.x;
     const int tx = tid % 16, ty = tid / 16;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
@@ -78,7 +79,7 @@ extern "C" int spy_gemm_simt(const void* A, int a_dtype, long long lda, const vo
     SPY_DISPATCH_DTYPE(a_dtype, TA, {
         SPY_DISPATCH_DTYPE(w_dtype, TW, {
             SPY_DISPATCH_DTYPE(c_dtype, TC, {
-                gemm_simt_kernel<TA, TW, TC><<<grid, 256, 0, stream>>>((const TA*)A, lda, (const TW*)W, ldw, (TC*)C, ldc, M, N, K);
+                spy_launch(gemm_simt_kernel<TA, TW, TC>, grid, dim3(256), 0, stream, (const TA*)A, lda, (const TW*)W, ldw, (TC*)C, ldc, M, N, K);
             })
         })
     })

@@ -239,12 +239,29 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
 
+    pdl_launch_dependents();   // the next kernel in the stream may begin its own prologue
     if (warp == 0) {
         if (lane == 0) {
-            for (int i = 0; i < num_kb; ++i) {
+            // The weight operand (X when swapped, Y otherwise) depends on no earlier kernel: its
+            // tiles for the first stages are requested before the wait for the kernels ahead in
+            // the stream, so weights already stream in while those are finishing.
+            const int pre = min(num_kb, T::STAGES);
+            for (int i = 0; i < pre; ++i) {
+                uint8_t* xs = tiles + (size_t)i * T::STAGE_BYTES;
+                mbar_expect_tx(full_bar + i, T::STAGE_BYTES);
+                if constexpr (SWAP) tma_load_2d(xs, &map_x, (kb0 + i) * BK, x0, full_bar + i);
+                else tma_load_2d(xs + T::X_BYTES, &map_y, (kb0 + i) * BK, y0, full_bar + i);
+            }
+            pdl_wait();
+            for (int i = 0; i < pre; ++i) {
+                uint8_t* xs = tiles + (size_t)i * T::STAGE_BYTES;
+                if constexpr (SWAP) tma_load_2d(xs + T::X_BYTES, &map_y, (kb0 + i) * BK, y0, full_bar + i);
+                else tma_load_2d(xs, &map_x, (kb0 + i) * BK, x0, full_bar + i);
+            }
+            for (int i = pre; i < num_kb; ++i) {
                 const int s = i % T::STAGES;
                 const uint32_t phase = (i / T::STAGES) & 1;
-                if (i >= T::STAGES && !mbar_wait(empty_bar + s, phase ^ 1, abort_flag)) break;
+                if (!mbar_wait(empty_bar + s, phase ^ 1, abort_flag)) break;
                 uint8_t* xs = tiles + (size_t)s * T::STAGE_BYTES;
                 uint8_t* ys = xs + T::X_BYTES;
                 mbar_expect_tx(full_bar + s, T::STAGE_BYTES);
@@ -276,6 +293,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     } else {
         // epilogue: warp w reads TMEM lanes 32*(w%4) .. +31, i.e. tile rows of X
         const int quarter = warp & 3;
+        pdl_wait();   // the output buffer may still be in use by a kernel ahead in the stream
         const bool ok = mbar_wait(accum_bar, 0, abort_flag);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const int x = x0 + quarter * 32 + lane;
@@ -373,6 +391,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 template <typename TC>
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, TC* __restrict__ out, long long elems, int splits)
 {
+    pdl_enter();
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < elems; i += (long long)gridDim.x * blockDim.x) {
         float acc = partial[i];
         for (int s = 1; s < splits; ++s) acc += partial[(size_t)s * elems + i];
@@ -425,7 +444,7 @@ static int launch(const CUtensorMap& mx, const CUtensorMap& my, void* out, long 
     const int per_split = (k_blocks + splits - 1) / splits;
     dim3 grid((x_rows + BM - 1) / BM, (y_rows + BN - 1) / BN, splits);
     if (grid.y > 65535 || grid.z > 65535) SPY_FAIL("gemm_tcgen05: the grid %u x %u x %u exceeds the launch limits", grid.x, grid.y, grid.z);
-    kernel<<<grid, NUM_THREADS, T::SMEM, stream>>>(mx, my, (TC*)out, ld, split_stride, x_rows, y_rows, k_blocks, per_split, status);
+    spy_launch(kernel, grid, dim3(NUM_THREADS), T::SMEM, stream, mx, my, (TC*)out, ld, split_stride, x_rows, y_rows, k_blocks, per_split, status);
     SPY_CHECK_LAUNCH("gemm_tcgen05");
     return 0;
 }
@@ -512,8 +531,8 @@ extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, 
         if (ldc != N) SPY_FAIL("gemm_tcgen05: split-K needs a contiguous output (ldc %lld, N %d)", ldc, N);
         long long blocks = (elems + 255) / 256;
         if (blocks > 148 * 8) blocks = 148 * 8;
-        if (c_dtype == SPY_F32) splitk_reduce_kernel<float><<<(int)blocks, 256, 0, stream>>>(scratch, (float*)C, elems, splits);
-        else splitk_reduce_kernel<bf16><<<(int)blocks, 256, 0, stream>>>(scratch, (bf16*)C, elems, splits);
+        if (c_dtype == SPY_F32) spy_launch(splitk_reduce_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, (const float*)scratch, (float*)C, elems, splits);
+        else spy_launch(splitk_reduce_kernel<bf16>, dim3((int)blocks), dim3(256), 0, stream, (const float*)scratch, (bf16*)C, elems, splits);
         SPY_CHECK_LAUNCH("gemm_tcgen05 split-K reduce");
     }
     return 0;

@@ -23,6 +23,7 @@ SPY_MODULE(spy_qk_rope_store)
 
 __global__ void rope_table_kernel(float2* __restrict__ table, const float* __restrict__ inv_freq, int rows, int rot_half)
 {
+    pdl_enter();
     const long long total = (long long)rows * rot_half;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const int pos = (int)(i / rot_half), j = (int)(i % rot_half);
@@ -37,7 +38,7 @@ extern "C" int spy_build_rope_table(float* table, const float* inv_freq, int row
     const long long total = (long long)rows * rot_half;
     long long blocks = (total + 255) / 256;
     if (blocks > 4096) blocks = 4096;
-    rope_table_kernel<<<(int)blocks, 256, 0, stream>>>((float2*)table, inv_freq, rows, rot_half);
+    spy_launch(rope_table_kernel, dim3((int)blocks), dim3(256), 0, stream, (float2*)table, inv_freq, rows, rot_half);
     SPY_CHECK_LAUNCH("rope table");
     return 0;
 }
@@ -52,6 +53,7 @@ __global__ void qk_rope_store_kernel(const TS* src, int src_splits, long long sr
                                      int page_size, int num_pages, int store, int* status)
 {
     extern __shared__ float head_buf[];  // WARPS_PER_BLOCK * hd
+    pdl_enter();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads = store ? nh + 2 * nkv : nh;
     const long long item = (long long)blockIdx.x * WARPS_PER_BLOCK + warp;
@@ -130,7 +132,7 @@ static int launch(const void* src, int src_splits, long long src_split_stride, v
     if (blocks > 0x7fffffffLL) SPY_FAIL("qk_rope_store: %lld work items exceed the grid limit", items);
     const size_t smem = (size_t)WARPS_PER_BLOCK * hd * sizeof(float);
     if (smem > 48 * 1024) SPY_FAIL("qk_rope_store: head_dim %d is too large (limit %d)", hd, 48 * 1024 / 4 / WARPS_PER_BLOCK);
-    qk_rope_store_kernel<TS, TQ, TC, TW><<<(int)blocks, WARPS_PER_BLOCK * 32, smem, stream>>>(
+    spy_launch(qk_rope_store_kernel<TS, TQ, TC, TW>, dim3((int)blocks), dim3(WARPS_PER_BLOCK * 32), smem, stream,
         (const TS*)src, src_splits, src_split_stride, (TQ*)q_out, q_out_stride, tokens, nh, nkv, hd, (const TW*)q_w, (const TW*)k_w, eps,
         (const float2*)cos_sin, rot_half, table_rows, positions, seq_of_token, block_table, table_width, (TC*)pages, page_size, num_pages, store,
         status);

@@ -41,6 +41,7 @@ __global__ void rmsnorm_kernel(TX* x, const TD* __restrict__ delta, int delta_sp
                                const TW* __restrict__ w, TO* __restrict__ out, int len, float eps, int write_back)
 {
     extern __shared__ float row_buf[];  // len floats, then 33 of scratch
+    pdl_enter();
     float* scratch = row_buf + len;
     const int src_row = rows ? rows[blockIdx.x] : blockIdx.x;
     TX* xr = x + (size_t)src_row * len;
@@ -105,7 +106,7 @@ static int launch(void* x, const void* delta, int delta_splits, long long delta_
     }
     int threads = vec ? (len / 4 + 31) / 32 * 32 : len;
     threads = threads < 64 ? 64 : (threads > 1024 ? 1024 : (threads + 31) / 32 * 32);
-    kernel<<<n, threads, smem, stream>>>((TX*)x, (const TD*)delta, delta_splits, delta_split_stride, rows, (const TW*)w, (TO*)out, len, eps,
+    spy_launch(kernel, dim3(n), dim3(threads), smem, stream, (TX*)x, (const TD*)delta, delta_splits, delta_split_stride, rows, (const TW*)w, (TO*)out, len, eps,
                                          write_back);
     SPY_CHECK_LAUNCH("rmsnorm");
     return 0;

@@ -54,6 +54,7 @@ __global__ void sample_slices_kernel(const float* __restrict__ logits, long long
                                      const long long* __restrict__ seed, const long long* __restrict__ draw, float* __restrict__ slice_v,
                                      int* __restrict__ slice_i)
 {
+    pdl_enter();
     const int r = blockIdx.y, lo = blockIdx.x * slice, hi = min(vocab, lo + slice);
     const float* row = logits + (size_t)r * row_stride;
     const float temp = temperature ? temperature[r] : 0.f;
@@ -74,6 +75,7 @@ __global__ void sample_slices_kernel(const float* __restrict__ logits, long long
 
 __global__ void sample_pick_kernel(const float* __restrict__ slice_v, const int* __restrict__ slice_i, int slices, int* __restrict__ tokens)
 {
+    pdl_enter();
     const int r = blockIdx.x;
     float bv = -INFINITY;
     int bi = NONE;
@@ -97,9 +99,9 @@ extern "C" int spy_sample(const float* logits, long long row_stride, int rows, i
     const int slices = spy_sample_slices(vocab);
     const int slice = (vocab + slices - 1) / slices;
     dim3 grid(slices, rows);
-    sample_slices_kernel<<<grid, 256, 0, stream>>>(logits, row_stride, vocab, slice, temperature, seed, draw, slice_v, slice_i);
+    spy_launch(sample_slices_kernel, grid, dim3(256), 0, stream, logits, row_stride, vocab, slice, temperature, seed, draw, slice_v, slice_i);
     SPY_CHECK_LAUNCH("sample (slices)");
-    sample_pick_kernel<<<rows, 64, 0, stream>>>(slice_v, slice_i, slices, tokens);
+    spy_launch(sample_pick_kernel, dim3(rows), dim3(64), 0, stream, slice_v, slice_i, slices, tokens);
     SPY_CHECK_LAUNCH("sample (pick)");
     return 0;
 }

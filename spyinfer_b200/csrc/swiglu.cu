@@ -9,6 +9,7 @@ SPY_MODULE(spy_swiglu)
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, long long total)
 {
+    pdl_enter();
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (; i < total; i += stride) {
@@ -29,7 +30,7 @@ extern "C" int spy_swiglu(const void* gate_up, void* out, int dtype, int tokens,
     long long blocks = (total + 255) / 256;
     if (blocks > 148LL * 32) blocks = 148LL * 32;
     SPY_DISPATCH_DTYPE(dtype, T, {
-        swiglu_kernel<T><<<(int)blocks, 256, 0, stream>>>((const T*)gate_up, (T*)out, inter, total);
+        spy_launch(swiglu_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, (const T*)gate_up, (T*)out, inter, total);
     })
     SPY_CHECK_LAUNCH("swiglu");
     return 0;

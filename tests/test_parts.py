@@ -74,7 +74,8 @@ def test_gated_mlp_part(dtype):
     w = bound(part, std=0.2)
     x = torch.randn(11, 72).to(dtype)
     want = plain_model.feed_forward(x.float(), w, "")
-    close(part.forward(x.to(DEV)), want, dtype)
+    got = part.forward(x.to(DEV))
+    close(got.sum(dim=0) if got.dim() == 3 else got, want, dtype)
 
 
 def one_step_batch(cache, lens, device):
@@ -115,7 +116,10 @@ def test_attention_part(dtype, nh, nkv, hd, window, rot):
     view = cache.view(0)
     view.block_table = batch.block_tables[0]
     x = torch.randn(sum(lens), H).to(dtype)
-    got = part.forward(x.to(DEV), batch, view).float().cpu()
+    got = part.forward(x.to(DEV), batch, view).float()
+    if got.dim() == 3:          # the output projection may hand over its split-K partial products unsummed
+        got = got.sum(dim=0)
+    got = got.cpu()
     assert batch.status[0].item() == 0
     cfg = {"num_attention_heads": nh, "num_key_value_heads": nkv, "head_dim": hd, "rms_norm_eps": eps, "rope_theta": theta}
     off = 0
