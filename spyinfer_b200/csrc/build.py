@@ -31,6 +31,7 @@ MODULES = ["embedding", "rmsnorm", "qk_rope_store", "attention_generic", "attent
 
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
+_dir_lock = threading.Lock()
 
 
 class KernelBuildError(RuntimeError):
@@ -45,19 +46,29 @@ def _nvcc() -> str:
                            "and this engine has no other path")
 
 
+_build_dir_cached = None
+
+
 def _build_dir() -> str:
-    local = os.path.join(HERE, "_build")
-    try:
-        os.makedirs(local, exist_ok=True)
-        probe = os.path.join(local, f".probe{os.getpid()}")
-        with open(probe, "w"):
-            pass
-        os.remove(probe)
-        return local
-    except OSError:
-        d = os.path.join(tempfile.gettempdir(), f"spyinfer_b200_build_{os.getuid()}")
-        os.makedirs(d, exist_ok=True)
-        return d
+    """Decided once per process: ``_build/`` beside the sources if it can be written, else a
+    per-user folder under the temporary folder."""
+    global _build_dir_cached
+    if _build_dir_cached is not None:
+        return _build_dir_cached
+    with _dir_lock:
+        if _build_dir_cached is None:
+            local = os.path.join(HERE, "_build")
+            try:
+                os.makedirs(local, exist_ok=True)
+                fd, probe = tempfile.mkstemp(prefix=".probe", dir=local)
+                os.close(fd)
+                os.remove(probe)
+                _build_dir_cached = local
+            except OSError:
+                d = os.path.join(tempfile.gettempdir(), f"spyinfer_b200_build_{os.getuid()}")
+                os.makedirs(d, exist_ok=True)
+                _build_dir_cached = d
+    return _build_dir_cached
 
 
 def _source_hash(module: str) -> str:

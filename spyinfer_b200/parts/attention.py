@@ -74,8 +74,6 @@ class Attention(Mixer):
             self.q_norm, self.k_norm = tensors[p + "q_norm.weight"], tensors[p + "k_norm.weight"]
             if self.q_norm.dtype != self.k_norm.dtype:
                 self.q_norm, self.k_norm = self.q_norm.float(), self.k_norm.float()
-        if self.position is not None:
-            self.rope_table = self.position.rotation_table()
 
     def modules(self):
         mods = ["qk_rope_store", "attention_mma" if self.fast else "attention_generic"] + self.qkv.modules() + self.o.modules()
@@ -87,6 +85,8 @@ class Attention(Mixer):
         return PagedCacheNeed(self.nkv, self.hd, int(self.window) if self.window is not None else None)
 
     def forward(self, x, batch, cache):
+        if self.rope_table is None and self.position is not None:
+            self.rope_table = self.position.rotation_table()   # built by the first step (an eager one)
         qkv = self.qkv(x, defer=True)
         q = None
         if qkv.dim() == 3:   # split-K partial products: summed inside the next kernel, q gets a buffer of its own
