@@ -306,3 +306,166 @@ def test_run_order_names_a_layer_twice_and_reads_another_entrys_cache(tiny_model
     cut = torch.cat([runner.step([StepEntry("c", tokens[a:b], range(b - a))]).cpu() for a, b in [(0, 9), (9, 11), (11, 12), (12, 21)]])
     torch.testing.assert_close(cut, want, rtol=1e-4, atol=1e-5)
     runner.check_status()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embedding_head_and_block_parts(dtype):
+    """Token embedding, tied and untied head, and the pre-norm block arrangement, each alone."""
+    from spyinfer_b200.cache import CacheManager
+    from spyinfer_b200.config import PartSpec
+    from spyinfer_b200.parts import build_block, build_part
+    V, H = 331, 72
+    ctx = ctx_for(dtype)
+    emb = build_part(PartSpec("token_embedding", {"vocab_size": V, "hidden_size": H, "weight": "emb.weight"}), ctx)
+    w_e = bound(emb, std=0.3)
+    ids = torch.tensor([0, 330, 17, 17, 5], dtype=torch.int32, device=DEV)
+    h = emb.forward(ids)
+    assert h.dtype == torch.float32                     # the residual stream is 32-bit in both paths
+    torch.testing.assert_close(h.cpu(), plain_model.embed_tokens(w_e["emb.weight"], ids.tolist()))
+    for tied in (True, False):
+        head = build_part(PartSpec("lm_head", {"vocab_size": V, "hidden_size": H, "tied": tied, "weight": "head.weight", "tied_to": "emb.weight"}), ctx)
+        if tied:
+            assert head.weight_decls() == [] and head.ignorable == ["head.weight"]
+            head.bind({"emb.weight": w_e["emb.weight"].to(DEV)})
+            w_h = w_e["emb.weight"]
+        else:
+            w_h = bound(head, std=0.2, seed=5)["head.weight"]
+        x = torch.randn(4, H).to(dtype)
+        logits = head.forward(x.to(DEV))
+        assert logits.dtype == torch.float32
+        close(logits, plain_model.linear(x.float(), w_h), dtype)
+    # block: h += attn(norm(h)); h += ffn(norm(h)), the second sum left pending as delta
+    nh, nkv, hd, eps = 4, 2, 16, 1e-5
+    norm1 = build_part(PartSpec("rms_norm", {"size": H, "eps": eps, "weight": "input_layernorm.weight"}), ctx)
+    norm2 = build_part(PartSpec("rms_norm", {"size": H, "eps": eps, "weight": "post_attention_layernorm.weight"}), ctx)
+    attn = build_part(PartSpec("attention", {"hidden_size": H, "num_heads": nh, "num_kv_heads": nkv, "head_dim": hd, "qk_norm_eps": eps,
+                                             "position": PartSpec("rotary_half", {"theta": 1e4, "rotary_dim": hd}), "window": None,
+                                             "scale": None, "prefix": "self_attn."}), ctx)
+    ffn = build_part(PartSpec("gated_mlp", {"hidden_size": H, "intermediate_size": 104, "activation": "silu", "prefix": "mlp."}), ctx)
+    w = {}
+    for i, part in enumerate((norm1, norm2, attn, ffn)):
+        w.update(bound(part, std=0.15, seed=10 + i))
+    block = build_block("pre_norm", norm1, attn, norm2, ffn)
+    n = 13
+    cache = CacheManager([attn.cache_need()], 4, 16, 2, 64, dtype=dtype, device=torch.device(DEV))
+    batch = one_step_batch(cache, [n], torch.device(DEV))
+    view = cache.view(0)
+    view.block_table = batch.block_tables[0]
+    h0 = torch.randn(n, H)
+    hidden, delta = block.forward(h0.to(DEV).clone(), None, batch, view)
+    delta = delta.float().sum(dim=0) if delta.dim() == 3 else delta.float()
+    cfg = {"num_attention_heads": nh, "num_key_value_heads": nkv, "head_dim": hd, "rms_norm_eps": eps, "rope_theta": 1e4}
+    named = {"model.layers.0." + k: v for k, v in w.items()}
+    want = plain_model.decoder_layer(h0, named, 0, cfg, list(range(n)))
+    close(hidden + delta, want, dtype)
+
+
+def register_more_toy_parts():
+    """A feed-forward with routing (top-1 of three tiny experts) and a position encoding with
+    angles of its own, both defined here and used through the public registry only."""
+    from spyinfer_b200.parts import FeedForward, PositionEncoding, register_part
+    from spyinfer_b200.weights import WeightDecl
+
+    @register_part("toy_routed_ffn")
+    class ToyRoutedFFN(FeedForward):
+        def __init__(self, params, ctx):
+            super().__init__(params, ctx)
+            self.h, self.i, self.e = params["hidden_size"], params["intermediate_size"], params["experts"]
+            self.w = {}
+
+        def weight_decls(self):
+            d = [WeightDecl("moe.router.weight", (self.e, self.h))]
+            for k in range(self.e):
+                d += [WeightDecl(f"moe.experts.{k}.in.weight", (self.i, self.h)), WeightDecl(f"moe.experts.{k}.out.weight", (self.h, self.i))]
+            return d
+
+        def bind(self, tensors):
+            self.w = {k: v.float() for k, v in tensors.items()}
+
+        def forward(self, x):
+            xf = x.float()
+            logits = xf @ self.w["moe.router.weight"].t()                      # router logits in 32-bit
+            prob = torch.softmax(logits, dim=-1)
+            pick = prob.argmax(dim=-1)
+            out = torch.zeros_like(xf)
+            for k in range(self.e):
+                rows = (pick == k).nonzero().squeeze(-1)
+                if rows.numel():
+                    hid = torch.relu(xf[rows] @ self.w[f"moe.experts.{k}.in.weight"].t())
+                    out[rows] = (hid @ self.w[f"moe.experts.{k}.out.weight"].t()) * prob[rows, k:k + 1]
+            return out.to(x.dtype)
+
+    @register_part("toy_linear_angles")
+    class ToyLinearAngles(PositionEncoding):
+        def rotation_table(self):
+            r = self.params["rotary_dim"] // 2
+            pos = torch.arange(self.ctx.max_model_len, dtype=torch.float32)[:, None]
+            angle = pos * (torch.arange(r, dtype=torch.float32)[None, :] + 1.0) * self.params["step"]
+            return torch.stack([torch.cos(angle), torch.sin(angle)], dim=-1).contiguous().to(self.ctx.device)
+
+
+def test_toy_routed_feed_forward_and_toy_position_encoding():
+    """Two layers with different feed-forwards and different position encodings, none of them
+    known to the package: built from a description, stepped whole and in portions, and compared
+    with a plain statement of the same model."""
+    from spyinfer_b200.config import EngineConfig, LayerSpec, ModelSpec, PartSpec, RunEntry
+    from spyinfer_b200.engine import Model, ModelRunner, StepEntry
+    from spyinfer_b200.weights import random_tensors
+    register_more_toy_parts()
+    H, V, nh, nkv, hd, I, E, step = 64, 113, 4, 1, 32, 48, 3, 0.013
+    norm = lambda name: PartSpec("rms_norm", {"size": H, "eps": 1e-6, "weight": name})
+    attn = lambda pos: PartSpec("attention", {"hidden_size": H, "num_heads": nh, "num_kv_heads": nkv, "head_dim": hd, "qk_norm_eps": None,
+                                              "position": pos, "window": None, "scale": 0.2, "prefix": "self_attn."})
+    layers = [
+        LayerSpec("pre_norm", norm("input_layernorm.weight"), attn(PartSpec("toy_linear_angles", {"rotary_dim": hd, "step": step})),
+                  norm("post_attention_layernorm.weight"), PartSpec("gated_mlp", {"hidden_size": H, "intermediate_size": I, "activation": "silu",
+                                                                                  "prefix": "mlp."}), "model.layers.0."),
+        LayerSpec("pre_norm", norm("input_layernorm.weight"), attn(None), norm("post_attention_layernorm.weight"),
+                  PartSpec("toy_routed_ffn", {"hidden_size": H, "intermediate_size": I, "experts": E}), "model.layers.1."),
+    ]
+    spec = ModelSpec(architecture="toy2", hidden_size=H, vocab_size=V,
+                     embedding=PartSpec("token_embedding", {"vocab_size": V, "hidden_size": H, "weight": "model.embed_tokens.weight"}),
+                     layers=layers, run_order=[RunEntry(0), RunEntry(1)], final_norm=norm("model.norm.weight"),
+                     head=PartSpec("lm_head", {"vocab_size": V, "hidden_size": H, "tied": False, "weight": "lm_head.weight",
+                                               "tied_to": "model.embed_tokens.weight"}), max_position=128)
+    cfg = EngineConfig(dtype="float32", max_num_seqs=2, max_model_len=64, kvcache_block_size=8, num_kvcache_blocks=16, max_num_batched_tokens=64)
+    model = Model(spec, torch.float32, cfg.device, cfg.max_model_len)
+    w = dict(random_tensors(model.weight_decls(), seed=8, std=0.15, norm_std=0.1))
+    model.bind({k: v.to(DEV) for k, v in w.items()})
+    runner = ModelRunner(model, cfg)
+    tokens = np.random.default_rng(1).integers(0, V, 27).tolist()
+
+    # plain statement
+    T, pos = len(tokens), list(range(len(tokens)))
+    h = plain_model.embed_tokens(w["model.embed_tokens.weight"], tokens)
+    for layer in range(2):
+        p = f"model.layers.{layer}."
+        n = plain_model.rms_norm(h, w[p + "input_layernorm.weight"], 1e-6)
+        q = plain_model.linear(n, w[p + "self_attn.q_proj.weight"]).reshape(T, nh, hd)
+        k = plain_model.linear(n, w[p + "self_attn.k_proj.weight"]).reshape(T, nkv, hd)
+        v = plain_model.linear(n, w[p + "self_attn.v_proj.weight"]).reshape(T, nkv, hd)
+        if layer == 0:
+            angle = torch.tensor(pos, dtype=torch.float32)[:, None] * (torch.arange(hd // 2, dtype=torch.float32)[None, :] + 1.0) * step
+            q, k = plain_model.rotate_half(q, torch.cos(angle), torch.sin(angle)), plain_model.rotate_half(k, torch.cos(angle), torch.sin(angle))
+        o = plain_model.causal_attention(q * (0.2 * math.sqrt(hd)), k, v, pos)          # the part's scale 0.2 replaces 1/sqrt(hd)
+        h = h + plain_model.linear(o.reshape(T, nh * hd), w[p + "self_attn.o_proj.weight"])
+        n = plain_model.rms_norm(h, w[p + "post_attention_layernorm.weight"], 1e-6)
+        if layer == 0:
+            h = h + plain_model.feed_forward(n, w, p)
+        else:
+            prob = torch.softmax(n @ w[p + "moe.router.weight"].float().t(), dim=-1)
+            pick = prob.argmax(dim=-1)
+            rows = []
+            for t in range(T):
+                e = int(pick[t])
+                hid = torch.relu(w[p + f"moe.experts.{e}.in.weight"].float() @ n[t])
+                rows.append((w[p + f"moe.experts.{e}.out.weight"].float() @ hid) * prob[t, e])
+            h = h + torch.stack(rows)
+    want = plain_model.linear(plain_model.rms_norm(h, w["model.norm.weight"], 1e-6), w["lm_head.weight"])
+
+    whole = runner.step([StepEntry("w", tokens, range(T))]).cpu()
+    torch.testing.assert_close(whole, want, rtol=1e-4, atol=2e-5)
+    runner.finish("w")
+    cut = torch.cat([runner.step([StepEntry("c", tokens[a:b], range(b - a))]).cpu() for a, b in [(0, 10), (10, 12), (12, 13), (13, 27)]])
+    torch.testing.assert_close(cut, want, rtol=1e-4, atol=2e-5)
+    runner.check_status()
