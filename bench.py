@@ -193,23 +193,19 @@ def main() -> int:
         return batch * steps / (ms / 1e3), ms / steps, kernels.launch_count() - launches0
 
     def decode_e2e(batch, context, steps, warm):
-        """The same through LLMEngine.step(): host tokens in, host tokens out, every step."""
-        start_ctx = context - (steps + warm) - 2
+        """The same through the public entry point: requests are submitted with real prompts,
+        prefilled by LLMEngine.step() (untimed), then `steps` decode steps are timed, each with
+        its host-to-device copy of the batch arrays and its read-back of the sampled tokens."""
+        # requests whose prompts finish early decode while the others are still prefilling:
+        # leave room for those extra tokens so that nobody finishes inside the timed region
+        extra = batch * context // engine.config.max_num_batched_tokens + 4
+        prompt_len = context - (steps + warm) - 2 - extra
         g = torch.Generator().manual_seed(1000 + batch)
-        sp = SamplingParams(max_new_tokens=steps + warm + 1, ignore_eos=True)
-        ids = []
-        for j in range(batch):
-            # the request's cache is filled directly; the engine sees a request whose prompt is already computed but for its last token
-            prompt = torch.randint(0, vocab, (start_ctx + 1,), generator=g).tolist()
-            rid = engine.add_request(prompt, sp)
-            seq = engine.scheduler.waiting.pop()
-            cache.add_request(rid)
-            cache.reserve(rid, start_ctx)
-            cache.commit(rid, start_ctx)
-            seq.num_computed = start_ctx
-            seq.status = type(seq.status).RUNNING
-            engine.scheduler.running.append(seq)
-            ids.append(rid)
+        sp = SamplingParams(max_new_tokens=steps + warm + 2 + extra, ignore_eos=True)
+        ids = [engine.add_request(torch.randint(0, vocab, (prompt_len,), generator=g).tolist(), sp) for _ in range(batch)]
+        started = set()
+        while len(started) < batch:                      # prompts, in portions under the token budget
+            started.update(r for r, _, _ in engine.step())
         n_out = 0
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         for i in range(steps + warm):
