@@ -287,6 +287,33 @@ def attention_mma(q: torch.Tensor, num_heads: int, head_dim: int, out: torch.Ten
     return out
 
 
+def attention_tc(q: torch.Tensor, num_heads: int, head_dim: int, out: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor,
+                 positions: torch.Tensor, q_start: torch.Tensor, num_seqs: int, scale: float, window: Optional[int] = None,
+                 status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Attention of a batch of prompt portions over its pages on tcgen05 (128-row blocks, scores
+    and output in tensor memory).  Same arguments and sizes as ``attention_mma`` in tiles mode."""
+    _check(q, "attention queries", torch.bfloat16, 2)
+    _check(out, "attention output", torch.bfloat16, 2)
+    _check(pages, "cache pages", torch.bfloat16, 5)
+    _check(block_table, "block table", torch.int32, 2)
+    _check(positions, "positions", torch.int32, 1)
+    _check(q_start, "q_start", torch.int32, 1)
+    T = q.shape[0]
+    num_pages, two, nkv, page_size, hd = pages.shape
+    if two != 2 or hd != head_dim:
+        raise KernelError(f"cache pages: expected [pages, 2, nkv, page_size, {head_dim}], found {tuple(pages.shape)}")
+    if q.shape[1] < num_heads * head_dim or tuple(out.shape) != (T, num_heads * head_dim):
+        raise KernelError(f"attention: q {tuple(q.shape)} / out {tuple(out.shape)} do not fit {num_heads} heads of {head_dim}")
+    if positions.shape[0] != T or q_start.shape[0] != num_seqs + 1 or block_table.shape[0] < num_seqs:
+        raise KernelError("attention: positions need one entry per token, q_start one per sequence plus one, the block table a row per sequence")
+    if status is None:
+        status = status_word(q.device)
+    _call("attention_tc", "spy_attention_tc", _ptr(q), ctypes.c_longlong(q.shape[1]), _ptr(out), _ptr(pages), _ptr(block_table),
+          block_table.shape[1], page_size, num_pages, num_heads, nkv, head_dim, _ptr(positions), _ptr(q_start), T, num_seqs,
+          int(window or 0), ctypes.c_float(scale), _ptr(status), _stream())
+    return out
+
+
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """``out[M, N] = a[M, K] @ w[N, K]^T`` on the CUDA cores in 32-bit, any sizes and dtypes."""
     _check(a, "gemm input", ndim=2)

@@ -1,7 +1,7 @@
 """Timings of single kernels at chosen sizes, for profiling and for the summaries under profiles/.
 
     python -m spyinfer_b200.microbench gemm --m 2048 --n 24576 --k 4096 [--out-dtype float32] [--iters 20]
-    python -m spyinfer_b200.microbench attention --batch 8 --context 8192 [--q-len 1] [--split-keys 576] [--iters 10]
+    python -m spyinfer_b200.microbench attention --batch 8 --context 8192 [--q-len 1] [--split-keys 576] [--kernel tc|mma] [--iters 10]
 
 Defaults are Qwen3-8B's sizes (32 query heads, 8 key/value heads, head size 128, pages of 16).
 Timing is by CUDA events around ``iters`` launches after a warm-up; the product cycles through
@@ -39,7 +39,7 @@ def bench_gemm(M: int, N: int, K: int, out_dtype=torch.bfloat16, iters: int = 20
 
 
 def bench_attention(batch: int, context: int, q_len: int = 1, split_keys: int = 0, nh: int = 32, nkv: int = 8, hd: int = 128,
-                    page_size: int = 16, iters: int = 10) -> dict:
+                    page_size: int = 16, iters: int = 10, kernel: str = "auto") -> dict:
     width = (context + page_size - 1) // page_size
     pages = torch.randn(batch * width + 1, 2, nkv, page_size, hd, device=DEV).to(torch.bfloat16)
     bt = torch.randperm(batch * width, device=DEV).view(batch, width).to(torch.int32)
@@ -50,8 +50,13 @@ def bench_attention(batch: int, context: int, q_len: int = 1, split_keys: int = 
     out = torch.empty(T, nh * hd, device=DEV, dtype=torch.bfloat16)
     max_splits = (context + split_keys - 1) // split_keys if split_keys else 0
 
+    use_tc = kernel == "tc" or (kernel == "auto" and split_keys == 0)
+
     def run():
-        kernels.attention_mma(q, nh, hd, out, pages, bt, pos, q_start, batch, 1 / math.sqrt(hd), split_keys=split_keys, max_splits=max_splits)
+        if use_tc:
+            kernels.attention_tc(q, nh, hd, out, pages, bt, pos, q_start, batch, 1 / math.sqrt(hd))
+        else:
+            kernels.attention_mma(q, nh, hd, out, pages, bt, pos, q_start, batch, 1 / math.sqrt(hd), split_keys=split_keys, max_splits=max_splits)
 
     run()
     torch.cuda.synchronize()
@@ -82,13 +87,14 @@ def main(argv=None) -> int:
     a.add_argument("--q-len", type=int, default=1)
     a.add_argument("--split-keys", type=int, default=0, help="0: tiles mode; else split mode with this range length")
     a.add_argument("--iters", type=int, default=10)
+    a.add_argument("--kernel", default="auto", choices=["auto", "tc", "mma"], help="auto: tcgen05 for tiles mode, mma.sync for split mode")
     args = ap.parse_args(argv)
     kernels.require_cuda()
     if args.what == "gemm":
         r = bench_gemm(args.m, args.n, args.k, getattr(torch, args.out_dtype), args.iters)
         print(f"gemm M={args.m} N={args.n} K={args.k}: {r['us']:.1f} us, {r['tflops']:.1f} TFLOP/s, {r['gbs']:.1f} GB/s")
     else:
-        r = bench_attention(args.batch, args.context, args.q_len, args.split_keys, iters=args.iters)
+        r = bench_attention(args.batch, args.context, args.q_len, args.split_keys, iters=args.iters, kernel=args.kernel)
         print(f"attention batch={args.batch} context={args.context} q_len={args.q_len} split_keys={args.split_keys}: {r['us']:.1f} us, "
               f"cache read at {r['kv_gbs']:.1f} GB/s, {r['tflops']:.1f} TFLOP/s")
     return 0

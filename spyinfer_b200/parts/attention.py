@@ -76,7 +76,7 @@ class Attention(Mixer):
                 self.q_norm, self.k_norm = self.q_norm.float(), self.k_norm.float()
 
     def modules(self):
-        mods = ["qk_rope_store", "attention_mma" if self.fast else "attention_generic"] + self.qkv.modules() + self.o.modules()
+        mods = ["qk_rope_store"] + (["attention_mma", "attention_tc"] if self.fast else ["attention_generic"]) + self.qkv.modules() + self.o.modules()
         if self.position is not None:
             mods += self.position.modules()
         return mods
@@ -104,6 +104,7 @@ class Attention(Mixer):
                                   batch.num_seqs, self.scale, window=self.window, split_keys=self.split_keys,
                                   max_splits=self.max_splits, status=batch.status)
         else:
-            kernels.attention_mma(q, self.nh, self.hd, out, cache.pages, cache.block_table, batch.positions, batch.q_start,
-                                  batch.num_seqs, self.scale, window=self.window, status=batch.status)
+            # prompt portions (and whatever decodes beside them): 128-row blocks on tcgen05
+            kernels.attention_tc(q, self.nh, self.hd, out, cache.pages, cache.block_table, batch.positions, batch.q_start,
+                                 batch.num_seqs, self.scale, window=self.window, status=batch.status)
         return self.o(out, defer=True)

@@ -449,3 +449,53 @@ def test_qk_rope_store_sums_a_stack_of_partial_products():
     assert torch.equal(pages_a, pages_b)
     with pytest.raises(kernels.KernelError):
         kernels.qk_rope_store(stack, nh, nkv, hd, qw, kw, 1e-6, table, positions, seq_of, bt, pages_a)    # a stack cannot be rotated in place
+
+
+@pytest.mark.parametrize("nh,nkv,hd,page_size,window", [(8, 2, 128, 16, None), (10, 2, 64, 16, 150), (4, 4, 128, 8, None), (16, 1, 64, 32, None),
+                                                        (6, 2, 128, 5, 33), (32, 8, 128, 16, None)])
+def test_attention_tc_mixed_batch(nh, nkv, hd, page_size, window):
+    """tcgen05 attention: portions, single tokens, a one-token sequence and a 300-token portion
+    (several 128-row blocks and several key tiles) in one batch; group sizes 1, 3, 4, 5, 16."""
+    from spyinfer_b200 import kernels
+    torch.manual_seed(nh * hd + 1)
+    lens = [1, 70, 333, 129, 40, 700]
+    pages, bt, ks, vs = paged_setup(6, lens, nkv, hd, page_size, torch.bfloat16)
+    toks = ([(0, 0)] + [(1, p) for p in range(30, 53)] + [(2, 332)] + [(3, 127), (3, 128)] + [(4, p) for p in range(40)]
+            + [(5, p) for p in range(400, 700)])
+    T = len(toks)
+    q = torch.randn(T, (nh + 2 * nkv) * hd, device=DEV).to(torch.bfloat16)
+    positions = torch.tensor([p for _, p in toks], dtype=torch.int32, device=DEV)
+    q_start = torch.tensor([0, 1, 24, 25, 27, 67, 367], dtype=torch.int32, device=DEV)
+    out = torch.full((T, nh * hd), float("nan"), device=DEV, dtype=torch.bfloat16)
+    scale = 1 / math.sqrt(hd)
+    kernels.attention_tc(q, nh, hd, out, pages, bt, positions, q_start, 6, scale, window=window)
+    torch.cuda.synchronize()
+    assert kernels.status_word(DEV)[0].item() == 0
+    assert torch.isfinite(out.float()).all()
+    for i, (s, p) in enumerate(toks):
+        if s == 5 and i % 7:          # check every 7th row of the long portion, and its first and last rows
+            if i not in (67, T - 1):
+                continue
+        ref = ref_attention(q[i, :nh * hd].view(nh, hd), ks[s], vs[s], p, scale, window)
+        torch.testing.assert_close(out[i].view(nh, hd).double(), ref, rtol=2e-2, atol=2e-2)
+
+
+def test_attention_tc_finds_one_far_key_and_survives_large_scores():
+    """One key stands out by a large score in a late tile (the running maximum jumps by far more
+    than the rescale threshold after earlier tiles have accumulated): the output must be that
+    key's value row; positions at tile and page edges, and a window's edge."""
+    from spyinfer_b200 import kernels
+    nh, nkv, hd, page_size, L = 4, 1, 64, 16, 700
+    pages, bt, ks, vs = paged_setup(1, [L], nkv, hd, page_size, torch.bfloat16)
+    q = torch.randn(1, nh * hd, device=DEV).to(torch.bfloat16)
+    pos = torch.tensor([L - 1], dtype=torch.int32, device=DEV)
+    q_start = torch.tensor([0, 1], dtype=torch.int32, device=DEV)
+    out = torch.empty(1, nh * hd, device=DEV, dtype=torch.bfloat16)
+    for window, far in [(None, 0), (None, 15), (None, 127), (None, 128), (None, 511), (None, 699), (300, L - 300), (300, L - 301)]:
+        pg = pages.clone()
+        page, slot = int(bt[0, far // page_size]), far % page_size
+        pg[page, 0, 0, slot] = (60.0 * q[0, :hd].float() / q[0, :hd].float().norm()).to(torch.bfloat16)
+        kernels.attention_tc(q, nh, hd, out, pg, bt, pos, q_start, 1, 1.0, window=window)
+        hit = torch.allclose(out[0, :hd].float(), vs[0][far, 0].float(), atol=2e-2)
+        inside = window is None or far > L - 1 - window
+        assert hit == inside, f"window {window}, far key {far}: expected {'a hit' if inside else 'no hit'}"
