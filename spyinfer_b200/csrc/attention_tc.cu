@@ -14,15 +14,23 @@
 // The output is rescaled only when a row's maximum grew by more than 2^8 (the stale maximum
 // keeps every probability below 256, harmless in bfloat16 and float32); then the warp reads,
 // scales and writes back its rows of O (tcgen05.ld / tcgen05.st).
-// Key/value tiles are double-buffered: the softmax warps request tile j + 1 with cp.async
-// before they work on tile j.  A fifth warp allocates tensor memory and issues the MMAs.
+// Scores, probabilities and the key and value tiles are double-buffered, so that the tensor
+// cores compute Q.K of the next tile and P.V of the last one while the softmax warps work on
+// the current one.  A fifth warp allocates tensor memory and issues the MMAs; two more bring
+// the key and the value tiles in with TMA, one box of 64 columns x page_size rows per page and
+// half of head_dim, straight from the paged cache (no cluster multicast), as soon as a stage
+// is free.  Pages the block table does not name are skipped; the stages are zeroed once, so
+// such rows hold finite values that the masks then exclude.
 // Every wait on an mbarrier is bounded; a wait that runs out raises the block's abort flag,
 // which ends all roles, and the status word reports it.
 //
 // Formula and masking: spymaster2h/spyinfer src/backends/cpu/cpu_attention.cpp:89-135.  The
 // reference's prefill kernel (src/backends/cuda/native/attention.cu:62-255) uses no tensor
 // cores and cannot see a cached prefix.
-// Limits (checked on the host): head_dim 64 or 128, G <= 16, bfloat16.
+// Limits (checked on the host): head_dim 64 or 128, G <= 16, bfloat16, a page size of 8, 16,
+// 32, 64 or 128 tokens (a page is one TMA box and must tile the 128-key tile).
+#include <cuda.h>
+
 #include "common.cuh"
 
 SPY_MODULE(spy_attention_tc)
@@ -31,7 +39,7 @@ namespace {
 
 constexpr int ROWS = 128;          // query rows per block = UMMA M
 constexpr int TILE = 128;          // keys per tile = UMMA N of the first product
-constexpr int NUM_THREADS = 160;   // warps 0..3: loads, softmax, epilogue; warp 4: TMEM + MMA
+constexpr int NUM_THREADS = 224;   // warps 0..3: Q load, softmax, epilogue; warp 4: TMEM + MMA; warps 5, 6: TMA of K and of V
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RESCALE_THRESHOLD = 8.0f;
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
@@ -66,6 +74,19 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count)
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar)
 {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint64_t* bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+        : "memory");
 }
 
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
@@ -176,6 +197,19 @@ __device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t (&r)[32])
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ void tmem_load_32_nowait(uint32_t taddr, uint32_t (&r)[32])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+
 __device__ __forceinline__ void tmem_store_32(uint32_t taddr, const uint32_t (&r)[32])
 {
     asm volatile(
@@ -204,40 +238,50 @@ __device__ __forceinline__ uint32_t tile_offset(int row, int chunk)
 }
 
 template <int HD> struct Smem {
-    static constexpr int HALVES = HD / 64;
     static constexpr int OPERAND_BYTES = ROWS * HD * 2;       // Q, K or V tile
     static constexpr int P_BYTES = ROWS * TILE * 2;
     static constexpr int Q_OFF = 0;
     static constexpr int K_OFF = Q_OFF + OPERAND_BYTES;       // two stages
     static constexpr int V_OFF = K_OFF + 2 * OPERAND_BYTES;   // two stages
-    static constexpr int P_OFF = V_OFF + 2 * OPERAND_BYTES;
-    static constexpr int BAR_OFF = P_OFF + P_BYTES;
-    static constexpr int TOTAL = BAR_OFF + 128 + 1024;        // barriers, then slack to align the base to 1024
-    static constexpr int TMEM_COLS = 256;                     // S: 128 columns, O: HD columns
+    static constexpr int P_OFF = V_OFF + 2 * OPERAND_BYTES;   // two stages
+    static constexpr int BAR_OFF = P_OFF + 2 * P_BYTES;
+    static constexpr int TOTAL = BAR_OFF + 192 + 1024;        // barriers, then slack to align the base to 1024
+    static constexpr int TMEM_COLS = 512;                     // S0, S1: 128 columns each; O: HD columns from 256
 };
 
+// Pipeline (tile t uses stage t & 1 of K, V, S and P):
+//   softmax warps, iteration t:  wait S_t | request K_{t+2} | read S_t, max, exp (registers) |
+//                                wait P.V_{t-1} | rescale O if needed | request V_{t+1} | write P_t | signal
+//   MMA thread:                  Q.K_0, Q.K_1, then for every t:  wait P_t and V_t | P.V_t | wait K_{t+2} | Q.K_{t+2}
+// so the tensor cores work on P.V_{t-1} and Q.K_{t+1} while the softmax warps work on tile t.
 template <int HD>
-__global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const Params p)
+__global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __grid_constant__ CUtensorMap page_map, const Params p)
 {
     using L = Smem<HD>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint64_t* bar_kv = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);   // [2] tile landed (128 arrivals)
-    uint64_t* bar_s = bar_kv + 2;                                        // scores complete (MMA commit)
-    uint64_t* bar_p = bar_s + 1;                                         // probabilities written (128 arrivals)
-    uint64_t* bar_o = bar_p + 1;                                         // P.V complete (MMA commit)
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_o + 1);
+    uint64_t* bar_k = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);   // [2] K tile landed (TMA bytes)
+    uint64_t* bar_v = bar_k + 2;                                        // [2] V tile landed (TMA bytes)
+    uint64_t* bar_s = bar_v + 2;                                        // [2] scores complete (MMA commit)
+    uint64_t* bar_p = bar_s + 2;                                        // [2] probabilities written (128 arrivals)
+    uint64_t* bar_o = bar_p + 2;                                        // [2] P.V complete (MMA commit)
+    uint64_t* bar_q = bar_o + 2;                                        // Q tile written (128 arrivals)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_q + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    int* s_info = reinterpret_cast<int*>(tmem_slot + 2);                 // seq, first token of the block
+    int* s_info = reinterpret_cast<int*>(tmem_slot + 2);                // seq, first token of the block
 
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
     const int tokens_per_block = ROWS / p.Gp;
     if (tid == 0) {
-        for (int i = 0; i < 2; ++i) mbar_init(bar_kv + i, ROWS);
-        mbar_init(bar_s, 1);
-        mbar_init(bar_p, ROWS);
-        mbar_init(bar_o, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bar_k + i, 1);
+            mbar_init(bar_v + i, 1);
+            mbar_init(bar_s + i, 1);
+            mbar_init(bar_p + i, ROWS);
+            mbar_init(bar_o + i, 1);
+        }
+        mbar_init(bar_q, ROWS);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -246,6 +290,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const Para
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    // rows of pages the block table does not name are never copied: keep them finite
+    for (int i = tid; i < 4 * L::OPERAND_BYTES / 16; i += NUM_THREADS) reinterpret_cast<uint4*>(smem + L::K_OFF)[i] = make_uint4(0, 0, 0, 0);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     pdl_wait();   // everything below reads what earlier kernels wrote
     if (tid == 0) {
         int b = blockIdx.x, seq = -1, tok0 = 0;
@@ -262,7 +309,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const Para
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + TILE;
+    const uint32_t tmem_o = tmem_base + 2 * TILE;
     const int seq = s_info[0], tok0 = s_info[1];
     const int kvh = blockIdx.y;
 
@@ -278,7 +325,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const Para
     const uint32_t q_s = smem_u32(smem + L::Q_OFF), k_s = smem_u32(smem + L::K_OFF), v_s = smem_u32(smem + L::V_OFF),
                    p_s = smem_u32(smem + L::P_OFF);
 
-    if (warp < 4 && seq >= 0) {
+    if (warp < 4 && seq >= 0 && n_tiles > 0) {
         // ---------------------------------------------------------------- loads, softmax, epilogue
         const int row = tid;                                  // this thread's query row = TMEM lane
         const int tok = tok0 + row / p.Gp, hg = row % p.Gp;
@@ -286,119 +333,100 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const Para
         const int head = kvh * p.G + hg;
         const int pos = row_ok ? p.positions[tok] : -1;
         const int lo = (row_ok && p.window > 0) ? max(0, pos - p.window + 1) : 0;
-        const int* bt = p.block_table + (size_t)seq * p.table_width;
-        const size_t plane = (size_t)p.nkv * p.page_size * HD;
-
-        // Q tile: this thread's row
-        {
-            const bf16* src = p.q + (size_t)(row_ok ? tok : 0) * p.q_stride + (size_t)head * HD;
-#pragma unroll
-            for (int c = 0; c < HD / 8; ++c) cp_async16(smem + L::Q_OFF + tile_offset(row, c), src + c * 8, row_ok);
+        // the Q tile: consecutive threads copy consecutive 16-byte pieces of a row
+        constexpr int CPR = HD / 8;
+        for (int idx = tid; idx < ROWS * CPR; idx += ROWS) {
+            const int r = idx / CPR, c = idx % CPR;
+            const int r_tok = tok0 + r / p.Gp, r_hg = r % p.Gp;
+            const bool ok = r_tok < tok_end && r_hg < p.G;
+            const bf16* src = p.q + (size_t)(ok ? r_tok : 0) * p.q_stride + (size_t)(kvh * p.G + (ok ? r_hg : 0)) * HD + c * 8;
+            cp_async16(smem + L::Q_OFF + tile_offset(r, c), src, ok);
         }
-        auto load_tile = [&](int t) {                         // key row (tile_first + t) * TILE + tid of K and V into stage t % 2
-            const int j = (tile_first + t) * TILE + tid;
-            bool ok = j >= block_lo && j <= block_last_pos;
-            const bf16* src = p.pages;
-            if (ok) {
-                const int lp = j / p.page_size;
-                const int page = lp < p.table_width ? bt[lp] : -1;
-                if (page < 0 || page >= p.num_pages) {
-                    report_status(p.status, SPY_STATUS_BAD_PAGE, tok0);
-                    ok = false;
-                } else {
-                    src = p.pages + (((size_t)page * 2) * p.nkv + kvh) * p.page_size * HD + (size_t)(j - lp * p.page_size) * HD;
-                }
-            }
-            uint8_t* kd = smem + L::K_OFF + (t & 1) * L::OPERAND_BYTES;
-            uint8_t* vd = smem + L::V_OFF + (t & 1) * L::OPERAND_BYTES;
-#pragma unroll
-            for (int c = 0; c < HD / 8; ++c) {
-                cp_async16(kd + tile_offset(tid, c), src + c * 8, ok);
-                cp_async16(vd + tile_offset(tid, c), src + plane + c * 8, ok);
-            }
-        };
-        if (n_tiles > 0) load_tile(0);
         asm volatile("cp.async.wait_all;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the MMA reads shared memory through the async proxy
-        mbar_arrive(bar_kv + 0);
+        mbar_arrive(bar_q);
 
         float m_used = -INFINITY, l = 0.f;   // the maximum the probabilities are taken against, and their sum
         const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
         bool alive = true;
-        for (int t = 0; t < n_tiles && alive; ++t) {
-            if (t > 0) alive = mbar_wait(bar_o, (t - 1) & 1, abort_flag);   // P.V of tile t-1 done: O, P and stage (t+1)%2 are free
-            if (!alive) break;
-            if (t + 1 < n_tiles) load_tile(t + 1);
-            alive = mbar_wait(bar_s, t & 1, abort_flag);
+        for (int t = 0; t < n_tiles; ++t) {
+            const int st = t & 1;
+            const uint32_t ph = (uint32_t)(t >> 1) & 1;
+            alive = mbar_wait(bar_s + st, ph, abort_flag);          // S_t is complete
             if (!alive) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int key0 = (tile_first + t) * TILE;
-            // pass 1: the row's maximum over the tile
-            float mx = -INFINITY;
-#pragma unroll 1
+            // the row's 128 scores, scaled (and masked where the tile is not visible whole to every row of the warp)
+            float sc[TILE];
+#pragma unroll
             for (int c = 0; c < TILE; c += 32) {
                 uint32_t r[32];
-                tmem_load_32(tmem_s + lane_addr + c, r);
+                tmem_load_32_nowait(tmem_base + st * TILE + lane_addr + c, r);
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int j = key0 + c + i;
-                    const float v = (j <= pos && j >= lo) ? __uint_as_float(r[i]) * p.scale_log2 : -INFINITY;
-                    mx = fmaxf(mx, v);
+                for (int i = 0; i < 32; ++i) sc[c + i] = __uint_as_float(r[i]);
+            }
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            const bool whole = __all_sync(0xffffffffu, !row_ok || (key0 >= lo && key0 + TILE - 1 <= pos));
+            float mx = -INFINITY;
+            if (whole) {
+#pragma unroll
+                for (int i = 0; i < TILE; ++i) {
+                    sc[i] *= p.scale_log2;
+                    mx = fmaxf(mx, sc[i]);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < TILE; ++i) {
+                    const int j = key0 + i;
+                    sc[i] = (j <= pos && j >= lo) ? sc[i] * p.scale_log2 : -INFINITY;
+                    mx = fmaxf(mx, sc[i]);
                 }
             }
-            // rescale O only when the maximum grew by more than the threshold (or from nothing)
+            // the maximum in use moves only when the row's maximum grew by more than the threshold (or from nothing)
             const float m_new = fmaxf(m_used, mx);
             const bool grow = m_new > m_used + RESCALE_THRESHOLD || (m_used == -INFINITY && m_new != -INFINITY);
-            if (__any_sync(0xffffffffu, grow)) {
-                const float alpha = grow ? (m_used == -INFINITY ? 0.f : fast_exp2(m_used - m_new)) : 1.f;
-                if (t > 0) {
-#pragma unroll 1
-                    for (int c = 0; c < HD; c += 32) {
-                        uint32_t r[32];
-                        tmem_load_32(tmem_o + lane_addr + c, r);
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-                        tmem_store_32(tmem_o + lane_addr + c, r);
-                    }
-                }
-                if (grow) {
-                    l *= alpha;
-                    m_used = m_new;
-                }
+            const float alpha = grow ? (m_used == -INFINITY ? 0.f : fast_exp2(m_used - m_new)) : 1.f;
+            if (grow) {
+                l *= alpha;
+                m_used = m_new;
             }
             const float m_sub = m_used == -INFINITY ? 0.f : m_used;
-            // pass 2: probabilities to shared memory as bfloat16 (A operand of P.V, K-major over the keys)
-#pragma unroll 1
-            for (int c = 0; c < TILE; c += 32) {
-                uint32_t r[32];
-                tmem_load_32(tmem_s + lane_addr + c, r);
-                uint32_t packed[16];
+            uint32_t packed[TILE / 2];
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const int j = key0 + c + i;
-                    const float s0 = (j <= pos && j >= lo) ? __uint_as_float(r[i]) * p.scale_log2 : -INFINITY;
-                    const float s1 = (j + 1 <= pos && j + 1 >= lo) ? __uint_as_float(r[i + 1]) * p.scale_log2 : -INFINITY;
-                    const float p0 = fast_exp2(s0 - m_sub), p1 = fast_exp2(s1 - m_sub);
-                    l += p0 + p1;
-                    packed[i / 2] = pack_bf16(p0, p1);
-                }
-#pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4)
-                    *reinterpret_cast<uint4*>(smem + L::P_OFF + tile_offset(row, c / 8 + q4)) =
-                        make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
+            for (int i = 0; i < TILE; i += 2) {
+                const float p0 = fast_exp2(sc[i] - m_sub), p1 = fast_exp2(sc[i + 1] - m_sub);
+                l += p0 + p1;
+                packed[i / 2] = pack_bf16(p0, p1);
             }
+            // P.V of tile t-1 must be complete before O is rescaled and (two tiles back, implied)
+            // before P's stage st is rewritten
+            if (t > 0) {
+                alive = mbar_wait(bar_o + ((t - 1) & 1), (uint32_t)((t - 1) >> 1) & 1, abort_flag);
+                if (!alive) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            }
+            if (t > 0 && __any_sync(0xffffffffu, grow)) {
+#pragma unroll 1
+                for (int c = 0; c < HD; c += 32) {
+                    uint32_t r[32];
+                    tmem_load_32(tmem_o + lane_addr + c, r);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                    tmem_store_32(tmem_o + lane_addr + c, r);
+                }
+            }
+            uint8_t* pdst = smem + L::P_OFF + st * L::P_BYTES;
+#pragma unroll
+            for (int c8 = 0; c8 < TILE / 8; ++c8)
+                *reinterpret_cast<uint4*>(pdst + tile_offset(row, c8)) =
+                    make_uint4(packed[4 * c8], packed[4 * c8 + 1], packed[4 * c8 + 2], packed[4 * c8 + 3]);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(bar_p);
-            if (t + 1 < n_tiles) {
-                asm volatile("cp.async.wait_all;" ::: "memory");
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                mbar_arrive(bar_kv + ((t + 1) & 1));
-            }
+            mbar_arrive(bar_p + st);
         }
         // ---- epilogue: O / l
-        if (alive && n_tiles > 0) alive = mbar_wait(bar_o, (n_tiles - 1) & 1, abort_flag);
-        if (alive && n_tiles > 0) {
+        if (alive) alive = mbar_wait(bar_o + ((n_tiles - 1) & 1), (uint32_t)((n_tiles - 1) >> 1) & 1, abort_flag);
+        if (alive) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const float inv = l > 0.f ? 1.f / l : 0.f;
             bf16* dst = p.out + ((size_t)(row_ok ? tok : 0) * p.nh + head) * HD;
@@ -419,7 +447,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const Para
                 }
             }
         }
-    } else if (warp == 4 && seq >= 0) {
+    } else if (warp == 4 && seq >= 0 && n_tiles > 0) {
         // ---------------------------------------------------------------- MMA issue
         if (lane == 0) {
             const uint32_t idesc_qk = instr_desc(TILE, false), idesc_pv = instr_desc(HD, true);
@@ -428,34 +456,89 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const Para
 #pragma unroll
                 for (int s = 0; s < HD / 16; ++s) {
                     const uint32_t off = (s >> 2) * (ROWS * 128) + (s & 3) * 32;   // 64-element half, then 32 bytes per 16 elements
-                    umma(tmem_s, desc_k_major(q_s + off), desc_k_major(kb + off), idesc_qk, s > 0 ? 1u : 0u);
+                    umma(tmem_base + (t & 1) * TILE, desc_k_major(q_s + off), desc_k_major(kb + off), idesc_qk, s > 0 ? 1u : 0u);
                 }
-                umma_commit(bar_s);
+                umma_commit(bar_s + (t & 1));
             };
-            bool ok = n_tiles > 0 && mbar_wait(bar_kv + 0, 0, abort_flag);
+            bool ok = mbar_wait(bar_q, 0, abort_flag) && mbar_wait(bar_k + 0, 0, abort_flag);
             if (ok) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 issue_qk(0);
             }
+            if (ok && n_tiles > 1) {
+                ok = mbar_wait(bar_k + 1, 0, abort_flag);
+                if (ok) {
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    issue_qk(1);
+                }
+            }
             for (int t = 0; t < n_tiles && ok; ++t) {
-                ok = mbar_wait(bar_p, t & 1, abort_flag);
+                const int st = t & 1;
+                const uint32_t ph = (uint32_t)(t >> 1) & 1;
+                ok = mbar_wait(bar_p + st, ph, abort_flag) && mbar_wait(bar_v + st, ph, abort_flag);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t vb = v_s + (t & 1) * L::OPERAND_BYTES;
+                const uint32_t vb = v_s + st * L::OPERAND_BYTES, pb = p_s + st * L::P_BYTES;
 #pragma unroll
                 for (int s = 0; s < TILE / 16; ++s) {
                     const uint32_t a_off = (s >> 2) * (ROWS * 128) + (s & 3) * 32;   // P: 16 keys = 32 bytes along its rows
                     const uint32_t b_off = s * 16 * 128;                             // V: 16 key rows of 128 bytes
-                    umma(tmem_o, desc_k_major(p_s + a_off), desc_mn_major(vb + b_off, ROWS * 128), idesc_pv, (t > 0 || s > 0) ? 1u : 0u);
+                    umma(tmem_o, desc_k_major(pb + a_off), desc_mn_major(vb + b_off, ROWS * 128), idesc_pv, (t > 0 || s > 0) ? 1u : 0u);
                 }
-                umma_commit(bar_o);
-                if (t + 1 < n_tiles) {
-                    ok = mbar_wait(bar_kv + ((t + 1) & 1), ((t + 1) >> 1) & 1, abort_flag);
+                umma_commit(bar_o + st);
+                if (t + 2 < n_tiles) {
+                    ok = mbar_wait(bar_k + st, (uint32_t)((t + 2) >> 1) & 1, abort_flag);   // S's stage st is free: P_t was read from it
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    issue_qk(t + 1);
+                    issue_qk(t + 2);
                 }
             }
+        }
+    }
+
+    else if (warp >= 5 && seq >= 0 && n_tiles > 0) {
+        // ---------------------------------------------------------------- TMA of K (warp 5) and V (warp 6) tiles
+        // One box per page and 64-column half; the lanes of the warp issue the boxes of a tile side
+        // by side (a single thread issuing them one after the other is the slower way: small boxes
+        // are bound by issue latency, not by bandwidth).
+        const int kv = warp - 5;
+        const int* bt = p.block_table + (size_t)seq * p.table_width;
+        const int pages_per_tile = TILE / p.page_size;
+        const int boxes = pages_per_tile * (HD / 64);
+        const uint32_t box_bytes = (uint32_t)p.page_size * 128;              // page_size rows of 64 elements
+        bool ok = true;
+        for (int t = 0; t < n_tiles; ++t) {
+            const int st = t & 1;
+            const int first_lp = (tile_first + t) * pages_per_tile;
+            uint64_t* bar = (kv == 0 ? bar_k : bar_v) + st;
+            if (lane == 0) {
+                // K's stage is free when Q.K of tile t-2 is complete, V's when P.V of tile t-2 is
+                if (t >= 2) ok = mbar_wait((kv == 0 ? bar_s : bar_o) + st, (uint32_t)((t - 2) >> 1) & 1, abort_flag);
+                if (ok) {
+                    int valid = 0;   // pages of this tile that the block table names and that hold keys some row can see
+                    for (int i = 0; i < pages_per_tile; ++i) {
+                        const int lp = first_lp + i;
+                        const int page = lp < p.table_width ? bt[lp] : -1;
+                        const bool in_range = lp * p.page_size <= block_last_pos && (lp + 1) * p.page_size > block_lo;
+                        if (in_range && (page < 0 || page >= p.num_pages)) report_status(p.status, SPY_STATUS_BAD_PAGE, tok0);
+                        if (in_range && page >= 0 && page < p.num_pages) ++valid;
+                    }
+                    mbar_expect_tx(bar, (uint32_t)valid * box_bytes * (HD / 64));
+                }
+            }
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            if (!ok) break;
+            const uint32_t stage = (kv == 0 ? k_s : v_s) + st * L::OPERAND_BYTES;
+            for (int b = lane; b < boxes; b += 32) {
+                const int i = b / (HD / 64), h = b % (HD / 64);
+                const int lp = first_lp + i;
+                const int page = lp < p.table_width ? bt[lp] : -1;
+                const bool in_range = lp * p.page_size <= block_last_pos && (lp + 1) * p.page_size > block_lo;
+                if (!in_range || page < 0 || page >= p.num_pages) continue;
+                const int y = ((page * 2 + kv) * p.nkv + kvh) * p.page_size;
+                tma_load_2d(stage + h * (ROWS * 128) + i * p.page_size * 128, &page_map, h * 64, y, bar);
+            }
+            __syncwarp();
         }
     }
 
@@ -474,6 +557,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const Para
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)L::TMEM_COLS) : "memory");
     }
 }
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 }  // namespace
 
@@ -498,6 +585,28 @@ extern "C" int spy_attention_tc(const void* q, long long q_row_stride, void* out
     p.q = (const bf16*)q; p.q_stride = q_row_stride; p.out = (bf16*)out; p.pages = (const bf16*)pages; p.block_table = block_table;
     p.positions = positions; p.q_start = q_start; p.status = status; p.table_width = table_width; p.page_size = page_size;
     p.num_pages = num_pages; p.nh = nh; p.nkv = nkv; p.G = G; p.Gp = Gp; p.S = seqs; p.window = window; p.scale_log2 = scale * LOG2E;
+    if (page_size < 8 || page_size > TILE || TILE % page_size != 0)
+        SPY_FAIL("attention_tc: page_size %d must be 8, 16, 32, 64 or 128 (one TMA box per page)", page_size);
+    // the pages of this cache as one matrix [num_pages * 2 * nkv * page_size rows, hd]; a box is one page's rows x 64 columns
+    static EncodeTiledFn encode = nullptr;
+    if (encode == nullptr) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qr) != cudaSuccess || qr != cudaDriverEntryPointSuccess)
+            SPY_FAIL("attention_tc: cuTensorMapEncodeTiled is not available from the driver");
+        encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    CUtensorMap page_map;
+    {
+        cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)num_pages * 2 * nkv * page_size};
+        cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
+        cuuint32_t box[2] = {64, (cuuint32_t)page_size};
+        cuuint32_t elem[2] = {1, 1};
+        CUresult r = encode(&page_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pages), dims, strides, box, elem,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) SPY_FAIL("attention_tc: cuTensorMapEncodeTiled failed with code %d", (int)r);
+    }
     const int tokens_per_block = ROWS / Gp;
     const long long blocks = (tokens + tokens_per_block - 1) / tokens_per_block + seqs;   // an upper bound without a host copy of q_start
     if (blocks > 0x7fffffffLL || nkv > 65535) SPY_FAIL("attention_tc: the batch exceeds the grid limits");
@@ -508,8 +617,8 @@ extern "C" int spy_attention_tc(const void* q, long long q_row_stride, void* out
         SPY_CUDA(cudaFuncSetAttribute(attention_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<128>::TOTAL));
         configured = true;
     }
-    if (hd == 64) spy_launch(attention_tc_kernel<64>, grid, dim3(NUM_THREADS), (size_t)Smem<64>::TOTAL, stream, p);
-    else spy_launch(attention_tc_kernel<128>, grid, dim3(NUM_THREADS), (size_t)Smem<128>::TOTAL, stream, p);
+    if (hd == 64) spy_launch(attention_tc_kernel<64>, grid, dim3(NUM_THREADS), (size_t)Smem<64>::TOTAL, stream, page_map, p);
+    else spy_launch(attention_tc_kernel<128>, grid, dim3(NUM_THREADS), (size_t)Smem<128>::TOTAL, stream, page_map, p);
     SPY_CHECK_LAUNCH("attention_tc");
     return 0;
 }

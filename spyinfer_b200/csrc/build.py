@@ -71,9 +71,14 @@ def _build_dir() -> str:
     return _build_dir_cached
 
 
+def _extra_flags() -> List[str]:
+    """More nvcc flags from the environment (``SPYINFER_NVCC_FLAGS``), e.g. ``-DNAME`` switches for experiments."""
+    return os.environ.get("SPYINFER_NVCC_FLAGS", "").split()
+
+
 def _source_hash(module: str) -> str:
     h = hashlib.sha256()
-    h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS).encode())
+    h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS + _extra_flags()).encode())
     for name in sorted(os.listdir(HERE)):
         if name.endswith(".cuh") or name.endswith(".h") or name == module + ".cu":
             with open(os.path.join(HERE, name), "rb") as f:
@@ -101,7 +106,7 @@ def _compile(module: str) -> None:
         raise KernelBuildError(f"no kernel module {module!r} ({src} does not exist)")
     so = library_path(module)
     tmp = f"{so}.{os.getpid()}.tmp"
-    cmd = [_nvcc()] + ARCH_FLAGS + NVCC_FLAGS + ["-I", HERE, "-o", tmp, src]
+    cmd = [_nvcc()] + ARCH_FLAGS + NVCC_FLAGS + _extra_flags() + ["-I", HERE, "-o", tmp, src]
     env = dict(os.environ)
     env.setdefault("TMPDIR", tempfile.gettempdir())
     t0 = time.time()

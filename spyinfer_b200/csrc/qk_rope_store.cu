@@ -120,6 +120,79 @@ __global__ void qk_rope_store_kernel(const TS* src, int src_splits, long long sr
     }
 }
 
+// The common case in one pass over registers: bfloat16 everywhere, head_dim 128, the whole head
+// rotated (or no rotation), one plain input array.  Lane l of the warp that owns a (token, head)
+// holds elements 4l .. 4l + 3 (one 8-byte access); the rotation partner of element j < 64 is
+// element j + 64, which lane l ^ 16 holds, so a shuffle replaces the staging in shared memory.
+template <typename TW>
+__global__ void __launch_bounds__(256) qk_rope_store_hd128_kernel(const bf16* src, bf16* q_out, long long q_out_stride, int tokens, int nh, int nkv,
+                                                                  const TW* __restrict__ q_w, const TW* __restrict__ k_w, float eps,
+                                                                  const float2* __restrict__ cos_sin, int table_rows,
+                                                                  const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                                                                  const int* __restrict__ block_table, int table_width, bf16* pages,
+                                                                  int page_size, int num_pages, int store, int* status)
+{
+    constexpr int HD = 128;
+    pdl_enter();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int heads = store ? nh + 2 * nkv : nh;
+    const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
+    if (item >= (long long)tokens * heads) return;
+    const int t = (int)(item / heads), head = (int)(item % heads);
+    const int kind = head < nh ? 0 : (head < nh + nkv ? 1 : 2);  // q, k, v
+    const bf16* in = src + (size_t)t * (nh + 2 * nkv) * HD + (size_t)head * HD + 4 * lane;
+    const int pos = positions[t];
+    bf16* dst;
+    if (kind == 0) {
+        dst = q_out + (size_t)t * q_out_stride + (size_t)head * HD + 4 * lane;
+    } else {
+        const int seq = seq_of_token[t];
+        const bool in_table = pos >= 0 && pos / page_size < table_width;
+        const int page = in_table ? block_table[(size_t)seq * table_width + pos / page_size] : -1;
+        if (page < 0 || page >= num_pages) {
+            if (lane == 0) report_status(status, SPY_STATUS_BAD_PAGE, t);
+            return;
+        }
+        const int kv_head = kind == 1 ? head - nh : head - nh - nkv;
+        dst = pages + ((((size_t)page * 2 + (kind - 1)) * nkv + kv_head) * page_size + pos % page_size) * HD + 4 * lane;
+    }
+    const uint2 raw = *reinterpret_cast<const uint2*>(in);
+    if (kind == 2) {
+        *reinterpret_cast<uint2*>(dst) = raw;
+        return;
+    }
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+    float v[4] = {__low2float(a), __high2float(a), __low2float(b), __high2float(b)};
+    const TW* w = kind == 0 ? q_w : k_w;
+    if (w != nullptr) {
+        float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)HD + eps);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[i] = (inv * v[i]) * to_f32(w[4 * lane + i]);
+    }
+    if (cos_sin != nullptr) {
+        if (pos < 0 || pos >= table_rows) {
+            if (lane == 0) report_status(status, SPY_STATUS_BAD_POSITION, t);
+            return;
+        }
+        const float4* cs4 = reinterpret_cast<const float4*>(cos_sin + (size_t)pos * 64 + 4 * (lane & 15));
+        const float4 c01 = cs4[0], c23 = cs4[1];   // (cos, sin) of pairs j, j+1 and j+2, j+3
+        const float cs_c[4] = {c01.x, c01.z, c23.x, c23.z}, cs_s[4] = {c01.y, c01.w, c23.y, c23.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float other = __shfl_xor_sync(0xffffffffu, v[i], 16);
+            // lanes 0..15 hold the low half (x_j), lanes 16..31 the high half (x_{j + 64})
+            v[i] = lane < 16 ? v[i] * cs_c[i] - other * cs_s[i] : other * cs_s[i] + v[i] * cs_c[i];
+        }
+    }
+    __nv_bfloat162 o0 = __floats2bfloat162_rn(v[0], v[1]), o1 = __floats2bfloat162_rn(v[2], v[3]);
+    uint2 outv;
+    outv.x = *reinterpret_cast<uint32_t*>(&o0);
+    outv.y = *reinterpret_cast<uint32_t*>(&o1);
+    *reinterpret_cast<uint2*>(dst) = outv;
+}
+
 template <typename TS, typename TQ, typename TC, typename TW>
 static int launch(const void* src, int src_splits, long long src_split_stride, void* q_out, long long q_out_stride, int tokens, int nh, int nkv,
                   int hd, const void* q_w, const void* k_w, float eps, const float* cos_sin, int rot_half, int table_rows, const int* positions,
@@ -159,6 +232,21 @@ extern "C" int spy_qk_rope_store(const void* src, int src_dtype, int src_splits,
     if (cos_sin && (rot_half <= 0 || 2 * rot_half > hd)) SPY_FAIL("qk_rope_store: rotary width %d does not fit head_dim %d", 2 * rot_half, hd);
     if (store && (page_size <= 0 || num_pages <= 0 || table_width <= 0 || !pages || !block_table))
         SPY_FAIL("qk_rope_store: storing needs pages, a block table and positive page_size/num_pages/table_width");
+    if (src_dtype == SPY_BF16 && q_dtype == SPY_BF16 && (!store || cache_dtype == SPY_BF16) && src_splits == 1 && hd == 128 &&
+        (cos_sin == nullptr || rot_half == 64) && q_out_stride % 4 == 0 &&
+        ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(pages)) & 7) == 0) {
+        const int heads = store ? nh + 2 * nkv : nh;
+        const long long items = (long long)tokens * heads;
+        const long long blocks = (items + 7) / 8;
+        if (blocks > 0x7fffffffLL) SPY_FAIL("qk_rope_store: %lld work items exceed the grid limit", items);
+        SPY_DISPATCH_DTYPE(w_dtype, TW, {
+            spy_launch(qk_rope_store_hd128_kernel<TW>, dim3((int)blocks), dim3(256), 0, stream, (const bf16*)src, (bf16*)q_out, q_out_stride,
+                       tokens, nh, nkv, (const TW*)q_w, (const TW*)k_w, eps, (const float2*)cos_sin, table_rows, positions, seq_of_token,
+                       block_table, table_width, (bf16*)pages, page_size, num_pages, store, status);
+        })
+        SPY_CHECK_LAUNCH("qk_rope_store (head_dim 128)");
+        return 0;
+    }
     SPY_DISPATCH_DTYPE(src_dtype, TS, {
         SPY_DISPATCH_DTYPE(q_dtype, TQ, {
             SPY_DISPATCH_DTYPE(cache_dtype, TC, {

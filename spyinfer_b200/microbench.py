@@ -87,6 +87,7 @@ def main(argv=None) -> int:
     a.add_argument("--q-len", type=int, default=1)
     a.add_argument("--split-keys", type=int, default=0, help="0: tiles mode; else split mode with this range length")
     a.add_argument("--iters", type=int, default=10)
+    a.add_argument("--page-size", type=int, default=16)
     a.add_argument("--kernel", default="auto", choices=["auto", "tc", "mma"], help="auto: tcgen05 for tiles mode, mma.sync for split mode")
     args = ap.parse_args(argv)
     kernels.require_cuda()
@@ -94,7 +95,7 @@ def main(argv=None) -> int:
         r = bench_gemm(args.m, args.n, args.k, getattr(torch, args.out_dtype), args.iters)
         print(f"gemm M={args.m} N={args.n} K={args.k}: {r['us']:.1f} us, {r['tflops']:.1f} TFLOP/s, {r['gbs']:.1f} GB/s")
     else:
-        r = bench_attention(args.batch, args.context, args.q_len, args.split_keys, iters=args.iters, kernel=args.kernel)
+        r = bench_attention(args.batch, args.context, args.q_len, args.split_keys, page_size=args.page_size, iters=args.iters, kernel=args.kernel)
         print(f"attention batch={args.batch} context={args.context} q_len={args.q_len} split_keys={args.split_keys}: {r['us']:.1f} us, "
               f"cache read at {r['kv_gbs']:.1f} GB/s, {r['tflops']:.1f} TFLOP/s")
     return 0

@@ -103,8 +103,11 @@ class Attention(Mixer):
             kernels.attention_mma(q, self.nh, self.hd, out, cache.pages, cache.block_table, batch.positions, batch.q_start,
                                   batch.num_seqs, self.scale, window=self.window, split_keys=self.split_keys,
                                   max_splits=self.max_splits, status=batch.status)
-        else:
-            # prompt portions (and whatever decodes beside them): 128-row blocks on tcgen05
+        elif cache.page_size in (8, 16, 32, 64, 128):
+            # prompt portions (and whatever decodes beside them): 128-row blocks on tcgen05, pages brought in by TMA
             kernels.attention_tc(q, self.nh, self.hd, out, cache.pages, cache.block_table, batch.positions, batch.q_start,
                                  batch.num_seqs, self.scale, window=self.window, status=batch.status)
+        else:
+            kernels.attention_mma(q, self.nh, self.hd, out, cache.pages, cache.block_table, batch.positions, batch.q_start,
+                                  batch.num_seqs, self.scale, window=self.window, status=batch.status)
         return self.o(out, defer=True)

@@ -173,7 +173,7 @@ def test_attention_generic_finds_one_far_key():
 
 @pytest.mark.parametrize("adtype,cdtype,wdtype", [(torch.float32, torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16, torch.bfloat16),
                                                   (torch.float32, torch.float32, torch.bfloat16)])
-@pytest.mark.parametrize("nh,nkv,hd,rot,page_size", [(4, 2, 16, 16, 4), (3, 3, 48, 32, 8), (8, 2, 128, 128, 16), (2, 1, 80, 80, 5)])
+@pytest.mark.parametrize("nh,nkv,hd,rot,page_size", [(4, 2, 16, 16, 4), (3, 3, 48, 32, 8), (8, 2, 128, 128, 16), (2, 1, 80, 80, 5), (5, 1, 128, 64, 16)])
 def test_qk_norm_rope_store(adtype, cdtype, wdtype, nh, nkv, hd, rot, page_size):
     from spyinfer_b200 import kernels
     torch.manual_seed(nh * hd)
@@ -452,7 +452,7 @@ def test_qk_rope_store_sums_a_stack_of_partial_products():
 
 
 @pytest.mark.parametrize("nh,nkv,hd,page_size,window", [(8, 2, 128, 16, None), (10, 2, 64, 16, 150), (4, 4, 128, 8, None), (16, 1, 64, 32, None),
-                                                        (6, 2, 128, 5, 33), (32, 8, 128, 16, None)])
+                                                        (6, 2, 128, 64, 33), (32, 8, 128, 16, None), (2, 1, 64, 128, None)])
 def test_attention_tc_mixed_batch(nh, nkv, hd, page_size, window):
     """tcgen05 attention: portions, single tokens, a one-token sequence and a 300-token portion
     (several 128-row blocks and several key tiles) in one batch; group sizes 1, 3, 4, 5, 16."""
@@ -478,6 +478,15 @@ def test_attention_tc_mixed_batch(nh, nkv, hd, page_size, window):
                 continue
         ref = ref_attention(q[i, :nh * hd].view(nh, hd), ks[s], vs[s], p, scale, window)
         torch.testing.assert_close(out[i].view(nh, hd).double(), ref, rtol=2e-2, atol=2e-2)
+
+
+def test_attention_tc_refuses_pages_that_are_no_tma_box():
+    from spyinfer_b200 import kernels
+    pages, bt, ks, vs = paged_setup(1, [20], 1, 64, 5, torch.bfloat16)
+    q = torch.zeros(1, 4 * 64, device=DEV, dtype=torch.bfloat16)
+    with pytest.raises(kernels.KernelError):
+        kernels.attention_tc(q, 4, 64, torch.empty_like(q), pages, bt, torch.tensor([19], dtype=torch.int32, device=DEV),
+                             torch.tensor([0, 1], dtype=torch.int32, device=DEV), 1, 1.0)
 
 
 def test_attention_tc_finds_one_far_key_and_survives_large_scores():
