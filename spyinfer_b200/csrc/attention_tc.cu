@@ -53,7 +53,9 @@ struct Params {
     const int* positions;      // [T]
     const int* q_start;        // [S + 1]
     int* status;
-    int table_width, page_size, num_pages, nh, nkv, G, Gp, S, window;
+    float* part_o;             // split mode: [T][nh][max_splits][HD] unnormalised partial outputs
+    float* part_ml;            //             [T][nh][max_splits][2]  (maximum in the log2 domain, sum)
+    int table_width, page_size, num_pages, nh, nkv, G, Gp, S, window, split_keys, max_splits;
     float scale_log2;
 };
 
@@ -254,7 +256,11 @@ template <int HD> struct Smem {
 //                                wait P.V_{t-1} | rescale O if needed | request V_{t+1} | write P_t | signal
 //   MMA thread:                  Q.K_0, Q.K_1, then for every t:  wait P_t and V_t | P.V_t | wait K_{t+2} | Q.K_{t+2}
 // so the tensor cores work on P.V_{t-1} and Q.K_{t+1} while the softmax warps work on tile t.
-template <int HD>
+// SPLIT (decoding: every sequence brings one token): grid (sequence, kv head, split); the block
+// takes the keys of split z only, its rows are the G heads of the one token (the first warp
+// alone does the softmax), and when the token's keys span several splits the unnormalised
+// output with its maximum and sum goes to scratch for attention_tc_merge_kernel.
+template <int HD, bool SPLIT>
 __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __grid_constant__ CUtensorMap page_map, const Params p)
 {
     using L = Smem<HD>;
@@ -272,13 +278,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
 
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
-    const int tokens_per_block = ROWS / p.Gp;
+    const int tokens_per_block = SPLIT ? 1 : ROWS / p.Gp;
+    constexpr int SOFTMAX_WARPS = SPLIT ? 1 : 4;
     if (tid == 0) {
         for (int i = 0; i < 2; ++i) {
             mbar_init(bar_k + i, 1);
             mbar_init(bar_v + i, 1);
             mbar_init(bar_s + i, 1);
-            mbar_init(bar_p + i, ROWS);
+            mbar_init(bar_p + i, SOFTMAX_WARPS * 32);
             mbar_init(bar_o + i, 1);
         }
         mbar_init(bar_q, ROWS);
@@ -296,11 +303,16 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
     pdl_wait();   // everything below reads what earlier kernels wrote
     if (tid == 0) {
         int b = blockIdx.x, seq = -1, tok0 = 0;
-        for (int s = 0; s < p.S; ++s) {
-            const int n = p.q_start[s + 1] - p.q_start[s];
-            const int blocks = (n + tokens_per_block - 1) / tokens_per_block;
-            if (b < blocks) { seq = s; tok0 = p.q_start[s] + b * tokens_per_block; break; }
-            b -= blocks;
+        if constexpr (SPLIT) {
+            seq = b;
+            tok0 = p.q_start[b];
+        } else {
+            for (int s = 0; s < p.S; ++s) {
+                const int n = p.q_start[s + 1] - p.q_start[s];
+                const int blocks = (n + tokens_per_block - 1) / tokens_per_block;
+                if (b < blocks) { seq = s; tok0 = p.q_start[s] + b * tokens_per_block; break; }
+                b -= blocks;
+            }
         }
         s_info[0] = seq;
         s_info[1] = tok0;
@@ -314,13 +326,23 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
     const int kvh = blockIdx.y;
 
     int n_tiles = 0, tile_first = 0, block_lo = 0, block_last_pos = -1, tok_end = 0;
+    int z_first = 0, z_last = 0;
     if (seq >= 0) {
-        tok_end = p.q_start[seq + 1];
+        tok_end = SPLIT ? tok0 + 1 : p.q_start[seq + 1];
         const int first_pos = p.positions[tok0];
         block_last_pos = p.positions[min(tok_end, tok0 + tokens_per_block) - 1];
         block_lo = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
-        tile_first = block_lo / TILE;
-        n_tiles = block_last_pos / TILE - tile_first + 1;
+        if constexpr (SPLIT) {
+            z_first = block_lo / p.split_keys;
+            z_last = block_last_pos / p.split_keys;
+            const int z = blockIdx.z;
+            block_lo = max(block_lo, z * p.split_keys);
+            block_last_pos = min(block_last_pos, (z + 1) * p.split_keys - 1);
+        }
+        if (block_lo <= block_last_pos) {
+            tile_first = block_lo / TILE;
+            n_tiles = block_last_pos / TILE - tile_first + 1;
+        }
     }
     const uint32_t q_s = smem_u32(smem + L::Q_OFF), k_s = smem_u32(smem + L::K_OFF), v_s = smem_u32(smem + L::V_OFF),
                    p_s = smem_u32(smem + L::P_OFF);
@@ -331,8 +353,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
         const int tok = tok0 + row / p.Gp, hg = row % p.Gp;
         const bool row_ok = tok < tok_end && hg < p.G;
         const int head = kvh * p.G + hg;
-        const int pos = row_ok ? p.positions[tok] : -1;
-        const int lo = (row_ok && p.window > 0) ? max(0, pos - p.window + 1) : 0;
+        // the keys this row sees, within the block's range (a split's range when decoding)
+        const int pos = row_ok ? min(p.positions[tok], block_last_pos) : -1;
+        const int lo = max((row_ok && p.window > 0) ? max(0, p.positions[tok] - p.window + 1) : 0, block_lo);
         // the Q tile: consecutive threads copy consecutive 16-byte pieces of a row
         constexpr int CPR = HD / 8;
         for (int idx = tid; idx < ROWS * CPR; idx += ROWS) {
@@ -349,7 +372,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
         float m_used = -INFINITY, l = 0.f;   // the maximum the probabilities are taken against, and their sum
         const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
         bool alive = true;
-        for (int t = 0; t < n_tiles; ++t) {
+        for (int t = 0; t < n_tiles && warp < SOFTMAX_WARPS; ++t) {
             const int st = t & 1;
             const uint32_t ph = (uint32_t)(t >> 1) & 1;
             alive = mbar_wait(bar_s + st, ph, abort_flag);          // S_t is complete
@@ -424,26 +447,41 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(bar_p + st);
         }
-        // ---- epilogue: O / l
-        if (alive) alive = mbar_wait(bar_o + ((n_tiles - 1) & 1), (uint32_t)((n_tiles - 1) >> 1) & 1, abort_flag);
-        if (alive) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const float inv = l > 0.f ? 1.f / l : 0.f;
-            bf16* dst = p.out + ((size_t)(row_ok ? tok : 0) * p.nh + head) * HD;
+        // ---- epilogue: O / l, or the partial result of this split
+        if (warp < SOFTMAX_WARPS) {
+            if (alive) alive = mbar_wait(bar_o + ((n_tiles - 1) & 1), (uint32_t)((n_tiles - 1) >> 1) & 1, abort_flag);
+            if (alive) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const bool direct = !SPLIT || z_first == z_last;
+                const float inv = direct ? (l > 0.f ? 1.f / l : 0.f) : 1.f;
+                bf16* dst = p.out + ((size_t)(row_ok ? tok : 0) * p.nh + head) * HD;
+                const size_t slot = SPLIT ? ((size_t)(row_ok ? tok : 0) * p.nh + head) * p.max_splits + blockIdx.z : 0;
 #pragma unroll 1
-            for (int c = 0; c < HD; c += 32) {
-                uint32_t r[32];
-                tmem_load_32(tmem_o + lane_addr + c, r);
-                if (row_ok) {
+                for (int c = 0; c < HD; c += 32) {
+                    uint32_t r[32];
+                    tmem_load_32(tmem_o + lane_addr + c, r);
+                    if (!row_ok) continue;
+                    if (direct) {
 #pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4) {
-                        uint4 v;
-                        v.x = pack_bf16(__uint_as_float(r[8 * q4]) * inv, __uint_as_float(r[8 * q4 + 1]) * inv);
-                        v.y = pack_bf16(__uint_as_float(r[8 * q4 + 2]) * inv, __uint_as_float(r[8 * q4 + 3]) * inv);
-                        v.z = pack_bf16(__uint_as_float(r[8 * q4 + 4]) * inv, __uint_as_float(r[8 * q4 + 5]) * inv);
-                        v.w = pack_bf16(__uint_as_float(r[8 * q4 + 6]) * inv, __uint_as_float(r[8 * q4 + 7]) * inv);
-                        *reinterpret_cast<uint4*>(dst + c + 8 * q4) = v;
+                        for (int q4 = 0; q4 < 4; ++q4) {
+                            uint4 v;
+                            v.x = pack_bf16(__uint_as_float(r[8 * q4]) * inv, __uint_as_float(r[8 * q4 + 1]) * inv);
+                            v.y = pack_bf16(__uint_as_float(r[8 * q4 + 2]) * inv, __uint_as_float(r[8 * q4 + 3]) * inv);
+                            v.z = pack_bf16(__uint_as_float(r[8 * q4 + 4]) * inv, __uint_as_float(r[8 * q4 + 5]) * inv);
+                            v.w = pack_bf16(__uint_as_float(r[8 * q4 + 6]) * inv, __uint_as_float(r[8 * q4 + 7]) * inv);
+                            *reinterpret_cast<uint4*>(dst + c + 8 * q4) = v;
+                        }
+                    } else {
+                        float4* po = reinterpret_cast<float4*>(p.part_o + slot * HD + c);
+#pragma unroll
+                        for (int q4 = 0; q4 < 8; ++q4)
+                            po[q4] = make_float4(__uint_as_float(r[4 * q4]), __uint_as_float(r[4 * q4 + 1]), __uint_as_float(r[4 * q4 + 2]),
+                                                 __uint_as_float(r[4 * q4 + 3]));
                     }
+                }
+                if (SPLIT && !direct && row_ok) {
+                    p.part_ml[slot * 2] = m_used;
+                    p.part_ml[slot * 2 + 1] = l;
                 }
             }
         }
@@ -558,16 +596,46 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
     }
 }
 
+// One block per (sequence, head); does nothing when the token's keys lay in one split.
+template <int HD>
+__global__ void attention_tc_merge_kernel(const Params p)
+{
+    pdl_enter();
+    const int seq = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
+    const int tok = p.q_start[seq];
+    const int pos = p.positions[tok];
+    const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    const int z_first = lo / p.split_keys, z_last = pos / p.split_keys;
+    if (z_first == z_last) return;
+    const size_t base = ((size_t)tok * p.nh + head) * p.max_splits;
+    float M = -INFINITY;
+    for (int z = z_first; z <= z_last; ++z) M = fmaxf(M, p.part_ml[(base + z) * 2]);
+    float L = 0.f, acc = 0.f;
+    for (int z = z_first; z <= z_last; ++z) {
+        const float mz = p.part_ml[(base + z) * 2];
+        const float f = mz == -INFINITY ? 0.f : exp2f(mz - M);
+        L += p.part_ml[(base + z) * 2 + 1] * f;
+        acc += p.part_o[(base + z) * HD + d] * f;
+    }
+    p.out[((size_t)tok * p.nh + head) * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 }  // namespace
 
-// Attention of a batch of prompt portions (any mix, single tokens included) over its pages.
+// Floats of scratch the split mode needs for `seqs` decoding sequences.
+extern "C" long long spy_attention_tc_scratch_floats(int seqs, int nh, int hd, int max_splits) { return (long long)seqs * nh * max_splits * (hd + 2); }
+
+// Attention of a batch over its pages.  split_keys == 0: prompt portions (any mix, single tokens
+// included).  split_keys > 0 (a multiple of 128): every sequence brings one token and its keys
+// are cut into at most max_splits ranges of split_keys, merged through `scratch`.
 extern "C" int spy_attention_tc(const void* q, long long q_row_stride, void* out, const void* pages, const int* block_table, int table_width,
                                 int page_size, int num_pages, int nh, int nkv, int hd, const int* positions, const int* q_start, int tokens,
-                                int seqs, int window, float scale, int* status, cudaStream_t stream)
+                                int seqs, int window, float scale, int split_keys, int max_splits, float* scratch, long long scratch_floats,
+                                int* status, cudaStream_t stream)
 {
     if (tokens <= 0 || seqs <= 0) return 0;
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0) SPY_FAIL("attention_tc: %d query heads do not group over %d key/value heads", nh, nkv);
@@ -585,6 +653,7 @@ extern "C" int spy_attention_tc(const void* q, long long q_row_stride, void* out
     p.q = (const bf16*)q; p.q_stride = q_row_stride; p.out = (bf16*)out; p.pages = (const bf16*)pages; p.block_table = block_table;
     p.positions = positions; p.q_start = q_start; p.status = status; p.table_width = table_width; p.page_size = page_size;
     p.num_pages = num_pages; p.nh = nh; p.nkv = nkv; p.G = G; p.Gp = Gp; p.S = seqs; p.window = window; p.scale_log2 = scale * LOG2E;
+    p.split_keys = split_keys; p.max_splits = max_splits; p.part_o = nullptr; p.part_ml = nullptr;
     if (page_size < 8 || page_size > TILE || TILE % page_size != 0)
         SPY_FAIL("attention_tc: page_size %d must be 8, 16, 32, 64 or 128 (one TMA box per page)", page_size);
     // the pages of this cache as one matrix [num_pages * 2 * nkv * page_size rows, hd]; a box is one page's rows x 64 columns
@@ -607,18 +676,42 @@ extern "C" int spy_attention_tc(const void* q, long long q_row_stride, void* out
                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) SPY_FAIL("attention_tc: cuTensorMapEncodeTiled failed with code %d", (int)r);
     }
+    static bool configured = false;
+    if (!configured) {
+        SPY_CUDA(cudaFuncSetAttribute(attention_tc_kernel<64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<64>::TOTAL));
+        SPY_CUDA(cudaFuncSetAttribute(attention_tc_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<128>::TOTAL));
+        SPY_CUDA(cudaFuncSetAttribute(attention_tc_kernel<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<64>::TOTAL));
+        SPY_CUDA(cudaFuncSetAttribute(attention_tc_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<128>::TOTAL));
+        configured = true;
+    }
+    if (split_keys > 0) {
+        if (tokens != seqs) SPY_FAIL("attention_tc: split mode needs one token per sequence (%d tokens, %d sequences)", tokens, seqs);
+        if (split_keys % TILE != 0 || max_splits <= 0 || max_splits > 65535)
+            SPY_FAIL("attention_tc: split_keys %d must be a multiple of %d and max_splits %d positive", split_keys, TILE, max_splits);
+        const long long need = spy_attention_tc_scratch_floats(seqs, nh, hd, max_splits);
+        if (max_splits > 1 && (scratch == nullptr || scratch_floats < need))
+            SPY_FAIL("attention_tc: %lld floats of scratch are needed, %lld were given", need, scratch_floats);
+        p.part_o = scratch;
+        p.part_ml = scratch ? scratch + (size_t)seqs * nh * max_splits * hd : nullptr;
+        if (nkv > 65535) SPY_FAIL("attention_tc: the batch exceeds the grid limits");
+        dim3 grid(seqs, nkv, max_splits);
+        if (hd == 64) spy_launch(attention_tc_kernel<64, true>, grid, dim3(NUM_THREADS), (size_t)Smem<64>::TOTAL, stream, page_map, p);
+        else spy_launch(attention_tc_kernel<128, true>, grid, dim3(NUM_THREADS), (size_t)Smem<128>::TOTAL, stream, page_map, p);
+        SPY_CHECK_LAUNCH("attention_tc (split)");
+        if (max_splits > 1) {
+            dim3 mgrid(seqs, nh);
+            if (hd == 64) spy_launch(attention_tc_merge_kernel<64>, mgrid, dim3(64), 0, stream, p);
+            else spy_launch(attention_tc_merge_kernel<128>, mgrid, dim3(128), 0, stream, p);
+            SPY_CHECK_LAUNCH("attention_tc (merge)");
+        }
+        return 0;
+    }
     const int tokens_per_block = ROWS / Gp;
     const long long blocks = (tokens + tokens_per_block - 1) / tokens_per_block + seqs;   // an upper bound without a host copy of q_start
     if (blocks > 0x7fffffffLL || nkv > 65535) SPY_FAIL("attention_tc: the batch exceeds the grid limits");
     dim3 grid((unsigned)blocks, nkv);
-    static bool configured = false;
-    if (!configured) {
-        SPY_CUDA(cudaFuncSetAttribute(attention_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<64>::TOTAL));
-        SPY_CUDA(cudaFuncSetAttribute(attention_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<128>::TOTAL));
-        configured = true;
-    }
-    if (hd == 64) spy_launch(attention_tc_kernel<64>, grid, dim3(NUM_THREADS), (size_t)Smem<64>::TOTAL, stream, page_map, p);
-    else spy_launch(attention_tc_kernel<128>, grid, dim3(NUM_THREADS), (size_t)Smem<128>::TOTAL, stream, page_map, p);
+    if (hd == 64) spy_launch(attention_tc_kernel<64, false>, grid, dim3(NUM_THREADS), (size_t)Smem<64>::TOTAL, stream, page_map, p);
+    else spy_launch(attention_tc_kernel<128, false>, grid, dim3(NUM_THREADS), (size_t)Smem<128>::TOTAL, stream, page_map, p);
     SPY_CHECK_LAUNCH("attention_tc");
     return 0;
 }

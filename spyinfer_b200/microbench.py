@@ -54,7 +54,7 @@ def bench_attention(batch: int, context: int, q_len: int = 1, split_keys: int = 
 
     def run():
         if use_tc:
-            kernels.attention_tc(q, nh, hd, out, pages, bt, pos, q_start, batch, 1 / math.sqrt(hd))
+            kernels.attention_tc(q, nh, hd, out, pages, bt, pos, q_start, batch, 1 / math.sqrt(hd), split_keys=split_keys, max_splits=max_splits)
         else:
             kernels.attention_mma(q, nh, hd, out, pages, bt, pos, q_start, batch, 1 / math.sqrt(hd), split_keys=split_keys, max_splits=max_splits)
 

@@ -95,16 +95,18 @@ class Attention(Mixer):
                                   self.rope_table, batch.positions, batch.seq_of_token, cache.block_table, cache.pages,
                                   store=cache.writes, status=batch.status, q_out=q)
         out = torch.empty((x.shape[0], self.nh * self.hd), dtype=x.dtype, device=x.device)
+        decoding = batch.num_tokens == batch.num_seqs         # every request brings one token
         if not self.fast:
             kernels.attention_generic(q, self.nh, self.hd, out, cache.pages, cache.block_table, batch.positions, batch.seq_of_token,
                                       self.scale, window=self.window, status=batch.status)
-        elif batch.num_tokens == batch.num_seqs:
-            # every request brings one token: decoding, keys split across blocks
+        elif decoding:
+            # memory-bound: keys split across blocks, two blocks per SM, K and V streamed by cp.async rings
+            # (the tcgen05 kernel's split mode fits one block per SM and measures slower here)
             kernels.attention_mma(q, self.nh, self.hd, out, cache.pages, cache.block_table, batch.positions, batch.q_start,
                                   batch.num_seqs, self.scale, window=self.window, split_keys=self.split_keys,
                                   max_splits=self.max_splits, status=batch.status)
         elif cache.page_size in (8, 16, 32, 64, 128):
-            # prompt portions (and whatever decodes beside them): 128-row blocks on tcgen05, pages brought in by TMA
+            # prompt portions (and whatever decodes beside them): 128-row blocks on tcgen05, a page is one TMA box
             kernels.attention_tc(q, self.nh, self.hd, out, cache.pages, cache.block_table, batch.positions, batch.q_start,
                                  batch.num_seqs, self.scale, window=self.window, status=batch.status)
         else:

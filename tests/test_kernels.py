@@ -480,6 +480,30 @@ def test_attention_tc_mixed_batch(nh, nkv, hd, page_size, window):
         torch.testing.assert_close(out[i].view(nh, hd).double(), ref, rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("nh,nkv,hd,page_size,window,split_keys", [(32, 8, 128, 16, None, 256), (10, 2, 64, 16, 300, 128), (8, 8, 128, 8, None, 128),
+                                                                   (12, 4, 64, 32, None, 512), (16, 1, 128, 16, 700, 384)])
+def test_attention_tc_split_decode(nh, nkv, hd, page_size, window, split_keys):
+    """tcgen05 attention, split mode: one token per sequence, contexts from 1 to 1500 keys so that
+    rows fall into one split, two splits and many, with and without a window."""
+    from spyinfer_b200 import kernels
+    torch.manual_seed(nh + hd + 3)
+    lens = [1, 17, split_keys, split_keys + 1, 700, 1500]
+    S = len(lens)
+    pages, bt, ks, vs = paged_setup(S, lens, nkv, hd, page_size, torch.bfloat16)
+    q = torch.randn(S, (nh + 2 * nkv) * hd, device=DEV).to(torch.bfloat16)
+    positions = torch.tensor([l - 1 for l in lens], dtype=torch.int32, device=DEV)
+    q_start = torch.arange(S + 1, dtype=torch.int32, device=DEV)
+    out = torch.full((S, nh * hd), float("nan"), device=DEV, dtype=torch.bfloat16)
+    scale = 1 / math.sqrt(hd)
+    max_splits = (1500 + split_keys - 1) // split_keys
+    kernels.attention_tc(q, nh, hd, out, pages, bt, positions, q_start, S, scale, window=window, split_keys=split_keys, max_splits=max_splits)
+    torch.cuda.synchronize()
+    assert kernels.status_word(DEV)[0].item() == 0
+    for i, l in enumerate(lens):
+        ref = ref_attention(q[i, :nh * hd].view(nh, hd), ks[i], vs[i], l - 1, scale, window)
+        torch.testing.assert_close(out[i].view(nh, hd).double(), ref, rtol=2e-2, atol=2e-2)
+
+
 def test_attention_tc_refuses_pages_that_are_no_tma_box():
     from spyinfer_b200 import kernels
     pages, bt, ks, vs = paged_setup(1, [20], 1, 64, 5, torch.bfloat16)
