@@ -50,6 +50,11 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes)
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
 
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
 {
     uint32_t ok;
@@ -387,6 +392,190 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     }
 }
 
+// Stores 32 consecutive accumulator columns of row x (normal mode), with the optional SwiGLU.
+template <typename TC, int EPI>
+__device__ __forceinline__ void store_chunk_normal(TC* base, long long ld, int x, int y, int x_rows, int y_rows, const uint32_t (&r)[32])
+{
+    if (x >= x_rows || y >= y_rows) return;
+    if constexpr (EPI == 1) {
+        uint32_t o[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(silu_mul(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1])));
+        TC* dst = base + (size_t)x * ld + y / 2;
+        const int valid = min(16, (y_rows - y) / 2);
+        if (valid >= 16 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0 && sizeof(TC) == 2) {
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                uint4 v;
+                __nv_bfloat162 t;
+                t = __floats2bfloat162_rn(__uint_as_float(o[8 * i]), __uint_as_float(o[8 * i + 1])); v.x = *reinterpret_cast<uint32_t*>(&t);
+                t = __floats2bfloat162_rn(__uint_as_float(o[8 * i + 2]), __uint_as_float(o[8 * i + 3])); v.y = *reinterpret_cast<uint32_t*>(&t);
+                t = __floats2bfloat162_rn(__uint_as_float(o[8 * i + 4]), __uint_as_float(o[8 * i + 5])); v.z = *reinterpret_cast<uint32_t*>(&t);
+                t = __floats2bfloat162_rn(__uint_as_float(o[8 * i + 6]), __uint_as_float(o[8 * i + 7])); v.w = *reinterpret_cast<uint32_t*>(&t);
+                reinterpret_cast<uint4*>(dst)[i] = v;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                if (j < valid) store_elem(dst + j, __uint_as_float(o[j]));
+        }
+    } else {
+        TC* dst = base + (size_t)x * ld + y;
+        const bool aligned = (reinterpret_cast<uintptr_t>(dst) & 15) == 0;
+        store_row32<TC>(dst, r, min(32, y_rows - y), aligned);
+    }
+}
+
+// The product for many tokens (normal mode, 128 x 256 tiles, one pass over K) as a PERSISTENT
+// kernel: one block per SM walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...; the TMA ring
+// runs on across tiles, and the accumulator is double-buffered in tensor memory (2 x 256
+// columns), so the epilogue of a tile (tcgen05.ld, conversion, stores) overlaps the main loop
+// of the next.  Tiles are numbered with the token tiles fastest, so blocks that run side by
+// side share a weight tile in L2.
+template <typename TC, int EPI>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, TC* __restrict__ out,
+                               long long ld, int x_rows, int y_rows, int k_blocks, int x_tiles, int num_tiles, int* status)
+{
+    constexpr int BN = 256;
+    using T = Tile<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* tiles = smem;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)T::STAGES * T::STAGE_BYTES);
+    uint64_t* empty_bar = full_bar + T::STAGES;
+    uint64_t* acc_full = empty_bar + T::STAGES;    // [2] accumulator complete (MMA commit)
+    uint64_t* acc_empty = acc_full + 2;            // [2] accumulator read out (128 arrivals)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < T::STAGES; ++s) {
+            mbar_init(full_bar + s, 1);
+            mbar_init(empty_bar + s, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(acc_full + b, 1);
+            mbar_init(acc_empty + b, 128);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2u * BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    pdl_launch_dependents();
+    if (warp == 0) {
+        if (lane == 0) {
+            long long g = 0;   // k-blocks requested so far: the ring position
+            bool first = true, ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int x0 = (tile % x_tiles) * BM, y0 = (tile / x_tiles) * BN;
+                int kb = 0;
+                if (first) {
+                    // weights (Y) of the first stages before the wait for the kernels ahead in the stream
+                    const int pre = min(k_blocks, T::STAGES);
+                    for (int i = 0; i < pre; ++i) {
+                        mbar_expect_tx(full_bar + i, T::STAGE_BYTES);
+                        tma_load_2d(tiles + (size_t)i * T::STAGE_BYTES + T::X_BYTES, &map_y, i * BK, y0, full_bar + i);
+                    }
+                    pdl_wait();
+                    for (int i = 0; i < pre; ++i) tma_load_2d(tiles + (size_t)i * T::STAGE_BYTES, &map_x, i * BK, x0, full_bar + i);
+                    kb = pre;
+                    g = pre;
+                    first = false;
+                }
+                for (; kb < k_blocks; ++kb, ++g) {
+                    const int s = (int)(g % T::STAGES);
+                    const uint32_t phase = (uint32_t)(g / T::STAGES) & 1;
+                    if (g >= T::STAGES && !mbar_wait(empty_bar + s, phase ^ 1, abort_flag)) { ok = false; break; }
+                    uint8_t* xs = tiles + (size_t)s * T::STAGE_BYTES;
+                    mbar_expect_tx(full_bar + s, T::STAGE_BYTES);
+                    tma_load_2d(xs, &map_x, kb * BK, x0, full_bar + s);
+                    tma_load_2d(xs + T::X_BYTES, &map_y, kb * BK, y0, full_bar + s);
+                }
+            }
+            if (first) pdl_wait();
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = make_instr_desc(BN);
+            long long g = 0;
+            int i = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++i) {
+                const int buf = i & 1;
+                const uint32_t aph = (uint32_t)(i >> 1) & 1;
+                if (i >= 2) ok = mbar_wait(acc_empty + buf, aph ^ 1, abort_flag);   // the epilogue has read this buffer's last tile
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t acc = tmem_base + (uint32_t)buf * BN;
+                for (int kb = 0; kb < k_blocks; ++kb, ++g) {
+                    const int s = (int)(g % T::STAGES);
+                    const uint32_t phase = (uint32_t)(g / T::STAGES) & 1;
+                    ok = mbar_wait(full_bar + s, phase, abort_flag);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint8_t* xs = tiles + (size_t)s * T::STAGE_BYTES;
+                    const uint64_t dx = make_smem_desc(xs), dy = make_smem_desc(xs + T::X_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        const uint64_t adv = (uint64_t)((k * UMMA_K * 2) >> 4);
+                        umma(acc, dx + adv, dy + adv, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(empty_bar + s);
+                }
+                if (ok) umma_commit(acc_full + buf);
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        pdl_wait();   // the output buffer may still be in use by a kernel ahead in the stream
+        int i = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++i) {
+            const int buf = i & 1;
+            const uint32_t aph = (uint32_t)(i >> 1) & 1;
+            const int x0 = (tile % x_tiles) * BM, y0 = (tile / x_tiles) * BN;
+            ok = mbar_wait(acc_full + buf, aph, abort_flag);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int x = x0 + quarter * 32 + lane;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                uint32_t r[32];
+                tmem_load_32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c), r);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                store_chunk_normal<TC, EPI>(out, ld, x, y0 + c, x_rows, y_rows, r);
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(acc_empty + buf);
+        }
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (*abort_flag) {
+        if (threadIdx.x == 0) {
+            const unsigned long long t0 = global_timer();
+            while (global_timer() - t0 < 2000000ull) { }
+            report_status(status, SPY_STATUS_WAIT_TIMEOUT, (int)blockIdx.x);
+        }
+        __syncthreads();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2u * BN) : "memory");
+    }
+}
+
 // Sums the splits of a scratch buffer in ascending order and stores the output type.
 template <typename TC>
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, TC* __restrict__ out, long long elems, int splits)
@@ -515,6 +704,37 @@ extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, 
     const long long ld = splits > 1 ? N : ldc;
     const long long split_stride = splits > 1 ? (long long)M * N : 0;
     const bool f32_out = splits > 1 || c_dtype == SPY_F32;
+    if (!swap && splits == 1) {
+        // many tokens, one pass over K: the persistent kernel (one block per SM)
+        static int num_sms = 0;
+        if (num_sms == 0) {
+            int dev = 0;
+            SPY_CUDA(cudaGetDevice(&dev));
+            SPY_CUDA(cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev));
+        }
+        const int x_tiles = (M + BM - 1) / BM, y_tiles = (N + 255) / 256;
+        const long long num_tiles = (long long)x_tiles * y_tiles;
+        if (num_tiles > 0x7fffffffLL) SPY_FAIL("gemm_tcgen05: %lld tiles exceed the kernel's range", num_tiles);
+        const int grid = (int)(num_tiles < num_sms ? num_tiles : num_sms);
+        static bool configured = false;
+        if (!configured) {
+            SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<bf16, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Tile<256>::SMEM));
+            SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<float, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Tile<256>::SMEM));
+            SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<bf16, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Tile<256>::SMEM));
+            configured = true;
+        }
+        if (epilogue == 1)
+            spy_launch(gemm_tcgen05_persistent_kernel<bf16, 1>, dim3(grid), dim3(NUM_THREADS), Tile<256>::SMEM, stream, mx, my, (bf16*)C, ldc, M, N,
+                       k_blocks, x_tiles, (int)num_tiles, status);
+        else if (c_dtype == SPY_F32)
+            spy_launch(gemm_tcgen05_persistent_kernel<float, 0>, dim3(grid), dim3(NUM_THREADS), Tile<256>::SMEM, stream, mx, my, (float*)C, ldc, M, N,
+                       k_blocks, x_tiles, (int)num_tiles, status);
+        else
+            spy_launch(gemm_tcgen05_persistent_kernel<bf16, 0>, dim3(grid), dim3(NUM_THREADS), Tile<256>::SMEM, stream, mx, my, (bf16*)C, ldc, M, N,
+                       k_blocks, x_tiles, (int)num_tiles, status);
+        SPY_CHECK_LAUNCH("gemm_tcgen05 (persistent)");
+        return 0;
+    }
     int rc;
 #define SPY_LAUNCH(BN_, SWAP_)                                                                                                          \
     rc = epilogue == 1 ? launch<BN_, bf16, SWAP_, 1>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, status, stream)       \

@@ -48,11 +48,7 @@ class Attention(Mixer):
         self.position = build_part(pos, ctx) if pos is not None else None
         self.qkv = self.o = self.q_norm = self.k_norm = self.rope_table = None
         self.fast = kernels.attention_mma_takes(self.nh, self.nkv, self.hd, ctx.dtype)
-        # decoding splits every sequence's keys into at most 8 ranges; the range length is
-        # fixed by the longest sequence the engine allows, so a row's arithmetic does not
-        # depend on the batch it decodes in
-        self.split_keys = max(256, ((ctx.max_model_len + 7) // 8 + 63) // 64 * 64)
-        self.max_splits = (ctx.max_model_len + self.split_keys - 1) // self.split_keys
+        self._split_plans = {}
 
     def weight_decls(self):
         p, nh, nkv, hd, H = self.prefix, self.nh, self.nkv, self.hd, self.hidden
@@ -84,6 +80,29 @@ class Attention(Mixer):
     def cache_need(self):
         return PagedCacheNeed(self.nkv, self.hd, int(self.window) if self.window is not None else None)
 
+    def split_plan(self, num_seqs: int):
+        """(split_keys, max_splits) for decoding ``num_seqs`` requests: the keys of every request
+        are cut into ranges so that (requests x key/value heads x ranges) blocks fill whole waves
+        of the GPU's 2 x 148 block slots as evenly as possible; at most 16 ranges, ranges of at
+        least 256 keys and a multiple of 64.  The plan depends on the (padded) batch size only."""
+        plan = self._split_plans.get(num_seqs)
+        if plan is None:
+            slots, per_split, best = 2 * 148, num_seqs * self.nkv, None
+            most = max(1, min(16, self.ctx.max_model_len // 256))
+            for splits in range(1, most + 1):
+                blocks = per_split * splits
+                waves = -(-blocks // slots)
+                fill = min(blocks, slots) / slots if waves == 1 else blocks / (waves * slots)
+                keys = self.ctx.max_model_len / splits
+                score = (fill * keys / (keys + 200.0), -splits)       # a block's fixed cost is worth about 200 keys
+                if best is None or score > best[0]:
+                    best = (score, splits)
+            splits = best[1]
+            split_keys = max(256, (-(-self.ctx.max_model_len // splits) + 63) // 64 * 64)
+            plan = (split_keys, -(-self.ctx.max_model_len // split_keys))
+            self._split_plans[num_seqs] = plan
+        return plan
+
     def forward(self, x, batch, cache):
         if self.rope_table is None and self.position is not None:
             self.rope_table = self.position.rotation_table()   # built by the first step (an eager one)
@@ -102,9 +121,10 @@ class Attention(Mixer):
         elif decoding:
             # memory-bound: keys split across blocks, two blocks per SM, K and V streamed by cp.async rings
             # (the tcgen05 kernel's split mode fits one block per SM and measures slower here)
+            split_keys, max_splits = self.split_plan(batch.num_seqs)
             kernels.attention_mma(q, self.nh, self.hd, out, cache.pages, cache.block_table, batch.positions, batch.q_start,
-                                  batch.num_seqs, self.scale, window=self.window, split_keys=self.split_keys,
-                                  max_splits=self.max_splits, status=batch.status)
+                                  batch.num_seqs, self.scale, window=self.window, split_keys=split_keys, max_splits=max_splits,
+                                  status=batch.status)
         elif cache.page_size in (8, 16, 32, 64, 128):
             # prompt portions (and whatever decodes beside them): 128-row blocks on tcgen05, a page is one TMA box
             kernels.attention_tc(q, self.nh, self.hd, out, cache.pages, cache.block_table, batch.positions, batch.q_start,

@@ -265,10 +265,12 @@ def test_sampling_greedy_and_distribution():
 
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("M,N,K", [(1, 128, 64), (5, 200, 96), (16, 4096, 4096), (17, 1000, 520), (33, 136, 72), (64, 6144, 512),
-                                   (65, 300, 136), (128, 256, 64), (129, 1187, 1032), (300, 512, 4096), (1000, 24, 200), (2048, 1024, 12288)])
+                                   (65, 300, 136), (128, 256, 64), (129, 1187, 1032), (300, 512, 4096), (1000, 24, 200), (2048, 1024, 12288),
+                                   (2048, 4096, 512), (1500, 3000, 264), (4100, 2600, 72)])
 def test_gemm_tcgen05(out_dtype, M, N, K):
     """Tensor-core product at sizes that exercise every tile class (16/32/64 tokens swapped,
-    128 x 256 tiles), tails in M, N and K, and split-K."""
+    128 x 256 tiles), tails in M, N and K, split-K, and the persistent kernel with one, two and
+    several tiles per block."""
     from spyinfer_b200 import kernels
     torch.manual_seed(M * 7 + N)
     a = torch.randn(M, K, device=DEV).to(torch.bfloat16)
