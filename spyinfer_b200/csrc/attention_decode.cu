@@ -1,0 +1,606 @@
+// bfloat16 attention for decoding (every sequence brings one token) on the 5th-generation
+// tensor cores, built to read the paged cache at the speed of the memory.
+//
+// The products are transposed so that the KEYS fill the 128 rows of the tensor-core tile and the
+// G query heads of one key/value head its (padded) 16 columns:
+//   S^T = K . Q^T      128 keys x 16 heads, K's tile as it lies in the pages (K-major A operand)
+//   softmax            128 threads, ONE KEY PER THREAD: tcgen05.ld brings the key's scores for the G
+//                      heads; the running maximum of each head over the tile is one redux per warp
+//                      and an exchange of four values through shared memory
+//   O^T += V^T . P^T   head_dim x 16 heads; V's tile as it lies in the pages (an MN-major A
+//                      operand), P^T written by the softmax threads as bfloat16
+// so no tensor-core row is wasted on padding and a tile of 128 keys costs a few hundred cycles
+// of one block, far below the time its 64 KB take to arrive.
+//
+// One persistent block per SM.  The work of the batch is the list of (sequence, kv head, tile of
+// 128 keys) units; block c takes units [c * per, (c + 1) * per): a balanced share whatever the
+// batch size and the context lengths are.  A block's share is a few SEGMENTS, runs of tiles of
+// one (sequence, kv head) pair.  A segment that is a whole pair writes the output; otherwise
+// its unnormalised output, maximum and sum go to scratch slot (pair + block) and
+// attention_decode_merge_kernel adds a pair's slots in block order.
+// Roles: warps 0-3 softmax and epilogue; warp 4 allocates tensor memory and issues the MMAs;
+// warp 5 brings K tiles (and the segments' queries), warp 6 V tiles, by TMA boxes of one page x
+// 64 columns straight from the paged cache (no cluster multicast), three tiles ahead and across
+// segment borders, so the memory pipe stays full from the first tile of a block to its last.
+// Every wait on an mbarrier is bounded; a wait that runs out raises the block's abort flag,
+// which ends all roles, and the status word reports it.
+//
+// Formula and masking: spymaster2h/spyinfer src/backends/cpu/cpu_attention.cpp:89-135; this
+// replaces its paged_attention_decode_kernel (src/backends/cuda/native/attention.cu:257-370),
+// which reads the cache once per query head on the CUDA cores.
+// Limits (checked on the host): head_dim 64 or 128, G <= 16, bfloat16, a page size of 8, 16, 32,
+// 64 or 128 tokens, at most 1024 sequences.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "tcgen05.cuh"
+
+SPY_MODULE(spy_attention_decode)
+
+namespace {
+
+using namespace tc;
+
+constexpr int TILE = 128;            // keys per tile = UMMA M of the first product
+constexpr int NCOLS = 16;            // UMMA N: the heads of one key/value head, padded
+constexpr int STAGES = 3;            // K and V tiles in flight
+constexpr int QSLOTS = 4;            // queries of segments in flight
+constexpr int MAX_SEQS = 1024;
+constexpr int NUM_THREADS = 224;
+constexpr int HALF_BYTES = TILE * 128;        // 128 rows of 64 elements
+constexpr int STAGE_BYTES = 2 * HALF_BYTES;   // a K or V tile: two halves of head_dim
+constexpr int QP_BYTES = 2 * NCOLS * 128;     // Q^T or P^T: 16 rows, two halves of 64 elements
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float RESCALE_THRESHOLD = 8.0f;
+
+constexpr int K_OFF = 0;
+constexpr int V_OFF = K_OFF + STAGES * STAGE_BYTES;
+constexpr int Q_OFF = V_OFF + STAGES * STAGE_BYTES;
+constexpr int P_OFF = Q_OFF + QSLOTS * QP_BYTES;
+constexpr int PREFIX_OFF = P_OFF + 2 * QP_BYTES;                 // int[MAX_SEQS + 1]
+constexpr int RED_OFF = PREFIX_OFF + (MAX_SEQS + 4) * 4;         // float[2][4][16] maxima, float[4][16] sums
+constexpr int BAR_OFF = RED_OFF + (2 * 4 * NCOLS + 4 * NCOLS) * 4;
+constexpr int NUM_BARS = 4 * STAGES + 3 * 2 + 2 * QSLOTS + 2 + 1;
+constexpr int SMEM_TOTAL = BAR_OFF + NUM_BARS * 8 + 32 + 1024;   // then slack to align the base to 1024
+constexpr int TMEM_COLS = 64;                                    // S^T: 2 x 16 columns; O^T: 16 columns from 32
+
+struct Params {
+    bf16* out;                 // [T, nh * HD]
+    const int* block_table;    // [S, table_width]
+    const int* positions;      // [T]
+    const int* q_start;        // [S + 1]
+    float* part_o;             // [slots][G][HD] unnormalised partial outputs
+    float* part_ml;            // [slots][G][2]  (maximum in the log2 domain, sum)
+    int* status;
+    int table_width, page_size, num_pages, nh, nkv, G, S, window, blocks, max_keys;
+    float scale_log2;
+};
+
+// A run of tiles [t, t_end) of pair (s, kvh), whose keys span `tiles` tiles; `left` units remain
+// for the block after this run.
+struct Seg {
+    int s, kvh, t0, t, t_end, tiles, left;
+};
+
+__device__ __forceinline__ bool seg_first(Seg& g, const int* prefix, int S, int nkv, int u0, int u1)
+{
+    if (u0 >= u1) return false;
+    int a = 0, b = S;   // nkv * prefix[a] <= u0 < nkv * prefix[b]
+    while (b - a > 1) {
+        const int mid = (a + b) >> 1;
+        if (nkv * prefix[mid] <= u0) a = mid; else b = mid;
+    }
+    g.s = a;
+    g.tiles = prefix[a + 1] - prefix[a];
+    const int r = u0 - nkv * prefix[a];
+    g.kvh = r / g.tiles;
+    g.t0 = g.t = r - g.kvh * g.tiles;
+    const int n = min(g.tiles - g.t, u1 - u0);
+    g.t_end = g.t + n;
+    g.left = u1 - u0 - n;
+    return true;
+}
+
+__device__ __forceinline__ bool seg_next(Seg& g, const int* prefix, int S, int nkv)
+{
+    if (g.left <= 0) return false;
+    if (++g.kvh == nkv) {
+        g.kvh = 0;
+        do {
+            if (++g.s >= S) return false;
+            g.tiles = prefix[g.s + 1] - prefix[g.s];
+        } while (g.tiles == 0);
+    }
+    const int n = min(g.tiles, g.left);
+    g.t0 = g.t = 0;
+    g.t_end = n;
+    g.left -= n;
+    return true;
+}
+
+// the keys a sequence's token sees: [lo, pos]; tiles of 128 keys at absolute positions
+__device__ __forceinline__ void key_range(const Params& p, int s, int& tok, int& pos, int& lo)
+{
+    tok = p.q_start[s];
+    pos = p.positions[tok];
+    if (pos >= p.max_keys) pos = -1;   // beyond the block table: the sequence is skipped (and reported)
+    lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+}
+
+__device__ __forceinline__ int tiles_of(int pos, int lo) { return pos >= 0 ? pos / TILE - lo / TILE + 1 : 0; }
+
+// floats map to integers of the same order (and back: the map is its own inverse)
+__device__ __forceinline__ int ordered(float f)
+{
+    const int i = __float_as_int(f);
+    return i ^ ((i >> 31) & 0x7fffffff);
+}
+__device__ __forceinline__ float unordered(int i) { return __int_as_float(i ^ ((i >> 31) & 0x7fffffff)); }
+
+template <int HD, int GN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __grid_constant__ CUtensorMap q_map, const Params p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    int* prefix = reinterpret_cast<int*>(smem + PREFIX_OFF);
+    float* red = reinterpret_cast<float*>(smem + RED_OFF);            // [2][4][NCOLS]
+    float* lred = red + 2 * 4 * NCOLS;                                // [4][NCOLS]
+    uint64_t* bar_kfull = reinterpret_cast<uint64_t*>(smem + BAR_OFF);   // [STAGES] K tile landed (TMA bytes)
+    uint64_t* bar_kfree = bar_kfull + STAGES;                            // [STAGES] its product is complete (MMA commit)
+    uint64_t* bar_vfull = bar_kfree + STAGES;
+    uint64_t* bar_vfree = bar_vfull + STAGES;
+    uint64_t* bar_s = bar_vfree + STAGES;                                // [2] scores complete (MMA commit)
+    uint64_t* bar_p = bar_s + 2;                                         // [2] probabilities written (128 arrivals)
+    uint64_t* bar_o = bar_p + 2;                                         // [2] V^T.P^T complete (MMA commit)
+    uint64_t* bar_qfull = bar_o + 2;                                     // [QSLOTS] a segment's queries landed
+    uint64_t* bar_qfree = bar_qfull + QSLOTS;                            // [QSLOTS] the segment's first products are complete
+    uint64_t* bar_red = bar_qfree + QSLOTS;                              // [2] the four warps' maxima are written
+    uint64_t* bar_lred = bar_red + 2;                                    // the four warps' sums are written
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_lred + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
+    if (tid == 0) {
+        for (int i = 0; i < STAGES; ++i) {
+            mbar_init(bar_kfull + i, 1);
+            mbar_init(bar_kfree + i, 1);
+            mbar_init(bar_vfull + i, 1);
+            mbar_init(bar_vfree + i, 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bar_s + i, 1);
+            mbar_init(bar_p + i, TILE);
+            mbar_init(bar_o + i, 1);
+            mbar_init(bar_red + i, 4);
+        }
+        for (int i = 0; i < QSLOTS; ++i) {
+            mbar_init(bar_qfull + i, 1);
+            mbar_init(bar_qfree + i, 1);
+        }
+        mbar_init(bar_lred, 4);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 4) tmem_alloc(tmem_slot, TMEM_COLS);
+    // Value rows that no copy fills (pages outside a sequence's keys) meet probabilities of zero and
+    // must be finite; rows of Q^T beyond the G heads must be too.  Stale rows later hold real values.
+    for (int i = tid; i < (STAGES * STAGE_BYTES + QSLOTS * QP_BYTES) / 16; i += NUM_THREADS)
+        reinterpret_cast<uint4*>(smem + V_OFF)[i] = make_uint4(0, 0, 0, 0);
+    fence_async_proxy();
+    pdl_wait();   // everything below reads what earlier kernels wrote
+
+    // ---- the batch's units: tiles of every sequence, prefix sums, this block's share
+    for (int s = tid; s < p.S; s += NUM_THREADS) {
+        int tok, pos, lo;
+        key_range(p, s, tok, pos, lo);
+        if (pos < 0 && blockIdx.x == 0) report_status(p.status, SPY_STATUS_BAD_POSITION, tok);
+        prefix[s + 1] = tiles_of(pos, lo);
+    }
+    __syncthreads();
+    if (warp == 0) {
+        int carry = 0;
+        for (int base = 0; base < p.S; base += 32) {
+            const int s = base + lane;
+            int v = s < p.S ? prefix[s + 1] : 0;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int up = __shfl_up_sync(0xffffffffu, v, o);
+                if (lane >= o) v += up;
+            }
+            if (s < p.S) prefix[s + 1] = carry + v;
+            carry += __shfl_sync(0xffffffffu, v, 31);
+        }
+        if (lane == 0) prefix[0] = 0;
+    }
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_o = tmem_base + 2 * NCOLS;
+    const int units = p.nkv * prefix[p.S];
+    const int per = (units + (int)gridDim.x - 1) / (int)gridDim.x;
+    const int u0 = min(units, (int)blockIdx.x * per), u1 = min(units, u0 + per);
+    const uint32_t k_s = smem_u32(smem + K_OFF), v_s = smem_u32(smem + V_OFF), q_s = smem_u32(smem + Q_OFF), p_s = smem_u32(smem + P_OFF);
+
+    if (warp < 4) {
+        // ---------------------------------------------------------------- softmax (one key per thread) and epilogue
+        const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+        Seg g;
+        bool more = seg_first(g, prefix, p.S, p.nkv, u0, u1), alive = true;
+        int gt = 0, seg = 0;   // tiles and segments this block has begun
+        while (more && alive) {
+            int tok, pos, lo;
+            key_range(p, g.s, tok, pos, lo);
+            const int tile_first = lo / TILE;
+            float m_used[GN], l[GN];   // the maximum the probabilities are taken against (equal in all threads); this thread's share of the sum
+#pragma unroll
+            for (int n = 0; n < GN; ++n) {
+                m_used[n] = -INFINITY;
+                l[n] = 0.f;
+            }
+            for (; g.t < g.t_end; ++g.t, ++gt) {
+                const int st = gt & 1;
+                const uint32_t ph = (uint32_t)(gt >> 1) & 1;
+                if (!(alive = mbar_wait(bar_s + st, ph, abort_flag))) break;
+                fence_after_sync();
+                uint32_t r[GN];
+                tmem_load<GN>(tmem_base + st * NCOLS + lane_addr, r);
+                tmem_wait_ld();
+                const int j = (tile_first + g.t) * TILE + tid;
+                const bool visible = j >= lo && j <= pos;
+                float sc[GN];
+#pragma unroll
+                for (int n = 0; n < GN; ++n) {
+                    sc[n] = visible ? __uint_as_float(r[n]) * p.scale_log2 : -INFINITY;
+                    const int mx = __reduce_max_sync(0xffffffffu, ordered(sc[n]));
+                    if (lane == n) red[(st * 4 + warp) * NCOLS + n] = unordered(mx);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_red + st);
+                if (!(alive = mbar_wait(bar_red + st, ph, abort_flag))) break;
+                // the maximum in use moves only when a head's maximum grew by more than the threshold (or from nothing)
+                float alpha[GN];
+                bool grew = false;
+#pragma unroll
+                for (int n = 0; n < GN; ++n) {
+                    const float* rr = red + st * 4 * NCOLS + n;
+                    const float m_new = fmaxf(fmaxf(m_used[n], fmaxf(rr[0], rr[NCOLS])), fmaxf(rr[2 * NCOLS], rr[3 * NCOLS]));
+                    const bool grow = m_new > m_used[n] + RESCALE_THRESHOLD || (m_used[n] == -INFINITY && m_new != -INFINITY);
+                    alpha[n] = grow ? (m_used[n] == -INFINITY ? 0.f : fast_exp2(m_used[n] - m_new)) : 1.f;
+                    if (grow) {
+                        l[n] *= alpha[n];
+                        m_used[n] = m_new;
+                        grew = true;
+                    }
+                }
+                uint16_t pb[GN];
+#pragma unroll
+                for (int n = 0; n < GN; ++n) {
+                    const float pr = fast_exp2(sc[n] - (m_used[n] == -INFINITY ? 0.f : m_used[n]));
+                    l[n] += pr;
+                    pb[n] = __bfloat16_as_ushort(__float2bfloat16_rn(pr));
+                }
+                // O^T is rescaled once the product of the tile before is complete (the segment's first product overwrites it)
+                if (grew && g.t > g.t0) {
+                    if (!(alive = mbar_wait(bar_o + ((gt - 1) & 1), (uint32_t)((gt - 1) >> 1) & 1, abort_flag))) break;
+                    fence_after_sync();
+                    uint32_t o[GN];
+                    tmem_load<GN>(tmem_o + lane_addr, o);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int n = 0; n < GN; ++n) o[n] = __float_as_uint(__uint_as_float(o[n]) * alpha[n]);
+                    tmem_store<GN>(tmem_o + lane_addr, o);
+                    tmem_wait_st();
+                }
+                // P^T's stage is free when the product of two tiles back is complete
+                if (gt >= 2 && !(alive = mbar_wait(bar_o + st, (uint32_t)((gt - 2) >> 1) & 1, abort_flag))) break;
+                uint8_t* pdst = smem + P_OFF + st * QP_BYTES + (tid >> 6) * (NCOLS * 128) + (tid & 7) * 2;
+                const int chunk = (tid & 63) >> 3;
+#pragma unroll
+                for (int n = 0; n < GN; ++n) *reinterpret_cast<uint16_t*>(pdst + n * 128 + ((chunk ^ (n & 7)) << 4)) = pb[n];
+                fence_async_proxy();
+                fence_before_sync();
+                mbar_arrive(bar_p + st);
+            }
+            if (!alive) break;
+            // ---- the segment's result: O^T / sum, or the partial result of this run of tiles
+            if (!(alive = mbar_wait(bar_o + ((gt - 1) & 1), (uint32_t)((gt - 1) >> 1) & 1, abort_flag))) break;
+            fence_after_sync();
+            uint32_t o[GN];
+            tmem_load<GN>(tmem_o + lane_addr, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int n = 0; n < GN; ++n) {
+                const float v = warp_sum(l[n]);
+                if (lane == n) lred[warp * NCOLS + n] = v;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_lred);
+            if (!(alive = mbar_wait(bar_lred, (uint32_t)seg & 1, abort_flag))) break;
+            const bool direct = g.t0 == 0 && g.t_end == g.tiles;
+            const size_t slot = (size_t)(g.s * p.nkv + g.kvh) + blockIdx.x;
+#pragma unroll
+            for (int n = 0; n < GN; ++n) {
+                if (n >= p.G) break;
+                const float sum = (lred[n] + lred[NCOLS + n]) + (lred[2 * NCOLS + n] + lred[3 * NCOLS + n]);
+                if (direct) {
+                    if (tid < HD) p.out[((size_t)tok * p.nh + g.kvh * p.G + n) * HD + tid] = __float2bfloat16_rn(sum > 0.f ? __uint_as_float(o[n]) / sum : 0.f);
+                } else {
+                    if (tid < HD) p.part_o[(slot * p.G + n) * HD + tid] = __uint_as_float(o[n]);
+                    if (tid == n) {
+                        p.part_ml[(slot * p.G + n) * 2] = m_used[n];
+                        p.part_ml[(slot * p.G + n) * 2 + 1] = sum;
+                    }
+                }
+            }
+            ++seg;
+            more = seg_next(g, prefix, p.S, p.nkv);
+        }
+    } else if (warp == 4) {
+        // ---------------------------------------------------------------- MMA issue
+        if (lane == 0 && u0 < u1) {
+            const uint32_t idesc_qk = instr_desc_bf16(TILE, NCOLS, false, false), idesc_pv = instr_desc_bf16(TILE, NCOLS, true, false);
+            Seg gq, gp;
+            bool moreq = seg_first(gq, prefix, p.S, p.nkv, u0, u1), ok = true;
+            seg_first(gp, prefix, p.S, p.nkv, u0, u1);
+            int iq = 0, segq = 0;
+            auto issue_qk = [&]() {   // S^T of the next tile
+                const int stage = iq % STAGES, slot = segq % QSLOTS;
+                if (gq.t == gq.t0) ok = mbar_wait(bar_qfull + slot, (uint32_t)(segq / QSLOTS) & 1, abort_flag);
+                ok = ok && mbar_wait(bar_kfull + stage, (uint32_t)(iq / STAGES) & 1, abort_flag);
+                if (!ok) return;
+                fence_after_sync();
+                const uint32_t kb = k_s + stage * STAGE_BYTES, qb = q_s + slot * QP_BYTES;
+#pragma unroll
+                for (int s = 0; s < HD / 16; ++s)   // 16 elements of head_dim: 32 bytes along the rows of a 64-element half
+                    umma(tmem_base + (iq & 1) * NCOLS, desc_k_major(kb + (s >> 2) * HALF_BYTES + (s & 3) * 32),
+                         desc_k_major(qb + (s >> 2) * (NCOLS * 128) + (s & 3) * 32), idesc_qk, s > 0 ? 1u : 0u);
+                umma_commit(bar_s + (iq & 1));
+                umma_commit(bar_kfree + stage);
+                ++iq;
+                if (++gq.t == gq.t_end) {
+                    umma_commit(bar_qfree + slot);
+                    ++segq;
+                    moreq = seg_next(gq, prefix, p.S, p.nkv);
+                }
+            };
+            issue_qk();
+            if (ok && moreq) issue_qk();
+            for (int ip = 0; ip < u1 - u0 && ok; ++ip) {
+                const int st = ip & 1, stage = ip % STAGES;
+                ok = mbar_wait(bar_p + st, (uint32_t)(ip >> 1) & 1, abort_flag) && mbar_wait(bar_vfull + stage, (uint32_t)(ip / STAGES) & 1, abort_flag);
+                if (!ok) break;
+                fence_after_sync();
+                const uint32_t vb = v_s + stage * STAGE_BYTES, pb = p_s + st * QP_BYTES;
+#pragma unroll
+                for (int s = 0; s < TILE / 16; ++s)   // 16 keys: 16 rows of V, 32 bytes along the rows of P^T
+                    umma(tmem_o, desc_mn_major(vb + s * 16 * 128, HALF_BYTES), desc_k_major(pb + (s >> 2) * (NCOLS * 128) + (s & 3) * 32), idesc_pv,
+                         (gp.t > gp.t0 || s > 0) ? 1u : 0u);
+                umma_commit(bar_o + st);
+                umma_commit(bar_vfree + stage);
+                if (++gp.t == gp.t_end) seg_next(gp, prefix, p.S, p.nkv);
+                if (moreq) issue_qk();   // S^T's stage st is free: P^T of this tile was made from it
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- TMA: K tiles and queries (warp 5), V tiles (warp 6)
+        // One box per page and 64-column half, one lane each (a single thread issuing them one after
+        // the other is the slower way: small boxes are bound by issue latency, not by bandwidth).
+        const int kv = warp - 5;
+        uint64_t* bar_full = kv == 0 ? bar_kfull : bar_vfull;
+        uint64_t* bar_free = kv == 0 ? bar_kfree : bar_vfree;
+        const uint32_t ring = kv == 0 ? k_s : v_s;
+        const int pages_per_tile = TILE / p.page_size;
+        const int boxes = pages_per_tile * (HD / 64);                        // at most 32
+        const uint32_t box_bytes = (uint32_t)p.page_size * 128;              // page_size rows of 64 elements
+        const int my_page = lane / (HD / 64), my_half = lane % (HD / 64);
+        Seg g;
+        bool more = seg_first(g, prefix, p.S, p.nkv, u0, u1), ok = true;
+        int i = 0, seg = 0;
+        while (more && ok) {
+            int tok, pos, lo;
+            key_range(p, g.s, tok, pos, lo);
+            const int tile_first = lo / TILE;
+            const int* bt = p.block_table + (size_t)g.s * p.table_width;
+            if (kv == 0) {
+                if (lane == 0) {
+                    const int slot = seg % QSLOTS;
+                    if (seg >= QSLOTS) ok = mbar_wait(bar_qfree + slot, (uint32_t)(seg / QSLOTS - 1) & 1, abort_flag);
+                    if (ok) {
+                        mbar_expect_tx(bar_qfull + slot, (uint32_t)p.G * HD * 2);
+#pragma unroll
+                        for (int h = 0; h < HD / 64; ++h)
+                            tma_load_3d(q_s + slot * QP_BYTES + h * (NCOLS * 128), &q_map, h * 64, g.kvh * p.G, tok, bar_qfull + slot);
+                    }
+                }
+                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                if (!ok) break;
+            }
+            for (; g.t < g.t_end; ++g.t, ++i) {
+                const int stage = i % STAGES;
+                // this lane's page of the tile (read before the wait for the stage, which hides the lookup)
+                const int lp = (tile_first + g.t) * pages_per_tile + my_page;
+                const bool in_range = lane < boxes && lp * p.page_size <= pos && (lp + 1) * p.page_size > lo;
+                const int page = (in_range && lp < p.table_width) ? bt[lp] : -1;
+                if (lane == 0 && lp + 4 * pages_per_tile < p.table_width) asm volatile("prefetch.global.L2 [%0];" ::"l"(bt + lp + 4 * pages_per_tile));
+                const bool valid = in_range && page >= 0 && page < p.num_pages;
+                if (in_range && !valid && kv == 0) report_status(p.status, SPY_STATUS_BAD_PAGE, tok);
+                const int count = __popc(__ballot_sync(0xffffffffu, valid));
+                if (lane == 0) {
+                    if (i >= STAGES) ok = mbar_wait(bar_free + stage, (uint32_t)(i / STAGES - 1) & 1, abort_flag);
+                    if (ok) mbar_expect_tx(bar_full + stage, (uint32_t)count * box_bytes);
+                }
+                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                if (!ok) break;
+                if (valid) {
+                    const int y = ((page * 2 + kv) * p.nkv + g.kvh) * p.page_size;
+                    tma_load_2d(ring + stage * STAGE_BYTES + my_half * HALF_BYTES + my_page * p.page_size * 128, &page_map, my_half * 64, y, bar_full + stage);
+                }
+            }
+            ++seg;
+            if (ok) more = seg_next(g, prefix, p.S, p.nkv);
+        }
+    }
+
+    fence_before_sync();
+    __syncthreads();
+    if (*abort_flag) {
+        if (tid == 0) {
+            const unsigned long long t0 = global_timer();
+            while (global_timer() - t0 < 2000000ull) { }   // let copies in flight land before the shared memory is released
+            report_status(p.status, SPY_STATUS_WAIT_TIMEOUT, (int)blockIdx.x);
+        }
+        __syncthreads();
+    }
+    if (warp == 4) {
+        fence_after_sync();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// One block per (sequence, head); does nothing when one block of the first kernel had the pair whole.
+template <int HD>
+__global__ void attention_decode_merge_kernel(const Params p)
+{
+    __shared__ int s_sum[2][HD / 32];
+    pdl_enter();
+    const int seq = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
+    const int kvh = head / p.G, n = head - kvh * p.G;
+    int before = 0, total = 0;
+    for (int s = d; s < p.S; s += HD) {
+        int tok, pos, lo;
+        key_range(p, s, tok, pos, lo);
+        const int t = tiles_of(pos, lo);
+        total += t;
+        if (s < seq) before += t;
+    }
+    before = __reduce_add_sync(0xffffffffu, before);
+    total = __reduce_add_sync(0xffffffffu, total);
+    if ((d & 31) == 0) {
+        s_sum[0][d >> 5] = before;
+        s_sum[1][d >> 5] = total;
+    }
+    __syncthreads();
+    before = total = 0;
+    for (int w = 0; w < HD / 32; ++w) {
+        before += s_sum[0][w];
+        total += s_sum[1][w];
+    }
+    int tok, pos, lo;
+    key_range(p, seq, tok, pos, lo);
+    const int tiles = tiles_of(pos, lo);
+    if (tiles == 0) return;
+    const int per = (p.nkv * total + p.blocks - 1) / p.blocks;
+    const int off = p.nkv * before + kvh * tiles;
+    const int c_first = off / per, c_last = (off + tiles - 1) / per;
+    if (c_first == c_last) return;
+    const size_t base = (size_t)(seq * p.nkv + kvh);
+    float M = -INFINITY;
+    for (int c = c_first; c <= c_last; ++c) M = fmaxf(M, p.part_ml[((base + c) * p.G + n) * 2]);
+    float L = 0.f, acc = 0.f;
+    for (int c = c_first; c <= c_last; ++c) {
+        const size_t slot = (base + c) * p.G + n;
+        const float mz = p.part_ml[slot * 2];
+        const float f = mz == -INFINITY ? 0.f : exp2f(mz - M);
+        L += p.part_ml[slot * 2 + 1] * f;
+        acc += p.part_o[slot * HD + d] * f;
+    }
+    p.out[((size_t)tok * p.nh + head) * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+}
+
+int sm_count()
+{
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms = 0;
+    }
+    return sms;
+}
+
+template <int HD, int GN>
+int launch(const CUtensorMap& page_map, const CUtensorMap& q_map, const Params& p, cudaStream_t stream)
+{
+    static bool configured = false;
+    if (!configured) {
+        SPY_CUDA(cudaFuncSetAttribute(attention_decode_kernel<HD, GN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL));
+        configured = true;
+    }
+    spy_launch(attention_decode_kernel<HD, GN>, dim3(p.blocks), dim3(NUM_THREADS), (size_t)SMEM_TOTAL, stream, page_map, q_map, p);
+    SPY_CHECK_LAUNCH("attention_decode");
+    spy_launch(attention_decode_merge_kernel<HD>, dim3(p.S, p.nh), dim3(HD), 0, stream, p);
+    SPY_CHECK_LAUNCH("attention_decode (merge)");
+    return 0;
+}
+
+}  // namespace
+
+// Floats of scratch a batch of `seqs` decoding sequences needs: one slot per (sequence, kv head) pair and per block.
+extern "C" long long spy_attention_decode_scratch_floats(int seqs, int nh, int nkv, int hd)
+{
+    if (nkv <= 0 || nh % nkv != 0) return 0;
+    return ((long long)seqs * nkv + sm_count()) * (nh / nkv) * (hd + 2);
+}
+
+// Attention of a decoding batch over its pages: every sequence brings one token (row
+// q_start[s] of q, at positions[q_start[s]]).
+extern "C" int spy_attention_decode(const void* q, long long q_row_stride, void* out, const void* pages, const int* block_table, int table_width,
+                                    int page_size, int num_pages, int nh, int nkv, int hd, const int* positions, const int* q_start, int tokens,
+                                    int seqs, int window, float scale, float* scratch, long long scratch_floats, int* status, cudaStream_t stream)
+{
+    if (tokens <= 0 || seqs <= 0) return 0;
+    if (nh <= 0 || nkv <= 0 || nh % nkv != 0) SPY_FAIL("attention_decode: %d query heads do not group over %d key/value heads", nh, nkv);
+    const int G = nh / nkv;
+    if (G > NCOLS) SPY_FAIL("attention_decode: %d query heads per key/value head exceed %d", G, NCOLS);
+    if (hd != 64 && hd != 128) SPY_FAIL("attention_decode: head_dim %d is not 64 or 128", hd);
+    if (seqs > MAX_SEQS) SPY_FAIL("attention_decode: %d sequences exceed %d", seqs, MAX_SEQS);
+    if (q_row_stride % 8 != 0 || q_row_stride < (long long)nh * hd || (reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(pages) & 15))
+        SPY_FAIL("attention_decode: queries and pages must be 16-byte aligned with rows a multiple of 8 elements");
+    if (num_pages <= 0 || table_width <= 0) SPY_FAIL("attention_decode: num_pages and table_width must be positive");
+    if (page_size < 8 || page_size > TILE || TILE % page_size != 0)
+        SPY_FAIL("attention_decode: page_size %d must be 8, 16, 32, 64 or 128 (one TMA box per page)", page_size);
+    if (window < 0) SPY_FAIL("attention_decode: window %d must be 0 (none) or positive", window);
+    const long long max_keys = (long long)table_width * page_size;
+    if (max_keys >= (1LL << 30) || (long long)seqs * nkv * (max_keys / TILE + 1) >= (1LL << 31))
+        SPY_FAIL("attention_decode: %d sequences of up to %lld keys exceed this kernel's counters", seqs, max_keys);
+    const int sms = sm_count();
+    if (sms <= 0) SPY_FAIL("attention_decode: the device's SM count is not available");
+    const long long need = spy_attention_decode_scratch_floats(seqs, nh, nkv, hd);
+    if (scratch == nullptr || scratch_floats < need) SPY_FAIL("attention_decode: %lld floats of scratch are needed, %lld were given", need, scratch_floats);
+    tc::EncodeTiledFn encode = tc::encode_tiled_fn();
+    if (encode == nullptr) SPY_FAIL("attention_decode: cuTensorMapEncodeTiled is not available from the driver");
+
+    Params p;
+    p.out = (bf16*)out; p.block_table = block_table; p.positions = positions; p.q_start = q_start; p.status = status;
+    p.part_o = scratch; p.part_ml = scratch + ((size_t)seqs * nkv + sms) * G * hd;
+    p.table_width = table_width; p.page_size = page_size; p.num_pages = num_pages; p.nh = nh; p.nkv = nkv; p.G = G; p.S = seqs;
+    p.window = window; p.blocks = sms; p.max_keys = (int)max_keys; p.scale_log2 = scale * LOG2E;
+
+    // the pages of this cache as one matrix [num_pages * 2 * nkv * page_size rows, hd]; a box is one page's rows x 64 columns
+    CUtensorMap page_map, q_map;
+    {
+        cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)num_pages * 2 * nkv * page_size};
+        cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
+        cuuint32_t box[2] = {64, (cuuint32_t)page_size};
+        cuuint32_t elem[2] = {1, 1};
+        CUresult r = encode(&page_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pages), dims, strides, box, elem,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) SPY_FAIL("attention_decode: cuTensorMapEncodeTiled (pages) failed with code %d", (int)r);
+    }
+    {   // the queries as [tokens][nh heads][hd]; a box is the G heads of one kv head x 64 columns of one token
+        cuuint64_t dims[3] = {(cuuint64_t)hd, (cuuint64_t)nh, (cuuint64_t)tokens};
+        cuuint64_t strides[2] = {(cuuint64_t)hd * 2, (cuuint64_t)q_row_stride * 2};
+        cuuint32_t box[3] = {64, (cuuint32_t)G, 1};
+        cuuint32_t elem[3] = {1, 1, 1};
+        CUresult r = encode(&q_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box, elem,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) SPY_FAIL("attention_decode: cuTensorMapEncodeTiled (queries) failed with code %d", (int)r);
+    }
+    const int gn = G <= 4 ? 4 : (G <= 8 ? 8 : 16);
+    if (hd == 64) return gn == 4 ? launch<64, 4>(page_map, q_map, p, stream) : (gn == 8 ? launch<64, 8>(page_map, q_map, p, stream) : launch<64, 16>(page_map, q_map, p, stream));
+    return gn == 4 ? launch<128, 4>(page_map, q_map, p, stream) : (gn == 8 ? launch<128, 8>(page_map, q_map, p, stream) : launch<128, 16>(page_map, q_map, p, stream));
+}

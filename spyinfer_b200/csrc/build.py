@@ -27,7 +27,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-shared",
               "-Xcompiler", "-fvisibility=default"]
-MODULES = ["embedding", "rmsnorm", "qk_rope_store", "attention_generic", "attention_mma", "attention_tc", "gemm_simt", "gemm_tcgen05", "swiglu", "sampling"]
+MODULES = ["embedding", "rmsnorm", "qk_rope_store", "attention_generic", "attention_mma", "attention_tc", "attention_decode", "gemm_simt", "gemm_tcgen05", "swiglu", "sampling"]
 
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()

@@ -322,6 +322,48 @@ def attention_tc(q: torch.Tensor, num_heads: int, head_dim: int, out: torch.Tens
     return out
 
 
+ATTENTION_DECODE_MAX_SEQS = 1024
+
+
+def attention_decode_takes(num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, dtype: torch.dtype) -> bool:
+    """Whether the persistent tcgen05 decode-attention kernel takes these sizes: bfloat16, head size
+    64 or 128, at most 16 query heads per key/value head, pages of 8 .. 128 tokens (a power of two)."""
+    return (dtype == torch.bfloat16 and head_dim in (64, 128) and num_kv_heads > 0 and num_heads % num_kv_heads == 0
+            and num_heads // num_kv_heads <= 16 and page_size in (8, 16, 32, 64, 128))
+
+
+def attention_decode(q: torch.Tensor, num_heads: int, head_dim: int, out: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor,
+                     positions: torch.Tensor, q_start: torch.Tensor, num_seqs: int, scale: float, window: Optional[int] = None,
+                     status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Attention of a decoding batch (one token per sequence) over its pages: one persistent block
+    per SM, keys in the rows of tcgen05 tiles, pages brought in by TMA, the batch's tiles shared out
+    evenly over the blocks and merged through scratch memory.  At most 1024 sequences."""
+    _check(q, "attention queries", torch.bfloat16, 2)
+    _check(out, "attention output", torch.bfloat16, 2)
+    _check(pages, "cache pages", torch.bfloat16, 5)
+    _check(block_table, "block table", torch.int32, 2)
+    _check(positions, "positions", torch.int32, 1)
+    _check(q_start, "q_start", torch.int32, 1)
+    T = q.shape[0]
+    num_pages, two, nkv, page_size, hd = pages.shape
+    if two != 2 or hd != head_dim:
+        raise KernelError(f"cache pages: expected [pages, 2, nkv, page_size, {head_dim}], found {tuple(pages.shape)}")
+    if q.shape[1] < num_heads * head_dim or tuple(out.shape) != (T, num_heads * head_dim):
+        raise KernelError(f"attention: q {tuple(q.shape)} / out {tuple(out.shape)} do not fit {num_heads} heads of {head_dim}")
+    if positions.shape[0] != T or q_start.shape[0] != num_seqs + 1 or block_table.shape[0] < num_seqs or T < num_seqs:
+        raise KernelError("attention: positions need one entry per token, q_start one per sequence plus one, the block table a row per sequence")
+    lib = build.load("attention_decode")
+    lib.spy_attention_decode_scratch_floats.restype = ctypes.c_longlong
+    floats = int(lib.spy_attention_decode_scratch_floats(num_seqs, num_heads, nkv, head_dim))
+    scratch = attention_scratch(q.device, floats)
+    if status is None:
+        status = status_word(q.device)
+    _call("attention_decode", "spy_attention_decode", _ptr(q), ctypes.c_longlong(q.shape[1]), _ptr(out), _ptr(pages), _ptr(block_table),
+          block_table.shape[1], page_size, num_pages, num_heads, nkv, head_dim, _ptr(positions), _ptr(q_start), T, num_seqs,
+          int(window or 0), ctypes.c_float(scale), _ptr(scratch), ctypes.c_longlong(scratch.numel()), _ptr(status), _stream())
+    return out
+
+
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """``out[M, N] = a[M, K] @ w[N, K]^T`` on the CUDA cores in 32-bit, any sizes and dtypes."""
     _check(a, "gemm input", ndim=2)

@@ -1,7 +1,7 @@
 """Timings of single kernels at chosen sizes, for profiling and for the summaries under profiles/.
 
     python -m spyinfer_b200.microbench gemm --m 2048 --n 24576 --k 4096 [--out-dtype float32] [--iters 20]
-    python -m spyinfer_b200.microbench attention --batch 8 --context 8192 [--q-len 1] [--split-keys 576] [--kernel tc|mma] [--iters 10]
+    python -m spyinfer_b200.microbench attention --batch 8 --context 8192 [--q-len 1] [--split-keys 576] [--kernel tc|mma|decode] [--iters 10]
 
 Defaults are Qwen3-8B's sizes (32 query heads, 8 key/value heads, head size 128, pages of 16).
 Timing is by CUDA events around ``iters`` launches after a warm-up; the product cycles through
@@ -53,7 +53,9 @@ def bench_attention(batch: int, context: int, q_len: int = 1, split_keys: int = 
     use_tc = kernel == "tc" or (kernel == "auto" and split_keys == 0)
 
     def run():
-        if use_tc:
+        if kernel == "decode":
+            kernels.attention_decode(q, nh, hd, out, pages, bt, pos, q_start, batch, 1 / math.sqrt(hd))
+        elif use_tc:
             kernels.attention_tc(q, nh, hd, out, pages, bt, pos, q_start, batch, 1 / math.sqrt(hd), split_keys=split_keys, max_splits=max_splits)
         else:
             kernels.attention_mma(q, nh, hd, out, pages, bt, pos, q_start, batch, 1 / math.sqrt(hd), split_keys=split_keys, max_splits=max_splits)
@@ -88,7 +90,8 @@ def main(argv=None) -> int:
     a.add_argument("--split-keys", type=int, default=0, help="0: tiles mode; else split mode with this range length")
     a.add_argument("--iters", type=int, default=10)
     a.add_argument("--page-size", type=int, default=16)
-    a.add_argument("--kernel", default="auto", choices=["auto", "tc", "mma"], help="auto: tcgen05 for tiles mode, mma.sync for split mode")
+    a.add_argument("--kernel", default="auto", choices=["auto", "tc", "mma", "decode"],
+                   help="auto: tcgen05 for tiles mode, mma.sync for split mode; decode: the persistent tcgen05 decode kernel (q-len 1)")
     args = ap.parse_args(argv)
     kernels.require_cuda()
     if args.what == "gemm":

@@ -72,7 +72,7 @@ class Attention(Mixer):
                 self.q_norm, self.k_norm = self.q_norm.float(), self.k_norm.float()
 
     def modules(self):
-        mods = ["qk_rope_store"] + (["attention_mma", "attention_tc"] if self.fast else ["attention_generic"]) + self.qkv.modules() + self.o.modules()
+        mods = ["qk_rope_store"] + (["attention_mma", "attention_tc", "attention_decode"] if self.fast else ["attention_generic"]) + self.qkv.modules() + self.o.modules()
         if self.position is not None:
             mods += self.position.modules()
         return mods
@@ -118,9 +118,13 @@ class Attention(Mixer):
         if not self.fast:
             kernels.attention_generic(q, self.nh, self.hd, out, cache.pages, cache.block_table, batch.positions, batch.seq_of_token,
                                       self.scale, window=self.window, status=batch.status)
+        elif decoding and batch.num_seqs <= kernels.ATTENTION_DECODE_MAX_SEQS and kernels.attention_decode_takes(
+                self.nh, self.nkv, self.hd, cache.page_size, x.dtype):
+            # memory-bound: one persistent block per SM, the batch's key tiles shared out evenly, pages by TMA
+            kernels.attention_decode(q, self.nh, self.hd, out, cache.pages, cache.block_table, batch.positions, batch.q_start,
+                                     batch.num_seqs, self.scale, window=self.window, status=batch.status)
         elif decoding:
-            # memory-bound: keys split across blocks, two blocks per SM, K and V streamed by cp.async rings
-            # (the tcgen05 kernel's split mode fits one block per SM and measures slower here)
+            # page sizes that are no TMA box, or very many requests: keys split across blocks by a plan per batch size
             split_keys, max_splits = self.split_plan(batch.num_seqs)
             kernels.attention_mma(q, self.nh, self.hd, out, cache.pages, cache.block_table, batch.positions, batch.q_start,
                                   batch.num_seqs, self.scale, window=self.window, split_keys=split_keys, max_splits=max_splits,

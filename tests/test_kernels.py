@@ -534,3 +534,105 @@ def test_attention_tc_finds_one_far_key_and_survives_large_scores():
         hit = torch.allclose(out[0, :hd].float(), vs[0][far, 0].float(), atol=2e-2)
         inside = window is None or far > L - 1 - window
         assert hit == inside, f"window {window}, far key {far}: expected {'a hit' if inside else 'no hit'}"
+
+
+@pytest.mark.parametrize("nh,nkv,hd,page_size,window", [(32, 8, 128, 16, None), (10, 2, 64, 16, 300), (8, 8, 128, 8, None), (12, 4, 64, 32, None),
+                                                        (16, 1, 128, 16, 700), (6, 1, 128, 128, None), (8, 2, 128, 64, 130)])
+def test_attention_decode_contexts_from_one_key_to_thousands(nh, nkv, hd, page_size, window):
+    """Persistent tcgen05 decode attention: one token per sequence, contexts at tile edges (127, 128,
+    129 keys) and long ones, so that pairs are written whole by one block, cut over two blocks and over
+    many; group sizes 1, 3, 4, 5, 6 and 16; with and without a window."""
+    from spyinfer_b200 import kernels
+    torch.manual_seed(nh + hd + 5)
+    lens = [1, 17, 127, 128, 129, 700, 1500, 3000]
+    S = len(lens)
+    pages, bt, ks, vs = paged_setup(S, lens, nkv, hd, page_size, torch.bfloat16)
+    q = torch.randn(S, (nh + 2 * nkv) * hd, device=DEV).to(torch.bfloat16)
+    positions = torch.tensor([l - 1 for l in lens], dtype=torch.int32, device=DEV)
+    q_start = torch.arange(S + 1, dtype=torch.int32, device=DEV)
+    out = torch.full((S, nh * hd), float("nan"), device=DEV, dtype=torch.bfloat16)
+    scale = 1 / math.sqrt(hd)
+    kernels.attention_decode(q, nh, hd, out, pages, bt, positions, q_start, S, scale, window=window)
+    torch.cuda.synchronize()
+    assert kernels.status_word(DEV)[0].item() == 0
+    for i, l in enumerate(lens):
+        ref = ref_attention(q[i, :nh * hd].view(nh, hd), ks[i], vs[i], l - 1, scale, window)
+        torch.testing.assert_close(out[i].view(nh, hd).double(), ref, rtol=2e-2, atol=2e-2)
+
+
+def test_attention_decode_many_short_sequences():
+    """More (sequence, kv head) pairs than blocks: every block walks several whole pairs and the
+    borders of its share fall inside pairs; queries of up to four segments are in flight."""
+    from spyinfer_b200 import kernels
+    torch.manual_seed(11)
+    nh, nkv, hd, page_size = 8, 2, 128, 16
+    lens = [int(x) for x in torch.randint(1, 400, (150,))] + [128, 256, 1, 2]
+    S = len(lens)
+    pages, bt, ks, vs = paged_setup(S, lens, nkv, hd, page_size, torch.bfloat16)
+    q = torch.randn(S, nh * hd, device=DEV).to(torch.bfloat16)
+    positions = torch.tensor([l - 1 for l in lens], dtype=torch.int32, device=DEV)
+    q_start = torch.arange(S + 1, dtype=torch.int32, device=DEV)
+    out = torch.full((S, nh * hd), float("nan"), device=DEV, dtype=torch.bfloat16)
+    scale = 1 / math.sqrt(hd)
+    for _ in range(2):   # twice: stale shared memory and scratch of the first run must not matter
+        kernels.attention_decode(q, nh, hd, out, pages, bt, positions, q_start, S, scale)
+    torch.cuda.synchronize()
+    assert kernels.status_word(DEV)[0].item() == 0
+    for i, l in enumerate(lens):
+        ref = ref_attention(q[i].view(nh, hd), ks[i], vs[i], l - 1, scale, None)
+        torch.testing.assert_close(out[i].view(nh, hd).double(), ref, rtol=2e-2, atol=2e-2)
+
+
+def test_attention_decode_finds_one_far_key_and_survives_large_scores():
+    """One key stands out by a large score (the running maximum jumps by far more than the rescale
+    threshold after earlier tiles have accumulated): the output must be that key's value row; keys at
+    tile and page edges, in the first and the last block of the pair, and at a window's edge."""
+    from spyinfer_b200 import kernels
+    nh, nkv, hd, page_size, L = 4, 1, 64, 16, 2000
+    pages, bt, ks, vs = paged_setup(1, [L], nkv, hd, page_size, torch.bfloat16)
+    q = torch.randn(1, nh * hd, device=DEV).to(torch.bfloat16)
+    pos = torch.tensor([L - 1], dtype=torch.int32, device=DEV)
+    q_start = torch.tensor([0, 1], dtype=torch.int32, device=DEV)
+    out = torch.empty(1, nh * hd, device=DEV, dtype=torch.bfloat16)
+    for window, far in [(None, 0), (None, 15), (None, 127), (None, 128), (None, 511), (None, 1999), (300, L - 300), (300, L - 301)]:
+        pg = pages.clone()
+        page, slot = int(bt[0, far // page_size]), far % page_size
+        pg[page, 0, 0, slot] = (60.0 * q[0, :hd].float() / q[0, :hd].float().norm()).to(torch.bfloat16)
+        kernels.attention_decode(q, nh, hd, out, pg, bt, pos, q_start, 1, 1.0, window=window)
+        hit = torch.allclose(out[0, :hd].float(), vs[0][far, 0].float(), atol=2e-2)
+        inside = window is None or far > L - 1 - window
+        assert hit == inside, f"window {window}, far key {far}: expected {'a hit' if inside else 'no hit'}"
+    # one sequence on a single block: a large score in a late tile after earlier tiles have accumulated
+    nkv2, L2 = 1, 640
+    S = 160   # enough other pairs that the long pair lies within one block's share
+    lens = [L2] + [100] * (S - 1)
+    pages, bt, ks, vs = paged_setup(S, lens, nkv2, hd, page_size, torch.bfloat16)
+    q = torch.randn(S, nh * hd, device=DEV).to(torch.bfloat16)
+    far = 600
+    page, slot = int(bt[0, far // page_size]), far % page_size
+    pages[page, 0, 0, slot] = (60.0 * q[0, :hd].float() / q[0, :hd].float().norm()).to(torch.bfloat16)
+    out = torch.empty(S, nh * hd, device=DEV, dtype=torch.bfloat16)
+    kernels.attention_decode(q, nh, hd, out, pages, bt, torch.tensor([l - 1 for l in lens], dtype=torch.int32, device=DEV),
+                             torch.arange(S + 1, dtype=torch.int32, device=DEV), S, 1.0)
+    assert torch.allclose(out[0, :hd].float(), vs[0][far, 0].float(), atol=2e-2)
+
+
+def test_attention_decode_reports_bad_pages_and_positions_and_refuses_odd_pages():
+    from spyinfer_b200 import kernels
+    nh, nkv, hd, page_size = 4, 2, 64, 16
+    pages, bt, ks, vs = paged_setup(2, [40, 300], nkv, hd, page_size, torch.bfloat16)
+    q = torch.randn(2, nh * hd, device=DEV).to(torch.bfloat16)
+    q_start = torch.arange(3, dtype=torch.int32, device=DEV)
+    out = torch.zeros(2, nh * hd, device=DEV, dtype=torch.bfloat16)
+    status = torch.zeros(2, dtype=torch.int32, device=DEV)
+    bad = bt.clone()
+    bad[1, 3] = pages.shape[0] + 7   # a page beyond the pool: skipped and reported
+    kernels.attention_decode(q, nh, hd, out, pages, bad, torch.tensor([39, 299], dtype=torch.int32, device=DEV), q_start, 2, 1.0, status=status)
+    assert status.tolist() == [3, 1]
+    status.zero_()
+    kernels.attention_decode(q, nh, hd, out, pages, bt, torch.tensor([39, bt.shape[1] * page_size], dtype=torch.int32, device=DEV), q_start, 2, 1.0,
+                             status=status)
+    assert status.tolist() == [2, 1]
+    pages5, bt5, _, _ = paged_setup(1, [20], 1, 64, 5, torch.bfloat16)
+    with pytest.raises(kernels.KernelError):
+        kernels.attention_decode(q[:1], 4, 64, out[:1], pages5, bt5, torch.tensor([19], dtype=torch.int32, device=DEV), q_start[:2], 1, 1.0)
