@@ -144,7 +144,7 @@ def main() -> int:
     pages_per_req = (ctx + page - 1) // page + 1
     num_pages = max_batch * pages_per_req + (args.prefill_tokens + page - 1) // page + 8
     torch.cuda.set_device(0)
-    engine = LLMEngine(model_config=model_config, seed=0, dtype="bfloat16", max_num_seqs=max_batch, max_model_len=ctx + 16,
+    engine = LLMEngine(model_config=model_config, seed=0, dtype="bfloat16", max_num_seqs=max_batch, max_model_len=max(ctx, args.prefill_tokens) + 16,
                        kvcache_block_size=page, num_kvcache_blocks=num_pages, max_num_batched_tokens=max(args.prefill_tokens, max_batch))
     runner, cache = engine.runner, engine.runner.cache
     for g in cache.groups:                      # random cache contents: the decode step's work does not depend on them

@@ -16,12 +16,21 @@
 // 128 keys) units; block c takes units [c * per, (c + 1) * per): a balanced share whatever the
 // batch size and the context lengths are.  A block's share is a few SEGMENTS, runs of tiles of
 // one (sequence, kv head) pair.  A segment that is a whole pair writes the output; otherwise
-// its unnormalised output, maximum and sum go to scratch slot (pair + block) and
-// attention_decode_merge_kernel adds a pair's slots in block order.
+// its unnormalised output, maximum and sum go to scratch slot (pair + block), and the warp that
+// arrives last at the pair's counter adds the pair's slots in block order and writes the output
+// (the counters live in a device array of this library and return to zero with every launch, so
+// launches that may overlap on the device must not share it: one stream).
 // Roles: warps 0-3 softmax and epilogue; warp 4 allocates tensor memory and issues the MMAs;
-// warp 5 brings K tiles (and the segments' queries), warp 6 V tiles, by TMA boxes of one page x
-// 64 columns straight from the paged cache (no cluster multicast), three tiles ahead and across
-// segment borders, so the memory pipe stays full from the first tile of a block to its last.
+// warp 5 brings K tiles, warp 6 V tiles, by TMA boxes of one page x 64 columns straight from
+// the paged cache (no cluster multicast), three tiles ahead and across segment borders, so the
+// memory pipe stays full from the first tile of a block to its last; warp 7 brings the
+// segments' queries.
+// Programmatic dependent launch: positions, q_start and the block table are read, and every key
+// tile but a pair's last (the one the step's new token lies in) is requested, BEFORE the wait
+// for the kernels ahead in the stream, so the cache already streams in while those finish.
+// The three arrays must therefore have been written before any kernel that can still be
+// running when this one starts (the engine copies them at the start of the step); the queries
+// and the new token's page are read after the wait.
 // Every wait on an mbarrier is bounded; a wait that runs out raises the block's abort flag,
 // which ends all roles, and the status word reports it.
 //
@@ -46,7 +55,8 @@ constexpr int NCOLS = 16;            // UMMA N: the heads of one key/value head,
 constexpr int STAGES = 3;            // K and V tiles in flight
 constexpr int QSLOTS = 4;            // queries of segments in flight
 constexpr int MAX_SEQS = 1024;
-constexpr int NUM_THREADS = 224;
+constexpr int NUM_THREADS = 256;
+constexpr int MAX_PAIRS = 65536;     // (sequence, kv head) pairs of one launch
 constexpr int HALF_BYTES = TILE * 128;        // 128 rows of 64 elements
 constexpr int STAGE_BYTES = 2 * HALF_BYTES;   // a K or V tile: two halves of head_dim
 constexpr int QP_BYTES = 2 * NCOLS * 128;     // Q^T or P^T: 16 rows, two halves of 64 elements
@@ -58,7 +68,8 @@ constexpr int V_OFF = K_OFF + STAGES * STAGE_BYTES;
 constexpr int Q_OFF = V_OFF + STAGES * STAGE_BYTES;
 constexpr int P_OFF = Q_OFF + QSLOTS * QP_BYTES;
 constexpr int PREFIX_OFF = P_OFF + 2 * QP_BYTES;                 // int[MAX_SEQS + 1]
-constexpr int RED_OFF = PREFIX_OFF + (MAX_SEQS + 4) * 4;         // float[2][4][16] maxima, float[4][16] sums
+constexpr int POS_OFF = PREFIX_OFF + (MAX_SEQS + 4) * 4;         // int[MAX_SEQS]: every sequence's position (-1: skipped)
+constexpr int RED_OFF = POS_OFF + MAX_SEQS * 4;                  // float[2][4][16] maxima, float[4][16] sums
 constexpr int BAR_OFF = RED_OFF + (2 * 4 * NCOLS + 4 * NCOLS) * 4;
 constexpr int NUM_BARS = 4 * STAGES + 3 * 2 + 2 * QSLOTS + 2 + 1;
 constexpr int SMEM_TOTAL = BAR_OFF + NUM_BARS * 8 + 32 + 1024;   // then slack to align the base to 1024
@@ -119,15 +130,25 @@ __device__ __forceinline__ bool seg_next(Seg& g, const int* prefix, int S, int n
 }
 
 // the keys a sequence's token sees: [lo, pos]; tiles of 128 keys at absolute positions
-__device__ __forceinline__ void key_range(const Params& p, int s, int& tok, int& pos, int& lo)
+__device__ __forceinline__ void key_range(const Params& p, const int* pos_s, int s, int& pos, int& lo)
 {
-    tok = p.q_start[s];
-    pos = p.positions[tok];
-    if (pos >= p.max_keys) pos = -1;   // beyond the block table: the sequence is skipped (and reported)
+    pos = pos_s[s];
     lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
 }
 
 __device__ __forceinline__ int tiles_of(int pos, int lo) { return pos >= 0 ? pos / TILE - lo / TILE + 1 : 0; }
+
+// -DSPY_TIMELINE: every block stamps the global timer at a few points of its life into a device
+// array that spy_attention_decode_timeline copies out (a debugging aid; off in normal builds).
+#ifdef SPY_TIMELINE
+__device__ unsigned long long g_timeline[256][16];
+#define STAMP(i) (g_timeline[blockIdx.x & 255][i] = global_timer())
+#else
+#define STAMP(i) ((void)0)
+#endif
+
+// arrivals of the warps that hold a part of a pair's result; the last one merges and resets it
+__device__ int g_pair_arrivals[MAX_PAIRS];
 
 // floats map to integers of the same order (and back: the map is its own inverse)
 __device__ __forceinline__ int ordered(float f)
@@ -144,6 +165,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     int* prefix = reinterpret_cast<int*>(smem + PREFIX_OFF);
+    int* pos_s = reinterpret_cast<int*>(smem + POS_OFF);
     float* red = reinterpret_cast<float*>(smem + RED_OFF);            // [2][4][NCOLS]
     float* lred = red + 2 * 4 * NCOLS;                                // [4][NCOLS]
     uint64_t* bar_kfull = reinterpret_cast<uint64_t*>(smem + BAR_OFF);   // [STAGES] K tile landed (TMA bytes)
@@ -163,6 +185,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
     if (tid == 0) {
+        STAMP(0);
         for (int i = 0; i < STAGES; ++i) {
             mbar_init(bar_kfull + i, 1);
             mbar_init(bar_kfree + i, 1);
@@ -184,19 +207,20 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 4) tmem_alloc(tmem_slot, TMEM_COLS);
-    // Value rows that no copy fills (pages outside a sequence's keys) meet probabilities of zero and
-    // must be finite; rows of Q^T beyond the G heads must be too.  Stale rows later hold real values.
-    for (int i = tid; i < (STAGES * STAGE_BYTES + QSLOTS * QP_BYTES) / 16; i += NUM_THREADS)
-        reinterpret_cast<uint4*>(smem + V_OFF)[i] = make_uint4(0, 0, 0, 0);
+    // rows of Q^T beyond the G heads are never copied: keep them zero (their columns of S^T and O^T are not used)
+    for (int i = tid; i < QSLOTS * QP_BYTES / 16; i += NUM_THREADS) reinterpret_cast<uint4*>(smem + Q_OFF)[i] = make_uint4(0, 0, 0, 0);
     fence_async_proxy();
-    pdl_wait();   // everything below reads what earlier kernels wrote
 
     // ---- the batch's units: tiles of every sequence, prefix sums, this block's share
     for (int s = tid; s < p.S; s += NUM_THREADS) {
-        int tok, pos, lo;
-        key_range(p, s, tok, pos, lo);
-        if (pos < 0 && blockIdx.x == 0) report_status(p.status, SPY_STATUS_BAD_POSITION, tok);
-        prefix[s + 1] = tiles_of(pos, lo);
+        const int tok = p.q_start[s];
+        int pos = p.positions[tok];
+        if (pos < 0 || pos >= p.max_keys) {   // outside the block table: the sequence is skipped and reported
+            pos = -1;
+            if (blockIdx.x == 0) report_status(p.status, SPY_STATUS_BAD_POSITION, tok);
+        }
+        pos_s[s] = pos;
+        prefix[s + 1] = tiles_of(pos, p.window > 0 ? max(0, pos - p.window + 1) : 0);
     }
     __syncthreads();
     if (warp == 0) {
@@ -219,6 +243,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
     fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_o = tmem_base + 2 * NCOLS;
+    if (tid == 0) STAMP(1);
     const int units = p.nkv * prefix[p.S];
     const int per = (units + (int)gridDim.x - 1) / (int)gridDim.x;
     const int u0 = min(units, (int)blockIdx.x * per), u1 = min(units, u0 + per);
@@ -231,8 +256,9 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
         bool more = seg_first(g, prefix, p.S, p.nkv, u0, u1), alive = true;
         int gt = 0, seg = 0;   // tiles and segments this block has begun
         while (more && alive) {
-            int tok, pos, lo;
-            key_range(p, g.s, tok, pos, lo);
+            int pos, lo;
+            key_range(p, pos_s, g.s, pos, lo);
+            const int tok = p.q_start[g.s];
             const int tile_first = lo / TILE;
             float m_used[GN], l[GN];   // the maximum the probabilities are taken against (equal in all threads); this thread's share of the sum
 #pragma unroll
@@ -244,6 +270,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
                 const int st = gt & 1;
                 const uint32_t ph = (uint32_t)(gt >> 1) & 1;
                 if (!(alive = mbar_wait(bar_s + st, ph, abort_flag))) break;
+                if (tid == 0 && gt == 0) STAMP(5);
                 fence_after_sync();
                 uint32_t r[GN];
                 tmem_load<GN>(tmem_base + st * NCOLS + lane_addr, r);
@@ -306,7 +333,9 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
             }
             if (!alive) break;
             // ---- the segment's result: O^T / sum, or the partial result of this run of tiles
+            if (tid == 0) STAMP(6);
             if (!(alive = mbar_wait(bar_o + ((gt - 1) & 1), (uint32_t)((gt - 1) >> 1) & 1, abort_flag))) break;
+            if (tid == 0) STAMP(7);
             fence_after_sync();
             uint32_t o[GN];
             tmem_load<GN>(tmem_o + lane_addr, o);
@@ -320,21 +349,94 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
             if (lane == 0) mbar_arrive(bar_lred);
             if (!(alive = mbar_wait(bar_lred, (uint32_t)seg & 1, abort_flag))) break;
             const bool direct = g.t0 == 0 && g.t_end == g.tiles;
-            const size_t slot = (size_t)(g.s * p.nkv + g.kvh) + blockIdx.x;
+            const int pair = g.s * p.nkv + g.kvh;
+            const size_t slot = (size_t)pair + blockIdx.x;
+            float sums[GN];
 #pragma unroll
-            for (int n = 0; n < GN; ++n) {
-                if (n >= p.G) break;
-                const float sum = (lred[n] + lred[NCOLS + n]) + (lred[2 * NCOLS + n] + lred[3 * NCOLS + n]);
-                if (direct) {
-                    if (tid < HD) p.out[((size_t)tok * p.nh + g.kvh * p.G + n) * HD + tid] = __float2bfloat16_rn(sum > 0.f ? __uint_as_float(o[n]) / sum : 0.f);
-                } else {
+            for (int n = 0; n < GN; ++n) sums[n] = (lred[n] + lred[NCOLS + n]) + (lred[2 * NCOLS + n] + lred[3 * NCOLS + n]);
+            if (direct) {
+#pragma unroll
+                for (int n = 0; n < GN; ++n)
+                    if (n < p.G && tid < HD)
+                        p.out[((size_t)tok * p.nh + g.kvh * p.G + n) * HD + tid] = __float2bfloat16_rn(sums[n] > 0.f ? __uint_as_float(o[n]) / sums[n] : 0.f);
+            } else {
+#pragma unroll
+                for (int n = 0; n < GN; ++n) {
+                    if (n >= p.G) break;
                     if (tid < HD) p.part_o[(slot * p.G + n) * HD + tid] = __uint_as_float(o[n]);
                     if (tid == n) {
                         p.part_ml[(slot * p.G + n) * 2] = m_used[n];
-                        p.part_ml[(slot * p.G + n) * 2 + 1] = sum;
+                        p.part_ml[(slot * p.G + n) * 2 + 1] = sums[n];
+                    }
+                }
+                // the pair's blocks: every warp of each arrives once; the last warp to arrive merges
+                const int off = p.nkv * prefix[g.s] + g.kvh * g.tiles;
+                const int c_first = off / per, c_last = (off + g.tiles - 1) / per;
+                __threadfence();
+                __syncwarp();
+                if (tid == 0) STAMP(8);
+                int last = 0;
+                if (lane == 0) {
+                    last = atomicAdd(&g_pair_arrivals[pair], 1) == 4 * (c_last - c_first + 1) - 1;
+                    if (last) g_pair_arrivals[pair] = 0;
+                }
+                last = __shfl_sync(0xffffffffu, last, 0);
+                if (last && lane == 0) STAMP(11);
+                if (last) {
+                    // this lane: 4 consecutive columns (head_dim 128) or 2 (head_dim 64) of every head; the
+                    // loads of four slots are in flight together
+                    __threadfence();
+                    constexpr int CPL = HD / 32;
+                    const float* ml0 = p.part_ml + (size_t)pair * p.G * 2;
+                    const float* o0 = p.part_o + (size_t)pair * p.G * HD + lane * CPL;
+                    float M[GN], L[GN], acc[GN][CPL];
+#pragma unroll
+                    for (int n = 0; n < GN; ++n) {
+                        float mx = -INFINITY;
+                        if (n < p.G)
+                            for (int c = c_first + lane; c <= c_last; c += 32) mx = fmaxf(mx, __ldcg(ml0 + ((size_t)c * p.G + n) * 2));
+                        M[n] = warp_max(mx);
+                        L[n] = 0.f;
+#pragma unroll
+                        for (int i = 0; i < CPL; ++i) acc[n][i] = 0.f;
+                    }
+                    if (lane == 0) STAMP(12);
+#pragma unroll 4
+                    for (int c = c_first; c <= c_last; ++c) {
+#pragma unroll
+                        for (int n = 0; n < GN; ++n) {
+                            if (n < p.G) {
+                                const size_t sl = (size_t)c * p.G + n;
+                                const float2 ml = __ldcg(reinterpret_cast<const float2*>(ml0 + sl * 2));
+                                float part[CPL];
+                                if constexpr (CPL == 4) {
+                                    const float4 v = __ldcg(reinterpret_cast<const float4*>(o0 + sl * HD));
+                                    part[0] = v.x; part[1] = v.y; part[2] = v.z; part[3] = v.w;
+                                } else {
+                                    const float2 v = __ldcg(reinterpret_cast<const float2*>(o0 + sl * HD));
+                                    part[0] = v.x; part[1] = v.y;
+                                }
+                                const float f = ml.x == -INFINITY ? 0.f : exp2f(ml.x - M[n]);
+                                L[n] += ml.y * f;
+#pragma unroll
+                                for (int i = 0; i < CPL; ++i) acc[n][i] += part[i] * f;
+                            }
+                        }
+                    }
+                    if (lane == 0) STAMP(13);
+#pragma unroll
+                    for (int n = 0; n < GN; ++n) {
+                        if (n < p.G) {
+                            bf16* dst = p.out + ((size_t)tok * p.nh + g.kvh * p.G + n) * HD + lane * CPL;
+                            const float inv = L[n] > 0.f ? 1.f / L[n] : 0.f;
+#pragma unroll
+                            for (int i = 0; i < CPL; i += 2)
+                                *reinterpret_cast<__nv_bfloat162*>(dst + i) = __floats2bfloat162_rn(acc[n][i] * inv, acc[n][i + 1] * inv);
+                        }
                     }
                 }
             }
+            if (tid == 0) STAMP(9);
             ++seg;
             more = seg_next(g, prefix, p.S, p.nkv);
         }
@@ -351,6 +453,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
                 if (gq.t == gq.t0) ok = mbar_wait(bar_qfull + slot, (uint32_t)(segq / QSLOTS) & 1, abort_flag);
                 ok = ok && mbar_wait(bar_kfull + stage, (uint32_t)(iq / STAGES) & 1, abort_flag);
                 if (!ok) return;
+                if (iq == 0) STAMP(4);
                 fence_after_sync();
                 const uint32_t kb = k_s + stage * STAGE_BYTES, qb = q_s + slot * QP_BYTES;
 #pragma unroll
@@ -384,8 +487,26 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
                 if (moreq) issue_qk();   // S^T's stage st is free: P^T of this tile was made from it
             }
         }
+    } else if (warp == 7) {
+        // ---------------------------------------------------------------- TMA: the segments' queries, which the kernel ahead wrote
+        if (lane == 0 && u0 < u1) {
+            pdl_wait();
+            STAMP(3);
+            Seg g;
+            bool more = seg_first(g, prefix, p.S, p.nkv, u0, u1);
+            for (int seg = 0; more; ++seg) {
+                const int slot = seg % QSLOTS;
+                const int tok = p.q_start[g.s];
+                if (seg >= QSLOTS && !mbar_wait(bar_qfree + slot, (uint32_t)(seg / QSLOTS - 1) & 1, abort_flag)) break;
+                mbar_expect_tx(bar_qfull + slot, (uint32_t)p.G * HD * 2);
+#pragma unroll
+                for (int h = 0; h < HD / 64; ++h)
+                    tma_load_3d(q_s + slot * QP_BYTES + h * (NCOLS * 128), &q_map, h * 64, g.kvh * p.G, tok, bar_qfull + slot);
+                more = seg_next(g, prefix, p.S, p.nkv);
+            }
+        }
     } else {
-        // ---------------------------------------------------------------- TMA: K tiles and queries (warp 5), V tiles (warp 6)
+        // ---------------------------------------------------------------- TMA: K tiles (warp 5), V tiles (warp 6)
         // One box per page and 64-column half, one lane each (a single thread issuing them one after
         // the other is the slower way: small boxes are bound by issue latency, not by bandwidth).
         const int kv = warp - 5;
@@ -397,49 +518,44 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
         const uint32_t box_bytes = (uint32_t)p.page_size * 128;              // page_size rows of 64 elements
         const int my_page = lane / (HD / 64), my_half = lane % (HD / 64);
         Seg g;
-        bool more = seg_first(g, prefix, p.S, p.nkv, u0, u1), ok = true;
-        int i = 0, seg = 0;
+        bool more = seg_first(g, prefix, p.S, p.nkv, u0, u1), ok = true, waited = false;
+        int i = 0;
+        if (lane == 0 && kv == 0) STAMP(15);
         while (more && ok) {
-            int tok, pos, lo;
-            key_range(p, g.s, tok, pos, lo);
+            int pos, lo;
+            key_range(p, pos_s, g.s, pos, lo);
             const int tile_first = lo / TILE;
             const int* bt = p.block_table + (size_t)g.s * p.table_width;
-            if (kv == 0) {
-                if (lane == 0) {
-                    const int slot = seg % QSLOTS;
-                    if (seg >= QSLOTS) ok = mbar_wait(bar_qfree + slot, (uint32_t)(seg / QSLOTS - 1) & 1, abort_flag);
-                    if (ok) {
-                        mbar_expect_tx(bar_qfull + slot, (uint32_t)p.G * HD * 2);
-#pragma unroll
-                        for (int h = 0; h < HD / 64; ++h)
-                            tma_load_3d(q_s + slot * QP_BYTES + h * (NCOLS * 128), &q_map, h * 64, g.kvh * p.G, tok, bar_qfull + slot);
-                    }
-                }
-                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-                if (!ok) break;
-            }
             for (; g.t < g.t_end; ++g.t, ++i) {
                 const int stage = i % STAGES;
-                // this lane's page of the tile (read before the wait for the stage, which hides the lookup)
+                if (!waited && g.t == g.tiles - 1) {   // the pair's last tile holds the token the kernel ahead has just stored
+                    pdl_wait();
+                    waited = true;
+                }
+                // This lane's page of the tile (read before the wait for the stage, which hides the lookup).
+                // Every box of the tile is copied, so that no row of the stage is ever stale: pages that hold
+                // none of the sequence's keys, or that the table does not name, are replaced by page 0, whose
+                // rows are finite like any page's and meet probabilities of zero.
                 const int lp = (tile_first + g.t) * pages_per_tile + my_page;
-                const bool in_range = lane < boxes && lp * p.page_size <= pos && (lp + 1) * p.page_size > lo;
-                const int page = (in_range && lp < p.table_width) ? bt[lp] : -1;
+                const bool in_range = lp * p.page_size <= pos && (lp + 1) * p.page_size > lo;
+                int page = (lane < boxes && in_range && lp < p.table_width) ? bt[lp] : 0;
                 if (lane == 0 && lp + 4 * pages_per_tile < p.table_width) asm volatile("prefetch.global.L2 [%0];" ::"l"(bt + lp + 4 * pages_per_tile));
-                const bool valid = in_range && page >= 0 && page < p.num_pages;
-                if (in_range && !valid && kv == 0) report_status(p.status, SPY_STATUS_BAD_PAGE, tok);
-                const int count = __popc(__ballot_sync(0xffffffffu, valid));
+                if (page < 0 || page >= p.num_pages) {
+                    if (kv == 0) report_status(p.status, SPY_STATUS_BAD_PAGE, p.q_start[g.s]);
+                    page = 0;
+                }
                 if (lane == 0) {
                     if (i >= STAGES) ok = mbar_wait(bar_free + stage, (uint32_t)(i / STAGES - 1) & 1, abort_flag);
-                    if (ok) mbar_expect_tx(bar_full + stage, (uint32_t)count * box_bytes);
+                    if (ok) mbar_expect_tx(bar_full + stage, (uint32_t)boxes * box_bytes);
                 }
                 ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
                 if (!ok) break;
-                if (valid) {
+                if (i == 0 && lane == 0 && kv == 0) STAMP(2);
+                if (lane < boxes) {
                     const int y = ((page * 2 + kv) * p.nkv + g.kvh) * p.page_size;
                     tma_load_2d(ring + stage * STAGE_BYTES + my_half * HALF_BYTES + my_page * p.page_size * 128, &page_map, my_half * 64, y, bar_full + stage);
                 }
             }
-            ++seg;
             if (ok) more = seg_next(g, prefix, p.S, p.nkv);
         }
     }
@@ -458,56 +574,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
         fence_after_sync();
         tmem_dealloc(tmem_base, TMEM_COLS);
     }
-}
-
-// One block per (sequence, head); does nothing when one block of the first kernel had the pair whole.
-template <int HD>
-__global__ void attention_decode_merge_kernel(const Params p)
-{
-    __shared__ int s_sum[2][HD / 32];
-    pdl_enter();
-    const int seq = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
-    const int kvh = head / p.G, n = head - kvh * p.G;
-    int before = 0, total = 0;
-    for (int s = d; s < p.S; s += HD) {
-        int tok, pos, lo;
-        key_range(p, s, tok, pos, lo);
-        const int t = tiles_of(pos, lo);
-        total += t;
-        if (s < seq) before += t;
-    }
-    before = __reduce_add_sync(0xffffffffu, before);
-    total = __reduce_add_sync(0xffffffffu, total);
-    if ((d & 31) == 0) {
-        s_sum[0][d >> 5] = before;
-        s_sum[1][d >> 5] = total;
-    }
-    __syncthreads();
-    before = total = 0;
-    for (int w = 0; w < HD / 32; ++w) {
-        before += s_sum[0][w];
-        total += s_sum[1][w];
-    }
-    int tok, pos, lo;
-    key_range(p, seq, tok, pos, lo);
-    const int tiles = tiles_of(pos, lo);
-    if (tiles == 0) return;
-    const int per = (p.nkv * total + p.blocks - 1) / p.blocks;
-    const int off = p.nkv * before + kvh * tiles;
-    const int c_first = off / per, c_last = (off + tiles - 1) / per;
-    if (c_first == c_last) return;
-    const size_t base = (size_t)(seq * p.nkv + kvh);
-    float M = -INFINITY;
-    for (int c = c_first; c <= c_last; ++c) M = fmaxf(M, p.part_ml[((base + c) * p.G + n) * 2]);
-    float L = 0.f, acc = 0.f;
-    for (int c = c_first; c <= c_last; ++c) {
-        const size_t slot = (base + c) * p.G + n;
-        const float mz = p.part_ml[slot * 2];
-        const float f = mz == -INFINITY ? 0.f : exp2f(mz - M);
-        L += p.part_ml[slot * 2 + 1] * f;
-        acc += p.part_o[slot * HD + d] * f;
-    }
-    p.out[((size_t)tok * p.nh + head) * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+    if (tid == 0) STAMP(10);
 }
 
 int sm_count()
@@ -530,12 +597,20 @@ int launch(const CUtensorMap& page_map, const CUtensorMap& q_map, const Params& 
     }
     spy_launch(attention_decode_kernel<HD, GN>, dim3(p.blocks), dim3(NUM_THREADS), (size_t)SMEM_TOTAL, stream, page_map, q_map, p);
     SPY_CHECK_LAUNCH("attention_decode");
-    spy_launch(attention_decode_merge_kernel<HD>, dim3(p.S, p.nh), dim3(HD), 0, stream, p);
-    SPY_CHECK_LAUNCH("attention_decode (merge)");
     return 0;
 }
 
 }  // namespace
+
+#ifdef SPY_TIMELINE
+// Copies the stamps of the last launch out: [256 blocks][16 points] of nanoseconds.
+extern "C" int spy_attention_decode_timeline(unsigned long long* host)
+{
+    SPY_CUDA(cudaDeviceSynchronize());
+    SPY_CUDA(cudaMemcpyFromSymbol(host, g_timeline, sizeof(g_timeline)));
+    return 0;
+}
+#endif
 
 // Floats of scratch a batch of `seqs` decoding sequences needs: one slot per (sequence, kv head) pair and per block.
 extern "C" long long spy_attention_decode_scratch_floats(int seqs, int nh, int nkv, int hd)
@@ -555,7 +630,8 @@ extern "C" int spy_attention_decode(const void* q, long long q_row_stride, void*
     const int G = nh / nkv;
     if (G > NCOLS) SPY_FAIL("attention_decode: %d query heads per key/value head exceed %d", G, NCOLS);
     if (hd != 64 && hd != 128) SPY_FAIL("attention_decode: head_dim %d is not 64 or 128", hd);
-    if (seqs > MAX_SEQS) SPY_FAIL("attention_decode: %d sequences exceed %d", seqs, MAX_SEQS);
+    if (seqs > MAX_SEQS || (long long)seqs * nkv > MAX_PAIRS)
+        SPY_FAIL("attention_decode: %d sequences of %d key/value heads exceed %d sequences or %d pairs", seqs, nkv, MAX_SEQS, MAX_PAIRS);
     if (q_row_stride % 8 != 0 || q_row_stride < (long long)nh * hd || (reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(pages) & 15))
         SPY_FAIL("attention_decode: queries and pages must be 16-byte aligned with rows a multiple of 8 elements");
     if (num_pages <= 0 || table_width <= 0) SPY_FAIL("attention_decode: num_pages and table_width must be positive");

@@ -124,8 +124,10 @@ __global__ void qk_rope_store_kernel(const TS* src, int src_splits, long long sr
 // rotated (or no rotation), one plain input array.  Lane l of the warp that owns a (token, head)
 // holds elements 4l .. 4l + 3 (one 8-byte access); the rotation partner of element j < 64 is
 // element j + 64, which lane l ^ 16 holds, so a shuffle replaces the staging in shared memory.
-template <typename TW>
-__global__ void __launch_bounds__(256) qk_rope_store_hd128_kernel(const bf16* src, bf16* q_out, long long q_out_stride, int tokens, int nh, int nkv,
+// The input is one bfloat16 array or a stack of float split-K partial products, summed in order.
+template <typename TS, typename TW>
+__global__ void __launch_bounds__(256) qk_rope_store_hd128_kernel(const TS* src, int src_splits, long long src_split_stride, bf16* q_out,
+                                                                  long long q_out_stride, int tokens, int nh, int nkv,
                                                                   const TW* __restrict__ q_w, const TW* __restrict__ k_w, float eps,
                                                                   const float2* __restrict__ cos_sin, int table_rows,
                                                                   const int* __restrict__ positions, const int* __restrict__ seq_of_token,
@@ -140,8 +142,22 @@ __global__ void __launch_bounds__(256) qk_rope_store_hd128_kernel(const bf16* sr
     if (item >= (long long)tokens * heads) return;
     const int t = (int)(item / heads), head = (int)(item % heads);
     const int kind = head < nh ? 0 : (head < nh + nkv ? 1 : 2);  // q, k, v
-    const bf16* in = src + (size_t)t * (nh + 2 * nkv) * HD + (size_t)head * HD + 4 * lane;
+    const TS* in = src + (size_t)t * (nh + 2 * nkv) * HD + (size_t)head * HD + 4 * lane;
     const int pos = positions[t];
+    float v[4];
+    if constexpr (sizeof(TS) == 2) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(in);
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+        v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
+    } else {
+        const float4 first = *reinterpret_cast<const float4*>(in);
+        v[0] = first.x; v[1] = first.y; v[2] = first.z; v[3] = first.w;
+#pragma unroll 8
+        for (int s = 1; s < src_splits; ++s) {
+            const float4 part = *reinterpret_cast<const float4*>(in + (size_t)s * src_split_stride);
+            v[0] += part.x; v[1] += part.y; v[2] += part.z; v[3] += part.w;
+        }
+    }
     bf16* dst;
     if (kind == 0) {
         dst = q_out + (size_t)t * q_out_stride + (size_t)head * HD + 4 * lane;
@@ -156,22 +172,15 @@ __global__ void __launch_bounds__(256) qk_rope_store_hd128_kernel(const bf16* sr
         const int kv_head = kind == 1 ? head - nh : head - nh - nkv;
         dst = pages + ((((size_t)page * 2 + (kind - 1)) * nkv + kv_head) * page_size + pos % page_size) * HD + 4 * lane;
     }
-    const uint2 raw = *reinterpret_cast<const uint2*>(in);
-    if (kind == 2) {
-        *reinterpret_cast<uint2*>(dst) = raw;
-        return;
-    }
-    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
-    float v[4] = {__low2float(a), __high2float(a), __low2float(b), __high2float(b)};
     const TW* w = kind == 0 ? q_w : k_w;
-    if (w != nullptr) {
+    if (kind != 2 && w != nullptr) {
         float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
         ss = warp_sum(ss);
         const float inv = 1.0f / sqrtf(ss / (float)HD + eps);
 #pragma unroll
         for (int i = 0; i < 4; ++i) v[i] = (inv * v[i]) * to_f32(w[4 * lane + i]);
     }
-    if (cos_sin != nullptr) {
+    if (kind != 2 && cos_sin != nullptr) {
         if (pos < 0 || pos >= table_rows) {
             if (lane == 0) report_status(status, SPY_STATUS_BAD_POSITION, t);
             return;
@@ -232,7 +241,9 @@ extern "C" int spy_qk_rope_store(const void* src, int src_dtype, int src_splits,
     if (cos_sin && (rot_half <= 0 || 2 * rot_half > hd)) SPY_FAIL("qk_rope_store: rotary width %d does not fit head_dim %d", 2 * rot_half, hd);
     if (store && (page_size <= 0 || num_pages <= 0 || table_width <= 0 || !pages || !block_table))
         SPY_FAIL("qk_rope_store: storing needs pages, a block table and positive page_size/num_pages/table_width");
-    if (src_dtype == SPY_BF16 && q_dtype == SPY_BF16 && (!store || cache_dtype == SPY_BF16) && src_splits == 1 && hd == 128 &&
+    const bool plain_bf16 = src_dtype == SPY_BF16 && src_splits == 1;
+    const bool float_stack = src_dtype == SPY_F32 && src_split_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0 && q_out != src;
+    if ((plain_bf16 || float_stack) && q_dtype == SPY_BF16 && (!store || cache_dtype == SPY_BF16) && hd == 128 &&
         (cos_sin == nullptr || rot_half == 64) && q_out_stride % 4 == 0 &&
         ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(pages)) & 7) == 0) {
         const int heads = store ? nh + 2 * nkv : nh;
@@ -240,9 +251,15 @@ extern "C" int spy_qk_rope_store(const void* src, int src_dtype, int src_splits,
         const long long blocks = (items + 7) / 8;
         if (blocks > 0x7fffffffLL) SPY_FAIL("qk_rope_store: %lld work items exceed the grid limit", items);
         SPY_DISPATCH_DTYPE(w_dtype, TW, {
-            spy_launch(qk_rope_store_hd128_kernel<TW>, dim3((int)blocks), dim3(256), 0, stream, (const bf16*)src, (bf16*)q_out, q_out_stride,
-                       tokens, nh, nkv, (const TW*)q_w, (const TW*)k_w, eps, (const float2*)cos_sin, table_rows, positions, seq_of_token,
-                       block_table, table_width, (bf16*)pages, page_size, num_pages, store, status);
+            if (plain_bf16)
+                spy_launch(qk_rope_store_hd128_kernel<bf16, TW>, dim3((int)blocks), dim3(256), 0, stream, (const bf16*)src, 1, 0LL, (bf16*)q_out,
+                           q_out_stride, tokens, nh, nkv, (const TW*)q_w, (const TW*)k_w, eps, (const float2*)cos_sin, table_rows, positions,
+                           seq_of_token, block_table, table_width, (bf16*)pages, page_size, num_pages, store, status);
+            else
+                spy_launch(qk_rope_store_hd128_kernel<float, TW>, dim3((int)blocks), dim3(256), 0, stream, (const float*)src, src_splits,
+                           src_split_stride, (bf16*)q_out, q_out_stride, tokens, nh, nkv, (const TW*)q_w, (const TW*)k_w, eps,
+                           (const float2*)cos_sin, table_rows, positions, seq_of_token, block_table, table_width, (bf16*)pages, page_size,
+                           num_pages, store, status);
         })
         SPY_CHECK_LAUNCH("qk_rope_store (head_dim 128)");
         return 0;

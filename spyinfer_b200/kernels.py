@@ -323,6 +323,7 @@ def attention_tc(q: torch.Tensor, num_heads: int, head_dim: int, out: torch.Tens
 
 
 ATTENTION_DECODE_MAX_SEQS = 1024
+ATTENTION_DECODE_MAX_PAIRS = 65536   # sequences x key/value heads
 
 
 def attention_decode_takes(num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, dtype: torch.dtype) -> bool:
@@ -337,7 +338,10 @@ def attention_decode(q: torch.Tensor, num_heads: int, head_dim: int, out: torch.
                      status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of a decoding batch (one token per sequence) over its pages: one persistent block
     per SM, keys in the rows of tcgen05 tiles, pages brought in by TMA, the batch's tiles shared out
-    evenly over the blocks and merged through scratch memory.  At most 1024 sequences."""
+    evenly over the blocks and merged through scratch memory.  At most 1024 sequences.  ``positions``,
+    ``q_start`` and ``block_table`` are read while kernels launched earlier may still be running: they
+    must be complete before those start (the engine copies them at the start of a step).  Launches
+    on different streams must not overlap (they share the counters of the merge)."""
     _check(q, "attention queries", torch.bfloat16, 2)
     _check(out, "attention output", torch.bfloat16, 2)
     _check(pages, "cache pages", torch.bfloat16, 5)

@@ -118,7 +118,7 @@ class Attention(Mixer):
         if not self.fast:
             kernels.attention_generic(q, self.nh, self.hd, out, cache.pages, cache.block_table, batch.positions, batch.seq_of_token,
                                       self.scale, window=self.window, status=batch.status)
-        elif decoding and batch.num_seqs <= kernels.ATTENTION_DECODE_MAX_SEQS and kernels.attention_decode_takes(
+        elif decoding and batch.num_seqs <= kernels.ATTENTION_DECODE_MAX_SEQS and batch.num_seqs * self.nkv <= kernels.ATTENTION_DECODE_MAX_PAIRS and kernels.attention_decode_takes(
                 self.nh, self.nkv, self.hd, cache.page_size, x.dtype):
             # memory-bound: one persistent block per SM, the batch's key tiles shared out evenly, pages by TMA
             kernels.attention_decode(q, self.nh, self.hd, out, cache.pages, cache.block_table, batch.positions, batch.q_start,
