@@ -228,7 +228,7 @@ def main() -> int:
         toks = torch.randint(0, vocab, (tokens,), generator=g).tolist()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         times = []
-        for i in range(3):                       # the first run is a warm-up
+        for i in range(6):                       # the first run is a warm-up; the median of the other five is reported
             torch.cuda.synchronize()
             e0.record()
             runner.step([StepEntry(f"p{i}", toks, [tokens - 1])])
@@ -236,7 +236,7 @@ def main() -> int:
             torch.cuda.synchronize()
             runner.finish(f"p{i}")
             times.append(e0.elapsed_time(e1))
-        best = min(times[1:])
+        best = sorted(times[1:])[len(times[1:]) // 2]
         runner.check_status()
         flops = 2.0 * tokens * layers * layer_params + 2.0 * V * H + layers * 4.0 * nh * hd * tokens * (tokens + 1) / 2
         return {"value": round(tokens / (best / 1e3), 1), "tokens": tokens, "ms": round(best, 3),

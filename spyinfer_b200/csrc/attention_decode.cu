@@ -186,6 +186,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
     if (tid == 0) {
         STAMP(0);
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&page_map) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&q_map) : "memory");
         for (int i = 0; i < STAGES; ++i) {
             mbar_init(bar_kfull + i, 1);
             mbar_init(bar_kfree + i, 1);
@@ -392,15 +394,12 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
                     float M[GN], L[GN], acc[GN][CPL];
 #pragma unroll
                     for (int n = 0; n < GN; ++n) {
-                        float mx = -INFINITY;
-                        if (n < p.G)
-                            for (int c = c_first + lane; c <= c_last; c += 32) mx = fmaxf(mx, __ldcg(ml0 + ((size_t)c * p.G + n) * 2));
-                        M[n] = warp_max(mx);
+                        M[n] = -INFINITY;
                         L[n] = 0.f;
 #pragma unroll
                         for (int i = 0; i < CPL; ++i) acc[n][i] = 0.f;
                     }
-                    if (lane == 0) STAMP(12);
+                    // one pass in block order; the running maximum rescales what has been added so far
 #pragma unroll 4
                     for (int c = c_first; c <= c_last; ++c) {
 #pragma unroll
@@ -416,10 +415,13 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
                                     const float2 v = __ldcg(reinterpret_cast<const float2*>(o0 + sl * HD));
                                     part[0] = v.x; part[1] = v.y;
                                 }
-                                const float f = ml.x == -INFINITY ? 0.f : exp2f(ml.x - M[n]);
-                                L[n] += ml.y * f;
+                                const float m_new = fmaxf(M[n], ml.x);
+                                const float keep = M[n] == -INFINITY ? 0.f : exp2f(M[n] - m_new);
+                                const float f = ml.x == -INFINITY ? 0.f : exp2f(ml.x - m_new);
+                                M[n] = m_new;
+                                L[n] = L[n] * keep + ml.y * f;
 #pragma unroll
-                                for (int i = 0; i < CPL; ++i) acc[n][i] += part[i] * f;
+                                for (int i = 0; i < CPL; ++i) acc[n][i] = acc[n][i] * keep + part[i] * f;
                             }
                         }
                     }

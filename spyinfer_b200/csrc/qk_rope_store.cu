@@ -125,7 +125,10 @@ __global__ void qk_rope_store_kernel(const TS* src, int src_splits, long long sr
 // holds elements 4l .. 4l + 3 (one 8-byte access); the rotation partner of element j < 64 is
 // element j + 64, which lane l ^ 16 holds, so a shuffle replaces the staging in shared memory.
 // The input is one bfloat16 array or a stack of float split-K partial products, summed in order.
-template <typename TS, typename TW>
+// A warp takes IPW consecutive (token, head) items and has the loads of all of them in flight
+// before it works on the first (prompt portions: many items, bound by memory latency); decoding
+// batches use IPW = 1 so that the few items spread over the SMs.
+template <typename TS, typename TW, int IPW>
 __global__ void __launch_bounds__(256) qk_rope_store_hd128_kernel(const TS* src, int src_splits, long long src_split_stride, bf16* q_out,
                                                                   long long q_out_stride, int tokens, int nh, int nkv,
                                                                   const TW* __restrict__ q_w, const TW* __restrict__ k_w, float eps,
@@ -138,68 +141,87 @@ __global__ void __launch_bounds__(256) qk_rope_store_hd128_kernel(const TS* src,
     pdl_enter();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads = store ? nh + 2 * nkv : nh;
-    const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
-    if (item >= (long long)tokens * heads) return;
-    const int t = (int)(item / heads), head = (int)(item % heads);
-    const int kind = head < nh ? 0 : (head < nh + nkv ? 1 : 2);  // q, k, v
-    const TS* in = src + (size_t)t * (nh + 2 * nkv) * HD + (size_t)head * HD + 4 * lane;
-    const int pos = positions[t];
-    float v[4];
-    if constexpr (sizeof(TS) == 2) {
-        const uint2 raw = *reinterpret_cast<const uint2*>(in);
-        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
-        v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
-    } else {
-        const float4 first = *reinterpret_cast<const float4*>(in);
-        v[0] = first.x; v[1] = first.y; v[2] = first.z; v[3] = first.w;
+    const long long items = (long long)tokens * heads;
+    const long long first = ((long long)blockIdx.x * (blockDim.x >> 5) + warp) * IPW;
+    float v[IPW][4];
+    float4 c01[IPW], c23[IPW];
+    bf16* dst[IPW];
+    int kind[IPW];
+    // ---- addresses and loads of all items
+#pragma unroll
+    for (int k = 0; k < IPW; ++k) {
+        const long long item = first + k;
+        dst[k] = nullptr;
+        kind[k] = 2;
+        if (item >= items) continue;
+        const int t = (int)(item / heads), head = (int)(item % heads);
+        kind[k] = head < nh ? 0 : (head < nh + nkv ? 1 : 2);  // q, k, v
+        const TS* in = src + (size_t)t * (nh + 2 * nkv) * HD + (size_t)head * HD + 4 * lane;
+        const int pos = positions[t];
+        if constexpr (sizeof(TS) == 2) {
+            const uint2 raw = *reinterpret_cast<const uint2*>(in);
+            const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+            v[k][0] = __low2float(a); v[k][1] = __high2float(a); v[k][2] = __low2float(b); v[k][3] = __high2float(b);
+        } else {
+            const float4 f = *reinterpret_cast<const float4*>(in);
+            v[k][0] = f.x; v[k][1] = f.y; v[k][2] = f.z; v[k][3] = f.w;
 #pragma unroll 8
-        for (int s = 1; s < src_splits; ++s) {
-            const float4 part = *reinterpret_cast<const float4*>(in + (size_t)s * src_split_stride);
-            v[0] += part.x; v[1] += part.y; v[2] += part.z; v[3] += part.w;
+            for (int s = 1; s < src_splits; ++s) {
+                const float4 part = *reinterpret_cast<const float4*>(in + (size_t)s * src_split_stride);
+                v[k][0] += part.x; v[k][1] += part.y; v[k][2] += part.z; v[k][3] += part.w;
+            }
+        }
+        if (kind[k] == 0) {
+            dst[k] = q_out + (size_t)t * q_out_stride + (size_t)head * HD + 4 * lane;
+        } else {
+            const int seq = seq_of_token[t];
+            const bool in_table = pos >= 0 && pos / page_size < table_width;
+            const int page = in_table ? block_table[(size_t)seq * table_width + pos / page_size] : -1;
+            if (page < 0 || page >= num_pages) {
+                if (lane == 0) report_status(status, SPY_STATUS_BAD_PAGE, t);
+                continue;
+            }
+            const int kv_head = kind[k] == 1 ? head - nh : head - nh - nkv;
+            dst[k] = pages + ((((size_t)page * 2 + (kind[k] - 1)) * nkv + kv_head) * page_size + pos % page_size) * HD + 4 * lane;
+        }
+        if (kind[k] != 2 && cos_sin != nullptr) {
+            if (pos < 0 || pos >= table_rows) {
+                if (lane == 0) report_status(status, SPY_STATUS_BAD_POSITION, t);
+                dst[k] = nullptr;
+                continue;
+            }
+            const float4* cs4 = reinterpret_cast<const float4*>(cos_sin + (size_t)pos * 64 + 4 * (lane & 15));
+            c01[k] = cs4[0];   // (cos, sin) of pairs j, j+1
+            c23[k] = cs4[1];   // and of pairs j+2, j+3
         }
     }
-    bf16* dst;
-    if (kind == 0) {
-        dst = q_out + (size_t)t * q_out_stride + (size_t)head * HD + 4 * lane;
-    } else {
-        const int seq = seq_of_token[t];
-        const bool in_table = pos >= 0 && pos / page_size < table_width;
-        const int page = in_table ? block_table[(size_t)seq * table_width + pos / page_size] : -1;
-        if (page < 0 || page >= num_pages) {
-            if (lane == 0) report_status(status, SPY_STATUS_BAD_PAGE, t);
-            return;
-        }
-        const int kv_head = kind == 1 ? head - nh : head - nh - nkv;
-        dst = pages + ((((size_t)page * 2 + (kind - 1)) * nkv + kv_head) * page_size + pos % page_size) * HD + 4 * lane;
-    }
-    const TW* w = kind == 0 ? q_w : k_w;
-    if (kind != 2 && w != nullptr) {
-        float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
-        ss = warp_sum(ss);
-        const float inv = 1.0f / sqrtf(ss / (float)HD + eps);
+    // ---- norm, rotation, store
 #pragma unroll
-        for (int i = 0; i < 4; ++i) v[i] = (inv * v[i]) * to_f32(w[4 * lane + i]);
-    }
-    if (kind != 2 && cos_sin != nullptr) {
-        if (pos < 0 || pos >= table_rows) {
-            if (lane == 0) report_status(status, SPY_STATUS_BAD_POSITION, t);
-            return;
-        }
-        const float4* cs4 = reinterpret_cast<const float4*>(cos_sin + (size_t)pos * 64 + 4 * (lane & 15));
-        const float4 c01 = cs4[0], c23 = cs4[1];   // (cos, sin) of pairs j, j+1 and j+2, j+3
-        const float cs_c[4] = {c01.x, c01.z, c23.x, c23.z}, cs_s[4] = {c01.y, c01.w, c23.y, c23.w};
+    for (int k = 0; k < IPW; ++k) {
+        if (dst[k] == nullptr) continue;   // uniform over the warp
+        const TW* w = kind[k] == 0 ? q_w : k_w;
+        if (kind[k] != 2 && w != nullptr) {
+            float ss = v[k][0] * v[k][0] + v[k][1] * v[k][1] + v[k][2] * v[k][2] + v[k][3] * v[k][3];
+            ss = warp_sum(ss);
+            const float inv = 1.0f / sqrtf(ss / (float)HD + eps);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float other = __shfl_xor_sync(0xffffffffu, v[i], 16);
-            // lanes 0..15 hold the low half (x_j), lanes 16..31 the high half (x_{j + 64})
-            v[i] = lane < 16 ? v[i] * cs_c[i] - other * cs_s[i] : other * cs_s[i] + v[i] * cs_c[i];
+            for (int i = 0; i < 4; ++i) v[k][i] = (inv * v[k][i]) * to_f32(w[4 * lane + i]);
         }
+        if (kind[k] != 2 && cos_sin != nullptr) {
+            const float cs_c[4] = {c01[k].x, c01[k].z, c23[k].x, c23[k].z}, cs_s[4] = {c01[k].y, c01[k].w, c23[k].y, c23[k].w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float other = __shfl_xor_sync(0xffffffffu, v[k][i], 16);
+                // lanes 0..15 hold the low half (x_j), lanes 16..31 the high half (x_{j + 64})
+                v[k][i] = lane < 16 ? v[k][i] * cs_c[i] - other * cs_s[i] : other * cs_s[i] + v[k][i] * cs_c[i];
+            }
+        }
+        __nv_bfloat162 o0 = __floats2bfloat162_rn(v[k][0], v[k][1]), o1 = __floats2bfloat162_rn(v[k][2], v[k][3]);
+        uint2 outv;
+        outv.x = *reinterpret_cast<uint32_t*>(&o0);
+        outv.y = *reinterpret_cast<uint32_t*>(&o1);
+        *reinterpret_cast<uint2*>(dst[k]) = outv;
     }
-    __nv_bfloat162 o0 = __floats2bfloat162_rn(v[0], v[1]), o1 = __floats2bfloat162_rn(v[2], v[3]);
-    uint2 outv;
-    outv.x = *reinterpret_cast<uint32_t*>(&o0);
-    outv.y = *reinterpret_cast<uint32_t*>(&o1);
-    *reinterpret_cast<uint2*>(dst) = outv;
 }
 
 template <typename TS, typename TQ, typename TC, typename TW>
@@ -248,19 +270,23 @@ extern "C" int spy_qk_rope_store(const void* src, int src_dtype, int src_splits,
         ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(pages)) & 7) == 0) {
         const int heads = store ? nh + 2 * nkv : nh;
         const long long items = (long long)tokens * heads;
-        const long long blocks = (items + 7) / 8;
+        const int ipw = items >= 8192 ? 4 : 1;
+        const long long blocks = (items + 8 * ipw - 1) / (8 * ipw);
         if (blocks > 0x7fffffffLL) SPY_FAIL("qk_rope_store: %lld work items exceed the grid limit", items);
+#define SPY_QK_HD128(TS_, IPW_, splits_, stride_)                                                                                         \
+    spy_launch(qk_rope_store_hd128_kernel<TS_, TW, IPW_>, dim3((int)blocks), dim3(256), 0, stream, (const TS_*)src, splits_, stride_,    \
+               (bf16*)q_out, q_out_stride, tokens, nh, nkv, (const TW*)q_w, (const TW*)k_w, eps, (const float2*)cos_sin, table_rows,     \
+               positions, seq_of_token, block_table, table_width, (bf16*)pages, page_size, num_pages, store, status)
         SPY_DISPATCH_DTYPE(w_dtype, TW, {
-            if (plain_bf16)
-                spy_launch(qk_rope_store_hd128_kernel<bf16, TW>, dim3((int)blocks), dim3(256), 0, stream, (const bf16*)src, 1, 0LL, (bf16*)q_out,
-                           q_out_stride, tokens, nh, nkv, (const TW*)q_w, (const TW*)k_w, eps, (const float2*)cos_sin, table_rows, positions,
-                           seq_of_token, block_table, table_width, (bf16*)pages, page_size, num_pages, store, status);
-            else
-                spy_launch(qk_rope_store_hd128_kernel<float, TW>, dim3((int)blocks), dim3(256), 0, stream, (const float*)src, src_splits,
-                           src_split_stride, (bf16*)q_out, q_out_stride, tokens, nh, nkv, (const TW*)q_w, (const TW*)k_w, eps,
-                           (const float2*)cos_sin, table_rows, positions, seq_of_token, block_table, table_width, (bf16*)pages, page_size,
-                           num_pages, store, status);
+            if (plain_bf16) {
+                if (ipw == 4) SPY_QK_HD128(bf16, 4, 1, 0LL);
+                else SPY_QK_HD128(bf16, 1, 1, 0LL);
+            } else {
+                if (ipw == 4) SPY_QK_HD128(float, 4, src_splits, src_split_stride);
+                else SPY_QK_HD128(float, 1, src_splits, src_split_stride);
+            }
         })
+#undef SPY_QK_HD128
         SPY_CHECK_LAUNCH("qk_rope_store (head_dim 128)");
         return 0;
     }

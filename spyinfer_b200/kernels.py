@@ -289,11 +289,9 @@ def attention_mma(q: torch.Tensor, num_heads: int, head_dim: int, out: torch.Ten
 
 def attention_tc(q: torch.Tensor, num_heads: int, head_dim: int, out: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor,
                  positions: torch.Tensor, q_start: torch.Tensor, num_seqs: int, scale: float, window: Optional[int] = None,
-                 split_keys: int = 0, max_splits: int = 0, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+                 status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of a batch over its pages on tcgen05 (128-row blocks, scores and output in tensor
-    memory, pages brought in by TMA).  ``split_keys == 0``: prompt portions, any mix.
-    ``split_keys > 0`` (a multiple of 128): every sequence brings one token and its keys are cut
-    into at most ``max_splits`` ranges, merged through scratch memory.  Page sizes 8 .. 128."""
+    memory, pages brought in by TMA): prompt portions, any mix.  Page sizes 8 .. 128."""
     _check(q, "attention queries", torch.bfloat16, 2)
     _check(out, "attention output", torch.bfloat16, 2)
     _check(pages, "cache pages", torch.bfloat16, 5)
@@ -308,17 +306,11 @@ def attention_tc(q: torch.Tensor, num_heads: int, head_dim: int, out: torch.Tens
         raise KernelError(f"attention: q {tuple(q.shape)} / out {tuple(out.shape)} do not fit {num_heads} heads of {head_dim}")
     if positions.shape[0] != T or q_start.shape[0] != num_seqs + 1 or block_table.shape[0] < num_seqs:
         raise KernelError("attention: positions need one entry per token, q_start one per sequence plus one, the block table a row per sequence")
-    scratch, floats = None, 0
-    if split_keys > 0 and max_splits > 1:
-        floats = num_seqs * num_heads * max_splits * (head_dim + 2)
-        scratch = attention_scratch(q.device, floats)
-        floats = scratch.numel()
     if status is None:
         status = status_word(q.device)
     _call("attention_tc", "spy_attention_tc", _ptr(q), ctypes.c_longlong(q.shape[1]), _ptr(out), _ptr(pages), _ptr(block_table),
           block_table.shape[1], page_size, num_pages, num_heads, nkv, head_dim, _ptr(positions), _ptr(q_start), T, num_seqs,
-          int(window or 0), ctypes.c_float(scale), int(split_keys), int(max_splits), _ptr(scratch), ctypes.c_longlong(floats),
-          _ptr(status), _stream())
+          int(window or 0), ctypes.c_float(scale), _ptr(status), _stream())
     return out
 
 

@@ -56,7 +56,7 @@ def bench_attention(batch: int, context: int, q_len: int = 1, split_keys: int = 
         if kernel == "decode":
             kernels.attention_decode(q, nh, hd, out, pages, bt, pos, q_start, batch, 1 / math.sqrt(hd))
         elif use_tc:
-            kernels.attention_tc(q, nh, hd, out, pages, bt, pos, q_start, batch, 1 / math.sqrt(hd), split_keys=split_keys, max_splits=max_splits)
+            kernels.attention_tc(q, nh, hd, out, pages, bt, pos, q_start, batch, 1 / math.sqrt(hd))
         else:
             kernels.attention_mma(q, nh, hd, out, pages, bt, pos, q_start, batch, 1 / math.sqrt(hd), split_keys=split_keys, max_splits=max_splits)
 
@@ -87,7 +87,7 @@ def main(argv=None) -> int:
     a.add_argument("--batch", type=int, required=True)
     a.add_argument("--context", type=int, required=True)
     a.add_argument("--q-len", type=int, default=1)
-    a.add_argument("--split-keys", type=int, default=0, help="0: tiles mode; else split mode with this range length")
+    a.add_argument("--split-keys", type=int, default=0, help="mma kernel only: 0: tiles mode; else split mode with this range length")
     a.add_argument("--iters", type=int, default=10)
     a.add_argument("--page-size", type=int, default=16)
     a.add_argument("--kernel", default="auto", choices=["auto", "tc", "mma", "decode"],
