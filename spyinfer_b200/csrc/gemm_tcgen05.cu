@@ -207,7 +207,7 @@ __device__ __forceinline__ float silu_mul(float g, float u) { return (g / (1.0f 
 template <int BN, typename TC, bool SWAP, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, BN <= 64 ? 2 : 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, TC* __restrict__ out,
-                    long long ld, long long split_stride, int x_rows, int y_rows, int k_blocks, int k_blocks_per_split, int* status)
+                    long long ld, long long split_stride, int x_rows, int y_rows, int k_blocks, int k_blocks_per_split, int tile_rows, int* status)
 {
     using T = Tile<BN>;
     extern __shared__ uint8_t smem_raw[];
@@ -220,7 +220,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int x0 = blockIdx.x * BM, y0 = blockIdx.y * BN;
+    // tile_rows (<= BM) rows of X belong to this block: the box of map_x has that many rows, the rest of
+    // the stage's 128 rows is stale and feeds accumulator rows that are never stored
+    const int x0 = blockIdx.x * tile_rows, y0 = blockIdx.y * BN;
+    const uint32_t stage_tx = (uint32_t)tile_rows * BK * 2 + T::Y_BYTES;
     const int kb0 = blockIdx.z * k_blocks_per_split;
     const int kb1 = min(k_blocks, kb0 + k_blocks_per_split);
     const int num_kb = kb1 - kb0;
@@ -253,7 +256,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             const int pre = min(num_kb, T::STAGES);
             for (int i = 0; i < pre; ++i) {
                 uint8_t* xs = tiles + (size_t)i * T::STAGE_BYTES;
-                mbar_expect_tx(full_bar + i, T::STAGE_BYTES);
+                mbar_expect_tx(full_bar + i, stage_tx);
                 if constexpr (SWAP) tma_load_2d(xs, &map_x, (kb0 + i) * BK, x0, full_bar + i);
                 else tma_load_2d(xs + T::X_BYTES, &map_y, (kb0 + i) * BK, y0, full_bar + i);
             }
@@ -269,7 +272,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 if (!mbar_wait(empty_bar + s, phase ^ 1, abort_flag)) break;
                 uint8_t* xs = tiles + (size_t)s * T::STAGE_BYTES;
                 uint8_t* ys = xs + T::X_BYTES;
-                mbar_expect_tx(full_bar + s, T::STAGE_BYTES);
+                mbar_expect_tx(full_bar + s, stage_tx);
                 tma_load_2d(xs, &map_x, (kb0 + i) * BK, x0, full_bar + s);
                 tma_load_2d(ys, &map_y, (kb0 + i) * BK, y0, full_bar + s);
             }
@@ -301,7 +304,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         pdl_wait();   // the output buffer may still be in use by a kernel ahead in the stream
         const bool ok = mbar_wait(accum_bar, 0, abort_flag);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const int x = x0 + quarter * 32 + lane;
+        const int x = quarter * 32 + lane < tile_rows ? x0 + quarter * 32 + lane : x_rows;   // rows beyond the tile's are the next block's
         TC* base = out + (size_t)blockIdx.z * split_stride;
         if (ok && num_kb > 0) {
 #pragma unroll 1
@@ -621,7 +624,7 @@ static int make_map(CUtensorMap* map, const void* ptr, long long rows, long long
 
 template <int BN, typename TC, bool SWAP, int EPI>
 static int launch(const CUtensorMap& mx, const CUtensorMap& my, void* out, long long ld, long long split_stride, int x_rows, int y_rows,
-                  int k_blocks, int splits, int* status, cudaStream_t stream)
+                  int k_blocks, int splits, int tile_rows, int* status, cudaStream_t stream)
 {
     using T = Tile<BN>;
     auto kernel = gemm_tcgen05_kernel<BN, TC, SWAP, EPI>;
@@ -631,41 +634,89 @@ static int launch(const CUtensorMap& mx, const CUtensorMap& my, void* out, long 
         configured = true;
     }
     const int per_split = (k_blocks + splits - 1) / splits;
-    dim3 grid((x_rows + BM - 1) / BM, (y_rows + BN - 1) / BN, splits);
+    dim3 grid((x_rows + tile_rows - 1) / tile_rows, (y_rows + BN - 1) / BN, splits);
     if (grid.y > 65535 || grid.z > 65535) SPY_FAIL("gemm_tcgen05: the grid %u x %u x %u exceeds the launch limits", grid.x, grid.y, grid.z);
-    spy_launch(kernel, grid, dim3(NUM_THREADS), T::SMEM, stream, mx, my, (TC*)out, ld, split_stride, x_rows, y_rows, k_blocks, per_split, status);
+    spy_launch(kernel, grid, dim3(NUM_THREADS), T::SMEM, stream, mx, my, (TC*)out, ld, split_stride, x_rows, y_rows, k_blocks, per_split, tile_rows,
+               status);
     SPY_CHECK_LAUNCH("gemm_tcgen05");
     return 0;
 }
 
 }  // namespace
 
-// How many splits of K a product of this shape uses, and the floats of scratch it needs.
-// The choice depends on M only through its class (<= 64 rows or more), never on M itself
-// within the class beyond the number of row tiles.  A plan that would need more than
-// scratch_limit floats falls back to one pass over K.
-extern "C" int spy_gemm_tcgen05_plan(int M, int N, int K, long long scratch_limit, int* splits_out, long long* scratch_floats_out)
+namespace {
+
+// The plan of a product: how many ways K is split and how many weight rows a block takes.
+// Many tokens (M > 64): 128 x 256 tiles, K split only when the tiles are fewer than the SMs.
+// Few tokens (decoding; the weights sit in the instruction's M slot, two blocks share an SM):
+// the product is bound by reading the weights, so what counts is that all 2 x SMs block
+// slots stream at once and end together.  When 128-row tiles times the splits would not fill
+// the slots, the tile takes fewer rows (a multiple of 4, at least 64: the TMA box shrinks, the
+// tensor core still multiplies 128 rows and the spare ones are dropped), so that tiles x splits
+// comes as close to the slots as it can; among the ways to split K the cheapest by a small
+// model wins (work per block, a fixed cost per block, a cost per split for the partial sums
+// the consumer has to add).  The choice depends on N, K and the class of M only.
+struct Plan {
+    int splits, tile_rows;
+};
+
+Plan make_plan(int M, int N, int K, bool may_split)
 {
     const int k_blocks = (K + BK - 1) / BK;
-    int tiles;
-    if (M <= 64) tiles = (N + BM - 1) / BM;
-    else tiles = ((M + BM - 1) / BM) * ((N + 255) / 256);
-    int splits = 1;
-    if (tiles < 148) {
-        splits = (296 + tiles - 1) / tiles;
-        const int most = k_blocks / 4 > 0 ? k_blocks / 4 : 1;   // at least four K blocks per split
-        if (splits > most) splits = most;
-        if (splits > 16) splits = 16;
+    Plan best = {1, BM};
+    if (M > 64) {
+        const int tiles = ((M + BM - 1) / BM) * ((N + 255) / 256);
+        if (tiles < 148 && may_split) {
+            int splits = (296 + tiles - 1) / tiles;
+            const int most = k_blocks / 4 > 0 ? k_blocks / 4 : 1;   // at least four K blocks per split
+            if (splits > most) splits = most;
+            if (splits > 16) splits = 16;
+            const int per = (k_blocks + splits - 1) / splits;       // no empty trailing split
+            best.splits = (k_blocks + per - 1) / per;
+        }
+        return best;
     }
-    // no empty trailing split
-    const int per = (k_blocks + splits - 1) / splits;
-    splits = (k_blocks + per - 1) / per;
-    *splits_out = splits;
-    *scratch_floats_out = splits > 1 ? (long long)splits * M * N : 0;
-    if (*scratch_floats_out > scratch_limit) {   // not enough scratch: one pass over K
-        *splits_out = 1;
-        *scratch_floats_out = 0;
+    const int slots = 296;
+    if ((N + BM - 1) / BM >= slots) return best;   // more 128-row tiles than slots: they spread evenly as they are
+    int most = may_split ? (k_blocks / 4 > 0 ? k_blocks / 4 : 1) : 1;
+    if (most > 16) most = 16;
+    double best_cost = 0;
+    for (int s = 1; s <= most; ++s) {
+        const int per = (k_blocks + s - 1) / s;
+        if ((k_blocks + per - 1) / per != s) continue;   // would leave an empty trailing split
+        int rows = BM;
+        const long long full = (long long)((N + BM - 1) / BM) * s;
+        if (full < slots) {
+            rows = ((N + slots / s - 1) / (slots / s) + 3) / 4 * 4;   // the fewest rows with which the tiles still fit the slots
+            if (rows < 64) rows = 64;
+            if (rows > BM) rows = BM;
+        }
+        const long long ctas = (long long)((N + rows - 1) / rows) * s;
+        const double waves = ctas <= slots ? 1.0 : (ctas <= 2 * slots ? 2.0 : (double)ctas / slots + 0.5);
+        const double cost = waves * ((double)rows * per + 344.0) + 20.0 * s;
+        if (s == 1 || cost < best_cost) {
+            best_cost = cost;
+            best.splits = s;
+            best.tile_rows = rows;
+        }
     }
+    return best;
+}
+
+}  // namespace
+
+// How many splits of K a product of this shape uses, and the floats of scratch it needs.
+// A plan that would need more than scratch_limit floats falls back to one pass over K.
+extern "C" int spy_gemm_tcgen05_plan(int M, int N, int K, long long scratch_limit, int* splits_out, long long* scratch_floats_out)
+{
+    Plan plan = make_plan(M, N, K, true);
+    long long need = plan.splits > 1 ? (long long)plan.splits * M * N : 0;
+    if (need > scratch_limit) {   // not enough scratch: one pass over K
+        plan = make_plan(M, N, K, false);
+        need = 0;
+    }
+    *splits_out = plan.splits;
+    *scratch_floats_out = need;
     return 0;
 }
 
@@ -686,16 +737,16 @@ extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, 
     if (c_dtype != SPY_F32 && c_dtype != SPY_BF16) SPY_FAIL("gemm_tcgen05: unknown output dtype code %d", c_dtype);
     if (epilogue != 0 && epilogue != 1) SPY_FAIL("gemm_tcgen05: unknown epilogue %d", epilogue);
     if (epilogue == 1 && (N % 2 != 0 || c_dtype != SPY_BF16)) SPY_FAIL("gemm_tcgen05: the SwiGLU epilogue needs an even N and bfloat16 output");
-    int splits = 1;
-    long long need = 0;
-    if (epilogue == 0) spy_gemm_tcgen05_plan(M, N, K, scratch ? scratch_floats : 0, &splits, &need);
+    Plan plan = make_plan(M, N, K, epilogue == 0);
+    if (plan.splits > 1 && (scratch == nullptr || (long long)plan.splits * M * N > scratch_floats)) plan = make_plan(M, N, K, false);
+    const int splits = plan.splits;
     if (splits_used) *splits_used = splits;
     const int k_blocks = (K + BK - 1) / BK;
     const bool swap = M <= 64;
     const int bn = swap ? (M <= 16 ? 16 : (M <= 32 ? 32 : 64)) : 256;
     CUtensorMap mx, my;
     if (swap) {
-        if (make_map(&mx, W, N, K, ldw, BM) || make_map(&my, A, M, K, lda, bn)) return 1;
+        if (make_map(&mx, W, N, K, ldw, plan.tile_rows) || make_map(&my, A, M, K, lda, bn)) return 1;
     } else {
         if (make_map(&mx, A, M, K, lda, BM) || make_map(&my, W, N, K, ldw, bn)) return 1;
     }
@@ -737,9 +788,9 @@ extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, 
     }
     int rc;
 #define SPY_LAUNCH(BN_, SWAP_)                                                                                                          \
-    rc = epilogue == 1 ? launch<BN_, bf16, SWAP_, 1>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, status, stream)       \
-         : f32_out     ? launch<BN_, float, SWAP_, 0>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, status, stream)      \
-                       : launch<BN_, bf16, SWAP_, 0>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, status, stream)
+    rc = epilogue == 1 ? launch<BN_, bf16, SWAP_, 1>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, plan.tile_rows, status, stream)   \
+         : f32_out     ? launch<BN_, float, SWAP_, 0>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, plan.tile_rows, status, stream)  \
+                       : launch<BN_, bf16, SWAP_, 0>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, plan.tile_rows, status, stream)
     if (!swap) SPY_LAUNCH(256, false);
     else if (bn == 16) SPY_LAUNCH(16, true);
     else if (bn == 32) SPY_LAUNCH(32, true);
