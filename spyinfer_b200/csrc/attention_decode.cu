@@ -83,43 +83,69 @@ struct Params {
     float* part_o;             // [slots][G][HD] unnormalised partial outputs
     float* part_ml;            // [slots][G][2]  (maximum in the log2 domain, sum)
     int* status;
-    int table_width, page_size, num_pages, nh, nkv, G, S, window, blocks, max_keys;
+    int table_width, page_size, num_pages, nh, nkv, G, S, window, blocks, max_keys, mode;
     float scale_log2;
 };
 
-// A run of tiles [t, t_end) of pair (s, kvh), whose keys span `tiles` tiles; `left` units remain
-// for the block after this run.
+// A block's share of the batch's units: either the contiguous range [u0, u1) of the list of all
+// (sequence, kv head, tile) units, which cuts pairs wherever the range ends, or (whole) the pairs
+// first, first + stride, ... each with all its tiles.
+struct Share {
+    const int* prefix;   // [S + 1] tiles of the sequences before s
+    int S, nkv, u0, u1, first, stride;
+    bool whole;
+};
+
+// A run of tiles [t, t_end) of pair (s, kvh), whose keys span `tiles` tiles; `left` units (or, whole,
+// the next pair's index) remain for the block after this run.
 struct Seg {
     int s, kvh, t0, t, t_end, tiles, left;
 };
 
-__device__ __forceinline__ bool seg_first(Seg& g, const int* prefix, int S, int nkv, int u0, int u1)
+__device__ __forceinline__ bool seg_whole(Seg& g, const Share& sh, int pair)
 {
-    if (u0 >= u1) return false;
-    int a = 0, b = S;   // nkv * prefix[a] <= u0 < nkv * prefix[b]
+    for (; pair < sh.S * sh.nkv; pair += sh.stride) {
+        g.s = pair / sh.nkv;
+        g.tiles = sh.prefix[g.s + 1] - sh.prefix[g.s];
+        if (g.tiles == 0) continue;
+        g.kvh = pair - g.s * sh.nkv;
+        g.t0 = g.t = 0;
+        g.t_end = g.tiles;
+        g.left = pair + sh.stride;
+        return true;
+    }
+    return false;
+}
+
+__device__ __forceinline__ bool seg_first(Seg& g, const Share& sh)
+{
+    if (sh.whole) return seg_whole(g, sh, sh.first);
+    if (sh.u0 >= sh.u1) return false;
+    int a = 0, b = sh.S;   // nkv * prefix[a] <= u0 < nkv * prefix[b]
     while (b - a > 1) {
         const int mid = (a + b) >> 1;
-        if (nkv * prefix[mid] <= u0) a = mid; else b = mid;
+        if (sh.nkv * sh.prefix[mid] <= sh.u0) a = mid; else b = mid;
     }
     g.s = a;
-    g.tiles = prefix[a + 1] - prefix[a];
-    const int r = u0 - nkv * prefix[a];
+    g.tiles = sh.prefix[a + 1] - sh.prefix[a];
+    const int r = sh.u0 - sh.nkv * sh.prefix[a];
     g.kvh = r / g.tiles;
     g.t0 = g.t = r - g.kvh * g.tiles;
-    const int n = min(g.tiles - g.t, u1 - u0);
+    const int n = min(g.tiles - g.t, sh.u1 - sh.u0);
     g.t_end = g.t + n;
-    g.left = u1 - u0 - n;
+    g.left = sh.u1 - sh.u0 - n;
     return true;
 }
 
-__device__ __forceinline__ bool seg_next(Seg& g, const int* prefix, int S, int nkv)
+__device__ __forceinline__ bool seg_next(Seg& g, const Share& sh)
 {
+    if (sh.whole) return seg_whole(g, sh, g.left);
     if (g.left <= 0) return false;
-    if (++g.kvh == nkv) {
+    if (++g.kvh == sh.nkv) {
         g.kvh = 0;
         do {
-            if (++g.s >= S) return false;
-            g.tiles = prefix[g.s + 1] - prefix[g.s];
+            if (++g.s >= sh.S) return false;
+            g.tiles = sh.prefix[g.s + 1] - sh.prefix[g.s];
         } while (g.tiles == 0);
     }
     const int n = min(g.tiles, g.left);
@@ -181,6 +207,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
     uint64_t* bar_lred = bar_red + 2;                                    // the four warps' sums are written
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_lred + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    int* s_max_tiles = reinterpret_cast<int*>(tmem_slot + 2);   // the most tiles any sequence has
 
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
@@ -226,10 +253,11 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
     }
     __syncthreads();
     if (warp == 0) {
-        int carry = 0;
+        int carry = 0, most = 0;
         for (int base = 0; base < p.S; base += 32) {
             const int s = base + lane;
             int v = s < p.S ? prefix[s + 1] : 0;
+            most = max(most, v);
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
                 const int up = __shfl_up_sync(0xffffffffu, v, o);
@@ -238,7 +266,11 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
             if (s < p.S) prefix[s + 1] = carry + v;
             carry += __shfl_sync(0xffffffffu, v, 31);
         }
-        if (lane == 0) prefix[0] = 0;
+        most = __reduce_max_sync(0xffffffffu, most);
+        if (lane == 0) {
+            prefix[0] = 0;
+            *s_max_tiles = most;
+        }
     }
     fence_before_sync();
     __syncthreads();
@@ -249,13 +281,18 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
     const int units = p.nkv * prefix[p.S];
     const int per = (units + (int)gridDim.x - 1) / (int)gridDim.x;
     const int u0 = min(units, (int)blockIdx.x * per), u1 = min(units, u0 + per);
+    // Whole pairs, dealt round-robin, need no merge; they pay when the blocks then end about when an
+    // even split of the units would (short contexts, or many pairs per block).
+    const int pairs = p.S * p.nkv, rounds = (pairs + (int)gridDim.x - 1) / (int)gridDim.x;
+    const bool whole = p.mode == 2 || (p.mode == 0 && (long long)rounds * *s_max_tiles * 4 <= (long long)per * 5 + 32);
+    const Share share = {prefix, p.S, p.nkv, u0, u1, (int)blockIdx.x, (int)gridDim.x, whole};
     const uint32_t k_s = smem_u32(smem + K_OFF), v_s = smem_u32(smem + V_OFF), q_s = smem_u32(smem + Q_OFF), p_s = smem_u32(smem + P_OFF);
 
     if (warp < 4) {
         // ---------------------------------------------------------------- softmax (one key per thread) and epilogue
         const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
         Seg g;
-        bool more = seg_first(g, prefix, p.S, p.nkv, u0, u1), alive = true;
+        bool more = seg_first(g, share), alive = true;
         int gt = 0, seg = 0;   // tiles and segments this block has begun
         while (more && alive) {
             int pos, lo;
@@ -440,15 +477,14 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
             }
             if (tid == 0) STAMP(9);
             ++seg;
-            more = seg_next(g, prefix, p.S, p.nkv);
+            more = seg_next(g, share);
         }
     } else if (warp == 4) {
         // ---------------------------------------------------------------- MMA issue
-        if (lane == 0 && u0 < u1) {
+        if (lane == 0) {
             const uint32_t idesc_qk = instr_desc_bf16(TILE, NCOLS, false, false), idesc_pv = instr_desc_bf16(TILE, NCOLS, true, false);
             Seg gq, gp;
-            bool moreq = seg_first(gq, prefix, p.S, p.nkv, u0, u1), ok = true;
-            seg_first(gp, prefix, p.S, p.nkv, u0, u1);
+            bool moreq = seg_first(gq, share), morep = seg_first(gp, share), ok = true;
             int iq = 0, segq = 0;
             auto issue_qk = [&]() {   // S^T of the next tile
                 const int stage = iq % STAGES, slot = segq % QSLOTS;
@@ -468,12 +504,12 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
                 if (++gq.t == gq.t_end) {
                     umma_commit(bar_qfree + slot);
                     ++segq;
-                    moreq = seg_next(gq, prefix, p.S, p.nkv);
+                    moreq = seg_next(gq, share);
                 }
             };
-            issue_qk();
+            if (moreq) issue_qk();
             if (ok && moreq) issue_qk();
-            for (int ip = 0; ip < u1 - u0 && ok; ++ip) {
+            for (int ip = 0; morep && ok; ++ip) {
                 const int st = ip & 1, stage = ip % STAGES;
                 ok = mbar_wait(bar_p + st, (uint32_t)(ip >> 1) & 1, abort_flag) && mbar_wait(bar_vfull + stage, (uint32_t)(ip / STAGES) & 1, abort_flag);
                 if (!ok) break;
@@ -485,17 +521,17 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
                          (gp.t > gp.t0 || s > 0) ? 1u : 0u);
                 umma_commit(bar_o + st);
                 umma_commit(bar_vfree + stage);
-                if (++gp.t == gp.t_end) seg_next(gp, prefix, p.S, p.nkv);
+                if (++gp.t == gp.t_end) morep = seg_next(gp, share);
                 if (moreq) issue_qk();   // S^T's stage st is free: P^T of this tile was made from it
             }
         }
     } else if (warp == 7) {
         // ---------------------------------------------------------------- TMA: the segments' queries, which the kernel ahead wrote
-        if (lane == 0 && u0 < u1) {
+        if (lane == 0) {
             pdl_wait();
             STAMP(3);
             Seg g;
-            bool more = seg_first(g, prefix, p.S, p.nkv, u0, u1);
+            bool more = seg_first(g, share);
             for (int seg = 0; more; ++seg) {
                 const int slot = seg % QSLOTS;
                 const int tok = p.q_start[g.s];
@@ -504,7 +540,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
 #pragma unroll
                 for (int h = 0; h < HD / 64; ++h)
                     tma_load_3d(q_s + slot * QP_BYTES + h * (NCOLS * 128), &q_map, h * 64, g.kvh * p.G, tok, bar_qfull + slot);
-                more = seg_next(g, prefix, p.S, p.nkv);
+                more = seg_next(g, share);
             }
         }
     } else {
@@ -520,7 +556,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
         const uint32_t box_bytes = (uint32_t)p.page_size * 128;              // page_size rows of 64 elements
         const int my_page = lane / (HD / 64), my_half = lane % (HD / 64);
         Seg g;
-        bool more = seg_first(g, prefix, p.S, p.nkv, u0, u1), ok = true, waited = false;
+        bool more = seg_first(g, share), ok = true, waited = false;
         int i = 0;
         if (lane == 0 && kv == 0) STAMP(15);
         while (more && ok) {
@@ -558,7 +594,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
                     tma_load_2d(ring + stage * STAGE_BYTES + my_half * HALF_BYTES + my_page * p.page_size * 128, &page_map, my_half * 64, y, bar_full + stage);
                 }
             }
-            if (ok) more = seg_next(g, prefix, p.S, p.nkv);
+            if (ok) more = seg_next(g, share);
         }
     }
 
@@ -622,10 +658,12 @@ extern "C" long long spy_attention_decode_scratch_floats(int seqs, int nh, int n
 }
 
 // Attention of a decoding batch over its pages: every sequence brings one token (row
-// q_start[s] of q, at positions[q_start[s]]).
+// q_start[s] of q, at positions[q_start[s]]).  mode 0: the kernel decides how the work is shared
+// out; 1: the units split evenly, pairs cut where a block's share ends; 2: whole pairs.
 extern "C" int spy_attention_decode(const void* q, long long q_row_stride, void* out, const void* pages, const int* block_table, int table_width,
                                     int page_size, int num_pages, int nh, int nkv, int hd, const int* positions, const int* q_start, int tokens,
-                                    int seqs, int window, float scale, float* scratch, long long scratch_floats, int* status, cudaStream_t stream)
+                                    int seqs, int window, float scale, int mode, float* scratch, long long scratch_floats, int* status,
+                                    cudaStream_t stream)
 {
     if (tokens <= 0 || seqs <= 0) return 0;
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0) SPY_FAIL("attention_decode: %d query heads do not group over %d key/value heads", nh, nkv);
@@ -640,6 +678,7 @@ extern "C" int spy_attention_decode(const void* q, long long q_row_stride, void*
     if (page_size < 8 || page_size > TILE || TILE % page_size != 0)
         SPY_FAIL("attention_decode: page_size %d must be 8, 16, 32, 64 or 128 (one TMA box per page)", page_size);
     if (window < 0) SPY_FAIL("attention_decode: window %d must be 0 (none) or positive", window);
+    if (mode < 0 || mode > 2) SPY_FAIL("attention_decode: mode %d is not 0 (the kernel decides), 1 (units split evenly) or 2 (whole pairs)", mode);
     const long long max_keys = (long long)table_width * page_size;
     if (max_keys >= (1LL << 30) || (long long)seqs * nkv * (max_keys / TILE + 1) >= (1LL << 31))
         SPY_FAIL("attention_decode: %d sequences of up to %lld keys exceed this kernel's counters", seqs, max_keys);
@@ -654,7 +693,7 @@ extern "C" int spy_attention_decode(const void* q, long long q_row_stride, void*
     p.out = (bf16*)out; p.block_table = block_table; p.positions = positions; p.q_start = q_start; p.status = status;
     p.part_o = scratch; p.part_ml = scratch + ((size_t)seqs * nkv + sms) * G * hd;
     p.table_width = table_width; p.page_size = page_size; p.num_pages = num_pages; p.nh = nh; p.nkv = nkv; p.G = G; p.S = seqs;
-    p.window = window; p.blocks = sms; p.max_keys = (int)max_keys; p.scale_log2 = scale * LOG2E;
+    p.window = window; p.blocks = sms; p.max_keys = (int)max_keys; p.mode = mode; p.scale_log2 = scale * LOG2E;
 
     // the pages of this cache as one matrix [num_pages * 2 * nkv * page_size rows, hd]; a box is one page's rows x 64 columns
     CUtensorMap page_map, q_map;

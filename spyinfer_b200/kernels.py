@@ -327,13 +327,17 @@ def attention_decode_takes(num_heads: int, num_kv_heads: int, head_dim: int, pag
 
 def attention_decode(q: torch.Tensor, num_heads: int, head_dim: int, out: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor,
                      positions: torch.Tensor, q_start: torch.Tensor, num_seqs: int, scale: float, window: Optional[int] = None,
-                     status: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     status: Optional[torch.Tensor] = None, share: str = "auto") -> torch.Tensor:
     """Attention of a decoding batch (one token per sequence) over its pages: one persistent block
     per SM, keys in the rows of tcgen05 tiles, pages brought in by TMA, the batch's tiles shared out
     evenly over the blocks and merged through scratch memory.  At most 1024 sequences.  ``positions``,
     ``q_start`` and ``block_table`` are read while kernels launched earlier may still be running: they
     must be complete before those start (the engine copies them at the start of a step).  Launches
-    on different streams must not overlap (they share the counters of the merge)."""
+    on different streams must not overlap (they share the counters of the merge).  ``share``: how
+    the work is dealt out, "auto" (the kernel decides), "split" (tiles split evenly, merged) or
+    "whole" ((sequence, kv head) pairs whole)."""
+    if share not in ("auto", "split", "whole"):
+        raise KernelError(f"attention_decode: share {share!r} is not 'auto', 'split' or 'whole'")
     _check(q, "attention queries", torch.bfloat16, 2)
     _check(out, "attention output", torch.bfloat16, 2)
     _check(pages, "cache pages", torch.bfloat16, 5)
@@ -356,7 +360,8 @@ def attention_decode(q: torch.Tensor, num_heads: int, head_dim: int, out: torch.
         status = status_word(q.device)
     _call("attention_decode", "spy_attention_decode", _ptr(q), ctypes.c_longlong(q.shape[1]), _ptr(out), _ptr(pages), _ptr(block_table),
           block_table.shape[1], page_size, num_pages, num_heads, nkv, head_dim, _ptr(positions), _ptr(q_start), T, num_seqs,
-          int(window or 0), ctypes.c_float(scale), _ptr(scratch), ctypes.c_longlong(scratch.numel()), _ptr(status), _stream())
+          int(window or 0), ctypes.c_float(scale), ("auto", "split", "whole").index(share), _ptr(scratch), ctypes.c_longlong(scratch.numel()),
+          _ptr(status), _stream())
     return out
 
 

@@ -39,7 +39,7 @@ def bench_gemm(M: int, N: int, K: int, out_dtype=torch.bfloat16, iters: int = 20
 
 
 def bench_attention(batch: int, context: int, q_len: int = 1, split_keys: int = 0, nh: int = 32, nkv: int = 8, hd: int = 128,
-                    page_size: int = 16, iters: int = 10, kernel: str = "auto") -> dict:
+                    page_size: int = 16, iters: int = 10, kernel: str = "auto", share: str = "auto", graph: bool = False) -> dict:
     width = (context + page_size - 1) // page_size
     pages = torch.randn(batch * width + 1, 2, nkv, page_size, hd, device=DEV).to(torch.bfloat16)
     bt = torch.randperm(batch * width, device=DEV).view(batch, width).to(torch.int32)
@@ -54,7 +54,7 @@ def bench_attention(batch: int, context: int, q_len: int = 1, split_keys: int = 
 
     def run():
         if kernel == "decode":
-            kernels.attention_decode(q, nh, hd, out, pages, bt, pos, q_start, batch, 1 / math.sqrt(hd))
+            kernels.attention_decode(q, nh, hd, out, pages, bt, pos, q_start, batch, 1 / math.sqrt(hd), share=share)
         elif use_tc:
             kernels.attention_tc(q, nh, hd, out, pages, bt, pos, q_start, batch, 1 / math.sqrt(hd))
         else:
@@ -63,10 +63,21 @@ def bench_attention(batch: int, context: int, q_len: int = 1, split_keys: int = 
     run()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(iters):
-        run()
-    e1.record()
+    if graph:   # the launches replayed from a CUDA graph: device time without the host's launch cost
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(iters):
+                run()
+        g.replay()
+        torch.cuda.synchronize()
+        e0.record()
+        g.replay()
+        e1.record()
+    else:
+        e0.record()
+        for _ in range(iters):
+            run()
+        e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / iters
     kv_bytes = batch * context * 2 * nkv * hd * 2
@@ -90,6 +101,8 @@ def main(argv=None) -> int:
     a.add_argument("--split-keys", type=int, default=0, help="mma kernel only: 0: tiles mode; else split mode with this range length")
     a.add_argument("--iters", type=int, default=10)
     a.add_argument("--page-size", type=int, default=16)
+    a.add_argument("--graph", action="store_true", help="replay the launches from a CUDA graph (device time without host launch cost)")
+    a.add_argument("--share", default="auto", choices=["auto", "split", "whole"], help="decode kernel: how the work is dealt out over the blocks")
     a.add_argument("--kernel", default="auto", choices=["auto", "tc", "mma", "decode"],
                    help="auto: tcgen05 for tiles mode, mma.sync for split mode; decode: the persistent tcgen05 decode kernel (q-len 1)")
     args = ap.parse_args(argv)
@@ -98,7 +111,7 @@ def main(argv=None) -> int:
         r = bench_gemm(args.m, args.n, args.k, getattr(torch, args.out_dtype), args.iters)
         print(f"gemm M={args.m} N={args.n} K={args.k}: {r['us']:.1f} us, {r['tflops']:.1f} TFLOP/s, {r['gbs']:.1f} GB/s")
     else:
-        r = bench_attention(args.batch, args.context, args.q_len, args.split_keys, page_size=args.page_size, iters=args.iters, kernel=args.kernel)
+        r = bench_attention(args.batch, args.context, args.q_len, args.split_keys, page_size=args.page_size, iters=args.iters, kernel=args.kernel, share=args.share, graph=args.graph)
         print(f"attention batch={args.batch} context={args.context} q_len={args.q_len} split_keys={args.split_keys}: {r['us']:.1f} us, "
               f"cache read at {r['kv_gbs']:.1f} GB/s, {r['tflops']:.1f} TFLOP/s")
     return 0

@@ -552,9 +552,10 @@ def test_attention_tc_finds_one_far_key_and_survives_large_scores():
         assert hit == inside, f"window {window}, far key {far}: expected {'a hit' if inside else 'no hit'}"
 
 
+@pytest.mark.parametrize("share", ["auto", "split", "whole"])
 @pytest.mark.parametrize("nh,nkv,hd,page_size,window", [(32, 8, 128, 16, None), (10, 2, 64, 16, 300), (8, 8, 128, 8, None), (12, 4, 64, 32, None),
                                                         (16, 1, 128, 16, 700), (6, 1, 128, 128, None), (8, 2, 128, 64, 130)])
-def test_attention_decode_contexts_from_one_key_to_thousands(nh, nkv, hd, page_size, window):
+def test_attention_decode_contexts_from_one_key_to_thousands(nh, nkv, hd, page_size, window, share):
     """Persistent tcgen05 decode attention: one token per sequence, contexts at tile edges (127, 128,
     129 keys) and long ones, so that pairs are written whole by one block, cut over two blocks and over
     many; group sizes 1, 3, 4, 5, 6 and 16; with and without a window."""
@@ -568,7 +569,7 @@ def test_attention_decode_contexts_from_one_key_to_thousands(nh, nkv, hd, page_s
     q_start = torch.arange(S + 1, dtype=torch.int32, device=DEV)
     out = torch.full((S, nh * hd), float("nan"), device=DEV, dtype=torch.bfloat16)
     scale = 1 / math.sqrt(hd)
-    kernels.attention_decode(q, nh, hd, out, pages, bt, positions, q_start, S, scale, window=window)
+    kernels.attention_decode(q, nh, hd, out, pages, bt, positions, q_start, S, scale, window=window, share=share)
     torch.cuda.synchronize()
     assert kernels.status_word(DEV)[0].item() == 0
     for i, l in enumerate(lens):
@@ -590,8 +591,9 @@ def test_attention_decode_many_short_sequences():
     q_start = torch.arange(S + 1, dtype=torch.int32, device=DEV)
     out = torch.full((S, nh * hd), float("nan"), device=DEV, dtype=torch.bfloat16)
     scale = 1 / math.sqrt(hd)
-    for _ in range(2):   # twice: stale shared memory and scratch of the first run must not matter
-        kernels.attention_decode(q, nh, hd, out, pages, bt, positions, q_start, S, scale)
+    for share in ("split", "whole", "auto"):   # several times: stale shared memory and scratch of an earlier run must not matter
+        out.fill_(float("nan"))
+        kernels.attention_decode(q, nh, hd, out, pages, bt, positions, q_start, S, scale, share=share)
     torch.cuda.synchronize()
     assert kernels.status_word(DEV)[0].item() == 0
     for i, l in enumerate(lens):
