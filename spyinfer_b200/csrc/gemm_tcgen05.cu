@@ -20,141 +20,18 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "tcgen05.cuh"
 
 SPY_MODULE(spy_gemm_tcgen05)
 
 namespace {
 
+using namespace tc;
+
 constexpr int BM = 128;            // rows of X per tile = UMMA M
 constexpr int BK = 64;             // 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int NUM_THREADS = 192;   // warp 0: TMA, warp 1: MMA + TMEM, warps 2..5: epilogue
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ unsigned long long global_timer()
-{
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count)
-{
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes)
-{
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar)
-{
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
-{
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-
-// Bounded wait: gives up after WAIT_LIMIT_NS (or at once when another role has given up),
-// raises the block's abort flag and returns false.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag)
-{
-    if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = global_timer();
-    uint32_t spins = 0;
-    while (!mbar_try_wait(bar, parity)) {
-        if ((++spins & 0x3ff) == 0) {
-            if (*abort_flag) return false;
-            if (global_timer() - t0 > WAIT_LIMIT_NS) {
-                *abort_flag = 1;
-                return false;
-            }
-        }
-    }
-    return true;
-}
-
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
-        : "memory");
-}
-
-__device__ __forceinline__ uint64_t make_smem_desc(const void* tile)
-{
-    // K-major, 128-byte swizzle: 8 rows of 128 bytes form one 1024-byte group
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_u32(tile) & 0x3FFFF) >> 4);   // start address
-    d |= (uint64_t)1 << 16;                             // leading byte offset (unused with swizzle)
-    d |= (uint64_t)(1024 >> 4) << 32;                   // stride byte offset between 8-row groups
-    d |= (uint64_t)1 << 46;                             // descriptor version of sm_100
-    d |= (uint64_t)2 << 61;                             // SWIZZLE_128B
-    return d;
-}
-
-__device__ __forceinline__ uint32_t make_instr_desc(int n)
-{
-    uint32_t d = 0;
-    d |= 1u << 4;                    // accumulator F32
-    d |= 1u << 7;                    // A BF16
-    d |= 1u << 10;                   // B BF16
-    d |= (uint32_t)(n >> 3) << 17;   // N
-    d |= (uint32_t)(BM >> 4) << 24;  // M
-    return d;                        // both operands K-major, no negation
-}
-
-__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate)
-{
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
-__device__ __forceinline__ void umma_commit(uint64_t* bar)
-{
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-
-__device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t (&r)[32])
-{
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
-          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr));
-}
-
-__device__ __forceinline__ void tmem_load_16(uint32_t taddr, uint32_t (&r)[32])
-{
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr));
-}
 
 template <int BN> struct Tile {
     static constexpr int X_BYTES = BM * BK * 2;
@@ -257,14 +134,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             for (int i = 0; i < pre; ++i) {
                 uint8_t* xs = tiles + (size_t)i * T::STAGE_BYTES;
                 mbar_expect_tx(full_bar + i, stage_tx);
-                if constexpr (SWAP) tma_load_2d(xs, &map_x, (kb0 + i) * BK, x0, full_bar + i);
-                else tma_load_2d(xs + T::X_BYTES, &map_y, (kb0 + i) * BK, y0, full_bar + i);
+                if constexpr (SWAP) tma_load_2d(smem_u32(xs), &map_x, (kb0 + i) * BK, x0, full_bar + i);
+                else tma_load_2d(smem_u32(xs + T::X_BYTES), &map_y, (kb0 + i) * BK, y0, full_bar + i);
             }
             pdl_wait();
             for (int i = 0; i < pre; ++i) {
                 uint8_t* xs = tiles + (size_t)i * T::STAGE_BYTES;
-                if constexpr (SWAP) tma_load_2d(xs + T::X_BYTES, &map_y, (kb0 + i) * BK, y0, full_bar + i);
-                else tma_load_2d(xs, &map_x, (kb0 + i) * BK, x0, full_bar + i);
+                if constexpr (SWAP) tma_load_2d(smem_u32(xs + T::X_BYTES), &map_y, (kb0 + i) * BK, y0, full_bar + i);
+                else tma_load_2d(smem_u32(xs), &map_x, (kb0 + i) * BK, x0, full_bar + i);
             }
             for (int i = pre; i < num_kb; ++i) {
                 const int s = i % T::STAGES;
@@ -273,13 +150,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 uint8_t* xs = tiles + (size_t)s * T::STAGE_BYTES;
                 uint8_t* ys = xs + T::X_BYTES;
                 mbar_expect_tx(full_bar + s, stage_tx);
-                tma_load_2d(xs, &map_x, (kb0 + i) * BK, x0, full_bar + s);
-                tma_load_2d(ys, &map_y, (kb0 + i) * BK, y0, full_bar + s);
+                tma_load_2d(smem_u32(xs), &map_x, (kb0 + i) * BK, x0, full_bar + s);
+                tma_load_2d(smem_u32(ys), &map_y, (kb0 + i) * BK, y0, full_bar + s);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            const uint32_t idesc = make_instr_desc(BN);
+            const uint32_t idesc = instr_desc_bf16(BM, BN, false, false);
             bool ok = true;
             for (int i = 0; i < num_kb && ok; ++i) {
                 const int s = i % T::STAGES;
@@ -288,7 +165,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint8_t* xs = tiles + (size_t)s * T::STAGE_BYTES;
-                const uint64_t dx = make_smem_desc(xs), dy = make_smem_desc(xs + T::X_BYTES);
+                const uint64_t dx = desc_k_major(smem_u32(xs)), dy = desc_k_major(smem_u32(xs + T::X_BYTES));
 #pragma unroll
                 for (int k = 0; k < BK / UMMA_K; ++k) {
                     const uint64_t adv = (uint64_t)((k * UMMA_K * 2) >> 4);
@@ -311,8 +188,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             for (int c = 0; c < BN; c += 32) {
                 uint32_t r[32];
                 const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c;
-                if constexpr (BN >= 32) tmem_load_32(taddr, r);
-                else tmem_load_16(taddr, r);
+                if constexpr (BN >= 32) tmem_load<32>(taddr, r);
+                else tmem_load<16>(taddr, *reinterpret_cast<uint32_t(*)[16]>(&r[0]));
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 const int cols = BN >= 32 ? 32 : BN;
                 const int y = y0 + c;
@@ -487,10 +364,10 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const 
                     const int pre = min(k_blocks, T::STAGES);
                     for (int i = 0; i < pre; ++i) {
                         mbar_expect_tx(full_bar + i, T::STAGE_BYTES);
-                        tma_load_2d(tiles + (size_t)i * T::STAGE_BYTES + T::X_BYTES, &map_y, i * BK, y0, full_bar + i);
+                        tma_load_2d(smem_u32(tiles + (size_t)i * T::STAGE_BYTES + T::X_BYTES), &map_y, i * BK, y0, full_bar + i);
                     }
                     pdl_wait();
-                    for (int i = 0; i < pre; ++i) tma_load_2d(tiles + (size_t)i * T::STAGE_BYTES, &map_x, i * BK, x0, full_bar + i);
+                    for (int i = 0; i < pre; ++i) tma_load_2d(smem_u32(tiles + (size_t)i * T::STAGE_BYTES), &map_x, i * BK, x0, full_bar + i);
                     kb = pre;
                     g = pre;
                     first = false;
@@ -501,15 +378,15 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const 
                     if (g >= T::STAGES && !mbar_wait(empty_bar + s, phase ^ 1, abort_flag)) { ok = false; break; }
                     uint8_t* xs = tiles + (size_t)s * T::STAGE_BYTES;
                     mbar_expect_tx(full_bar + s, T::STAGE_BYTES);
-                    tma_load_2d(xs, &map_x, kb * BK, x0, full_bar + s);
-                    tma_load_2d(xs + T::X_BYTES, &map_y, kb * BK, y0, full_bar + s);
+                    tma_load_2d(smem_u32(xs), &map_x, kb * BK, x0, full_bar + s);
+                    tma_load_2d(smem_u32(xs + T::X_BYTES), &map_y, kb * BK, y0, full_bar + s);
                 }
             }
             if (first) pdl_wait();
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            const uint32_t idesc = make_instr_desc(BN);
+            const uint32_t idesc = instr_desc_bf16(BM, BN, false, false);
             long long g = 0;
             int i = 0;
             bool ok = true;
@@ -527,7 +404,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const 
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint8_t* xs = tiles + (size_t)s * T::STAGE_BYTES;
-                    const uint64_t dx = make_smem_desc(xs), dy = make_smem_desc(xs + T::X_BYTES);
+                    const uint64_t dx = desc_k_major(smem_u32(xs)), dy = desc_k_major(smem_u32(xs + T::X_BYTES));
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k) {
                         const uint64_t adv = (uint64_t)((k * UMMA_K * 2) >> 4);
@@ -554,7 +431,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const 
 #pragma unroll 1
             for (int c = 0; c < BN; c += 32) {
                 uint32_t r[32];
-                tmem_load_32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c), r);
+                tmem_load<32>(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c), r);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 store_chunk_normal<TC, EPI>(out, ld, x, y0 + c, x_rows, y_rows, r);
             }
@@ -591,26 +468,10 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, TC* __re
     }
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn()
-{
-    static EncodeTiledFn fn = nullptr;
-    if (fn == nullptr) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    }
-    return fn;
-}
-
 // A [rows, K] bfloat16 matrix with K contiguous; box = 64 columns x box_rows rows, 128-byte swizzle.
 static int make_map(CUtensorMap* map, const void* ptr, long long rows, long long K, long long ld, int box_rows)
 {
-    EncodeTiledFn fn = encode_fn();
+    EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) SPY_FAIL("gemm_tcgen05: cuTensorMapEncodeTiled is not available from the driver");
     cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
