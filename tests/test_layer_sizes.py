@@ -1,0 +1,93 @@
+"""The engine at the layer sizes of Qwen3-8B, 14B and 32B (one layer each, a small vocabulary
+that is no power of two, seeded random weights) against the plain implementation, in 32-bit
+and in bfloat16, under every way of cutting the work: whole, most of it in one step and the
+last 32 tokens one by one, portions of changing size, and mixed with page reuse.  These are
+the shapes the fast kernels were built for: group sizes 4, 5 and 8, widths 4096 and 5120,
+feed-forward widths 12288, 17408 and 25600."""
+import json
+import random
+
+import numpy as np
+import pytest
+
+import plain_model
+from trace_tools import TraceBuilder, mixed_trace, peak_tokens, run_trace
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = {
+    "8b": dict(hidden_size=4096, num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=12288),
+    "14b": dict(hidden_size=5120, num_attention_heads=40, num_key_value_heads=8, head_dim=128, intermediate_size=17408),
+    "32b": dict(hidden_size=5120, num_attention_heads=64, num_key_value_heads=8, head_dim=128, intermediate_size=25600),
+}
+LENGTHS = [3, 40, 131]
+PORTIONS = (7, 2, 19, 3, 2, 33)
+# the same bounds as the tiny models' replay tests
+TOL = {"float32": dict(max_rel=3e-5, rms_rel=1e-5), "bfloat16": dict(max_rel=5e-2, rms_rel=2e-2)}
+
+
+def config_of(name):
+    cfg = {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "hidden_act": "silu", "num_hidden_layers": 1, "vocab_size": 389,
+           "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "max_position_embeddings": 4096,
+           "bos_token_id": 0, "eos_token_id": 1}
+    cfg.update(SHAPES[name])
+    return cfg
+
+
+@pytest.fixture(scope="module")
+def layer_models(tmp_path_factory):
+    from safetensors.torch import save_file
+
+    memo = {}
+
+    def get(name):
+        if name not in memo:
+            cfg = config_of(name)
+            d = tmp_path_factory.mktemp(f"layer_{name}")
+            with open(d / "config.json", "w") as f:
+                json.dump(cfg, f)
+            w = plain_model.random_weights(cfg, 100 + len(name), 0.02, 0.05)
+            save_file({k: v.contiguous() for k, v in w.items()}, str(d / "model.safetensors"))
+            rng = random.Random(len(name))
+            reqs = {f"r{n}": [rng.randrange(cfg["vocab_size"]) for _ in range(n)] for n in LENGTHS}
+            want = {rid: plain_model.forward_logits(w, cfg, toks).numpy() for rid, toks in reqs.items()}
+            memo[name] = (str(d), cfg, reqs, want)
+        return memo[name]
+
+    return get
+
+
+def build(reqs):
+    b = TraceBuilder()
+    tokens_of = {}
+    for rid, toks in reqs.items():
+        b.whole("w_" + rid, toks)
+        b.tail_one_by_one("t_" + rid, toks, tail=32)
+        b.portions("p_" + rid, toks, PORTIONS)
+        for prefix in "wtp":
+            tokens_of[prefix + "_" + rid] = toks
+    mixed = {"m_" + rid: toks for rid, toks in reqs.items()}
+    mixed_trace(b, mixed, {rid: max(1, len(toks) - 12) for rid, toks in mixed.items()}, random.Random(5), max_live=3)
+    tokens_of.update(mixed)
+    return b, tokens_of
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(SHAPES))
+def test_layer_sizes_match_plain_under_every_cut(name, dtype, layer_models, tmp_path):
+    folder, cfg, reqs, want = layer_models(name)
+    b, tokens_of = build(reqs)
+    rows = run_trace(folder, dtype, b, str(tmp_path), peak_tokens(b), cfg["vocab_size"])
+    tol = TOL[dtype]
+    for rid, toks in tokens_of.items():
+        ref = want[rid[2:]]
+        got = np.stack([rows[(rid, p)] for p in range(len(toks))])
+        assert np.isfinite(got).all(), f"{name} {rid}: logits are not finite"
+        err = np.abs(got - ref)
+        scale, rms = np.abs(ref).max(), np.sqrt((ref ** 2).mean())
+        bad = np.argwhere(err > tol["max_rel"] * scale)
+        if len(bad):
+            first = int(bad[:, 0].min())
+            raise AssertionError(f"{name} {rid} ({len(toks)} tokens): first wrong position {first}, error {err[first].max():.3g} against a "
+                                 f"largest logit of {scale:.3g} (allowed {tol['max_rel'] * scale:.3g})")
+        assert np.sqrt((err ** 2).mean()) <= tol["rms_rel"] * rms, f"{name} {rid}: rms error {np.sqrt((err ** 2).mean()):.3g} vs rms logit {rms:.3g}"
