@@ -42,6 +42,12 @@ QWEN3_8B = {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "hidde
             "hidden_size": 4096, "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 12288,
             "vocab_size": 151936, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": False,
             "max_position_embeddings": 40960, "eos_token_id": 151645}
+# the other two benchmark shapes (same options; --shape picks one, the default is the 8B shape the metric is quoted on)
+SHAPES = {
+    "8b": {},
+    "14b": {"num_hidden_layers": 40, "hidden_size": 5120, "num_attention_heads": 40, "intermediate_size": 17408},
+    "32b": {"num_hidden_layers": 64, "hidden_size": 5120, "num_attention_heads": 64, "intermediate_size": 25600},
+}
 REFERENCE_UNAVAILABLE = ("spymaster2h/spyinfer is a C++/xmake project without a Python package: pip cannot install it offline "
                          "(no setup.py or pyproject.toml), xmake is not in the image, and its CUDA path cannot hold a step of 100 or "
                          "more tokens or a cache of more than 400 tokens")
@@ -112,6 +118,7 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the model has (both numbers are reported)")
+    ap.add_argument("--shape", default="8b", choices=sorted(SHAPES), help="Qwen3 layer sizes; the metric is quoted on 8b")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--prefill-tokens", type=int, default=2048)
@@ -133,6 +140,7 @@ def main() -> int:
 
     hbm_gbs, bf16_tflops, peak_src = peaks()
     cfg_json = dict(QWEN3_8B)
+    cfg_json.update(SHAPES[args.shape])
     full_layers = cfg_json["num_hidden_layers"]
     layers = args.layers or full_layers
     cfg_json["num_hidden_layers"] = layers
@@ -248,11 +256,11 @@ def main() -> int:
     step_bytes = weight_bytes + kv_bytes_per_token * (ctx - args.steps // 2) * args.batch
     achieved = step_bytes / (ms_per_step / 1e3) / 1e9
     out = {
-        "metric": "decode tokens/s (Qwen3-8B shape, bf16, batch 8, context 8192)", "value": round(value, 1), "unit": "tokens/s",
+        "metric": f"decode tokens/s (Qwen3-{args.shape.upper()} shape, bf16, batch {args.batch}, context {ctx})", "value": round(value, 1), "unit": "tokens/s",
         "n_gpus": 1, "steps": args.steps, "warmup": warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: seeded random weights, random token ids, random cache contents of the stated context length",
-        "config": {"model": "Qwen3-8B shape", "num_layers": layers, "num_layers_full": full_layers, "hidden_size": H,
+        "config": {"model": f"Qwen3-{args.shape.upper()} shape", "num_layers": layers, "num_layers_full": full_layers, "hidden_size": H,
                    "num_attention_heads": nh, "num_key_value_heads": nkv, "head_dim": hd, "intermediate_size": I, "vocab_size": V,
                    "global_batch": args.batch, "seq_len": ctx, "page_size": page, "parallelism": "single GPU",
                    "l2": "inputs (weights and cache) exceed L2 many times", "peaks": peak_src},
