@@ -13,8 +13,9 @@ what the layers need, and slots for per-request state of fixed size.
   its end.  Entries with a ``StateCacheNeed`` keep ``[entries, slots, *shape]`` tensors that
   are indexed by it; a slot's state is zeroed when the slot is handed out.  An architecture
   without such layers (Qwen3) still gets the slot: the batch carries it.
-* All bookkeeping is host-side and works without a GPU (``device=None``), which is how the
-  CPU tests drive it.
+* All bookkeeping is host-side, in the C++ engine core (``csrc/engine_core.cpp``), and works
+  without a GPU (``device=None``), which is how the CPU tests drive it; this class owns the
+  device tensors and the views.
 
 The reference's counterpart is one free list for all layers and a per-sequence vector
 (spymaster2h/spyinfer src/engine/block_manager.cpp, src/engine/sequence.hpp:29,
@@ -23,6 +24,7 @@ src/engine/scheduler.cpp:24-35, 77-82); it frees only in remove_request
 """
 from __future__ import annotations
 
+import ctypes
 from dataclasses import dataclass
 from typing import Dict, Hashable, List, Optional, Sequence
 
@@ -30,11 +32,10 @@ import numpy as np
 import torch
 
 from ..config.spec import PagedCacheNeed, StateCacheNeed
-from .pages import OutOfPages, PagePool
+from . import core
+from .core import NoFreeSlot, OutOfPages
 
-
-class NoFreeSlot(RuntimeError):
-    pass
+__all__ = ["CacheManager", "CacheView", "NoFreeSlot", "OutOfPages"]
 
 
 @dataclass
@@ -52,19 +53,14 @@ class CacheView:
 
 
 class _PagedGroup:
-    def __init__(self, need: PagedCacheNeed, num_pages: int, max_num_seqs: int, width: int):
+    """A group's need, the run-order entries it serves, its device tensor and a view of its block
+    tables (``[max_num_seqs, width]``, row = state slot), which live in the engine core."""
+
+    def __init__(self, need: PagedCacheNeed):
         self.need = need
-        self.pool = PagePool(num_pages)
         self.entries: List[int] = []
-        self.tables = np.full((max_num_seqs, width), -1, dtype=np.int32)  # row = state slot
+        self.tables: Optional[np.ndarray] = None
         self.pages: Optional[torch.Tensor] = None
-
-
-class _Request:
-    def __init__(self, slot: int):
-        self.slot = slot
-        self.length = 0      # tokens stored (committed)
-        self.reserved = 0    # tokens that have pages
 
 
 class CacheManager:
@@ -99,7 +95,7 @@ class CacheManager:
                 key = need.group_key()
                 if key not in by_key:
                     by_key[key] = len(self.groups)
-                    self.groups.append(_PagedGroup(need, num_pages, max_num_seqs, self.width))
+                    self.groups.append(_PagedGroup(need))
                 g = by_key[key]
                 self._entry_slot_in_group.append(len(self.groups[g].entries))
                 self.groups[g].entries.append(i)
@@ -114,6 +110,14 @@ class CacheManager:
                 self.state_tensors.append(t)
             else:
                 raise TypeError(f"run-order entry {i}: unknown cache need {need!r}")
+        # the bookkeeping (pools, block tables, slots, requests) lives in the C++ engine core
+        self._lib = core.lib()
+        windows = (ctypes.c_int * max(1, len(self.groups)))(*[(-1 if g.need.window is None else int(g.need.window)) for g in self.groups])
+        self._h = self._lib.spy_cache_create(len(self.groups), windows, page_size, num_pages, max_num_seqs, max_model_len)
+        if not self._h:
+            raise ValueError(core.build.last_error("engine_core"))
+        for gi, g in enumerate(self.groups):
+            g.tables = np.ctypeslib.as_array(self._lib.spy_cache_tables(self._h, gi), shape=(max_num_seqs, self.width))
         if device is not None:
             for g in self.groups:
                 n = g.need
@@ -125,8 +129,33 @@ class CacheManager:
                 v.pages = self.groups[v.group].pages[self._entry_slot_in_group[i]]
             if v.kind == "state" and not v.writes and cache_of[i] is not None:
                 v.state = self._views[cache_of[i]].state
-        self._free_slots: List[int] = list(range(max_num_seqs - 1, -1, -1))
-        self._requests: Dict[Hashable, _Request] = {}
+        self._handles: Dict[Hashable, int] = {}    # request ids that are no small integers -> handles of the core
+        self._names: Dict[int, Hashable] = {}
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            self._lib.spy_cache_destroy(self._h)
+            self._h = None
+
+    # ---- request ids ------------------------------------------------------------------------
+    def handle(self, rid) -> int:
+        """The 64-bit handle the core knows a request by: the id itself when it is an integer
+        below 2^62, else a number above that, given out at first use."""
+        if isinstance(rid, int) and not isinstance(rid, bool) and 0 <= rid < (1 << 62):
+            return rid
+        h = self._handles.get(rid)
+        if h is None:
+            h = (1 << 62) + len(self._handles)
+            self._handles[rid] = h
+            self._names[h] = rid
+        return h
+
+    def _record(self, rid):
+        slot, length, reserved = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+        rc = self._lib.spy_cache_request(self._h, self.handle(rid), ctypes.byref(slot), ctypes.byref(length), ctypes.byref(reserved))
+        if rc != 0:
+            raise KeyError(rid)
+        return slot.value, length.value, reserved.value
 
     # ---- sizes -------------------------------------------------------------------------
     @staticmethod
@@ -140,100 +169,81 @@ class CacheManager:
 
     # ---- requests ----------------------------------------------------------------------
     def has_request(self, rid) -> bool:
-        return rid in self._requests
+        return bool(self._lib.spy_cache_has_request(self._h, self.handle(rid)))
 
     def live_requests(self) -> List:
-        return list(self._requests)
+        n = self._lib.spy_cache_num_live(self._h)
+        out = np.empty(max(1, n), dtype=np.int64)
+        n = self._lib.spy_cache_live(self._h, core.i64(out))
+        return [self._names.get(int(h), int(h)) for h in out[:n]]
 
     def num_free_slots(self) -> int:
-        return len(self._free_slots)
+        return self._lib.spy_cache_num_free_slots(self._h)
 
     def num_free_pages(self, group: int = 0) -> int:
-        return self.groups[group].pool.num_free if self.groups else self.num_pages
+        return self._lib.spy_cache_num_free_pages(self._h, group)
 
     def min_free_pages(self) -> int:
-        return min((g.pool.num_free for g in self.groups), default=self.num_pages)
+        return self._lib.spy_cache_min_free_pages(self._h)
 
     def add_request(self, rid) -> int:
-        if rid in self._requests:
+        slot = ctypes.c_int()
+        rc = self._lib.spy_cache_add_request(self._h, self.handle(rid), ctypes.byref(slot))
+        if rc == 2:
             raise ValueError(f"request {rid!r} is already live")
-        if not self._free_slots:
-            raise NoFreeSlot(f"all {self.max_num_seqs} request slots are taken")
-        slot = self._free_slots.pop()
-        self._requests[rid] = _Request(slot)
+        core.check(rc)
+        self.zero_state(slot.value)
+        return slot.value
+
+    def zero_state(self, slot: int) -> None:
+        """A slot that has just been handed out starts from zero state."""
         for t in self.state_tensors:
             if t is not None:
                 t[slot].zero_()
-        return slot
 
     def slot(self, rid) -> int:
-        return self._requests[rid].slot
+        return self._record(rid)[0]
 
     def length(self, rid) -> int:
-        return self._requests[rid].length
-
-    def _first_needed_page(self, g: _PagedGroup, length: int) -> int:
-        """Lowest logical page that a query at position ``length`` or later can still see."""
-        if g.need.window is None:
-            return 0
-        return max(0, length - g.need.window + 1) // self.page_size
+        return self._record(rid)[1]
 
     def pages_needed(self, rid, new_length: int) -> int:
         """Pages (the most over the groups) that ``reserve(rid, new_length)`` would take."""
-        r = self._requests[rid]
-        have = self.pages_for(r.reserved)
-        return max(0, self.pages_for(new_length) - have)
+        pages = ctypes.c_int()
+        if self._lib.spy_cache_pages_needed(self._h, self.handle(rid), int(new_length), ctypes.byref(pages)) != 0:
+            raise KeyError(rid)
+        return pages.value
 
     def can_reserve(self, rid, new_length: int) -> bool:
-        need = self.pages_needed(rid, new_length)
-        return new_length <= self.max_model_len and all(g.pool.num_free >= need for g in self.groups)
+        yes = ctypes.c_int()
+        if self._lib.spy_cache_can_reserve(self._h, self.handle(rid), int(new_length), ctypes.byref(yes)) != 0:
+            raise KeyError(rid)
+        return bool(yes.value)
 
     def reserve(self, rid, new_length: int) -> None:
         """Gives the request the pages its positions ``[reserved, new_length)`` will be stored
         in, in every group.  All or nothing: raises OutOfPages without taking any."""
-        r = self._requests[rid]
-        if new_length > self.max_model_len:
+        rc = self._lib.spy_cache_reserve(self._h, self.handle(rid), int(new_length))
+        if rc == 5:
+            raise KeyError(rid)
+        if rc == 2:
             raise ValueError(f"request {rid!r}: {new_length} tokens exceed max_model_len {self.max_model_len}")
-        if new_length <= r.reserved:
-            return
-        need = self.pages_needed(rid, new_length)
-        for g in self.groups:
-            if g.pool.num_free < need:
-                raise OutOfPages("Out of memory: No free blocks available.")
-        first, last = self.pages_for(r.reserved), self.pages_for(new_length)
-        for g in self.groups:
-            row = g.tables[r.slot]
-            for lp in range(first, last):
-                row[lp] = g.pool.allocate()
-        r.reserved = new_length
+        core.check(rc)
 
     def commit(self, rid, new_length: int) -> None:
         """The step that stored positions up to ``new_length`` has been issued: the request's
         length advances and windowed groups give back the pages no later query can see."""
-        r = self._requests[rid]
-        if new_length > r.reserved:
-            raise ValueError(f"request {rid!r}: commit of {new_length} tokens, only {r.reserved} have pages")
-        if new_length < r.length:
-            raise ValueError(f"request {rid!r}: length cannot shrink from {r.length} to {new_length}")
-        r.length = new_length
-        for g in self.groups:
-            if g.need.window is None:
-                continue
-            row = g.tables[r.slot]
-            for lp in range(self._first_needed_page(g, new_length)):
-                if row[lp] >= 0:
-                    g.pool.free(int(row[lp]))
-                    row[lp] = -1
+        rc = self._lib.spy_cache_commit(self._h, self.handle(rid), int(new_length))
+        if rc == 5:
+            raise KeyError(rid)
+        core.check(rc)
 
     def free_request(self, rid) -> None:
         """Everything the request holds goes back: pages of every group and the slot."""
-        r = self._requests.pop(rid)
-        for g in self.groups:
-            row = g.tables[r.slot]
-            for lp in np.nonzero(row >= 0)[0]:
-                g.pool.free(int(row[lp]))
-            row[:] = -1
-        self._free_slots.append(r.slot)
+        rc = self._lib.spy_cache_free_request(self._h, self.handle(rid))
+        if rc == 5:
+            raise KeyError(rid)
+        core.check(rc)
 
     @property
     def spare_page(self) -> int:
@@ -241,12 +251,20 @@ class CacheManager:
         return self.num_pages
 
     def block_table(self, rid, group: int = 0) -> np.ndarray:
-        return self.groups[group].tables[self._requests[rid].slot]
+        return self.groups[group].tables[self.slot(rid)]
 
-    def gather_block_tables(self, rids: Sequence, group: int, width: Optional[int] = None) -> np.ndarray:
-        slots = [self._requests[r].slot for r in rids]
-        t = self.groups[group].tables[slots]
-        return t if width is None else t[:, :width]
+    def gather_block_tables(self, rids: Sequence, group: int, width: Optional[int] = None, out: Optional[np.ndarray] = None) -> np.ndarray:
+        """The block-table rows of ``rids`` in group ``group``, ``width`` entries each (default: all),
+        into ``out[:len(rids), :width]`` when it is given."""
+        width = self.width if width is None else width
+        handles = np.asarray([self.handle(r) for r in rids], dtype=np.int64)
+        if out is None:
+            out = np.empty((len(rids), width), dtype=np.int32)
+        rc = self._lib.spy_cache_gather(self._h, group, len(rids), core.i64(handles), width, core.i32(out), out.strides[0] // 4)
+        if rc == 5:
+            raise KeyError(core.build.last_error("engine_core"))
+        core.check(rc)
+        return out[:len(rids), :width]
 
     # ---- views for the model --------------------------------------------------------------
     def view(self, entry: int) -> CacheView:
@@ -258,23 +276,4 @@ class CacheManager:
     # ---- checks ------------------------------------------------------------------------------
     def check_invariants(self) -> None:
         """No page is lost, held twice, or both free and held; slots likewise."""
-        for gi, g in enumerate(self.groups):
-            held = []
-            for rid, r in self._requests.items():
-                held += [int(p) for p in g.tables[r.slot] if p >= 0]
-            if len(held) != len(set(held)):
-                raise AssertionError(f"group {gi}: a page is held twice: {sorted(held)}")
-            free = list(g.pool._free)
-            if len(free) != len(set(free)):
-                raise AssertionError(f"group {gi}: a page is on the free list twice")
-            if set(free) & set(held):
-                raise AssertionError(f"group {gi}: pages both free and held: {sorted(set(free) & set(held))}")
-            if len(free) + len(held) != g.pool.num_pages:
-                raise AssertionError(f"group {gi}: {g.pool.num_pages - len(free) - len(held)} pages are lost")
-            live_slots = {r.slot for r in self._requests.values()}
-            for s in range(self.max_num_seqs):
-                if s not in live_slots and (g.tables[s] >= 0).any():
-                    raise AssertionError(f"group {gi}: slot {s} has no request but still names pages")
-        slots = [r.slot for r in self._requests.values()]
-        if len(slots) != len(set(slots)) or set(slots) & set(self._free_slots) or len(slots) + len(self._free_slots) != self.max_num_seqs:
-            raise AssertionError("state slots are lost or held twice")
+        core.check(self._lib.spy_cache_check(self._h))

@@ -3,16 +3,17 @@
 Same behaviour as the reference's BlockManager (spymaster2h/spyinfer
 src/engine/block_manager.cpp:5-42: ids ``0..N-1``, ``allocate`` pops one, ``free`` pushes
 back), which makes a page that was just given back the next one handed out.  Double frees
-and foreign ids are errors here instead of silent corruption.
+and foreign ids are errors here instead of silent corruption.  The pool itself lives in the
+C++ engine core; this class is its handle.
 """
 from __future__ import annotations
 
-from typing import List
+import ctypes
 
+from . import core
+from .core import OutOfPages
 
-class OutOfPages(RuntimeError):
-    """Same condition as the reference's "Out of memory: No free blocks available."
-    (src/engine/block_manager.cpp:20-23)."""
+__all__ = ["OutOfPages", "PagePool"]
 
 
 class PagePool:
@@ -20,27 +21,25 @@ class PagePool:
         if num_pages <= 0:
             raise ValueError(f"a page pool needs at least one page, found {num_pages}")
         self.num_pages = num_pages
-        self._free: List[int] = list(range(num_pages - 1, -1, -1))  # page 0 is handed out first
-        self._is_free = [True] * num_pages
+        self._lib = core.lib()
+        self._h = self._lib.spy_pool_create(num_pages)
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            self._lib.spy_pool_destroy(self._h)
+            self._h = None
 
     @property
     def num_free(self) -> int:
-        return len(self._free)
+        return self._lib.spy_pool_num_free(self._h)
 
     def allocate(self) -> int:
-        if not self._free:
-            raise OutOfPages("Out of memory: No free blocks available.")
-        page = self._free.pop()
-        self._is_free[page] = False
-        return page
+        page = ctypes.c_int()
+        core.check(self._lib.spy_pool_allocate(self._h, ctypes.byref(page)))
+        return page.value
 
     def free(self, page: int) -> None:
-        if not 0 <= page < self.num_pages:
-            raise ValueError(f"page {page} is not of this pool (0..{self.num_pages - 1})")
-        if self._is_free[page]:
-            raise ValueError(f"page {page} is freed twice")
-        self._is_free[page] = True
-        self._free.append(page)
+        core.check(self._lib.spy_pool_free(self._h, int(page)))
 
     def is_free(self, page: int) -> bool:
-        return self._is_free[page]
+        return bool(self._lib.spy_pool_is_free(self._h, int(page)))

@@ -1,7 +1,8 @@
-"""Builds and loads the CUDA kernel modules.
+"""Builds and loads the native modules: the CUDA kernels and the host-side engine core.
 
 Every ``<module>.cu`` in this folder becomes one shared library with a C interface, built
-with nvcc for sm_100a and loaded with ctypes.  A module is built the first time something
+with nvcc for sm_100a and loaded with ctypes; ``engine_core.cpp`` (the cache's bookkeeping,
+the scheduler's decisions and the batch assembly, no CUDA) is built with the host compiler.  A module is built the first time something
 asks for it (or all at once by ``build_all``), into ``_build/`` beside the sources when that
 folder can be written, else into a per-user folder under the system's temporary folder.  A
 library is reused when the hash of its sources, the shared header and the flags is the one
@@ -27,6 +28,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-shared",
               "-Xcompiler", "-fvisibility=default"]
+HOST_MODULES = ["engine_core"]                 # plain C++, built with the host compiler
+HOST_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=default"]
 MODULES = ["embedding", "rmsnorm", "qk_rope_store", "attention_generic", "attention_mma", "attention_tc", "attention_decode", "gemm_simt", "gemm_tcgen05", "swiglu", "sampling"]
 
 _loaded: Dict[str, ctypes.CDLL] = {}
@@ -71,6 +74,13 @@ def _build_dir() -> str:
     return _build_dir_cached
 
 
+def _cxx() -> str:
+    for cand in (os.environ.get("CXX"), shutil.which("g++"), shutil.which("c++"), shutil.which("clang++")):
+        if cand and shutil.which(cand):
+            return shutil.which(cand)
+    raise KernelBuildError("no C++ compiler was found (looked at $CXX, g++, c++, clang++): the engine core cannot be built")
+
+
 def _extra_flags() -> List[str]:
     """More nvcc flags from the environment (``SPYINFER_NVCC_FLAGS``), e.g. ``-DNAME`` switches for experiments."""
     return os.environ.get("SPYINFER_NVCC_FLAGS", "").split()
@@ -78,6 +88,11 @@ def _extra_flags() -> List[str]:
 
 def _source_hash(module: str) -> str:
     h = hashlib.sha256()
+    if module in HOST_MODULES:
+        h.update(" ".join(HOST_FLAGS).encode())
+        with open(os.path.join(HERE, module + ".cpp"), "rb") as f:
+            h.update(f.read())
+        return h.hexdigest()
     h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS + _extra_flags()).encode())
     for name in sorted(os.listdir(HERE)):
         if name.endswith(".cuh") or name.endswith(".h") or name == module + ".cu":
@@ -101,12 +116,16 @@ def _is_current(module: str) -> bool:
 
 
 def _compile(module: str) -> None:
-    src = os.path.join(HERE, module + ".cu")
+    host = module in HOST_MODULES
+    src = os.path.join(HERE, module + (".cpp" if host else ".cu"))
     if not os.path.isfile(src):
-        raise KernelBuildError(f"no kernel module {module!r} ({src} does not exist)")
+        raise KernelBuildError(f"no native module {module!r} ({src} does not exist)")
     so = library_path(module)
     tmp = f"{so}.{os.getpid()}.tmp"
-    cmd = [_nvcc()] + ARCH_FLAGS + NVCC_FLAGS + _extra_flags() + ["-I", HERE, "-o", tmp, src]
+    if host:
+        cmd = [_cxx()] + HOST_FLAGS + ["-o", tmp, src]
+    else:
+        cmd = [_nvcc()] + ARCH_FLAGS + NVCC_FLAGS + _extra_flags() + ["-I", HERE, "-o", tmp, src]
     env = dict(os.environ)
     env.setdefault("TMPDIR", tempfile.gettempdir())
     t0 = time.time()
@@ -115,7 +134,7 @@ def _compile(module: str) -> None:
 
     def ticker():
         while not done.wait(15.0):
-            print(f"[spyinfer_b200] still compiling {module}.cu ({time.time() - t0:.0f} s)", file=sys.stderr, flush=True)
+            print(f"[spyinfer_b200] still compiling {os.path.basename(src)} ({time.time() - t0:.0f} s)", file=sys.stderr, flush=True)
 
     th = threading.Thread(target=ticker, daemon=True)
     th.start()
@@ -124,11 +143,11 @@ def _compile(module: str) -> None:
     if proc.returncode != 0:
         if os.path.exists(tmp):
             os.remove(tmp)
-        raise KernelBuildError(f"nvcc failed on {module}.cu:\n$ {' '.join(cmd)}\n{out}")
+        raise KernelBuildError(f"the compiler failed on {os.path.basename(src)}:\n$ {' '.join(cmd)}\n{out}")
     os.replace(tmp, so)
     with open(so + ".hash", "w") as f:
         f.write(_source_hash(module))
-    print(f"[spyinfer_b200] compiled {module}.cu in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
+    print(f"[spyinfer_b200] compiled {os.path.basename(src)} in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
 
 
 def ensure_built(modules: Iterable[str]) -> None:
@@ -136,15 +155,15 @@ def ensure_built(modules: Iterable[str]) -> None:
     todo = [m for m in dict.fromkeys(modules) if not _is_current(m)]
     if not todo:
         return
-    print(f"[spyinfer_b200] compiling {len(todo)} CUDA kernel module(s) for sm_100a: {', '.join(todo)}", file=sys.stderr, flush=True)
+    print(f"[spyinfer_b200] compiling {len(todo)} native module(s) (CUDA kernels for sm_100a, host core): {', '.join(todo)}", file=sys.stderr, flush=True)
     with ThreadPoolExecutor(max_workers=min(len(todo), os.cpu_count() or 1)) as pool:
         for f in [pool.submit(_compile, m) for m in todo]:
             f.result()
 
 
 def build_all() -> List[str]:
-    ensure_built(MODULES)
-    return [library_path(m) for m in MODULES]
+    ensure_built(MODULES + HOST_MODULES)
+    return [library_path(m) for m in MODULES + HOST_MODULES]
 
 
 def load(module: str) -> ctypes.CDLL:

@@ -10,13 +10,15 @@ the engine above this class here.
 """
 from __future__ import annotations
 
+import ctypes
+
 from typing import List, Optional, Sequence
 
 import numpy as np
 import torch
 
 from .. import kernels
-from ..cache import CacheManager
+from ..cache import CacheManager, core
 from ..config.engine_config import EngineConfig
 from .batch import BatchStager, StepBatch, StepEntry
 from .model import Model
@@ -60,45 +62,49 @@ class ModelRunner:
         return int(min(pages, most))
 
     # ---- the step ----------------------------------------------------------------------------
+    def _fill(self, entries: Sequence[StepEntry]):
+        """The step's flat arrays, assembled by the C++ engine core (``spy_cache_fill_batch``): requests
+        that are new get a slot, pages for the new tokens are reserved, token ids and wanted places
+        are checked.  Returns the arrays (numpy, int32) and the longest context."""
+        cache, lib = self.cache, core.lib()
+        n = len(entries)
+        rids = [e.request for e in entries]
+        fresh = [r for r in rids if not cache.has_request(r)]
+        counts = np.asarray([len(e.tokens) for e in entries] or [0], dtype=np.int32)
+        T = int(counts[:n].sum())
+        try:
+            tokens = np.fromiter((int(t) for e in entries for t in e.tokens), dtype=np.int32, count=T) if T else np.zeros(1, np.int32)
+        except OverflowError:
+            raise StepError(f"a token id of this step is outside the vocabulary of {self.vocab_size}") from None
+        want_start = np.zeros(n + 1, dtype=np.int32)
+        np.cumsum([len(e.want) for e in entries], out=want_start[1:])
+        R = int(want_start[n])
+        want = np.fromiter((int(w) for e in entries for w in e.want), dtype=np.int32, count=R) if R else np.zeros(1, np.int32)
+        handles = np.asarray([cache.handle(r) for r in rids] or [0], dtype=np.int64)
+        token_ids, positions, seq_of_token = (np.empty(max(1, T), dtype=np.int32) for _ in range(3))
+        q_start, ctx_len, slots, logit_rows = np.empty(n + 1, np.int32), np.empty(max(1, n), np.int32), np.empty(max(1, n), np.int32), np.empty(max(1, R), np.int32)
+        t_out, r_out, longest = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+        rc = lib.spy_cache_fill_batch(cache._h, n, core.i64(handles), core.i32(counts), core.i32(tokens), core.i32(want_start), core.i32(want),
+                                      int(self.vocab_size), core.i32(token_ids), core.i32(positions), core.i32(seq_of_token), core.i32(q_start),
+                                      core.i32(ctx_len), core.i32(slots), core.i32(logit_rows), ctypes.byref(t_out), ctypes.byref(r_out),
+                                      ctypes.byref(longest))
+        for r in fresh:                       # slots handed out by this call start from zero state
+            if cache.has_request(r):
+                cache.zero_state(cache.slot(r))
+        if rc == 2:
+            message = core.build.last_error("engine_core")
+            k = int(message.split()[1].rstrip(":")) if message.startswith("entry ") else -1
+            who = f"request {rids[k]!r}: " if 0 <= k < n else ""
+            raise StepError(who + message)
+        core.check(rc)
+        return rids, token_ids[:T], positions[:T], seq_of_token[:T], q_start, ctx_len[:n], slots[:n], logit_rows[:R], longest.value
+
     def build_batch(self, entries: Sequence[StepEntry], pad_tokens: int = 0, pad_seqs: int = 0) -> StepBatch:
         cache = self.cache
-        seen = set()
-        token_ids: List[int] = []
-        positions: List[int] = []
-        seq_of_token: List[int] = []
-        logit_rows: List[int] = []
-        q_start, ctx_len, slots = [0], [], []
-        for s, e in enumerate(entries):
-            if e.request in seen:
-                raise StepError(f"request {e.request!r} appears twice in one step")
-            seen.add(e.request)
-            n = len(e.tokens)
-            if n == 0:
-                raise StepError(f"request {e.request!r} brings no tokens to this step")
-            if not cache.has_request(e.request):
-                cache.add_request(e.request)
-            start = cache.length(e.request)
-            cache.reserve(e.request, start + n)
-            base = len(token_ids)
-            for t in e.tokens:
-                if not 0 <= int(t) < self.vocab_size:
-                    raise StepError(f"request {e.request!r}: token id {t} is outside the vocabulary of {self.vocab_size}")
-            token_ids += [int(t) for t in e.tokens]
-            positions += range(start, start + n)
-            seq_of_token += [s] * n
-            for wpos in e.want:
-                if not 0 <= int(wpos) < n:
-                    raise StepError(f"request {e.request!r}: wanted place {wpos} is not among its {n} tokens")
-                logit_rows.append(base + int(wpos))
-            q_start.append(base + n)
-            ctx_len.append(start + n)
-            slots.append(cache.slot(e.request))
-        rids = [e.request for e in entries]
-        width = max(1, cache.pages_for(max(ctx_len))) if not pad_seqs else cache.width
+        rids, token_ids, positions, seq_of_token, q_start, ctx_len, slots, logit_rows, longest = self._fill(entries)
+        width = max(1, cache.pages_for(longest)) if not pad_seqs else cache.width
         tables = [cache.gather_block_tables(rids, g, width) for g in range(cache.num_groups())]
-        i32 = lambda a: np.asarray(a, dtype=np.int32)
-        return self.stager.stage(i32(token_ids), i32(positions), i32(seq_of_token), i32(q_start), i32(ctx_len), i32(slots),
-                                 i32(logit_rows), tables, pad_tokens, pad_seqs)
+        return self.stager.stage(token_ids, positions, seq_of_token, q_start, ctx_len, slots, logit_rows, tables, pad_tokens, pad_seqs)
 
     def commit(self, entries: Sequence[StepEntry]) -> None:
         for e in entries:
@@ -115,24 +121,19 @@ class ModelRunner:
         """A batch of ``bucket`` one-token rows at fixed device offsets: the entries first, then
         padding rows that read and write only the cache's spare page."""
         cache, S = self.cache, len(entries)
+        for e in entries:
+            if len(e.tokens) != 1:
+                raise StepError(f"request {e.request!r}: a decode step brings one token, found {len(e.tokens)}")
+        rids, tok, pos, _, _, ctx, slot, _, _ = self._fill(entries)
         token_ids = np.zeros(bucket, np.int32)
         positions = np.zeros(bucket, np.int32)
         ctx_len = np.ones(bucket, np.int32)
         slots = np.zeros(bucket, np.int32)
-        for s, e in enumerate(entries):
-            if not cache.has_request(e.request):
-                cache.add_request(e.request)
-            start = cache.length(e.request)
-            cache.reserve(e.request, start + 1)
-            t = int(e.tokens[0])
-            if not 0 <= t < self.vocab_size:
-                raise StepError(f"request {e.request!r}: token id {t} is outside the vocabulary of {self.vocab_size}")
-            token_ids[s], positions[s], ctx_len[s], slots[s] = t, start, start + 1, cache.slot(e.request)
-        rids = [e.request for e in entries]
+        token_ids[:S], positions[:S], ctx_len[:S], slots[:S] = tok, pos, ctx, slot
         tables = []
         for g in range(cache.num_groups()):
             t = np.full((bucket, cache.width), -1, np.int32)
-            t[:S] = cache.gather_block_tables(rids, g)
+            cache.gather_block_tables(rids, g, out=t)
             t[S:, 0] = cache.spare_page
             tables.append(t)
         ar = np.arange(bucket + 1, dtype=np.int32)

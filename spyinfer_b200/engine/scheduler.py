@@ -21,11 +21,14 @@ submission here.
 """
 from __future__ import annotations
 
+import ctypes
 from collections import deque
 from dataclasses import dataclass
 from typing import Deque, List
 
-from ..cache import CacheManager
+import numpy as np
+
+from ..cache import CacheManager, core
 from ..config.engine_config import EngineConfig
 from .sequence import Sequence, SequenceStatus
 
@@ -65,15 +68,6 @@ class Scheduler:
     def has_unfinished(self) -> bool:
         return bool(self.waiting or self.running)
 
-    def _preempt(self, seq: Sequence) -> None:
-        self.running.remove(seq)
-        self.cache.free_request(seq.id)
-        seq.num_computed = 0
-        seq.status = SequenceStatus.WAITING
-        seq.num_preemptions += 1
-        self.num_preemptions += 1
-        self.waiting.appendleft(seq)
-
     def finish(self, seq: Sequence, reason: str) -> None:
         """The request is over: it leaves the running list and gives back what it holds."""
         seq.status, seq.finish_reason = SequenceStatus.FINISHED, reason
@@ -84,57 +78,40 @@ class Scheduler:
 
     def schedule(self) -> List[ScheduledPortion]:
         """The portions of the next step.  Pages for them are reserved; the caller runs them
-        through the step function and reports sampled tokens back."""
-        while True:
-            out = self._schedule_once()
-            if out or not self.running:
-                return out
-            # live requests, yet none can run (prompts in progress hold every page): the
-            # request admitted last gives its pages back and is recomputed later
-            self._preempt(self.running[-1])
+        through the step function and reports sampled tokens back.
 
-    def _schedule_once(self) -> List[ScheduledPortion]:
-        budget = self.config.max_num_batched_tokens
-        cache, ps = self.cache, self.cache.page_size
-        out: List[ScheduledPortion] = []
-        # 1. decoding requests, oldest first
-        for seq in list(self.running):
-            if seq not in self.running or seq.remaining != 1 or budget <= 0:
-                continue
-            while not cache.can_reserve(seq.id, len(seq)) and self.running[-1] is not seq:
-                victim = self.running[-1]
-                out = [p for p in out if p.seq is not victim]   # a victim that already got its token this step loses it
-                self._preempt(victim)
-            if not cache.can_reserve(seq.id, len(seq)):
-                continue                                        # it is the newest itself: it waits (or is preempted above)
-            cache.reserve(seq.id, len(seq))
-            out.append(ScheduledPortion(seq, seq.num_computed, 1, True))
-            budget -= 1
-        # 2. prompts of running requests, in portions
-        for seq in self.running:
-            if seq.remaining <= 1 or budget <= 0:
-                continue
-            fit = (cache.pages_for(seq.num_computed) + cache.min_free_pages()) * ps - seq.num_computed
-            n = min(seq.remaining, budget, fit)
-            if n <= 0:
-                continue
-            cache.reserve(seq.id, seq.num_computed + n)
-            out.append(ScheduledPortion(seq, seq.num_computed, n, seq.num_computed + n == len(seq)))
-            budget -= n
-        # 3. admission, first come first served
-        while self.waiting and budget > 0 and len(self.running) < self.config.max_num_seqs and cache.num_free_slots() > 0:
-            seq = self.waiting[0]
-            n = min(seq.remaining, budget)
-            if cache.pages_for(n) > cache.min_free_pages():
-                fit = cache.min_free_pages() * ps
-                if self.running or fit <= 0:
-                    break                       # wait for running requests to finish and free pages
-                n = min(n, fit)                 # nothing else is running: start with what fits
-            self.waiting.popleft()
-            cache.add_request(seq.id)
-            cache.reserve(seq.id, n)
+        The decision itself (the three rules of the module's header, preemption included) is
+        ``spy_sched_step`` of the C++ engine core, which sees the two queues as arrays of
+        (request, tokens so far, tokens already run) and works on the cache's bookkeeping
+        directly; what it decided is applied to the request records and the queues here."""
+        lib, cache = core.lib(), self.cache
+        run, wait = list(self.running), list(self.waiting)
+        n_run, n_wait = len(run), len(wait)
+        run_ids = np.asarray([cache.handle(q.id) for q in run] or [0], dtype=np.int64)
+        run_len = np.asarray([len(q) for q in run] or [0], dtype=np.int32)
+        run_done = np.asarray([q.num_computed for q in run] or [0], dtype=np.int32)
+        wait_ids = np.asarray([cache.handle(q.id) for q in wait] or [0], dtype=np.int64)
+        wait_len = np.asarray([len(q) for q in wait] or [0], dtype=np.int32)
+        cap = n_run + n_wait + 1
+        out_ids, preempted = np.empty(cap, dtype=np.int64), np.empty(cap, dtype=np.int64)
+        out_start, out_count, out_samples = (np.empty(cap, dtype=np.int32) for _ in range(3))
+        n_out, n_pre, n_adm = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+        core.check(lib.spy_sched_step(cache._h, int(self.config.max_num_batched_tokens), int(self.config.max_num_seqs), n_run, core.i64(run_ids),
+                                      core.i32(run_len), core.i32(run_done), n_wait, core.i64(wait_ids), core.i32(wait_len), core.i64(out_ids),
+                                      core.i32(out_start), core.i32(out_count), core.i32(out_samples), ctypes.byref(n_out), core.i64(preempted),
+                                      ctypes.byref(n_pre), ctypes.byref(n_adm)))
+        by_handle = {cache.handle(q.id): q for q in run + wait}
+        for h in preempted[:n_pre.value]:          # in the order of preemption, each to the very front of the queue
+            seq = by_handle[int(h)]
+            self.running.remove(seq)
+            seq.num_computed = 0
+            seq.status = SequenceStatus.WAITING
+            seq.num_preemptions += 1
+            self.num_preemptions += 1
+            self.waiting.appendleft(seq)
+        for _ in range(n_adm.value):               # the first of the queue as it now stands
+            seq = self.waiting.popleft()
             seq.status = SequenceStatus.RUNNING
             self.running.append(seq)
-            out.append(ScheduledPortion(seq, 0, n, n == len(seq)))
-            budget -= n
-        return out
+            cache.zero_state(cache.slot(seq.id))
+        return [ScheduledPortion(by_handle[int(out_ids[i])], int(out_start[i]), int(out_count[i]), bool(out_samples[i])) for i in range(n_out.value)]
