@@ -266,6 +266,44 @@ class CacheManager:
         core.check(rc)
         return out[:len(rids), :width]
 
+    # ---- the batch arrays of a step -----------------------------------------------------------
+    def assemble(self, rids: Sequence, token_lists: Sequence[Sequence[int]], want_lists: Sequence[Sequence[int]], vocab_size: int):
+        """The flat arrays of one step, made by the engine core (``spy_cache_fill_batch``): request
+        ``rids[i]`` brings ``token_lists[i]`` and wants logits at the places ``want_lists[i]`` among
+        them.  Requests that are new get a slot (zero state), pages for the new tokens are reserved,
+        token ids and wanted places are checked (ValueError names the request).  Returns
+        ``token_ids[T], positions[T], seq_of_token[T], q_start[S + 1], ctx_len[S], state_slot[S],
+        logit_rows[R]`` (numpy int32) and the longest context."""
+        n = len(rids)
+        fresh = [r for r in rids if not self.has_request(r)]
+        counts = np.asarray([len(t) for t in token_lists] or [0], dtype=np.int32)
+        T = int(counts[:n].sum())
+        try:
+            tokens = np.fromiter((int(t) for ts in token_lists for t in ts), dtype=np.int32, count=T) if T else np.zeros(1, np.int32)
+        except OverflowError:
+            raise ValueError(f"a token id of this step is outside the vocabulary of {vocab_size}") from None
+        want_start = np.zeros(n + 1, dtype=np.int32)
+        np.cumsum([len(w) for w in want_lists], out=want_start[1:])
+        R = int(want_start[n])
+        want = np.fromiter((int(w) for ws in want_lists for w in ws), dtype=np.int32, count=R) if R else np.zeros(1, np.int32)
+        handles = np.asarray([self.handle(r) for r in rids] or [0], dtype=np.int64)
+        token_ids, positions, seq_of_token = (np.empty(max(1, T), dtype=np.int32) for _ in range(3))
+        q_start, ctx_len, slots, logit_rows = np.empty(n + 1, np.int32), np.empty(max(1, n), np.int32), np.empty(max(1, n), np.int32), np.empty(max(1, R), np.int32)
+        t_out, r_out, longest = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+        rc = self._lib.spy_cache_fill_batch(self._h, n, core.i64(handles), core.i32(counts), core.i32(tokens), core.i32(want_start), core.i32(want),
+                                            int(vocab_size), core.i32(token_ids), core.i32(positions), core.i32(seq_of_token), core.i32(q_start),
+                                            core.i32(ctx_len), core.i32(slots), core.i32(logit_rows), ctypes.byref(t_out), ctypes.byref(r_out),
+                                            ctypes.byref(longest))
+        for r in fresh:                       # slots handed out by this call start from zero state
+            if self.has_request(r):
+                self.zero_state(self.slot(r))
+        if rc == 2:
+            message = core.build.last_error("engine_core")
+            k = int(message.split()[1].rstrip(":")) if message.startswith("entry ") else -1
+            raise ValueError((f"request {rids[k]!r}: " if 0 <= k < n else "") + message)
+        core.check(rc)
+        return token_ids[:T], positions[:T], seq_of_token[:T], q_start, ctx_len[:n], slots[:n], logit_rows[:R], longest.value
+
     # ---- views for the model --------------------------------------------------------------
     def view(self, entry: int) -> CacheView:
         return self._views[entry]

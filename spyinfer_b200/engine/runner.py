@@ -10,15 +10,13 @@ the engine above this class here.
 """
 from __future__ import annotations
 
-import ctypes
-
 from typing import List, Optional, Sequence
 
 import numpy as np
 import torch
 
 from .. import kernels
-from ..cache import CacheManager, core
+from ..cache import CacheManager
 from ..config.engine_config import EngineConfig
 from .batch import BatchStager, StepBatch, StepEntry
 from .model import Model
@@ -63,41 +61,12 @@ class ModelRunner:
 
     # ---- the step ----------------------------------------------------------------------------
     def _fill(self, entries: Sequence[StepEntry]):
-        """The step's flat arrays, assembled by the C++ engine core (``spy_cache_fill_batch``): requests
-        that are new get a slot, pages for the new tokens are reserved, token ids and wanted places
-        are checked.  Returns the arrays (numpy, int32) and the longest context."""
-        cache, lib = self.cache, core.lib()
-        n = len(entries)
+        """The step's flat arrays (``CacheManager.assemble``, which is the C++ engine core's work)."""
         rids = [e.request for e in entries]
-        fresh = [r for r in rids if not cache.has_request(r)]
-        counts = np.asarray([len(e.tokens) for e in entries] or [0], dtype=np.int32)
-        T = int(counts[:n].sum())
         try:
-            tokens = np.fromiter((int(t) for e in entries for t in e.tokens), dtype=np.int32, count=T) if T else np.zeros(1, np.int32)
-        except OverflowError:
-            raise StepError(f"a token id of this step is outside the vocabulary of {self.vocab_size}") from None
-        want_start = np.zeros(n + 1, dtype=np.int32)
-        np.cumsum([len(e.want) for e in entries], out=want_start[1:])
-        R = int(want_start[n])
-        want = np.fromiter((int(w) for e in entries for w in e.want), dtype=np.int32, count=R) if R else np.zeros(1, np.int32)
-        handles = np.asarray([cache.handle(r) for r in rids] or [0], dtype=np.int64)
-        token_ids, positions, seq_of_token = (np.empty(max(1, T), dtype=np.int32) for _ in range(3))
-        q_start, ctx_len, slots, logit_rows = np.empty(n + 1, np.int32), np.empty(max(1, n), np.int32), np.empty(max(1, n), np.int32), np.empty(max(1, R), np.int32)
-        t_out, r_out, longest = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
-        rc = lib.spy_cache_fill_batch(cache._h, n, core.i64(handles), core.i32(counts), core.i32(tokens), core.i32(want_start), core.i32(want),
-                                      int(self.vocab_size), core.i32(token_ids), core.i32(positions), core.i32(seq_of_token), core.i32(q_start),
-                                      core.i32(ctx_len), core.i32(slots), core.i32(logit_rows), ctypes.byref(t_out), ctypes.byref(r_out),
-                                      ctypes.byref(longest))
-        for r in fresh:                       # slots handed out by this call start from zero state
-            if cache.has_request(r):
-                cache.zero_state(cache.slot(r))
-        if rc == 2:
-            message = core.build.last_error("engine_core")
-            k = int(message.split()[1].rstrip(":")) if message.startswith("entry ") else -1
-            who = f"request {rids[k]!r}: " if 0 <= k < n else ""
-            raise StepError(who + message)
-        core.check(rc)
-        return rids, token_ids[:T], positions[:T], seq_of_token[:T], q_start, ctx_len[:n], slots[:n], logit_rows[:R], longest.value
+            return (rids,) + self.cache.assemble(rids, [e.tokens for e in entries], [e.want for e in entries], self.vocab_size)
+        except ValueError as e:
+            raise StepError(str(e)) from None
 
     def build_batch(self, entries: Sequence[StepEntry], pad_tokens: int = 0, pad_seqs: int = 0) -> StepBatch:
         cache = self.cache

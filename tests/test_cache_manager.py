@@ -150,3 +150,26 @@ def test_random_orders_lose_no_page(seed):
     for rid in list(lengths):
         m.free_request(rid)
     assert m.num_free_pages(0) == 20 and m.num_free_pages(1) == 20 and m.num_free_slots() == 5
+
+
+def test_a_steps_batch_arrays_are_assembled_with_slots_pages_and_checks():
+    """Portions of prompts beside single decoded tokens: the flat arrays, the pages and the errors."""
+    m = manager(page_size=4, num_pages=12)
+    m.add_request("old")
+    m.reserve("old", 6)
+    m.commit("old", 6)
+    tok, pos, seq_of, q_start, ctx, slots, rows, longest = m.assemble(["new", "old"], [[5, 6, 7, 8, 9], [3]], [[0, 4], [0]], vocab_size=10)
+    assert list(tok) == [5, 6, 7, 8, 9, 3] and list(pos) == [0, 1, 2, 3, 4, 6] and list(seq_of) == [0, 0, 0, 0, 0, 1]
+    assert list(q_start) == [0, 5, 6] and list(ctx) == [5, 7] and list(rows) == [0, 4, 5] and longest == 7
+    assert list(slots) == [m.slot("new"), m.slot("old")] and m.has_request("new")
+    assert (m.block_table("new")[:2] >= 0).all() and m.block_table("new")[2] == -1      # five tokens: two pages of four
+    assert m.length("new") == 0 and m.length("old") == 6                                # nothing is committed yet
+    m.check_invariants()
+    for rids, toks, want, what in [(["old", "old"], [[1], [2]], [[], []], "twice"), (["old"], [[]], [[]], "no tokens"),
+                                   (["old"], [[10]], [[0]], "vocabulary"), (["old"], [[-1]], [[0]], "vocabulary"),
+                                   (["old"], [[1, 2]], [[2]], "wanted place")]:
+        with pytest.raises(ValueError, match=what):
+            m.assemble(rids, toks, want, vocab_size=10)
+    with pytest.raises(OutOfPages):
+        m.assemble(["big"], [list(range(9)) * 5], [[]], vocab_size=10)                  # 45 tokens: twelve pages, ten are free
+    m.check_invariants()
