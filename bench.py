@@ -229,7 +229,7 @@ def main() -> int:
             engine.remove_request(r)
         assert n_out == batch * steps, (n_out, batch, steps)
         h2d = 4 * (4 * batch + 3 * batch + 1 + batch * cache.width)
-        return n_out / (ms / 1e3), h2d, 4 * batch
+        return n_out / (ms / 1e3), h2d, 4 * batch + 8     # the sampled tokens and the two words of the status
 
     def prefill(tokens):
         g = torch.Generator().manual_seed(7)

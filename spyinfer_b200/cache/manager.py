@@ -238,6 +238,15 @@ class CacheManager:
             raise KeyError(rid)
         core.check(rc)
 
+    def advance(self, rids: Sequence, counts: Sequence[int]) -> None:
+        """A step has been issued: every request of it is committed at its length plus the tokens it brought."""
+        handles = np.asarray([self.handle(r) for r in rids] or [0], dtype=np.int64)
+        counts = np.asarray(list(counts) or [0], dtype=np.int32)
+        rc = self._lib.spy_cache_advance(self._h, len(rids), core.i64(handles), core.i32(counts))
+        if rc == 5:
+            raise KeyError(core.build.last_error("engine_core"))
+        core.check(rc)
+
     def free_request(self, rid) -> None:
         """Everything the request holds goes back: pages of every group and the slot."""
         rc = self._lib.spy_cache_free_request(self._h, self.handle(rid))

@@ -285,6 +285,20 @@ int spy_cache_commit(void* h, int64_t rid, int new_length)
 
 int spy_cache_free_request(void* h, int64_t rid) { return static_cast<Cache*>(h)->release_request(rid); }
 
+int spy_cache_commit(void* h, int64_t rid, int new_length);
+
+// A step has been issued: every request of it advances by the tokens it brought.
+int spy_cache_advance(void* h, int n, const int64_t* rids, const int32_t* counts)
+{
+    Cache* c = static_cast<Cache*>(h);
+    for (int i = 0; i < n; ++i) {
+        Request* r = c->find(rids[i]);
+        if (!r) return fail(UNKNOWN_REQUEST, "request %lld is not live", (long long)rids[i]);
+        if (int rc = spy_cache_commit(h, rids[i], r->length + counts[i])) return rc;
+    }
+    return OK;
+}
+
 // Rows of group `group`'s block table for n requests, `width` entries each, into out (rows out_stride apart).
 int spy_cache_gather(void* h, int group, int n, const int64_t* rids, int width, int32_t* out, int out_stride)
 {

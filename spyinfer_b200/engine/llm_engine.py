@@ -115,8 +115,7 @@ class LLMEngine:
         sampled = [p.seq for p in portions if p.samples]
         if not sampled:
             return []
-        tokens = self.sampler.sample(logits, [s.sampling for s in sampled], [s.num_generated for s in sampled]).tolist()
-        self.runner.check_status()
+        tokens = self.runner.read_tokens(self.sampler.sample(logits, [s.sampling for s in sampled], [s.num_generated for s in sampled]))
         results = []
         for seq, tok in zip(sampled, tokens):
             seq.tokens.append(int(tok))

@@ -44,6 +44,8 @@ class ModelRunner:
         self.steps = 0
         self.tokens_run = 0
         self.graph_steps = 0
+        self._host_tokens = None
+        self._tokens_copied = torch.cuda.Event()
         self._graphs = {}          # decode batch size (padded) -> (graph, logits, kernel launches it holds)
         self._use_graphs = bool(config.use_cuda_graphs) and model.graph_safe()
 
@@ -76,8 +78,7 @@ class ModelRunner:
         return self.stager.stage(token_ids, positions, seq_of_token, q_start, ctx_len, slots, logit_rows, tables, pad_tokens, pad_seqs)
 
     def commit(self, entries: Sequence[StepEntry]) -> None:
-        for e in entries:
-            self.cache.commit(e.request, self.cache.length(e.request) + len(e.tokens))
+        self.cache.advance([e.request for e in entries], [len(e.tokens) for e in entries])
 
     # ---- decoding through a captured graph -----------------------------------------------------
     def _decode_bucket(self, n: int) -> int:
@@ -164,6 +165,23 @@ class ModelRunner:
         """The request is over: its pages and its slot are given back."""
         if self.cache.has_request(request):
             self.cache.free_request(request)
+
+    def read_tokens(self, tokens: torch.Tensor) -> List[int]:
+        """The sampled tokens of a step on the host, and the status word checked, with one wait for
+        the device: both are copied into pinned memory behind the step's kernels."""
+        n = tokens.shape[0]
+        if self._host_tokens is None or self._host_tokens.shape[0] < n + 2:
+            self._host_tokens = torch.empty(max(n + 2, self.config.max_num_seqs + 2), dtype=torch.int32, pin_memory=True)
+        host = self._host_tokens
+        host[:n].copy_(tokens, non_blocking=True)
+        host[n:n + 2].copy_(self.stager.status, non_blocking=True)
+        self._tokens_copied.record()
+        self._tokens_copied.synchronize()
+        out = host[:n + 2].tolist()
+        if out[n] != 0:
+            self.stager.status.zero_()
+            raise StepError("a kernel refused " + kernels.STATUS_MESSAGES.get(out[n], f"status {out[n]}").format(detail=out[n + 1]))
+        return out[:n]
 
     def check_status(self) -> None:
         """Raises if a kernel of an earlier step met an index that would have left its buffers
