@@ -26,6 +26,7 @@ class EngineConfig:
     dtype: str = "bfloat16"
     device: str = "cuda:0"
     use_cuda_graphs: bool = True
+    lookahead_decode: bool = True     # launch the next decode step before the last one's tokens are read (see LLMEngine.step)
 
     def __post_init__(self):
         if self.dtype not in _DTYPES:

@@ -15,10 +15,12 @@ parameter map (src/engine/llm_engine.cpp:11-16): ``max_num_batched_tokens``,
 """
 from __future__ import annotations
 
+from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence as Seq, Tuple, Union
 
 import torch
 
+from ..cache import OutOfPages
 from ..config import ArchitectureConfig, EngineConfig, load_model_config
 from ..sampling import Sampler, SamplingParams
 from .batch import StepEntry
@@ -26,6 +28,26 @@ from .model import Model
 from .runner import ModelRunner
 from .scheduler import Scheduler
 from .sequence import Sequence, SequenceStatus
+
+
+PLACEHOLDER = -1     # stands in a request's tokens for a token that has been sampled on the device and not read yet
+
+
+@dataclass
+class _InFlight:
+    """A step whose sampled tokens are still on the device."""
+
+    seqs: List[Sequence]
+    places: List[int]        # where in each request's tokens the sampled token goes
+    tokens: torch.Tensor     # int32 [len(seqs)] on the device
+    pending: object          # the queued copy of the tokens to the host (ModelRunner.start_read)
+
+
+def _known(tokens: List[int]) -> List[int]:
+    n = len(tokens)
+    while n > 0 and tokens[n - 1] == PLACEHOLDER:
+        n -= 1
+    return tokens[:n]
 
 
 class LLMEngine:
@@ -56,6 +78,7 @@ class LLMEngine:
         self.eos_token_id = spec.eos_token_id
         self._sequences: Dict[int, Sequence] = {}
         self._next_id = 0
+        self._inflight: Optional[_InFlight] = None
 
     # ---- requests ----------------------------------------------------------------------------
     def add_request(self, prompt_token_ids: Seq[int], sampling_params: Optional[SamplingParams] = None) -> int:
@@ -83,11 +106,11 @@ class LLMEngine:
     def get_output_tokens(self, request_id: int) -> List[int]:
         """Every token of the request, prompt first (as the reference returns them)."""
         seq = self._sequences.get(request_id)
-        return list(seq.tokens) if seq is not None else []
+        return _known(seq.tokens) if seq is not None else []
 
     def get_generated_tokens(self, request_id: int) -> List[int]:
         seq = self._sequences.get(request_id)
-        return seq.output_tokens if seq is not None else []
+        return _known(seq.tokens)[seq.num_prompt_tokens:] if seq is not None else []
 
     def finish_reason(self, request_id: int) -> Optional[str]:
         seq = self._sequences.get(request_id)
@@ -102,11 +125,29 @@ class LLMEngine:
 
     # ---- one step ------------------------------------------------------------------------------
     def step(self) -> List[Tuple[int, int, bool]]:
-        """Schedules and runs one batch.  Returns ``(request id, new token, finished)`` for every
-        request that produced a token in this step."""
+        """Schedules and runs one batch.  Returns ``(request id, new token, finished)`` for the
+        tokens that became known in this call.
+
+        With ``lookahead_decode`` (the default) a step in which every request decodes is launched
+        and left in flight: its tokens are read, and returned, by the next call, AFTER that call has
+        launched the following decode step for the same requests, whose token ids it takes on the
+        device from the sampler's output.  The device then never waits for the host between decode
+        steps.  The following step is launched only when its batch is certain: nothing is waiting, no
+        request of the step in flight ends by ``max_new_tokens`` or ``max_model_len``, pages are
+        free; a request that ends by its end-of-sequence token has then run one token too many,
+        which is dropped.  Everything else (prompts, mixed steps, a changed set of requests) is
+        read before the next step is decided, as without the option."""
+        prev, self._inflight = self._inflight, None
+        results: List[Tuple[int, int, bool]] = []
+        if prev is not None:
+            ahead = self._look_ahead(prev)
+            results = self._absorb(prev, self.runner.finish_read(prev.pending))
+            if ahead is not None:
+                self._inflight = ahead
+                return results
         portions = self.scheduler.schedule()
         if not portions:
-            return []
+            return results
         entries = [StepEntry(p.seq.id, p.seq.tokens[p.start:p.start + p.num_tokens], [p.num_tokens - 1] if p.samples else [])
                    for p in portions]
         logits = self.runner.step(entries)
@@ -114,22 +155,70 @@ class LLMEngine:
             p.seq.num_computed = p.start + p.num_tokens
         sampled = [p.seq for p in portions if p.samples]
         if not sampled:
-            return []
-        tokens = self.runner.read_tokens(self.sampler.sample(logits, [s.sampling for s in sampled], [s.num_generated for s in sampled]))
+            return results
+        flight = self._sample(sampled, logits)
+        if self.config.lookahead_decode and all(p.num_tokens == 1 and p.samples for p in portions):
+            self._inflight = flight
+            return results
+        return results + self._absorb(flight, self.runner.finish_read(flight.pending))
+
+    def _sample(self, seqs: List[Sequence], logits: torch.Tensor) -> "_InFlight":
+        """Samples the next token of every request on the device; each request gets a placeholder
+        where the token will go once it has been read."""
+        tokens = self.sampler.sample(logits, [s.sampling for s in seqs], [s.num_generated for s in seqs])
+        places = []
+        for s in seqs:
+            places.append(len(s.tokens))
+            s.tokens.append(PLACEHOLDER)
+        return _InFlight(seqs, places, tokens, self.runner.start_read(tokens))   # the copy is queued now, ahead of any step launched later
+
+    def _ends_at(self, seq: Sequence, place: int, token: Optional[int]) -> Optional[str]:
+        """Why the request ends with the token at ``place`` (None: it goes on); ``token`` None: not known yet."""
+        if token is not None and token == self.eos_token_id and not seq.sampling.ignore_eos:
+            return "eos"
+        if seq.sampling.max_new_tokens is not None and place + 1 - seq.num_prompt_tokens >= seq.sampling.max_new_tokens:
+            return "max_new_tokens"
+        if place + 1 >= self.config.max_model_len:
+            return "max_model_len"
+        return None
+
+    def _absorb(self, flight: "_InFlight", tokens: List[int]) -> List[Tuple[int, int, bool]]:
+        """The tokens of a step have been read: they take their places, requests that end are finished."""
         results = []
-        for seq, tok in zip(sampled, tokens):
-            seq.tokens.append(int(tok))
-            reason = None
-            if tok == self.eos_token_id and not seq.sampling.ignore_eos:
-                reason = "eos"
-            elif seq.sampling.max_new_tokens is not None and seq.num_generated >= seq.sampling.max_new_tokens:
-                reason = "max_new_tokens"
-            elif len(seq) >= self.config.max_model_len:
-                reason = "max_model_len"
+        for seq, place, tok in zip(flight.seqs, flight.places, tokens):
+            if seq.status == SequenceStatus.FINISHED:
+                continue                                   # it ended while this step was in flight: the token is dropped
+            tok = int(tok)
+            seq.tokens[place] = tok
+            reason = self._ends_at(seq, place, tok)
             if reason is not None:
+                del seq.tokens[place + 1:]                 # the placeholder of a step launched ahead
                 self.scheduler.finish(seq, reason)
-            results.append((seq.id, int(tok), reason is not None))
+            results.append((seq.id, tok, reason is not None))
         return results
+
+    def _look_ahead(self, prev: "_InFlight") -> Optional["_InFlight"]:
+        """Launches the decode step that follows the one in flight, if its batch is certain."""
+        sch = self.scheduler
+        if not self.config.lookahead_decode or sch.waiting or len(sch.running) != len(prev.seqs):
+            return None
+        for seq, place in zip(prev.seqs, prev.places):
+            if seq.status != SequenceStatus.RUNNING or place != len(seq.tokens) - 1 or self._ends_at(seq, place, None) is not None:
+                return None
+        if {id(s) for s in sch.running} != {id(s) for s in prev.seqs}:
+            return None
+        try:
+            logits = self.runner.step([StepEntry(seq.id, [0], [0]) for seq in prev.seqs], tokens_from=prev.tokens)
+        except OutOfPages:
+            return None                                    # the scheduler decides who gives way, once the tokens are known
+        for seq in prev.seqs:
+            seq.num_computed = len(seq.tokens)
+        return self._sample(prev.seqs, logits)
+
+    def drain(self) -> List[Tuple[int, int, bool]]:
+        """Reads the step in flight, if there is one, without launching another."""
+        prev, self._inflight = self._inflight, None
+        return self._absorb(prev, self.runner.finish_read(prev.pending)) if prev is not None else []
 
     # ---- whole generations -----------------------------------------------------------------------
     def generate(self, prompts: Seq[Seq[int]], sampling_params: Union[SamplingParams, Seq[SamplingParams], None] = None) -> List[List[int]]:
@@ -140,6 +229,7 @@ class LLMEngine:
         ids = [self.add_request(p, sp) for p, sp in zip(prompts, sampling_params)]
         while any(not self.is_request_finished(i) for i in ids):
             self.step()
+        self.drain()
         out = [self.get_generated_tokens(i) for i in ids]
         for i in ids:
             self.remove_request(i)

@@ -44,8 +44,9 @@ class ModelRunner:
         self.steps = 0
         self.tokens_run = 0
         self.graph_steps = 0
-        self._host_tokens = None
-        self._tokens_copied = torch.cuda.Event()
+        self._host_tokens = [None, None]
+        self._tokens_copied = [torch.cuda.Event(), torch.cuda.Event()]
+        self._read_turn = 0
         self._graphs = {}          # decode batch size (padded) -> (graph, logits, kernel launches it holds)
         self._use_graphs = bool(config.use_cuda_graphs) and model.graph_safe()
 
@@ -109,10 +110,12 @@ class ModelRunner:
         ar = np.arange(bucket + 1, dtype=np.int32)
         return self.stager.stage(token_ids, positions, ar[:bucket], ar, ctx_len, slots, ar[:bucket], tables, bucket, bucket)
 
-    def _step_graph(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def _step_graph(self, entries: Sequence[StepEntry], tokens_from: Optional[torch.Tensor] = None) -> torch.Tensor:
         S = len(entries)
         bucket = self._decode_bucket(S)
         batch = self._build_decode_batch(entries, bucket)
+        if tokens_from is not None:
+            batch.token_ids[:S].copy_(tokens_from[:S])   # behind the staging copy on the stream, ahead of the kernels
         held = self._graphs.get(bucket)
         if held is None:
             # the first step of this size runs eagerly (it also makes every lazy allocation);
@@ -142,19 +145,27 @@ class ModelRunner:
         self.tokens_run += S
         return logits[:S]
 
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], tokens_from: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Runs the entries as one batch.  Returns float32 logits ``[wanted, vocab]`` on the
         device, rows in the order of the entries and of each entry's ``want``; None when
         nothing is wanted.  A batch in which every request brings one token and wants its
         logits (a decode step) is replayed from a CUDA graph captured for its size; the
-        returned tensor is then the graph's own output buffer, valid until the next step."""
+        returned tensor is then the graph's own output buffer, valid until the next step.
+
+        ``tokens_from`` (int32 on the device, one per entry; every entry brings one token): the token
+        ids are taken from it on the device instead of from the entries, whose tokens only stand in.
+        This is how a decode step is launched before the host knows what the last one sampled."""
         if not entries:
             return None
+        if tokens_from is not None and any(len(e.tokens) != 1 for e in entries):
+            raise StepError("tokens_from needs entries of one token each")
         if self._use_graphs and all(len(e.tokens) == 1 and len(e.want) == 1 and int(e.want[0]) == 0 for e in entries):
             if len({e.request for e in entries}) != len(entries):
                 raise StepError("a request appears twice in one step")
-            return self._step_graph(entries)
+            return self._step_graph(entries, tokens_from)
         batch = self.build_batch(entries)
+        if tokens_from is not None:
+            batch.token_ids.copy_(tokens_from[:batch.num_tokens])
         logits = self.model.forward(batch, self.cache)
         self.commit(entries)
         self.steps += 1
@@ -166,22 +177,33 @@ class ModelRunner:
         if self.cache.has_request(request):
             self.cache.free_request(request)
 
-    def read_tokens(self, tokens: torch.Tensor) -> List[int]:
-        """The sampled tokens of a step on the host, and the status word checked, with one wait for
-        the device: both are copied into pinned memory behind the step's kernels."""
+    def start_read(self, tokens: torch.Tensor):
+        """Queues, behind the kernels launched so far, the copy of a step's sampled tokens and of the
+        status word into pinned memory.  Returns what ``finish_read`` needs.  Two steps may be in
+        flight at a time (the buffers alternate)."""
         n = tokens.shape[0]
-        if self._host_tokens is None or self._host_tokens.shape[0] < n + 2:
-            self._host_tokens = torch.empty(max(n + 2, self.config.max_num_seqs + 2), dtype=torch.int32, pin_memory=True)
-        host = self._host_tokens
+        self._read_turn ^= 1
+        host, event = self._host_tokens[self._read_turn], self._tokens_copied[self._read_turn]
+        if host is None or host.shape[0] < n + 2:
+            host = self._host_tokens[self._read_turn] = torch.empty(max(n + 2, self.config.max_num_seqs + 2), dtype=torch.int32, pin_memory=True)
         host[:n].copy_(tokens, non_blocking=True)
         host[n:n + 2].copy_(self.stager.status, non_blocking=True)
-        self._tokens_copied.record()
-        self._tokens_copied.synchronize()
+        event.record()
+        return host, event, n
+
+    def finish_read(self, pending) -> List[int]:
+        """Waits for a copy queued by ``start_read``; raises if a kernel had refused an index."""
+        host, event, n = pending
+        event.synchronize()
         out = host[:n + 2].tolist()
         if out[n] != 0:
             self.stager.status.zero_()
             raise StepError("a kernel refused " + kernels.STATUS_MESSAGES.get(out[n], f"status {out[n]}").format(detail=out[n + 1]))
         return out[:n]
+
+    def read_tokens(self, tokens: torch.Tensor) -> List[int]:
+        """The sampled tokens of a step on the host, and the status word checked, with one wait for the device."""
+        return self.finish_read(self.start_read(tokens))
 
     def check_status(self) -> None:
         """Raises if a kernel of an earlier step met an index that would have left its buffers

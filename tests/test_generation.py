@@ -138,3 +138,38 @@ def test_command_line_generates(tiny_models):
     assert "steps" in lines[-1]
     bad = subprocess.run([sys.executable, os.path.join(root, "bin", "spyinfer"), "-m", folder, "-b", "cpu"], capture_output=True, text=True)
     assert bad.returncode == 1 and "Invalid backend type" in bad.stderr
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decode_steps_launched_ahead_give_the_same_tokens(dtype, tiny_models):
+    """``lookahead_decode`` launches the next decode step before the last one's tokens are read (their ids
+    stay on the device).  The tokens must be those of the engine that reads every step first: greedy
+    and seeded temperature sampling, requests of different lengths that end at different steps, and a
+    request that ends by its end-of-sequence token, whose one token too many is dropped.  Through
+    ``step()`` every token is reported exactly once, a call later."""
+    from spyinfer_b200 import SamplingParams
+    folder, cfg, weights = tiny_models["d"]
+    rng = np.random.default_rng(9)
+    prompts = [rng.integers(0, cfg["vocab_size"], n).tolist() for n in (3, 17, 40)]
+    params = [SamplingParams(max_new_tokens=25, ignore_eos=True), SamplingParams(max_new_tokens=9, ignore_eos=True),
+              SamplingParams(temperature=0.8, seed=4, max_new_tokens=30, ignore_eos=True)]
+    plain = engine_for(folder, dtype, lookahead_decode=False)
+    ahead = engine_for(folder, dtype, lookahead_decode=True)
+    want = plain.generate(prompts, params)
+    assert ahead.generate(prompts, params) == want
+    assert [len(w) for w in want] == [25, 9, 30]
+    # end of sequence in the middle of decoding
+    eos = want[0][10]
+    first = want[0].index(eos)
+    for engine in (plain, ahead):
+        engine.eos_token_id = eos
+        rid = engine.add_request(prompts[0], SamplingParams(max_new_tokens=25))
+        seen = []
+        while not engine.is_request_finished(rid):
+            seen += [(tok, done) for r, tok, done in engine.step() if r == rid]
+        assert [t for t, _ in seen] == want[0][:first + 1] and [d for _, d in seen] == [False] * first + [True]
+        assert engine.get_generated_tokens(rid) == want[0][:first + 1] and engine.finish_reason(rid) == "eos"
+        engine.remove_request(rid)
+        assert all(r != rid for r, _, _ in engine.drain())     # what was launched ahead for it is dropped
+        engine.runner.cache.check_invariants()
+        assert engine.runner.cache.num_free_slots() == 4 and engine.runner.cache.min_free_pages() == 64
