@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Benchmark of the engine's decode step and prefill on one GPU.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--batch B] [--context C] [--impl ours|reference]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--shape 8b|14b|32b] [--batch B] [--context C] [--impl ours|reference]
 
 The model has the layer sizes of Qwen3-8B (36 layers, hidden 4096, 32 query heads, 8 key/value
 heads, head size 128, intermediate 12288, vocabulary 151936, untied head) with seeded random
@@ -12,8 +12,11 @@ on their content), so no prefill is timed.  One JSON line is printed:
 
 * ``value``: decoded tokens a second, timed with CUDA events around K steps after W warm-up
   steps; between steps the inputs (weights + cache, > 20 GB) are far larger than L2;
-* ``e2e``: the same through the Python entry point ``LLMEngine.step()``: every step copies
-  that step's batch arrays from pinned host memory and reads the sampled tokens back;
+* ``e2e``: the same through the Python entry point ``LLMEngine.step()``: every call copies
+  its step's batch arrays from pinned host memory and reads a step's sampled tokens back (the
+  engine launches a decode step before it has read the step before, so the tokens a call
+  returns are those of the step launched by the call before it; every step's tokens are
+  read, once);
 * ``prefill``: one step of 2048 prompt tokens of one request; ``frac`` = flops / time / peak;
 * ``roofline``: bytes the decode step has to read (every weight it uses once, and the cache
   of the live requests) / its time, against the measured copy bandwidth;
