@@ -462,9 +462,8 @@ def test_qk_rope_store_sums_a_stack_of_partial_products(hd, splits):
 
 @pytest.mark.parametrize("stacked", [False, True])
 def test_qk_rope_store_many_tokens_at_once_equal_few_at_a_time(stacked):
-    """A long prompt portion takes the register path with several (token, head) items per warp; it must
-    give bit for bit what the same tokens give in small portions (one item per warp); 1001 tokens so
-    that the last warps run out of items."""
+    """A long prompt portion through the register path of head size 128 gives bit for bit what the same
+    tokens give in small portions; 1001 tokens so that the last block has warps without an item."""
     from spyinfer_b200 import kernels
     torch.manual_seed(5)
     nh, nkv, hd, page_size, T = 8, 2, 128, 16, 1001
