@@ -104,7 +104,13 @@ static int launch(void* x, const void* delta, int delta_splits, long long delta_
         if (smem > 227 * 1024) SPY_FAIL("rmsnorm: a row of %d elements does not fit in shared memory (limit %d)", len, (227 * 1024) / 4 - 33);
         SPY_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     }
-    int threads = vec ? (len / 4 + 31) / 32 * 32 : len;
+#ifndef SPY_RMS_ELEMS
+#define SPY_RMS_ELEMS 4
+#endif
+    // many rows: fewer threads per row, several 16-byte loads each, more blocks per SM, so that rows in their load
+    // phase overlap rows in their store phase; few rows (decoding): one load per thread, the row spread as wide as it goes
+    const int per_thread = vec ? (n >= 512 ? SPY_RMS_ELEMS * 4 : 4) : 1;
+    int threads = (len / per_thread + 31) / 32 * 32;
     threads = threads < 64 ? 64 : (threads > 1024 ? 1024 : (threads + 31) / 32 * 32);
     spy_launch(kernel, dim3(n), dim3(threads), smem, stream, (TX*)x, (const TD*)delta, delta_splits, delta_split_stride, rows, (const TW*)w, (TO*)out, len, eps,
                                          write_back);
