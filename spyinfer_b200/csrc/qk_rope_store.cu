@@ -120,14 +120,14 @@ __global__ void qk_rope_store_kernel(const TS* src, int src_splits, long long sr
     }
 }
 
-// The common case in one pass over registers: bfloat16 everywhere, head_dim 128, the whole head
-// rotated (or no rotation), one plain input array.  Lane l of the warp that owns a (token, head)
-// holds elements 4l .. 4l + 3 (one 8-byte access); the rotation partner of element j < 64 is
-// element j + 64, which lane l ^ 16 holds, so a shuffle replaces the staging in shared memory.
-// The input is one bfloat16 array or a stack of float split-K partial products, summed in order.
-// A warp takes IPW consecutive (token, head) items (1 as launched) and issues the loads of all of
-// them, in rounds without branches, before it works on the first.
-template <typename TS, typename TW, int IPW>
+// The common case in one pass over registers: bfloat16 output and cache, head_dim 128, the whole
+// head rotated (or no rotation); the input is one bfloat16 array or a stack of float split-K
+// partial products, summed in order.  Half a warp owns a (token, head): lane l of it holds
+// elements 8l .. 8l + 7 (one 16-byte access of bfloat16); the rotation partner of element
+// j < 64 is element j + 64, which lane l ^ 8 holds, so a shuffle replaces the staging in shared
+// memory, and the sum of squares is four shuffles.  All loads of an item (input, position,
+// block table, rotation table) are issued in rounds without branches before the arithmetic.
+template <typename TS, typename TW>
 __global__ void __launch_bounds__(256) qk_rope_store_hd128_kernel(const TS* src, int src_splits, long long src_split_stride, bf16* q_out,
                                                                   long long q_out_stride, int tokens, int nh, int nkv,
                                                                   const TW* __restrict__ q_w, const TW* __restrict__ k_w, float eps,
@@ -138,93 +138,98 @@ __global__ void __launch_bounds__(256) qk_rope_store_hd128_kernel(const TS* src,
 {
     constexpr int HD = 128;
     pdl_enter();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, l = lane & 15;
     const int heads = store ? nh + 2 * nkv : nh;
     const int items = tokens * heads;   // the host refuses batches whose items do not fit 31 bits: 32-bit divisions below
-    const int first = (blockIdx.x * (blockDim.x >> 5) + warp) * IPW;
-    if (first >= items) return;
-    float v[IPW][4];
-    float4 c01[IPW], c23[IPW];
-    bf16* dst[IPW];
-    int kind[IPW], tok[IPW], pos[IPW], seq[IPW], head_of[IPW];
-    // ---- loads of all items, in rounds without branches so that they are in flight together: positions
-    // and inputs first, then what a position leads to (block table, rotation table)
+    const int mine = (blockIdx.x * (blockDim.x >> 5) + warp) * 2 + (lane >> 4);
+    const bool live = mine < items;
+    const int item = min(mine, items - 1);   // an item beyond the end repeats the last one and stores nothing
+    const int t = item / heads, head = item - t * heads;
+    const int kind = head < nh ? 0 : (head < nh + nkv ? 1 : 2);  // q, k, v
+    // ---- round 1: the position and the input
+    const int pos = positions[t];
+    const int seq = kind == 0 ? 0 : seq_of_token[t];
+    const TS* in = src + (size_t)t * (nh + 2 * nkv) * HD + (size_t)head * HD + 8 * l;
+    float v[8];
+    if constexpr (sizeof(TS) == 2) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(in);
+        const uint32_t w4[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-    for (int k = 0; k < IPW; ++k) {
-        const int item = min(first + k, items - 1);   // items beyond the end repeat the last one and store nothing
-        tok[k] = item / heads;
-        head_of[k] = item - tok[k] * heads;
-        kind[k] = head_of[k] < nh ? 0 : (head_of[k] < nh + nkv ? 1 : 2);  // q, k, v
-        pos[k] = positions[tok[k]];
-        seq[k] = kind[k] == 0 ? 0 : seq_of_token[tok[k]];
-        const TS* in = src + (size_t)tok[k] * (nh + 2 * nkv) * HD + (size_t)head_of[k] * HD + 4 * lane;
-        if constexpr (sizeof(TS) == 2) {
-            const uint2 raw = *reinterpret_cast<const uint2*>(in);
-            const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
-            v[k][0] = __low2float(a); v[k][1] = __high2float(a); v[k][2] = __low2float(b); v[k][3] = __high2float(b);
+        for (int i = 0; i < 4; ++i) {
+            const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&w4[i]);
+            v[2 * i] = __low2float(a);
+            v[2 * i + 1] = __high2float(a);
+        }
+    } else {
+        const float4 f0 = *reinterpret_cast<const float4*>(in), f1 = *reinterpret_cast<const float4*>(in + 4);
+        v[0] = f0.x; v[1] = f0.y; v[2] = f0.z; v[3] = f0.w; v[4] = f1.x; v[5] = f1.y; v[6] = f1.z; v[7] = f1.w;
+#pragma unroll 4
+        for (int s = 1; s < src_splits; ++s) {
+            const float4 p0 = *reinterpret_cast<const float4*>(in + (size_t)s * src_split_stride);
+            const float4 p1 = *reinterpret_cast<const float4*>(in + (size_t)s * src_split_stride + 4);
+            v[0] += p0.x; v[1] += p0.y; v[2] += p0.z; v[3] += p0.w; v[4] += p1.x; v[5] += p1.y; v[6] += p1.z; v[7] += p1.w;
+        }
+    }
+    // ---- round 2: what the position leads to
+    const bool in_table = kind != 0 && pos >= 0 && pos / page_size < table_width;
+    const int page = in_table ? block_table[(size_t)seq * table_width + pos / page_size] : -1;
+    const bool rotate = kind != 2 && cos_sin != nullptr;
+    const bool pos_ok = pos >= 0 && pos < table_rows;
+    float4 cs[4];   // (cos, sin) of the pairs 8 (l & 7) .. + 7
+    {
+        const float4* cs4 = reinterpret_cast<const float4*>(cos_sin + (size_t)((rotate && pos_ok) ? pos : 0) * 64 + 8 * (l & 7));
+#pragma unroll
+        for (int i = 0; i < 4; ++i) cs[i] = (rotate && pos_ok) ? cs4[i] : make_float4(1.f, 0.f, 1.f, 0.f);
+    }
+    bf16* dst = nullptr;
+    if (live) {
+        if (kind == 0) {
+            dst = q_out + (size_t)t * q_out_stride + (size_t)head * HD + 8 * l;
+        } else if (page < 0 || page >= num_pages) {
+            if (l == 0) report_status(status, SPY_STATUS_BAD_PAGE, t);
         } else {
-            const float4 f = *reinterpret_cast<const float4*>(in);
-            v[k][0] = f.x; v[k][1] = f.y; v[k][2] = f.z; v[k][3] = f.w;
-#pragma unroll 8
-            for (int s = 1; s < src_splits; ++s) {
-                const float4 part = *reinterpret_cast<const float4*>(in + (size_t)s * src_split_stride);
-                v[k][0] += part.x; v[k][1] += part.y; v[k][2] += part.z; v[k][3] += part.w;
-            }
+            const int kv_head = kind == 1 ? head - nh : head - nh - nkv;
+            dst = pages + ((((size_t)page * 2 + (kind - 1)) * nkv + kv_head) * page_size + pos % page_size) * HD + 8 * l;
+        }
+        if (rotate && !pos_ok) {
+            if (l == 0) report_status(status, SPY_STATUS_BAD_POSITION, t);
+            dst = nullptr;
         }
     }
-    int page[IPW];
+    // ---- norm, rotation, store (both halves of the warp run the shuffles)
+    const TW* w = kind == 0 ? q_w : k_w;
+    if (q_w != nullptr) {
+        float ss = 0.f;
 #pragma unroll
-    for (int k = 0; k < IPW; ++k) {
-        const bool in_table = kind[k] != 0 && pos[k] >= 0 && pos[k] / page_size < table_width;
-        page[k] = in_table ? block_table[(size_t)seq[k] * table_width + pos[k] / page_size] : -1;
-        const bool rotate = kind[k] != 2 && cos_sin != nullptr && pos[k] >= 0 && pos[k] < table_rows;
-        const float4* cs4 = reinterpret_cast<const float4*>(cos_sin + (size_t)(rotate ? pos[k] : 0) * 64 + 4 * (lane & 15));
-        c01[k] = rotate ? cs4[0] : make_float4(1.f, 0.f, 1.f, 0.f);   // (cos, sin) of pairs j, j+1
-        c23[k] = rotate ? cs4[1] : make_float4(1.f, 0.f, 1.f, 0.f);   // and of pairs j+2, j+3
-    }
+        for (int i = 0; i < 8; ++i) ss += v[i] * v[i];
 #pragma unroll
-    for (int k = 0; k < IPW; ++k) {
-        dst[k] = nullptr;
-        if (first + k >= items) continue;
-        if (kind[k] == 0) {
-            dst[k] = q_out + (size_t)tok[k] * q_out_stride + (size_t)head_of[k] * HD + 4 * lane;
-        } else if (page[k] < 0 || page[k] >= num_pages) {
-            if (lane == 0) report_status(status, SPY_STATUS_BAD_PAGE, tok[k]);
-        } else {
-            const int kv_head = kind[k] == 1 ? head_of[k] - nh : head_of[k] - nh - nkv;
-            dst[k] = pages + ((((size_t)page[k] * 2 + (kind[k] - 1)) * nkv + kv_head) * page_size + pos[k] % page_size) * HD + 4 * lane;
-        }
-        if (kind[k] != 2 && cos_sin != nullptr && (pos[k] < 0 || pos[k] >= table_rows)) {
-            if (lane == 0) report_status(status, SPY_STATUS_BAD_POSITION, tok[k]);
-            dst[k] = nullptr;
-        }
-    }
-    // ---- norm, rotation, store
-#pragma unroll
-    for (int k = 0; k < IPW; ++k) {
-        if (dst[k] == nullptr) continue;   // uniform over the warp
-        const TW* w = kind[k] == 0 ? q_w : k_w;
-        if (kind[k] != 2 && w != nullptr) {
-            float ss = v[k][0] * v[k][0] + v[k][1] * v[k][1] + v[k][2] * v[k][2] + v[k][3] * v[k][3];
-            ss = warp_sum(ss);
+        for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (kind != 2) {
             const float inv = 1.0f / sqrtf(ss / (float)HD + eps);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) v[k][i] = (inv * v[k][i]) * to_f32(w[4 * lane + i]);
+            for (int i = 0; i < 8; ++i) v[i] = (inv * v[i]) * to_f32(w[8 * l + i]);
         }
-        if (kind[k] != 2 && cos_sin != nullptr) {
-            const float cs_c[4] = {c01[k].x, c01[k].z, c23[k].x, c23[k].z}, cs_s[4] = {c01[k].y, c01[k].w, c23[k].y, c23[k].w};
+    }
+    if (cos_sin != nullptr) {
+        const float c[8] = {cs[0].x, cs[0].z, cs[1].x, cs[1].z, cs[2].x, cs[2].z, cs[3].x, cs[3].z};
+        const float sn[8] = {cs[0].y, cs[0].w, cs[1].y, cs[1].w, cs[2].y, cs[2].w, cs[3].y, cs[3].w};
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float other = __shfl_xor_sync(0xffffffffu, v[k][i], 16);
-                // lanes 0..15 hold the low half (x_j), lanes 16..31 the high half (x_{j + 64})
-                v[k][i] = lane < 16 ? v[k][i] * cs_c[i] - other * cs_s[i] : other * cs_s[i] + v[k][i] * cs_c[i];
-            }
+        for (int i = 0; i < 8; ++i) {
+            const float other = __shfl_xor_sync(0xffffffffu, v[i], 8);
+            // lanes 0..7 of the half hold the low half (x_j), lanes 8..15 the high half (x_{j + 64})
+            const float r = l < 8 ? v[i] * c[i] - other * sn[i] : other * sn[i] + v[i] * c[i];
+            if (rotate) v[i] = r;
         }
-        __nv_bfloat162 o0 = __floats2bfloat162_rn(v[k][0], v[k][1]), o1 = __floats2bfloat162_rn(v[k][2], v[k][3]);
-        uint2 outv;
-        outv.x = *reinterpret_cast<uint32_t*>(&o0);
-        outv.y = *reinterpret_cast<uint32_t*>(&o1);
-        *reinterpret_cast<uint2*>(dst[k]) = outv;
+    }
+    if (dst != nullptr) {
+        uint4 outv;
+        uint32_t* o = reinterpret_cast<uint32_t*>(&outv);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __nv_bfloat162 p = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+            o[i] = *reinterpret_cast<uint32_t*>(&p);
+        }
+        *reinterpret_cast<uint4*>(dst) = outv;
     }
 }
 
@@ -270,16 +275,14 @@ extern "C" int spy_qk_rope_store(const void* src, int src_dtype, int src_splits,
     const bool plain_bf16 = src_dtype == SPY_BF16 && src_splits == 1;
     const bool float_stack = src_dtype == SPY_F32 && src_split_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0 && q_out != src;
     if ((plain_bf16 || float_stack) && q_dtype == SPY_BF16 && (!store || cache_dtype == SPY_BF16) && hd == 128 &&
-        (cos_sin == nullptr || rot_half == 64) && q_out_stride % 4 == 0 &&
-        ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(pages)) & 7) == 0) {
+        (cos_sin == nullptr || rot_half == 64) && q_out_stride % 8 == 0 &&
+        ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(pages)) & 15) == 0) {
         const int heads = store ? nh + 2 * nkv : nh;
         const long long items = (long long)tokens * heads;
-        // one item per warp: four per warp with their loads in flight together measured slower
-        // (42 against 28 microseconds at 2,048 tokens of 48 heads), the SM holds enough warps as it is
-        const long long blocks = (items + 7) / 8;
-        if (items + 8 > 0x7fffffffLL) SPY_FAIL("qk_rope_store: %lld work items exceed the kernel's 31-bit counters", items);
+        const long long blocks = (items + 15) / 16;   // two items per warp, eight warps per block
+        if (items + 16 > 0x7fffffffLL) SPY_FAIL("qk_rope_store: %lld work items exceed the kernel's 31-bit counters", items);
 #define SPY_QK_HD128(TS_, splits_, stride_)                                                                                            \
-    spy_launch(qk_rope_store_hd128_kernel<TS_, TW, 1>, dim3((int)blocks), dim3(256), 0, stream, (const TS_*)src, splits_, stride_,      \
+    spy_launch(qk_rope_store_hd128_kernel<TS_, TW>, dim3((int)blocks), dim3(256), 0, stream, (const TS_*)src, splits_, stride_,         \
                (bf16*)q_out, q_out_stride, tokens, nh, nkv, (const TW*)q_w, (const TW*)k_w, eps, (const float2*)cos_sin, table_rows,    \
                positions, seq_of_token, block_table, table_width, (bf16*)pages, page_size, num_pages, store, status)
         SPY_DISPATCH_DTYPE(w_dtype, TW, {
