@@ -173,3 +173,22 @@ def test_decode_steps_launched_ahead_give_the_same_tokens(dtype, tiny_models):
         assert all(r != rid for r, _, _ in engine.drain())     # what was launched ahead for it is dropped
         engine.runner.cache.check_invariants()
         assert engine.runner.cache.num_free_slots() == 4 and engine.runner.cache.min_free_pages() == 64
+
+
+def test_launching_ahead_gives_way_when_pages_run_out(tiny_models):
+    """A pool so small that requests are preempted: the step launched ahead finds no page, the
+    scheduler decides who gives way once the tokens are known, and the tokens are those of the engine
+    that never launches ahead."""
+    from spyinfer_b200 import SamplingParams
+    folder, cfg, weights = tiny_models["b"]
+    rng = np.random.default_rng(21)
+    prompts = [rng.integers(0, cfg["vocab_size"], n).tolist() for n in (30, 11, 45, 8, 27, 19)]
+    sp = [SamplingParams(max_new_tokens=n, ignore_eos=True, temperature=t, seed=3) for n, t in ((30, 0.0), (22, 0.7), (17, 0.0), (30, 0.0), (9, 1.1), (25, 0.0))]
+    outs = []
+    for ahead in (False, True):
+        engine = engine_for(folder, "float32", num_kvcache_blocks=9, max_num_batched_tokens=24, lookahead_decode=ahead)
+        outs.append(engine.generate(prompts, sp))
+        assert engine.scheduler.num_preemptions > 0, "the pool was meant to be too small"
+        engine.runner.cache.check_invariants()
+        assert engine.runner.cache.min_free_pages() == 9 and engine.runner.cache.num_free_slots() == 4
+    assert outs[0] == outs[1] and [len(o) for o in outs[0]] == [30, 22, 17, 30, 9, 25]
