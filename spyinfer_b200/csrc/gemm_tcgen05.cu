@@ -456,6 +456,154 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const 
     }
 }
 
+// The product for many tokens on PAIRS of blocks (cta_group::2): a cluster of two blocks on
+// neighbouring SMs computes one 256 x 256 tile.  Each block loads its 128 rows of X and its 128 of
+// the tile's 256 rows of Y (a third less shared-memory fill per flop than 128 x 256 tiles of
+// single blocks), the leader (rank 0) issues tcgen05.mma.cta_group::2 instructions of 256 x 256 x 16
+// that read both blocks' shared memory and accumulate each block's 128 rows in its own tensor
+// memory; both blocks' four epilogue warps read their halves back.  Barriers: the TMA loads of
+// both blocks complete on the LEADER's full barrier (no multicast of data; the barrier operand is
+// the leader's, which cta_group::2 loads allow); a commit with cluster multicast frees a stage,
+// and publishes an accumulator, in both blocks; the peer's epilogue threads arrive on the
+// leader's accumulator-empty barrier through the cluster's shared window.  Persistent: cluster c
+// walks tiles c, c + clusters, ...; two accumulators (2 x 256 columns) as in the kernel above.
+constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_X_BYTES = BM * BK * 2;                    // 128 rows of X
+constexpr int PAIR_STAGE_BYTES = 2 * PAIR_X_BYTES;           // and 128 rows of Y
+constexpr size_t PAIR_SMEM = (size_t)PAIR_STAGES * PAIR_STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+
+template <typename TC, int EPI>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, TC* __restrict__ out,
+                         long long ld, int x_rows, int y_rows, int k_blocks, int x_tiles, int num_tiles, int* status)
+{
+    constexpr int BN = 256;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* tiles = smem;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)PAIR_STAGES * PAIR_STAGE_BYTES);   // the leader's are used
+    uint64_t* empty_bar = full_bar + PAIR_STAGES;   // every block's own
+    uint64_t* acc_full = empty_bar + PAIR_STAGES;   // [2] every block's own
+    uint64_t* acc_empty = acc_full + 2;             // [2] the leader's are used: 256 arrivals
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int cluster = blockIdx.x >> 1, clusters = gridDim.x >> 1;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < PAIR_STAGES; ++s) {
+            mbar_init(full_bar + s, 1);
+            mbar_init(empty_bar + s, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(acc_full + b, 1);
+            mbar_init(acc_empty + b, 256);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc_pair(tmem_slot, 2u * BN);
+    fence_before_sync();
+    __syncthreads();
+    cluster_sync();   // both blocks' barriers are initialised and their tensor memory is allocated before either is used from the other side
+    fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    pdl_launch_dependents();
+    if (warp == 0) {
+        if (lane == 0) {
+            pdl_wait();
+            long long g = 0;
+            bool ok = true;
+            for (int tile = cluster; tile < num_tiles && ok; tile += clusters) {
+                const int x0 = (tile % x_tiles) * (2 * BM) + (int)rank * BM, y0 = (tile / x_tiles) * BN + (int)rank * (BN / 2);
+                for (int kb = 0; kb < k_blocks; ++kb, ++g) {
+                    const int s = (int)(g % PAIR_STAGES);
+                    const uint32_t phase = (uint32_t)(g / PAIR_STAGES) & 1;
+                    if (g >= PAIR_STAGES && !mbar_wait(empty_bar + s, phase ^ 1, abort_flag)) { ok = false; break; }
+                    uint8_t* xs = tiles + (size_t)s * PAIR_STAGE_BYTES;
+                    if (rank == 0) mbar_expect_tx(full_bar + s, 2 * PAIR_STAGE_BYTES);   // both blocks' bytes
+                    const uint32_t leader_full = map_to_rank(smem_u32(full_bar + s), 0);
+                    tma_load_2d_pair(smem_u32(xs), &map_x, kb * BK, x0, leader_full);
+                    tma_load_2d_pair(smem_u32(xs + PAIR_X_BYTES), &map_y, kb * BK, y0, leader_full);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc = instr_desc_bf16(2 * BM, BN, false, false);
+            long long g = 0;
+            int i = 0;
+            bool ok = true;
+            for (int tile = cluster; tile < num_tiles && ok; tile += clusters, ++i) {
+                const int buf = i & 1;
+                const uint32_t aph = (uint32_t)(i >> 1) & 1;
+                if (i >= 2) ok = mbar_wait(acc_empty + buf, aph ^ 1, abort_flag);   // both blocks' epilogues have read this buffer's last tile
+                if (!ok) break;
+                fence_after_sync();
+                const uint32_t acc = tmem_base + (uint32_t)buf * BN;
+                for (int kb = 0; kb < k_blocks; ++kb, ++g) {
+                    const int s = (int)(g % PAIR_STAGES);
+                    const uint32_t phase = (uint32_t)(g / PAIR_STAGES) & 1;
+                    ok = mbar_wait(full_bar + s, phase, abort_flag);
+                    if (!ok) break;
+                    fence_after_sync();
+                    const uint8_t* xs = tiles + (size_t)s * PAIR_STAGE_BYTES;
+                    const uint64_t dx = desc_k_major(smem_u32(xs)), dy = desc_k_major(smem_u32(xs + PAIR_X_BYTES));
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        const uint64_t adv = (uint64_t)((k * UMMA_K * 2) >> 4);
+                        umma_pair(acc, dx + adv, dy + adv, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit_pair(empty_bar + s);
+                }
+                if (ok) umma_commit_pair(acc_full + buf);
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        pdl_wait();   // the output buffer may still be in use by a kernel ahead in the stream
+        int i = 0;
+        bool ok = true;
+        for (int tile = cluster; tile < num_tiles && ok; tile += clusters, ++i) {
+            const int buf = i & 1;
+            const uint32_t aph = (uint32_t)(i >> 1) & 1;
+            const int x0 = (tile % x_tiles) * (2 * BM) + (int)rank * BM, y0 = (tile / x_tiles) * BN;
+            ok = mbar_wait(acc_full + buf, aph, abort_flag);
+            if (!ok) break;
+            fence_after_sync();
+            const int x = x0 + quarter * 32 + lane;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                uint32_t r[32];
+                tmem_load<32>(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c), r);
+                tmem_wait_ld();
+                store_chunk_normal<TC, EPI>(out, ld, x, y0 + c, x_rows, y_rows, r);
+            }
+            fence_before_sync();
+            if (rank == 0) mbar_arrive(acc_empty + buf);
+            else mbar_arrive_cluster(map_to_rank(smem_u32(acc_empty + buf), 0));
+        }
+    }
+
+    fence_before_sync();
+    __syncthreads();
+    if (*abort_flag) {
+        if (threadIdx.x == 0) {
+            const unsigned long long t0 = global_timer();
+            while (global_timer() - t0 < 2000000ull) { }
+            report_status(status, SPY_STATUS_WAIT_TIMEOUT, (int)blockIdx.x);
+        }
+        __syncthreads();
+    }
+    cluster_sync();   // neither block leaves (and frees tensor memory the pair shares) while the other may still use it
+    if (warp == 1) {
+        fence_after_sync();
+        tmem_dealloc_pair(tmem_base, 2u * BN);
+    }
+}
+
 // Sums the splits of a scratch buffer in ascending order and stores the output type.
 template <typename TC>
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, TC* __restrict__ out, long long elems, int splits)
@@ -517,6 +665,17 @@ namespace {
 // comes as close to the slots as it can; among the ways to split K the cheapest by a small
 // model wins (work per block, a fixed cost per block, a cost per split for the partial sums
 // the consumer has to add).  The choice depends on N, K and the class of M only.
+// SPYINFER_GEMM_PAIRS=0 in the environment keeps the products for many tokens on single blocks.
+bool pair_kernel_enabled()
+{
+    static int enabled = -1;
+    if (enabled < 0) {
+        const char* e = getenv("SPYINFER_GEMM_PAIRS");
+        enabled = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    return enabled == 1;
+}
+
 struct Plan {
     int splits, tile_rows;
 };
@@ -616,6 +775,50 @@ extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, 
     const long long ld = splits > 1 ? N : ldc;
     const long long split_stride = splits > 1 ? (long long)M * N : 0;
     const bool f32_out = splits > 1 || c_dtype == SPY_F32;
+    if (!swap && splits == 1 && M >= 512 && pair_kernel_enabled()) {
+        // many tokens, one pass over K, at least two 256-row tiles: pairs of blocks on 256 x 256 tiles
+        CUtensorMap my_half;
+        if (make_map(&my_half, W, N, K, ldw, BM)) return 1;
+        const int x_tiles = (M + 2 * BM - 1) / (2 * BM), y_tiles = (N + 255) / 256;
+        const long long num_tiles = (long long)x_tiles * y_tiles;
+        if (num_tiles > 0x7fffffffLL) SPY_FAIL("gemm_tcgen05: %lld tiles exceed the kernel's range", num_tiles);
+        static int clusters_max = 0;
+        if (clusters_max == 0) {
+            SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<bf16, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PAIR_SMEM));
+            SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<float, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PAIR_SMEM));
+            SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<bf16, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PAIR_SMEM));
+            int dev = 0, sms = 0;
+            SPY_CUDA(cudaGetDevice(&dev));
+            SPY_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(sms / 2 * 2);
+            cfg.blockDim = dim3(NUM_THREADS);
+            cfg.dynamicSmemBytes = PAIR_SMEM;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = 2;
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            int active = 0;
+            SPY_CUDA(cudaOccupancyMaxActiveClusters(&active, gemm_tcgen05_pair_kernel<bf16, 0>, &cfg));
+            if (active <= 0) SPY_FAIL("gemm_tcgen05: no cluster of two blocks fits the device");
+            clusters_max = active < sms / 2 ? active : sms / 2;
+        }
+        const int clusters = (int)(num_tiles < clusters_max ? num_tiles : clusters_max);
+        if (epilogue == 1)
+            spy_launch_cluster(gemm_tcgen05_pair_kernel<bf16, 1>, dim3(2 * clusters), dim3(NUM_THREADS), PAIR_SMEM, stream, 2u, mx, my_half, (bf16*)C, ldc,
+                               M, N, k_blocks, x_tiles, (int)num_tiles, status);
+        else if (c_dtype == SPY_F32)
+            spy_launch_cluster(gemm_tcgen05_pair_kernel<float, 0>, dim3(2 * clusters), dim3(NUM_THREADS), PAIR_SMEM, stream, 2u, mx, my_half, (float*)C, ldc,
+                               M, N, k_blocks, x_tiles, (int)num_tiles, status);
+        else
+            spy_launch_cluster(gemm_tcgen05_pair_kernel<bf16, 0>, dim3(2 * clusters), dim3(NUM_THREADS), PAIR_SMEM, stream, 2u, mx, my_half, (bf16*)C, ldc,
+                               M, N, k_blocks, x_tiles, (int)num_tiles, status);
+        SPY_CHECK_LAUNCH("gemm_tcgen05 (pairs)");
+        return 0;
+    }
     if (!swap && splits == 1) {
         // many tokens, one pass over K: the persistent kernel (one block per SM)
         static int num_sms = 0;

@@ -387,7 +387,8 @@ def test_attention_mma_finds_one_far_key(split_keys):
         assert hit == inside, f"window {window}, far key {far}: expected {'a hit' if inside else 'no hit'}"
 
 
-@pytest.mark.parametrize("M,I,K", [(3, 100, 64), (16, 328, 200), (40, 1000, 136), (64, 6144, 512), (130, 520, 264), (300, 12288, 1024)])
+@pytest.mark.parametrize("M,I,K", [(3, 100, 64), (16, 328, 200), (40, 1000, 136), (64, 6144, 512), (130, 520, 264), (300, 12288, 1024),
+                                   (520, 1000, 136), (1100, 2304, 512)])   # 512 rows and more: pairs of blocks on 256 x 256 tiles
 def test_gemm_tcgen05_swiglu_epilogue(M, I, K):
     """Gate and up rows interleaved in the weight; the product's epilogue applies SwiGLU."""
     from spyinfer_b200 import kernels
