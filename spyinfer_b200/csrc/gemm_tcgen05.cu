@@ -513,12 +513,26 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
     pdl_launch_dependents();
     if (warp == 0) {
         if (lane == 0) {
-            pdl_wait();
             long long g = 0;
-            bool ok = true;
+            bool ok = true, first = true;
             for (int tile = cluster; tile < num_tiles && ok; tile += clusters) {
                 const int x0 = (tile % x_tiles) * (2 * BM) + (int)rank * BM, y0 = (tile / x_tiles) * BN + (int)rank * (BN / 2);
-                for (int kb = 0; kb < k_blocks; ++kb, ++g) {
+                int kb = 0;
+                if (first) {
+                    // the weights (Y) of the first stages are requested before the wait for the kernels ahead in the stream
+                    const int pre = min(k_blocks, PAIR_STAGES);
+                    for (int i = 0; i < pre; ++i) {
+                        if (rank == 0) mbar_expect_tx(full_bar + i, 2 * PAIR_STAGE_BYTES);
+                        tma_load_2d_pair(smem_u32(tiles + (size_t)i * PAIR_STAGE_BYTES + PAIR_X_BYTES), &map_y, i * BK, y0, map_to_rank(smem_u32(full_bar + i), 0));
+                    }
+                    pdl_wait();
+                    for (int i = 0; i < pre; ++i)
+                        tma_load_2d_pair(smem_u32(tiles + (size_t)i * PAIR_STAGE_BYTES), &map_x, i * BK, x0, map_to_rank(smem_u32(full_bar + i), 0));
+                    kb = pre;
+                    g = pre;
+                    first = false;
+                }
+                for (; kb < k_blocks; ++kb, ++g) {
                     const int s = (int)(g % PAIR_STAGES);
                     const uint32_t phase = (uint32_t)(g / PAIR_STAGES) & 1;
                     if (g >= PAIR_STAGES && !mbar_wait(empty_bar + s, phase ^ 1, abort_flag)) { ok = false; break; }
@@ -529,6 +543,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
                     tma_load_2d_pair(smem_u32(xs + PAIR_X_BYTES), &map_y, kb * BK, y0, leader_full);
                 }
             }
+            if (first) pdl_wait();
         }
     } else if (warp == 1) {
         if (lane == 0 && rank == 0) {
