@@ -436,29 +436,47 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
 #pragma unroll
                         for (int i = 0; i < CPL; ++i) acc[n][i] = 0.f;
                     }
-                    // one pass in block order; the running maximum rescales what has been added so far
-#pragma unroll 4
-                    for (int c = c_first; c <= c_last; ++c) {
+                    // one pass in block order; the running maximum rescales what has been added so far.
+                    // The loads of CH parts are issued together (a part beyond the last reads the last
+                    // one again and counts for nothing), so a pair of two to four parts costs one
+                    // round trip to L2 instead of one per part.
+                    constexpr int CH = GN <= 4 ? 4 : (GN <= 8 ? 2 : 1);
+                    for (int c0 = c_first; c0 <= c_last; c0 += CH) {
+                        float2 ml[CH][GN];
+                        float part[CH][GN][CPL];
 #pragma unroll
-                        for (int n = 0; n < GN; ++n) {
-                            if (n < p.G) {
-                                const size_t sl = (size_t)c * p.G + n;
-                                const float2 ml = __ldcg(reinterpret_cast<const float2*>(ml0 + sl * 2));
-                                float part[CPL];
-                                if constexpr (CPL == 4) {
-                                    const float4 v = __ldcg(reinterpret_cast<const float4*>(o0 + sl * HD));
-                                    part[0] = v.x; part[1] = v.y; part[2] = v.z; part[3] = v.w;
-                                } else {
-                                    const float2 v = __ldcg(reinterpret_cast<const float2*>(o0 + sl * HD));
-                                    part[0] = v.x; part[1] = v.y;
+                        for (int j = 0; j < CH; ++j) {
+                            const int c = min(c0 + j, c_last);
+#pragma unroll
+                            for (int n = 0; n < GN; ++n) {
+                                if (n < p.G) {
+                                    const size_t sl = (size_t)c * p.G + n;
+                                    ml[j][n] = __ldcg(reinterpret_cast<const float2*>(ml0 + sl * 2));
+                                    if constexpr (CPL == 4) {
+                                        const float4 v = __ldcg(reinterpret_cast<const float4*>(o0 + sl * HD));
+                                        part[j][n][0] = v.x; part[j][n][1] = v.y; part[j][n][2] = v.z; part[j][n][3] = v.w;
+                                    } else {
+                                        const float2 v = __ldcg(reinterpret_cast<const float2*>(o0 + sl * HD));
+                                        part[j][n][0] = v.x; part[j][n][1] = v.y;
+                                    }
                                 }
-                                const float m_new = fmaxf(M[n], ml.x);
-                                const float keep = M[n] == -INFINITY ? 0.f : exp2f(M[n] - m_new);
-                                const float f = ml.x == -INFINITY ? 0.f : exp2f(ml.x - m_new);
-                                M[n] = m_new;
-                                L[n] = L[n] * keep + ml.y * f;
+                            }
+                        }
 #pragma unroll
-                                for (int i = 0; i < CPL; ++i) acc[n][i] = acc[n][i] * keep + part[i] * f;
+                        for (int j = 0; j < CH; ++j) {
+                            const bool live = c0 + j <= c_last;
+#pragma unroll
+                            for (int n = 0; n < GN; ++n) {
+                                if (n < p.G) {
+                                    const float mj = live ? ml[j][n].x : -INFINITY;
+                                    const float m_new = fmaxf(M[n], mj);
+                                    const float keep = M[n] == -INFINITY ? 0.f : exp2f(M[n] - m_new);
+                                    const float f = mj == -INFINITY ? 0.f : exp2f(mj - m_new);
+                                    M[n] = m_new;
+                                    L[n] = L[n] * keep + ml[j][n].y * f;
+#pragma unroll
+                                    for (int i = 0; i < CPL; ++i) acc[n][i] = acc[n][i] * keep + part[j][n][i] * f;
+                                }
                             }
                         }
                     }

@@ -1,0 +1,107 @@
+"""Device timelines of the two tcgen05 attention kernels, for the summaries under profiles/.
+
+    SPYINFER_NVCC_FLAGS=-DSPY_TIMELINE python -m spyinfer_b200.timeline decode [--layers 6] [--batch 8] [--context 8192]
+    SPYINFER_NVCC_FLAGS=-DSPY_TIMELINE python -m spyinfer_b200.timeline prompt [--tokens 8192]
+
+With ``-DSPY_TIMELINE`` the kernels stamp the global timer at points of a block's life into a
+device array; this program runs them, copies the stamps out and prints, per point, the minimum,
+median and maximum over the blocks.  ``decode``: the decode attention of the LAST layer inside
+the engine's captured decode graph of a model with Qwen3-8B's layer sizes (so the kernels
+ahead of it and behind it are the real ones).  ``prompt``: the prompt attention alone, one
+sequence of ``--tokens`` tokens, stamps of every block's tenth key tile.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import sys
+
+import numpy as np
+import torch
+
+QWEN3_8B_LAYER = {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "hidden_act": "silu", "hidden_size": 4096,
+                  "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 12288, "vocab_size": 151936,
+                  "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "max_position_embeddings": 40960}
+
+
+def _stamps(module: str, fn: str, blocks: int, points: int = 16) -> np.ndarray:
+    from .csrc import build
+    lib = build.load(module)
+    if not hasattr(lib, fn):
+        raise SystemExit(f"{module} was built without -DSPY_TIMELINE: set SPYINFER_NVCC_FLAGS=-DSPY_TIMELINE")
+    buf = (ctypes.c_ulonglong * (blocks * points))()
+    if getattr(lib, fn)(buf) != 0:
+        raise SystemExit(build.last_error(module))
+    return np.array(buf, dtype=np.uint64).reshape(blocks, points).astype(np.int64)
+
+
+def decode(layers: int, batch: int, context: int) -> None:
+    from . import SamplingParams, config_from_json
+    from .engine import LLMEngine, StepEntry
+    cfg = dict(QWEN3_8B_LAYER, num_hidden_layers=layers)
+    eng = LLMEngine(model_config=config_from_json(cfg), seed=0, dtype="bfloat16", max_num_seqs=batch, max_model_len=context + 64,
+                    kvcache_block_size=16, num_kvcache_blocks=batch * ((context + 64) // 16 + 2) + 8, max_num_batched_tokens=2048)
+    runner, cache = eng.runner, eng.runner.cache
+    for g in cache.groups:
+        g.pages.normal_()
+    rids = [f"r{i}" for i in range(batch)]
+    for r in rids:
+        cache.add_request(r)
+        cache.reserve(r, context - 20)
+        cache.commit(r, context - 20)
+    for _ in range(10):
+        logits = runner.step([StepEntry(r, [5], [0]) for r in rids])
+        eng.sampler.sample(logits, [SamplingParams()] * batch, [0] * batch)
+    torch.cuda.synchronize()
+    t = _stamps("attention_decode", "spy_attention_decode_timeline", 256)[:148]
+    names = ["entry", "prologue done", "first K box requested", "kernel ahead complete (wait returned)", "first Q.K issued", "first scores ready",
+             "last probabilities written", "last P.V complete", "partial result written", "segment done", "exit", "merge: arrived last",
+             "-", "merge: parts added", "-", "producer: first segment known"]
+    busy = t[:, 5] > 0
+    t0 = t[busy, 0].min()
+    print(f"decode attention of the last of {layers} layers, batch {batch}, {context} keys; {busy.sum()} blocks with work; "
+          "ns after the first block's entry: min / median / max")
+    for i, n in enumerate(names):
+        col = t[busy, i]
+        col = col[col >= t0] - t0
+        if n != "-" and len(col):
+            print(f"  {n:38s} {col.min():8d} {int(np.median(col)):8d} {col.max():8d}")
+
+
+def prompt(tokens: int) -> None:
+    from . import microbench
+    r = microbench.bench_attention(1, tokens, tokens, 0, iters=2, kernel="tc")
+    print(f"prompt attention, {tokens} tokens: {r['us']:.1f} us, {r['tflops']:.1f} TFLOP/s")
+    t = _stamps("attention_tc", "spy_attention_tc_timeline", 1024)
+    t = t[(t[:, 0] > 0) & (t[:, 5] > 0) & (t[:, 10] > 0)]
+    names = ["scores of tile 10 ready (softmax)", "scores loaded", "maxima exchanged", "exponentials done", "P of tile 10 written",
+             "scores of tile 11 ready (softmax)", "MMA: P of tile 10 seen", "MMA: V of tile 10 seen", "MMA: P.V of tile 10 issued",
+             "MMA: K of tile 12 seen", "MMA: Q.K of tile 12 issued", "K warp: stage free for tile 13", "K warp: tile 13 requested"]
+    print(f"{len(t)} blocks with more than twelve tiles; ns after the block's scores of tile 10 were ready: median (10 % .. 90 %)")
+    for i, n in enumerate(names):
+        d = (t[:, i] - t[:, 0])[t[:, i] > 0]
+        if len(d):
+            print(f"  {n:38s} {int(np.median(d)):7d}  ({int(np.percentile(d, 10))} .. {int(np.percentile(d, 90))})")
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    sub = ap.add_subparsers(dest="what", required=True)
+    d = sub.add_parser("decode")
+    d.add_argument("--layers", type=int, default=6)
+    d.add_argument("--batch", type=int, default=8)
+    d.add_argument("--context", type=int, default=8192)
+    p = sub.add_parser("prompt")
+    p.add_argument("--tokens", type=int, default=8192)
+    args = ap.parse_args(argv)
+    from . import kernels
+    kernels.require_cuda()
+    if args.what == "decode":
+        decode(args.layers, args.batch, args.context)
+    else:
+        prompt(args.tokens)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
