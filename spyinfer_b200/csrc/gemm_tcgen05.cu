@@ -41,9 +41,39 @@ template <int BN> struct Tile {
     static constexpr int STAGES = BN <= 64 ? (100 * 1024) / STAGE_BYTES : (200 * 1024) / STAGE_BYTES;
     static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
     static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+    // The one-tile kernel packs its stages: a tile of fewer than 128 weight rows takes only its
+    // own bytes (rounded up to the swizzle's 1 KB), so more stages fit the same area and as many
+    // bytes stay in flight as with full tiles.  The tensor core still reads 128 rows: the spare
+    // ones come from whatever lies behind (the next stage; AREA ends with room for that) and
+    // feed accumulator rows that are never stored.
+    static constexpr int AREA = BN <= 64 ? 110 * 1024 : STAGES * STAGE_BYTES;
+    static constexpr int MAX_STAGES = 12;
+    static constexpr size_t SMEM_PACKED = (size_t)AREA + 1024 /* alignment slack */ + 256 /* barriers */;
+    __host__ __device__ static constexpr int x_bytes(int tile_rows) { return (tile_rows * BK * 2 + 1023) & ~1023; }
+    __host__ __device__ static constexpr int stages(int tile_rows)
+    {
+        const int n = (AREA - (X_BYTES - x_bytes(tile_rows))) / (x_bytes(tile_rows) + Y_BYTES);
+        return n < MAX_STAGES ? n : MAX_STAGES;
+    }
 };
 
 template <typename TC> __device__ __forceinline__ void store_elem(TC* p, float v) { *p = from_f32<TC>(v); }
+
+// -DSPY_TIMELINE: the blocks of the one-tile kernel stamp the global timer at a few points of
+// their life into a device array, one plane per launch (the host numbers the launches; a
+// captured graph keeps the numbers it was captured with), which spy_gemm_tcgen05_timeline
+// copies out (a debugging aid; off in normal builds).
+#ifdef SPY_TIMELINE
+constexpr int TL_LAUNCHES = 64, TL_BLOCKS = 320, TL_POINTS = 10;
+__device__ unsigned long long g_timeline[TL_LAUNCHES][TL_BLOCKS][TL_POINTS];
+#define GSTAMP(i)                                                                                                  \
+    do {                                                                                                           \
+        const unsigned b_ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);                        \
+        if (b_ < TL_BLOCKS) g_timeline[launch_no % TL_LAUNCHES][b_][i] = global_timer();                          \
+    } while (0)
+#else
+#define GSTAMP(i) ((void)0)
+#endif
 
 // Stores 32 consecutive columns of one row, vectorised when the row allows it.
 template <typename TC>
@@ -84,29 +114,38 @@ __device__ __forceinline__ float silu_mul(float g, float u) { return (g / (1.0f 
 template <int BN, typename TC, bool SWAP, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, BN <= 64 ? 2 : 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, TC* __restrict__ out,
-                    long long ld, long long split_stride, int x_rows, int y_rows, int k_blocks, int k_blocks_per_split, int tile_rows, int* status)
+                    long long ld, long long split_stride, int x_rows, int y_rows, int k_blocks, int k_blocks_per_split, int tile_rows, int launch_no,
+                    int* status)
 {
     using T = Tile<BN>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* tiles = smem;
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)T::STAGES * T::STAGE_BYTES);
-    uint64_t* empty_bar = full_bar + T::STAGES;
-    uint64_t* accum_bar = empty_bar + T::STAGES;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + T::AREA);
+    uint64_t* empty_bar = full_bar + T::MAX_STAGES;
+    uint64_t* accum_bar = empty_bar + T::MAX_STAGES;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef SPY_TIMELINE
+    if (threadIdx.x == 0) {
+        GSTAMP(0);
+        const unsigned b_ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+        if (b_ < TL_BLOCKS) g_timeline[launch_no % TL_LAUNCHES][b_][9] = gridDim.x * gridDim.y * gridDim.z;
+    }
+#endif
     // tile_rows (<= BM) rows of X belong to this block: the box of map_x has that many rows, the rest of
     // the stage's 128 rows is stale and feeds accumulator rows that are never stored
     const int x0 = blockIdx.x * tile_rows, y0 = blockIdx.y * BN;
     const uint32_t stage_tx = (uint32_t)tile_rows * BK * 2 + T::Y_BYTES;
+    const int x_bytes = T::x_bytes(tile_rows), stage_bytes = x_bytes + T::Y_BYTES, stages = T::stages(tile_rows);
     const int kb0 = blockIdx.z * k_blocks_per_split;
     const int kb1 = min(k_blocks, kb0 + k_blocks_per_split);
     const int num_kb = kb1 - kb0;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < T::STAGES; ++s) {
+        for (int s = 0; s < stages; ++s) {
             mbar_init(full_bar + s, 1);
             mbar_init(empty_bar + s, 1);
         }
@@ -123,6 +162,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) GSTAMP(1);
 
     pdl_launch_dependents();   // the next kernel in the stream may begin its own prologue
     if (warp == 0) {
@@ -130,48 +170,57 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             // The weight operand (X when swapped, Y otherwise) depends on no earlier kernel: its
             // tiles for the first stages are requested before the wait for the kernels ahead in
             // the stream, so weights already stream in while those are finishing.
-            const int pre = min(num_kb, T::STAGES);
+            const int pre = min(num_kb, stages);
             for (int i = 0; i < pre; ++i) {
-                uint8_t* xs = tiles + (size_t)i * T::STAGE_BYTES;
+                uint8_t* xs = tiles + (size_t)i * stage_bytes;
                 mbar_expect_tx(full_bar + i, stage_tx);
                 if constexpr (SWAP) tma_load_2d(smem_u32(xs), &map_x, (kb0 + i) * BK, x0, full_bar + i);
-                else tma_load_2d(smem_u32(xs + T::X_BYTES), &map_y, (kb0 + i) * BK, y0, full_bar + i);
+                else tma_load_2d(smem_u32(xs + x_bytes), &map_y, (kb0 + i) * BK, y0, full_bar + i);
             }
             pdl_wait();
+            GSTAMP(2);
             for (int i = 0; i < pre; ++i) {
-                uint8_t* xs = tiles + (size_t)i * T::STAGE_BYTES;
-                if constexpr (SWAP) tma_load_2d(smem_u32(xs + T::X_BYTES), &map_y, (kb0 + i) * BK, y0, full_bar + i);
+                uint8_t* xs = tiles + (size_t)i * stage_bytes;
+                if constexpr (SWAP) tma_load_2d(smem_u32(xs + x_bytes), &map_y, (kb0 + i) * BK, y0, full_bar + i);
                 else tma_load_2d(smem_u32(xs), &map_x, (kb0 + i) * BK, x0, full_bar + i);
             }
+            int s = 0;
+            uint32_t phase = 1;   // of the round before: the first wait on a stage is for its first release
             for (int i = pre; i < num_kb; ++i) {
-                const int s = i % T::STAGES;
-                const uint32_t phase = (i / T::STAGES) & 1;
                 if (!mbar_wait(empty_bar + s, phase ^ 1, abort_flag)) break;
-                uint8_t* xs = tiles + (size_t)s * T::STAGE_BYTES;
-                uint8_t* ys = xs + T::X_BYTES;
+                uint8_t* xs = tiles + (size_t)s * stage_bytes;
+                uint8_t* ys = xs + x_bytes;
                 mbar_expect_tx(full_bar + s, stage_tx);
                 tma_load_2d(smem_u32(xs), &map_x, (kb0 + i) * BK, x0, full_bar + s);
                 tma_load_2d(smem_u32(ys), &map_y, (kb0 + i) * BK, y0, full_bar + s);
+                if (++s == stages) {
+                    s = 0;
+                    phase ^= 1;
+                }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = instr_desc_bf16(BM, BN, false, false);
-            bool ok = true;
-            for (int i = 0; i < num_kb && ok; ++i) {
-                const int s = i % T::STAGES;
-                const uint32_t phase = (i / T::STAGES) & 1;
-                ok = mbar_wait(full_bar + s, phase, abort_flag);
-                if (!ok) break;
+            int s = 0;
+            uint32_t phase = 0;
+            for (int i = 0; i < num_kb; ++i) {
+                if (!mbar_wait(full_bar + s, phase, abort_flag)) break;
+                if (i == 0) GSTAMP(3);
+                if (i == num_kb - 1) GSTAMP(4);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint8_t* xs = tiles + (size_t)s * T::STAGE_BYTES;
-                const uint64_t dx = desc_k_major(smem_u32(xs)), dy = desc_k_major(smem_u32(xs + T::X_BYTES));
+                const uint8_t* xs = tiles + (size_t)s * stage_bytes;
+                const uint64_t dx = desc_k_major(smem_u32(xs)), dy = desc_k_major(smem_u32(xs + x_bytes));
 #pragma unroll
                 for (int k = 0; k < BK / UMMA_K; ++k) {
                     const uint64_t adv = (uint64_t)((k * UMMA_K * 2) >> 4);
                     umma(tmem_base, dx + adv, dy + adv, idesc, (i > 0 || k > 0) ? 1u : 0u);
                 }
                 umma_commit(empty_bar + s);   // the stage is free again when these MMAs have read it
+                if (++s == stages) {
+                    s = 0;
+                    phase ^= 1;
+                }
             }
             umma_commit(accum_bar);           // the accumulator is complete when every MMA has finished
         }
@@ -180,6 +229,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         const int quarter = warp & 3;
         pdl_wait();   // the output buffer may still be in use by a kernel ahead in the stream
         const bool ok = mbar_wait(accum_bar, 0, abort_flag);
+        if (warp == 2 && lane == 0) GSTAMP(5);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const int x = quarter * 32 + lane < tile_rows ? x0 + quarter * 32 + lane : x_rows;   // rows beyond the tile's are the next block's
         TC* base = out + (size_t)blockIdx.z * split_stride;
@@ -254,8 +304,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         }
     }
 
+    if (warp == 2 && lane == 0) GSTAMP(6);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if (threadIdx.x == 0) GSTAMP(7);
     if (*abort_flag) {
         // a wait ran out: give copies that may still be in flight time to land before the
         // shared memory is released, then report
@@ -646,6 +698,8 @@ static int make_map(CUtensorMap* map, const void* ptr, long long rows, long long
     return 0;
 }
 
+int g_launch_no = 0;   // numbers the launches of the one-tile kernel for the timeline build; unused otherwise
+
 template <int BN, typename TC, bool SWAP, int EPI>
 static int launch(const CUtensorMap& mx, const CUtensorMap& my, void* out, long long ld, long long split_stride, int x_rows, int y_rows,
                   int k_blocks, int splits, int tile_rows, int* status, cudaStream_t stream)
@@ -654,14 +708,14 @@ static int launch(const CUtensorMap& mx, const CUtensorMap& my, void* out, long 
     auto kernel = gemm_tcgen05_kernel<BN, TC, SWAP, EPI>;
     static bool configured = false;
     if (!configured) {
-        SPY_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)T::SMEM));
+        SPY_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)T::SMEM_PACKED));
         configured = true;
     }
     const int per_split = (k_blocks + splits - 1) / splits;
     dim3 grid((x_rows + tile_rows - 1) / tile_rows, (y_rows + BN - 1) / BN, splits);
     if (grid.y > 65535 || grid.z > 65535) SPY_FAIL("gemm_tcgen05: the grid %u x %u x %u exceeds the launch limits", grid.x, grid.y, grid.z);
-    spy_launch(kernel, grid, dim3(NUM_THREADS), T::SMEM, stream, mx, my, (TC*)out, ld, split_stride, x_rows, y_rows, k_blocks, per_split, tile_rows,
-               status);
+    spy_launch(kernel, grid, dim3(NUM_THREADS), T::SMEM_PACKED, stream, mx, my, (TC*)out, ld, split_stride, x_rows, y_rows, k_blocks, per_split, tile_rows,
+               g_launch_no++, status);
     SPY_CHECK_LAUNCH("gemm_tcgen05");
     return 0;
 }
@@ -887,6 +941,18 @@ extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, 
     }
     return 0;
 }
+
+#ifdef SPY_TIMELINE
+// Copies the stamps out: [64 launches][320 blocks][10 points] of nanoseconds (point 9: the grid's
+// size); *next_launch is the number the next launch will get.
+extern "C" int spy_gemm_tcgen05_timeline(unsigned long long* host, int* next_launch)
+{
+    SPY_CUDA(cudaDeviceSynchronize());
+    SPY_CUDA(cudaMemcpyFromSymbol(host, g_timeline, sizeof(g_timeline)));
+    *next_launch = g_launch_no;
+    return 0;
+}
+#endif
 
 // The plain product: no epilogue, partial products summed before it returns.
 extern "C" int spy_gemm_tcgen05(const void* A, long long lda, const void* W, long long ldw, void* C, int c_dtype, long long ldc, int M, int N,

@@ -137,7 +137,10 @@ __global__ void __launch_bounds__(256) qk_rope_store_hd128_kernel(const TS* src,
                                                                   int page_size, int num_pages, int store, int* status)
 {
     constexpr int HD = 128;
-    pdl_enter();
+    // What depends on no kernel ahead in the stream (the batch's positions and block table, which
+    // the host wrote; the rotation table and the norm weights) is loaded before the wait for those
+    // kernels; only the input (their product) is read after it.
+    pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, l = lane & 15;
     const int heads = store ? nh + 2 * nkv : nh;
     const int items = tokens * heads;   // the host refuses batches whose items do not fit 31 bits: 32-bit divisions below
@@ -146,9 +149,26 @@ __global__ void __launch_bounds__(256) qk_rope_store_hd128_kernel(const TS* src,
     const int item = min(mine, items - 1);   // an item beyond the end repeats the last one and stores nothing
     const int t = item / heads, head = item - t * heads;
     const int kind = head < nh ? 0 : (head < nh + nkv ? 1 : 2);  // q, k, v
-    // ---- round 1: the position and the input
+    // ---- round 1: the position
     const int pos = positions[t];
     const int seq = kind == 0 ? 0 : seq_of_token[t];
+    const TW* w = kind == 0 ? q_w : k_w;
+    float wv[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) wv[i] = (q_w != nullptr && kind != 2) ? to_f32(w[8 * l + i]) : 1.f;
+    // ---- round 2: what the position leads to
+    const bool in_table = kind != 0 && pos >= 0 && pos / page_size < table_width;
+    const int page = in_table ? block_table[(size_t)seq * table_width + pos / page_size] : -1;
+    const bool rotate = kind != 2 && cos_sin != nullptr;
+    const bool pos_ok = pos >= 0 && pos < table_rows;
+    float4 cs[4];   // (cos, sin) of the pairs 8 (l & 7) .. + 7
+    {
+        const float4* cs4 = reinterpret_cast<const float4*>(cos_sin + (size_t)((rotate && pos_ok) ? pos : 0) * 64 + 8 * (l & 7));
+#pragma unroll
+        for (int i = 0; i < 4; ++i) cs[i] = (rotate && pos_ok) ? cs4[i] : make_float4(1.f, 0.f, 1.f, 0.f);
+    }
+    pdl_wait();
+    // ---- the input
     const TS* in = src + (size_t)t * (nh + 2 * nkv) * HD + (size_t)head * HD + 8 * l;
     float v[8];
     if constexpr (sizeof(TS) == 2) {
@@ -170,17 +190,6 @@ __global__ void __launch_bounds__(256) qk_rope_store_hd128_kernel(const TS* src,
             v[0] += p0.x; v[1] += p0.y; v[2] += p0.z; v[3] += p0.w; v[4] += p1.x; v[5] += p1.y; v[6] += p1.z; v[7] += p1.w;
         }
     }
-    // ---- round 2: what the position leads to
-    const bool in_table = kind != 0 && pos >= 0 && pos / page_size < table_width;
-    const int page = in_table ? block_table[(size_t)seq * table_width + pos / page_size] : -1;
-    const bool rotate = kind != 2 && cos_sin != nullptr;
-    const bool pos_ok = pos >= 0 && pos < table_rows;
-    float4 cs[4];   // (cos, sin) of the pairs 8 (l & 7) .. + 7
-    {
-        const float4* cs4 = reinterpret_cast<const float4*>(cos_sin + (size_t)((rotate && pos_ok) ? pos : 0) * 64 + 8 * (l & 7));
-#pragma unroll
-        for (int i = 0; i < 4; ++i) cs[i] = (rotate && pos_ok) ? cs4[i] : make_float4(1.f, 0.f, 1.f, 0.f);
-    }
     bf16* dst = nullptr;
     if (live) {
         if (kind == 0) {
@@ -197,7 +206,6 @@ __global__ void __launch_bounds__(256) qk_rope_store_hd128_kernel(const TS* src,
         }
     }
     // ---- norm, rotation, store (both halves of the warp run the shuffles)
-    const TW* w = kind == 0 ? q_w : k_w;
     if (q_w != nullptr) {
         float ss = 0.f;
 #pragma unroll
@@ -207,7 +215,7 @@ __global__ void __launch_bounds__(256) qk_rope_store_hd128_kernel(const TS* src,
         if (kind != 2) {
             const float inv = 1.0f / sqrtf(ss / (float)HD + eps);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] = (inv * v[i]) * to_f32(w[8 * l + i]);
+            for (int i = 0; i < 8; ++i) v[i] = (inv * v[i]) * wv[i];
         }
     }
     if (cos_sin != nullptr) {

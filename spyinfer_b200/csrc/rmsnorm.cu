@@ -36,12 +36,42 @@ template <> struct Quad<bf16> {
     }
 };
 
+// -DSPY_TIMELINE: thread 0 of every block stamps the global timer at a few points into a ring of
+// the last 128 blocks, which spy_rmsnorm_timeline copies out (a debugging aid; off in normal builds).
+#ifdef SPY_TIMELINE
+__device__ unsigned long long g_timeline[128][8];
+__device__ unsigned int g_timeline_next;
+__device__ __forceinline__ unsigned long long timer_ns()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define RSTAMP(i) do { if (threadIdx.x == 0) g_timeline[tl_slot][i] = timer_ns(); } while (0)
+#else
+#define RSTAMP(i) ((void)0)
+#endif
+
 template <typename TX, typename TD, typename TW, typename TO, bool VEC>
-__global__ void rmsnorm_kernel(TX* x, const TD* __restrict__ delta, int delta_splits, long long delta_split_stride, const int* __restrict__ rows,
+__global__ void __launch_bounds__(1024) rmsnorm_kernel(TX* x, const TD* __restrict__ delta, int delta_splits, long long delta_split_stride, const int* __restrict__ rows,
                                const TW* __restrict__ w, TO* __restrict__ out, int len, float eps, int write_back)
 {
     extern __shared__ float row_buf[];  // len floats, then 33 of scratch
-    pdl_enter();
+#ifdef SPY_TIMELINE
+    unsigned int tl_slot = 0;
+    if (threadIdx.x == 0) tl_slot = atomicAdd(&g_timeline_next, 1u) % 128u;
+#endif
+    RSTAMP(0);
+    // The weight depends on no kernel ahead in the stream: the first quad of it (all of it when
+    // the block spans the row, as in decoding) is loaded before the wait for those kernels.
+    pdl_launch_dependents();
+    float w_first[4] = {0.f, 0.f, 0.f, 0.f};
+    if constexpr (VEC) {
+        if ((int)threadIdx.x * 4 < len) Quad<TW>::load(w + threadIdx.x * 4, w_first);
+    }
+    RSTAMP(1);
+    pdl_wait();
+    RSTAMP(2);
     float* scratch = row_buf + len;
     const int src_row = rows ? rows[blockIdx.x] : blockIdx.x;
     TX* xr = x + (size_t)src_row * len;
@@ -53,11 +83,20 @@ __global__ void rmsnorm_kernel(TX* x, const TD* __restrict__ delta, int delta_sp
             float v[4];
             Quad<TX>::load(xr + i, v);
             if (dr) {
-                for (int s = 0; s < delta_splits; ++s) {
-                    float d[4];
-                    Quad<TD>::load(dr + (size_t)s * delta_split_stride + i, d);
+                // the partial products are added in their order; eight loads are in flight at a time (a
+                // round trip to L2 takes microseconds while the next product's weights stream in)
+                for (int s0 = 0; s0 < delta_splits; s0 += 8) {
+                    float d[8][4];
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) v[e] += d[e];
+                    for (int j = 0; j < 8; ++j)
+                        if (s0 + j < delta_splits) Quad<TD>::load(dr + (size_t)(s0 + j) * delta_split_stride + i, d[j]);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        if (s0 + j < delta_splits) {
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) v[e] += d[j][e];
+                        }
+                    }
                 }
             }
 #pragma unroll
@@ -77,12 +116,19 @@ __global__ void rmsnorm_kernel(TX* x, const TD* __restrict__ delta, int delta_sp
             if (write_back) xr[i] = from_f32<TX>(v);
         }
     }
+    RSTAMP(3);
     ss = block_sum(ss, scratch);
+    RSTAMP(4);
     const float inv = 1.0f / sqrtf(ss / (float)len + eps);
     if constexpr (VEC) {
         for (int i = threadIdx.x * 4; i < len; i += blockDim.x * 4) {
             float wv[4], o[4];
-            Quad<TW>::load(w + i, wv);
+            if (i == (int)threadIdx.x * 4) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) wv[e] = w_first[e];
+            } else {
+                Quad<TW>::load(w + i, wv);
+            }
 #pragma unroll
             for (int e = 0; e < 4; ++e) o[e] = (inv * row_buf[i + e]) * wv[e];
             Quad<TO>::store(orow + i, o);
@@ -90,7 +136,19 @@ __global__ void rmsnorm_kernel(TX* x, const TD* __restrict__ delta, int delta_sp
     } else {
         for (int i = threadIdx.x; i < len; i += blockDim.x) orow[i] = from_f32<TO>((inv * row_buf[i]) * to_f32(w[i]));
     }
+    RSTAMP(5);
 }
+
+#ifdef SPY_TIMELINE
+// Copies the ring out: [128 blocks][8 points] of nanoseconds (entry, weights requested, wait
+// returned, row summed, statistics known, stored).
+extern "C" int spy_rmsnorm_timeline(unsigned long long* host)
+{
+    SPY_CUDA(cudaDeviceSynchronize());
+    SPY_CUDA(cudaMemcpyFromSymbol(host, g_timeline, sizeof(g_timeline)));
+    return 0;
+}
+#endif
 
 template <typename TX, typename TD, typename TW, typename TO>
 static int launch(void* x, const void* delta, int delta_splits, long long delta_split_stride, const int* rows, const void* w, void* out, int n,

@@ -2,13 +2,16 @@
 
     SPYINFER_NVCC_FLAGS=-DSPY_TIMELINE python -m spyinfer_b200.timeline decode [--layers 6] [--batch 8] [--context 8192]
     SPYINFER_NVCC_FLAGS=-DSPY_TIMELINE python -m spyinfer_b200.timeline prompt [--tokens 8192]
+    SPYINFER_NVCC_FLAGS=-DSPY_TIMELINE python -m spyinfer_b200.timeline chain [--layers 2] [--batch 8] [--context 8192]
 
 With ``-DSPY_TIMELINE`` the kernels stamp the global timer at points of a block's life into a
 device array; this program runs them, copies the stamps out and prints, per point, the minimum,
 median and maximum over the blocks.  ``decode``: the decode attention of the LAST layer inside
 the engine's captured decode graph of a model with Qwen3-8B's layer sizes (so the kernels
 ahead of it and behind it are the real ones).  ``prompt``: the prompt attention alone, one
-sequence of ``--tokens`` tokens, stamps of every block's tenth key tile.
+sequence of ``--tokens`` tokens, stamps of every block's tenth key tile.  ``chain``: the
+few-token products (one-tile tcgen05 kernel) of one decode step in the order they ran, with
+the last layer's decode attention between them, on one time axis.
 """
 from __future__ import annotations
 
@@ -35,7 +38,7 @@ def _stamps(module: str, fn: str, blocks: int, points: int = 16) -> np.ndarray:
     return np.array(buf, dtype=np.uint64).reshape(blocks, points).astype(np.int64)
 
 
-def decode(layers: int, batch: int, context: int) -> None:
+def _decode_steps(layers: int, batch: int, context: int, steps: int = 10):
     from . import SamplingParams, config_from_json
     from .engine import LLMEngine, StepEntry
     cfg = dict(QWEN3_8B_LAYER, num_hidden_layers=layers)
@@ -49,10 +52,65 @@ def decode(layers: int, batch: int, context: int) -> None:
         cache.add_request(r)
         cache.reserve(r, context - 20)
         cache.commit(r, context - 20)
-    for _ in range(10):
+    for _ in range(steps):
         logits = runner.step([StepEntry(r, [5], [0]) for r in rids])
         eng.sampler.sample(logits, [SamplingParams()] * batch, [0] * batch)
     torch.cuda.synchronize()
+
+
+def chain(layers: int, batch: int, context: int) -> None:
+    from .csrc import build
+    _decode_steps(layers, batch, context)
+    lib = build.load("gemm_tcgen05")
+    if not hasattr(lib, "spy_gemm_tcgen05_timeline"):
+        raise SystemExit("gemm_tcgen05 was built without -DSPY_TIMELINE: set SPYINFER_NVCC_FLAGS=-DSPY_TIMELINE")
+    launches, blocks, points = 64, 320, 10
+    buf = (ctypes.c_ulonglong * (launches * blocks * points))()
+    nxt = ctypes.c_int(0)
+    if lib.spy_gemm_tcgen05_timeline(buf, ctypes.byref(nxt)) != 0:
+        raise SystemExit(build.last_error("gemm_tcgen05"))
+    g = np.array(buf, dtype=np.uint64).reshape(launches, blocks, points).astype(np.int64)
+    a = _stamps("attention_decode", "spy_attention_decode_timeline", 256)[:148]
+    a = a[a[:, 5] > 0]
+    rows = []
+    for plane in g:
+        n = int(min(plane[0, 9], blocks)) if plane[0, 0] > 0 else 0
+        if n:
+            rows.append((int(plane[:n, 0].min()), "product", plane[:n], int(plane[0, 9])))
+    if not rows:
+        raise SystemExit("no stamps: did the step run the one-tile product kernel?")
+    rows = sorted(rows, key=lambda r: r[0])[-(4 * layers + 1):]   # the last step's launches: four a layer and the output head
+    rows.append((int(a[:, 0].min()), "attention", a, len(a)))
+    norms = _stamps("rmsnorm", "spy_rmsnorm_timeline", 128, 8)
+    norms = norms[norms[:, 0] >= rows[0][0] - 20_000]
+    for start in sorted(set(int(x) for x in norms[:, 0] // 2000)):   # blocks of one launch enter within two microseconds
+        group = norms[norms[:, 0] // 2000 == start]
+        rows.append((int(group[:, 0].min()), "norm", group, len(group)))
+    rows.sort(key=lambda r: r[0])
+    t0 = rows[0][0]
+    print(f"{layers} layers, batch {batch}, {context} keys: the last step's few-token products (first {blocks} blocks of each) and the last "
+          "layer's decode attention; microseconds after the first entry")
+    print(f"{'kernel':10s} {'blocks':>6s} {'entry':>15s} {'wait returned':>15s} {'first stage in':>15s} {'last stage in':>15s} {'sums ready':>11s} {'stored':>8s} {'exit':>8s}")
+
+    def span(col):
+        col = (col[col > 0] - t0) / 1000.0
+        return f"{col.min():6.1f} ..{col.max():6.1f}" if len(col) else " " * 15
+
+    def last(col):
+        col = (col[col > 0] - t0) / 1000.0
+        return f"{col.max():8.1f}" if len(col) else " " * 8
+
+    for _, kind, t, n in rows:
+        if kind == "product":
+            print(f"{kind:10s} {n:6d} {span(t[:, 0])} {span(t[:, 2])} {span(t[:, 3])} {span(t[:, 4])} {last(t[:, 5]):>11s} {last(t[:, 6])} {last(t[:, 7])}")
+        elif kind == "attention":
+            print(f"{kind:10s} {n:6d} {span(t[:, 0])} {span(t[:, 3])} {'first scores':>15s} {span(t[:, 5])} {'':>11s} {last(t[:, 8])} {last(t[:, 10])}")
+        else:
+            print(f"{kind:10s} {n:6d} {span(t[:, 0])} {span(t[:, 2])} {'row summed':>15s} {span(t[:, 3])} {last(t[:, 4]):>11s} {last(t[:, 5])}")
+
+
+def decode(layers: int, batch: int, context: int) -> None:
+    _decode_steps(layers, batch, context)
     t = _stamps("attention_decode", "spy_attention_decode_timeline", 256)[:148]
     names = ["entry", "prologue done", "first K box requested", "kernel ahead complete (wait returned)", "first Q.K issued", "first scores ready",
              "last probabilities written", "last P.V complete", "partial result written", "segment done", "exit", "merge: arrived last",
@@ -91,6 +149,10 @@ def main(argv=None) -> int:
     d.add_argument("--layers", type=int, default=6)
     d.add_argument("--batch", type=int, default=8)
     d.add_argument("--context", type=int, default=8192)
+    c = sub.add_parser("chain")
+    c.add_argument("--layers", type=int, default=2)
+    c.add_argument("--batch", type=int, default=8)
+    c.add_argument("--context", type=int, default=8192)
     p = sub.add_parser("prompt")
     p.add_argument("--tokens", type=int, default=8192)
     args = ap.parse_args(argv)
@@ -98,6 +160,8 @@ def main(argv=None) -> int:
     kernels.require_cuda()
     if args.what == "decode":
         decode(args.layers, args.batch, args.context)
+    elif args.what == "chain":
+        chain(args.layers, args.batch, args.context)
     else:
         prompt(args.tokens)
     return 0
