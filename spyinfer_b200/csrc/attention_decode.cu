@@ -185,7 +185,7 @@ __device__ __forceinline__ int ordered(float f)
 __device__ __forceinline__ float unordered(int i) { return __int_as_float(i ^ ((i >> 31) & 0x7fffffff)); }
 
 template <int HD, int GN>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __maxnreg__(160)
 attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __grid_constant__ CUtensorMap q_map, const Params p)
 {
     extern __shared__ uint8_t smem_raw[];
@@ -422,73 +422,59 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
                 last = __shfl_sync(0xffffffffu, last, 0);
                 if (last && lane == 0) STAMP(11);
                 if (last) {
-                    // this lane: 4 consecutive columns (head_dim 128) or 2 (head_dim 64) of every head; the
-                    // loads of four slots are in flight together
+                    // 32 / GN lanes share a head; a lane merges W consecutive columns of its head.  The
+                    // loads of CH parts are issued together (a pair of two to four parts then costs one
+                    // round trip to L2 instead of one per part); the parts are added in block order and
+                    // the running maximum rescales what has been added so far.
                     __threadfence();
-                    constexpr int CPL = HD / 32;
-                    const float* ml0 = p.part_ml + (size_t)pair * p.G * 2;
-                    const float* o0 = p.part_o + (size_t)pair * p.G * HD + lane * CPL;
-                    float M[GN], L[GN], acc[GN][CPL];
+                    constexpr int LPH = 32 / GN, W = HD / LPH, CH = W <= 16 ? 4 : (W <= 32 ? 2 : 1);
+                    const int n = lane / LPH, col = (lane % LPH) * W;
+                    if (n < p.G) {
+                        const float* ml0 = p.part_ml + ((size_t)pair * p.G + n) * 2;
+                        const float* o0 = p.part_o + ((size_t)pair * p.G + n) * HD + col;
+                        float M = -INFINITY, L = 0.f, acc[W];
 #pragma unroll
-                    for (int n = 0; n < GN; ++n) {
-                        M[n] = -INFINITY;
-                        L[n] = 0.f;
+                        for (int i = 0; i < W; ++i) acc[i] = 0.f;
+                        for (int c0 = c_first; c0 <= c_last; c0 += CH) {
+                            float2 ml[CH];
+                            float4 part[CH][W / 4];
 #pragma unroll
-                        for (int i = 0; i < CPL; ++i) acc[n][i] = 0.f;
-                    }
-                    // one pass in block order; the running maximum rescales what has been added so far.
-                    // The loads of CH parts are issued together (a part beyond the last reads the last
-                    // one again and counts for nothing), so a pair of two to four parts costs one
-                    // round trip to L2 instead of one per part.
-                    constexpr int CH = GN <= 4 ? 4 : (GN <= 8 ? 2 : 1);
-                    for (int c0 = c_first; c0 <= c_last; c0 += CH) {
-                        float2 ml[CH][GN];
-                        float part[CH][GN][CPL];
+                            for (int j = 0; j < CH; ++j) {
+                                const size_t sl = (size_t)min(c0 + j, c_last) * p.G;   // beyond the last: the last again, counted for nothing
+                                ml[j] = __ldcg(reinterpret_cast<const float2*>(ml0 + sl * 2));
 #pragma unroll
-                        for (int j = 0; j < CH; ++j) {
-                            const int c = min(c0 + j, c_last);
+                                for (int i = 0; i < W / 4; ++i) part[j][i] = __ldcg(reinterpret_cast<const float4*>(o0 + sl * HD) + i);
+                            }
 #pragma unroll
-                            for (int n = 0; n < GN; ++n) {
-                                if (n < p.G) {
-                                    const size_t sl = (size_t)c * p.G + n;
-                                    ml[j][n] = __ldcg(reinterpret_cast<const float2*>(ml0 + sl * 2));
-                                    if constexpr (CPL == 4) {
-                                        const float4 v = __ldcg(reinterpret_cast<const float4*>(o0 + sl * HD));
-                                        part[j][n][0] = v.x; part[j][n][1] = v.y; part[j][n][2] = v.z; part[j][n][3] = v.w;
-                                    } else {
-                                        const float2 v = __ldcg(reinterpret_cast<const float2*>(o0 + sl * HD));
-                                        part[j][n][0] = v.x; part[j][n][1] = v.y;
-                                    }
+                            for (int j = 0; j < CH; ++j) {
+                                const float mj = c0 + j <= c_last ? ml[j].x : -INFINITY;
+                                const float m_new = fmaxf(M, mj);
+                                const float keep = M == -INFINITY ? 0.f : exp2f(M - m_new);
+                                const float f = mj == -INFINITY ? 0.f : exp2f(mj - m_new);
+                                M = m_new;
+                                L = L * keep + ml[j].y * f;
+#pragma unroll
+                                for (int i = 0; i < W / 4; ++i) {
+                                    acc[4 * i] = acc[4 * i] * keep + part[j][i].x * f;
+                                    acc[4 * i + 1] = acc[4 * i + 1] * keep + part[j][i].y * f;
+                                    acc[4 * i + 2] = acc[4 * i + 2] * keep + part[j][i].z * f;
+                                    acc[4 * i + 3] = acc[4 * i + 3] * keep + part[j][i].w * f;
                                 }
                             }
                         }
+                        if (lane == 0) STAMP(13);
+                        bf16* dst = p.out + ((size_t)tok * p.nh + g.kvh * p.G + n) * HD + col;
+                        const float inv = L > 0.f ? 1.f / L : 0.f;
 #pragma unroll
-                        for (int j = 0; j < CH; ++j) {
-                            const bool live = c0 + j <= c_last;
+                        for (int i = 0; i < W; i += 8) {
+                            uint4 v;
+                            uint32_t* u = reinterpret_cast<uint32_t*>(&v);
 #pragma unroll
-                            for (int n = 0; n < GN; ++n) {
-                                if (n < p.G) {
-                                    const float mj = live ? ml[j][n].x : -INFINITY;
-                                    const float m_new = fmaxf(M[n], mj);
-                                    const float keep = M[n] == -INFINITY ? 0.f : exp2f(M[n] - m_new);
-                                    const float f = mj == -INFINITY ? 0.f : exp2f(mj - m_new);
-                                    M[n] = m_new;
-                                    L[n] = L[n] * keep + ml[j][n].y * f;
-#pragma unroll
-                                    for (int i = 0; i < CPL; ++i) acc[n][i] = acc[n][i] * keep + part[j][n][i] * f;
-                                }
+                            for (int e = 0; e < 4; ++e) {
+                                const __nv_bfloat162 t2 = __floats2bfloat162_rn(acc[i + 2 * e] * inv, acc[i + 2 * e + 1] * inv);
+                                u[e] = *reinterpret_cast<const uint32_t*>(&t2);
                             }
-                        }
-                    }
-                    if (lane == 0) STAMP(13);
-#pragma unroll
-                    for (int n = 0; n < GN; ++n) {
-                        if (n < p.G) {
-                            bf16* dst = p.out + ((size_t)tok * p.nh + g.kvh * p.G + n) * HD + lane * CPL;
-                            const float inv = L[n] > 0.f ? 1.f / L[n] : 0.f;
-#pragma unroll
-                            for (int i = 0; i < CPL; i += 2)
-                                *reinterpret_cast<__nv_bfloat162*>(dst + i) = __floats2bfloat162_rn(acc[n][i] * inv, acc[n][i + 1] * inv);
+                            *reinterpret_cast<uint4*>(dst + i) = v;
                         }
                     }
                 }

@@ -83,15 +83,14 @@ __global__ void __launch_bounds__(1024) rmsnorm_kernel(TX* x, const TD* __restri
             float v[4];
             Quad<TX>::load(xr + i, v);
             if (dr) {
-                // the partial products are added in their order; eight loads are in flight at a time (a
-                // round trip to L2 takes microseconds while the next product's weights stream in)
-                for (int s0 = 0; s0 < delta_splits; s0 += 8) {
-                    float d[8][4];
+                // the partial products are added in their order; four loads are in flight at a time
+                for (int s0 = 0; s0 < delta_splits; s0 += 4) {
+                    float d[4][4];
 #pragma unroll
-                    for (int j = 0; j < 8; ++j)
+                    for (int j = 0; j < 4; ++j)
                         if (s0 + j < delta_splits) Quad<TD>::load(dr + (size_t)(s0 + j) * delta_split_stride + i, d[j]);
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
+                    for (int j = 0; j < 4; ++j) {
                         if (s0 + j < delta_splits) {
 #pragma unroll
                             for (int e = 0; e < 4; ++e) v[e] += d[j][e];
@@ -150,6 +149,93 @@ extern "C" int spy_rmsnorm_timeline(unsigned long long* host)
 }
 #endif
 
+// Few rows (decoding): one block per row, the row in registers (QUADS quads of four elements per
+// thread), no shared row buffer, at most 48 registers: a block of 1,024 threads then leaves
+// room on its SM for the blocks of the product that follows, which start streaming their
+// weights before this kernel has finished.  All partial products of a thread's elements are
+// requested together, six quads at a time.
+template <typename TX, typename TD, typename TW, typename TO, int QUADS>
+__global__ void __maxnreg__(48) rmsnorm_row_kernel(TX* x, const TD* __restrict__ delta, int delta_splits, long long delta_split_stride,
+                                                   const int* __restrict__ rows, const TW* __restrict__ w, TO* __restrict__ out, int len, float eps,
+                                                   int write_back)
+{
+    __shared__ float scratch[33];
+#ifdef SPY_TIMELINE
+    unsigned int tl_slot = 0;
+    if (threadIdx.x == 0) tl_slot = atomicAdd(&g_timeline_next, 1u) % 128u;
+#endif
+    RSTAMP(0);
+    pdl_launch_dependents();
+    // the weight depends on no kernel ahead in the stream: it is loaded before the wait for them
+    float wv[QUADS][4];
+#pragma unroll
+    for (int q = 0; q < QUADS; ++q) {
+        const int i = (q * blockDim.x + threadIdx.x) * 4;
+        if (i < len) Quad<TW>::load(w + i, wv[q]);
+    }
+    RSTAMP(1);
+    pdl_wait();
+    RSTAMP(2);
+    const int src_row = rows ? rows[blockIdx.x] : blockIdx.x;
+    TX* xr = x + (size_t)src_row * len;
+    const TD* dr = delta ? delta + (size_t)src_row * len : nullptr;
+    TO* orow = out + (size_t)blockIdx.x * len;
+    float v[QUADS][4];
+#pragma unroll
+    for (int q = 0; q < QUADS; ++q) {
+        const int i = (q * blockDim.x + threadIdx.x) * 4;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[q][e] = 0.f;
+        if (i < len) Quad<TX>::load(xr + i, v[q]);
+    }
+    if (dr) {
+        constexpr int B = 6 / QUADS;
+        for (int s0 = 0; s0 < delta_splits; s0 += B) {
+            float d[B][QUADS][4];
+#pragma unroll
+            for (int j = 0; j < B; ++j)
+#pragma unroll
+                for (int q = 0; q < QUADS; ++q) {
+                    const int i = (q * blockDim.x + threadIdx.x) * 4;
+                    if (s0 + j < delta_splits && i < len) Quad<TD>::load(dr + (size_t)(s0 + j) * delta_split_stride + i, d[j][q]);
+                }
+#pragma unroll
+            for (int j = 0; j < B; ++j)
+#pragma unroll
+                for (int q = 0; q < QUADS; ++q) {
+                    const int i = (q * blockDim.x + threadIdx.x) * 4;
+                    if (s0 + j < delta_splits && i < len) {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) v[q][e] += d[j][q][e];
+                    }
+                }
+        }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int q = 0; q < QUADS; ++q) {
+        const int i = (q * blockDim.x + threadIdx.x) * 4;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) ss += v[q][e] * v[q][e];
+        if (write_back && i < len) Quad<TX>::store(xr + i, v[q]);
+    }
+    RSTAMP(3);
+    ss = block_sum(ss, scratch);
+    RSTAMP(4);
+    const float inv = 1.0f / sqrtf(ss / (float)len + eps);
+#pragma unroll
+    for (int q = 0; q < QUADS; ++q) {
+        const int i = (q * blockDim.x + threadIdx.x) * 4;
+        if (i < len) {
+            float o[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o[e] = (inv * v[q][e]) * wv[q][e];
+            Quad<TO>::store(orow + i, o);
+        }
+    }
+    RSTAMP(5);
+}
+
 template <typename TX, typename TD, typename TW, typename TO>
 static int launch(void* x, const void* delta, int delta_splits, long long delta_split_stride, const int* rows, const void* w, void* out, int n,
                   int len, float eps, int write_back, cudaStream_t stream)
@@ -157,6 +243,20 @@ static int launch(void* x, const void* delta, int delta_splits, long long delta_
     const size_t smem = (size_t)(len + 33) * sizeof(float);
     const bool vec = len % 4 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(delta) | reinterpret_cast<uintptr_t>(w) |
                                        reinterpret_cast<uintptr_t>(out)) & 15) == 0 && delta_split_stride % 4 == 0;
+    if (vec && n < 512 && len <= 8192) {
+        // few rows: the row lives in registers, one or two quads per thread
+        const int quads = len <= 4096 ? 1 : 2;
+        int threads = ((len / 4 + quads - 1) / quads + 31) / 32 * 32;
+        if (threads < 64) threads = 64;
+        if (quads == 1)
+            spy_launch(rmsnorm_row_kernel<TX, TD, TW, TO, 1>, dim3(n), dim3(threads), 0, stream, (TX*)x, (const TD*)delta, delta_splits, delta_split_stride, rows,
+                       (const TW*)w, (TO*)out, len, eps, write_back);
+        else
+            spy_launch(rmsnorm_row_kernel<TX, TD, TW, TO, 2>, dim3(n), dim3(threads), 0, stream, (TX*)x, (const TD*)delta, delta_splits, delta_split_stride, rows,
+                       (const TW*)w, (TO*)out, len, eps, write_back);
+        SPY_CHECK_LAUNCH("rmsnorm (row in registers)");
+        return 0;
+    }
     auto kernel = vec ? rmsnorm_kernel<TX, TD, TW, TO, true> : rmsnorm_kernel<TX, TD, TW, TO, false>;
     if (smem > 48 * 1024) {
         if (smem > 227 * 1024) SPY_FAIL("rmsnorm: a row of %d elements does not fit in shared memory (limit %d)", len, (227 * 1024) / 4 - 33);
