@@ -364,10 +364,67 @@ __device__ __forceinline__ void store_chunk_normal(TC* base, long long ld, int x
 // columns), so the epilogue of a tile (tcgen05.ld, conversion, stores) overlaps the main loop
 // of the next.  Tiles are numbered with the token tiles fastest, so blocks that run side by
 // side share a weight tile in L2.
+// How the persistent kernel deals out its work.  stream_tiles == 0: whole tiles, block b takes
+// tiles b, b + blocks, ...  Otherwise (stream-K) the first stream_tiles tiles are shared out by
+// K blocks: their K blocks are numbered through, tile after tile, and block b takes the numbers
+// [b * per_block, (b + 1) * per_block); the tiles behind them are taken whole as before.  Every SM
+// then gets the same share of the product, where whole tiles would leave SMs idle.  The host shares
+// the tiles out only when there are fewer tiles than SMs (a few hundred tokens): with more, whole
+// tiles round by round are faster although the last round is not full, because the blocks of a
+// round walk K in step and the tiles of a row or column block meet in L2.
+// A block's share is cut into segments, each a range of K blocks of one tile.  A segment that
+// holds a tile's first K block OWNS the tile: if it ends before the tile does (it is then the
+// last segment of the block's share), the following blocks hold the rest (each as its FIRST
+// segment, long finished by then), leave their 32-bit partial tiles in the workspace and raise a
+// flag; the owner adds them in block order and stores the tile.  Flags return to zero by themselves.
+struct Segment {
+    int tile, kb0, kb1;
+};
+struct SegmentWalk {
+    long long at, end;    // K-block numbers of this block's share of the stream tiles
+    int tile, num_tiles;  // the block's next whole tile
+    int k_blocks;
+    __device__ SegmentWalk(int num_tiles_, int k_blocks_, int stream_tiles, int per_block) : num_tiles(num_tiles_), k_blocks(k_blocks_)
+    {
+        const long long total = (long long)stream_tiles * k_blocks;
+        at = (long long)blockIdx.x * per_block;
+        end = at + per_block < total ? at + per_block : total;
+        tile = stream_tiles + blockIdx.x;
+    }
+    __device__ bool next(Segment& s)
+    {
+        if (at < end) {
+            s.tile = (int)(at / k_blocks);
+            s.kb0 = (int)(at - (long long)s.tile * k_blocks);
+            const long long left = end - at;
+            s.kb1 = left < k_blocks - s.kb0 ? s.kb0 + (int)left : k_blocks;
+            at += s.kb1 - s.kb0;
+            return true;
+        }
+        if (tile < num_tiles) {
+            s.tile = tile;
+            s.kb0 = 0;
+            s.kb1 = k_blocks;
+            tile += gridDim.x;
+            return true;
+        }
+        return false;
+    }
+};
+// a partial tile in the workspace: [32-column chunk][quad of the chunk][row][4 floats], so that a
+// warp's 16-byte accesses are contiguous
+__device__ __forceinline__ size_t partial_index(int c, int j, int row) { return ((size_t)((c >> 5) * 8 + j) * BM + row) * 4; }
+__device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+constexpr int STREAM_MAX_BLOCKS = 1024;
+constexpr int STREAM_MIN_KB = 8;   // a block's share is at least this many K blocks
+constexpr int STREAM_TILE_FLOATS = BM * 256;
+__device__ int g_stream_flags[STREAM_MAX_BLOCKS];
+
 template <typename TC, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, TC* __restrict__ out,
-                               long long ld, int x_rows, int y_rows, int k_blocks, int x_tiles, int num_tiles, int* status)
+                               long long ld, int x_rows, int y_rows, int k_blocks, int x_tiles, int num_tiles, int stream_tiles, int per_block,
+                               float* workspace, int* status)
 {
     constexpr int BN = 256;
     using T = Tile<BN>;
@@ -408,23 +465,25 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const 
         if (lane == 0) {
             long long g = 0;   // k-blocks requested so far: the ring position
             bool first = true, ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                const int x0 = (tile % x_tiles) * BM, y0 = (tile / x_tiles) * BN;
-                int kb = 0;
+            SegmentWalk walk(num_tiles, k_blocks, stream_tiles, per_block);
+            Segment sg;
+            while (ok && walk.next(sg)) {
+                const int x0 = (sg.tile % x_tiles) * BM, y0 = (sg.tile / x_tiles) * BN;
+                int kb = sg.kb0;
                 if (first) {
                     // weights (Y) of the first stages before the wait for the kernels ahead in the stream
-                    const int pre = min(k_blocks, T::STAGES);
+                    const int pre = min(sg.kb1 - sg.kb0, T::STAGES);
                     for (int i = 0; i < pre; ++i) {
                         mbar_expect_tx(full_bar + i, T::STAGE_BYTES);
-                        tma_load_2d(smem_u32(tiles + (size_t)i * T::STAGE_BYTES + T::X_BYTES), &map_y, i * BK, y0, full_bar + i);
+                        tma_load_2d(smem_u32(tiles + (size_t)i * T::STAGE_BYTES + T::X_BYTES), &map_y, (sg.kb0 + i) * BK, y0, full_bar + i);
                     }
                     pdl_wait();
-                    for (int i = 0; i < pre; ++i) tma_load_2d(smem_u32(tiles + (size_t)i * T::STAGE_BYTES), &map_x, i * BK, x0, full_bar + i);
-                    kb = pre;
+                    for (int i = 0; i < pre; ++i) tma_load_2d(smem_u32(tiles + (size_t)i * T::STAGE_BYTES), &map_x, (sg.kb0 + i) * BK, x0, full_bar + i);
+                    kb = sg.kb0 + pre;
                     g = pre;
                     first = false;
                 }
-                for (; kb < k_blocks; ++kb, ++g) {
+                for (; kb < sg.kb1; ++kb, ++g) {
                     const int s = (int)(g % T::STAGES);
                     const uint32_t phase = (uint32_t)(g / T::STAGES) & 1;
                     if (g >= T::STAGES && !mbar_wait(empty_bar + s, phase ^ 1, abort_flag)) { ok = false; break; }
@@ -442,14 +501,16 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const 
             long long g = 0;
             int i = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++i) {
+            SegmentWalk walk(num_tiles, k_blocks, stream_tiles, per_block);
+            Segment sg;
+            for (; ok && walk.next(sg); ++i) {
                 const int buf = i & 1;
                 const uint32_t aph = (uint32_t)(i >> 1) & 1;
                 if (i >= 2) ok = mbar_wait(acc_empty + buf, aph ^ 1, abort_flag);   // the epilogue has read this buffer's last tile
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t acc = tmem_base + (uint32_t)buf * BN;
-                for (int kb = 0; kb < k_blocks; ++kb, ++g) {
+                for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++g) {
                     const int s = (int)(g % T::STAGES);
                     const uint32_t phase = (uint32_t)(g / T::STAGES) & 1;
                     ok = mbar_wait(full_bar + s, phase, abort_flag);
@@ -460,7 +521,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const 
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k) {
                         const uint64_t adv = (uint64_t)((k * UMMA_K * 2) >> 4);
-                        umma(acc, dx + adv, dy + adv, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        umma(acc, dx + adv, dy + adv, idesc, (kb > sg.kb0 || k > 0) ? 1u : 0u);
                     }
                     umma_commit(empty_bar + s);
                 }
@@ -472,20 +533,109 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const 
         pdl_wait();   // the output buffer may still be in use by a kernel ahead in the stream
         int i = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++i) {
+        SegmentWalk walk(num_tiles, k_blocks, stream_tiles, per_block);
+        Segment sg;
+        for (; ok && walk.next(sg); ++i) {
             const int buf = i & 1;
             const uint32_t aph = (uint32_t)(i >> 1) & 1;
-            const int x0 = (tile % x_tiles) * BM, y0 = (tile / x_tiles) * BN;
+            const int x0 = (sg.tile % x_tiles) * BM, y0 = (sg.tile / x_tiles) * BN;
             ok = mbar_wait(acc_full + buf, aph, abort_flag);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int x = x0 + quarter * 32 + lane;
+            const int row = quarter * 32 + lane, x = x0 + row;
+            if (sg.kb0 > 0) {
+                // the rest of a tile that a block before this one owns: the partial tile goes to the workspace
+                float* mine = workspace + (size_t)blockIdx.x * STREAM_TILE_FLOATS;
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
-                uint32_t r[32];
-                tmem_load<32>(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c), r);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                store_chunk_normal<TC, EPI>(out, ld, x, y0 + c, x_rows, y_rows, r);
+                for (int c = 0; c < BN; c += 32) {
+                    uint32_t r[32];
+                    tmem_load<32>(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c), r);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        __stcg(reinterpret_cast<float4*>(mine + partial_index(c, j, row)),
+                               make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3])));
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                mbar_arrive(acc_empty + buf);
+                __threadfence();
+                epilogue_barrier();
+                if (row == 0) {
+                    __threadfence();
+                    atomicExch(&g_stream_flags[blockIdx.x], 1);
+                }
+                continue;
+            }
+            const int helpers_kb = k_blocks - sg.kb1;   // K blocks of this tile that the following blocks hold
+            int helper = blockIdx.x + 1;
+            if (helpers_kb > 0) {
+                // every following block holds per_block K blocks of the rest, the last one what is left
+                for (int rest = helpers_kb, h = helper; rest > 0 && ok; rest -= per_block, ++h) {
+                    const unsigned long long t0 = global_timer();
+                    while (atomicAdd(&g_stream_flags[h], 0) == 0) {
+                        if (global_timer() - t0 > WAIT_LIMIT_NS) {
+                            *abort_flag = 1;
+                            ok = false;
+                            break;
+                        }
+                    }
+                }
+                __threadfence();
+            }
+            if (helpers_kb > 0 && ok) {
+                // the helpers' partial chunks are requested two chunks ahead of their use: a round trip to L2
+                // a chunk would otherwise hold the accumulator, and with it the tensor core, for microseconds
+                float4 pre[3][8];
+                auto fetch = [&](int c, float4 (&dst)[8]) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) dst[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int rest = helpers_kb, h = helper; rest > 0; rest -= per_block, ++h) {
+                        const float* theirs = workspace + (size_t)h * STREAM_TILE_FLOATS;
+                        float4 v[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) v[j] = __ldcg(reinterpret_cast<const float4*>(theirs + partial_index(c, j, row)));
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            dst[j].x += v[j].x;
+                            dst[j].y += v[j].y;
+                            dst[j].z += v[j].z;
+                            dst[j].w += v[j].w;
+                        }
+                    }
+                };
+                fetch(0, pre[0]);
+                fetch(32, pre[1]);
+#pragma unroll
+                for (int ci = 0; ci < BN / 32; ++ci) {
+                    const int c = ci * 32;
+                    if (ci + 2 < BN / 32) fetch(c + 64, pre[(ci + 2) % 3]);
+                    uint32_t r[32];
+                    tmem_load<32>(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c), r);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float4 v = pre[ci % 3][j];
+                        r[4 * j] = __float_as_uint(__uint_as_float(r[4 * j]) + v.x);
+                        r[4 * j + 1] = __float_as_uint(__uint_as_float(r[4 * j + 1]) + v.y);
+                        r[4 * j + 2] = __float_as_uint(__uint_as_float(r[4 * j + 2]) + v.z);
+                        r[4 * j + 3] = __float_as_uint(__uint_as_float(r[4 * j + 3]) + v.w);
+                    }
+                    store_chunk_normal<TC, EPI>(out, ld, x, y0 + c, x_rows, y_rows, r);
+                }
+            } else {
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 32) {
+                    uint32_t r[32];
+                    tmem_load<32>(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c), r);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    store_chunk_normal<TC, EPI>(out, ld, x, y0 + c, x_rows, y_rows, r);
+                }
+            }
+            if (helpers_kb > 0) {
+                // every thread has read the partial tiles: their flags go back to zero for the next product
+                epilogue_barrier();
+                if (row == 0)
+                    for (int rest = helpers_kb, h = helper; rest > 0; rest -= per_block, ++h) g_stream_flags[h] = 0;
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(acc_empty + buf);
@@ -737,12 +887,8 @@ namespace {
 // SPYINFER_GEMM_PAIRS=0 in the environment keeps the products for many tokens on single blocks.
 bool pair_kernel_enabled()
 {
-    static int enabled = -1;
-    if (enabled < 0) {
-        const char* e = getenv("SPYINFER_GEMM_PAIRS");
-        enabled = (e != nullptr && e[0] == '0') ? 0 : 1;
-    }
-    return enabled == 1;
+    const char* e = getenv("SPYINFER_GEMM_PAIRS");   // read at every call: a test may switch it
+    return !(e != nullptr && e[0] == '0');
 }
 
 struct Plan {
@@ -753,18 +899,7 @@ Plan make_plan(int M, int N, int K, bool may_split)
 {
     const int k_blocks = (K + BK - 1) / BK;
     Plan best = {1, BM};
-    if (M > 64) {
-        const int tiles = ((M + BM - 1) / BM) * ((N + 255) / 256);
-        if (tiles < 148 && may_split) {
-            int splits = (296 + tiles - 1) / tiles;
-            const int most = k_blocks / 4 > 0 ? k_blocks / 4 : 1;   // at least four K blocks per split
-            if (splits > most) splits = most;
-            if (splits > 16) splits = 16;
-            const int per = (k_blocks + splits - 1) / splits;       // no empty trailing split
-            best.splits = (k_blocks + per - 1) / per;
-        }
-        return best;
-    }
+    if (M > 64) return best;   // many tokens: the persistent kernels share the work out themselves (stream-K)
     const int slots = 296;
     if ((N + BM - 1) / BM >= slots) return best;   // more 128-row tiles than slots: they spread evenly as they are
     int most = may_split ? (k_blocks / 4 > 0 ? k_blocks / 4 : 1) : 1;
@@ -844,7 +979,9 @@ extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, 
     const long long ld = splits > 1 ? N : ldc;
     const long long split_stride = splits > 1 ? (long long)M * N : 0;
     const bool f32_out = splits > 1 || c_dtype == SPY_F32;
-    if (!swap && splits == 1 && M >= 512 && pair_kernel_enabled()) {
+    // pairs need enough 256 x 256 tiles to occupy at least half of the clusters; smaller products go to single
+    // blocks, which share the K blocks of their 128 x 256 tiles out over all SMs
+    if (!swap && splits == 1 && M >= 512 && (long long)((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256) >= 37 && pair_kernel_enabled()) {
         // many tokens, one pass over K, at least two 256-row tiles: pairs of blocks on 256 x 256 tiles
         CUtensorMap my_half;
         if (make_map(&my_half, W, N, K, ldw, BM)) return 1;
@@ -899,7 +1036,28 @@ extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, 
         const int x_tiles = (M + BM - 1) / BM, y_tiles = (N + 255) / 256;
         const long long num_tiles = (long long)x_tiles * y_tiles;
         if (num_tiles > 0x7fffffffLL) SPY_FAIL("gemm_tcgen05: %lld tiles exceed the kernel's range", num_tiles);
-        const int grid = (int)(num_tiles < num_sms ? num_tiles : num_sms);
+        int grid = (int)(num_tiles < num_sms ? num_tiles : num_sms);
+        // stream-K when the scratch holds a partial tile for every block: the K blocks of all tiles are
+        // shared out evenly over as many blocks as there are SMs (fewer for very small products)
+        int per_block = 0, stream_tiles = 0;
+        long long blocks = num_sms;
+        if (blocks > STREAM_MAX_BLOCKS) blocks = STREAM_MAX_BLOCKS;
+        if (scratch != nullptr && blocks > scratch_floats / STREAM_TILE_FLOATS) blocks = scratch_floats / STREAM_TILE_FLOATS;
+        if (scratch != nullptr && blocks >= 1 && num_tiles < blocks) {
+            // Fewer tiles than SMs: their K blocks are shared out, so that a block gets at least a quarter of a
+            // tile and STREAM_MIN_KB K blocks.  With more tiles than SMs whole tiles stay faster, although the
+            // last round is not full (measured at 2,048 tokens: 55.7 against 62 to 64 microseconds for N = K =
+            // 4096): the blocks of a round walk K in step, so the tiles of a row or column block meet in L2,
+            // and blocks with shares start at different K and do not.
+            stream_tiles = (int)num_tiles;
+            const long long total = (long long)stream_tiles * k_blocks;
+            long long least = k_blocks / 4 > STREAM_MIN_KB ? k_blocks / 4 : STREAM_MIN_KB;
+            if (least > k_blocks) least = k_blocks;
+            if (total / blocks < least) blocks = total / least > 0 ? total / least : 1;
+            per_block = (int)((total + blocks - 1) / blocks);
+            grid = (int)((total + per_block - 1) / per_block);
+            if (num_tiles > stream_tiles && grid < blocks) grid = (int)blocks;   // whole tiles behind the shared ones: every block takes some
+        }
         static bool configured = false;
         if (!configured) {
             SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<bf16, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Tile<256>::SMEM));
@@ -909,13 +1067,13 @@ extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, 
         }
         if (epilogue == 1)
             spy_launch(gemm_tcgen05_persistent_kernel<bf16, 1>, dim3(grid), dim3(NUM_THREADS), Tile<256>::SMEM, stream, mx, my, (bf16*)C, ldc, M, N,
-                       k_blocks, x_tiles, (int)num_tiles, status);
+                       k_blocks, x_tiles, (int)num_tiles, stream_tiles, per_block, scratch, status);
         else if (c_dtype == SPY_F32)
             spy_launch(gemm_tcgen05_persistent_kernel<float, 0>, dim3(grid), dim3(NUM_THREADS), Tile<256>::SMEM, stream, mx, my, (float*)C, ldc, M, N,
-                       k_blocks, x_tiles, (int)num_tiles, status);
+                       k_blocks, x_tiles, (int)num_tiles, stream_tiles, per_block, scratch, status);
         else
             spy_launch(gemm_tcgen05_persistent_kernel<bf16, 0>, dim3(grid), dim3(NUM_THREADS), Tile<256>::SMEM, stream, mx, my, (bf16*)C, ldc, M, N,
-                       k_blocks, x_tiles, (int)num_tiles, status);
+                       k_blocks, x_tiles, (int)num_tiles, stream_tiles, per_block, scratch, status);
         SPY_CHECK_LAUNCH("gemm_tcgen05 (persistent)");
         return 0;
     }

@@ -404,7 +404,32 @@ def test_gemm_tcgen05_swiglu_epilogue(M, I, K):
     torch.testing.assert_close(out.float(), ref.to(torch.bfloat16).float(), rtol=1.6e-2, atol=2e-3)
 
 
-@pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (24, 1024, 2048), (64, 384, 12288), (200, 512, 4096)])
+@pytest.mark.parametrize("M,N,K,epilogue", [(200, 512, 4096, None), (65, 256, 64, None), (130, 4096, 4096, None), (640, 4096, 4096, "swiglu"),
+                                              (1000, 1280, 12288, None), (2048, 4096, 4096, None), (300, 776, 1096, "swiglu")])
+def test_gemm_tcgen05_shares_k_blocks_evenly(M, N, K, epilogue, monkeypatch):
+    """Many tokens on single blocks (pairs switched off): the K blocks of all tiles are shared out
+    evenly over the SMs, tiles that straddle two blocks are summed through the workspace; the result
+    is the product, twice in a row (the flags have to come back to zero) and the same both times."""
+    from spyinfer_b200 import kernels
+    monkeypatch.setenv("SPYINFER_GEMM_PAIRS", "0")
+    torch.manual_seed(M + N)
+    a = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
+    ref = a.float() @ w.float().t()
+    if epilogue == "swiglu":
+        g, u = ref[:, 0::2], ref[:, 1::2]
+        ref = ((g / (1 + torch.exp(-g))) * u).to(torch.bfloat16).float()
+        outs = [kernels.gemm_tcgen05(a, w, epilogue="swiglu").float() for _ in range(2)]
+        tol = dict(rtol=1.6e-2, atol=2e-3)
+    else:
+        outs = [kernels.gemm_tcgen05(a, w, out_dtype=torch.float32) for _ in range(2)]
+        tol = dict(rtol=1e-4, atol=3e-4)
+    torch.cuda.synchronize()
+    assert torch.equal(outs[0], outs[1])
+    torch.testing.assert_close(outs[0], ref, **tol)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (24, 1024, 2048), (64, 384, 12288)])
 def test_gemm_tcgen05_deferred_reduction(M, N, K):
     """With defer=True a split-K product hands back its partial products; their sum is the product."""
     from spyinfer_b200 import kernels
