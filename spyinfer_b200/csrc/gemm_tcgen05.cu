@@ -269,13 +269,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                         }
                     }
                 } else if constexpr (EPI == 1 && SWAP) {
-                    // lanes 2i and 2i + 1 hold gate row and up row of output x / 2 for every token
+                    // lanes 2i and 2i + 1 hold gate row and up row of output x / 2 for every token.  Two tokens
+                    // at a time: the even lane sends the second token's gate and finishes the first token, the
+                    // odd lane sends the first token's up and finishes the second, so every lane computes and stores
+                    const bool odd = (lane & 1) != 0;
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
+                    for (int j = 0; j < 32; j += 2) {
                         if (j < cols) {
-                            const float mine = __uint_as_float(r[j]);
-                            const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
-                            if ((lane & 1) == 0 && x < x_rows && y + j < y_rows) store_elem(base + (size_t)(y + j) * ld + x / 2, silu_mul(mine, other));
+                            const float a = __uint_as_float(r[j]), b = __uint_as_float(r[j + 1]);
+                            const float got = __shfl_xor_sync(0xffffffffu, odd ? a : b, 1);
+                            const float v = silu_mul(odd ? got : a, odd ? b : got);
+                            const int t = y + j + (odd ? 1 : 0);
+                            if (x < x_rows && t < y_rows) store_elem(base + (size_t)t * ld + x / 2, v);
                         }
                     }
                 } else if constexpr (!SWAP) {
