@@ -10,8 +10,11 @@
 // inside the library (SPY_GEMM_STATIC_SCRATCH_FLOATS floats on every GPU that loads it), so
 // the call makes no cudaMalloc, no cudaFree and no call into an allocating library.
 //
-// * Sizes whose plan needs more scratch than that are refused (return 1; the message is at
-//   spy_gemm_tcgen05_last_error()).
+// * Few tokens (at most 64): K may be split, and the plans of that class need less than the
+//   array; a plan that needed more would be refused (return 1; the message is at
+//   spy_gemm_tcgen05_last_error()).  A few hundred tokens with fewer tiles than SMs: the K
+//   blocks are shared out over the SMs, one partial tile of 128 x 256 floats a block, over as
+//   many blocks as the array holds tiles for (128).
 // * The first call on a device looks the array's device address up (cudaGetSymbolAddress);
 //   make it before any stream capture.
 // * All calls on a device share the array.  Nothing needs clearing between calls; calls that
