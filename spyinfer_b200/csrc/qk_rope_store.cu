@@ -149,14 +149,14 @@ __global__ void __launch_bounds__(256) qk_rope_store_hd128_kernel(const TS* src,
     const int item = min(mine, items - 1);   // an item beyond the end repeats the last one and stores nothing
     const int t = item / heads, head = item - t * heads;
     const int kind = head < nh ? 0 : (head < nh + nkv ? 1 : 2);  // q, k, v
-    // ---- round 1: the position
+    // ---- first loads: the position
     const int pos = positions[t];
     const int seq = kind == 0 ? 0 : seq_of_token[t];
     const TW* w = kind == 0 ? q_w : k_w;
     float wv[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) wv[i] = (q_w != nullptr && kind != 2) ? to_f32(w[8 * l + i]) : 1.f;
-    // ---- round 2: what the position leads to
+    // ---- second loads: what the position leads to
     const bool in_table = kind != 0 && pos >= 0 && pos / page_size < table_width;
     const int page = in_table ? block_table[(size_t)seq * table_width + pos / page_size] : -1;
     const bool rotate = kind != 2 && cos_sin != nullptr;
