@@ -151,10 +151,21 @@ def main() -> int:
     page = 16
     max_batch = max(args.batch, 1 if args.no_points else 64)
     ctx = args.context
+    torch.cuda.set_device(0)
+    # a batch of 64 at the full context does not fit beside the weights of every shape (32B: 137 GB of
+    # cache beside 65 GB of weights): the batch-64 points are then left out, and the line says so
+    c0 = model_config
+    est_weights = 2 * (layers * (c0.hidden_size * (c0.num_attention_heads + 2 * c0.num_key_value_heads) * c0.head_dim
+                                 + c0.num_attention_heads * c0.head_dim * c0.hidden_size + 3 * c0.hidden_size * c0.intermediate_size)
+                       + 2 * c0.vocab_size * c0.hidden_size)
+    est_cache = lambda b: b * (ctx + 32) * 4 * c0.num_key_value_heads * c0.head_dim * layers
+    points_batches = (1, 64)
+    if not args.no_points and est_weights + est_cache(64) > 0.92 * torch.cuda.get_device_properties(0).total_memory:
+        points_batches = (1,)
+        max_batch = max(args.batch, 1)
     total_steps = warmup + args.steps + 8
     pages_per_req = (ctx + page - 1) // page + 1
     num_pages = max_batch * pages_per_req + (args.prefill_tokens + page - 1) // page + 8
-    torch.cuda.set_device(0)
     engine = LLMEngine(model_config=model_config, seed=0, dtype="bfloat16", max_num_seqs=max_batch, max_model_len=max(ctx, args.prefill_tokens) + 16,
                        kvcache_block_size=page, num_kvcache_blocks=num_pages, max_num_batched_tokens=max(args.prefill_tokens, max_batch))
     runner, cache = engine.runner, engine.runner.cache
@@ -277,9 +288,9 @@ def main() -> int:
         out["e2e"] = {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
     if not args.no_points:
         points = {}
-        for b in (1, 64):
+        for b in points_batches:
             points[f"decode_b{b}"] = round(decode_device(b, ctx, args.steps, warmup)[0], 1)
-        for b in (1, 8, 64):
+        for b in (1, 8) + points_batches[1:]:
             points[f"decode_b{b}_ctx640"] = round(decode_device(b, 640 + (args.steps + warmup) // 2, args.steps, warmup)[0], 1)
         out["points"] = points
     print(json.dumps(out))
