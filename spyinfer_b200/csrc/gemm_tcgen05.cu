@@ -104,7 +104,14 @@ __device__ __forceinline__ void store_row32(TC* dst, const uint32_t (&r)[32], in
     }
 }
 
-__device__ __forceinline__ float silu_mul(float g, float u) { return (g / (1.0f + expf(-g))) * u; }
+__device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }   // the four epilogue warps
+constexpr int SWIGLU_STAGE_LD = 66;   // bf16 elements between the tokens of a staged SwiGLU tile (64 outputs and a pad)
+
+// silu(g) * u for a bfloat16 result: the fast exponential and division (2 ulp of float each) are far
+// inside the result's rounding, and the accurate ones cost the epilogue warps more instructions than all
+// the rest of a tile's read-out (64 tokens: 4.0 against 1.5 microseconds).  A gate below -87 gives
+// g / inf = -0, the limit.  The 32-bit path has its own SwiGLU kernel with the accurate functions.
+__device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
 
 // X: [x_rows, K] in the instruction's M slot; Y: [y_rows, K] in its N slot.
 // SWAP == false: out[x, y] (row stride ld);  SWAP == true: out[y, x].
@@ -271,16 +278,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 } else if constexpr (EPI == 1 && SWAP) {
                     // lanes 2i and 2i + 1 hold gate row and up row of output x / 2 for every token.  Two tokens
                     // at a time: the even lane sends the second token's gate and finishes the first token, the
-                    // odd lane sends the first token's up and finishes the second, so every lane computes and stores
+                    // odd lane sends the first token's up and finishes the second, so every lane computes.
+                    // The results go to shared memory (the stages are free by now) and from there to the
+                    // output in rows: a 2-byte store per token and lane straight from here queues behind the
+                    // weight tiles that the next product's blocks on this SM have already asked for.
                     const bool odd = (lane & 1) != 0;
+                    bf16* staged = reinterpret_cast<bf16*>(tiles);
 #pragma unroll
                     for (int j = 0; j < 32; j += 2) {
                         if (j < cols) {
                             const float a = __uint_as_float(r[j]), b = __uint_as_float(r[j + 1]);
                             const float got = __shfl_xor_sync(0xffffffffu, odd ? a : b, 1);
                             const float v = silu_mul(odd ? got : a, odd ? b : got);
-                            const int t = y + j + (odd ? 1 : 0);
-                            if (x < x_rows && t < y_rows) store_elem(base + (size_t)t * ld + x / 2, v);
+                            staged[(c + j + (odd ? 1 : 0)) * SWIGLU_STAGE_LD + ((quarter * 32 + lane) >> 1)] = __float2bfloat16_rn(v);
                         }
                     }
                 } else if constexpr (!SWAP) {
@@ -294,6 +304,26 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 #pragma unroll
                         for (int j = 0; j < 32; ++j)
                             if (j < cols && y + j < y_rows) store_elem(base + (size_t)(y + j) * ld + x, __uint_as_float(r[j]));
+                    }
+                }
+            }
+            if constexpr (EPI == 1 && SWAP) {
+                // rows of the staged tile to the output, 4 bytes a lane where the row allows it
+                epilogue_barrier();
+                const bf16* staged = reinterpret_cast<const bf16*>(tiles);
+                const int e = quarter * 32 + lane;
+                const int outs = min(tile_rows, x_rows - x0) / 2, rows = min(BN, y_rows - y0);
+                TC* gout = base + (size_t)y0 * ld + x0 / 2;
+                if ((outs & 1) == 0 && (ld & 1) == 0 && (reinterpret_cast<uintptr_t>(gout) & 3) == 0) {
+                    const int words = outs / 2;
+                    for (int i = e; i < rows * words; i += 128) {
+                        const int t = i / words, q = i - t * words;
+                        *reinterpret_cast<uint32_t*>(gout + (size_t)t * ld + 2 * q) = *reinterpret_cast<const uint32_t*>(staged + t * SWIGLU_STAGE_LD + 2 * q);
+                    }
+                } else {
+                    for (int i = e; i < rows * outs; i += 128) {
+                        const int t = i / outs, q = i - t * outs;
+                        gout[(size_t)t * ld + q] = staged[t * SWIGLU_STAGE_LD + q];
                     }
                 }
             }
@@ -419,7 +449,6 @@ struct SegmentWalk {
 // a partial tile in the workspace: [32-column chunk][quad of the chunk][row][4 floats], so that a
 // warp's 16-byte accesses are contiguous
 __device__ __forceinline__ size_t partial_index(int c, int j, int row) { return ((size_t)((c >> 5) * 8 + j) * BM + row) * 4; }
-__device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 constexpr int STREAM_MAX_BLOCKS = 1024;
 constexpr int STREAM_MIN_KB = 8;   // a block's share is at least this many K blocks
 constexpr int STREAM_TILE_FLOATS = BM * 256;
