@@ -265,7 +265,7 @@ def test_sampling_greedy_and_distribution():
 
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("M,N,K", [(1, 128, 64), (5, 200, 96), (16, 4096, 4096), (17, 1000, 520), (33, 136, 72), (64, 6144, 512),
-                                   (65, 300, 136), (128, 256, 64), (129, 1187, 1032), (300, 512, 4096), (1000, 24, 200), (2048, 1024, 12288),
+                                   (65, 300, 136), (128, 256, 64), (100, 4096, 4096), (128, 6144, 4096), (90, 1187, 1032), (129, 1187, 1032), (300, 512, 4096), (1000, 24, 200), (2048, 1024, 12288),
                                    (2048, 4096, 512), (1500, 3000, 264), (4100, 2600, 72)])
 def test_gemm_tcgen05(out_dtype, M, N, K):
     """Tensor-core product at sizes that exercise every tile class (16/32/64 tokens swapped,
@@ -387,7 +387,7 @@ def test_attention_mma_finds_one_far_key(split_keys):
         assert hit == inside, f"window {window}, far key {far}: expected {'a hit' if inside else 'no hit'}"
 
 
-@pytest.mark.parametrize("M,I,K", [(3, 100, 64), (16, 328, 200), (40, 1000, 136), (64, 6144, 512), (130, 520, 264), (300, 12288, 1024),
+@pytest.mark.parametrize("M,I,K", [(3, 100, 64), (16, 328, 200), (40, 1000, 136), (64, 6144, 512), (70, 520, 264), (128, 12288, 1024), (130, 520, 264), (300, 12288, 1024),
                                    (520, 1000, 136), (1100, 2304, 512)])   # 512 rows and more: pairs of blocks on 256 x 256 tiles
 def test_gemm_tcgen05_swiglu_epilogue(M, I, K):
     """Gate and up rows interleaved in the weight; the product's epilogue applies SwiGLU."""
@@ -429,7 +429,7 @@ def test_gemm_tcgen05_shares_k_blocks_evenly(M, N, K, epilogue, monkeypatch):
     torch.testing.assert_close(outs[0], ref, **tol)
 
 
-@pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (24, 1024, 2048), (64, 384, 12288)])
+@pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (24, 1024, 2048), (64, 384, 12288), (100, 4096, 4096), (128, 1024, 12288)])
 def test_gemm_tcgen05_deferred_reduction(M, N, K):
     """With defer=True a split-K product hands back its partial products; their sum is the product."""
     from spyinfer_b200 import kernels
