@@ -61,10 +61,23 @@ __global__ void sample_slices_kernel(const float* __restrict__ logits, long long
     const uint64_t key = mix64((seed ? (uint64_t)seed[r] : 0) ^ mix64(draw ? (uint64_t)draw[r] : 0));
     float bv = -INFINITY;
     int bi = NONE;
-    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
-        float v = row[i];
+    auto take = [&](float v, int i) {
         if (temp > 0.f) v = v / temp - logf(-logf(uniform_open(key, (uint32_t)i)));
         if (bi == NONE || v > bv) { bv = v; bi = i; }   // ascending i: the lowest index is kept on ties
+    };
+    if (((reinterpret_cast<uintptr_t>(row) | (uintptr_t)lo * 4) & 15) == 0) {
+        // 16-byte loads; a thread's indices still ascend
+        const int quads = (hi - lo) / 4;
+        for (int q = threadIdx.x; q < quads; q += blockDim.x) {
+            const float4 v = *reinterpret_cast<const float4*>(row + lo + 4 * q);
+            take(v.x, lo + 4 * q);
+            take(v.y, lo + 4 * q + 1);
+            take(v.z, lo + 4 * q + 2);
+            take(v.w, lo + 4 * q + 3);
+        }
+        for (int i = lo + 4 * quads + threadIdx.x; i < hi; i += blockDim.x) take(row[i], i);
+    } else {
+        for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) take(row[i], i);
     }
     block_best(bv, bi);
     if (threadIdx.x == 0) {
@@ -97,7 +110,7 @@ extern "C" int spy_sample(const float* logits, long long row_stride, int rows, i
     if (vocab <= 0 || row_stride < vocab) SPY_FAIL("sample: vocab %d must be positive and fit the row stride %lld", vocab, row_stride);
     if (rows > 65535) SPY_FAIL("sample: %d rows exceed the grid limit", rows);
     const int slices = spy_sample_slices(vocab);
-    const int slice = (vocab + slices - 1) / slices;
+    const int slice = ((vocab + slices - 1) / slices + 3) / 4 * 4;   // a multiple of 4: slices start on 16-byte boundaries
     dim3 grid(slices, rows);
     spy_launch(sample_slices_kernel, grid, dim3(256), 0, stream, logits, row_stride, vocab, slice, temperature, seed, draw, slice_v, slice_i);
     SPY_CHECK_LAUNCH("sample (slices)");
