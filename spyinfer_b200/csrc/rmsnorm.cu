@@ -155,7 +155,7 @@ extern "C" int spy_rmsnorm_timeline(unsigned long long* host)
 // weights before this kernel has finished.  All partial products of a thread's elements are
 // requested together, six quads at a time.
 template <typename TX, typename TD, typename TW, typename TO, int QUADS>
-__global__ void __maxnreg__(48) rmsnorm_row_kernel(TX* x, const TD* __restrict__ delta, int delta_splits, long long delta_split_stride,
+__global__ void __maxnreg__(QUADS <= 2 ? 48 : 80) rmsnorm_row_kernel(TX* x, const TD* __restrict__ delta, int delta_splits, long long delta_split_stride,
                                                    const int* __restrict__ rows, const TW* __restrict__ w, TO* __restrict__ out, int len, float eps,
                                                    int write_back)
 {
@@ -189,7 +189,7 @@ __global__ void __maxnreg__(48) rmsnorm_row_kernel(TX* x, const TD* __restrict__
         if (i < len) Quad<TX>::load(xr + i, v[q]);
     }
     if (dr) {
-        constexpr int B = 6 / QUADS;
+        constexpr int B = QUADS <= 2 ? 6 / QUADS : 1;
         for (int s0 = 0; s0 < delta_splits; s0 += B) {
             float d[B][QUADS][4];
 #pragma unroll
@@ -243,17 +243,19 @@ static int launch(void* x, const void* delta, int delta_splits, long long delta_
     const size_t smem = (size_t)(len + 33) * sizeof(float);
     const bool vec = len % 4 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(delta) | reinterpret_cast<uintptr_t>(w) |
                                        reinterpret_cast<uintptr_t>(out)) & 15) == 0 && delta_split_stride % 4 == 0;
-    if (vec && n < 512 && len <= 8192) {
-        // few rows: the row lives in registers, one or two quads per thread
-        const int quads = len <= 4096 ? 1 : 2;
+    if (vec && (n < 512 ? len <= 8192 : len <= 16384)) {
+        // the row lives in registers.  Few rows: one or two quads per thread, the row spread as wide as it goes;
+        // many rows: four quads per thread, all their loads in flight together, several blocks an SM
+        const int quads = n >= 512 ? 4 : (len <= 4096 ? 1 : 2);
         int threads = ((len / 4 + quads - 1) / quads + 31) / 32 * 32;
         if (threads < 64) threads = 64;
-        if (quads == 1)
-            spy_launch(rmsnorm_row_kernel<TX, TD, TW, TO, 1>, dim3(n), dim3(threads), 0, stream, (TX*)x, (const TD*)delta, delta_splits, delta_split_stride, rows,
-                       (const TW*)w, (TO*)out, len, eps, write_back);
-        else
-            spy_launch(rmsnorm_row_kernel<TX, TD, TW, TO, 2>, dim3(n), dim3(threads), 0, stream, (TX*)x, (const TD*)delta, delta_splits, delta_split_stride, rows,
-                       (const TW*)w, (TO*)out, len, eps, write_back);
+#define SPY_RMS_ROW(Q_)                                                                                                                          \
+    spy_launch(rmsnorm_row_kernel<TX, TD, TW, TO, Q_>, dim3(n), dim3(threads), 0, stream, (TX*)x, (const TD*)delta, delta_splits, delta_split_stride, \
+               rows, (const TW*)w, (TO*)out, len, eps, write_back)
+        if (quads == 1) SPY_RMS_ROW(1);
+        else if (quads == 2) SPY_RMS_ROW(2);
+        else SPY_RMS_ROW(4);
+#undef SPY_RMS_ROW
         SPY_CHECK_LAUNCH("rmsnorm (row in registers)");
         return 0;
     }
