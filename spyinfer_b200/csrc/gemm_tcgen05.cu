@@ -4,13 +4,15 @@
 // tcgen05.mma (128 x BN x 16 per instruction), four warps read the accumulator back with
 // tcgen05.ld and store bfloat16 or float32.
 //
-// One block computes one 128 x BN tile of "X . Y^T" over a range of K:
-//   normal mode: X = activations (128 tokens), Y = weights (BN = 128 or 256 outputs);
-//   swapped mode (few tokens): X = weights (128 outputs fill the instruction's M slot),
-//     Y = activations (BN = 16, 32 or 64 tokens); the tile is stored transposed.
-// With split-K every split stores its 32-bit partial tile into scratch memory and a second
-// kernel sums the splits in a fixed order; the number of splits depends only on the shape
-// class, so a token's result does not depend on the batch beyond rounding.
+// Three kernels, chosen by the number of tokens M:
+//   up to 256 tokens (gemm_tcgen05_kernel): one block computes one tile over a range of K with the
+//     weights in the instruction's M slot (up to 128 outputs) and a tile of 16, 32 or 64 tokens in
+//     its N slot; the tile is stored transposed.  With split-K every split stores its 32-bit
+//     partial tile into scratch memory and the consumer (or a second kernel) sums the splits in a
+//     fixed order; the number of splits depends only on the shape class, so a token's result
+//     does not depend on the batch beyond rounding;
+//   more tokens (gemm_tcgen05_persistent_kernel): 128 tokens x 256 outputs a tile, one block an SM;
+//   512 tokens and more (gemm_tcgen05_pair_kernel): 256 x 256 tiles on pairs of blocks.
 // Tails: rows beyond M or N and the end of K are zero-filled by TMA; stores are predicated.
 // K must be a multiple of 8 (16-byte rows for TMA).  No cluster multicast is used.
 //
@@ -33,28 +35,35 @@ constexpr int BK = 64;             // 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int NUM_THREADS = 192;   // warp 0: TMA, warp 1: MMA + TMEM, warps 2..5: epilogue
 
+// The one-tile kernel (few tokens): BN tokens in the N slot, up to 128 weight rows in the M slot.
+// Two blocks share an SM, each with AREA bytes of stages.  The stages are packed: a tile of fewer
+// than 128 weight rows takes only its own bytes (rounded up to the swizzle's 1 KB), so more stages
+// fit the area and as many bytes stay in flight as with full tiles.  The tensor core still reads
+// 128 rows: the spare ones come from whatever lies behind (the next stage; the area ends with
+// room for that) and feed accumulator rows that are never stored.
 template <int BN> struct Tile {
     static constexpr int X_BYTES = BM * BK * 2;
     static constexpr int Y_BYTES = BN * BK * 2;
-    static constexpr int STAGE_BYTES = X_BYTES + Y_BYTES;
-    // few-token tiles keep about 100 KB so that two blocks share an SM; large tiles take the SM
-    static constexpr int STAGES = BN <= 64 ? (100 * 1024) / STAGE_BYTES : (200 * 1024) / STAGE_BYTES;
     static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
-    static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
-    // The one-tile kernel packs its stages: a tile of fewer than 128 weight rows takes only its
-    // own bytes (rounded up to the swizzle's 1 KB), so more stages fit the same area and as many
-    // bytes stay in flight as with full tiles.  The tensor core still reads 128 rows: the spare
-    // ones come from whatever lies behind (the next stage; AREA ends with room for that) and
-    // feed accumulator rows that are never stored.
-    static constexpr int AREA = BN <= 64 ? 110 * 1024 : STAGES * STAGE_BYTES;
+    static constexpr int AREA = 110 * 1024;
     static constexpr int MAX_STAGES = 12;
-    static constexpr size_t SMEM_PACKED = (size_t)AREA + 1024 /* alignment slack */ + 256 /* barriers */;
+    static constexpr size_t SMEM = (size_t)AREA + 1024 /* alignment slack */ + 256 /* barriers */;
     __host__ __device__ static constexpr int x_bytes(int tile_rows) { return (tile_rows * BK * 2 + 1023) & ~1023; }
     __host__ __device__ static constexpr int stages(int tile_rows)
     {
         const int n = (AREA - (X_BYTES - x_bytes(tile_rows))) / (x_bytes(tile_rows) + Y_BYTES);
         return n < MAX_STAGES ? n : MAX_STAGES;
     }
+};
+
+// The persistent kernel on single blocks (many tokens): 128 tokens x 256 weight rows a tile, one block an SM.
+struct WideTile {
+    static constexpr int BN = 256;
+    static constexpr int X_BYTES = BM * BK * 2;
+    static constexpr int Y_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = X_BYTES + Y_BYTES;
+    static constexpr int STAGES = (200 * 1024) / STAGE_BYTES;
+    static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
 };
 
 template <typename TC> __device__ __forceinline__ void store_elem(TC* p, float v) { *p = from_f32<TC>(v); }
@@ -113,13 +122,12 @@ constexpr int SWIGLU_STAGE_LD = 66;   // bf16 elements between the tokens of a s
 // g / inf = -0, the limit.  The 32-bit path has its own SwiGLU kernel with the accurate functions.
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
 
-// X: [x_rows, K] in the instruction's M slot; Y: [y_rows, K] in its N slot.
-// SWAP == false: out[x, y] (row stride ld);  SWAP == true: out[y, x].
-// splits > 1: out is the float scratch [splits][rows][ld] and TC is float.
+// X: the weights [x_rows, K] in the instruction's M slot; Y: the tokens [y_rows, K] in its N slot;
+// out[y, x] (row stride ld).  splits > 1: out is the float scratch [splits][rows][ld] and TC is float.
 // EPI == 1 (SwiGLU): the weight's rows alternate gate, up, gate, up, ...; the kernel stores
 // silu(gate) * up, half as many output columns (ld counts those); one pass over K only.
-template <int BN, typename TC, bool SWAP, int EPI>
-__global__ void __launch_bounds__(NUM_THREADS, BN <= 64 ? 2 : 1)
+template <int BN, typename TC, int EPI>
+__global__ void __launch_bounds__(NUM_THREADS, 2)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, TC* __restrict__ out,
                     long long ld, long long split_stride, int x_rows, int y_rows, int k_blocks, int k_blocks_per_split, int tile_rows, int launch_no,
                     int* status)
@@ -144,9 +152,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 #endif
     // tile_rows (<= BM) rows of X belong to this block: the box of map_x has that many rows, the rest of
     // the stage's 128 rows is stale and feeds accumulator rows that are never stored
-    // swapped: the token tile is the grid's fastest dimension, so that the blocks that share a weight
-    // tile (65 to 128 tokens are two tiles of 64) start together and the second finds it in L2
-    const int x0 = (SWAP ? blockIdx.y : blockIdx.x) * tile_rows, y0 = (SWAP ? blockIdx.x : blockIdx.y) * BN;
+    // the token tile is the grid's fastest dimension, so that the blocks that share a weight tile
+    // (65 to 256 tokens are two to four tiles of 64) start together and the later ones find it in L2
+    const int x0 = blockIdx.y * tile_rows, y0 = blockIdx.x * BN;
     const uint32_t stage_tx = (uint32_t)tile_rows * BK * 2 + T::Y_BYTES;
     const int x_bytes = T::x_bytes(tile_rows), stage_bytes = x_bytes + T::Y_BYTES, stages = T::stages(tile_rows);
     const int kb0 = blockIdx.z * k_blocks_per_split;
@@ -183,15 +191,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             for (int i = 0; i < pre; ++i) {
                 uint8_t* xs = tiles + (size_t)i * stage_bytes;
                 mbar_expect_tx(full_bar + i, stage_tx);
-                if constexpr (SWAP) tma_load_2d(smem_u32(xs), &map_x, (kb0 + i) * BK, x0, full_bar + i);
-                else tma_load_2d(smem_u32(xs + x_bytes), &map_y, (kb0 + i) * BK, y0, full_bar + i);
+                tma_load_2d(smem_u32(xs), &map_x, (kb0 + i) * BK, x0, full_bar + i);
             }
             pdl_wait();
             GSTAMP(2);
             for (int i = 0; i < pre; ++i) {
                 uint8_t* xs = tiles + (size_t)i * stage_bytes;
-                if constexpr (SWAP) tma_load_2d(smem_u32(xs + x_bytes), &map_y, (kb0 + i) * BK, y0, full_bar + i);
-                else tma_load_2d(smem_u32(xs), &map_x, (kb0 + i) * BK, x0, full_bar + i);
+                tma_load_2d(smem_u32(xs + x_bytes), &map_y, (kb0 + i) * BK, y0, full_bar + i);
             }
             int s = 0;
             uint32_t phase = 1;   // of the round before: the first wait on a stage is for its first release
@@ -252,32 +258,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 const int cols = BN >= 32 ? 32 : BN;
                 const int y = y0 + c;
-                if constexpr (EPI == 1 && !SWAP) {
-                    // this thread holds 16 (gate, up) pairs of row x: outputs y / 2 .. y / 2 + 15
-                    if (x < x_rows && y < y_rows) {
-                        uint32_t o[32];
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(silu_mul(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1])));
-                        TC* dst = base + (size_t)x * ld + y / 2;
-                        const int valid = min(16, (y_rows - y) / 2);
-                        if (valid >= 16 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0 && sizeof(TC) == 2) {
-#pragma unroll
-                            for (int i = 0; i < 2; ++i) {
-                                uint4 v;
-                                __nv_bfloat162 t;
-                                t = __floats2bfloat162_rn(__uint_as_float(o[8 * i]), __uint_as_float(o[8 * i + 1])); v.x = *reinterpret_cast<uint32_t*>(&t);
-                                t = __floats2bfloat162_rn(__uint_as_float(o[8 * i + 2]), __uint_as_float(o[8 * i + 3])); v.y = *reinterpret_cast<uint32_t*>(&t);
-                                t = __floats2bfloat162_rn(__uint_as_float(o[8 * i + 4]), __uint_as_float(o[8 * i + 5])); v.z = *reinterpret_cast<uint32_t*>(&t);
-                                t = __floats2bfloat162_rn(__uint_as_float(o[8 * i + 6]), __uint_as_float(o[8 * i + 7])); v.w = *reinterpret_cast<uint32_t*>(&t);
-                                reinterpret_cast<uint4*>(dst)[i] = v;
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 16; ++j)
-                                if (j < valid) store_elem(dst + j, __uint_as_float(o[j]));
-                        }
-                    }
-                } else if constexpr (EPI == 1 && SWAP) {
+                if constexpr (EPI == 1) {
                     // lanes 2i and 2i + 1 hold gate row and up row of output x / 2 for every token.  Two tokens
                     // at a time: the even lane sends the second token's gate and finishes the first token, the
                     // odd lane sends the first token's up and finishes the second, so every lane computes.
@@ -295,12 +276,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                             staged[(c + j + (odd ? 1 : 0)) * SWIGLU_STAGE_LD + ((quarter * 32 + lane) >> 1)] = __float2bfloat16_rn(v);
                         }
                     }
-                } else if constexpr (!SWAP) {
-                    if (x < x_rows && y < y_rows) {
-                        TC* dst = base + (size_t)x * ld + y;
-                        const bool aligned = (reinterpret_cast<uintptr_t>(dst) & 15) == 0;
-                        store_row32<TC>(dst, r, min(cols, y_rows - y), aligned && cols == 32);
-                    }
                 } else {
                     if (x < x_rows) {
 #pragma unroll
@@ -309,7 +284,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     }
                 }
             }
-            if constexpr (EPI == 1 && SWAP) {
+            if constexpr (EPI == 1) {
                 // rows of the staged tile to the output, 4 bytes a lane where the row allows it
                 epilogue_barrier();
                 const bf16* staged = reinterpret_cast<const bf16*>(tiles);
@@ -334,8 +309,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             for (int c = 0; c < BN; ++c) {
                 const int y = y0 + c;
                 if (x < x_rows && y < y_rows) {
-                    if constexpr (!SWAP) store_elem(base + (size_t)x * ld + y, 0.f);
-                    else store_elem(base + (size_t)y * ld + x, 0.f);
+                    store_elem(base + (size_t)y * ld + x, 0.f);
                 }
             }
         }
@@ -462,8 +436,8 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const 
                                long long ld, int x_rows, int y_rows, int k_blocks, int x_tiles, int num_tiles, int stream_tiles, int per_block,
                                float* workspace, int* status)
 {
-    constexpr int BN = 256;
-    using T = Tile<BN>;
+    using T = WideTile;
+    constexpr int BN = T::BN;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* tiles = smem;
@@ -886,22 +860,21 @@ static int make_map(CUtensorMap* map, const void* ptr, long long rows, long long
 
 int g_launch_no = 0;   // numbers the launches of the one-tile kernel for the timeline build; unused otherwise
 
-template <int BN, typename TC, bool SWAP, int EPI>
+template <int BN, typename TC, int EPI>
 static int launch(const CUtensorMap& mx, const CUtensorMap& my, void* out, long long ld, long long split_stride, int x_rows, int y_rows,
                   int k_blocks, int splits, int tile_rows, int* status, cudaStream_t stream)
 {
     using T = Tile<BN>;
-    auto kernel = gemm_tcgen05_kernel<BN, TC, SWAP, EPI>;
+    auto kernel = gemm_tcgen05_kernel<BN, TC, EPI>;
     static bool configured = false;
     if (!configured) {
-        SPY_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)T::SMEM_PACKED));
+        SPY_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)T::SMEM));
         configured = true;
     }
     const int per_split = (k_blocks + splits - 1) / splits;
-    dim3 grid((x_rows + tile_rows - 1) / tile_rows, (y_rows + BN - 1) / BN, splits);
-    if (SWAP) grid = dim3(grid.y, grid.x, grid.z);
+    dim3 grid((y_rows + BN - 1) / BN, (x_rows + tile_rows - 1) / tile_rows, splits);   // token tiles fastest
     if (grid.y > 65535 || grid.z > 65535) SPY_FAIL("gemm_tcgen05: the grid %u x %u x %u exceeds the launch limits", grid.x, grid.y, grid.z);
-    spy_launch(kernel, grid, dim3(NUM_THREADS), T::SMEM_PACKED, stream, mx, my, (TC*)out, ld, split_stride, x_rows, y_rows, k_blocks, per_split, tile_rows,
+    spy_launch(kernel, grid, dim3(NUM_THREADS), T::SMEM, stream, mx, my, (TC*)out, ld, split_stride, x_rows, y_rows, k_blocks, per_split, tile_rows,
                g_launch_no++, status);
     SPY_CHECK_LAUNCH("gemm_tcgen05");
     return 0;
@@ -1102,32 +1075,32 @@ extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, 
         }
         static bool configured = false;
         if (!configured) {
-            SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<bf16, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Tile<256>::SMEM));
-            SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<float, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Tile<256>::SMEM));
-            SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<bf16, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Tile<256>::SMEM));
+            SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<bf16, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WideTile::SMEM));
+            SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<float, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WideTile::SMEM));
+            SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<bf16, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WideTile::SMEM));
             configured = true;
         }
         if (epilogue == 1)
-            spy_launch(gemm_tcgen05_persistent_kernel<bf16, 1>, dim3(grid), dim3(NUM_THREADS), Tile<256>::SMEM, stream, mx, my, (bf16*)C, ldc, M, N,
+            spy_launch(gemm_tcgen05_persistent_kernel<bf16, 1>, dim3(grid), dim3(NUM_THREADS), WideTile::SMEM, stream, mx, my, (bf16*)C, ldc, M, N,
                        k_blocks, x_tiles, (int)num_tiles, stream_tiles, per_block, scratch, status);
         else if (c_dtype == SPY_F32)
-            spy_launch(gemm_tcgen05_persistent_kernel<float, 0>, dim3(grid), dim3(NUM_THREADS), Tile<256>::SMEM, stream, mx, my, (float*)C, ldc, M, N,
+            spy_launch(gemm_tcgen05_persistent_kernel<float, 0>, dim3(grid), dim3(NUM_THREADS), WideTile::SMEM, stream, mx, my, (float*)C, ldc, M, N,
                        k_blocks, x_tiles, (int)num_tiles, stream_tiles, per_block, scratch, status);
         else
-            spy_launch(gemm_tcgen05_persistent_kernel<bf16, 0>, dim3(grid), dim3(NUM_THREADS), Tile<256>::SMEM, stream, mx, my, (bf16*)C, ldc, M, N,
+            spy_launch(gemm_tcgen05_persistent_kernel<bf16, 0>, dim3(grid), dim3(NUM_THREADS), WideTile::SMEM, stream, mx, my, (bf16*)C, ldc, M, N,
                        k_blocks, x_tiles, (int)num_tiles, stream_tiles, per_block, scratch, status);
         SPY_CHECK_LAUNCH("gemm_tcgen05 (persistent)");
         return 0;
     }
+    if (!swap) SPY_FAIL("gemm_tcgen05: no kernel was chosen for M=%d N=%d K=%d (splits %d)", M, N, K, splits);
     int rc;
-#define SPY_LAUNCH(BN_, SWAP_)                                                                                                          \
-    rc = epilogue == 1 ? launch<BN_, bf16, SWAP_, 1>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, plan.tile_rows, status, stream)   \
-         : f32_out     ? launch<BN_, float, SWAP_, 0>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, plan.tile_rows, status, stream)  \
-                       : launch<BN_, bf16, SWAP_, 0>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, plan.tile_rows, status, stream)
-    if (!swap) SPY_LAUNCH(256, false);
-    else if (bn == 16) SPY_LAUNCH(16, true);
-    else if (bn == 32) SPY_LAUNCH(32, true);
-    else SPY_LAUNCH(64, true);
+#define SPY_LAUNCH(BN_)                                                                                                             \
+    rc = epilogue == 1 ? launch<BN_, bf16, 1>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, plan.tile_rows, status, stream)   \
+         : f32_out     ? launch<BN_, float, 0>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, plan.tile_rows, status, stream)  \
+                       : launch<BN_, bf16, 0>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, plan.tile_rows, status, stream)
+    if (bn == 16) SPY_LAUNCH(16);
+    else if (bn == 32) SPY_LAUNCH(32);
+    else SPY_LAUNCH(64);
 #undef SPY_LAUNCH
     if (rc) return rc;
     if (splits > 1 && !defer_reduce) {
