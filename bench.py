@@ -2,6 +2,7 @@
 """Benchmark of the engine's decode step and prefill on one GPU.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--shape 8b|14b|32b] [--batch B] [--context C] [--impl ours|reference]
+    python bench.py --workload mixed [--shape 14b] [--requests 64] [--budget 2048]     (a continuous batch through LLMEngine; its own line)
 
 The model has the layer sizes of Qwen3-8B (36 layers, hidden 4096, 32 query heads, 8 key/value
 heads, head size 128, intermediate 12288, vocabulary 151936, untied head) with seeded random
@@ -114,6 +115,61 @@ class ClockSampler:
                 "samples": len(self.samples)}
 
 
+def mixed_workload(args, model_config, layers, full_layers, page) -> int:
+    """A continuous batch as a user runs it: ``--requests`` requests (64) with prompt lengths uniform
+    in [64, 2048] and 128 generated tokens each are all submitted to ``LLMEngine`` at once; the
+    scheduler admits them, cuts their prompts into portions under ``--budget`` tokens a step beside
+    the decode tokens of the requests already running, and the loop calls ``step()`` until all are
+    done.  Timed on the host around the whole loop (the device is idle before and after); tokens go
+    in and come out on the host.  The first pass is a warm-up (graph captures, first launches), the
+    second is reported."""
+    import torch
+
+    from spyinfer_b200 import SamplingParams
+    from spyinfer_b200.engine import LLMEngine
+
+    n_req, new_tokens = args.requests, 128
+    g = torch.Generator().manual_seed(11)
+    lengths = torch.randint(64, 2049, (n_req,), generator=g).tolist()
+    prompts = [torch.randint(0, model_config.vocab_size, (n,), generator=g).tolist() for n in lengths]
+    num_pages = sum((n + new_tokens + page - 1) // page + 1 for n in lengths) + 8
+    engine = LLMEngine(model_config=model_config, seed=0, dtype="bfloat16", max_num_seqs=n_req, max_model_len=2048 + new_tokens + 16,
+                       kvcache_block_size=page, num_kvcache_blocks=num_pages, max_num_batched_tokens=args.budget)
+    sp = SamplingParams(max_new_tokens=new_tokens, ignore_eos=True)
+    result = None
+    for run in range(2):
+        with ClockSampler() as clocks:
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            ids = [engine.add_request(p, sp) for p in prompts]
+            steps = generated = 0
+            first_token_at = {}
+            while engine.has_unfinished_requests():
+                for rid, _tok, _fin in engine.step():
+                    generated += 1
+                    first_token_at.setdefault(rid, time.perf_counter() - t0)
+                steps += 1
+            torch.cuda.synchronize()
+            seconds = time.perf_counter() - t0
+        assert generated == n_req * new_tokens, (generated, n_req * new_tokens)
+        for rid in ids:
+            engine.remove_request(rid)
+        ttft = sorted(first_token_at.values())
+        result = {"metric": f"generated tokens/s, mixed continuous batch (Qwen3-{args.shape.upper()} shape, bf16, {n_req} requests, prompts 64..2048, "
+                            f"{new_tokens} generated each)", "value": round(generated / seconds, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps,
+                  "warmup": 1, "ms_per_step": round(seconds * 1e3 / steps, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                  "dtype": "bf16", "data": "synthetic: seeded random weights and random token ids",
+                  "config": {"model": f"Qwen3-{args.shape.upper()} shape", "num_layers": layers, "num_layers_full": full_layers,
+                             "requests": n_req, "prompt_tokens_total": sum(lengths), "generated_tokens_total": generated,
+                             "max_num_batched_tokens": args.budget, "page_size": page, "parallelism": "single GPU",
+                             "timing": "host clock around the whole loop, device idle on both sides"},
+                  "total_tokens_per_s": round((sum(lengths) + generated) / seconds, 1), "seconds": round(seconds, 3),
+                  "first_token_s": {"median": round(ttft[len(ttft) // 2], 3), "max": round(ttft[-1], 3)},
+                  "preemptions": engine.scheduler.num_preemptions, "clocks": clocks.summary()}
+    print(json.dumps(result))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -127,6 +183,11 @@ def main() -> int:
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1/64 and short-context points")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--workload", default="decode", choices=["decode", "mixed"],
+                    help="decode: the contract's line (default); mixed: a continuous batch of --requests requests with prompts of 64 to 2,048 "
+                         "tokens and 128 generated tokens each through LLMEngine, its own line")
+    ap.add_argument("--requests", type=int, default=64, help="mixed workload: number of requests")
+    ap.add_argument("--budget", type=int, default=2048, help="mixed workload: max_num_batched_tokens")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
@@ -149,6 +210,8 @@ def main() -> int:
     cfg_json["num_hidden_layers"] = layers
     model_config = config_from_json(cfg_json)
     page = 16
+    if args.workload == "mixed":
+        return mixed_workload(args, model_config, layers, full_layers, page)
     max_batch = max(args.batch, 1 if args.no_points else 64)
     ctx = args.context
     torch.cuda.set_device(0)

@@ -3,7 +3,8 @@ and of the keys its ``LLMEngine`` accepts (src/engine/llm_engine.cpp:11-16) wher
 
 Differences from the reference, which reads only some of its own fields:
 ``max_num_batched_tokens`` and ``max_num_seqs`` are honoured here (the token budget of a
-step and the number of live requests); ``num_kvcache_blocks`` may be left out, and is then
+step and the number of live requests), and ``chunk_size`` (not in the reference, which runs a prompt whole) caps
+one request's prompt portion in a step; ``num_kvcache_blocks`` may be left out, and is then
 derived from free device memory and ``gpu_memory_utilization``; ``kvcache_block_size``
 defaults to 16 tokens rather than 4.
 """
@@ -19,6 +20,7 @@ _DTYPES = {"bfloat16": "bfloat16", "bf16": "bfloat16", "float32": "float32", "fp
 class EngineConfig:
     max_num_batched_tokens: int = 16384
     max_num_seqs: int = 512
+    chunk_size: Optional[int] = None  # most prompt tokens of ONE request in a step; None: the token budget alone cuts prompts
     max_model_len: int = 4096
     gpu_memory_utilization: float = 0.9
     kvcache_block_size: int = 16
@@ -36,6 +38,8 @@ class EngineConfig:
             v = getattr(self, name)
             if not isinstance(v, int) or v <= 0:
                 raise ValueError(f"{name} must be a positive integer, found {v!r}")
+        if self.chunk_size is not None and (not isinstance(self.chunk_size, int) or self.chunk_size <= 0):
+            raise ValueError(f"chunk_size must be a positive integer or None, found {self.chunk_size!r}")
         if self.num_kvcache_blocks is not None and self.num_kvcache_blocks <= 0:
             raise ValueError(f"num_kvcache_blocks must be positive, found {self.num_kvcache_blocks!r}")
         if not 0.0 < self.gpu_memory_utilization <= 1.0:

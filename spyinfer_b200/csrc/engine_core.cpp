@@ -413,8 +413,8 @@ int spy_cache_fill_batch(void* h, int n, const int64_t* rids, const int32_t* cou
 //      holds is given back, the caller puts it at the front of the waiting queue and recomputes it
 //      from its tokens so far) until a page is free; a request is never preempted in favour of a
 //      request admitted after it;
-//   2. running requests still in their prompt get a portion of min(rest, budget left, what the free
-//      pages hold);
+//   2. running requests still in their prompt get a portion of min(rest, chunk, budget left, what the
+//      free pages hold); chunk <= 0 means no cap of its own on a portion;
 //   3. waiting requests are admitted first come first served while a slot is free, fewer than
 //      max_num_seqs requests are live, budget is left and pages for the first portion are free; the
 //      first that does not fit stops admission (as in the reference, scheduler.cpp:20-43);
@@ -425,7 +425,7 @@ int spy_cache_fill_batch(void* h, int n, const int64_t* rids, const int32_t* cou
 // requests in the order of preemption, and how many waiting requests were admitted (they are the
 // first of the queue as the caller knows it, after the preempted ones have been put at its front in
 // order, each at the very front).  Pages of the portions are reserved; admitted requests hold slots.
-int spy_sched_step(void* h, int budget, int max_num_seqs, int n_run, const int64_t* run_ids, const int32_t* run_len, const int32_t* run_done, int n_wait,
+int spy_sched_step(void* h, int budget, int chunk, int max_num_seqs, int n_run, const int64_t* run_ids, const int32_t* run_len, const int32_t* run_done, int n_wait,
                    const int64_t* wait_ids, const int32_t* wait_len, int64_t* out_ids, int32_t* out_start, int32_t* out_count, int32_t* out_samples,
                    int* n_out, int64_t* preempted, int* n_preempted, int* n_admitted)
 {
@@ -444,6 +444,7 @@ int spy_sched_step(void* h, int budget, int max_num_seqs, int n_run, const int64
     std::vector<Portion> out;
     int np = 0, admitted = 0;
     const int initial_budget = budget;
+    if (chunk <= 0) chunk = budget;   // no cap of its own on a portion
     auto preempt_last = [&]() -> int {
         Seq victim = running.back();
         running.pop_back();
@@ -478,7 +479,7 @@ int spy_sched_step(void* h, int budget, int max_num_seqs, int n_run, const int64
             Request* r = c->find(s.id);
             if (!r) return fail(UNKNOWN_REQUEST, "running request %lld holds nothing in the cache", (long long)s.id);
             const int fit = (c->pages_for(s.done) + c->min_free_pages()) * c->page_size - s.done;
-            const int n = std::min(std::min(rest, budget), fit);
+            const int n = std::min(std::min(rest, chunk), std::min(budget, fit));
             if (n <= 0) continue;
             if (int rc = c->reserve(s.id, *r, s.done + n)) return rc;
             out.push_back({s.id, s.done, n, s.done + n == s.len ? 1 : 0});
@@ -487,7 +488,7 @@ int spy_sched_step(void* h, int budget, int max_num_seqs, int n_run, const int64
         // 3. admission, first come first served
         while (!waiting.empty() && budget > 0 && (int)running.size() < max_num_seqs && !c->free_slots.empty()) {
             Seq s = waiting.front();
-            int n = std::min(s.len - s.done, budget);
+            int n = std::min(std::min(s.len - s.done, chunk), budget);
             if (c->pages_for(n) > c->min_free_pages()) {
                 const int fit = c->min_free_pages() * c->page_size;
                 if (!running.empty() || fit <= 0) break;   // wait for running requests to finish and free pages

@@ -5,6 +5,10 @@
 //     argmax_i (logits[i] / temperature - log(-log(u_i))), u_i uniform in (0, 1) from a
 //     counter-based generator keyed by (seed, draw, i).  A row's token depends only on its
 //     logits, seed and draw number, never on the rest of the batch.
+//   top_k > 0 (with a temperature): the draw is among the row's k largest logits only.  A
+//     kernel ahead finds the row's k-th largest value by a radix select on the floats' bit
+//     patterns (four passes of eight bits); logits below it take no part.  Logits equal to the
+//     k-th value all stay, so a tie at the edge keeps more than k.
 // Two stages so that a row of a large vocabulary is read by many blocks: every block finds
 // the best of its slice of the row, then one block per row picks among the slices' bests.
 #include "common.cuh"
@@ -50,18 +54,76 @@ __device__ __forceinline__ void block_best(float& bv, int& bi)
     }
 }
 
+// Bit pattern of a float as an unsigned integer whose order is the floats' order.
+__device__ __forceinline__ uint32_t ordered_bits(float v)
+{
+    const uint32_t b = __float_as_uint(v);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float from_ordered_bits(uint32_t k)
+{
+    return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+
+// One block per row: floor[r] = the row's top_k[r]-th largest logit (-inf where top_k[r] <= 0
+// or top_k[r] >= vocab: every logit takes part).
+__global__ void topk_floor_kernel(const float* __restrict__ logits, long long row_stride, int vocab, const int* __restrict__ top_k,
+                                  float* __restrict__ floor_out)
+{
+    pdl_enter();
+    __shared__ unsigned int hist[256];
+    __shared__ uint32_t s_prefix;
+    __shared__ int s_want;
+    const int r = blockIdx.x;
+    const int k = top_k[r];
+    if (k <= 0 || k >= vocab) {
+        if (threadIdx.x == 0) floor_out[r] = -INFINITY;
+        return;
+    }
+    const float* row = logits + (size_t)r * row_stride;
+    uint32_t prefix = 0;   // the bits of the k-th largest key found so far (from the top)
+    int want = k;          // its rank among the keys that share the prefix
+    for (int pass = 0; pass < 4; ++pass) {
+        const int shift = 24 - 8 * pass;
+        const uint32_t mask = pass == 0 ? 0u : 0xffffffffu << (shift + 8);
+        for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
+        __syncthreads();
+        for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+            const uint32_t key = ordered_bits(row[i]);
+            if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int left = want, d = 255;
+            for (; d > 0; --d) {
+                if ((int)hist[d] >= left) break;
+                left -= (int)hist[d];
+            }
+            s_prefix = prefix | ((uint32_t)d << shift);
+            s_want = left;
+        }
+        __syncthreads();
+        prefix = s_prefix;
+        want = s_want;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) floor_out[r] = from_ordered_bits(prefix);
+}
+
 __global__ void sample_slices_kernel(const float* __restrict__ logits, long long row_stride, int vocab, int slice, const float* __restrict__ temperature,
-                                     const long long* __restrict__ seed, const long long* __restrict__ draw, float* __restrict__ slice_v,
-                                     int* __restrict__ slice_i)
+                                     const long long* __restrict__ seed, const long long* __restrict__ draw, const float* __restrict__ floor_in,
+                                     float* __restrict__ slice_v, int* __restrict__ slice_i)
 {
     pdl_enter();
     const int r = blockIdx.y, lo = blockIdx.x * slice, hi = min(vocab, lo + slice);
     const float* row = logits + (size_t)r * row_stride;
     const float temp = temperature ? temperature[r] : 0.f;
+    const float floor_v = (floor_in && temp > 0.f) ? floor_in[r] : -INFINITY;
     const uint64_t key = mix64((seed ? (uint64_t)seed[r] : 0) ^ mix64(draw ? (uint64_t)draw[r] : 0));
     float bv = -INFINITY;
     int bi = NONE;
     auto take = [&](float v, int i) {
+        if (v < floor_v) return;   // outside the row's top k
         if (temp > 0.f) v = v / temp - logf(-logf(uniform_open(key, (uint32_t)i)));
         if (bi == NONE || v > bv) { bv = v; bi = i; }   // ascending i: the lowest index is kept on ties
     };
@@ -101,10 +163,12 @@ __global__ void sample_pick_kernel(const float* __restrict__ slice_v, const int*
 extern "C" int spy_sample_slices(int vocab) { return vocab <= 4096 ? 1 : (vocab + 4095) / 4096; }
 
 // logits: [rows, vocab] floats, rows row_stride apart.  temperature/seed/draw: per row, or
-// null for greedy.  tokens: [rows] int32 out.  slice_v / slice_i: rows * spy_sample_slices(vocab)
-// floats / ints of scratch.
+// null for greedy.  top_k: per row (0 or less: the whole row), or null; floor_v: [rows] floats of
+// scratch when top_k is given.  tokens: [rows] int32 out.  slice_v / slice_i:
+// rows * spy_sample_slices(vocab) floats / ints of scratch.
 extern "C" int spy_sample(const float* logits, long long row_stride, int rows, int vocab, const float* temperature, const long long* seed,
-                          const long long* draw, int* tokens, float* slice_v, int* slice_i, cudaStream_t stream)
+                          const long long* draw, const int* top_k, float* floor_v, int* tokens, float* slice_v, int* slice_i,
+                          cudaStream_t stream)
 {
     if (rows <= 0) return 0;
     if (vocab <= 0 || row_stride < vocab) SPY_FAIL("sample: vocab %d must be positive and fit the row stride %lld", vocab, row_stride);
@@ -112,7 +176,15 @@ extern "C" int spy_sample(const float* logits, long long row_stride, int rows, i
     const int slices = spy_sample_slices(vocab);
     const int slice = ((vocab + slices - 1) / slices + 3) / 4 * 4;   // a multiple of 4: slices start on 16-byte boundaries
     dim3 grid(slices, rows);
-    spy_launch(sample_slices_kernel, grid, dim3(256), 0, stream, logits, row_stride, vocab, slice, temperature, seed, draw, slice_v, slice_i);
+    const float* floor_in = nullptr;
+    if (top_k && temperature) {
+        if (!floor_v) SPY_FAIL("sample: top_k needs its scratch of %d floats", rows);
+        spy_launch(topk_floor_kernel, dim3(rows), dim3(1024), 0, stream, logits, row_stride, vocab, top_k, floor_v);
+        SPY_CHECK_LAUNCH("sample (top-k floor)");
+        floor_in = floor_v;
+    }
+    spy_launch(sample_slices_kernel, grid, dim3(256), 0, stream, logits, row_stride, vocab, slice, temperature, seed, draw, floor_in, slice_v,
+               slice_i);
     SPY_CHECK_LAUNCH("sample (slices)");
     spy_launch(sample_pick_kernel, dim3(rows), dim3(64), 0, stream, slice_v, slice_i, slices, tokens);
     SPY_CHECK_LAUNCH("sample (pick)");

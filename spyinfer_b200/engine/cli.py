@@ -7,7 +7,7 @@ ids, streamed as they are generated.  Lines of one conversation are appended to 
 ``/new`` starts a fresh one.
 
     spyinfer -m /path/to/model [-b cuda] [--dtype bfloat16|float32] [--max-new-tokens N]
-             [--temperature X] [--seed N] [--prompt-tokens 1,2,3] [--stats]
+             [--temperature X] [--top-k K] [--seed N] [--prompt-tokens 1,2,3] [--stats]
     spyinfer --random CONFIG.json --seed 7 ...        (random weights instead of a checkpoint)
 """
 from __future__ import annotations
@@ -33,9 +33,11 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--prompt-tokens", help="run this one prompt (comma-separated ids) and exit")
     ap.add_argument("--max-new-tokens", type=int, default=64)
     ap.add_argument("--temperature", type=float, default=0.0)
+    ap.add_argument("--top-k", type=int, default=0, help="with a temperature: draw among the k most likely tokens only (0: all)")
     ap.add_argument("--ignore-eos", action="store_true")
     ap.add_argument("--max-num-batched-tokens", type=int, default=None)
     ap.add_argument("--max-num-seqs", type=int, default=None)
+    ap.add_argument("--chunk-size", type=int, default=None, help="most prompt tokens of one request in a step")
     ap.add_argument("--max-model-len", type=int, default=None)
     ap.add_argument("--kvcache-block-size", type=int, default=None)
     ap.add_argument("--num-kvcache-blocks", type=int, default=None)
@@ -60,7 +62,7 @@ def main(argv=None) -> int:
     from .llm_engine import LLMEngine
 
     params = {"dtype": args.dtype}
-    for key in ("max_num_batched_tokens", "max_num_seqs", "max_model_len", "kvcache_block_size", "num_kvcache_blocks"):
+    for key in ("max_num_batched_tokens", "max_num_seqs", "chunk_size", "max_model_len", "kvcache_block_size", "num_kvcache_blocks"):
         if getattr(args, key) is not None:
             params[key] = getattr(args, key)
     print("Using CUDA backend", flush=True)
@@ -69,7 +71,7 @@ def main(argv=None) -> int:
     else:
         with open(args.random) as f:
             engine = LLMEngine(model_config=config_from_json(json.load(f)), seed=args.seed, backend_type=args.backend, **params)
-    sampling = SamplingParams(temperature=args.temperature, seed=args.seed, max_new_tokens=args.max_new_tokens, ignore_eos=args.ignore_eos)
+    sampling = SamplingParams(temperature=args.temperature, seed=args.seed, top_k=args.top_k, max_new_tokens=args.max_new_tokens, ignore_eos=args.ignore_eos)
 
     def run(tokens):
         rid = engine.add_request(tokens, sampling)

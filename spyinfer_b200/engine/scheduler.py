@@ -8,7 +8,8 @@ Every step:
    admitted last is preempted (its pages and slot are given back, it returns to the front
    of the waiting queue and is recomputed from its tokens so far) until a page is free; a
    request is never preempted in favour of a request admitted after it;
-2. running requests still in their prompt get a portion of ``min(rest, budget left)`` tokens;
+2. running requests still in their prompt get a portion of ``min(rest, chunk_size, budget left)``
+   tokens (``chunk_size`` is optional: without it the budget alone cuts);
 3. waiting requests are admitted first-come-first-served while a slot is free, the number of
    live requests is below ``max_num_seqs``, token budget is left and pages for the first
    portion are free; the first that does not fit stops admission (as in the reference).
@@ -96,7 +97,7 @@ class Scheduler:
         out_ids, preempted = np.empty(cap, dtype=np.int64), np.empty(cap, dtype=np.int64)
         out_start, out_count, out_samples = (np.empty(cap, dtype=np.int32) for _ in range(3))
         n_out, n_pre, n_adm = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
-        core.check(lib.spy_sched_step(cache._h, int(self.config.max_num_batched_tokens), int(self.config.max_num_seqs), n_run, core.i64(run_ids),
+        core.check(lib.spy_sched_step(cache._h, int(self.config.max_num_batched_tokens), int(self.config.chunk_size or 0), int(self.config.max_num_seqs), n_run, core.i64(run_ids),
                                       core.i32(run_len), core.i32(run_done), n_wait, core.i64(wait_ids), core.i32(wait_len), core.i64(out_ids),
                                       core.i32(out_start), core.i32(out_count), core.i32(out_samples), ctypes.byref(n_out), core.i64(preempted),
                                       ctypes.byref(n_pre), ctypes.byref(n_adm)))

@@ -391,10 +391,11 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
 
 
 def sample(logits: torch.Tensor, tokens: torch.Tensor, temperature: Optional[torch.Tensor] = None, seed: Optional[torch.Tensor] = None,
-           draw: Optional[torch.Tensor] = None) -> torch.Tensor:
+           draw: Optional[torch.Tensor] = None, top_k: Optional[torch.Tensor] = None) -> torch.Tensor:
     """One token per row of ``logits [R, V]`` float32 into ``tokens [R]`` int32: argmax where the
     row's temperature is 0 (or no temperatures are given), else a seeded draw from
-    ``softmax(logits / temperature)``."""
+    ``softmax(logits / temperature)``, among the row's ``top_k[r]`` largest logits only where
+    that is positive (logits equal to the k-th largest all stay)."""
     _check(logits, "logits", torch.float32, 2)
     _check(tokens, "sampled tokens", torch.int32, 1)
     R, V = logits.shape
@@ -406,12 +407,20 @@ def sample(logits: torch.Tensor, tokens: torch.Tensor, temperature: Optional[tor
         _check(draw, "draw counters", torch.int64, 1)
         if not (temperature.shape[0] == seed.shape[0] == draw.shape[0] == R):
             raise KernelError("sample: temperature, seed and draw need one entry per row")
+    floor_v = None
+    if top_k is not None:
+        if temperature is None:
+            raise KernelError("sample: top_k is for rows with a temperature; give the temperatures too")
+        _check(top_k, "top_k", torch.int32, 1)
+        if top_k.shape[0] != R:
+            raise KernelError("sample: top_k needs one entry per row")
+        floor_v = torch.empty(R, dtype=torch.float32, device=logits.device)
     lib = build.load("sampling")
     slices = lib.spy_sample_slices(V)
     slice_v = torch.empty(R * slices, dtype=torch.float32, device=logits.device)
     slice_i = torch.empty(R * slices, dtype=torch.int32, device=logits.device)
-    _call("sampling", "spy_sample", _ptr(logits), ctypes.c_longlong(V), R, V, _ptr(temperature), _ptr(seed), _ptr(draw), _ptr(tokens),
-          _ptr(slice_v), _ptr(slice_i), _stream())
+    _call("sampling", "spy_sample", _ptr(logits), ctypes.c_longlong(V), R, V, _ptr(temperature), _ptr(seed), _ptr(draw), _ptr(top_k),
+          _ptr(floor_v), _ptr(tokens), _ptr(slice_v), _ptr(slice_i), _stream())
     return tokens
 
 

@@ -28,4 +28,7 @@ class Sampler:
         t = torch.tensor([p.temperature for p in params], dtype=torch.float32).to(logits.device, non_blocking=True)
         s = torch.tensor([p.seed for p in params], dtype=torch.int64).to(logits.device, non_blocking=True)
         d = torch.tensor(list(draws), dtype=torch.int64).to(logits.device, non_blocking=True)
-        return kernels.sample(logits, tokens, t, s, d)
+        k = None
+        if any(p.top_k > 0 and p.temperature > 0.0 for p in params):
+            k = torch.tensor([p.top_k for p in params], dtype=torch.int32).to(logits.device, non_blocking=True)
+        return kernels.sample(logits, tokens, t, s, d, k)

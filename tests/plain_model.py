@@ -213,6 +213,16 @@ def softmax_probabilities(logits: torch.Tensor, temperature: float) -> torch.Ten
     return p / p.sum(dim=-1, keepdim=True)
 
 
+def top_k_probabilities(logits: torch.Tensor, temperature: float, top_k: int) -> torch.Tensor:
+    """``softmax(logits / temperature)`` over the ``top_k`` largest logits (those equal to the
+    k-th largest all stay), zero elsewhere.  The reference has no such sampler; this is the
+    usual definition, written out for the engine's own option."""
+    z = logits.to(torch.float64)
+    kth = torch.sort(z, descending=True).values[..., top_k - 1]
+    z = torch.where(z >= kth.unsqueeze(-1), z, torch.full_like(z, float("-inf")))
+    return softmax_probabilities(z, temperature)
+
+
 def random_weights(cfg, seed: int, std: float = 0.02, norm_std: float = 0.05):
     """Seeded bf16 weights with the checkpoint's tensor names: linears and embeddings
     ``N(0, std)``, norm weights ``1 + N(0, norm_std)``.  Independent of the package's own

@@ -263,6 +263,43 @@ def test_sampling_greedy_and_distribution():
     assert (again == int(row.argmax())).all()
 
 
+def test_sampling_top_k_draws_only_among_the_largest():
+    """Top-k at a vocabulary that is no power of two and larger than one slice: frequencies follow
+    the softmax over the k largest logits, nothing else is ever drawn; k = 1 is the argmax; ties at
+    the k-th value stay; a row without top_k beside rows with it draws from the whole row; negative
+    logits and equal bit patterns across the radix passes (values that share their top bytes)."""
+    from spyinfer_b200 import kernels
+    import plain_model
+    torch.manual_seed(5)
+    V, n, temp = 5003, 20000, 1.3
+    row = torch.randn(V, device=DEV) * 0.01 - 3.0       # close values: they share the top bytes of their bit patterns
+    top = torch.randperm(V, device=DEV)[:9]
+    row[top] = torch.tensor([2.0, 1.5, 1.5, 1.0, 0.5, 0.0, -0.5, -1.0, -1.0], device=DEV)
+    lg = row.expand(n, V).contiguous()
+    t = torch.full((n,), temp, device=DEV)
+    seed = torch.full((n,), 7, dtype=torch.int64, device=DEV)
+    draw = torch.arange(n, dtype=torch.int64, device=DEV)
+    for k in (1, 3, 5, 8, 40):
+        out = torch.empty(n, dtype=torch.int32, device=DEV)
+        kernels.sample(lg, out, t, seed, draw, torch.full((n,), k, dtype=torch.int32, device=DEV))
+        freq = torch.bincount(out.long(), minlength=V).double() / n
+        p = plain_model.top_k_probabilities(row.cpu(), temp, k).to(DEV)
+        assert (freq[p == 0] == 0).all(), k
+        assert (freq - p).abs().max() < 4 * math.sqrt(0.25 / n) + 1e-3, k
+    # k = 8 cuts between the two equal values -1.0: both stay
+    assert int((plain_model.top_k_probabilities(row.cpu(), temp, 8) > 0).sum()) == 9
+    # rows with and without top_k in one call; k beyond the vocabulary means all
+    ks = torch.tensor([2, 0, V + 5, 1], dtype=torch.int32, device=DEV).repeat(n // 4)
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    kernels.sample(lg, out, t, seed, draw, ks)
+    whole = torch.empty(n, dtype=torch.int32, device=DEV)
+    kernels.sample(lg, whole, t, seed, draw)
+    assert torch.equal(out[1::4], whole[1::4]) and torch.equal(out[2::4], whole[2::4])
+    assert (out[3::4] == int(row.argmax())).all()
+    two = set(top[:3].tolist())                          # 2.0 and the two 1.5: k = 2 keeps the tie
+    assert set(out[0::4].tolist()) <= two
+
+
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("M,N,K", [(1, 128, 64), (5, 200, 96), (16, 4096, 4096), (17, 1000, 520), (33, 136, 72), (64, 6144, 512),
                                    (65, 300, 136), (128, 256, 64), (100, 4096, 4096), (128, 6144, 4096), (90, 1187, 1032), (129, 1187, 1032), (300, 512, 4096), (1000, 24, 200), (2048, 1024, 12288),

@@ -12,8 +12,8 @@ from spyinfer_b200.engine.sequence import Sequence, SequenceStatus
 from spyinfer_b200.sampling import SamplingParams
 
 
-def make(num_pages=16, page_size=4, budget=32, max_num_seqs=4, max_model_len=64):
-    cfg = EngineConfig(max_num_batched_tokens=budget, max_num_seqs=max_num_seqs, max_model_len=max_model_len,
+def make(num_pages=16, page_size=4, budget=32, max_num_seqs=4, max_model_len=64, chunk_size=None):
+    cfg = EngineConfig(max_num_batched_tokens=budget, max_num_seqs=max_num_seqs, max_model_len=max_model_len, chunk_size=chunk_size,
                        kvcache_block_size=page_size, num_kvcache_blocks=num_pages)
     cache = CacheManager([PagedCacheNeed(1, 16, None)], page_size, num_pages, max_num_seqs, max_model_len, device=None)
     return Scheduler(cfg, cache), cache
@@ -66,6 +66,25 @@ def test_prompt_is_cut_into_portions_by_the_budget():
     assert sizes == [[(0, 5)], [(5, 5)], [(10, 5)], [(15, 2)], [(17, 1)]]
     assert a.status == SequenceStatus.FINISHED and a.finish_reason == "max_new_tokens"
     assert cache.num_free_pages() == 32 and cache.num_free_slots() == 4
+
+
+def test_chunk_size_caps_each_requests_portion_beside_the_budget():
+    """Two prompts under a budget of 16 and a chunk size of 6: each gets at most 6 tokens a step, both
+    run in the same step, and a decoding request still gets its one token first."""
+    sched, cache = make(num_pages=32, budget=16, max_model_len=128, chunk_size=6)
+    a, b = seq(0, 14, max_new=3), seq(1, 9, max_new=2)
+    sched.add_sequence(a)
+    sched.add_sequence(b)
+    seen = []
+    while sched.has_unfinished():
+        p = sched.schedule()
+        seen.append([(x.seq.id, x.start, x.num_tokens) for x in p])
+        run_step(sched, cache, p)
+    assert seen[:3] == [[(0, 0, 6), (1, 0, 6)], [(0, 6, 6), (1, 6, 3)], [(1, 9, 1), (0, 12, 2)]]
+    assert all(n <= 6 for step in seen for _, _, n in step)
+    assert cache.num_free_pages() == 32
+    with pytest.raises(ValueError):
+        make(chunk_size=0)
 
 
 def test_max_num_seqs_limits_live_requests():
