@@ -1,10 +1,13 @@
 """Typed configuration of the Qwen3 dense decoder (``Qwen3ForCausalLM``).
 
 Keys, defaults and meanings follow spymaster2h/spyinfer src/models/model_config.hpp:27-47:
-``model_type`` and ``hidden_act`` are required, ``head_dim`` defaults to
-``hidden_size / num_attention_heads``, ``rope_theta`` to 1e6, ``rms_norm_eps`` to 1e-6,
-``max_position_embeddings`` to 16384, ``tie_word_embeddings`` to false.  Unlike the
-reference, which lets -1 defaults flow through, every size is required and checked.
+``head_dim`` defaults to ``hidden_size / num_attention_heads``, ``rope_theta`` to 1e6,
+``rms_norm_eps`` to 1e-6, ``max_position_embeddings`` to 16384, ``tie_word_embeddings`` to
+false.  Unlike the reference, which lets -1 defaults flow through, every size is required and
+checked.  ``model_type`` and ``hidden_act``, which the reference demands and then never uses
+(:32-33; its activation is SiLU in code), default to ``"qwen3"`` and ``"silu"`` here; another
+activation is refused.  ``rope_theta`` may also stand inside ``rope_parameters`` (newer
+checkpoints write it there), and ``eos_token_id`` may be a list, whose first entry counts.
 
 Read beyond the reference's keys: ``use_sliding_window``, ``sliding_window`` and
 ``layer_types`` (a layer of type ``"sliding_attention"`` sees the last ``sliding_window``
@@ -27,7 +30,7 @@ _REQUIRED_INTS = ("hidden_size", "intermediate_size", "num_hidden_layers", "num_
                   "num_key_value_heads", "vocab_size")
 
 
-@register_architecture("Qwen3ForCausalLM")
+@register_architecture("Qwen3ForCausalLM", model_type="qwen3")
 @dataclass
 class Qwen3Config(ArchitectureConfig):
     hidden_size: int
@@ -53,9 +56,12 @@ class Qwen3Config(ArchitectureConfig):
     @classmethod
     def from_json(cls, data: Dict[str, Any]) -> "Qwen3Config":
         problems = []
+        data = dict(data)
+        data.setdefault("model_type", "qwen3")
+        data.setdefault("hidden_act", "silu")
         for key in ("model_type", "hidden_act"):
-            if key not in data:
-                problems.append(f"missing key {key!r}")
+            if not isinstance(data[key], str):
+                problems.append(f"{key!r} must be a string, found {data[key]!r}")
         for key in _REQUIRED_INTS:
             v = data.get(key)
             if not isinstance(v, int) or isinstance(v, bool) or v <= 0:
@@ -64,8 +70,20 @@ class Qwen3Config(ArchitectureConfig):
             raise ConfigError("Qwen3 config.json: " + "; ".join(problems))
         if data["hidden_act"] != "silu":
             raise ConfigError(f"Qwen3 config.json: hidden_act {data['hidden_act']!r} is not implemented (only \"silu\")")
-        if data.get("rope_scaling") not in (None, {}):
-            raise ConfigError("Qwen3 config.json: rope_scaling is not implemented; remove it or set it to null")
+        rope_parameters = data.get("rope_parameters") if isinstance(data.get("rope_parameters"), dict) else {}
+        for key in ("rope_scaling", "rope_parameters"):
+            scaling = data.get(key)
+            if scaling in (None, {}):
+                continue
+            kind = scaling.get("rope_type", scaling.get("type", "default")) if isinstance(scaling, dict) else scaling
+            if kind != "default":
+                raise ConfigError(f"Qwen3 config.json: {key} of type {kind!r} is not implemented (only plain rotary positions); "
+                                  "remove it or set it to null")
+        if "rope_theta" not in data and "rope_theta" in rope_parameters:
+            data["rope_theta"] = rope_parameters["rope_theta"]
+        for key in ("bos_token_id", "eos_token_id"):
+            if isinstance(data.get(key), list):
+                data[key] = data[key][0] if data[key] else None
         if data.get("attention_bias", False):
             raise ConfigError("Qwen3 config.json: attention_bias=true is not implemented")
         nh, nkv = data["num_attention_heads"], data["num_key_value_heads"]
@@ -94,7 +112,7 @@ class Qwen3Config(ArchitectureConfig):
                 bad = sorted(set(layer_types) - {"full_attention", "sliding_attention"})
                 if bad:
                     raise ConfigError(f"Qwen3 config.json: unknown layer_types {bad}")
-        known = {f for f in cls.__dataclass_fields__ if f != "extra"} | {"architectures"}
+        known = {f for f in cls.__dataclass_fields__ if f != "extra"} | {"architectures", "rope_parameters"}
         return cls(
             hidden_size=data["hidden_size"], intermediate_size=data["intermediate_size"],
             num_hidden_layers=data["num_hidden_layers"], num_attention_heads=nh, num_key_value_heads=nkv,

@@ -21,8 +21,27 @@ def test_unknown_architecture_lists_known_ones():
     with pytest.raises(ConfigError) as e:
         config_from_json(data)
     assert "LlamaForCausalLM" in str(e.value) and "Qwen3ForCausalLM" in str(e.value)
+    # without an architectures list the model_type names the model; an unknown one is an error that lists both
+    by_type = config_from_json({k: v for k, v in TINY["a"]["config"].items() if k != "architectures"})
+    assert by_type.architecture == "Qwen3ForCausalLM"
+    with pytest.raises(ConfigError) as e:
+        config_from_json({k: v for k, v in dict(data, model_type="llama").items() if k != "architectures"})
+    assert "llama" in str(e.value) and "qwen3" in str(e.value)
+
+
+def test_keys_as_newer_checkpoints_write_them():
+    """``rope_theta`` inside ``rope_parameters``, a default-typed ``rope_scaling``, ``eos_token_id`` as a
+    list, no ``model_type``/``hidden_act`` (the reference demands both and uses neither), and keys
+    that change nothing (``torch_dtype``, ``use_cache``, ``attention_dropout``) are accepted."""
+    data = {k: v for k, v in TINY["b"]["config"].items() if k not in ("rope_theta", "model_type", "hidden_act")}
+    data.update(rope_parameters={"rope_theta": 12345.0, "rope_type": "default"}, rope_scaling={"rope_type": "default"},
+                eos_token_id=[7, 9], torch_dtype="bfloat16", use_cache=True, attention_dropout=0.0, attention_bias=False,
+                sliding_window=None, max_window_layers=28)
+    cfg = config_from_json(data)
+    assert cfg.rope_theta == 12345.0 and cfg.eos_token_id == 7 and cfg.hidden_act == "silu" and cfg.model_type == "qwen3"
+    assert config_from_json(cfg.to_json()).to_spec().layers[0].mixer.params["position"].params["theta"] == 12345.0
     with pytest.raises(ConfigError):
-        config_from_json({k: v for k, v in data.items() if k != "architectures"})
+        config_from_json(dict(data, rope_parameters={"rope_theta": 1e6, "rope_type": "yarn", "factor": 4.0}))
 
 
 def test_defaults_follow_the_reference():
@@ -33,7 +52,7 @@ def test_defaults_follow_the_reference():
     assert cfg.tie_word_embeddings is False and cfg.max_position_embeddings == 16384
 
 
-@pytest.mark.parametrize("key", ["model_type", "hidden_act", "hidden_size", "intermediate_size", "num_hidden_layers",
+@pytest.mark.parametrize("key", ["hidden_size", "intermediate_size", "num_hidden_layers",
                                  "num_attention_heads", "num_key_value_heads", "vocab_size"])
 def test_missing_keys_are_named(key):
     data = {k: v for k, v in TINY["a"]["config"].items() if k != key}
