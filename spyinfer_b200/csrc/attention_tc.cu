@@ -72,8 +72,20 @@ struct Params {
 #ifdef SPY_TIMELINE
 __device__ unsigned long long g_timeline[1024][16];
 #define STAMP(t, i) do { if ((t) == 10) g_timeline[(blockIdx.x + gridDim.x * blockIdx.y) & 1023][i] = global_timer(); } while (0)
+// ... and at points of the block's life (thread 0): spy_attention_tc_block_life copies these out
+__device__ __forceinline__ unsigned smid()
+{
+    unsigned v;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(v));
+    return v;
+}
+__device__ unsigned long long g_block_life[1024][8];
+#define LIFE(i) do { if (threadIdx.x == 0) g_block_life[(blockIdx.x + gridDim.x * blockIdx.y) & 1023][i] = global_timer(); } while (0)
+#define LIFE_VALUE(i, v) do { if (threadIdx.x == 0) g_block_life[(blockIdx.x + gridDim.x * blockIdx.y) & 1023][i] = (unsigned long long)(v); } while (0)
 #else
 #define STAMP(t, i) ((void)0)
+#define LIFE(i) ((void)0)
+#define LIFE_VALUE(i, v) ((void)0)
 #endif
 
 // Byte offset of 16-byte chunk `chunk` (0 .. HD / 8 - 1, or 0 .. 15 for the 128-key P tile) of
@@ -123,6 +135,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
     int* s_info = reinterpret_cast<int*>(tmem_slot + 2);                // seq, first token of the block
 
     pdl_launch_dependents();
+    LIFE(0);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
     const int tokens_per_block = ROWS / p.Gp;
     if (tid == 0) {
@@ -163,6 +176,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
     fence_before_sync();
     __syncthreads();
     fence_after_sync();
+    LIFE(1);
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_o = tmem_base + 2 * TILE;
     const int seq = s_info[0], tok0 = s_info[1];
@@ -202,6 +216,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
         asm volatile("cp.async.wait_all;" ::: "memory");
         fence_async_proxy();   // the MMA reads shared memory through the async proxy
         mbar_arrive(bar_q);
+        LIFE(2);
+        LIFE_VALUE(7, (unsigned)n_tiles | (smid() << 16));
 
         float m_used = -INFINITY, l = 0.f;   // the maximum the probabilities are taken against (equal in both threads of a row); this thread's share of their sum
         const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
@@ -213,6 +229,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
             const uint32_t ph = (uint32_t)(t >> 1) & 1;
             alive = mbar_wait(bar_s + st, ph, abort_flag);          // S_t is complete
             if (!alive) break;
+            if (t == 0) LIFE(3);
             if (tid == 0) { STAMP(t, 0); STAMP(t - 1, 5); }
             fence_after_sync();
             const int key0 = (tile_first + t) * TILE + half * COLS;
@@ -302,7 +319,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
             if (tid == 0) STAMP(t, 4);
         }
         // ---- epilogue: O / l
+        LIFE(4);
         if (alive) alive = mbar_wait(bar_o + ((n_tiles - 1) & 1), (uint32_t)((n_tiles - 1) >> 1) & 1, abort_flag);
+        LIFE(5);
         if (alive) {
             fence_after_sync();
             xsum[half * ROWS + row] = l;   // every thread has read the maxima of the last tile: it wrote P after that, and P.V is complete
@@ -330,6 +349,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
                 }
             }
         }
+        LIFE(6);
     } else if (warp == 8 && seq >= 0 && n_tiles > 0) {
         // ---------------------------------------------------------------- MMA issue
         if (lane == 0) {
@@ -444,6 +464,12 @@ extern "C" int spy_attention_tc_timeline(unsigned long long* host)
 {
     SPY_CUDA(cudaDeviceSynchronize());
     SPY_CUDA(cudaMemcpyFromSymbol(host, g_timeline, sizeof(g_timeline)));
+    return 0;
+}
+extern "C" int spy_attention_tc_block_life(unsigned long long* host)
+{
+    SPY_CUDA(cudaDeviceSynchronize());
+    SPY_CUDA(cudaMemcpyFromSymbol(host, g_block_life, sizeof(g_block_life)));
     return 0;
 }
 #endif

@@ -114,6 +114,7 @@ __device__ __forceinline__ void store_row32(TC* dst, const uint32_t (&r)[32], in
 }
 
 __device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }   // the four epilogue warps
+constexpr int PLAIN_STAGE_LD = 132;   // floats between the tokens of a staged plain tile (128 weight rows and a pad, rows 16 bytes aligned)
 constexpr int SWIGLU_STAGE_LD = 66;   // bf16 elements between the tokens of a staged SwiGLU tile (64 outputs and a pad)
 
 // silu(g) * u for a bfloat16 result: the fast exponential and division (2 ulp of float each) are far
@@ -276,11 +277,46 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                             staged[(c + j + (odd ? 1 : 0)) * SWIGLU_STAGE_LD + ((quarter * 32 + lane) >> 1)] = __float2bfloat16_rn(v);
                         }
                     }
+                } else if constexpr (BN >= 32) {
+                    // 32 tokens and more: through shared memory as well, so that the output leaves in rows of
+                    // 16 bytes a lane (a quarter of the store requests of 4 bytes a lane and token)
+                    float* staged = reinterpret_cast<float*>(tiles);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) staged[(c + j) * PLAIN_STAGE_LD + quarter * 32 + lane] = __uint_as_float(r[j]);
                 } else {
                     if (x < x_rows) {
 #pragma unroll
                         for (int j = 0; j < 32; ++j)
                             if (j < cols && y + j < y_rows) store_elem(base + (size_t)(y + j) * ld + x, __uint_as_float(r[j]));
+                    }
+                }
+            }
+            if constexpr (EPI == 0 && BN >= 32) {
+                epilogue_barrier();
+                const float* staged = reinterpret_cast<const float*>(tiles);
+                const int e = quarter * 32 + lane;
+                const int outs = min(tile_rows, x_rows - x0), rows = min(BN, y_rows - y0);
+                TC* gout = base + (size_t)y0 * ld + x0;
+                if ((outs & 3) == 0 && (ld & 3) == 0 && (reinterpret_cast<uintptr_t>(gout) & 15) == 0) {
+                    const int quads = outs >> 2;
+                    for (int i = e; i < rows * quads; i += 128) {
+                        const int t = i / quads, q = i - t * quads;
+                        const float4 v = *reinterpret_cast<const float4*>(staged + t * PLAIN_STAGE_LD + 4 * q);
+                        TC* dst = gout + (size_t)t * ld + 4 * q;
+                        if constexpr (sizeof(TC) == 4) {
+                            *reinterpret_cast<float4*>(dst) = v;
+                        } else {
+                            __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+                            uint2 w;
+                            w.x = *reinterpret_cast<uint32_t*>(&lo);
+                            w.y = *reinterpret_cast<uint32_t*>(&hi);
+                            *reinterpret_cast<uint2*>(dst) = w;
+                        }
+                    }
+                } else {
+                    for (int i = e; i < rows * outs; i += 128) {
+                        const int t = i / outs, q = i - t * outs;
+                        store_elem(gout + (size_t)t * ld + q, staged[t * PLAIN_STAGE_LD + q]);
                     }
                 }
             }

@@ -2,6 +2,7 @@
 
     SPYINFER_NVCC_FLAGS=-DSPY_TIMELINE python -m spyinfer_b200.timeline decode [--layers 6] [--batch 8] [--context 8192]
     SPYINFER_NVCC_FLAGS=-DSPY_TIMELINE python -m spyinfer_b200.timeline prompt [--tokens 8192]
+    SPYINFER_NVCC_FLAGS=-DSPY_TIMELINE python -m spyinfer_b200.timeline prompt-blocks [--tokens 2048]
     SPYINFER_NVCC_FLAGS=-DSPY_TIMELINE python -m spyinfer_b200.timeline chain [--layers 2] [--batch 8] [--context 8192]
 
 With ``-DSPY_TIMELINE`` the kernels stamp the global timer at points of a block's life into a
@@ -9,7 +10,9 @@ device array; this program runs them, copies the stamps out and prints, per poin
 median and maximum over the blocks.  ``decode``: the decode attention of the LAST layer inside
 the engine's captured decode graph of a model with Qwen3-8B's layer sizes (so the kernels
 ahead of it and behind it are the real ones).  ``prompt``: the prompt attention alone, one
-sequence of ``--tokens`` tokens, stamps of every block's tenth key tile.  ``chain``: the
+sequence of ``--tokens`` tokens, stamps of every block's tenth key tile.  ``prompt-blocks``: the
+same kernel, stamps of each block's life (set-up, Q tile, first scores, loop, output) and how
+the blocks follow one another on their SMs.  ``chain``: the
 few-token products (one-tile tcgen05 kernel) of one decode step in the order they ran, with
 the last layer's decode attention between them, on one time axis.
 """
@@ -142,6 +145,34 @@ def prompt(tokens: int) -> None:
             print(f"  {n:38s} {int(np.median(d)):7d}  ({int(np.percentile(d, 10))} .. {int(np.percentile(d, 90))})")
 
 
+def prompt_blocks(tokens: int) -> None:
+    """Where the blocks of the prompt attention spend their lives, and how the SMs fill up."""
+    from . import microbench
+    r = microbench.bench_attention(1, tokens, tokens, 0, iters=2, kernel="tc")
+    print(f"prompt attention, {tokens} tokens: {r['us']:.1f} us, {r['tflops']:.1f} TFLOP/s")
+    t = _stamps("attention_tc", "spy_attention_tc_block_life", 1024, 8)
+    t = t[(t[:, 0] > 0) & (t[:, 6] > 0)]
+    tiles, sm = t[:, 7] & 0xffff, t[:, 7] >> 16
+    t0 = t[:, 0].min()
+    print(f"{len(t)} blocks on {len(set(sm.tolist()))} SMs; the kernel's span (first entry to last exit) {(t[:, 6].max() - t0) / 1e3:.1f} us")
+    names = ["entry -> set-up done (tensor memory, barriers, stages cleared)", "set-up done -> Q tile in shared memory", "Q tile -> first scores ready",
+             "first scores -> last probabilities written", "last probabilities -> last P.V complete", "last P.V -> output stored"]
+    for i, n in enumerate(names):
+        d = t[:, i + 1] - t[:, i]
+        print(f"  {n:64s} median {int(np.median(d)):7d} ns  (10 % {int(np.percentile(d, 10))}, 90 % {int(np.percentile(d, 90))})")
+    loop = (t[:, 4] - t[:, 3]) / np.maximum(tiles - 1, 1)
+    print(f"  per tile inside the loop: median {int(np.median(loop[tiles > 2]))} ns; tiles a block: {int(tiles.min())} .. {int(tiles.max())}, {int(tiles.sum())} in all")
+    busy, gaps, ends = [], [], []
+    for s_ in sorted(set(sm.tolist())):
+        b = t[sm == s_]
+        b = b[np.argsort(b[:, 0])]
+        busy.append((b[:, 6] - b[:, 0]).sum())
+        gaps += (b[1:, 0] - b[:-1, 6]).tolist()
+        ends.append(b[:, 6].max() - t0)
+    print(f"  per SM: blocks' lives sum to median {np.median(busy) / 1e3:.1f} us; gap between a block's exit and the next one's entry median "
+          f"{int(np.median(gaps)) if gaps else 0} ns; last exit {min(ends) / 1e3:.1f} .. {max(ends) / 1e3:.1f} us")
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="what", required=True)
@@ -155,6 +186,8 @@ def main(argv=None) -> int:
     c.add_argument("--context", type=int, default=8192)
     p = sub.add_parser("prompt")
     p.add_argument("--tokens", type=int, default=8192)
+    b = sub.add_parser("prompt-blocks")
+    b.add_argument("--tokens", type=int, default=2048)
     args = ap.parse_args(argv)
     from . import kernels
     kernels.require_cuda()
@@ -162,6 +195,8 @@ def main(argv=None) -> int:
         decode(args.layers, args.batch, args.context)
     elif args.what == "chain":
         chain(args.layers, args.batch, args.context)
+    elif args.what == "prompt-blocks":
+        prompt_blocks(args.tokens)
     else:
         prompt(args.tokens)
     return 0
