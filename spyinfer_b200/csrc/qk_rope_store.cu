@@ -241,6 +241,112 @@ __global__ void __launch_bounds__(256) qk_rope_store_hd128_kernel(const TS* src,
     }
 }
 
+// Prompt portions (many tokens, bfloat16 input in one array): half a warp owns FOUR consecutive
+// heads of one token (the host takes this kernel only when the heads of a token are a multiple of
+// four), so the token's position, page and (cos, sin) row and the two norm weights are loaded once
+// for the four, and the four inputs are in flight together.  Lane layout and arithmetic are those
+// of the kernel above.
+template <typename TW>
+__global__ void __launch_bounds__(256) qk_rope_store_hd128_x4_kernel(const bf16* src, bf16* q_out, long long q_out_stride, int tokens, int nh, int nkv,
+                                                                     const TW* __restrict__ q_w, const TW* __restrict__ k_w, float eps,
+                                                                     const float2* __restrict__ cos_sin, int table_rows,
+                                                                     const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                                                                     const int* __restrict__ block_table, int table_width, bf16* pages,
+                                                                     int page_size, int num_pages, int store, int* status)
+{
+    constexpr int HD = 128, PER = 4;
+    pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, l = lane & 15;
+    const int heads = store ? nh + 2 * nkv : nh;
+    const int groups = tokens * (heads / PER);   // the host refuses batches whose items do not fit 31 bits
+    const int mine = (blockIdx.x * (blockDim.x >> 5) + warp) * 2 + (lane >> 4);
+    const bool live = mine < groups;
+    const int group = min(mine, groups - 1);   // a group beyond the end repeats the last one and stores nothing
+    const int t = group / (heads / PER), head0 = (group - t * (heads / PER)) * PER;
+    // ---- what no kernel ahead writes: position, page, rotation row, norm weights
+    const int pos = positions[t];
+    const int seq = store ? seq_of_token[t] : 0;
+    float wq[8], wk[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        wq[i] = q_w != nullptr ? to_f32(q_w[8 * l + i]) : 1.f;
+        wk[i] = k_w != nullptr ? to_f32(k_w[8 * l + i]) : 1.f;
+    }
+    const bool in_table = store && pos >= 0 && pos / page_size < table_width;
+    const int page = in_table ? block_table[(size_t)seq * table_width + pos / page_size] : -1;
+    const bool pos_ok = pos >= 0 && pos < table_rows;
+    const bool have_rot = cos_sin != nullptr;
+    float4 cs[4];   // (cos, sin) of the pairs 8 (l & 7) .. + 7
+    {
+        const float4* cs4 = reinterpret_cast<const float4*>(cos_sin + (size_t)((have_rot && pos_ok) ? pos : 0) * 64 + 8 * (l & 7));
+#pragma unroll
+        for (int i = 0; i < 4; ++i) cs[i] = (have_rot && pos_ok) ? cs4[i] : make_float4(1.f, 0.f, 1.f, 0.f);
+    }
+    pdl_wait();
+    // ---- the four inputs
+    const bf16* in = src + (size_t)t * (nh + 2 * nkv) * HD + (size_t)head0 * HD + 8 * l;
+    uint4 raw[PER];
+#pragma unroll
+    for (int h = 0; h < PER; ++h) raw[h] = *reinterpret_cast<const uint4*>(in + h * HD);
+    if (live && have_rot && !pos_ok && l == 0) report_status(status, SPY_STATUS_BAD_POSITION, t);
+    const float c[8] = {cs[0].x, cs[0].z, cs[1].x, cs[1].z, cs[2].x, cs[2].z, cs[3].x, cs[3].z};
+    const float sn[8] = {cs[0].y, cs[0].w, cs[1].y, cs[1].w, cs[2].y, cs[2].w, cs[3].y, cs[3].w};
+#pragma unroll
+    for (int h = 0; h < PER; ++h) {
+        const int head = head0 + h;
+        const int kind = head < nh ? 0 : (head < nh + nkv ? 1 : 2);  // q, k, v
+        const uint32_t w4[4] = {raw[h].x, raw[h].y, raw[h].z, raw[h].w};
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&w4[i]);
+            v[2 * i] = __low2float(a);
+            v[2 * i + 1] = __high2float(a);
+        }
+        bf16* dst = nullptr;
+        if (live && !(have_rot && kind != 2 && !pos_ok)) {
+            if (kind == 0) {
+                dst = q_out + (size_t)t * q_out_stride + (size_t)head * HD + 8 * l;
+            } else if (page < 0 || page >= num_pages) {
+                if (l == 0) report_status(status, SPY_STATUS_BAD_PAGE, t);
+            } else {
+                const int kv_head = kind == 1 ? head - nh : head - nh - nkv;
+                dst = pages + ((((size_t)page * 2 + (kind - 1)) * nkv + kv_head) * page_size + pos % page_size) * HD + 8 * l;
+            }
+        }
+        if (q_w != nullptr) {   // both halves of the warp run the shuffles
+            float ss = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ss += v[i] * v[i];
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            if (kind != 2) {
+                const float inv = 1.0f / sqrtf(ss / (float)HD + eps);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = (inv * v[i]) * (kind == 0 ? wq[i] : wk[i]);
+            }
+        }
+        if (have_rot) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float other = __shfl_xor_sync(0xffffffffu, v[i], 8);
+                const float r = l < 8 ? v[i] * c[i] - other * sn[i] : other * sn[i] + v[i] * c[i];
+                if (kind != 2) v[i] = r;
+            }
+        }
+        if (dst != nullptr) {
+            uint4 outv;
+            uint32_t* o = reinterpret_cast<uint32_t*>(&outv);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                __nv_bfloat162 pk = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+                o[i] = *reinterpret_cast<uint32_t*>(&pk);
+            }
+            *reinterpret_cast<uint4*>(dst) = outv;
+        }
+    }
+}
+
 template <typename TS, typename TQ, typename TC, typename TW>
 static int launch(const void* src, int src_splits, long long src_split_stride, void* q_out, long long q_out_stride, int tokens, int nh, int nkv,
                   int hd, const void* q_w, const void* k_w, float eps, const float* cos_sin, int rot_half, int table_rows, const int* positions,
@@ -293,6 +399,17 @@ extern "C" int spy_qk_rope_store(const void* src, int src_dtype, int src_splits,
     spy_launch(qk_rope_store_hd128_kernel<TS_, TW>, dim3((int)blocks), dim3(256), 0, stream, (const TS_*)src, splits_, stride_,         \
                (bf16*)q_out, q_out_stride, tokens, nh, nkv, (const TW*)q_w, (const TW*)k_w, eps, (const float2*)cos_sin, table_rows,    \
                positions, seq_of_token, block_table, table_width, (bf16*)pages, page_size, num_pages, store, status)
+        if (plain_bf16 && tokens >= 64 && heads % 4 == 0) {
+            // prompt portions: four heads of a token per half warp
+            const long long groups = items / 4, blocks4 = (groups + 15) / 16;
+            SPY_DISPATCH_DTYPE(w_dtype, TW, {
+                spy_launch(qk_rope_store_hd128_x4_kernel<TW>, dim3((int)blocks4), dim3(256), 0, stream, (const bf16*)src, (bf16*)q_out, q_out_stride,
+                           tokens, nh, nkv, (const TW*)q_w, (const TW*)k_w, eps, (const float2*)cos_sin, table_rows, positions, seq_of_token,
+                           block_table, table_width, (bf16*)pages, page_size, num_pages, store, status);
+            })
+            SPY_CHECK_LAUNCH("qk_rope_store (head_dim 128, four heads a half warp)");
+            return 0;
+        }
         SPY_DISPATCH_DTYPE(w_dtype, TW, {
             if (plain_bf16) SPY_QK_HD128(bf16, 1, 0LL);
             else SPY_QK_HD128(float, src_splits, src_split_stride);

@@ -524,12 +524,16 @@ def test_qk_rope_store_sums_a_stack_of_partial_products(hd, splits):
 
 
 @pytest.mark.parametrize("stacked", [False, True])
-def test_qk_rope_store_many_tokens_at_once_equal_few_at_a_time(stacked):
-    """A long prompt portion through the register path of head size 128 gives bit for bit what the same
-    tokens give in small portions; 1001 tokens so that the last block has warps without an item."""
+@pytest.mark.parametrize("nh,nkv", [(8, 2), (6, 1)])
+def test_qk_rope_store_many_tokens_at_once_equal_few_at_a_time(stacked, nh, nkv):
+    """A long prompt portion through the register paths of head size 128 gives bit for bit what the same
+    tokens give in small portions; 1001 tokens so that the last block has warps without an item.
+    Portions of 64 tokens and more of a bfloat16 array take the kernel with four heads a half warp,
+    portions of 40 the one with one head (which the test above holds against the plain formulas); with
+    6 query heads and one key/value head a group of four holds queries, the key and the value."""
     from spyinfer_b200 import kernels
     torch.manual_seed(5)
-    nh, nkv, hd, page_size, T = 8, 2, 128, 16, 1001
+    hd, page_size, T = 128, 16, 1001
     width = (nh + 2 * nkv) * hd
     src = torch.randn(3, T, width, device=DEV) if stacked else torch.randn(T, width, device=DEV).to(torch.bfloat16)
     qw = (1 + 0.1 * torch.randn(hd, device=DEV)).to(torch.bfloat16)
@@ -541,7 +545,7 @@ def test_qk_rope_store_many_tokens_at_once_equal_few_at_a_time(stacked):
     n_pages = (T + page_size - 1) // page_size
     bt = torch.randperm(n_pages).to(torch.int32).view(1, n_pages).to(DEV)
     outs = []
-    for step in (T, 100):
+    for step in (T, 100, 40):
         pages = torch.zeros(n_pages, 2, nkv, page_size, hd, device=DEV, dtype=torch.bfloat16)
         q = torch.empty(T, nh * hd, device=DEV, dtype=torch.bfloat16)
         for a in range(0, T, step):
@@ -551,7 +555,8 @@ def test_qk_rope_store_many_tokens_at_once_equal_few_at_a_time(stacked):
                                            q_out=torch.empty(b - a, nh * hd, device=DEV, dtype=torch.bfloat16) if stacked else None)[:, :nh * hd]
         outs.append((q, pages))
     assert kernels.status_word(DEV)[0].item() == 0
-    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    for other in outs[1:]:
+        assert torch.equal(outs[0][0], other[0]) and torch.equal(outs[0][1], other[1])
     assert outs[0][1].float().abs().sum() > 0
 
 
