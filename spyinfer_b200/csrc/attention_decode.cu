@@ -532,19 +532,21 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
     } else if (warp == 7) {
         // ---------------------------------------------------------------- TMA: the segments' queries, which the kernel ahead wrote
         if (lane == 0) {
-            pdl_wait();
-            STAMP(3);
             Seg g;
             bool more = seg_first(g, share);
+            int tok_next = more ? p.q_start[g.s] : 0;   // the host wrote q_start: read ahead of the wait and of each segment's load
+            pdl_wait();
+            STAMP(3);
             for (int seg = 0; more; ++seg) {
                 const int slot = seg % QSLOTS;
-                const int tok = p.q_start[g.s];
+                const int tok = tok_next;
                 if (seg >= QSLOTS && !mbar_wait(bar_qfree + slot, (uint32_t)(seg / QSLOTS - 1) & 1, abort_flag)) break;
                 mbar_expect_tx(bar_qfull + slot, (uint32_t)p.G * HD * 2);
 #pragma unroll
                 for (int h = 0; h < HD / 64; ++h)
                     tma_load_3d(q_s + slot * QP_BYTES + h * (NCOLS * 128), &q_map, h * 64, g.kvh * p.G, tok, bar_qfull + slot);
                 more = seg_next(g, share);
+                if (more) tok_next = p.q_start[g.s];
             }
         }
     } else {

@@ -220,12 +220,13 @@ __global__ void __launch_bounds__(256) qk_rope_store_hd128_kernel(const TS* src,
     }
     if (cos_sin != nullptr) {
         const float c[8] = {cs[0].x, cs[0].z, cs[1].x, cs[1].z, cs[2].x, cs[2].z, cs[3].x, cs[3].z};
-        const float sn[8] = {cs[0].y, cs[0].w, cs[1].y, cs[1].w, cs[2].y, cs[2].w, cs[3].y, cs[3].w};
+        // lanes 0..7 of the half hold the low half (x_j), lanes 8..15 the high half (x_{j + 64}): the sine enters with its sign
+        const float sg = l < 8 ? -1.f : 1.f;
+        const float sn[8] = {sg * cs[0].y, sg * cs[0].w, sg * cs[1].y, sg * cs[1].w, sg * cs[2].y, sg * cs[2].w, sg * cs[3].y, sg * cs[3].w};
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             const float other = __shfl_xor_sync(0xffffffffu, v[i], 8);
-            // lanes 0..7 of the half hold the low half (x_j), lanes 8..15 the high half (x_{j + 64})
-            const float r = l < 8 ? v[i] * c[i] - other * sn[i] : other * sn[i] + v[i] * c[i];
+            const float r = fmaf(other, sn[i], v[i] * c[i]);   // x_j cos - x_{j+64} sin, or x_j sin + x_{j+64} cos
             if (rotate) v[i] = r;
         }
     }
@@ -247,7 +248,7 @@ __global__ void __launch_bounds__(256) qk_rope_store_hd128_kernel(const TS* src,
 // for the four, and the four inputs are in flight together.  Lane layout and arithmetic are those
 // of the kernel above.
 template <typename TW>
-__global__ void __launch_bounds__(256) qk_rope_store_hd128_x4_kernel(const bf16* src, bf16* q_out, long long q_out_stride, int tokens, int nh, int nkv,
+__global__ void __launch_bounds__(256, 4) qk_rope_store_hd128_x4_kernel(const bf16* src, bf16* q_out, long long q_out_stride, int tokens, int nh, int nkv,
                                                                      const TW* __restrict__ q_w, const TW* __restrict__ k_w, float eps,
                                                                      const float2* __restrict__ cos_sin, int table_rows,
                                                                      const int* __restrict__ positions, const int* __restrict__ seq_of_token,
@@ -290,7 +291,9 @@ __global__ void __launch_bounds__(256) qk_rope_store_hd128_x4_kernel(const bf16*
     for (int h = 0; h < PER; ++h) raw[h] = *reinterpret_cast<const uint4*>(in + h * HD);
     if (live && have_rot && !pos_ok && l == 0) report_status(status, SPY_STATUS_BAD_POSITION, t);
     const float c[8] = {cs[0].x, cs[0].z, cs[1].x, cs[1].z, cs[2].x, cs[2].z, cs[3].x, cs[3].z};
-    const float sn[8] = {cs[0].y, cs[0].w, cs[1].y, cs[1].w, cs[2].y, cs[2].w, cs[3].y, cs[3].w};
+    // lanes 0..7 of the half hold the low half (x_j), lanes 8..15 the high half (x_{j + 64}): the sine enters with its sign
+    const float sg = l < 8 ? -1.f : 1.f;
+    const float sn[8] = {sg * cs[0].y, sg * cs[0].w, sg * cs[1].y, sg * cs[1].w, sg * cs[2].y, sg * cs[2].w, sg * cs[3].y, sg * cs[3].w};
 #pragma unroll
     for (int h = 0; h < PER; ++h) {
         const int head = head0 + h;
@@ -330,7 +333,7 @@ __global__ void __launch_bounds__(256) qk_rope_store_hd128_x4_kernel(const bf16*
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 const float other = __shfl_xor_sync(0xffffffffu, v[i], 8);
-                const float r = l < 8 ? v[i] * c[i] - other * sn[i] : other * sn[i] + v[i] * c[i];
+                const float r = fmaf(other, sn[i], v[i] * c[i]);   // x_j cos - x_{j+64} sin, or x_j sin + x_{j+64} cos
                 if (kind != 2) v[i] = r;
             }
         }
