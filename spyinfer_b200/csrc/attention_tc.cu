@@ -64,7 +64,13 @@ struct Params {
     const int* q_start;        // [S + 1]
     int* status;
     int table_width, page_size, num_pages, nh, nkv, G, Gp, S, window;
+    int x_blocks, items;       // 128-row blocks along the tokens (an upper bound), and x_blocks * nkv work items
     float scale_log2;
+};
+
+// One work item: 128 query rows of one sequence and key/value head, and the key tiles they see.
+struct Item {
+    int seq, tok0, kvh, n_tiles, tile_first, block_lo, block_last_pos, tok_end;
 };
 
 // -DSPY_TIMELINE: blocks stamp the global timer at points of their tenth tile into a device array
@@ -80,12 +86,12 @@ __device__ __forceinline__ unsigned smid()
     return v;
 }
 __device__ unsigned long long g_block_life[1024][8];
-#define LIFE(i) do { if (threadIdx.x == 0) g_block_life[(blockIdx.x + gridDim.x * blockIdx.y) & 1023][i] = global_timer(); } while (0)
-#define LIFE_VALUE(i, v) do { if (threadIdx.x == 0) g_block_life[(blockIdx.x + gridDim.x * blockIdx.y) & 1023][i] = (unsigned long long)(v); } while (0)
+#define LIFE(item, i) do { if (threadIdx.x == 0) g_block_life[(item) & 1023][i] = global_timer(); } while (0)
+#define LIFE_VALUE(item, i, v) do { if (threadIdx.x == 0) g_block_life[(item) & 1023][i] = (unsigned long long)(v); } while (0)
 #else
 #define STAMP(t, i) ((void)0)
-#define LIFE(i) ((void)0)
-#define LIFE_VALUE(i, v) ((void)0)
+#define LIFE(item, i) ((void)0)
+#define LIFE_VALUE(item, i, v) ((void)0)
 #endif
 
 // Byte offset of 16-byte chunk `chunk` (0 .. HD / 8 - 1, or 0 .. 15 for the 128-key P tile) of
@@ -103,8 +109,8 @@ template <int HD> struct Smem {
     // what the two threads of a row tell each other: bfloat16[2 score stages][2 halves][128 rows] maxima, at the end float[2 halves][128 rows] sums
     static constexpr int X_OFF = V_OFF + STAGES * OPERAND_BYTES;
     static constexpr int BAR_OFF = X_OFF + 2 * ROWS * 4;
-    // barriers (192 bytes), then slack to align the base to 1024 (the base is aligned to 128)
-    static constexpr int TOTAL = BAR_OFF + 192 + 896;
+    // barriers and the two work items (320 bytes), then slack to align the base to 1024 (the base is aligned to 128)
+    static constexpr int TOTAL = BAR_OFF + 320 + 896;
     static constexpr int TMEM_COLS = 512;                     // S0, S1: 128 columns each (P_t over the first 64 of S_t); O: HD columns from 256
 };
 
@@ -129,13 +135,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
     uint64_t* bar_p = bar_s + 2;                                        // [2] probabilities written (256 arrivals)
     uint64_t* bar_o = bar_p + 2;                                        // [2] P.V complete (MMA commit)
     uint64_t* bar_x = bar_o + 2;                                        // [2] the halves' maxima are written (256 arrivals)
-    uint64_t* bar_q = bar_x + 2;                                        // first phase: Q tile written; second: the halves' sums written (256 arrivals each)
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_q + 1);
+    uint64_t* bar_q = bar_x + 2;                                        // the item's Q tile is written (256 arrivals)
+    uint64_t* bar_sum = bar_q + 1;                                      // the halves' sums of the item are written (256 arrivals)
+    uint64_t* bar_item = bar_sum + 1;                                   // [2] the block's next work item is described (thread 0)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_item + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    int* s_info = reinterpret_cast<int*>(tmem_slot + 2);                // seq, first token of the block
+    Item* item_ring = reinterpret_cast<Item*>(tmem_slot + 2);           // [2]
 
     pdl_launch_dependents();
-    LIFE(0);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
     const int tokens_per_block = ROWS / p.Gp;
     if (tid == 0) {
@@ -150,8 +157,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
             mbar_init(bar_p + i, SOFTMAX_THREADS);
             mbar_init(bar_o + i, 1);
             mbar_init(bar_x + i, SOFTMAX_THREADS);
+            mbar_init(bar_item + i, 1);
         }
         mbar_init(bar_q, SOFTMAX_THREADS);
+        mbar_init(bar_sum, SOFTMAX_THREADS);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -160,284 +169,339 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
     for (int i = tid; i < 2 * STAGES * L::OPERAND_BYTES / 16; i += NUM_THREADS) reinterpret_cast<uint4*>(smem + L::K_OFF)[i] = make_uint4(0, 0, 0, 0);
     fence_async_proxy();
     pdl_wait();   // everything below reads what earlier kernels wrote
-    if (tid == 0) {
-        // blocks are handed out from the last one back: in a causal prompt the late rows see the most
-        // keys, and the long blocks should start first
-        int b = (int)(gridDim.x - 1 - blockIdx.x), seq = -1, tok0 = 0;
-        for (int s = 0; s < p.S; ++s) {
-            const int n = p.q_start[s + 1] - p.q_start[s];
-            const int blocks = (n + tokens_per_block - 1) / tokens_per_block;
-            if (b < blocks) { seq = s; tok0 = p.q_start[s] + b * tokens_per_block; break; }
-            b -= blocks;
+
+    // The block's work items.  The items are numbered with the long ones first (in a causal prompt the
+    // late rows see the most keys): item i is the block of rows x_blocks - 1 - i / nkv, counted through
+    // the sequences, of key/value head i % nkv.  The block takes one item a round, forwards in even rounds
+    // and backwards in odd ones, so that a long item of one round meets a short one of the next.
+    const int G_blocks = (int)gridDim.x, blk = (int)blockIdx.x;
+    auto item_index = [&](int k) { return k * G_blocks + ((k & 1) ? G_blocks - 1 - blk : blk); };
+    // Thread 0 describes the block's (j + 1)-th item WITH TILES while the block works on the j-th; every role
+    // waits for the description.  Rounds whose item has no tiles (x_blocks is an upper bound; a window may
+    // leave a block without keys) are passed over here, so that every entry of the ring is real work: thread 0
+    // can then never be two entries ahead of a role that has not read its entry yet.  After the last item an
+    // entry with n_tiles = -1 ends the roles.
+    int next_round = 0;   // thread 0 only
+    auto describe_next = [&](int j) {
+        Item it;
+        it.seq = -1; it.tok0 = 0; it.kvh = 0; it.n_tiles = -1; it.tile_first = 0; it.block_lo = 0; it.block_last_pos = -1; it.tok_end = 0;
+        for (; it.n_tiles <= 0; ++next_round) {
+            const int i = item_index(next_round);
+            if (i >= p.items) { it.n_tiles = -1; break; }
+            it.kvh = i % p.nkv;
+            it.seq = -1;
+            int b = p.x_blocks - 1 - i / p.nkv;
+            for (int s = 0; s < p.S; ++s) {
+                const int n = p.q_start[s + 1] - p.q_start[s];
+                const int blocks = (n + tokens_per_block - 1) / tokens_per_block;
+                if (b < blocks) { it.seq = s; it.tok0 = p.q_start[s] + b * tokens_per_block; break; }
+                b -= blocks;
+            }
+            if (it.seq < 0) continue;
+            it.tok_end = p.q_start[it.seq + 1];
+            const int first_pos = p.positions[it.tok0];
+            it.block_last_pos = p.positions[min(it.tok_end, it.tok0 + tokens_per_block) - 1];
+            it.block_lo = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
+            if (it.block_lo <= it.block_last_pos) {
+                it.tile_first = it.block_lo / TILE;
+                it.n_tiles = it.block_last_pos / TILE - it.tile_first + 1;
+            }
         }
-        s_info[0] = seq;
-        s_info[1] = tok0;
-    }
+        item_ring[j & 1] = it;
+        mbar_arrive(bar_item + (j & 1));   // releases the description to the waiting roles
+    };
+    if (tid == 0) describe_next(0);
     fence_before_sync();
     __syncthreads();
     fence_after_sync();
-    LIFE(1);
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_o = tmem_base + 2 * TILE;
-    const int seq = s_info[0], tok0 = s_info[1];
-    const int kvh = blockIdx.y;
-
-    int n_tiles = 0, tile_first = 0, block_lo = 0, block_last_pos = -1, tok_end = 0;
-    if (seq >= 0) {
-        tok_end = p.q_start[seq + 1];
-        const int first_pos = p.positions[tok0];
-        block_last_pos = p.positions[min(tok_end, tok0 + tokens_per_block) - 1];
-        block_lo = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
-        if (block_lo <= block_last_pos) {
-            tile_first = block_lo / TILE;
-            n_tiles = block_last_pos / TILE - tile_first + 1;
-        }
-    }
     const uint32_t q_s = smem_u32(smem + L::Q_OFF), k_s = smem_u32(smem + L::K_OFF), v_s = smem_u32(smem + L::V_OFF);
+    // Every role walks the same entries j = 0, 1, ... and counts the same tiles: `base` tiles before the
+    // current item's; the barriers' stages and phases follow the running tile number base + t.
 
-    if (warp < 8 && seq >= 0 && n_tiles > 0) {
+    if (warp < 8) {
         // ---------------------------------------------------------------- loads, softmax, epilogue
         const int row = tid & (ROWS - 1), half = tid >> 7;    // this thread's query row = TMEM lane, and its half of the row's columns
-        const int tok = tok0 + row / p.Gp, hg = row % p.Gp;
-        const bool row_ok = tok < tok_end && hg < p.G;
-        const int head = kvh * p.G + hg;
-        // the keys this row sees
-        const int pos = row_ok ? min(p.positions[tok], block_last_pos) : -1;
-        const int lo = max((row_ok && p.window > 0) ? max(0, p.positions[tok] - p.window + 1) : 0, block_lo);
-        // the Q tile: consecutive threads copy consecutive 16-byte pieces of a row
-        constexpr int CPR = HD / 8;
-        for (int idx = tid; idx < ROWS * CPR; idx += SOFTMAX_THREADS) {
-            const int r = idx / CPR, c = idx % CPR;
-            const int r_tok = tok0 + r / p.Gp, r_hg = r % p.Gp;
-            const bool ok = r_tok < tok_end && r_hg < p.G;
-            const bf16* src = p.q + (size_t)(ok ? r_tok : 0) * p.q_stride + (size_t)(kvh * p.G + (ok ? r_hg : 0)) * HD + c * 8;
-            cp_async16(smem + L::Q_OFF + tile_offset(r, c), src, ok);
-        }
-        asm volatile("cp.async.wait_all;" ::: "memory");
-        fence_async_proxy();   // the MMA reads shared memory through the async proxy
-        mbar_arrive(bar_q);
-        LIFE(2);
-        LIFE_VALUE(7, (unsigned)n_tiles | (smid() << 16));
-
-        float m_used = -INFINITY, l = 0.f;   // the maximum the probabilities are taken against (equal in both threads of a row); this thread's share of their sum
         const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
         constexpr int COLS = TILE / 2;       // scores per thread
         constexpr int OCOLS = HD / 2;        // output columns per thread
         bool alive = true;
-        for (int t = 0; t < n_tiles; ++t) {
-            const int st = t & 1;
-            const uint32_t ph = (uint32_t)(t >> 1) & 1;
-            alive = mbar_wait(bar_s + st, ph, abort_flag);          // S_t is complete
+        int base = 0;
+        for (int j = 0; alive; ++j) {
+            alive = mbar_wait(bar_item + (j & 1), (uint32_t)(j >> 1) & 1, abort_flag);
             if (!alive) break;
-            if (t == 0) LIFE(3);
-            if (tid == 0) { STAMP(t, 0); STAMP(t - 1, 5); }
-            fence_after_sync();
-            const int key0 = (tile_first + t) * TILE + half * COLS;
-            // This thread's 64 raw scores (masked where the tile is not visible whole to every row of the warp).
-            // The scale is folded into the exponent's argument, exp2(s * scale - m), one packed FMA for two
-            // scores; the maximum is taken on the raw scores (the scale is positive) by 3-input max in four
-            // independent chains; the sum runs in two packed accumulators.
-            uint32_t sc[COLS];
-#pragma unroll
-            for (int c = 0; c < COLS; c += 32) tmem_load<32>(tmem_base + st * TILE + lane_addr + half * COLS + c, *reinterpret_cast<uint32_t(*)[32]>(&sc[c]));
-            tmem_wait_ld();
-            if (tid == 0) STAMP(t, 1);
-            const bool whole = __all_sync(0xffffffffu, !row_ok || (key0 >= lo && key0 + COLS - 1 <= pos));
-            if (!whole) {
-#pragma unroll
-                for (int i = 0; i < COLS; ++i) {
-                    const int j = key0 + i;
-                    if (!(j <= pos && j >= lo)) sc[i] = 0xff800000u;   // -inf
-                }
+            const Item it = item_ring[j & 1];
+            if (it.n_tiles < 0) break;
+            const int item_no = blockIdx.x + gridDim.x * j;   // for the timeline build's stamps
+            (void)item_no;
+            LIFE(item_no, 0);
+            const int n_tiles = it.n_tiles, tile_first = it.tile_first, tok0 = it.tok0, tok_end = it.tok_end, kvh = it.kvh;
+            const int tok = tok0 + row / p.Gp, hg = row % p.Gp;
+            const bool row_ok = tok < tok_end && hg < p.G;
+            const int head = kvh * p.G + hg;
+            // the keys this row sees
+            const int pos = row_ok ? min(p.positions[tok], it.block_last_pos) : -1;
+            const int lo = max((row_ok && p.window > 0) ? max(0, p.positions[tok] - p.window + 1) : 0, it.block_lo);
+            // the Q tile: consecutive threads copy consecutive 16-byte pieces of a row (the products of the item
+            // before are complete: its last P.V was waited for)
+            constexpr int CPR = HD / 8;
+            for (int idx = tid; idx < ROWS * CPR; idx += SOFTMAX_THREADS) {
+                const int r = idx / CPR, c = idx % CPR;
+                const int r_tok = tok0 + r / p.Gp, r_hg = r % p.Gp;
+                const bool ok = r_tok < tok_end && r_hg < p.G;
+                const bf16* src = p.q + (size_t)(ok ? r_tok : 0) * p.q_stride + (size_t)(kvh * p.G + (ok ? r_hg : 0)) * HD + c * 8;
+                cp_async16(smem + L::Q_OFF + tile_offset(r, c), src, ok);
             }
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-            for (int i = 0; i < COLS; i += 8) {
-#pragma unroll
-                for (int c = 0; c < 4; ++c) mx4[c] = max3(mx4[c], __uint_as_float(sc[i + 2 * c]), __uint_as_float(sc[i + 2 * c + 1]));
-            }
-            // The halves tell each other their maxima rounded UP to bfloat16: any common upper bound serves
-            // as the value the exponentials are taken against, and both threads must use the same one.
-            const __nv_bfloat16 mine = __float2bfloat16_ru(fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])));
-            xch[(st * 2 + half) * ROWS + row] = mine;
-            mbar_arrive(bar_x + st);
-            alive = mbar_wait(bar_x + st, ph, abort_flag);
-            if (!alive) break;
-            if (tid == 0) STAMP(t, 2);
-            const float mx = fmaxf(__bfloat162float(mine), __bfloat162float(xch[(st * 2 + (half ^ 1)) * ROWS + row])) * p.scale_log2;
-            // the maximum in use moves only when the row's maximum grew by more than the threshold (or from nothing)
-            const float m_new = fmaxf(m_used, mx);
-            const bool grow = m_new > m_used + RESCALE_THRESHOLD || (m_used == -INFINITY && m_new != -INFINITY);
-            const float alpha = grow ? (m_used == -INFINITY ? 0.f : fast_exp2(m_used - m_new)) : 1.f;
-            if (grow) {
-                l *= alpha;
-                m_used = m_new;
-            }
-            const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
-            const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), neg2 = pack2(neg_m, neg_m);
-            uint64_t sum2[2] = {0ull, 0ull};
-            uint32_t packed[COLS / 2];
-#pragma unroll
-            for (int i = 0; i < COLS; i += 2) {
-                float a0, a1;
-                unpack2(fma2(pack2(__uint_as_float(sc[i]), __uint_as_float(sc[i + 1])), scale2, neg2), a0, a1);
-                const float p0 = fast_exp2(a0), p1 = fast_exp2(a1);
-                sum2[(i >> 1) & 1] = add2(sum2[(i >> 1) & 1], pack2(p0, p1));
-                packed[i / 2] = pack_bf16(p0, p1);
-            }
-            {
-                float s0, s1;
-                unpack2(add2(sum2[0], sum2[1]), s0, s1);
-                l += s0 + s1;
-            }
-            if (tid == 0) STAMP(t, 3);
-            // Only a rescale of O has to wait for P.V of tile t-1, so in the common case P_t is ready before
-            // that product ends and the next one follows it without a gap.
-            if (t > 0 && __any_sync(0xffffffffu, grow)) {   // the warp with the row's other half decides the same
-                alive = mbar_wait(bar_o + ((t - 1) & 1), (uint32_t)((t - 1) >> 1) & 1, abort_flag);
+            asm volatile("cp.async.wait_all;" ::: "memory");
+            fence_async_proxy();   // the MMA reads shared memory through the async proxy
+            mbar_arrive(bar_q);
+            if (tid == 0) describe_next(j + 1);   // while the first scores are on their way
+            LIFE(item_no, 2);
+            LIFE_VALUE(item_no, 7, (unsigned)n_tiles | (smid() << 16));
+
+            float m_used = -INFINITY, l = 0.f;   // the maximum the probabilities are taken against (equal in both threads of a row); this thread's share of their sum
+            for (int t = 0; t < n_tiles; ++t) {
+                const int gt = base + t, st = gt & 1;
+                const uint32_t ph = (uint32_t)(gt >> 1) & 1;
+                alive = mbar_wait(bar_s + st, ph, abort_flag);          // S_t is complete
                 if (!alive) break;
+                if (t == 0) LIFE(item_no, 3);
+                if (tid == 0) { STAMP(t, 0); STAMP(t - 1, 5); }
                 fence_after_sync();
+                const int key0 = (tile_first + t) * TILE + half * COLS;
+                // This thread's 64 raw scores (masked where the tile is not visible whole to every row of the warp).
+                // The scale is folded into the exponent's argument, exp2(s * scale - m), one packed FMA for two
+                // scores; the maximum is taken on the raw scores (the scale is positive) by 3-input max in four
+                // independent chains; the sum runs in two packed accumulators.
+                uint32_t sc[COLS];
+#pragma unroll
+                for (int c = 0; c < COLS; c += 32) tmem_load<32>(tmem_base + st * TILE + lane_addr + half * COLS + c, *reinterpret_cast<uint32_t(*)[32]>(&sc[c]));
+                tmem_wait_ld();
+                if (tid == 0) STAMP(t, 1);
+                const bool whole = __all_sync(0xffffffffu, !row_ok || (key0 >= lo && key0 + COLS - 1 <= pos));
+                if (!whole) {
+#pragma unroll
+                    for (int i = 0; i < COLS; ++i) {
+                        const int j = key0 + i;
+                        if (!(j <= pos && j >= lo)) sc[i] = 0xff800000u;   // -inf
+                    }
+                }
+                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                for (int i = 0; i < COLS; i += 8) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) mx4[c] = max3(mx4[c], __uint_as_float(sc[i + 2 * c]), __uint_as_float(sc[i + 2 * c + 1]));
+                }
+                // The halves tell each other their maxima rounded UP to bfloat16: any common upper bound serves
+                // as the value the exponentials are taken against, and both threads must use the same one.
+                const __nv_bfloat16 mine = __float2bfloat16_ru(fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])));
+                xch[(st * 2 + half) * ROWS + row] = mine;
+                mbar_arrive(bar_x + st);
+                alive = mbar_wait(bar_x + st, ph, abort_flag);
+                if (!alive) break;
+                if (tid == 0) STAMP(t, 2);
+                const float mx = fmaxf(__bfloat162float(mine), __bfloat162float(xch[(st * 2 + (half ^ 1)) * ROWS + row])) * p.scale_log2;
+                // the maximum in use moves only when the row's maximum grew by more than the threshold (or from nothing)
+                const float m_new = fmaxf(m_used, mx);
+                const bool grow = m_new > m_used + RESCALE_THRESHOLD || (m_used == -INFINITY && m_new != -INFINITY);
+                const float alpha = grow ? (m_used == -INFINITY ? 0.f : fast_exp2(m_used - m_new)) : 1.f;
+                if (grow) {
+                    l *= alpha;
+                    m_used = m_new;
+                }
+                const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
+                const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), neg2 = pack2(neg_m, neg_m);
+                uint64_t sum2[2] = {0ull, 0ull};
+                uint32_t packed[COLS / 2];
+#pragma unroll
+                for (int i = 0; i < COLS; i += 2) {
+                    float a0, a1;
+                    unpack2(fma2(pack2(__uint_as_float(sc[i]), __uint_as_float(sc[i + 1])), scale2, neg2), a0, a1);
+                    const float p0 = fast_exp2(a0), p1 = fast_exp2(a1);
+                    sum2[(i >> 1) & 1] = add2(sum2[(i >> 1) & 1], pack2(p0, p1));
+                    packed[i / 2] = pack_bf16(p0, p1);
+                }
+                {
+                    float s0, s1;
+                    unpack2(add2(sum2[0], sum2[1]), s0, s1);
+                    l += s0 + s1;
+                }
+                if (tid == 0) STAMP(t, 3);
+                // Only a rescale of O has to wait for P.V of tile t-1, so in the common case P_t is ready before
+                // that product ends and the next one follows it without a gap.
+                if (t > 0 && __any_sync(0xffffffffu, grow)) {   // the warp with the row's other half decides the same
+                    alive = mbar_wait(bar_o + ((gt - 1) & 1), (uint32_t)((gt - 1) >> 1) & 1, abort_flag);
+                    if (!alive) break;
+                    fence_after_sync();
+#pragma unroll 1
+                    for (int c = 0; c < OCOLS; c += 32) {
+                        uint32_t r[32];
+                        tmem_load<32>(tmem_o + lane_addr + half * OCOLS + c, r);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                        tmem_store<32>(tmem_o + lane_addr + half * OCOLS + c, r);
+                        tmem_wait_st();
+                    }
+                }
+                // P_t over the first 64 columns of S_t: both threads of the row have their scores in registers
+                // (the partner loaded its own before it arrived at the exchange)
+#pragma unroll
+                for (int c = 0; c < COLS / 2; c += 32)
+                    tmem_store<32>(tmem_base + st * TILE + lane_addr + half * (COLS / 2) + c, *reinterpret_cast<uint32_t(*)[32]>(&packed[c]));
+                tmem_wait_st();
+                fence_before_sync();
+                mbar_arrive(bar_p + st);
+                if (tid == 0) STAMP(t, 4);
+            }
+            if (!alive) break;
+            // ---- the item's epilogue: O / l
+            LIFE(item_no, 4);
+            const int gl = base + n_tiles - 1;
+            alive = mbar_wait(bar_o + (gl & 1), (uint32_t)(gl >> 1) & 1, abort_flag);
+            if (!alive) break;
+            LIFE(item_no, 5);
+            fence_after_sync();
+            xsum[half * ROWS + row] = l;   // every thread has read the maxima of the last tile: it wrote P after that, and P.V is complete
+            mbar_arrive(bar_sum);
+            alive = mbar_wait(bar_sum, (uint32_t)j & 1, abort_flag);
+            if (!alive) break;
+            {
+                const float sum = half == 0 ? l + xsum[ROWS + row] : xsum[row] + l;   // the same order in both threads
+                const float inv = sum > 0.f ? 1.f / sum : 0.f;
+                bf16* dst = p.out + ((size_t)(row_ok ? tok : 0) * p.nh + head) * HD + half * OCOLS;
 #pragma unroll 1
                 for (int c = 0; c < OCOLS; c += 32) {
                     uint32_t r[32];
                     tmem_load<32>(tmem_o + lane_addr + half * OCOLS + c, r);
                     tmem_wait_ld();
+                    if (!row_ok) continue;
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-                    tmem_store<32>(tmem_o + lane_addr + half * OCOLS + c, r);
-                    tmem_wait_st();
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        uint4 v;
+                        v.x = pack_bf16(__uint_as_float(r[8 * q4]) * inv, __uint_as_float(r[8 * q4 + 1]) * inv);
+                        v.y = pack_bf16(__uint_as_float(r[8 * q4 + 2]) * inv, __uint_as_float(r[8 * q4 + 3]) * inv);
+                        v.z = pack_bf16(__uint_as_float(r[8 * q4 + 4]) * inv, __uint_as_float(r[8 * q4 + 5]) * inv);
+                        v.w = pack_bf16(__uint_as_float(r[8 * q4 + 6]) * inv, __uint_as_float(r[8 * q4 + 7]) * inv);
+                        *reinterpret_cast<uint4*>(dst + c + 8 * q4) = v;
+                    }
                 }
             }
-            // P_t over the first 64 columns of S_t: both threads of the row have their scores in registers
-            // (the partner loaded its own before it arrived at the exchange)
-#pragma unroll
-            for (int c = 0; c < COLS / 2; c += 32)
-                tmem_store<32>(tmem_base + st * TILE + lane_addr + half * (COLS / 2) + c, *reinterpret_cast<uint32_t(*)[32]>(&packed[c]));
-            tmem_wait_st();
+            // the next item's first P.V overwrites O: it needs that item's probabilities, which every thread writes
+            // only after it has read its part of O here
             fence_before_sync();
-            mbar_arrive(bar_p + st);
-            if (tid == 0) STAMP(t, 4);
+            LIFE(item_no, 6);
+            base += n_tiles;
         }
-        // ---- epilogue: O / l
-        LIFE(4);
-        if (alive) alive = mbar_wait(bar_o + ((n_tiles - 1) & 1), (uint32_t)((n_tiles - 1) >> 1) & 1, abort_flag);
-        LIFE(5);
-        if (alive) {
-            fence_after_sync();
-            xsum[half * ROWS + row] = l;   // every thread has read the maxima of the last tile: it wrote P after that, and P.V is complete
-            mbar_arrive(bar_q);
-            alive = mbar_wait(bar_q, 1, abort_flag);
-        }
-        if (alive) {
-            const float sum = half == 0 ? l + xsum[ROWS + row] : xsum[row] + l;   // the same order in both threads
-            const float inv = sum > 0.f ? 1.f / sum : 0.f;
-            bf16* dst = p.out + ((size_t)(row_ok ? tok : 0) * p.nh + head) * HD + half * OCOLS;
-#pragma unroll 1
-            for (int c = 0; c < OCOLS; c += 32) {
-                uint32_t r[32];
-                tmem_load<32>(tmem_o + lane_addr + half * OCOLS + c, r);
-                tmem_wait_ld();
-                if (!row_ok) continue;
-#pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    uint4 v;
-                    v.x = pack_bf16(__uint_as_float(r[8 * q4]) * inv, __uint_as_float(r[8 * q4 + 1]) * inv);
-                    v.y = pack_bf16(__uint_as_float(r[8 * q4 + 2]) * inv, __uint_as_float(r[8 * q4 + 3]) * inv);
-                    v.z = pack_bf16(__uint_as_float(r[8 * q4 + 4]) * inv, __uint_as_float(r[8 * q4 + 5]) * inv);
-                    v.w = pack_bf16(__uint_as_float(r[8 * q4 + 6]) * inv, __uint_as_float(r[8 * q4 + 7]) * inv);
-                    *reinterpret_cast<uint4*>(dst + c + 8 * q4) = v;
-                }
-            }
-        }
-        LIFE(6);
-    } else if (warp == 8 && seq >= 0 && n_tiles > 0) {
+    } else if (warp == 8) {
         // ---------------------------------------------------------------- MMA issue
         if (lane == 0) {
             const uint32_t idesc_qk = instr_desc_bf16(ROWS, TILE, false, false), idesc_pv = instr_desc_bf16(ROWS, HD, false, true);
-            auto issue_qk = [&](int t) {
-                const uint32_t kb = k_s + (t % STAGES) * L::OPERAND_BYTES;
+            auto issue_qk = [&](int gt) {   // gt: the running tile number
+                const uint32_t kb = k_s + (gt % STAGES) * L::OPERAND_BYTES;
 #pragma unroll
                 for (int s = 0; s < HD / 16; ++s) {
                     const uint32_t off = (s >> 2) * (ROWS * 128) + (s & 3) * 32;   // 64-element half, then 32 bytes per 16 elements
-                    umma(tmem_base + (t & 1) * TILE, desc_k_major(q_s + off), desc_k_major(kb + off), idesc_qk, s > 0 ? 1u : 0u);
+                    umma(tmem_base + (gt & 1) * TILE, desc_k_major(q_s + off), desc_k_major(kb + off), idesc_qk, s > 0 ? 1u : 0u);
                 }
-                umma_commit(bar_s + (t & 1));
-                umma_commit(bar_kfree + t % STAGES);
+                umma_commit(bar_s + (gt & 1));
+                umma_commit(bar_kfree + gt % STAGES);
             };
-            bool ok = mbar_wait(bar_q, 0, abort_flag) && mbar_wait(bar_k + 0, 0, abort_flag);
-            if (ok) {
-                fence_after_sync();
-                issue_qk(0);
-            }
-            if (ok && n_tiles > 1) {
-                ok = mbar_wait(bar_k + 1, 0, abort_flag);
+            bool ok = true;
+            int base = 0;
+            for (int j = 0; ok; ++j) {
+                ok = mbar_wait(bar_item + (j & 1), (uint32_t)(j >> 1) & 1, abort_flag);
+                if (!ok) break;
+                const int n_tiles = item_ring[j & 1].n_tiles;
+                if (n_tiles < 0) break;
+                // the item's Q tile is in shared memory (and the scores' stages are free: every P.V of the item before
+                // has been issued, and the tensor core runs in order)
+                ok = mbar_wait(bar_q, (uint32_t)j & 1, abort_flag) && mbar_wait(bar_k + base % STAGES, (uint32_t)(base / STAGES) & 1, abort_flag);
                 if (ok) {
                     fence_after_sync();
-                    issue_qk(1);
+                    issue_qk(base);
                 }
-            }
-            for (int t = 0; t < n_tiles && ok; ++t) {
-                const int st = t & 1, stage = t % STAGES;
-                ok = mbar_wait(bar_p + st, (uint32_t)(t >> 1) & 1, abort_flag);
-                STAMP(t, 6);
-                ok = ok && mbar_wait(bar_v + stage, (uint32_t)(t / STAGES) & 1, abort_flag);
-                if (!ok) break;
-                STAMP(t, 7);
-                fence_after_sync();
-                const uint32_t vb = v_s + stage * L::OPERAND_BYTES;
-#pragma unroll
-                for (int s = 0; s < TILE / 16; ++s)   // 16 keys: 8 columns of P (two bfloat16 each), 16 rows of V of 128 bytes
-                    umma_ts(tmem_o, tmem_base + st * TILE + s * 8, desc_mn_major(vb + s * 16 * 128, ROWS * 128), idesc_pv, (t > 0 || s > 0) ? 1u : 0u);
-                umma_commit(bar_o + st);
-                umma_commit(bar_vfree + stage);
-                STAMP(t, 8);
-                if (t + 2 < n_tiles) {
-                    // S's stage st is free: P_t lies in it and the product above reads it first (the tensor core runs in order)
-                    ok = mbar_wait(bar_k + (t + 2) % STAGES, (uint32_t)((t + 2) / STAGES) & 1, abort_flag);
+                if (ok && n_tiles > 1) {
+                    ok = mbar_wait(bar_k + (base + 1) % STAGES, (uint32_t)((base + 1) / STAGES) & 1, abort_flag);
+                    if (ok) {
+                        fence_after_sync();
+                        issue_qk(base + 1);
+                    }
+                }
+                for (int t = 0; t < n_tiles && ok; ++t) {
+                    const int gt = base + t, st = gt & 1, stage = gt % STAGES;
+                    ok = mbar_wait(bar_p + st, (uint32_t)(gt >> 1) & 1, abort_flag);
+                    STAMP(t, 6);
+                    ok = ok && mbar_wait(bar_v + stage, (uint32_t)(gt / STAGES) & 1, abort_flag);
                     if (!ok) break;
-                    STAMP(t, 9);
+                    STAMP(t, 7);
                     fence_after_sync();
-                    issue_qk(t + 2);
-                    STAMP(t, 10);
+                    const uint32_t vb = v_s + stage * L::OPERAND_BYTES;
+#pragma unroll
+                    for (int s = 0; s < TILE / 16; ++s)   // 16 keys: 8 columns of P (two bfloat16 each), 16 rows of V of 128 bytes
+                        umma_ts(tmem_o, tmem_base + st * TILE + s * 8, desc_mn_major(vb + s * 16 * 128, ROWS * 128), idesc_pv, (t > 0 || s > 0) ? 1u : 0u);
+                    umma_commit(bar_o + st);
+                    umma_commit(bar_vfree + stage);
+                    STAMP(t, 8);
+                    if (t + 2 < n_tiles) {
+                        // S's stage st is free: P_t lies in it and the product above reads it first (the tensor core runs in order)
+                        ok = mbar_wait(bar_k + (gt + 2) % STAGES, (uint32_t)((gt + 2) / STAGES) & 1, abort_flag);
+                        if (!ok) break;
+                        STAMP(t, 9);
+                        fence_after_sync();
+                        issue_qk(gt + 2);
+                        STAMP(t, 10);
+                    }
                 }
+                base += n_tiles;
             }
         }
-    } else if (warp >= 9 && seq >= 0 && n_tiles > 0) {
+    } else {
         // ---------------------------------------------------------------- TMA of K (warp 9) and V (warp 10) tiles
         // One box per page and 64-column half; the lanes of the warp issue the boxes of a tile side
         // by side (a single thread issuing them one after the other is the slower way: small boxes
-        // are bound by issue latency, not by bandwidth).
+        // are bound by issue latency, not by bandwidth).  The warps run ahead into the next item's tiles
+        // as far as the stages allow, so an item's first keys are there when its Q tile is.
         const int kv = warp - 9;
-        const int* bt = p.block_table + (size_t)seq * p.table_width;
         const int pages_per_tile = TILE / p.page_size;
         const int boxes = pages_per_tile * (HD / 64);
         const uint32_t box_bytes = (uint32_t)p.page_size * 128;              // page_size rows of 64 elements
         const int my_page = lane / (HD / 64), my_half = lane % (HD / 64);   // this lane's box of a tile
         bool ok = true;
-        for (int t = 0; t < n_tiles; ++t) {
-            const int st = t % STAGES;
-            uint64_t* bar = (kv == 0 ? bar_k : bar_v) + st;
-            // this lane's page of the tile, looked up before the wait for the stage (which hides the lookup);
-            // pages that hold keys no row of the block can see, or that the table does not name, are skipped
-            const int lp = (tile_first + t) * pages_per_tile + my_page;
-            const bool in_range = lane < boxes && lp * p.page_size <= block_last_pos && (lp + 1) * p.page_size > block_lo;
-            const int page = (in_range && lp < p.table_width) ? bt[lp] : -1;
-            const bool valid = in_range && page >= 0 && page < p.num_pages;
-            if (in_range && !valid && kv == 0) report_status(p.status, SPY_STATUS_BAD_PAGE, tok0);
-            const int count = __popc(__ballot_sync(0xffffffffu, valid));
-            if (lane == 0) {
-                // K's stage is free when Q.K of the tile three back is complete, V's when its P.V is
-                if (t >= STAGES) ok = mbar_wait((kv == 0 ? bar_kfree : bar_vfree) + st, (uint32_t)(t / STAGES - 1) & 1, abort_flag);
-                if (kv == 0) STAMP(t - 3, 11);
-                if (ok) mbar_expect_tx(bar, (uint32_t)count * box_bytes);
-            }
-            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        int base = 0;
+        for (int j = 0; ok; ++j) {
+            ok = mbar_wait(bar_item + (j & 1), (uint32_t)(j >> 1) & 1, abort_flag);
             if (!ok) break;
-            if (valid) {
-                const int y = ((page * 2 + kv) * p.nkv + kvh) * p.page_size;
-                tma_load_2d((kv == 0 ? k_s : v_s) + st * L::OPERAND_BYTES + my_half * (ROWS * 128) + my_page * p.page_size * 128, &page_map, my_half * 64, y, bar);
+            const Item it = item_ring[j & 1];
+            if (it.n_tiles < 0) break;
+            const int* bt = p.block_table + (size_t)it.seq * p.table_width;
+            for (int t = 0; t < it.n_tiles; ++t) {
+                const int gt = base + t, st = gt % STAGES;
+                uint64_t* bar = (kv == 0 ? bar_k : bar_v) + st;
+                // this lane's page of the tile, looked up before the wait for the stage (which hides the lookup);
+                // pages that hold keys no row of the block can see, or that the table does not name, are skipped
+                const int lp = (it.tile_first + t) * pages_per_tile + my_page;
+                const bool in_range = lane < boxes && lp * p.page_size <= it.block_last_pos && (lp + 1) * p.page_size > it.block_lo;
+                const int page = (in_range && lp < p.table_width) ? bt[lp] : -1;
+                const bool valid = in_range && page >= 0 && page < p.num_pages;
+                if (in_range && !valid && kv == 0) report_status(p.status, SPY_STATUS_BAD_PAGE, it.tok0);
+                const int count = __popc(__ballot_sync(0xffffffffu, valid));
+                if (lane == 0) {
+                    // K's stage is free when Q.K of the tile three back is complete, V's when its P.V is
+                    if (gt >= STAGES) ok = mbar_wait((kv == 0 ? bar_kfree : bar_vfree) + st, (uint32_t)(gt / STAGES - 1) & 1, abort_flag);
+                    if (kv == 0) STAMP(t - 3, 11);
+                    if (ok) mbar_expect_tx(bar, (uint32_t)count * box_bytes);
+                }
+                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                if (!ok) break;
+                if (valid) {
+                    const int y = ((page * 2 + kv) * p.nkv + it.kvh) * p.page_size;
+                    tma_load_2d((kv == 0 ? k_s : v_s) + st * L::OPERAND_BYTES + my_half * (ROWS * 128) + my_page * p.page_size * 128, &page_map, my_half * 64, y, bar);
+                }
+                if (kv == 0 && lane == 0) STAMP(t - 3, 12);
             }
-            if (kv == 0 && lane == 0) STAMP(t - 3, 12);
+            base += it.n_tiles;
         }
     }
 
@@ -519,8 +583,19 @@ extern "C" int spy_attention_tc(const void* q, long long q_row_stride, void* out
     }
     const int tokens_per_block = ROWS / Gp;
     const long long blocks = (tokens + tokens_per_block - 1) / tokens_per_block + seqs;   // an upper bound without a host copy of q_start
-    if (blocks > 0x7fffffffLL || nkv > 65535) SPY_FAIL("attention_tc: the batch exceeds the grid limits");
-    dim3 grid((unsigned)blocks, nkv);
+    const long long items = blocks * nkv;
+    if (items > 0x7fffffffLL) SPY_FAIL("attention_tc: the batch's %lld work items exceed the kernel's range", items);
+    p.x_blocks = (int)blocks;
+    p.items = (int)items;
+    // one resident block per SM walks through the items (set-up once, the next item's keys requested while the
+    // last tiles of the one before are worked on)
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        SPY_CUDA(cudaGetDevice(&dev));
+        SPY_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    }
+    dim3 grid((unsigned)(items < sms ? items : sms));
     if (hd == 64) spy_launch(attention_tc_kernel<64>, grid, dim3(NUM_THREADS), (size_t)Smem<64>::TOTAL, stream, page_map, p);
     else spy_launch(attention_tc_kernel<128>, grid, dim3(NUM_THREADS), (size_t)Smem<128>::TOTAL, stream, page_map, p);
     SPY_CHECK_LAUNCH("attention_tc");

@@ -146,7 +146,7 @@ def prompt(tokens: int) -> None:
 
 
 def prompt_blocks(tokens: int) -> None:
-    """Where the blocks of the prompt attention spend their lives, and how the SMs fill up."""
+    """Where the work items of the prompt attention spend their lives, and how they follow one another on the SMs."""
     from . import microbench
     r = microbench.bench_attention(1, tokens, tokens, 0, iters=2, kernel="tc")
     print(f"prompt attention, {tokens} tokens: {r['us']:.1f} us, {r['tflops']:.1f} TFLOP/s")
@@ -154,11 +154,13 @@ def prompt_blocks(tokens: int) -> None:
     t = t[(t[:, 0] > 0) & (t[:, 6] > 0)]
     tiles, sm = t[:, 7] & 0xffff, t[:, 7] >> 16
     t0 = t[:, 0].min()
-    print(f"{len(t)} blocks on {len(set(sm.tolist()))} SMs; the kernel's span (first entry to last exit) {(t[:, 6].max() - t0) / 1e3:.1f} us")
-    names = ["entry -> set-up done (tensor memory, barriers, stages cleared)", "set-up done -> Q tile in shared memory", "Q tile -> first scores ready",
-             "first scores -> last probabilities written", "last probabilities -> last P.V complete", "last P.V -> output stored"]
-    for i, n in enumerate(names):
-        d = t[:, i + 1] - t[:, i]
+    print(f"{len(t)} work items on {len(set(sm.tolist()))} SMs (one resident block a SM walks through its items); the kernel's span "
+          f"(first item's start to last output stored) {(t[:, 6].max() - t0) / 1e3:.1f} us")
+    names = [(0, 2, "item read -> Q tile in shared memory (positions read, cp.async)"), (2, 3, "Q tile -> first scores ready"),
+             (3, 4, "first scores -> last probabilities written"), (4, 5, "last probabilities -> last P.V complete"),
+             (5, 6, "last P.V -> output stored")]
+    for a, b, n in names:
+        d = t[:, b] - t[:, a]
         print(f"  {n:64s} median {int(np.median(d)):7d} ns  (10 % {int(np.percentile(d, 10))}, 90 % {int(np.percentile(d, 90))})")
     loop = (t[:, 4] - t[:, 3]) / np.maximum(tiles - 1, 1)
     print(f"  per tile inside the loop: median {int(np.median(loop[tiles > 2]))} ns; tiles a block: {int(tiles.min())} .. {int(tiles.max())}, {int(tiles.sum())} in all")
@@ -169,7 +171,7 @@ def prompt_blocks(tokens: int) -> None:
         busy.append((b[:, 6] - b[:, 0]).sum())
         gaps += (b[1:, 0] - b[:-1, 6]).tolist()
         ends.append(b[:, 6].max() - t0)
-    print(f"  per SM: blocks' lives sum to median {np.median(busy) / 1e3:.1f} us; gap between a block's exit and the next one's entry median "
+    print(f"  per SM: the items' lives sum to median {np.median(busy) / 1e3:.1f} us; gap between an item's output and the next item's start median "
           f"{int(np.median(gaps)) if gaps else 0} ns; last exit {min(ends) / 1e3:.1f} .. {max(ends) / 1e3:.1f} us")
 
 
