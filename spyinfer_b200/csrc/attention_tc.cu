@@ -226,8 +226,21 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
         const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
         constexpr int COLS = TILE / 2;       // scores per thread
         constexpr int OCOLS = HD / 2;        // output columns per thread
-        bool alive = true;
+        bool alive = true, q_requested = false;
         int base = 0;
+        // The item's Q tile: consecutive threads copy consecutive 16-byte pieces of a row.  It is requested as soon
+        // as the item before has its last scores (every Q.K of that item is then complete), and so arrives
+        // while that item's output is read and stored.
+        auto request_q = [&](const Item& it) {
+            constexpr int CPR = HD / 8;
+            for (int idx = tid; idx < ROWS * CPR; idx += SOFTMAX_THREADS) {
+                const int r = idx / CPR, c = idx % CPR;
+                const int r_tok = it.tok0 + r / p.Gp, r_hg = r % p.Gp;
+                const bool ok = r_tok < it.tok_end && r_hg < p.G;
+                const bf16* src = p.q + (size_t)(ok ? r_tok : 0) * p.q_stride + (size_t)(it.kvh * p.G + (ok ? r_hg : 0)) * HD + c * 8;
+                cp_async16(smem + L::Q_OFF + tile_offset(r, c), src, ok);
+            }
+        };
         for (int j = 0; alive; ++j) {
             alive = mbar_wait(bar_item + (j & 1), (uint32_t)(j >> 1) & 1, abort_flag);
             if (!alive) break;
@@ -243,16 +256,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
             // the keys this row sees
             const int pos = row_ok ? min(p.positions[tok], it.block_last_pos) : -1;
             const int lo = max((row_ok && p.window > 0) ? max(0, p.positions[tok] - p.window + 1) : 0, it.block_lo);
-            // the Q tile: consecutive threads copy consecutive 16-byte pieces of a row (the products of the item
-            // before are complete: its last P.V was waited for)
-            constexpr int CPR = HD / 8;
-            for (int idx = tid; idx < ROWS * CPR; idx += SOFTMAX_THREADS) {
-                const int r = idx / CPR, c = idx % CPR;
-                const int r_tok = tok0 + r / p.Gp, r_hg = r % p.Gp;
-                const bool ok = r_tok < tok_end && r_hg < p.G;
-                const bf16* src = p.q + (size_t)(ok ? r_tok : 0) * p.q_stride + (size_t)(kvh * p.G + (ok ? r_hg : 0)) * HD + c * 8;
-                cp_async16(smem + L::Q_OFF + tile_offset(r, c), src, ok);
-            }
+            if (!q_requested) request_q(it);   // the block's first item
             asm volatile("cp.async.wait_all;" ::: "memory");
             fence_async_proxy();   // the MMA reads shared memory through the async proxy
             mbar_arrive(bar_q);
@@ -356,7 +360,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
                 if (tid == 0) STAMP(t, 4);
             }
             if (!alive) break;
-            // ---- the item's epilogue: O / l
+            // ---- the next item's Q tile is requested ...
+            alive = mbar_wait(bar_item + ((j + 1) & 1), (uint32_t)((j + 1) >> 1) & 1, abort_flag);
+            if (!alive) break;
+            q_requested = item_ring[(j + 1) & 1].n_tiles > 0;
+            if (q_requested) request_q(item_ring[(j + 1) & 1]);
+            // ---- ... and this item's epilogue runs meanwhile: O / l
             LIFE(item_no, 4);
             const int gl = base + n_tiles - 1;
             alive = mbar_wait(bar_o + (gl & 1), (uint32_t)(gl >> 1) & 1, abort_flag);

@@ -123,6 +123,25 @@ def test_temperature_sampling_is_seeded_and_follows_the_distribution(tiny_models
     assert np.abs(freq - p).max() < 4 * np.sqrt(p.max() / n) + 2e-3
 
 
+def test_top_k_of_one_is_greedy_and_top_k_limits_the_draws(tiny_models):
+    """Through the entry point: with ``top_k=1`` a temperature draws the argmax; with ``top_k=3`` every first
+    token over many seeds is one of the plain implementation's three most likely."""
+    from spyinfer_b200 import SamplingParams
+    folder, cfg, weights = tiny_models["b"]
+    engine = engine_for(folder, "float32", max_num_seqs=64, num_kvcache_blocks=128, max_num_batched_tokens=512)
+    prompt = [9, 8, 7, 6]
+    greedy = engine.generate([prompt], SamplingParams(max_new_tokens=6, ignore_eos=True))[0]
+    one = engine.generate([prompt] * 2, [SamplingParams(temperature=2.0, top_k=1, seed=s, max_new_tokens=6, ignore_eos=True) for s in (3, 4)])
+    assert one[0] == greedy and one[1] == greedy
+    outs = engine.generate([prompt] * 60, [SamplingParams(temperature=3.0, top_k=3, seed=s, max_new_tokens=1, ignore_eos=True) for s in range(60)])
+    logits = plain_model.forward_logits(weights, cfg, prompt)[-1]
+    top3 = set(torch.topk(logits, 3).indices.tolist())
+    firsts = {o[0] for o in outs}
+    assert firsts <= top3 and len(firsts) >= 2
+    with pytest.raises(ValueError):
+        SamplingParams(top_k=-1)
+
+
 def test_command_line_generates(tiny_models):
     import os, subprocess, sys
     folder, cfg, weights = tiny_models["a"]
