@@ -723,9 +723,14 @@ constexpr size_t PAIR_SMEM = (size_t)PAIR_STAGES * PAIR_STAGE_BYTES + 1024 /* al
 template <typename TC, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, TC* __restrict__ out,
-                         long long ld, int x_rows, int y_rows, int k_blocks, int x_tiles, int num_tiles, int* status)
+                         long long ld, int x_rows, int y_rows, int k_blocks, int x_tiles, int num_tiles, int splits, int kb_per_split,
+                         long long split_stride, int* status)
 {
+    // splits > 1 (few tiles, 512 tokens or so): a work unit is one tile over one range of kb_per_split K blocks; unit u is
+    // tile u % num_tiles of range u / num_tiles, and its 32-bit partial tile goes to out + range * split_stride (the
+    // caller sums the ranges in order).  With one range a unit is a whole tile.
     constexpr int BN = 256;
+    const int num_units = num_tiles * splits;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* tiles = smem;
@@ -763,32 +768,34 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
         if (lane == 0) {
             long long g = 0;
             bool ok = true, first = true;
-            for (int tile = cluster; tile < num_tiles && ok; tile += clusters) {
+            for (int unit = cluster; unit < num_units && ok; unit += clusters) {
+                const int tile = unit % num_tiles, kb0 = (unit / num_tiles) * kb_per_split;
+                const int nkb = min(k_blocks, kb0 + kb_per_split) - kb0;
                 const int x0 = (tile % x_tiles) * (2 * BM) + (int)rank * BM, y0 = (tile / x_tiles) * BN + (int)rank * (BN / 2);
                 int kb = 0;
                 if (first) {
                     // the weights (Y) of the first stages are requested before the wait for the kernels ahead in the stream
-                    const int pre = min(k_blocks, PAIR_STAGES);
+                    const int pre = min(nkb, PAIR_STAGES);
                     for (int i = 0; i < pre; ++i) {
                         if (rank == 0) mbar_expect_tx(full_bar + i, 2 * PAIR_STAGE_BYTES);
-                        tma_load_2d_pair(smem_u32(tiles + (size_t)i * PAIR_STAGE_BYTES + PAIR_X_BYTES), &map_y, i * BK, y0, map_to_rank(smem_u32(full_bar + i), 0));
+                        tma_load_2d_pair(smem_u32(tiles + (size_t)i * PAIR_STAGE_BYTES + PAIR_X_BYTES), &map_y, (kb0 + i) * BK, y0, map_to_rank(smem_u32(full_bar + i), 0));
                     }
                     pdl_wait();
                     for (int i = 0; i < pre; ++i)
-                        tma_load_2d_pair(smem_u32(tiles + (size_t)i * PAIR_STAGE_BYTES), &map_x, i * BK, x0, map_to_rank(smem_u32(full_bar + i), 0));
+                        tma_load_2d_pair(smem_u32(tiles + (size_t)i * PAIR_STAGE_BYTES), &map_x, (kb0 + i) * BK, x0, map_to_rank(smem_u32(full_bar + i), 0));
                     kb = pre;
                     g = pre;
                     first = false;
                 }
-                for (; kb < k_blocks; ++kb, ++g) {
+                for (; kb < nkb; ++kb, ++g) {
                     const int s = (int)(g % PAIR_STAGES);
                     const uint32_t phase = (uint32_t)(g / PAIR_STAGES) & 1;
                     if (g >= PAIR_STAGES && !mbar_wait(empty_bar + s, phase ^ 1, abort_flag)) { ok = false; break; }
                     uint8_t* xs = tiles + (size_t)s * PAIR_STAGE_BYTES;
                     if (rank == 0) mbar_expect_tx(full_bar + s, 2 * PAIR_STAGE_BYTES);   // both blocks' bytes
                     const uint32_t leader_full = map_to_rank(smem_u32(full_bar + s), 0);
-                    tma_load_2d_pair(smem_u32(xs), &map_x, kb * BK, x0, leader_full);
-                    tma_load_2d_pair(smem_u32(xs + PAIR_X_BYTES), &map_y, kb * BK, y0, leader_full);
+                    tma_load_2d_pair(smem_u32(xs), &map_x, (kb0 + kb) * BK, x0, leader_full);
+                    tma_load_2d_pair(smem_u32(xs + PAIR_X_BYTES), &map_y, (kb0 + kb) * BK, y0, leader_full);
                 }
             }
             if (first) pdl_wait();
@@ -799,14 +806,16 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
             long long g = 0;
             int i = 0;
             bool ok = true;
-            for (int tile = cluster; tile < num_tiles && ok; tile += clusters, ++i) {
+            for (int unit = cluster; unit < num_units && ok; unit += clusters, ++i) {
+                const int kb0 = (unit / num_tiles) * kb_per_split;
+                const int nkb = min(k_blocks, kb0 + kb_per_split) - kb0;
                 const int buf = i & 1;
                 const uint32_t aph = (uint32_t)(i >> 1) & 1;
                 if (i >= 2) ok = mbar_wait(acc_empty + buf, aph ^ 1, abort_flag);   // both blocks' epilogues have read this buffer's last tile
                 if (!ok) break;
                 fence_after_sync();
                 const uint32_t acc = tmem_base + (uint32_t)buf * BN;
-                for (int kb = 0; kb < k_blocks; ++kb, ++g) {
+                for (int kb = 0; kb < nkb; ++kb, ++g) {
                     const int s = (int)(g % PAIR_STAGES);
                     const uint32_t phase = (uint32_t)(g / PAIR_STAGES) & 1;
                     ok = mbar_wait(full_bar + s, phase, abort_flag);
@@ -829,7 +838,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
         pdl_wait();   // the output buffer may still be in use by a kernel ahead in the stream
         int i = 0;
         bool ok = true;
-        for (int tile = cluster; tile < num_tiles && ok; tile += clusters, ++i) {
+        for (int unit = cluster; unit < num_units && ok; unit += clusters, ++i) {
+            const int tile = unit % num_tiles;
+            TC* unit_out = out + (size_t)(unit / num_tiles) * split_stride;
             const int buf = i & 1;
             const uint32_t aph = (uint32_t)(i >> 1) & 1;
             const int x0 = (tile % x_tiles) * (2 * BM) + (int)rank * BM, y0 = (tile / x_tiles) * BN;
@@ -842,7 +853,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
                 uint32_t r[32];
                 tmem_load<32>(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c), r);
                 tmem_wait_ld();
-                store_chunk_normal<TC, EPI>(out, ld, x, y0 + c, x_rows, y_rows, r);
+                store_chunk_normal<TC, EPI>(unit_out, ld, x, y0 + c, x_rows, y_rows, r);
             }
             fence_before_sync();
             if (rank == 0) mbar_arrive(acc_empty + buf);
@@ -891,6 +902,19 @@ static int make_map(CUtensorMap* map, const void* ptr, long long rows, long long
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) SPY_FAIL("gemm_tcgen05: cuTensorMapEncodeTiled failed with code %d (rows %lld, K %lld, ld %lld)", (int)r, rows, K, ld);
+    return 0;
+}
+
+// The partial products [splits][M][N] of the scratch summed in order into C.
+static int reduce_splits(const float* scratch, void* C, int c_dtype, long long ldc, int M, int N, int splits, cudaStream_t stream)
+{
+    const long long elems = (long long)M * N;
+    if (ldc != N) SPY_FAIL("gemm_tcgen05: split-K needs a contiguous output (ldc %lld, N %d)", ldc, N);
+    long long blocks = (elems + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (c_dtype == SPY_F32) spy_launch(splitk_reduce_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, scratch, (float*)C, elems, splits);
+    else spy_launch(splitk_reduce_kernel<bf16>, dim3((int)blocks), dim3(256), 0, stream, scratch, (bf16*)C, elems, splits);
+    SPY_CHECK_LAUNCH("gemm_tcgen05 split-K reduce");
     return 0;
 }
 
@@ -946,10 +970,25 @@ struct Plan {
     int splits, tile_rows;
 };
 
+constexpr int PAIR_MIN_TILES = 37;   // whole 256 x 256 tiles occupy at least half of the clusters from here on
+
 Plan make_plan(int M, int N, int K, bool may_split)
 {
     const int k_blocks = (K + BK - 1) / BK;
     Plan best = {1, BM};
+    if (M >= 512 && may_split && pair_kernel_enabled()) {
+        // 512 tokens or so on pairs of blocks: with too few 256 x 256 tiles for the clusters (o and down at the 8B
+        // shape: 32), K is cut into two to four ranges, so that tiles x ranges occupy most of the 74 clusters; the
+        // partial tiles are summed by the caller or by the reduce kernel.  At least 16 K blocks a range.
+        const long long tiles = (long long)((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
+        if (tiles >= 8 && tiles < PAIR_MIN_TILES) {
+            int s = (int)(74 / tiles);
+            if (s > 4) s = 4;
+            while (s > 1 && (k_blocks / s < 16 || (k_blocks + (k_blocks + s - 1) / s - 1) / ((k_blocks + s - 1) / s) != s)) --s;
+            best.splits = s;
+        }
+        return best;
+    }
     if (M > 256) return best;   // many tokens: the persistent kernels share the work out themselves (stream-K)
     const int slots = 296 / ((M + 63) / 64 > 0 ? (M + 63) / 64 : 1);   // 65 to 256 tokens: two to four token tiles share every weight tile
     if ((N + BM - 1) / BM >= slots) return best;   // more 128-row tiles than slots: they spread evenly as they are
@@ -1032,7 +1071,7 @@ extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, 
     const bool f32_out = splits > 1 || c_dtype == SPY_F32;
     // pairs need enough 256 x 256 tiles to occupy at least half of the clusters; smaller products go to single
     // blocks, which share the K blocks of their 128 x 256 tiles out over all SMs
-    if (!swap && splits == 1 && M >= 512 && (long long)((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256) >= 37 && pair_kernel_enabled()) {
+    if (!swap && M >= 512 && (splits > 1 || (long long)((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256) >= PAIR_MIN_TILES) && pair_kernel_enabled()) {
         // many tokens, one pass over K, at least two 256-row tiles: pairs of blocks on 256 x 256 tiles
         CUtensorMap my_half;
         if (make_map(&my_half, W, N, K, ldw, BM)) return 1;
@@ -1063,16 +1102,28 @@ extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, 
             if (active <= 0) SPY_FAIL("gemm_tcgen05: no cluster of two blocks fits the device");
             clusters_max = active < sms / 2 ? active : sms / 2;
         }
-        const int clusters = (int)(num_tiles < clusters_max ? num_tiles : clusters_max);
+        const long long num_units = num_tiles * splits;
+        const int clusters = (int)(num_units < clusters_max ? num_units : clusters_max);
+        const int kb_per_split = (k_blocks + splits - 1) / splits;
+        if (splits > 1) {
+            // ranges of K: 32-bit partial tiles into the scratch, [range][M][N]
+            spy_launch_cluster(gemm_tcgen05_pair_kernel<float, 0>, dim3(2 * clusters), dim3(NUM_THREADS), PAIR_SMEM, stream, 2u, mx, my_half, (float*)scratch,
+                               (long long)N, M, N, k_blocks, x_tiles, (int)num_tiles, splits, kb_per_split, split_stride, status);
+            SPY_CHECK_LAUNCH("gemm_tcgen05 (pairs, K ranges)");
+            if (!defer_reduce) {
+                if (int rc = reduce_splits(scratch, C, c_dtype, ldc, M, N, splits, stream)) return rc;
+            }
+            return 0;
+        }
         if (epilogue == 1)
             spy_launch_cluster(gemm_tcgen05_pair_kernel<bf16, 1>, dim3(2 * clusters), dim3(NUM_THREADS), PAIR_SMEM, stream, 2u, mx, my_half, (bf16*)C, ldc,
-                               M, N, k_blocks, x_tiles, (int)num_tiles, status);
+                               M, N, k_blocks, x_tiles, (int)num_tiles, 1, k_blocks, 0LL, status);
         else if (c_dtype == SPY_F32)
             spy_launch_cluster(gemm_tcgen05_pair_kernel<float, 0>, dim3(2 * clusters), dim3(NUM_THREADS), PAIR_SMEM, stream, 2u, mx, my_half, (float*)C, ldc,
-                               M, N, k_blocks, x_tiles, (int)num_tiles, status);
+                               M, N, k_blocks, x_tiles, (int)num_tiles, 1, k_blocks, 0LL, status);
         else
             spy_launch_cluster(gemm_tcgen05_pair_kernel<bf16, 0>, dim3(2 * clusters), dim3(NUM_THREADS), PAIR_SMEM, stream, 2u, mx, my_half, (bf16*)C, ldc,
-                               M, N, k_blocks, x_tiles, (int)num_tiles, status);
+                               M, N, k_blocks, x_tiles, (int)num_tiles, 1, k_blocks, 0LL, status);
         SPY_CHECK_LAUNCH("gemm_tcgen05 (pairs)");
         return 0;
     }
@@ -1139,15 +1190,7 @@ extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, 
     else SPY_LAUNCH(64);
 #undef SPY_LAUNCH
     if (rc) return rc;
-    if (splits > 1 && !defer_reduce) {
-        const long long elems = (long long)M * N;
-        if (ldc != N) SPY_FAIL("gemm_tcgen05: split-K needs a contiguous output (ldc %lld, N %d)", ldc, N);
-        long long blocks = (elems + 255) / 256;
-        if (blocks > 148 * 8) blocks = 148 * 8;
-        if (c_dtype == SPY_F32) spy_launch(splitk_reduce_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, (const float*)scratch, (float*)C, elems, splits);
-        else spy_launch(splitk_reduce_kernel<bf16>, dim3((int)blocks), dim3(256), 0, stream, (const float*)scratch, (bf16*)C, elems, splits);
-        SPY_CHECK_LAUNCH("gemm_tcgen05 split-K reduce");
-    }
+    if (splits > 1 && !defer_reduce) return reduce_splits(scratch, C, c_dtype, ldc, M, N, splits, stream);
     return 0;
 }
 

@@ -302,7 +302,7 @@ def test_sampling_top_k_draws_only_among_the_largest():
 
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("M,N,K", [(1, 128, 64), (5, 200, 96), (16, 4096, 4096), (17, 1000, 520), (33, 136, 72), (64, 6144, 512),
-                                   (65, 300, 136), (128, 256, 64), (100, 4096, 4096), (128, 6144, 4096), (90, 1187, 1032), (129, 1187, 1032), (300, 512, 4096), (1000, 24, 200), (2048, 1024, 12288),
+                                   (65, 300, 136), (128, 256, 64), (100, 4096, 4096), (128, 6144, 4096), (90, 1187, 1032), (129, 1187, 1032), (300, 512, 4096), (1000, 24, 200), (2048, 1024, 12288), (512, 4096, 4096), (600, 3000, 4096),
                                    (2048, 4096, 512), (1500, 3000, 264), (4100, 2600, 72)])
 def test_gemm_tcgen05(out_dtype, M, N, K):
     """Tensor-core product at sizes that exercise every tile class (16/32/64 tokens swapped,
@@ -466,9 +466,12 @@ def test_gemm_tcgen05_shares_k_blocks_evenly(M, N, K, epilogue, monkeypatch):
     torch.testing.assert_close(outs[0], ref, **tol)
 
 
-@pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (24, 1024, 2048), (64, 384, 12288), (100, 4096, 4096), (128, 1024, 12288)])
+@pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (24, 1024, 2048), (64, 384, 12288), (100, 4096, 4096), (128, 1024, 12288),
+                                   (512, 4096, 4096), (600, 3000, 4096), (700, 1500, 12288)])
 def test_gemm_tcgen05_deferred_reduction(M, N, K):
-    """With defer=True a split-K product hands back its partial products; their sum is the product."""
+    """With defer=True a split-K product hands back its partial products; their sum is the product.  The last three
+    are 512 tokens and more with too few 256 x 256 tiles for the pairs of blocks: K is cut into two to four ranges
+    (32 tiles x 2, 36 x 2 with tails in both directions, 18 x 4)."""
     from spyinfer_b200 import kernels
     a = torch.randn(M, K, device=DEV).to(torch.bfloat16)
     w = (torch.randn(N, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
