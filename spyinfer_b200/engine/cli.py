@@ -7,7 +7,7 @@ ids, streamed as they are generated.  Lines of one conversation are appended to 
 ``/new`` starts a fresh one.
 
     spyinfer -m /path/to/model [-b cuda] [--dtype bfloat16|float32] [--max-new-tokens N]
-             [--temperature X] [--top-k K] [--seed N] [--prompt-tokens 1,2,3] [--stats]
+             [--temperature X] [--top-k K] [--seed N] [--prompt-tokens 1,2,3 | --prompt-len N] [--stats]
     spyinfer --random CONFIG.json --seed 7 ...        (random weights instead of a checkpoint)
 """
 from __future__ import annotations
@@ -31,6 +31,7 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--seed", type=int, default=0, help="seed of random weights and of temperature sampling")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "bf16", "float32", "fp32"])
     ap.add_argument("--prompt-tokens", help="run this one prompt (comma-separated ids) and exit")
+    ap.add_argument("--prompt-len", type=int, default=None, help="run one prompt of this many seeded random token ids and exit")
     ap.add_argument("--max-new-tokens", type=int, default=64)
     ap.add_argument("--temperature", type=float, default=0.0)
     ap.add_argument("--top-k", type=int, default=0, help="with a temperature: draw among the k most likely tokens only (0: all)")
@@ -39,8 +40,9 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--max-num-seqs", type=int, default=None)
     ap.add_argument("--chunk-size", type=int, default=None, help="most prompt tokens of one request in a step")
     ap.add_argument("--max-model-len", type=int, default=None)
-    ap.add_argument("--kvcache-block-size", type=int, default=None)
-    ap.add_argument("--num-kvcache-blocks", type=int, default=None)
+    ap.add_argument("--kvcache-block-size", "--page-size", dest="kvcache_block_size", type=int, default=None, help="tokens a cache page holds")
+    ap.add_argument("--num-kvcache-blocks", "--num-pages", dest="num_kvcache_blocks", type=int, default=None,
+                    help="pages of the cache pool (default: from free device memory)")
     ap.add_argument("--stats", action="store_true", help="print engine counters at the end")
     return ap
 
@@ -86,6 +88,10 @@ def main(argv=None) -> int:
 
     if args.prompt_tokens is not None:
         run(_parse_tokens(args.prompt_tokens))
+    elif args.prompt_len is not None:
+        import random
+        rng = random.Random(args.seed)
+        run([rng.randrange(engine.model.spec.vocab_size) for _ in range(max(1, args.prompt_len))])
     else:
         history = []
         while True:

@@ -215,6 +215,22 @@ class LLMEngine:
             seq.num_computed = len(seq.tokens)
         return self._sample(prev.seqs, logits)
 
+    def step_raw(self, entries: Seq[StepEntry]):
+        """One batch straight through the step function, outside the scheduler: ``entries`` are
+        ``StepEntry(request, tokens, want)`` (any hashable request name; a request lives until
+        ``release_raw``).  Returns the float32 logits at the wanted places as a NumPy array
+        ``[wanted, vocab]``, or None when nothing is wanted.  Meant for tests and for comparing
+        with other engines; requests made here are unknown to ``step()``."""
+        if self._inflight is not None:
+            raise RuntimeError("step_raw: a scheduled step is still in flight; call drain() first")
+        logits = self.runner.step(list(entries))
+        self.runner.check_status()
+        return None if logits is None else logits.float().cpu().numpy()
+
+    def release_raw(self, request) -> None:
+        """Gives back what a request of ``step_raw`` holds."""
+        self.runner.finish(request)
+
     def drain(self) -> List[Tuple[int, int, bool]]:
         """Reads the step in flight, if there is one, without launching another."""
         prev, self._inflight = self._inflight, None

@@ -142,6 +142,31 @@ def test_top_k_of_one_is_greedy_and_top_k_limits_the_draws(tiny_models):
         SamplingParams(top_k=-1)
 
 
+def test_step_raw_gives_the_plain_logits_and_leaves_the_scheduler_alone(tiny_models):
+    """``LLMEngine.step_raw``: a prompt in two portions and a decoded token, logits against the plain
+    implementation; afterwards the engine generates as if nothing had happened and every page is back."""
+    from spyinfer_b200.engine import StepEntry
+    folder, cfg, weights = tiny_models["a"]
+    engine = engine_for(folder, "float32", max_num_seqs=4, num_kvcache_blocks=32, max_num_batched_tokens=64)
+    free = engine.stats()["free_pages"]
+    toks = [3, 14, 15, 92, 65, 35, 89]
+    ref = plain_model.forward_logits(weights, cfg, toks).numpy()
+    a = engine.step_raw([StepEntry("x", toks[:4], [3])])
+    assert engine.step_raw([StepEntry("x", toks[4:6], [])]) is None
+    b = engine.step_raw([StepEntry("x", toks[6:], [0])])
+    np.testing.assert_allclose(a[0], ref[3], rtol=2e-4, atol=2e-5)
+    np.testing.assert_allclose(b[0], ref[6], rtol=2e-4, atol=2e-5)
+    engine.release_raw("x")
+    assert engine.stats()["free_pages"] == free
+    out = engine.generate([toks[:3]], SamplingParamsFor(4))[0]
+    check_greedy(weights, cfg, toks[:3], out, "float32")
+
+
+def SamplingParamsFor(n):
+    from spyinfer_b200 import SamplingParams
+    return SamplingParams(max_new_tokens=n, ignore_eos=True)
+
+
 def test_command_line_generates(tiny_models):
     import os, subprocess, sys
     folder, cfg, weights = tiny_models["a"]
@@ -155,6 +180,12 @@ def test_command_line_generates(tiny_models):
     assert len(tokens) == 5
     check_greedy(weights, cfg, [5, 6, 7], tokens, "float32")
     assert "steps" in lines[-1]
+    # a seeded random prompt of a given length, pages named by the short options
+    cmd = [sys.executable, os.path.join(root, "bin", "spyinfer"), "-m", folder, "--dtype", "float32", "--prompt-len", "9", "--seed", "3",
+           "--max-new-tokens", "3", "--ignore-eos", "--max-model-len", "64", "--page-size", "4", "--num-pages", "16"]
+    proc = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert len([int(t) for t in proc.stdout.strip().splitlines()[1].split()]) == 3
     bad = subprocess.run([sys.executable, os.path.join(root, "bin", "spyinfer"), "-m", folder, "-b", "cpu"], capture_output=True, text=True)
     assert bad.returncode == 1 and "Invalid backend type" in bad.stderr
 
