@@ -158,10 +158,11 @@ def test_tight_pool_and_small_budget_always_make_progress():
     assert a.num_generated == 2 and b.num_generated == 2 and cache.num_free_pages() == 4
 
 
-@pytest.mark.parametrize("seed", range(4))
+@pytest.mark.parametrize("seed", range(8))
 def test_random_workloads_finish_with_everything_given_back(seed):
     rng = random.Random(seed)
-    sched, cache = make(num_pages=12, page_size=4, budget=rng.choice([3, 8, 32]), max_num_seqs=3, max_model_len=40)
+    chunk = rng.choice([None, None, 2, 5])
+    sched, cache = make(num_pages=12, page_size=4, budget=rng.choice([3, 8, 32]), max_num_seqs=3, max_model_len=40, chunk_size=chunk)
     seqs = []
     for i in range(12):
         s = seq(i, rng.randint(1, 20), max_new=rng.randint(1, 12))
@@ -174,6 +175,7 @@ def test_random_workloads_finish_with_everything_given_back(seed):
             sched.add_sequence(pending.pop(0))
         p = sched.schedule()
         assert sum(x.num_tokens for x in p) <= sched.config.max_num_batched_tokens
+        assert chunk is None or all(x.num_tokens <= chunk for x in p)
         assert len({x.seq.id for x in p}) == len(p) and len(sched.running) <= 3
         run_step(sched, cache, p)
         steps += 1
