@@ -25,8 +25,9 @@ on their content), so no prefill is timed.  One JSON line is printed:
   tokens that the reference workload "prompts of 512, 256 generated tokens" averages;
 * ``clocks``: SM clocks and throttle reasons sampled with nvidia-smi during the timed region.
 
-Peaks come from MEASURED_PEAKS.json beside this file when it exists, else 6.65 TB/s and
-1.59 PFLOP/s.  ``--gpus N`` with N > 1 prints one line saying that this engine is
+Peaks come from MEASURED_PEAKS.json beside this file when it exists (the copy bandwidth, and for the
+prefill, a long step under the power cap, the sustained bf16 rate if the file has one), else 6.65 TB/s
+and 1.59 PFLOP/s.  ``--gpus N`` with N > 1 prints one line saying that this engine is
 single-GPU and exits with 2.  ``--impl reference`` prints why the reference cannot run here.
 """
 from __future__ import annotations
@@ -58,6 +59,10 @@ REFERENCE_UNAVAILABLE = ("spymaster2h/spyinfer is a C++/xmake project without a 
 
 
 def peaks():
+    """Copy bandwidth (GB/s) and bf16 product rate (TFLOP/s) the fractions are taken against.  From
+    MEASURED_PEAKS.json when it exists: ``hbm_gbs`` and, for the prefill (a step of tens of
+    milliseconds under the power cap), ``bf16_tflops_sustained`` if the file has it, else the burst
+    figure ``bf16_tflops``.  Else 6.65 TB/s and 1.59 PFLOP/s."""
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     hbm, flops, src = 6650.0, 1590.0, "fallback"
     if os.path.isfile(path):
@@ -65,9 +70,11 @@ def peaks():
             with open(path) as f:
                 d = json.load(f)
             hbm = float(d.get("hbm_gbs", hbm))
-            flops = float(d.get("bf16_tflops", flops))
-            src = "measured"
-        except (ValueError, OSError):
+            if d.get("bf16_tflops_sustained"):
+                flops, src = float(d["bf16_tflops_sustained"]), "measured (bf16 sustained)"
+            else:
+                flops, src = float(d.get("bf16_tflops", flops)), "measured"
+        except (ValueError, OSError, TypeError):
             pass
     return hbm, flops, src
 
@@ -325,7 +332,7 @@ def main() -> int:
         runner.check_status()
         flops = 2.0 * tokens * layers * layer_params + 2.0 * V * H + layers * 4.0 * nh * hd * tokens * (tokens + 1) / 2
         return {"value": round(tokens / (best / 1e3), 1), "tokens": tokens, "ms": round(best, 3),
-                "frac": round(flops / (best / 1e3) / (bf16_tflops * 1e12), 4)}
+                "frac": round(flops / (best / 1e3) / (bf16_tflops * 1e12), 4), "peak_tflops": bf16_tflops}
 
     with ClockSampler() as clocks:
         value, ms_per_step, launches = decode_device(args.batch, ctx, args.steps, warmup)
