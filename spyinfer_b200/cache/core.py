@@ -65,7 +65,7 @@ def lib() -> ctypes.CDLL:
         L.spy_cache_gather.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, c_i64_p, ctypes.c_int, c_i32_p, ctypes.c_int]
         L.spy_cache_fill_batch.argtypes = [ctypes.c_void_p, ctypes.c_int, c_i64_p, c_i32_p, c_i32_p, c_i32_p, c_i32_p, ctypes.c_int] + [c_i32_p] * 7 + [c_int_p] * 3
         L.spy_sched_step.argtypes = ([ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, c_i64_p, c_i32_p, c_i32_p, ctypes.c_int, c_i64_p, c_i32_p]
-                                     + [c_i64_p, c_i32_p, c_i32_p, c_i32_p, c_int_p, c_i64_p, c_int_p, c_int_p])
+                                     + [c_i64_p, c_i32_p, c_i32_p, c_i32_p, c_int_p, c_i64_p, c_int_p, c_int_p, c_i64_p])
         _lib = L
     return _lib
 

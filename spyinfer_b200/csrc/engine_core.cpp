@@ -360,19 +360,45 @@ int spy_cache_check(void* h)
 // Requests that are not live yet get a slot.  Pages for the new tokens are reserved.  Writes
 //   token_ids[T], positions[T], seq_of_token[T], q_start[n + 1], ctx_len[n], state_slot[n],
 //   logit_rows[R]; *tokens_out = T, *rows_out = R, *max_ctx = the longest context.
-// On an error nothing is half-done beyond slots and pages of the entries before the failing one.
+// All or nothing: every entry is checked first (each request once, token ids, wanted places,
+// max_model_len, and the slots and pages that ALL entries together need against what is free), so an
+// error leaves no slot taken and no page reserved.
 int spy_cache_fill_batch(void* h, int n, const int64_t* rids, const int32_t* counts, const int32_t* tokens, const int32_t* want_start,
                          const int32_t* want, int vocab_size, int32_t* token_ids, int32_t* positions, int32_t* seq_of_token, int32_t* q_start,
                          int32_t* ctx_len, int32_t* state_slot, int32_t* logit_rows, int* tokens_out, int* rows_out, int* max_ctx)
 {
     Cache* c = static_cast<Cache*>(h);
     int T = 0, R = 0, longest = 0;
+    {   // the checks, before anything is taken
+        std::unordered_set<int64_t> seen;
+        long long pages = 0;
+        int slots = 0, t0 = 0;
+        for (int i = 0; i < n; ++i) {
+            if (!seen.insert(rids[i]).second) return fail(BAD_VALUE, "entry %d: its request appears twice in one step", i);
+            const int cnt = counts[i];
+            if (cnt <= 0) return fail(BAD_VALUE, "entry %d: its request brings no tokens to this step", i);
+            const Request* r = c->find(rids[i]);
+            const Request fresh{-1, 0, 0};
+            if (!r) ++slots;
+            const Request& q = r ? *r : fresh;
+            if (q.length + cnt > c->max_model_len)
+                return fail(BAD_VALUE, "entry %d: request %lld: %d tokens exceed max_model_len %d", i, (long long)rids[i], q.length + cnt, c->max_model_len);
+            pages += c->pages_needed(q, q.length + cnt);
+            for (int k = 0; k < cnt; ++k) {
+                const int t = tokens[t0 + k];
+                if (t < 0 || t >= vocab_size) return fail(BAD_VALUE, "entry %d: token id %d is outside the vocabulary of %d", i, t, vocab_size);
+            }
+            for (int w = want_start[i]; w < want_start[i + 1]; ++w)
+                if (want[w] < 0 || want[w] >= cnt) return fail(BAD_VALUE, "entry %d: wanted place %d is not among its %d tokens", i, want[w], cnt);
+            t0 += cnt;
+        }
+        if (slots > (int)c->free_slots.size()) return fail(NO_SLOT, "the step brings %d new requests, %d of %d request slots are free", slots, (int)c->free_slots.size(), c->max_num_seqs);
+        for (const Group& g : c->groups)
+            if (g.pool.num_free() < pages) return fail(OUT_OF_PAGES, "Out of memory: No free blocks available.");
+    }
     q_start[0] = 0;
-    std::unordered_set<int64_t> seen;
     for (int i = 0; i < n; ++i) {
-        if (!seen.insert(rids[i]).second) return fail(BAD_VALUE, "entry %d: its request appears twice in one step", i);
         const int cnt = counts[i];
-        if (cnt <= 0) return fail(BAD_VALUE, "entry %d: its request brings no tokens to this step", i);
         Request* r = c->find(rids[i]);
         if (!r) {
             if (int rc = c->add(rids[i], nullptr)) return rc;
@@ -381,16 +407,11 @@ int spy_cache_fill_batch(void* h, int n, const int64_t* rids, const int32_t* cou
         const int start = r->length;
         if (int rc = c->reserve(rids[i], *r, start + cnt)) return rc;
         for (int k = 0; k < cnt; ++k) {
-            const int t = tokens[T + k];
-            if (t < 0 || t >= vocab_size) return fail(BAD_VALUE, "entry %d: token id %d is outside the vocabulary of %d", i, t, vocab_size);
-            token_ids[T + k] = t;
+            token_ids[T + k] = tokens[T + k];
             positions[T + k] = start + k;
             seq_of_token[T + k] = i;
         }
-        for (int w = want_start[i]; w < want_start[i + 1]; ++w) {
-            if (want[w] < 0 || want[w] >= cnt) return fail(BAD_VALUE, "entry %d: wanted place %d is not among its %d tokens", i, want[w], cnt);
-            logit_rows[R++] = T + want[w];
-        }
+        for (int w = want_start[i]; w < want_start[i + 1]; ++w) logit_rows[R++] = T + want[w];
         T += cnt;
         q_start[i + 1] = T;
         ctx_len[i] = start + cnt;
@@ -419,15 +440,20 @@ int spy_cache_fill_batch(void* h, int n, const int64_t* rids, const int32_t* cou
 //      max_num_seqs requests are live, budget is left and pages for the first portion are free; the
 //      first that does not fit stops admission (as in the reference, scheduler.cpp:20-43);
 //   and when live requests exist but none can run (prompts in progress hold every page), the request
-//   admitted last is preempted and the step is decided again.
+//   admitted last is preempted and the step is decided again.  A request is preempted only in favour
+//   of an older one: when the ONLY running request cannot go on, no preemption would ever give it the
+//   page it needs (it holds all there is to hold), so it is reported as stuck instead and the caller
+//   ends it; recomputing it would come to the same place for ever.
 // The reference has no budget, no portions and no preemption (scheduler.cpp:59-87).
 // Out: portions (request, start, count, samples) in the order they are to be run, the preempted
 // requests in the order of preemption, and how many waiting requests were admitted (they are the
 // first of the queue as the caller knows it, after the preempted ones have been put at its front in
 // order, each at the very front).  Pages of the portions are reserved; admitted requests hold slots.
+// *stuck is the lone running request that can never go on, or -1; nothing else has been decided then,
+// and the caller calls again after ending it.
 int spy_sched_step(void* h, int budget, int chunk, int max_num_seqs, int n_run, const int64_t* run_ids, const int32_t* run_len, const int32_t* run_done, int n_wait,
                    const int64_t* wait_ids, const int32_t* wait_len, int64_t* out_ids, int32_t* out_start, int32_t* out_count, int32_t* out_samples,
-                   int* n_out, int64_t* preempted, int* n_preempted, int* n_admitted)
+                   int* n_out, int64_t* preempted, int* n_preempted, int* n_admitted, int64_t* stuck)
 {
     Cache* c = static_cast<Cache*>(h);
     struct Seq {
@@ -443,6 +469,7 @@ int spy_sched_step(void* h, int budget, int chunk, int max_num_seqs, int n_run, 
     };
     std::vector<Portion> out;
     int np = 0, admitted = 0;
+    *stuck = -1;
     const int initial_budget = budget;
     if (chunk <= 0) chunk = budget;   // no cap of its own on a portion
     auto preempt_last = [&]() -> int {
@@ -503,6 +530,10 @@ int spy_sched_step(void* h, int budget, int chunk, int max_num_seqs, int n_run, 
             ++admitted;
         }
         if (!out.empty() || running.empty()) break;
+        if (running.size() == 1) {   // nobody is left whose pages could help it
+            *stuck = running[0].id;
+            break;
+        }
         // live requests, yet none can run: the request admitted last gives its pages back and is recomputed later.
         // A request admitted in this very round cannot be the one (it would have got a portion).
         if (int rc = preempt_last()) return rc;

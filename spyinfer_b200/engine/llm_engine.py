@@ -124,9 +124,11 @@ class LLMEngine:
             self.scheduler.finish(seq, "removed")
 
     # ---- one step ------------------------------------------------------------------------------
-    def step(self) -> List[Tuple[int, int, bool]]:
+    def step(self) -> List[Tuple[int, Optional[int], bool]]:
         """Schedules and runs one batch.  Returns ``(request id, new token, finished)`` for the
-        tokens that became known in this call.
+        tokens that became known in this call.  A request that the scheduler had to end because it
+        could not go on even alone (``finish_reason`` ``"out_of_pages"``) appears once as
+        ``(request id, None, True)``.
 
         With ``lookahead_decode`` (the default) a step in which every request decodes is launched
         and left in flight: its tokens are read, and returned, by the next call, AFTER that call has
@@ -146,6 +148,10 @@ class LLMEngine:
                 self._inflight = ahead
                 return results
         portions = self.scheduler.schedule()
+        for seq in self.scheduler.ended_without_token:
+            del seq.tokens[len(_known(seq.tokens)):]
+            results.append((seq.id, None, True))
+        self.scheduler.ended_without_token.clear()
         if not portions:
             return results
         entries = [StepEntry(p.seq.id, p.seq.tokens[p.start:p.start + p.num_tokens], [p.num_tokens - 1] if p.samples else [])
@@ -180,6 +186,8 @@ class LLMEngine:
             return "max_new_tokens"
         if place + 1 >= self.config.max_model_len:
             return "max_model_len"
+        if place + 1 > self.scheduler.most_tokens_alone():
+            return "out_of_pages"                          # the pool could not hold the token's keys even if the request were alone
         return None
 
     def _absorb(self, flight: "_InFlight", tokens: List[int]) -> List[Tuple[int, int, bool]]:

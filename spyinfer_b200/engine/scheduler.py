@@ -17,8 +17,13 @@ Every step:
 The reference's scheduler (spymaster2h/spyinfer src/engine/scheduler.cpp:17-122) admits by
 block count, always runs a prompt whole (no budget, no portions: :59-70), and when a
 decoding sequence finds no block it skips it with half-written batch arrays (:77-87); it has
-no preemption.  A request that could never finish in the pool even alone is refused at
-submission here.
+no preemption.  A request whose stated length (prompt plus ``max_new_tokens``) could never
+be held by the pool even alone is refused at submission here.  A request without
+``max_new_tokens`` may grow to ``max_model_len``; when the pool is smaller than that, the
+request ends with the reason ``"out_of_pages"`` at the last token the pool can hold
+(``Scheduler.most_tokens_alone``), as it would end at ``max_model_len``.  And whatever the
+cause, the only running request is never preempted: if it cannot go on, nothing would change
+by recomputing it, so it is ended with that reason (``ended_without_token``).
 """
 from __future__ import annotations
 
@@ -52,6 +57,11 @@ class Scheduler:
         self.waiting: Deque[Sequence] = deque()
         self.running: List[Sequence] = []
         self.num_preemptions = 0
+        self.ended_without_token: List[Sequence] = []   # requests that schedule() had to end; the caller reports and clears them
+
+    def most_tokens_alone(self) -> int:
+        """The most tokens of one request that the pool can hold when the request is alone."""
+        return self.cache.num_pages * self.cache.page_size
 
     def check_fits(self, seq: Sequence, max_new_tokens: int) -> None:
         """Refuses a request that could never run to its end even alone in the pool."""
@@ -85,6 +95,14 @@ class Scheduler:
         ``spy_sched_step`` of the C++ engine core, which sees the two queues as arrays of
         (request, tokens so far, tokens already run) and works on the cache's bookkeeping
         directly; what it decided is applied to the request records and the queues here."""
+        while True:
+            portions, stuck = self._decide()
+            if stuck is None:
+                return portions
+            self.ended_without_token.append(stuck)
+            self.finish(stuck, "out_of_pages")
+
+    def _decide(self):
         lib, cache = core.lib(), self.cache
         run, wait = list(self.running), list(self.waiting)
         n_run, n_wait = len(run), len(wait)
@@ -96,11 +114,11 @@ class Scheduler:
         cap = n_run + n_wait + 1
         out_ids, preempted = np.empty(cap, dtype=np.int64), np.empty(cap, dtype=np.int64)
         out_start, out_count, out_samples = (np.empty(cap, dtype=np.int32) for _ in range(3))
-        n_out, n_pre, n_adm = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+        n_out, n_pre, n_adm, stuck = ctypes.c_int(), ctypes.c_int(), ctypes.c_int(), ctypes.c_int64(-1)
         core.check(lib.spy_sched_step(cache._h, int(self.config.max_num_batched_tokens), int(self.config.chunk_size or 0), int(self.config.max_num_seqs), n_run, core.i64(run_ids),
                                       core.i32(run_len), core.i32(run_done), n_wait, core.i64(wait_ids), core.i32(wait_len), core.i64(out_ids),
                                       core.i32(out_start), core.i32(out_count), core.i32(out_samples), ctypes.byref(n_out), core.i64(preempted),
-                                      ctypes.byref(n_pre), ctypes.byref(n_adm)))
+                                      ctypes.byref(n_pre), ctypes.byref(n_adm), ctypes.byref(stuck)))
         by_handle = {cache.handle(q.id): q for q in run + wait}
         for h in preempted[:n_pre.value]:          # in the order of preemption, each to the very front of the queue
             seq = by_handle[int(h)]
@@ -115,4 +133,5 @@ class Scheduler:
             seq.status = SequenceStatus.RUNNING
             self.running.append(seq)
             cache.zero_state(cache.slot(seq.id))
-        return [ScheduledPortion(by_handle[int(out_ids[i])], int(out_start[i]), int(out_count[i]), bool(out_samples[i])) for i in range(n_out.value)]
+        portions = [ScheduledPortion(by_handle[int(out_ids[i])], int(out_start[i]), int(out_count[i]), bool(out_samples[i])) for i in range(n_out.value)]
+        return portions, (by_handle[stuck.value] if stuck.value >= 0 else None)

@@ -173,3 +173,26 @@ def test_a_steps_batch_arrays_are_assembled_with_slots_pages_and_checks():
     with pytest.raises(OutOfPages):
         m.assemble(["big"], [list(range(9)) * 5], [[]], vocab_size=10)                  # 45 tokens: twelve pages, ten are free
     m.check_invariants()
+
+
+def test_a_step_that_cannot_be_assembled_takes_nothing():
+    """All or nothing: when a later entry of the step fails (no page, no slot, a bad token, too long),
+    the entries before it have taken no slot and no page, so nothing is left reserved for a step that
+    never ran."""
+    m = manager(page_size=4, num_pages=6, max_num_seqs=3)
+    m.add_request("old")
+    m.reserve("old", 8)
+    m.commit("old", 8)                                       # two pages held, four free, two slots free
+    free_pages, free_slots = m.num_free_pages(), m.num_free_slots()
+    bad = [(["a", "old", "b"], [[1] * 8, [2], [3] * 8], OutOfPages),                # 2 + 1 + 2 pages, four are free
+           (["a", "b", "c"], [[1], [2], [3]], NoFreeSlot),                          # three new requests, two slots
+           (["a", "old"], [[1, 2, 3], [10]], ValueError),                           # token outside the vocabulary
+           (["a", "old"], [[1, 2, 3], [1] * 57], ValueError)]                       # beyond max_model_len (64)
+    for rids, toks, error in bad:
+        with pytest.raises(error):
+            m.assemble(rids, toks, [[] for _ in rids], vocab_size=10)
+        assert m.num_free_pages() == free_pages and m.num_free_slots() == free_slots
+        assert m.live_requests() == ["old"] and m.pages_needed("old", 9) == 1
+        m.check_invariants()
+    m.assemble(["a", "old"], [[1] * 8, [2]], [[], [0]], vocab_size=10)              # 2 + 1 pages: fits
+    assert m.num_free_pages() == free_pages - 3

@@ -105,6 +105,32 @@ def test_eos_and_max_model_len_finish_requests(tiny_models):
         engine.add_request([cfg["vocab_size"]])      # outside the vocabulary
 
 
+@pytest.mark.parametrize("lookahead", [True, False])
+def test_requests_without_a_token_limit_end_where_the_pool_ends(lookahead, tiny_models):
+    """The default ``SamplingParams()`` in a pool (3 pages of 16) smaller than ``max_model_len`` (512):
+    the requests run to the pool's last token and end with the reason "out_of_pages"; the second one
+    is preempted once for the first and recomputed.  ``generate`` returns, and the tokens are those of
+    a roomy engine."""
+    from spyinfer_b200 import SamplingParams
+    folder, cfg, weights = tiny_models["a"]
+    prompts = [[3, 9, 27, 81, 5, 6, 7], [2, 4, 8, 16]]
+    roomy = engine_for(folder, "float32")
+    want = roomy.generate(prompts, SamplingParams(max_new_tokens=48, ignore_eos=True))
+    del roomy
+    engine = engine_for(folder, "float32", num_kvcache_blocks=3, lookahead_decode=lookahead)
+    got = engine.generate(prompts, SamplingParams(ignore_eos=True))
+    assert [len(p) + len(o) for p, o in zip(prompts, got)] == [49, 49]          # 48 tokens in the cache and the one sampled from them
+    assert got == [w[:len(g)] for w, g in zip(want, got)]
+    assert engine.scheduler.num_preemptions == 1
+    assert engine.runner.cache.min_free_pages() == 3 and engine.runner.cache.num_free_slots() == 4
+    rid = engine.add_request(prompts[0])
+    seen = []
+    while engine.has_unfinished_requests():
+        seen += engine.step()
+    seen += engine.drain()
+    assert engine.finish_reason(rid) == "out_of_pages" and [t for _, t, _ in seen] == got[0] and seen[-1][2]
+
+
 def test_temperature_sampling_is_seeded_and_follows_the_distribution(tiny_models):
     from spyinfer_b200 import SamplingParams
     folder, cfg, weights = tiny_models["a"]

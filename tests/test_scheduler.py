@@ -23,8 +23,10 @@ def seq(i, n, max_new=8):
     return Sequence(i, list(range(n)), n, SamplingParams(max_new_tokens=max_new))
 
 
-def run_step(sched, cache, portions, next_token=7):
-    """What the engine does with a step's portions: runs them, commits, appends samples, finishes."""
+def run_step(sched, cache, portions, next_token=7, cap_at_pool=True):
+    """What the engine does with a step's portions: runs them, commits, appends samples, finishes
+    (by count, by ``max_model_len``, and, as ``LLMEngine`` does, at the last token that the pool
+    could hold for a request alone; ``cap_at_pool=False`` leaves that to the scheduler)."""
     finished = []
     for p in portions:
         assert p.start == p.seq.num_computed == cache.length(p.seq.id)
@@ -33,8 +35,14 @@ def run_step(sched, cache, portions, next_token=7):
         assert p.samples == (p.seq.num_computed == len(p.seq))
         if p.samples:
             p.seq.tokens.append(next_token)
-            if p.seq.num_generated >= p.seq.sampling.max_new_tokens:
+            limit = p.seq.sampling.max_new_tokens
+            if limit is not None and p.seq.num_generated >= limit:
                 sched.finish(p.seq, "max_new_tokens")
+            elif len(p.seq) >= sched.config.max_model_len:
+                sched.finish(p.seq, "max_model_len")
+            elif cap_at_pool and len(p.seq) > sched.most_tokens_alone():
+                sched.finish(p.seq, "out_of_pages")
+            if p.seq.status == SequenceStatus.FINISHED:
                 finished.append(p.seq.id)
     cache.check_invariants()
     return finished
@@ -143,6 +151,46 @@ def test_a_request_that_can_never_fit_is_refused_at_submission():
         sched.check_fits(seq(0, 64), max_new_tokens=1)   # no room to generate
 
 
+@pytest.mark.parametrize("cap_at_pool", [True, False])
+def test_a_lone_request_without_a_token_limit_ends_where_the_pool_ends(cap_at_pool):
+    """4 pages of 4 tokens, ``max_model_len`` 64, no ``max_new_tokens``: the request may grow to 64
+    tokens, the pool holds 16.  It is admitted (it may meet its end-of-sequence token early), runs to
+    the pool's last token and ends there with the reason "out_of_pages": through the engine's own
+    check, or, without it, by the scheduler, which never preempts the only running request."""
+    sched, cache = make(num_pages=4, page_size=4, budget=64, max_model_len=64)
+    a = seq(0, 10, max_new=None)
+    sched.check_fits(a, 1)
+    sched.add_sequence(a)
+    steps = 0
+    while sched.has_unfinished():
+        p = sched.schedule()
+        run_step(sched, cache, p, cap_at_pool=cap_at_pool)
+        steps += 1
+        assert steps <= 8, "one prompt step and six or seven decode steps, then the end"
+    assert a.status == SequenceStatus.FINISHED and a.finish_reason == "out_of_pages"
+    assert len(a) == 17 and a.num_preemptions == 0 and sched.num_preemptions == 0
+    assert (sched.ended_without_token == [a]) == (not cap_at_pool)
+    assert cache.num_free_pages() == 4 and cache.num_free_slots() == 4
+
+
+def test_an_unlimited_request_gives_way_then_ends_and_the_preempted_one_comes_back():
+    """Two requests without a token limit in a pool that holds neither to ``max_model_len``: the newer
+    one is preempted once for the older, the older ends at the pool's end, the newer is recomputed,
+    runs on alone and ends there too.  No request is preempted in favour of nobody."""
+    sched, cache = make(num_pages=4, page_size=4, budget=64, max_model_len=64)
+    a, b = seq(0, 6, max_new=None), seq(1, 6, max_new=None)
+    sched.add_sequence(a)
+    sched.add_sequence(b)
+    steps = 0
+    while sched.has_unfinished():
+        run_step(sched, cache, sched.schedule(), cap_at_pool=False)
+        steps += 1
+        assert steps < 40
+    assert a.finish_reason == b.finish_reason == "out_of_pages" and len(a) == len(b) == 17
+    assert a.num_preemptions == 0 and b.num_preemptions == 1
+    assert cache.num_free_pages() == 4 and cache.num_free_slots() == 4
+
+
 def test_tight_pool_and_small_budget_always_make_progress():
     sched, cache = make(num_pages=4, page_size=4, budget=6, max_model_len=64)
     a, b = seq(0, 12, max_new=2), seq(1, 12, max_new=2)
@@ -165,8 +213,8 @@ def test_random_workloads_finish_with_everything_given_back(seed):
     sched, cache = make(num_pages=12, page_size=4, budget=rng.choice([3, 8, 32]), max_num_seqs=3, max_model_len=40, chunk_size=chunk)
     seqs = []
     for i in range(12):
-        s = seq(i, rng.randint(1, 20), max_new=rng.randint(1, 12))
-        sched.check_fits(s, s.sampling.max_new_tokens)
+        s = seq(i, rng.randint(1, 20), max_new=rng.choice([None, rng.randint(1, 12), rng.randint(1, 12)]))
+        sched.check_fits(s, s.sampling.max_new_tokens or 1)
         seqs.append(s)
     pending = list(seqs)
     steps = 0
@@ -180,5 +228,38 @@ def test_random_workloads_finish_with_everything_given_back(seed):
         run_step(sched, cache, p)
         steps += 1
         assert steps < 2000
-    assert all(s.status == SequenceStatus.FINISHED and s.num_generated == s.sampling.max_new_tokens for s in seqs)
+    for s in seqs:
+        assert s.status == SequenceStatus.FINISHED
+        if s.sampling.max_new_tokens is not None:
+            assert s.num_generated == s.sampling.max_new_tokens and s.finish_reason == "max_new_tokens"
+        else:
+            assert len(s) == 40 and s.finish_reason == "max_model_len"     # the pool holds 48 tokens, max_model_len is 40
     assert cache.num_free_pages() == 12 and cache.num_free_slots() == 3
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_workloads_in_a_pool_smaller_than_max_model_len(seed):
+    """As above, but the pool (24 tokens) is smaller than ``max_model_len`` (40) and a third of the
+    requests have no token limit; half of the runs leave the pool's cap to the scheduler."""
+    rng = random.Random(100 + seed)
+    sched, cache = make(num_pages=6, page_size=4, budget=rng.choice([3, 8, 32]), max_num_seqs=3, max_model_len=40, chunk_size=rng.choice([None, 5]))
+    seqs = []
+    for i in range(10):
+        s = seq(i, rng.randint(1, 14), max_new=rng.choice([None, rng.randint(1, 8), rng.randint(1, 8)]))
+        sched.check_fits(s, s.sampling.max_new_tokens or 1)
+        seqs.append(s)
+    pending = list(seqs)
+    steps = 0
+    while sched.has_unfinished() or pending:
+        while pending and rng.random() < 0.5:
+            sched.add_sequence(pending.pop(0))
+        run_step(sched, cache, sched.schedule(), cap_at_pool=seed % 2 == 0)
+        steps += 1
+        assert steps < 2000
+    for s in seqs:
+        assert s.status == SequenceStatus.FINISHED
+        if s.sampling.max_new_tokens is None:
+            assert s.finish_reason == "out_of_pages" and len(s) == 25
+        else:
+            assert s.finish_reason == "max_new_tokens" and s.num_generated == s.sampling.max_new_tokens
+    assert cache.num_free_pages() == 6 and cache.num_free_slots() == 3
