@@ -9,10 +9,17 @@ checked.  ``model_type`` and ``hidden_act``, which the reference demands and the
 activation is refused.  ``rope_theta`` may also stand inside ``rope_parameters`` (newer
 checkpoints write it there), and ``eos_token_id`` may be a list, whose first entry counts.
 
-Read beyond the reference's keys: ``use_sliding_window``, ``sliding_window`` and
-``layer_types`` (a layer of type ``"sliding_attention"`` sees the last ``sliding_window``
-keys, its own included; ``"full_attention"`` sees all).  Keys that would change the result
-and are not implemented are refused: ``rope_scaling``, ``attention_bias``.
+Read beyond the reference's keys: ``use_sliding_window``, ``sliding_window``, and which
+layers have the window: ``layer_types`` (a layer of type ``"sliding_attention"`` sees the
+last ``sliding_window`` keys, its own included; ``"full_attention"`` sees all) or, where that
+list is absent, ``max_window_layers`` (layers ``0 .. max_window_layers - 1`` see every key,
+the layers from ``max_window_layers`` on have the window).  ``use_sliding_window`` with
+neither is refused: it would not say which layers are meant.  Where both are given the list
+counts.  The reference reads none of these keys (every layer of its model sees all keys),
+so their meaning here is this engine's statement, pinned by its own tests only.  Keys that
+would change the result and are not implemented are refused: ``rope_scaling``,
+``attention_bias``.  A key that is not read at all and is not known to be without effect on
+the logits (``_NO_EFFECT``) is named in a warning, never dropped silently.
 
 The layer structure itself (pre-norm blocks of grouped-query attention with per-head q/k
 RMSNorm and rotate-half RoPE, SwiGLU feed-forward, tied or untied head) restates
@@ -20,11 +27,16 @@ src/models/qwen3.hpp:19-54 (tensor names) and :122-308 (order of operations).
 """
 from __future__ import annotations
 
+import warnings
 from dataclasses import asdict, dataclass, field
 from typing import Any, Dict, List, Optional
 
 from .model_config import ArchitectureConfig, ConfigError, register_architecture
 from .spec import LayerSpec, ModelSpec, PartSpec, RunEntry
+
+# keys that checkpoints carry and that do not change what a forward pass computes
+_NO_EFFECT = {"architectures", "torch_dtype", "dtype", "transformers_version", "use_cache", "attention_dropout", "initializer_range",
+              "pad_token_id", "attention_bias", "rope_scaling", "rope_parameters", "_name_or_path"}
 
 _REQUIRED_INTS = ("hidden_size", "intermediate_size", "num_hidden_layers", "num_attention_heads",
                   "num_key_value_heads", "vocab_size")
@@ -51,6 +63,7 @@ class Qwen3Config(ArchitectureConfig):
     use_sliding_window: bool = False
     sliding_window: Optional[int] = None
     layer_types: Optional[List[str]] = None
+    max_window_layers: Optional[int] = None
     extra: Dict[str, Any] = field(default_factory=dict)
 
     @classmethod
@@ -103,16 +116,25 @@ class Qwen3Config(ArchitectureConfig):
         use_window = bool(data.get("use_sliding_window", False))
         window = data.get("sliding_window")
         layer_types = data.get("layer_types")
+        first_windowed = data.get("max_window_layers")
         if use_window:
-            if not isinstance(window, int) or window <= 0:
+            if not isinstance(window, int) or isinstance(window, bool) or window <= 0:
                 raise ConfigError(f"Qwen3 config.json: use_sliding_window needs a positive sliding_window, found {window!r}")
             if layer_types is not None:
-                if len(layer_types) != data["num_hidden_layers"]:
+                if not isinstance(layer_types, list) or len(layer_types) != data["num_hidden_layers"]:
                     raise ConfigError("Qwen3 config.json: layer_types must name every layer")
                 bad = sorted(set(layer_types) - {"full_attention", "sliding_attention"})
                 if bad:
                     raise ConfigError(f"Qwen3 config.json: unknown layer_types {bad}")
-        known = {f for f in cls.__dataclass_fields__ if f != "extra"} | {"architectures", "rope_parameters"}
+            elif first_windowed is None:
+                raise ConfigError("Qwen3 config.json: use_sliding_window without layer_types or max_window_layers does not say which "
+                                  "layers have the window")
+            elif not isinstance(first_windowed, int) or isinstance(first_windowed, bool) or not 0 <= first_windowed <= data["num_hidden_layers"]:
+                raise ConfigError(f"Qwen3 config.json: max_window_layers must lie in 0..num_hidden_layers, found {first_windowed!r}")
+        known = {f for f in cls.__dataclass_fields__ if f != "extra"}
+        unread = sorted(k for k in data if k not in known and k not in _NO_EFFECT)
+        if unread:
+            warnings.warn(f"Qwen3 config.json: keys that this engine does not read: {unread}", stacklevel=2)
         return cls(
             hidden_size=data["hidden_size"], intermediate_size=data["intermediate_size"],
             num_hidden_layers=data["num_hidden_layers"], num_attention_heads=nh, num_key_value_heads=nkv,
@@ -123,7 +145,8 @@ class Qwen3Config(ArchitectureConfig):
             eos_token_id=int(data.get("eos_token_id", -1) if data.get("eos_token_id") is not None else -1),
             use_sliding_window=use_window, sliding_window=window if use_window else None,
             layer_types=list(layer_types) if (use_window and layer_types is not None) else None,
-            extra={k: v for k, v in data.items() if k not in known},
+            max_window_layers=first_windowed if (use_window and layer_types is None) else None,
+            extra={k: v for k, v in data.items() if k not in known and k not in ("architectures", "rope_parameters")},
         )
 
     def to_json(self) -> Dict[str, Any]:
@@ -138,9 +161,9 @@ class Qwen3Config(ArchitectureConfig):
     def layer_window(self, layer: int) -> Optional[int]:
         if not self.use_sliding_window:
             return None
-        if self.layer_types is None or self.layer_types[layer] == "sliding_attention":
-            return self.sliding_window
-        return None
+        if self.layer_types is not None:
+            return self.sliding_window if self.layer_types[layer] == "sliding_attention" else None
+        return self.sliding_window if layer >= self.max_window_layers else None
 
     def to_spec(self) -> ModelSpec:
         H = self.hidden_size

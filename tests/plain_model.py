@@ -162,15 +162,22 @@ def layer_windows(cfg):
     """Window of each layer, ``None`` for a layer that sees every key.
 
     The reference reads no window key (src/models/model_config.hpp:27-47): all layers are
-    full attention.  The engine under test also takes ``use_sliding_window``,
-    ``sliding_window`` and ``layer_types`` from config.json; a layer whose type is
-    ``"sliding_attention"`` sees ``sliding_window`` keys.
+    full attention.  The engine under test also takes ``use_sliding_window`` and
+    ``sliding_window`` from config.json, with the layers that have the window named either
+    by ``layer_types`` (``"sliding_attention"``) or by ``max_window_layers`` (the first
+    ``max_window_layers`` layers see every key, the others have the window).  Stated here
+    layer by layer, on its own, so that a different reading in the engine shows.
     """
-    n = cfg["num_hidden_layers"]
-    if not cfg.get("use_sliding_window", False):
-        return [None] * n
-    types = cfg.get("layer_types") or ["sliding_attention"] * n
-    return [cfg["sliding_window"] if t == "sliding_attention" else None for t in types]
+    out = []
+    for i in range(cfg["num_hidden_layers"]):
+        windowed = False
+        if cfg.get("use_sliding_window", False):
+            if cfg.get("layer_types") is not None:
+                windowed = cfg["layer_types"][i] == "sliding_attention"
+            else:
+                windowed = i + 1 > cfg["max_window_layers"]
+        out.append(cfg["sliding_window"] if windowed else None)
+    return out
 
 
 def forward_logits(w, cfg, token_ids, compute=torch.float32) -> torch.Tensor:

@@ -64,6 +64,9 @@ def test_missing_keys_are_named(key):
 @pytest.mark.parametrize("patch", [{"num_key_value_heads": 3}, {"hidden_act": "gelu"}, {"rope_scaling": {"type": "yarn"}},
                                    {"attention_bias": True}, {"head_dim": 15}, {"vocab_size": -1},
                                    {"use_sliding_window": True, "sliding_window": None},
+                                   {"use_sliding_window": True, "sliding_window": 8},
+                                   {"use_sliding_window": True, "sliding_window": 8, "max_window_layers": 3},
+                                   {"use_sliding_window": True, "sliding_window": 8, "max_window_layers": "1"},
                                    {"use_sliding_window": True, "sliding_window": 8, "layer_types": ["full_attention"]}])
 def test_values_the_engine_cannot_run_are_refused(patch):
     with pytest.raises(ConfigError):
@@ -83,6 +86,35 @@ def test_spec_is_data_layer_by_layer():
     # a window key without use_sliding_window changes nothing
     plain = dict(TINY["c"]["config"], use_sliding_window=False)
     assert [l.mixer.params["window"] for l in config_from_json(plain).to_spec().layers] == [None] * 4
+
+
+def test_which_layers_have_the_window_in_both_spellings():
+    """``layer_types`` names the layers one by one; without it ``max_window_layers`` says how many
+    layers at the bottom see every key.  The plain implementation states the same rule on its own."""
+    import plain_model
+    base = {k: v for k, v in TINY["c"]["config"].items() if k != "layer_types"}
+    for first, want in [(0, [40, 40, 40, 40]), (2, [None, None, 40, 40]), (4, [None] * 4)]:
+        data = dict(base, max_window_layers=first)
+        cfg = config_from_json(data)
+        assert [cfg.layer_window(i) for i in range(4)] == want == plain_model.layer_windows(data)
+        assert [l.mixer.params["window"] for l in config_from_json(cfg.to_json()).to_spec().layers] == want
+    both = dict(TINY["c"]["config"], max_window_layers=1)              # the list counts where both are given
+    assert [config_from_json(both).layer_window(i) for i in range(4)] == [40, None, 40, None] == plain_model.layer_windows(both)
+    off = dict(base, use_sliding_window=False, max_window_layers=2)
+    assert [config_from_json(off).layer_window(i) for i in range(4)] == [None] * 4 == plain_model.layer_windows(off)
+
+
+def test_keys_that_are_not_read_are_named_in_a_warning():
+    import warnings
+    with pytest.warns(UserWarning, match="logit_cap.*mystery"):
+        cfg = config_from_json(dict(TINY["a"]["config"], mystery=1, logit_cap=30.0))
+    assert cfg.extra == {"logit_cap": 30.0, "mystery": 1}
+    with warnings.catch_warnings():
+        warnings.simplefilter("error")
+        for name in TINY:
+            config_from_json(TINY[name]["config"])
+        config_from_json(dict(TINY["a"]["config"], torch_dtype="bfloat16", use_cache=True, attention_dropout=0.0, transformers_version="x",
+                              sliding_window=None, max_window_layers=28, use_sliding_window=False))
 
 
 def test_config_round_trips_through_json(tmp_path):

@@ -11,7 +11,7 @@ import numpy as np
 import pytest
 
 import plain_model
-from trace_tools import TraceBuilder, mixed_trace, peak_tokens, run_trace
+from trace_tools import TraceBuilder, mixed_trace, peak_pages, peak_tokens, run_trace
 
 pytestmark = pytest.mark.gpu
 
@@ -72,12 +72,19 @@ def build(reqs):
     return b, tokens_of
 
 
+# (shape, page size): every shape in the program's own pages of 16, and the 8B shape in pages of 4,
+# which are no TMA box: the bfloat16 run then takes the mma.sync attention kernel (split mode for
+# decoding steps, tiles mode for portions) at head size 128, with the pool at the trace's exact peak
+CASES = [(name, None) for name in SHAPES] + [("8b", 4)]
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", list(SHAPES))
-def test_layer_sizes_match_plain_under_every_cut(name, dtype, layer_models, tmp_path):
+@pytest.mark.parametrize("name,page_size", CASES, ids=[f"{n}-page{p or 16}" for n, p in CASES])
+def test_layer_sizes_match_plain_under_every_cut(name, page_size, dtype, layer_models, tmp_path):
     folder, cfg, reqs, want = layer_models(name)
     b, tokens_of = build(reqs)
-    rows = run_trace(folder, dtype, b, str(tmp_path), peak_tokens(b), cfg["vocab_size"])
+    options = [] if page_size is None else ["--page-size", page_size, "--num-pages", peak_pages(b, page_size)]
+    rows = run_trace(folder, dtype, b, str(tmp_path), peak_tokens(b), cfg["vocab_size"], options=options)
     tol = TOL[dtype]
     for rid, toks in tokens_of.items():
         ref = want[rid[2:]]

@@ -108,12 +108,28 @@ def peak_tokens(builder: TraceBuilder, round_to: int = 64) -> int:
     return peak
 
 
+def peak_pages(builder: TraceBuilder, page_size: int) -> int:
+    """The most pages of ``page_size`` tokens that live requests hold at any time: the smallest pool the
+    trace can run in, so that every page a request gives back is needed again."""
+    held: Dict[str, int] = {}
+    peak = 0
+    for st in builder.steps:
+        for e in st["entries"]:
+            held[e["id"]] = held.get(e["id"], 0) + len(e["tokens"])
+        peak = max(peak, sum((n + page_size - 1) // page_size for n in held.values()))
+        for r in st["end"]:
+            held.pop(r, None)
+    return peak
+
+
 def run_trace(model_dir: str, dtype: str, builder: TraceBuilder, out_dir: str, max_tokens: int, vocab: int, timeout: float = 600.0,
-              env=None) -> Dict[Tuple[str, int], np.ndarray]:
+              env=None, options: Sequence[str] = (), model_args: Sequence[str] = ()) -> Dict[Tuple[str, int], np.ndarray]:
+    """``options``: further options of the program (``--page-size`` and the like); ``model_args``
+    replaces ``--model model_dir`` (for ``--random``)."""
     os.makedirs(out_dir, exist_ok=True)
     text = "".join(json.dumps(s) + "\n" for s in builder.steps)
-    cmd = [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_dir, "--dtype", dtype, "--out", out_dir,
-           "--max-tokens", str(max_tokens)]
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "trace_run"), *(model_args or ["--model", model_dir]), "--dtype", dtype, "--out", out_dir,
+           "--max-tokens", str(max_tokens), *[str(o) for o in options]]
     proc = subprocess.run(cmd, input=text, capture_output=True, text=True, timeout=timeout, env=env)
     if proc.returncode != 0:
         raise RuntimeError(f"trace_run exited with {proc.returncode}\nstdout:\n{proc.stdout[-2000:]}\nstderr:\n{proc.stderr[-4000:]}")
