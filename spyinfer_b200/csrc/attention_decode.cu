@@ -164,14 +164,6 @@ __device__ __forceinline__ void key_range(const Params& p, const int* pos_s, int
 
 __device__ __forceinline__ int tiles_of(int pos, int lo) { return pos >= 0 ? pos / TILE - lo / TILE + 1 : 0; }
 
-// -DSPY_TIMELINE: every block stamps the global timer at a few points of its life into a device
-// array that spy_attention_decode_timeline copies out (a debugging aid; off in normal builds).
-#ifdef SPY_TIMELINE
-__device__ unsigned long long g_timeline[256][16];
-#define STAMP(i) (g_timeline[blockIdx.x & 255][i] = global_timer())
-#else
-#define STAMP(i) ((void)0)
-#endif
 
 // arrivals of the warps that hold a part of a pair's result; the last one merges and resets it
 __device__ int g_pair_arrivals[MAX_PAIRS];
@@ -212,7 +204,6 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
     if (tid == 0) {
-        STAMP(0);
         asm volatile("prefetch.tensormap [%0];" ::"l"(&page_map) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&q_map) : "memory");
         for (int i = 0; i < STAGES; ++i) {
@@ -277,7 +268,6 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
     fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_o = tmem_base + 2 * NCOLS;
-    if (tid == 0) STAMP(1);
     const int units = p.nkv * prefix[p.S];
     const int per = (units + (int)gridDim.x - 1) / (int)gridDim.x;
     const int u0 = min(units, (int)blockIdx.x * per), u1 = min(units, u0 + per);
@@ -309,7 +299,6 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
                 const int st = gt & 1;
                 const uint32_t ph = (uint32_t)(gt >> 1) & 1;
                 if (!(alive = mbar_wait(bar_s + st, ph, abort_flag))) break;
-                if (tid == 0 && gt == 0) STAMP(5);
                 fence_after_sync();
                 uint32_t r[GN];
                 tmem_load<GN>(tmem_base + st * NCOLS + lane_addr, r);
@@ -372,9 +361,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
             }
             if (!alive) break;
             // ---- the segment's result: O^T / sum, or the partial result of this run of tiles
-            if (tid == 0) STAMP(6);
             if (!(alive = mbar_wait(bar_o + ((gt - 1) & 1), (uint32_t)((gt - 1) >> 1) & 1, abort_flag))) break;
-            if (tid == 0) STAMP(7);
             fence_after_sync();
             uint32_t o[GN];
             tmem_load<GN>(tmem_o + lane_addr, o);
@@ -413,14 +400,12 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
                 const int c_first = off / per, c_last = (off + g.tiles - 1) / per;
                 __threadfence();
                 __syncwarp();
-                if (tid == 0) STAMP(8);
                 int last = 0;
                 if (lane == 0) {
                     last = atomicAdd(&g_pair_arrivals[pair], 1) == 4 * (c_last - c_first + 1) - 1;
                     if (last) g_pair_arrivals[pair] = 0;
                 }
                 last = __shfl_sync(0xffffffffu, last, 0);
-                if (last && lane == 0) STAMP(11);
                 if (last) {
                     // 32 / GN lanes share a head; a lane merges W consecutive columns of its head.  The
                     // loads of CH parts are issued together (a pair of two to four parts then costs one
@@ -462,7 +447,6 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
                                 }
                             }
                         }
-                        if (lane == 0) STAMP(13);
                         bf16* dst = p.out + ((size_t)tok * p.nh + g.kvh * p.G + n) * HD + col;
                         const float inv = L > 0.f ? 1.f / L : 0.f;
 #pragma unroll
@@ -479,7 +463,6 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
                     }
                 }
             }
-            if (tid == 0) STAMP(9);
             ++seg;
             more = seg_next(g, share);
         }
@@ -495,7 +478,6 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
                 if (gq.t == gq.t0) ok = mbar_wait(bar_qfull + slot, (uint32_t)(segq / QSLOTS) & 1, abort_flag);
                 ok = ok && mbar_wait(bar_kfull + stage, (uint32_t)(iq / STAGES) & 1, abort_flag);
                 if (!ok) return;
-                if (iq == 0) STAMP(4);
                 fence_after_sync();
                 const uint32_t kb = k_s + stage * STAGE_BYTES, qb = q_s + slot * QP_BYTES;
 #pragma unroll
@@ -536,7 +518,6 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
             bool more = seg_first(g, share);
             int tok_next = more ? p.q_start[g.s] : 0;   // the host wrote q_start: read ahead of the wait and of each segment's load
             pdl_wait();
-            STAMP(3);
             for (int seg = 0; more; ++seg) {
                 const int slot = seg % QSLOTS;
                 const int tok = tok_next;
@@ -564,7 +545,6 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
         Seg g;
         bool more = seg_first(g, share), ok = true, waited = false;
         int i = 0;
-        if (lane == 0 && kv == 0) STAMP(15);
         while (more && ok) {
             int pos, lo;
             key_range(p, pos_s, g.s, pos, lo);
@@ -594,7 +574,6 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
                 }
                 ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
                 if (!ok) break;
-                if (i == 0 && lane == 0 && kv == 0) STAMP(2);
                 if (lane < boxes) {
                     const int y = ((page * 2 + kv) * p.nkv + g.kvh) * p.page_size;
                     tma_load_2d(ring + stage * STAGE_BYTES + my_half * HALF_BYTES + my_page * p.page_size * 128, &page_map, my_half * 64, y, bar_full + stage);
@@ -618,26 +597,15 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
         fence_after_sync();
         tmem_dealloc(tmem_base, TMEM_COLS);
     }
-    if (tid == 0) STAMP(10);
 }
 
-int sm_count()
-{
-    static int sms = 0;
-    if (sms == 0) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms = 0;
-    }
-    return sms;
-}
+int sm_count() { return spy_sm_count(); }
 
 template <int HD, int GN>
 int launch(const CUtensorMap& page_map, const CUtensorMap& q_map, const Params& p, cudaStream_t stream)
 {
-    static bool configured = false;
-    if (!configured) {
+    SPY_ONCE_PER_DEVICE {
         SPY_CUDA(cudaFuncSetAttribute(attention_decode_kernel<HD, GN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL));
-        configured = true;
     }
     spy_launch(attention_decode_kernel<HD, GN>, dim3(p.blocks), dim3(NUM_THREADS), (size_t)SMEM_TOTAL, stream, page_map, q_map, p);
     SPY_CHECK_LAUNCH("attention_decode");
@@ -646,15 +614,6 @@ int launch(const CUtensorMap& page_map, const CUtensorMap& q_map, const Params& 
 
 }  // namespace
 
-#ifdef SPY_TIMELINE
-// Copies the stamps of the last launch out: [256 blocks][16 points] of nanoseconds.
-extern "C" int spy_attention_decode_timeline(unsigned long long* host)
-{
-    SPY_CUDA(cudaDeviceSynchronize());
-    SPY_CUDA(cudaMemcpyFromSymbol(host, g_timeline, sizeof(g_timeline)));
-    return 0;
-}
-#endif
 
 // Floats of scratch a batch of `seqs` decoding sequences needs: one slot per (sequence, kv head) pair and per block.
 extern "C" long long spy_attention_decode_scratch_floats(int seqs, int nh, int nkv, int hd)

@@ -687,11 +687,9 @@ extern "C" int spy_attention_mma(const void* q, long long q_row_stride, void* ou
         if (blocks > 0x7fffffffLL || nkv > 65535) SPY_FAIL("attention_mma: the batch exceeds the grid limits");
         dim3 grid((unsigned)blocks, nkv);
         const size_t tile_bytes = (size_t)TILE_STAGES * 2 * TILE_KEYS * (hd / 8) * sizeof(uint4);
-        static bool tiles_configured = false;
-        if (!tiles_configured) {
+        SPY_ONCE_PER_DEVICE {
             SPY_CUDA(cudaFuncSetAttribute(attention_tiles_kernel<64, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
             SPY_CUDA(cudaFuncSetAttribute(attention_tiles_kernel<128, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
-            tiles_configured = true;
         }
         if (hd == 64) spy_launch(attention_tiles_kernel<64, TW>, grid, dim3(TW * 32), tile_bytes, stream, p);
         else spy_launch(attention_tiles_kernel<128, TW>, grid, dim3(TW * 32), tile_bytes, stream, p);
@@ -713,11 +711,9 @@ extern "C" int spy_attention_mma(const void* q, long long q_row_stride, void* ou
     const size_t table_bytes = (size_t)(split_keys + 2) * sizeof(int);   // page_size 1 is the worst case
     const size_t smem = (ring_bytes > merge_bytes ? ring_bytes : merge_bytes) + table_bytes;
     if (smem > 110 * 1024) SPY_FAIL("attention_mma: split_keys %d needs %zu bytes of shared memory (limit %d)", split_keys, smem, 110 * 1024);
-    static bool configured = false;
-    if (!configured) {
+    SPY_ONCE_PER_DEVICE {
         SPY_CUDA(cudaFuncSetAttribute(attention_split_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024));
         SPY_CUDA(cudaFuncSetAttribute(attention_split_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024));
-        configured = true;
     }
     if (hd == 64) spy_launch(attention_split_kernel<64>, grid, dim3(WARPS * 32), smem, stream, p);
     else spy_launch(attention_split_kernel<128>, grid, dim3(WARPS * 32), smem, stream, p);

@@ -73,26 +73,6 @@ struct Item {
     int seq, tok0, kvh, n_tiles, tile_first, block_lo, block_last_pos, tok_end;
 };
 
-// -DSPY_TIMELINE: blocks stamp the global timer at points of their tenth tile into a device array
-// that spy_attention_tc_timeline copies out (a debugging aid; off in normal builds).
-#ifdef SPY_TIMELINE
-__device__ unsigned long long g_timeline[1024][16];
-#define STAMP(t, i) do { if ((t) == 10) g_timeline[(blockIdx.x + gridDim.x * blockIdx.y) & 1023][i] = global_timer(); } while (0)
-// ... and at points of the block's life (thread 0): spy_attention_tc_block_life copies these out
-__device__ __forceinline__ unsigned smid()
-{
-    unsigned v;
-    asm volatile("mov.u32 %0, %%smid;" : "=r"(v));
-    return v;
-}
-__device__ unsigned long long g_block_life[1024][8];
-#define LIFE(item, i) do { if (threadIdx.x == 0) g_block_life[(item) & 1023][i] = global_timer(); } while (0)
-#define LIFE_VALUE(item, i, v) do { if (threadIdx.x == 0) g_block_life[(item) & 1023][i] = (unsigned long long)(v); } while (0)
-#else
-#define STAMP(t, i) ((void)0)
-#define LIFE(item, i) ((void)0)
-#define LIFE_VALUE(item, i, v) ((void)0)
-#endif
 
 // Byte offset of 16-byte chunk `chunk` (0 .. HD / 8 - 1, or 0 .. 15 for the 128-key P tile) of
 // row `row` in a [128 rows][64-element halves] tile with 128-byte swizzle.
@@ -246,9 +226,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
             if (!alive) break;
             const Item it = item_ring[j & 1];
             if (it.n_tiles < 0) break;
-            const int item_no = blockIdx.x + gridDim.x * j;   // for the timeline build's stamps
-            (void)item_no;
-            LIFE(item_no, 0);
             const int n_tiles = it.n_tiles, tile_first = it.tile_first, tok0 = it.tok0, tok_end = it.tok_end, kvh = it.kvh;
             const int tok = tok0 + row / p.Gp, hg = row % p.Gp;
             const bool row_ok = tok < tok_end && hg < p.G;
@@ -261,8 +238,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
             fence_async_proxy();   // the MMA reads shared memory through the async proxy
             mbar_arrive(bar_q);
             if (tid == 0) describe_next(j + 1);   // while the first scores are on their way
-            LIFE(item_no, 2);
-            LIFE_VALUE(item_no, 7, (unsigned)n_tiles | (smid() << 16));
 
             float m_used = -INFINITY, l = 0.f;   // the maximum the probabilities are taken against (equal in both threads of a row); this thread's share of their sum
             for (int t = 0; t < n_tiles; ++t) {
@@ -270,8 +245,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
                 const uint32_t ph = (uint32_t)(gt >> 1) & 1;
                 alive = mbar_wait(bar_s + st, ph, abort_flag);          // S_t is complete
                 if (!alive) break;
-                if (t == 0) LIFE(item_no, 3);
-                if (tid == 0) { STAMP(t, 0); STAMP(t - 1, 5); }
                 fence_after_sync();
                 const int key0 = (tile_first + t) * TILE + half * COLS;
                 // This thread's 64 raw scores (masked where the tile is not visible whole to every row of the warp).
@@ -282,7 +255,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
 #pragma unroll
                 for (int c = 0; c < COLS; c += 32) tmem_load<32>(tmem_base + st * TILE + lane_addr + half * COLS + c, *reinterpret_cast<uint32_t(*)[32]>(&sc[c]));
                 tmem_wait_ld();
-                if (tid == 0) STAMP(t, 1);
                 const bool whole = __all_sync(0xffffffffu, !row_ok || (key0 >= lo && key0 + COLS - 1 <= pos));
                 if (!whole) {
 #pragma unroll
@@ -304,7 +276,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
                 mbar_arrive(bar_x + st);
                 alive = mbar_wait(bar_x + st, ph, abort_flag);
                 if (!alive) break;
-                if (tid == 0) STAMP(t, 2);
                 const float mx = fmaxf(__bfloat162float(mine), __bfloat162float(xch[(st * 2 + (half ^ 1)) * ROWS + row])) * p.scale_log2;
                 // the maximum in use moves only when the row's maximum grew by more than the threshold (or from nothing)
                 const float m_new = fmaxf(m_used, mx);
@@ -331,7 +302,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
                     unpack2(add2(sum2[0], sum2[1]), s0, s1);
                     l += s0 + s1;
                 }
-                if (tid == 0) STAMP(t, 3);
                 // Only a rescale of O has to wait for P.V of tile t-1, so in the common case P_t is ready before
                 // that product ends and the next one follows it without a gap.
                 if (t > 0 && __any_sync(0xffffffffu, grow)) {   // the warp with the row's other half decides the same
@@ -357,7 +327,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
                 tmem_wait_st();
                 fence_before_sync();
                 mbar_arrive(bar_p + st);
-                if (tid == 0) STAMP(t, 4);
             }
             if (!alive) break;
             // ---- the next item's Q tile is requested ...
@@ -366,11 +335,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
             q_requested = item_ring[(j + 1) & 1].n_tiles > 0;
             if (q_requested) request_q(item_ring[(j + 1) & 1]);
             // ---- ... and this item's epilogue runs meanwhile: O / l
-            LIFE(item_no, 4);
             const int gl = base + n_tiles - 1;
             alive = mbar_wait(bar_o + (gl & 1), (uint32_t)(gl >> 1) & 1, abort_flag);
             if (!alive) break;
-            LIFE(item_no, 5);
             fence_after_sync();
             xsum[half * ROWS + row] = l;   // every thread has read the maxima of the last tile: it wrote P after that, and P.V is complete
             mbar_arrive(bar_sum);
@@ -400,7 +367,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
             // the next item's first P.V overwrites O: it needs that item's probabilities, which every thread writes
             // only after it has read its part of O here
             fence_before_sync();
-            LIFE(item_no, 6);
             base += n_tiles;
         }
     } else if (warp == 8) {
@@ -441,10 +407,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
                 for (int t = 0; t < n_tiles && ok; ++t) {
                     const int gt = base + t, st = gt & 1, stage = gt % STAGES;
                     ok = mbar_wait(bar_p + st, (uint32_t)(gt >> 1) & 1, abort_flag);
-                    STAMP(t, 6);
                     ok = ok && mbar_wait(bar_v + stage, (uint32_t)(gt / STAGES) & 1, abort_flag);
                     if (!ok) break;
-                    STAMP(t, 7);
                     fence_after_sync();
                     const uint32_t vb = v_s + stage * L::OPERAND_BYTES;
 #pragma unroll
@@ -452,15 +416,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
                         umma_ts(tmem_o, tmem_base + st * TILE + s * 8, desc_mn_major(vb + s * 16 * 128, ROWS * 128), idesc_pv, (t > 0 || s > 0) ? 1u : 0u);
                     umma_commit(bar_o + st);
                     umma_commit(bar_vfree + stage);
-                    STAMP(t, 8);
                     if (t + 2 < n_tiles) {
                         // S's stage st is free: P_t lies in it and the product above reads it first (the tensor core runs in order)
                         ok = mbar_wait(bar_k + (gt + 2) % STAGES, (uint32_t)((gt + 2) / STAGES) & 1, abort_flag);
                         if (!ok) break;
-                        STAMP(t, 9);
                         fence_after_sync();
                         issue_qk(gt + 2);
-                        STAMP(t, 10);
                     }
                 }
                 base += n_tiles;
@@ -499,7 +460,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
                 if (lane == 0) {
                     // K's stage is free when Q.K of the tile three back is complete, V's when its P.V is
                     if (gt >= STAGES) ok = mbar_wait((kv == 0 ? bar_kfree : bar_vfree) + st, (uint32_t)(gt / STAGES - 1) & 1, abort_flag);
-                    if (kv == 0) STAMP(t - 3, 11);
                     if (ok) mbar_expect_tx(bar, (uint32_t)count * box_bytes);
                 }
                 ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -508,7 +468,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
                     const int y = ((page * 2 + kv) * p.nkv + it.kvh) * p.page_size;
                     tma_load_2d((kv == 0 ? k_s : v_s) + st * L::OPERAND_BYTES + my_half * (ROWS * 128) + my_page * p.page_size * 128, &page_map, my_half * 64, y, bar);
                 }
-                if (kv == 0 && lane == 0) STAMP(t - 3, 12);
             }
             base += it.n_tiles;
         }
@@ -532,20 +491,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
 
 }  // namespace
 
-#ifdef SPY_TIMELINE
-extern "C" int spy_attention_tc_timeline(unsigned long long* host)
-{
-    SPY_CUDA(cudaDeviceSynchronize());
-    SPY_CUDA(cudaMemcpyFromSymbol(host, g_timeline, sizeof(g_timeline)));
-    return 0;
-}
-extern "C" int spy_attention_tc_block_life(unsigned long long* host)
-{
-    SPY_CUDA(cudaDeviceSynchronize());
-    SPY_CUDA(cudaMemcpyFromSymbol(host, g_block_life, sizeof(g_block_life)));
-    return 0;
-}
-#endif
 
 // Attention of a batch over its pages: prompt portions, any mix, single tokens included.
 extern "C" int spy_attention_tc(const void* q, long long q_row_stride, void* out, const void* pages, const int* block_table, int table_width,
@@ -584,11 +529,9 @@ extern "C" int spy_attention_tc(const void* q, long long q_row_stride, void* out
                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) SPY_FAIL("attention_tc: cuTensorMapEncodeTiled failed with code %d", (int)r);
     }
-    static bool configured = false;
-    if (!configured) {
+    SPY_ONCE_PER_DEVICE {
         SPY_CUDA(cudaFuncSetAttribute(attention_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<64>::TOTAL));
         SPY_CUDA(cudaFuncSetAttribute(attention_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<128>::TOTAL));
-        configured = true;
     }
     const int tokens_per_block = ROWS / Gp;
     const long long blocks = (tokens + tokens_per_block - 1) / tokens_per_block + seqs;   // an upper bound without a host copy of q_start
@@ -598,12 +541,7 @@ extern "C" int spy_attention_tc(const void* q, long long q_row_stride, void* out
     p.items = (int)items;
     // one resident block per SM walks through the items (set-up once, the next item's keys requested while the
     // last tiles of the one before are worked on)
-    static int sms = 0;
-    if (sms == 0) {
-        int dev = 0;
-        SPY_CUDA(cudaGetDevice(&dev));
-        SPY_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    }
+    const int sms = spy_sm_count();
     dim3 grid((unsigned)(items < sms ? items : sms));
     if (hd == 64) spy_launch(attention_tc_kernel<64>, grid, dim3(NUM_THREADS), (size_t)Smem<64>::TOTAL, stream, page_map, p);
     else spy_launch(attention_tc_kernel<128>, grid, dim3(NUM_THREADS), (size_t)Smem<128>::TOTAL, stream, page_map, p);

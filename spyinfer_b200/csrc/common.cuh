@@ -45,6 +45,38 @@ enum {
         if (e_ != cudaSuccess) SPY_FAIL("%s: %s", #call, cudaGetErrorString(e_));          \
     } while (0)
 
+// ---- what CUDA keeps per device ----------------------------------------------------------------
+// Function attributes (the dynamic shared memory a kernel may use), occupancy figures and the
+// number of SMs belong to a device, not to the process: set-up that is done "once" is done once
+// per device, with that device current, and remembered by the device's index.
+constexpr int SPY_MAX_DEVICES = 64;
+
+static inline int spy_device()
+{
+    int d = 0;
+    if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= SPY_MAX_DEVICES) d = 0;
+    return d;
+}
+
+// The current device's number of SMs (at least 1), asked once per device.
+static inline int spy_sm_count()
+{
+    static int sms[SPY_MAX_DEVICES] = {};
+    const int d = spy_device();
+    if (sms[d] <= 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, d) != cudaSuccess || n <= 0) n = 1;
+        sms[d] = n;
+    }
+    return sms[d];
+}
+
+// Opens a block that runs once per device:  SPY_ONCE_PER_DEVICE { ...set-up... }
+#define SPY_ONCE_PER_DEVICE                                                                \
+    static bool spy_done_[SPY_MAX_DEVICES] = {};                                           \
+    const int spy_dev_ = spy_device();                                                     \
+    for (bool spy_run_ = !spy_done_[spy_dev_]; spy_run_; spy_run_ = false, spy_done_[spy_dev_] = true)
+
 // ---- launches with programmatic dependent launch --------------------------------------------
 // Every kernel of this library is launched with the programmatic-stream-serialization
 // attribute: it may begin while the kernel before it in the stream is still finishing.  In

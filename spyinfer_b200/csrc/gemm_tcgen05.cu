@@ -68,22 +68,6 @@ struct WideTile {
 
 template <typename TC> __device__ __forceinline__ void store_elem(TC* p, float v) { *p = from_f32<TC>(v); }
 
-// -DSPY_TIMELINE: the blocks of the one-tile kernel stamp the global timer at a few points of
-// their life into a device array, one plane per launch (the host numbers the launches; a
-// captured graph keeps the numbers it was captured with), which spy_gemm_tcgen05_timeline
-// copies out (a debugging aid; off in normal builds).
-#ifdef SPY_TIMELINE
-constexpr int TL_LAUNCHES = 64, TL_BLOCKS = 320, TL_POINTS = 10;
-__device__ unsigned long long g_timeline[TL_LAUNCHES][TL_BLOCKS][TL_POINTS];
-#define GSTAMP(i)                                                                                                  \
-    do {                                                                                                           \
-        const unsigned b_ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);                        \
-        if (b_ < TL_BLOCKS) g_timeline[launch_no % TL_LAUNCHES][b_][i] = global_timer();                          \
-    } while (0)
-#else
-#define GSTAMP(i) ((void)0)
-#endif
-
 // Stores 32 consecutive columns of one row, vectorised when the row allows it.
 template <typename TC>
 __device__ __forceinline__ void store_row32(TC* dst, const uint32_t (&r)[32], int valid, bool aligned)
@@ -130,7 +114,7 @@ __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(
 template <int BN, typename TC, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 2)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, TC* __restrict__ out,
-                    long long ld, long long split_stride, int x_rows, int y_rows, int k_blocks, int k_blocks_per_split, int tile_rows, int launch_no,
+                    long long ld, long long split_stride, int x_rows, int y_rows, int k_blocks, int k_blocks_per_split, int tile_rows,
                     int* status)
 {
     using T = Tile<BN>;
@@ -144,13 +128,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-#ifdef SPY_TIMELINE
-    if (threadIdx.x == 0) {
-        GSTAMP(0);
-        const unsigned b_ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
-        if (b_ < TL_BLOCKS) g_timeline[launch_no % TL_LAUNCHES][b_][9] = gridDim.x * gridDim.y * gridDim.z;
-    }
-#endif
     // tile_rows (<= BM) rows of X belong to this block: the box of map_x has that many rows, the rest of
     // the stage's 128 rows is stale and feeds accumulator rows that are never stored
     // the token tile is the grid's fastest dimension, so that the blocks that share a weight tile
@@ -180,7 +157,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
-    if (threadIdx.x == 0) GSTAMP(1);
 
     pdl_launch_dependents();   // the next kernel in the stream may begin its own prologue
     if (warp == 0) {
@@ -195,7 +171,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 tma_load_2d(smem_u32(xs), &map_x, (kb0 + i) * BK, x0, full_bar + i);
             }
             pdl_wait();
-            GSTAMP(2);
             for (int i = 0; i < pre; ++i) {
                 uint8_t* xs = tiles + (size_t)i * stage_bytes;
                 tma_load_2d(smem_u32(xs + x_bytes), &map_y, (kb0 + i) * BK, y0, full_bar + i);
@@ -222,8 +197,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             uint32_t phase = 0;
             for (int i = 0; i < num_kb; ++i) {
                 if (!mbar_wait(full_bar + s, phase, abort_flag)) break;
-                if (i == 0) GSTAMP(3);
-                if (i == num_kb - 1) GSTAMP(4);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint8_t* xs = tiles + (size_t)s * stage_bytes;
                 const uint64_t dx = desc_k_major(smem_u32(xs)), dy = desc_k_major(smem_u32(xs + x_bytes));
@@ -245,7 +218,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         const int quarter = warp & 3;
         pdl_wait();   // the output buffer may still be in use by a kernel ahead in the stream
         const bool ok = mbar_wait(accum_bar, 0, abort_flag);
-        if (warp == 2 && lane == 0) GSTAMP(5);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const int x = quarter * 32 + lane < tile_rows ? x0 + quarter * 32 + lane : x_rows;   // rows beyond the tile's are the next block's
         TC* base = out + (size_t)blockIdx.z * split_stride;
@@ -351,10 +323,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         }
     }
 
-    if (warp == 2 && lane == 0) GSTAMP(6);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (threadIdx.x == 0) GSTAMP(7);
     if (*abort_flag) {
         // a wait ran out: give copies that may still be in flight time to land before the
         // shared memory is released, then report
@@ -911,14 +881,12 @@ static int reduce_splits(const float* scratch, void* C, int c_dtype, long long l
     const long long elems = (long long)M * N;
     if (ldc != N) SPY_FAIL("gemm_tcgen05: split-K needs a contiguous output (ldc %lld, N %d)", ldc, N);
     long long blocks = (elems + 255) / 256;
-    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (blocks > spy_sm_count() * 8) blocks = spy_sm_count() * 8;
     if (c_dtype == SPY_F32) spy_launch(splitk_reduce_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, scratch, (float*)C, elems, splits);
     else spy_launch(splitk_reduce_kernel<bf16>, dim3((int)blocks), dim3(256), 0, stream, scratch, (bf16*)C, elems, splits);
     SPY_CHECK_LAUNCH("gemm_tcgen05 split-K reduce");
     return 0;
 }
-
-int g_launch_no = 0;   // numbers the launches of the one-tile kernel for the timeline build; unused otherwise
 
 template <int BN, typename TC, int EPI>
 static int launch(const CUtensorMap& mx, const CUtensorMap& my, void* out, long long ld, long long split_stride, int x_rows, int y_rows,
@@ -926,16 +894,14 @@ static int launch(const CUtensorMap& mx, const CUtensorMap& my, void* out, long 
 {
     using T = Tile<BN>;
     auto kernel = gemm_tcgen05_kernel<BN, TC, EPI>;
-    static bool configured = false;
-    if (!configured) {
+    SPY_ONCE_PER_DEVICE {
         SPY_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)T::SMEM));
-        configured = true;
     }
     const int per_split = (k_blocks + splits - 1) / splits;
     dim3 grid((y_rows + BN - 1) / BN, (x_rows + tile_rows - 1) / tile_rows, splits);   // token tiles fastest
     if (grid.y > 65535 || grid.z > 65535) SPY_FAIL("gemm_tcgen05: the grid %u x %u x %u exceeds the launch limits", grid.x, grid.y, grid.z);
     spy_launch(kernel, grid, dim3(NUM_THREADS), T::SMEM, stream, mx, my, (TC*)out, ld, split_stride, x_rows, y_rows, k_blocks, per_split, tile_rows,
-               g_launch_no++, status);
+               status);
     SPY_CHECK_LAUNCH("gemm_tcgen05");
     return 0;
 }
@@ -970,7 +936,7 @@ struct Plan {
     int splits, tile_rows;
 };
 
-constexpr int PAIR_MIN_TILES = 37;   // whole 256 x 256 tiles occupy at least half of the clusters from here on
+static inline int pair_min_tiles() { return (spy_sm_count() / 2 + 1) / 2; }   // whole 256 x 256 tiles occupy at least half of the clusters (SMs / 2) from here on
 
 Plan make_plan(int M, int N, int K, bool may_split)
 {
@@ -978,11 +944,11 @@ Plan make_plan(int M, int N, int K, bool may_split)
     Plan best = {1, BM};
     if (M >= 512 && may_split && pair_kernel_enabled()) {
         // 512 tokens or so on pairs of blocks: with too few 256 x 256 tiles for the clusters (o and down at the 8B
-        // shape: 32), K is cut into two to four ranges, so that tiles x ranges occupy most of the 74 clusters; the
+        // shape: 32), K is cut into two to four ranges, so that tiles x ranges occupy most of the clusters (SMs / 2); the
         // partial tiles are summed by the caller or by the reduce kernel.  At least 16 K blocks a range.
         const long long tiles = (long long)((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
-        if (tiles >= 8 && tiles < PAIR_MIN_TILES) {
-            int s = (int)(74 / tiles);
+        if (tiles >= 8 && tiles < pair_min_tiles()) {
+            int s = (int)(spy_sm_count() / 2 / tiles);
             if (s > 4) s = 4;
             while (s > 1 && (k_blocks / s < 16 || (k_blocks + (k_blocks + s - 1) / s - 1) / ((k_blocks + s - 1) / s) != s)) --s;
             best.splits = s;
@@ -990,7 +956,7 @@ Plan make_plan(int M, int N, int K, bool may_split)
         return best;
     }
     if (M > 256) return best;   // many tokens: the persistent kernels share the work out themselves (stream-K)
-    const int slots = 296 / ((M + 63) / 64 > 0 ? (M + 63) / 64 : 1);   // 65 to 256 tokens: two to four token tiles share every weight tile
+    const int slots = 2 * spy_sm_count() / ((M + 63) / 64 > 0 ? (M + 63) / 64 : 1);   // 65 to 256 tokens: two to four token tiles share every weight tile
     if ((N + BM - 1) / BM >= slots) return best;   // more 128-row tiles than slots: they spread evenly as they are
     int most = may_split ? (k_blocks / 4 > 0 ? k_blocks / 4 : 1) : 1;
     if (most > 16) most = 16;
@@ -1071,21 +1037,20 @@ extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, 
     const bool f32_out = splits > 1 || c_dtype == SPY_F32;
     // pairs need enough 256 x 256 tiles to occupy at least half of the clusters; smaller products go to single
     // blocks, which share the K blocks of their 128 x 256 tiles out over all SMs
-    if (!swap && M >= 512 && (splits > 1 || (long long)((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256) >= PAIR_MIN_TILES) && pair_kernel_enabled()) {
+    if (!swap && M >= 512 && (splits > 1 || (long long)((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256) >= pair_min_tiles()) && pair_kernel_enabled()) {
         // many tokens, one pass over K, at least two 256-row tiles: pairs of blocks on 256 x 256 tiles
         CUtensorMap my_half;
         if (make_map(&my_half, W, N, K, ldw, BM)) return 1;
         const int x_tiles = (M + 2 * BM - 1) / (2 * BM), y_tiles = (N + 255) / 256;
         const long long num_tiles = (long long)x_tiles * y_tiles;
         if (num_tiles > 0x7fffffffLL) SPY_FAIL("gemm_tcgen05: %lld tiles exceed the kernel's range", num_tiles);
-        static int clusters_max = 0;
+        static int clusters_of_device[SPY_MAX_DEVICES] = {};
+        int& clusters_max = clusters_of_device[spy_device()];
         if (clusters_max == 0) {
             SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<bf16, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PAIR_SMEM));
             SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<float, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PAIR_SMEM));
             SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<bf16, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PAIR_SMEM));
-            int dev = 0, sms = 0;
-            SPY_CUDA(cudaGetDevice(&dev));
-            SPY_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+            const int sms = spy_sm_count();
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3(sms / 2 * 2);
             cfg.blockDim = dim3(NUM_THREADS);
@@ -1129,12 +1094,7 @@ extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, 
     }
     if (!swap && splits == 1) {
         // many tokens, one pass over K: the persistent kernel (one block per SM)
-        static int num_sms = 0;
-        if (num_sms == 0) {
-            int dev = 0;
-            SPY_CUDA(cudaGetDevice(&dev));
-            SPY_CUDA(cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev));
-        }
+        const int num_sms = spy_sm_count();
         const int x_tiles = (M + BM - 1) / BM, y_tiles = (N + 255) / 256;
         const long long num_tiles = (long long)x_tiles * y_tiles;
         if (num_tiles > 0x7fffffffLL) SPY_FAIL("gemm_tcgen05: %lld tiles exceed the kernel's range", num_tiles);
@@ -1160,12 +1120,10 @@ extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, 
             grid = (int)((total + per_block - 1) / per_block);
             if (num_tiles > stream_tiles && grid < blocks) grid = (int)blocks;   // whole tiles behind the shared ones: every block takes some
         }
-        static bool configured = false;
-        if (!configured) {
+        SPY_ONCE_PER_DEVICE {
             SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<bf16, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WideTile::SMEM));
             SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<float, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WideTile::SMEM));
             SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<bf16, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WideTile::SMEM));
-            configured = true;
         }
         if (epilogue == 1)
             spy_launch(gemm_tcgen05_persistent_kernel<bf16, 1>, dim3(grid), dim3(NUM_THREADS), WideTile::SMEM, stream, mx, my, (bf16*)C, ldc, M, N,
@@ -1194,23 +1152,65 @@ extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, 
     return 0;
 }
 
-#ifdef SPY_TIMELINE
-// Copies the stamps out: [64 launches][320 blocks][10 points] of nanoseconds (point 9: the grid's
-// size); *next_launch is the number the next launch will get.
-extern "C" int spy_gemm_tcgen05_timeline(unsigned long long* host, int* next_launch)
-{
-    SPY_CUDA(cudaDeviceSynchronize());
-    SPY_CUDA(cudaMemcpyFromSymbol(host, g_timeline, sizeof(g_timeline)));
-    *next_launch = g_launch_no;
-    return 0;
-}
-#endif
 
 // The plain product: no epilogue, partial products summed before it returns.
 extern "C" int spy_gemm_tcgen05(const void* A, long long lda, const void* W, long long ldw, void* C, int c_dtype, long long ldc, int M, int N,
                                 int K, float* scratch, long long scratch_floats, int* status, cudaStream_t stream)
 {
     return spy_gemm_tcgen05_ex(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, scratch, scratch_floats, 0, 0, nullptr, status, stream);
+}
+
+// ---------------------------------------------------------------------------------------------
+// After a wait ran out (status word SPY_STATUS_WAIT_TIMEOUT) the flags by which the blocks of a
+// product with shared K blocks tell one another that a partial tile is ready may be left raised:
+// the owner that gave up did not lower them.  The next such product would then add partial tiles
+// that are not there yet.  Call this before the next product on that device; it lowers all flags,
+// in stream order.  The flags are one array per device for the whole library (this entry point,
+// spy_gemm_tcgen05_ex and spy_gemm_tcgen05_static_scratch alike), so products that share K blocks
+// (more than 256 tokens and fewer tiles than SMs) must be ordered by their streams, not overlap.
+extern "C" int spy_gemm_tcgen05_reset(cudaStream_t stream)
+{
+    void* flags = nullptr;
+    SPY_CUDA(cudaGetSymbolAddress(&flags, g_stream_flags));
+    SPY_CUDA(cudaMemsetAsync(flags, 0, sizeof(int) * STREAM_MAX_BLOCKS, stream));
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Self-test of the bounded wait that every tensor-core kernel of this library relies on: one warp
+// waits on an mbarrier at which nothing ever arrives, with a limit of limit_ns.  The wait must give
+// up after the limit, raise the abort flag and return; the kernel then reports
+// SPY_STATUS_WAIT_TIMEOUT through the status word exactly as the products and attention kernels
+// do, stores how long thread 0 waited, and ends.  It holds no tensor memory and starts no copy.
+// Limits above 100 ms are refused: the test is meant to cost a millisecond.
+namespace {
+__global__ void wait_selftest_kernel(unsigned long long limit_ns, int* status, unsigned long long* waited_ns)
+{
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    const unsigned long long t0 = global_timer();
+    const bool ok = mbar_wait(&bar, 0, &abort_flag, limit_ns);
+    const unsigned long long waited = global_timer() - t0;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (waited_ns != nullptr) *waited_ns = waited;
+        if (!ok || abort_flag) report_status(status, SPY_STATUS_WAIT_TIMEOUT, -1);
+    }
+}
+}  // namespace
+
+extern "C" int spy_tcgen05_wait_selftest(unsigned long long limit_ns, int* status, unsigned long long* waited_ns, cudaStream_t stream)
+{
+    if (limit_ns == 0 || limit_ns > 100000000ull) SPY_FAIL("wait self-test: the limit must lie between 1 ns and 100 ms, found %llu ns", limit_ns);
+    wait_selftest_kernel<<<1, 32, 0, stream>>>(limit_ns, status, waited_ns);
+    SPY_CHECK_LAUNCH("wait self-test");
+    return 0;
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -36,32 +36,12 @@ template <> struct Quad<bf16> {
     }
 };
 
-// -DSPY_TIMELINE: thread 0 of every block stamps the global timer at a few points into a ring of
-// the last 128 blocks, which spy_rmsnorm_timeline copies out (a debugging aid; off in normal builds).
-#ifdef SPY_TIMELINE
-__device__ unsigned long long g_timeline[128][8];
-__device__ unsigned int g_timeline_next;
-__device__ __forceinline__ unsigned long long timer_ns()
-{
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-#define RSTAMP(i) do { if (threadIdx.x == 0) g_timeline[tl_slot][i] = timer_ns(); } while (0)
-#else
-#define RSTAMP(i) ((void)0)
-#endif
 
 template <typename TX, typename TD, typename TW, typename TO, bool VEC>
 __global__ void __launch_bounds__(1024) rmsnorm_kernel(TX* x, const TD* __restrict__ delta, int delta_splits, long long delta_split_stride, const int* __restrict__ rows,
                                const TW* __restrict__ w, TO* __restrict__ out, int len, float eps, int write_back)
 {
     extern __shared__ float row_buf[];  // len floats, then 33 of scratch
-#ifdef SPY_TIMELINE
-    unsigned int tl_slot = 0;
-    if (threadIdx.x == 0) tl_slot = atomicAdd(&g_timeline_next, 1u) % 128u;
-#endif
-    RSTAMP(0);
     // The weight depends on no kernel ahead in the stream: the first quad of it (all of it when
     // the block spans the row, as in decoding) is loaded before the wait for those kernels.
     pdl_launch_dependents();
@@ -69,9 +49,7 @@ __global__ void __launch_bounds__(1024) rmsnorm_kernel(TX* x, const TD* __restri
     if constexpr (VEC) {
         if ((int)threadIdx.x * 4 < len) Quad<TW>::load(w + threadIdx.x * 4, w_first);
     }
-    RSTAMP(1);
     pdl_wait();
-    RSTAMP(2);
     float* scratch = row_buf + len;
     const int src_row = rows ? rows[blockIdx.x] : blockIdx.x;
     TX* xr = x + (size_t)src_row * len;
@@ -115,9 +93,7 @@ __global__ void __launch_bounds__(1024) rmsnorm_kernel(TX* x, const TD* __restri
             if (write_back) xr[i] = from_f32<TX>(v);
         }
     }
-    RSTAMP(3);
     ss = block_sum(ss, scratch);
-    RSTAMP(4);
     const float inv = 1.0f / sqrtf(ss / (float)len + eps);
     if constexpr (VEC) {
         for (int i = threadIdx.x * 4; i < len; i += blockDim.x * 4) {
@@ -135,19 +111,8 @@ __global__ void __launch_bounds__(1024) rmsnorm_kernel(TX* x, const TD* __restri
     } else {
         for (int i = threadIdx.x; i < len; i += blockDim.x) orow[i] = from_f32<TO>((inv * row_buf[i]) * to_f32(w[i]));
     }
-    RSTAMP(5);
 }
 
-#ifdef SPY_TIMELINE
-// Copies the ring out: [128 blocks][8 points] of nanoseconds (entry, weights requested, wait
-// returned, row summed, statistics known, stored).
-extern "C" int spy_rmsnorm_timeline(unsigned long long* host)
-{
-    SPY_CUDA(cudaDeviceSynchronize());
-    SPY_CUDA(cudaMemcpyFromSymbol(host, g_timeline, sizeof(g_timeline)));
-    return 0;
-}
-#endif
 
 // Few rows (decoding): one block per row, the row in registers (QUADS quads of four elements per
 // thread), no shared row buffer, at most 48 registers: a block of 1,024 threads then leaves
@@ -160,11 +125,6 @@ __global__ void __maxnreg__(QUADS <= 2 ? 48 : 80) rmsnorm_row_kernel(TX* x, cons
                                                    int write_back)
 {
     __shared__ float scratch[33];
-#ifdef SPY_TIMELINE
-    unsigned int tl_slot = 0;
-    if (threadIdx.x == 0) tl_slot = atomicAdd(&g_timeline_next, 1u) % 128u;
-#endif
-    RSTAMP(0);
     pdl_launch_dependents();
     // the weight depends on no kernel ahead in the stream: it is loaded before the wait for them
     float wv[QUADS][4];
@@ -173,9 +133,7 @@ __global__ void __maxnreg__(QUADS <= 2 ? 48 : 80) rmsnorm_row_kernel(TX* x, cons
         const int i = (q * blockDim.x + threadIdx.x) * 4;
         if (i < len) Quad<TW>::load(w + i, wv[q]);
     }
-    RSTAMP(1);
     pdl_wait();
-    RSTAMP(2);
     const int src_row = rows ? rows[blockIdx.x] : blockIdx.x;
     TX* xr = x + (size_t)src_row * len;
     const TD* dr = delta ? delta + (size_t)src_row * len : nullptr;
@@ -219,9 +177,7 @@ __global__ void __maxnreg__(QUADS <= 2 ? 48 : 80) rmsnorm_row_kernel(TX* x, cons
         for (int e = 0; e < 4; ++e) ss += v[q][e] * v[q][e];
         if (write_back && i < len) Quad<TX>::store(xr + i, v[q]);
     }
-    RSTAMP(3);
     ss = block_sum(ss, scratch);
-    RSTAMP(4);
     const float inv = 1.0f / sqrtf(ss / (float)len + eps);
 #pragma unroll
     for (int q = 0; q < QUADS; ++q) {
@@ -233,7 +189,6 @@ __global__ void __maxnreg__(QUADS <= 2 ? 48 : 80) rmsnorm_row_kernel(TX* x, cons
             Quad<TO>::store(orow + i, o);
         }
     }
-    RSTAMP(5);
 }
 
 template <typename TX, typename TD, typename TW, typename TO>

@@ -28,7 +28,8 @@ extern "C" int spy_swiglu(const void* gate_up, void* out, int dtype, int tokens,
     if (inter <= 0) SPY_FAIL("swiglu: intermediate size %d must be positive", inter);
     const long long total = (long long)tokens * inter;
     long long blocks = (total + 255) / 256;
-    if (blocks > 148LL * 32) blocks = 148LL * 32;
+    const long long most = (long long)spy_sm_count() * 32;
+    if (blocks > most) blocks = most;
     SPY_DISPATCH_DTYPE(dtype, T, {
         spy_launch(swiglu_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, (const T*)gate_up, (T*)out, inter, total);
     })

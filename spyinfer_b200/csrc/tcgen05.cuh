@@ -47,9 +47,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
     return ok != 0;
 }
 
-// Waits for the phase of the given parity, at most WAIT_LIMIT_NS; on giving up (or when
-// another thread has given up) raises the block's abort flag and returns false.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag)
+// Waits for the phase of the given parity, at most limit_ns (WAIT_LIMIT_NS unless the caller says
+// otherwise); on giving up (or when another thread has given up) raises the block's abort flag and
+// returns false.  The kernels then let copies in flight land, free their tensor memory, store
+// SPY_STATUS_WAIT_TIMEOUT in the status word and return: a wait that nothing ends costs the limit,
+// never the GPU.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, unsigned long long limit_ns = WAIT_LIMIT_NS)
 {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_timer();
@@ -57,7 +60,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     while (!mbar_try_wait(bar, parity)) {
         if ((++spins & 0x3ff) == 0) {
             if (*abort_flag) return false;
-            if (global_timer() - t0 > WAIT_LIMIT_NS) {
+            if (global_timer() - t0 > limit_ns) {
                 *abort_flag = 1;
                 return false;
             }

@@ -7,6 +7,7 @@ src/models/qwen3.hpp:283-301; only the wanted rows are computed here).
 """
 from __future__ import annotations
 
+import warnings
 from typing import Dict, List, Optional
 
 import torch
@@ -73,7 +74,15 @@ class Model:
         build.ensure_built(self.kernel_modules())
 
     def load(self, model_dir: str) -> None:
-        self.bind(load_checkpoint(model_dir, self.weight_decls(), self.ctx.device, self.ignorable_tensors()))
+        tensors = load_checkpoint(model_dir, self.weight_decls(), self.ctx.device, self.ignorable_tensors())
+        if self.ctx.dtype == torch.bfloat16:
+            wide = [n for n, t in tensors.items() if t.dim() == 2 and t.dtype == torch.float32]
+            if wide:
+                # a tensor stored in 32-bit stays so, and a 32-bit matrix cannot go to the bfloat16 tensor-core product
+                warnings.warn(f"{model_dir}: {len(wide)} matrices are stored in 32-bit (or 16-bit float, which is widened), the first being "
+                              f"{wide[0]!r}; they stay 32-bit and are multiplied by the CUDA-core kernel, which is far slower than "
+                              "the bfloat16 tensor-core one. Store the checkpoint in bfloat16 for speed.", stacklevel=2)
+        self.bind(tensors)
 
     def init_random(self, seed: int, std: float = 0.02, norm_std: float = 0.05) -> None:
         """Seeded random weights made on the device, tensor by tensor (no host copy)."""

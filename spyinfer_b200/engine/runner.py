@@ -197,8 +197,7 @@ class ModelRunner:
         event.synchronize()
         out = host[:n + 2].tolist()
         if out[n] != 0:
-            self.stager.status.zero_()
-            raise StepError("a kernel refused " + kernels.STATUS_MESSAGES.get(out[n], f"status {out[n]}").format(detail=out[n + 1]))
+            self._raise_status(out[n], out[n + 1])
         return out[:n]
 
     def read_tokens(self, tokens: torch.Tensor) -> List[int]:
@@ -210,5 +209,13 @@ class ModelRunner:
         (it skipped the access).  Synchronises with the device."""
         code, detail = self.stager.status.tolist()
         if code != 0:
-            self.stager.status.zero_()
-            raise StepError("a kernel refused " + kernels.STATUS_MESSAGES.get(code, f"status {code}").format(detail=detail))
+            self._raise_status(code, detail)
+
+    def _raise_status(self, code: int, detail: int) -> None:
+        """The status word was set: it is cleared, and what a kernel that gave up may have left
+        behind is put right, before the error is raised; the engine can go on with other steps."""
+        self.stager.status.zero_()
+        if code == kernels.STATUS_WAIT_TIMEOUT:
+            kernels.gemm_tcgen05_reset()
+            raise StepError("a kernel gave up: " + kernels.STATUS_MESSAGES[code].format(detail=detail) + "; the results of the step are not valid")
+        raise StepError("a kernel refused " + kernels.STATUS_MESSAGES.get(code, f"status {code}").format(detail=detail))

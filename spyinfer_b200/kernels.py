@@ -20,8 +20,9 @@ STATUS_MESSAGES = {
     1: "a token id outside the vocabulary (batch token index {detail})",
     2: "a position beyond the position table (batch token index {detail})",
     3: "a block-table entry that is no page of the pool (batch token index {detail})",
-    4: "a wait inside a kernel ran out of its iteration limit (code {detail})",
+    4: "a wait inside it ran out of its time limit (code {detail})",
 }
+STATUS_WAIT_TIMEOUT = 4
 
 
 class KernelError(RuntimeError):
@@ -500,3 +501,24 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] =
           _code(out, "gemm output"), ctypes.c_longlong(n_out), M, N, K, _ptr(scratch), ctypes.c_longlong(scratch.numel()),
           1 if epilogue == "swiglu" else 0, 0, None, _ptr(status), _stream())
     return out
+
+
+def gemm_tcgen05_reset() -> None:
+    """Lowers the flags that the blocks of a product with shared K blocks signal one another by.
+    To be called after a status word of 4 (a wait ran out): the product that gave up may have left
+    flags raised, which the next such product would take for partial tiles that are ready."""
+    _call("gemm_tcgen05", "spy_gemm_tcgen05_reset", _stream())
+
+
+def wait_selftest(limit_ns: int, status: Optional[torch.Tensor] = None) -> int:
+    """Runs the kernels' bounded wait on a barrier that nothing arrives at, with ``limit_ns`` as its
+    limit (at most 100 ms).  The kernel returns by itself and leaves code 4 in the status word; the
+    nanoseconds its first thread waited are returned.  A health check of the mechanism that keeps a
+    lost signal inside a tensor-core kernel from holding the GPU."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if status is None else status.device
+    if status is None:
+        status = status_word(dev)
+    waited = torch.zeros(1, dtype=torch.int64, device=dev)
+    _call("gemm_tcgen05", "spy_tcgen05_wait_selftest", ctypes.c_ulonglong(int(limit_ns)), _ptr(status), _ptr(waited), _stream())
+    return int(waited.item())
+

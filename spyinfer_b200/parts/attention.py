@@ -83,11 +83,11 @@ class Attention(Mixer):
     def split_plan(self, num_seqs: int):
         """(split_keys, max_splits) for decoding ``num_seqs`` requests: the keys of every request
         are cut into ranges so that (requests x key/value heads x ranges) blocks fill whole waves
-        of the GPU's 2 x 148 block slots as evenly as possible; at most 16 ranges, ranges of at
+        of the GPU's block slots (two a SM) as evenly as possible; at most 16 ranges, ranges of at
         least 256 keys and a multiple of 64.  The plan depends on the (padded) batch size only."""
         plan = self._split_plans.get(num_seqs)
         if plan is None:
-            slots, per_split, best = 2 * 148, num_seqs * self.nkv, None
+            slots, per_split, best = 2 * torch.cuda.get_device_properties(self.ctx.device).multi_processor_count, num_seqs * self.nkv, None
             most = max(1, min(16, self.ctx.max_model_len // 256))
             for splits in range(1, most + 1):
                 blocks = per_split * splits

@@ -81,9 +81,13 @@ def load_checkpoint(model_dir: str, decls: Iterable[WeightDecl], device, ignorab
         if is_int != d.integer:
             wrong.append(f"{d.name}: expected {'an integer' if d.integer else 'a floating-point'} tensor, found {f.dtype(d.name)} in {f.path}")
     unexpected = sorted(n for n in where if n not in wanted and n not in set(ignorable))
-    if missing or unexpected or wrong:
-        raise WeightError(model_dir, missing, unexpected, wrong)
-    out = {}
-    for d in decls:
-        out[d.name] = _store(where[d.name].tensor(d.name), d).to(device).contiguous()
-    return out
+    try:
+        if missing or unexpected or wrong:
+            raise WeightError(model_dir, missing, unexpected, wrong)
+        out = {}
+        for d in decls:
+            out[d.name] = _store(where[d.name].tensor(d.name), d).to(device).contiguous()
+        return out
+    finally:
+        for f in files:
+            f.close()

@@ -131,6 +131,29 @@ def test_requests_without_a_token_limit_end_where_the_pool_ends(lookahead, tiny_
     assert engine.finish_reason(rid) == "out_of_pages" and [t for _, t, _ in seen] == got[0] and seen[-1][2]
 
 
+def test_a_checkpoint_stored_in_32_bit_stays_so_and_the_bfloat16_engine_says_what_that_costs(tiny_models, tmp_path):
+    import json
+    import warnings
+
+    from safetensors.torch import save_file
+
+    from spyinfer_b200 import SamplingParams
+    folder, cfg, weights = tiny_models["d"]
+    with open(tmp_path / "config.json", "w") as f:
+        json.dump(cfg, f)
+    save_file({k: v.float().contiguous() for k, v in weights.items()}, str(tmp_path / "model.safetensors"))
+    with pytest.warns(UserWarning, match="stored in 32-bit.*CUDA-core kernel"):
+        engine = engine_for(str(tmp_path), "bfloat16")
+    assert engine.model.layers[0].mixer.o.weight.dtype == torch.float32 and not engine.model.layers[0].mixer.o.fast
+    prompt = [9, 8, 7, 6, 5]
+    out = engine.generate([prompt], SamplingParams(max_new_tokens=6, ignore_eos=True))[0]
+    check_greedy(weights, cfg, prompt, out, "bfloat16")
+    with warnings.catch_warnings():
+        warnings.simplefilter("error")
+        engine_for(folder, "bfloat16")                       # the bfloat16 checkpoint: no warning
+        engine_for(str(tmp_path), "float32")                 # the 32-bit engine multiplies 32-bit matrices anyway
+
+
 def test_temperature_sampling_is_seeded_and_follows_the_distribution(tiny_models):
     from spyinfer_b200 import SamplingParams
     folder, cfg, weights = tiny_models["a"]

@@ -329,6 +329,56 @@ def test_gemm_tcgen05(out_dtype, M, N, K):
         assert torch.equal(one[0], out[M - 1])      # within a tile class a row does not depend on the batch
 
 
+@pytest.mark.parametrize("K", [4096, 5120])
+def test_gemm_tcgen05_output_head_at_its_real_size(K):
+    """The output head of the benchmark shapes: 151,936 rows (1,187 tiles of 128, no multiple of 256)
+    by 4,096 or 5,120, 32-bit logits, at every class of the number of wanted rows: one, a decoding
+    batch of 8 and of 64, a few hundred, and a whole prompt of 2,048."""
+    from spyinfer_b200 import kernels
+    N = 151936
+    torch.manual_seed(K)
+    w = (torch.randn(N, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
+    w32 = w.float()
+    status = kernels.status_word(DEV)
+    for M in (1, 8, 64, 300, 2048):
+        a = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+        out = torch.full((M, N), float("nan"), device=DEV, dtype=torch.float32)
+        kernels.gemm_tcgen05(a, w, out)
+        torch.cuda.synchronize()
+        assert status[0].item() == 0
+        ref = a.float() @ w32.t()
+        err = (out - ref).abs().max().item()
+        assert torch.isfinite(out).all() and err <= 2e-4 + 1e-4 * ref.abs().max().item(), f"M = {M}: largest error {err:.3g}"
+        # the last tile (rows 151,808 to 151,935) and the first, exactly where a tail in N would go wrong
+        torch.testing.assert_close(out[:, -128:], ref[:, -128:], rtol=1e-4, atol=2e-4)
+        del out, ref
+
+
+def test_a_wait_that_nothing_ends_gives_up_reports_and_leaves_the_engine_usable(tiny_models):
+    """The tensor-core kernels wait on barriers with a time limit.  Here a barrier that nothing ever
+    arrives at is waited on with a limit of one millisecond: the kernel returns by itself, the status
+    word says so, the step function raises, and the engine generates as before afterwards."""
+    import time
+
+    from spyinfer_b200 import LLMEngine, SamplingParams, kernels
+    from spyinfer_b200.engine import StepError
+    folder, cfg, _ = tiny_models["d"]
+    engine = LLMEngine(folder, dtype="bfloat16", max_num_seqs=2, max_model_len=64, num_kvcache_blocks=8, max_num_batched_tokens=64)
+    sp = SamplingParams(max_new_tokens=4, ignore_eos=True)
+    before = engine.generate([[5, 6, 7]], sp)
+    t0 = time.perf_counter()
+    waited = kernels.wait_selftest(1_000_000, engine.runner.stager.status)
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 1.0
+    assert 1_000_000 <= waited < 50_000_000, f"the wait took {waited} ns against a limit of 1 ms"
+    with pytest.raises(StepError, match="gave up.*time limit"):
+        engine.runner.check_status()
+    engine.runner.check_status()                          # the word is clear again
+    assert engine.generate([[5, 6, 7]], sp) == before
+    with pytest.raises(kernels.KernelError):
+        kernels.wait_selftest(10**9)                      # limits above 100 ms are refused
+
+
 def test_gemm_tcgen05_finds_one_large_product():
     """One input element and one weight element are made large: exactly one output element
     must stand out, wherever in K the pair lies (start of a 64-block, its end, the K tail)."""

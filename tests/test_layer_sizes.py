@@ -98,3 +98,32 @@ def test_layer_sizes_match_plain_under_every_cut(name, page_size, dtype, layer_m
             raise AssertionError(f"{name} {rid} ({len(toks)} tokens): first wrong position {first}, error {err[first].max():.3g} against a "
                                  f"largest logit of {scale:.3g} (allowed {tol['max_rel'] * scale:.3g})")
         assert np.sqrt((err ** 2).mean()) <= tol["rms_rel"] * rms, f"{name} {rid}: rms error {np.sqrt((err ** 2).mean()):.3g} vs rms logit {rms:.3g}"
+
+
+def test_eight_layers_at_8b_sizes_in_bfloat16_stay_within_the_bound(tmp_path, capsys):
+    """Depth: eight layers at the 8B layer sizes (the other tests run one to four), bfloat16, a
+    prompt of 64 tokens in one step and eight more tokens one by one, every row against the plain
+    implementation in 32-bit.  The error that eight layers of bfloat16 roundings build up is
+    printed and held to the bound of the one-layer tests."""
+    from safetensors.torch import save_file
+
+    cfg = dict(config_of("8b"), num_hidden_layers=8)
+    w = plain_model.random_weights(cfg, 808, 0.02, 0.05)
+    with open(tmp_path / "config.json", "w") as f:
+        json.dump(cfg, f)
+    save_file({k: v.contiguous() for k, v in w.items()}, str(tmp_path / "model.safetensors"))
+    rng = random.Random(8)
+    toks = [rng.randrange(cfg["vocab_size"]) for _ in range(72)]
+    b = TraceBuilder()
+    b.tail_one_by_one("x", toks, tail=8)
+    rows = run_trace(str(tmp_path), "bfloat16", b, str(tmp_path / "out"), peak_tokens(b), cfg["vocab_size"])
+    want = plain_model.forward_logits(w, cfg, toks).numpy()
+    got = np.stack([rows[("x", p)] for p in range(len(toks))])
+    assert np.isfinite(got).all()
+    err = np.abs(got - want)
+    scale, rms = np.abs(want).max(), np.sqrt((want ** 2).mean())
+    worst, err_rms = err.max() / scale, np.sqrt((err ** 2).mean()) / rms
+    with capsys.disabled():
+        print(f"\n  eight 8B-sized layers in bfloat16: largest error {worst:.4f} of the largest logit, rms error {err_rms:.4f} of the rms logit "
+              f"(decoded rows alone: {err[64:].max() / scale:.4f})")
+    assert worst <= TOL["bfloat16"]["max_rel"] and err_rms <= TOL["bfloat16"]["rms_rel"]
