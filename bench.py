@@ -18,16 +18,24 @@ on their content), so no prefill is timed.  One JSON line is printed:
   engine launches a decode step before it has read the step before, so the tokens a call
   returns are those of the step launched by the call before it; every step's tokens are
   read, once);
-* ``prefill``: one step of 2048 prompt tokens of one request; ``frac`` = flops / time / peak;
+* ``prefill``: one step of 2048 prompt tokens of one request; ``frac`` = flops / time / the bf16
+  peak of a kernel timed alone (the burst figure), ``frac_sustained`` the same against the rate a
+  seconds-long loop of products holds under the power cap;
 * ``roofline``: bytes the decode step has to read (every weight it uses once, and the cache
   of the live requests) / its time, against the measured copy bandwidth;
-* ``points``: decoding at batch 1 and 64 (same context), and at the context of about 640
-  tokens that the reference workload "prompts of 512, 256 generated tokens" averages;
+* ``points``: tokens a second of decoding at batch 1 and 64 (same context), and at the context of
+  about 640 tokens that the reference workload "prompts of 512, 256 generated tokens" averages;
+  ``points_detail`` gives each of them its ``ms_per_step`` and its own ``roofline`` block;
+* ``kernels``: each dominant kernel alone at the step's sizes, timed by CUDA events around a loop that
+  walks through the layers' own weights (far more than L2 holds): the q|k|v, o, gate|up and down
+  products and the output head at the decoding batch, at batch 64 and at 2048 tokens, the decode
+  attention at batch 64 and the prompt attention at 2048 tokens, each with microseconds, achieved
+  GB/s (decoding: the bytes it has to read and write) or TFLOP/s (prompt) and the fraction of the
+  measured copy bandwidth or of the bf16 burst peak;
 * ``clocks``: SM clocks and throttle reasons sampled with nvidia-smi during the timed region.
 
-Peaks come from MEASURED_PEAKS.json beside this file when it exists (the copy bandwidth, and for the
-prefill, a long step under the power cap, the sustained bf16 rate if the file has one), else 6.65 TB/s
-and 1.59 PFLOP/s.  ``--gpus N`` with N > 1 prints one line saying that this engine is
+Peaks come from MEASURED_PEAKS.json beside this file when it exists (``hbm_gbs``, ``bf16_tflops``,
+``bf16_tflops_sustained``), else 6.65 TB/s and 1.59 PFLOP/s (sustained: 1.4).  ``--gpus N`` with N > 1 prints one line saying that this engine is
 single-GPU and exits with 2.  ``--impl reference`` prints why the reference cannot run here.
 """
 from __future__ import annotations
@@ -59,24 +67,99 @@ REFERENCE_UNAVAILABLE = ("spymaster2h/spyinfer is a C++/xmake project without a 
 
 
 def peaks():
-    """Copy bandwidth (GB/s) and bf16 product rate (TFLOP/s) the fractions are taken against.  From
-    MEASURED_PEAKS.json when it exists: ``hbm_gbs`` and, for the prefill (a step of tens of
-    milliseconds under the power cap), ``bf16_tflops_sustained`` if the file has it, else the burst
-    figure ``bf16_tflops``.  Else 6.65 TB/s and 1.59 PFLOP/s."""
+    """Copy bandwidth (GB/s), bf16 product rate of a kernel timed alone and of a seconds-long loop under
+    the power cap (TFLOP/s), and where they come from: MEASURED_PEAKS.json beside this file when it
+    exists (``hbm_gbs``, ``bf16_tflops``, ``bf16_tflops_sustained``), else 6.65 TB/s, 1.59 and 1.4 PFLOP/s."""
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    hbm, flops, src = 6650.0, 1590.0, "fallback"
+    hbm, burst, sustained, src = 6650.0, 1590.0, 1400.0, "fallback"
     if os.path.isfile(path):
         try:
             with open(path) as f:
                 d = json.load(f)
             hbm = float(d.get("hbm_gbs", hbm))
-            if d.get("bf16_tflops_sustained"):
-                flops, src = float(d["bf16_tflops_sustained"]), "measured (bf16 sustained)"
-            else:
-                flops, src = float(d.get("bf16_tflops", flops)), "measured"
+            burst = float(d.get("bf16_tflops", burst))
+            sustained = float(d.get("bf16_tflops_sustained") or burst)
+            src = "measured"
         except (ValueError, OSError, TypeError):
             pass
-    return hbm, flops, src
+    return hbm, burst, sustained, src
+
+
+def kernel_rooflines(engine, batches, prompt_tokens, hbm_gbs, bf16_tflops, page):
+    """Each dominant kernel alone, at the sizes it has inside the benchmark's steps.
+
+    The products are called exactly as the model's parts call them (same plans, epilogues and
+    deferred reductions), through the layers' own ``Linear`` objects, one layer after the other, so
+    that every call reads weights that no earlier call left in L2; the attention kernels run on a
+    cache of their own of the stated length.  Decoding sizes are read against the copy bandwidth
+    (bytes = the weight or the cache read once, plus activations in and out), 2,048 tokens against
+    the bf16 peak of a kernel timed alone."""
+    import torch
+
+    from spyinfer_b200 import microbench
+
+    model = engine.model
+    layers = model.layers
+    dev = engine.config.device
+    out = {}
+
+    def timed(calls, reps):
+        """Microseconds a call.  The calls are captured into a CUDA graph and replayed, as the engine
+        replays its decode steps: the time is the device's, without the host's launch cost."""
+        for f in calls[:2]:
+            f()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for f in calls:
+                f()
+        graph.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / (reps * len(calls))
+
+    def product(name, linears, M, epilogue=None, defer=False, out_dtype=None, reps=3):
+        K, N = linears[0].in_features, linears[0].out_features
+        x = torch.randn(M, K, device=dev).to(torch.bfloat16)
+        calls = [(lambda lin=lin: lin(x, epilogue=epilogue, defer=defer, out_dtype=out_dtype)) for lin in linears]
+        if len(calls) == 1:
+            calls = calls * 8               # the head: one matrix, itself ten times L2
+        us = timed(calls, reps)
+        n_out = N // 2 if epilogue == "swiglu" else N
+        nbytes = 2 * N * K + 2 * M * K + M * n_out * (4 if out_dtype == torch.float32 else 2)
+        flops = 2.0 * M * N * K
+        rec = {"us": round(us, 2)}
+        if M <= 256:
+            gbs = nbytes / us / 1e3
+            rec.update(achieved=round(gbs, 1), unit="GB/s", frac=round(gbs / hbm_gbs, 4))
+        else:
+            tf = flops / us / 1e6
+            rec.update(achieved=round(tf, 1), unit="TFLOP/s", frac=round(tf / bf16_tflops, 4))
+        out[name] = rec
+
+    sizes = [(f"b{b}", b) for b in batches] + [(f"t{prompt_tokens}", prompt_tokens)]
+    for tag, M in sizes:
+        product(f"qkv_{tag}", [l.mixer.qkv for l in layers], M, defer=True)
+        product(f"o_{tag}", [l.mixer.o for l in layers], M, defer=True)
+        product(f"gate_up_{tag}", [l.feed_forward.gate_up for l in layers], M, epilogue="swiglu")
+        product(f"down_{tag}", [l.feed_forward.down for l in layers], M, defer=True)
+    for tag, M in sizes[:-1]:
+        product(f"lm_head_{tag}", [model.head.linear], M, out_dtype=torch.float32)
+    spec = layers[0].mixer
+    nh, nkv, hd = spec.nh, spec.nkv, spec.hd
+    for context in (640, 8192):
+        r = microbench.bench_attention(64, context, nh=nh, nkv=nkv, hd=hd, page_size=page, kernel="decode", iters=20, graph=True)
+        out[f"attention_decode_b64_ctx{context}"] = {"us": round(r["us"], 2), "achieved": round(r["kv_gbs"], 1), "unit": "GB/s",
+                                                      "frac": round(r["kv_gbs"] / hbm_gbs, 4)}
+    r = microbench.bench_attention(1, prompt_tokens, q_len=prompt_tokens, nh=nh, nkv=nkv, hd=hd, page_size=page, kernel="tc", iters=20, graph=True)
+    out[f"attention_prompt_t{prompt_tokens}"] = {"us": round(r["us"], 2), "achieved": round(r["tflops"], 1), "unit": "TFLOP/s",
+                                                  "frac": round(r["tflops"] / bf16_tflops, 4)}
+    return out
 
 
 class ClockSampler:
@@ -190,6 +273,7 @@ def main() -> int:
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1/64 and short-context points")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel rooflines")
     ap.add_argument("--workload", default="decode", choices=["decode", "mixed"],
                     help="decode: the contract's line (default); mixed: a continuous batch of --requests requests with prompts of 64 to 2,048 "
                          "tokens and 128 generated tokens each through LLMEngine, its own line")
@@ -209,7 +293,7 @@ def main() -> int:
     from spyinfer_b200 import SamplingParams, config_from_json, kernels
     from spyinfer_b200.engine import LLMEngine, StepEntry
 
-    hbm_gbs, bf16_tflops, peak_src = peaks()
+    hbm_gbs, bf16_tflops, bf16_sustained, peak_src = peaks()
     cfg_json = dict(QWEN3_8B)
     cfg_json.update(SHAPES[args.shape])
     full_layers = cfg_json["num_hidden_layers"]
@@ -332,7 +416,8 @@ def main() -> int:
         runner.check_status()
         flops = 2.0 * tokens * layers * layer_params + 2.0 * V * H + layers * 4.0 * nh * hd * tokens * (tokens + 1) / 2
         return {"value": round(tokens / (best / 1e3), 1), "tokens": tokens, "ms": round(best, 3),
-                "frac": round(flops / (best / 1e3) / (bf16_tflops * 1e12), 4), "peak_tflops": bf16_tflops}
+                "frac": round(flops / (best / 1e3) / (bf16_tflops * 1e12), 4), "peak_tflops": bf16_tflops,
+                "frac_sustained": round(flops / (best / 1e3) / (bf16_sustained * 1e12), 4), "peak_tflops_sustained": bf16_sustained}
 
     with ClockSampler() as clocks:
         value, ms_per_step, launches = decode_device(args.batch, ctx, args.steps, warmup)
@@ -357,12 +442,24 @@ def main() -> int:
         e2e, h2d, d2h = decode_e2e(args.batch, ctx, args.steps, warmup)
         out["e2e"] = {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
     if not args.no_points:
-        points = {}
+        points, detail = {}, {}
+
+        def point(name, b, context):
+            tps, ms, _ = decode_device(b, context, args.steps, warmup)
+            nbytes = weight_bytes + kv_bytes_per_token * (context - args.steps // 2) * b
+            gbs = nbytes / (ms / 1e3) / 1e9
+            points[name] = round(tps, 1)
+            detail[name] = {"value": round(tps, 1), "ms_per_step": round(ms, 4), "batch": b, "context": context,
+                            "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": hbm_gbs, "unit": "GB/s", "frac": round(gbs / hbm_gbs, 4)}}
+
         for b in points_batches:
-            points[f"decode_b{b}"] = round(decode_device(b, ctx, args.steps, warmup)[0], 1)
+            point(f"decode_b{b}", b, ctx)
         for b in (1, 8) + points_batches[1:]:
-            points[f"decode_b{b}_ctx640"] = round(decode_device(b, 640 + (args.steps + warmup) // 2, args.steps, warmup)[0], 1)
+            point(f"decode_b{b}_ctx640", b, 640 + (args.steps + warmup) // 2)
         out["points"] = points
+        out["points_detail"] = detail
+    if not args.no_kernels:
+        out["kernels"] = kernel_rooflines(engine, sorted({args.batch, 64}), args.prefill_tokens, hbm_gbs, bf16_tflops, page)
     print(json.dumps(out))
     return 0
 

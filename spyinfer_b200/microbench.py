@@ -1,4 +1,4 @@
-"""Timings of single kernels at chosen sizes, for profiling and for the summaries under profiles/.
+"""Timings of single kernels at chosen sizes.
 
     python -m spyinfer_b200.microbench gemm --m 2048 --n 24576 --k 4096 [--out-dtype float32] [--iters 20]
     python -m spyinfer_b200.microbench attention --batch 8 --context 8192 [--q-len 1] [--split-keys 576] [--kernel tc|mma|decode] [--iters 10]
