@@ -36,7 +36,8 @@ on their content), so no prefill is timed.  One JSON line is printed:
 
 Peaks come from MEASURED_PEAKS.json beside this file when it exists (``hbm_gbs``, ``bf16_tflops``,
 ``bf16_tflops_sustained``), else 6.65 TB/s and 1.59 PFLOP/s (sustained: 1.4).  ``--gpus N`` with N > 1 prints one line saying that this engine is
-single-GPU and exits with 2.  ``--impl reference`` prints why the reference cannot run here.
+single-GPU and exits with 2.  ``--impl reference`` runs the unmodified reference's CUDA decode path on the same shape,
+batch, context and steps (see ``reference_arm``) and prints the same line with ``"impl": "reference"``.
 """
 from __future__ import annotations
 
@@ -61,9 +62,94 @@ SHAPES = {
     "14b": {"num_hidden_layers": 40, "hidden_size": 5120, "num_attention_heads": 40, "intermediate_size": 17408},
     "32b": {"num_hidden_layers": 64, "hidden_size": 5120, "num_attention_heads": 64, "intermediate_size": 25600},
 }
-REFERENCE_UNAVAILABLE = ("spymaster2h/spyinfer is a C++/xmake project without a Python package: pip cannot install it offline "
-                         "(no setup.py or pyproject.toml), xmake is not in the image, and its CUDA path cannot hold a step of 100 or "
-                         "more tokens or a cache of more than 400 tokens")
+
+
+def reference_arm(args) -> int:
+    """``--impl reference``: the unmodified reference on its own CUDA backend, same model shape, batch,
+    context, page size and number of steps.
+
+    spymaster2h/spyinfer is a C++/xmake project, no Python package, so it is built by hand from its
+    own sources (``baseline/build_reference.py``: nvcc and the host compiler over the file list of its
+    xmake target, cuBLAS) into ``baseline/_ref`` together with ``baseline/reference_decode.cpp``, which
+    drives its stock ``Qwen3::forward`` and ``compute_logits`` on ``CUDABackend`` for decoding steps and
+    does with the logits what its ``ModelRunner`` does (copy to the host, widen, argmax).  The model is
+    a seeded random bfloat16 checkpoint of the benchmark's shape, written in shards as checkpoints of
+    this size are; the reference converts it to float16 at load.  What cannot be had from it: a prompt
+    step of 100 or more tokens (its scratch holds 100 rows), hence no ``prefill`` block, and batches of
+    100 or more.  If the build fails the line says ``unavailable`` with the compiler's message."""
+    import tempfile
+
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    try:
+        import build_reference
+        exe = build_reference.build(os.environ.get("SPYINFER_REFERENCE", build_reference.DEFAULT_REFERENCE))
+    except Exception as e:                                              # noqa: BLE001: whatever stops the build is the reason
+        print(json.dumps({"impl": "reference", "unavailable": "the hand build of the reference failed: " + " ".join(str(e).split())[-600:]}))
+        return 0
+    if args.gpus != 1:
+        print(json.dumps({"impl": "reference", "unavailable": "the reference runs on one GPU (devices_[0]); --gpus %d has no meaning for it" % args.gpus}))
+        return 0
+    import torch
+
+    from spyinfer_b200 import config_from_json
+    from spyinfer_b200.weights import write_model_folder
+
+    hbm_gbs, _, _, peak_src = peaks()
+    cfg_json = dict(QWEN3_8B)
+    cfg_json.update(SHAPES[args.shape])
+    full_layers = cfg_json["num_hidden_layers"]
+    layers = args.layers or full_layers
+    cfg_json["num_hidden_layers"] = layers
+    c = config_from_json(cfg_json)
+    H, I, V, nh, nkv, hd = c.hidden_size, c.intermediate_size, c.vocab_size, c.num_attention_heads, c.num_key_value_heads, c.head_dim
+    weight_bytes = 2 * (layers * (H * (nh + 2 * nkv) * hd + nh * hd * H + 3 * H * I) + V * H)
+    kv_bytes_per_token = 2 * 2 * nkv * hd * layers
+    warmup, page, ctx = max(3, args.warmup), 16, args.context
+    short = 640 + (args.steps + warmup) // 2
+    point_steps = min(args.steps, 10)
+    works = [(args.batch, ctx, args.steps)]
+    if not args.no_points:
+        works += [(1, ctx, point_steps), (64, ctx, point_steps), (1, short, point_steps), (8, short, point_steps), (64, short, point_steps)]
+    with tempfile.TemporaryDirectory(prefix="reference_model_") as model_dir:
+        write_model_folder(model_dir, c, 0, shard_bytes=3 << 30, device="cuda:0" if torch.cuda.is_available() else "cpu")
+        torch.cuda.empty_cache()
+        with ClockSampler() as clocks:
+            proc = subprocess.run([exe, model_dir, str(page), str(warmup)] + [f"{b}x{n}x{k}" for b, n, k in works], capture_output=True, text=True)
+    lines = [json.loads(l) for l in proc.stdout.splitlines() if l.startswith("{")]
+    if proc.returncode != 0 or len(lines) != len(works):
+        print(json.dumps({"impl": "reference", "unavailable": f"the reference's decode run ended with code {proc.returncode}: "
+                          + " ".join((proc.stderr or proc.stdout).split())[-400:]}))
+        return 0
+    main_run = lines[0]
+
+    def roofline(r):
+        nbytes = weight_bytes + kv_bytes_per_token * (r["context"] - r["steps"] // 2) * r["batch"]
+        gbs = nbytes / (r["ms_per_step"] / 1e3) / 1e9
+        return {"bound": "hbm", "achieved": round(gbs, 1), "peak": hbm_gbs, "unit": "GB/s", "frac": round(gbs / hbm_gbs, 4)}
+
+    out = {"impl": "reference",
+           "metric": f"decode tokens/s (Qwen3-{args.shape.upper()} shape, bf16, batch {args.batch}, context {ctx})", "value": round(main_run["tokens_per_s"], 1),
+           "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup, "ms_per_step": round(main_run["ms_per_step"], 4),
+           "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp16 (the reference converts the bf16 checkpoint at load)",
+           "data": "synthetic: seeded random weights, token ids from the model's own argmax, zeroed cache of the stated context length",
+           "config": {"model": f"Qwen3-{args.shape.upper()} shape", "num_layers": layers, "num_layers_full": full_layers, "hidden_size": H,
+                      "num_attention_heads": nh, "num_key_value_heads": nkv, "head_dim": hd, "intermediate_size": I, "vocab_size": V,
+                      "global_batch": args.batch, "seq_len": ctx, "page_size": page, "parallelism": "single GPU",
+                      "l2": "inputs (weights and cache) exceed L2 many times", "peaks": peak_src,
+                      "api": "Qwen3::forward + compute_logits on CUDABackend, logits to the host and argmax as ModelRunner does; "
+                             "LLMEngine takes text through a tokenizer, and execute_model reads freed host memory on CUDA"},
+           "gpu_launches": None, "roofline": roofline(main_run), "clocks": clocks.summary(),
+           "e2e": {"value": round(main_run["wall_tokens_per_s"], 1), "unit": "tokens/s", "h2d_bytes_per_step": main_run["h2d_bytes_per_step"],
+                   "d2h_bytes_per_step": main_run["d2h_bytes_per_step"]},
+           "prefill": {"unavailable": "a step of 100 or more tokens overruns the reference's scratch (src/models/qwen3.hpp:13, 97)"}}
+    if len(lines) > 1:
+        names = ["decode_b1", "decode_b64", "decode_b1_ctx640", "decode_b8_ctx640", "decode_b64_ctx640"]
+        out["points"] = {n: round(r["tokens_per_s"], 1) for n, r in zip(names, lines[1:])}
+        out["points_detail"] = {n: {"value": round(r["tokens_per_s"], 1), "ms_per_step": round(r["ms_per_step"], 4), "batch": r["batch"],
+                                    "context": r["context"], "steps": r["steps"], "roofline": roofline(r)} for n, r in zip(names, lines[1:])}
+    print(json.dumps(out))
+    return 0
+
 
 
 def peaks():
@@ -281,8 +367,7 @@ def main() -> int:
     ap.add_argument("--budget", type=int, default=2048, help="mixed workload: max_num_batched_tokens")
     args = ap.parse_args()
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
-        return 0
+        return reference_arm(args)
     if args.gpus != 1:
         print(json.dumps({"error": f"this engine runs on one GPU; --gpus {args.gpus} is not supported", "n_gpus": args.gpus}))
         return 2

@@ -47,14 +47,41 @@ def random_tensors(decls: Iterable[WeightDecl], seed: int, std: float = 0.02, no
         yield d.name, random_tensor(d, seed, std, norm_std, device)
 
 
-def write_model_folder(model_dir: str, config, seed: int, std: float = 0.02, norm_std: float = 0.05) -> None:
-    """``config`` is an ``ArchitectureConfig``; the folder gets its config.json and one
-    model.safetensors with every tensor the model declares."""
+def write_model_folder(model_dir: str, config, seed: int, std: float = 0.02, norm_std: float = 0.05, shard_bytes: int = 0,
+                       device="cpu") -> None:
+    """``config`` is an ``ArchitectureConfig``; the folder gets its config.json and every tensor the
+    model declares: in one model.safetensors, or, with ``shard_bytes``, in files of about that size
+    (a tensor is never cut) named by a model.safetensors.index.json, as large checkpoints are
+    stored.  ``device``: where the values are drawn (see the module's header: CPU and CUDA draw
+    different values from one seed)."""
     from ..engine.model import declared_weights  # late: the engine imports this package
 
     os.makedirs(model_dir, exist_ok=True)
     with open(os.path.join(model_dir, "config.json"), "w") as f:
         json.dump(config.to_json(), f, indent=1)
     decls = declared_weights(config.to_spec())
-    layout = [(d.name, torch.bfloat16, tuple(d.shape)) for d in decls]
-    write_safetensors(os.path.join(model_dir, "model.safetensors"), layout, random_tensors(decls, seed, std, norm_std, "cpu"))
+
+    def nbytes(d):
+        n = 2
+        for k in d.shape:
+            n *= int(k)
+        return n
+
+    shards, size = [[]], 0
+    for d in decls:
+        if shard_bytes and shards[-1] and size + nbytes(d) > shard_bytes:
+            shards.append([])
+            size = 0
+        shards[-1].append(d)
+        size += nbytes(d)
+    if len(shards) == 1:
+        names = ["model.safetensors"]
+    else:
+        names = [f"model-{i + 1:05d}-of-{len(shards):05d}.safetensors" for i in range(len(shards))]
+        index = {"metadata": {"total_size": sum(nbytes(d) for d in decls)},
+                 "weight_map": {d.name: name for name, part in zip(names, shards) for d in part}}
+        with open(os.path.join(model_dir, "model.safetensors.index.json"), "w") as f:
+            json.dump(index, f, indent=1)
+    for name, part in zip(names, shards):
+        layout = [(d.name, torch.bfloat16, tuple(d.shape)) for d in part]
+        write_safetensors(os.path.join(model_dir, name), layout, random_tensors(part, seed, std, norm_std, device))

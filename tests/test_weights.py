@@ -131,3 +131,22 @@ def test_random_model_folder_is_seeded_and_loads(tmp_path):
     # a tensor's values do not depend on the other tensors of the model
     alone = dict(random_tensors([d for d in decls if d.name == "model.norm.weight"], 5, 0.03, 0.1))
     assert torch.equal(alone["model.norm.weight"], a["model.norm.weight"])
+
+
+def test_random_model_folder_in_shards_reads_back_as_the_single_file_does(tmp_path):
+    """``write_model_folder`` with ``shard_bytes``: several files and an index, no tensor cut, and the
+    loader finds in them exactly the tensors of the one-file folder of the same seed."""
+    from spyinfer_b200.config import config_from_json
+    from spyinfer_b200.engine.model import declared_weights
+    from spyinfer_b200.weights import write_model_folder
+    from conftest import TINY
+
+    cfg = config_from_json(TINY["b"]["config"])
+    write_model_folder(str(tmp_path / "one"), cfg, 3, 0.03, 0.1)
+    write_model_folder(str(tmp_path / "many"), cfg, 3, 0.03, 0.1, shard_bytes=60000)
+    files = sorted(p.name for p in (tmp_path / "many").iterdir())
+    assert "model.safetensors.index.json" in files and len([f for f in files if f.endswith(".safetensors")]) > 3
+    decls = declared_weights(cfg.to_spec())
+    one = load_checkpoint(str(tmp_path / "one"), decls, "cpu")
+    many = load_checkpoint(str(tmp_path / "many"), decls, "cpu")
+    assert one.keys() == many.keys() and all(torch.equal(one[k], many[k]) for k in one)
