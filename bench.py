@@ -314,6 +314,7 @@ def mixed_workload(args, model_config, layers, full_layers, page) -> int:
     sp = SamplingParams(max_new_tokens=new_tokens, ignore_eos=True)
     result = None
     for run in range(2):
+        engine.runner.step_events = []
         with ClockSampler() as clocks:
             torch.cuda.synchronize()
             t0 = time.perf_counter()
@@ -330,6 +331,13 @@ def mixed_workload(args, model_config, layers, full_layers, page) -> int:
         assert generated == n_req * new_tokens, (generated, n_req * new_tokens)
         for rid in ids:
             engine.remove_request(rid)
+        # the device's share of the time: each step's launches lie between two events on the stream; an event is stamped
+        # when the stream reaches it, so the time between one step's last and the next step's first event is time the
+        # device waited for the host
+        pairs = engine.runner.step_events
+        busy_ms = sum(a.elapsed_time(b) for a, b in pairs)
+        span_ms = pairs[0][0].elapsed_time(pairs[-1][1])
+
         ttft = sorted(first_token_at.values())
         result = {"metric": f"generated tokens/s, mixed continuous batch (Qwen3-{args.shape.upper()} shape, bf16, {n_req} requests, prompts 64..2048, "
                             f"{new_tokens} generated each)", "value": round(generated / seconds, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps,
@@ -341,7 +349,9 @@ def mixed_workload(args, model_config, layers, full_layers, page) -> int:
                              "timing": "host clock around the whole loop, device idle on both sides"},
                   "total_tokens_per_s": round((sum(lengths) + generated) / seconds, 1), "seconds": round(seconds, 3),
                   "first_token_s": {"median": round(ttft[len(ttft) // 2], 3), "max": round(ttft[-1], 3)},
-                  "preemptions": engine.scheduler.num_preemptions, "clocks": clocks.summary()}
+                  "preemptions": engine.scheduler.num_preemptions, "clocks": clocks.summary(),
+                  "device_busy": {"busy_ms": round(busy_ms, 1), "span_ms": round(span_ms, 1), "frac": round(busy_ms / span_ms, 4),
+                                  "how": "CUDA events before the first and after the last launch of every step; busy = sum over steps, span = first to last event"}}
     print(json.dumps(result))
     return 0
 

@@ -115,7 +115,7 @@ template <int BN, typename TC, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 2)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, TC* __restrict__ out,
                     long long ld, long long split_stride, int x_rows, int y_rows, int k_blocks, int k_blocks_per_split, int tile_rows,
-                    int* status)
+                    int* status, const uint8_t* __restrict__ next_weights, long long next_bytes)
 {
     using T = Tile<BN>;
     extern __shared__ uint8_t smem_raw[];
@@ -187,6 +187,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 if (++s == stages) {
                     s = 0;
                     phase ^= 1;
+                }
+            }
+            // Every load of this block has been requested.  What follows this product in a decode step is a
+            // stretch of short kernels (a norm, the q/k rotation, the attention's start) that move few bytes
+            // and leave the memory idle, and then a product whose weights are known now: this block asks for
+            // its share of them to be brought into L2 meanwhile.  A hint only: nothing waits for it.
+            if (next_bytes > 0) {
+                const long long blocks = (long long)gridDim.x * gridDim.y * gridDim.z;
+                const long long me = blockIdx.x + (long long)gridDim.x * (blockIdx.y + (long long)gridDim.y * blockIdx.z);
+                const long long share = ((next_bytes + blocks - 1) / blocks + 127) / 128 * 128;
+                long long at = me * share;
+                const long long end = at + share < next_bytes ? at + share : next_bytes;
+                for (; at < end; at += 16384) {
+                    const long long n = end - at < 16384 ? end - at : 16384;
+                    l2_prefetch(next_weights + at, (uint32_t)(n & ~15LL));
                 }
             }
         }
@@ -890,7 +905,7 @@ static int reduce_splits(const float* scratch, void* C, int c_dtype, long long l
 
 template <int BN, typename TC, int EPI>
 static int launch(const CUtensorMap& mx, const CUtensorMap& my, void* out, long long ld, long long split_stride, int x_rows, int y_rows,
-                  int k_blocks, int splits, int tile_rows, int* status, cudaStream_t stream)
+                  int k_blocks, int splits, int tile_rows, int* status, cudaStream_t stream, const void* next_weights, long long next_bytes)
 {
     using T = Tile<BN>;
     auto kernel = gemm_tcgen05_kernel<BN, TC, EPI>;
@@ -901,7 +916,7 @@ static int launch(const CUtensorMap& mx, const CUtensorMap& my, void* out, long 
     dim3 grid((y_rows + BN - 1) / BN, (x_rows + tile_rows - 1) / tile_rows, splits);   // token tiles fastest
     if (grid.y > 65535 || grid.z > 65535) SPY_FAIL("gemm_tcgen05: the grid %u x %u x %u exceeds the launch limits", grid.x, grid.y, grid.z);
     spy_launch(kernel, grid, dim3(NUM_THREADS), T::SMEM, stream, mx, my, (TC*)out, ld, split_stride, x_rows, y_rows, k_blocks, per_split, tile_rows,
-               status);
+               status, (const uint8_t*)next_weights, next_bytes);
     SPY_CHECK_LAUNCH("gemm_tcgen05");
     return 0;
 }
@@ -1005,10 +1020,17 @@ extern "C" int spy_gemm_tcgen05_plan(int M, int N, int K, long long scratch_limi
 // epilogue 1 (SwiGLU): W's rows alternate gate and up rows, C is [M, N / 2], K is not split.
 // defer_reduce: when the plan splits K, the partial products stay in scratch as
 // [splits][M][N] floats for the consumer to sum (C is not written); *splits_used tells.
+// next_weights / next_bytes (may be null / 0; used by products of up to 256 tokens only): memory that a
+// later kernel of the stream will read, typically the next product's weights; the blocks ask for it to
+// be brought into L2 once their own loads are requested.  16-byte aligned.
 extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, long long ldw, void* C, int c_dtype, long long ldc, int M, int N,
                                    int K, float* scratch, long long scratch_floats, int epilogue, int defer_reduce, int* splits_used,
-                                   int* status, cudaStream_t stream)
+                                   int* status, cudaStream_t stream, const void* next_weights, long long next_bytes)
 {
+    if (next_weights == nullptr || next_bytes <= 0 || (reinterpret_cast<uintptr_t>(next_weights) & 15)) {
+        next_weights = nullptr;
+        next_bytes = 0;
+    }
     if (splits_used) *splits_used = 1;
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 != 0) SPY_FAIL("gemm_tcgen05: K %d must be a positive multiple of 8 (16-byte rows for TMA)", K);
@@ -1140,9 +1162,9 @@ extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, 
     if (!swap) SPY_FAIL("gemm_tcgen05: no kernel was chosen for M=%d N=%d K=%d (splits %d)", M, N, K, splits);
     int rc;
 #define SPY_LAUNCH(BN_)                                                                                                             \
-    rc = epilogue == 1 ? launch<BN_, bf16, 1>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, plan.tile_rows, status, stream)   \
-         : f32_out     ? launch<BN_, float, 0>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, plan.tile_rows, status, stream)  \
-                       : launch<BN_, bf16, 0>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, plan.tile_rows, status, stream)
+    rc = epilogue == 1 ? launch<BN_, bf16, 1>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, plan.tile_rows, status, stream, next_weights, next_bytes)   \
+         : f32_out     ? launch<BN_, float, 0>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, plan.tile_rows, status, stream, next_weights, next_bytes)  \
+                       : launch<BN_, bf16, 0>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, plan.tile_rows, status, stream, next_weights, next_bytes)
     if (bn == 16) SPY_LAUNCH(16);
     else if (bn == 32) SPY_LAUNCH(32);
     else SPY_LAUNCH(64);
@@ -1157,7 +1179,7 @@ extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, 
 extern "C" int spy_gemm_tcgen05(const void* A, long long lda, const void* W, long long ldw, void* C, int c_dtype, long long ldc, int M, int N,
                                 int K, float* scratch, long long scratch_floats, int* status, cudaStream_t stream)
 {
-    return spy_gemm_tcgen05_ex(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, scratch, scratch_floats, 0, 0, nullptr, status, stream);
+    return spy_gemm_tcgen05_ex(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, scratch, scratch_floats, 0, 0, nullptr, status, stream, nullptr, 0);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -85,6 +85,13 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
         : "memory");
 }
 
+// Asks the memory system to bring `bytes` (a multiple of 16, from a 16-byte aligned address) into
+// L2.  A hint: nothing waits for it and nothing is written to the SM.
+__device__ __forceinline__ void l2_prefetch(const void* p, uint32_t bytes)
+{
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* src, bool valid)
 {
     const int bytes = valid ? 16 : 0;   // 0 source bytes: the 16 bytes are filled with zeros

@@ -71,6 +71,10 @@ class Model:
         self.final_norm.bind(sub(self.final_norm, ""))
         head_names = {d.name for d in self.head.weight_decls()} | {getattr(self.head, "weight_name", None)} - {None}
         self.head.bind({n: tensors[n] for n in head_names if n in tensors})
+        # every product learns which weight the step reads after its own (the hint is a weight's address, nothing else)
+        chain = [lin for e in self.spec.run_order for part in self.layers[e.layer].parts() for lin in part.linears()] + self.head.linears()
+        for lin, following in zip(chain, chain[1:]):
+            lin.next_weight = following.weight
         build.ensure_built(self.kernel_modules())
 
     def load(self, model_dir: str) -> None:

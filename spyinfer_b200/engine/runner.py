@@ -49,6 +49,10 @@ class ModelRunner:
         self._read_turn = 0
         self._graphs = {}          # decode batch size (padded) -> (graph, logits, kernel launches it holds)
         self._use_graphs = bool(config.use_cuda_graphs) and model.graph_safe()
+        #: set to a list to have every step append a pair of CUDA events (timing enabled) recorded
+        #: before its first and after its last launch: the sum of the pairs' times against the span
+        #: from the first to the last event is the share of the time the device was at work
+        self.step_events: Optional[list] = None
 
     def _pages_from_free_memory(self, needs) -> int:
         per_page = CacheManager.bytes_per_page(needs, self.config.kvcache_block_size, self.model.ctx.dtype)
@@ -157,6 +161,16 @@ class ModelRunner:
         This is how a decode step is launched before the host knows what the last one sampled."""
         if not entries:
             return None
+        if self.step_events is None:
+            return self._step(entries, tokens_from)
+        pair = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+        pair[0].record()
+        logits = self._step(entries, tokens_from)
+        pair[1].record()
+        self.step_events.append(pair)
+        return logits
+
+    def _step(self, entries: Sequence[StepEntry], tokens_from: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         if tokens_from is not None and any(len(e.tokens) != 1 for e in entries):
             raise StepError("tokens_from needs entries of one token each")
         if self._use_graphs and all(len(e.tokens) == 1 and len(e.want) == 1 and int(e.want[0]) == 0 for e in entries):

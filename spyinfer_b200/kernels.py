@@ -458,14 +458,18 @@ def _scratch(device) -> torch.Tensor:
 
 
 def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None,
-                 out_dtype: Optional[torch.dtype] = None, epilogue: Optional[str] = None, defer: bool = False) -> torch.Tensor:
+                 out_dtype: Optional[torch.dtype] = None, epilogue: Optional[str] = None, defer: bool = False,
+                 prefetch: Optional[torch.Tensor] = None, prefetch_bytes: int = 0) -> torch.Tensor:
     """``a[M, K] @ w[N, K]^T`` on the tensor cores: bfloat16 operands, 32-bit accumulation,
     bfloat16 or float32 output.  K must be a multiple of 8.
 
     ``epilogue="swiglu"``: ``w``'s rows alternate gate and up rows and the result is
     ``silu(gate) * up``, ``[M, N / 2]``.  ``defer=True``: when the kernel splits K, the float32
     partial products are returned unsummed as ``[splits, M, N]`` for a consumer that adds them
-    (``rmsnorm``'s delta, ``qk_rope_store``'s input); otherwise the result is ``[M, N]``."""
+    (``rmsnorm``'s delta, ``qk_rope_store``'s input); otherwise the result is ``[M, N]``.
+    ``prefetch``: a tensor that a later kernel will read (the next product's weights); with up to 256
+    rows in ``a`` the blocks ask for its first ``prefetch_bytes`` bytes (0: all) to be brought into L2
+    once their own loads are on their way."""
     _check(a, "gemm input", torch.bfloat16, 2)
     _check(w, "gemm weight", torch.bfloat16, 2)
     M, K = a.shape
@@ -478,6 +482,10 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] =
     if status is None:
         status = status_word(a.device)
     lib = build.load("gemm_tcgen05")
+    pf_ptr, pf_bytes = None, 0
+    if prefetch is not None and M <= 256:
+        total = prefetch.numel() * prefetch.element_size()
+        pf_ptr, pf_bytes = _ptr(prefetch), min(total, prefetch_bytes) if prefetch_bytes > 0 else total
     if defer and epilogue is None and out is None:
         splits, need = ctypes.c_int(1), ctypes.c_longlong(0)
         lib.spy_gemm_tcgen05_plan(M, N, K, ctypes.c_longlong(1 << 40), ctypes.byref(splits), ctypes.byref(need))
@@ -486,7 +494,7 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] =
             used = ctypes.c_int(0)
             _call("gemm_tcgen05", "spy_gemm_tcgen05_ex", _ptr(a), ctypes.c_longlong(K), _ptr(w), ctypes.c_longlong(K), None, BF16,
                   ctypes.c_longlong(N), M, N, K, _ptr(stack), ctypes.c_longlong(stack.numel()), 0, 1, ctypes.byref(used), _ptr(status),
-                  _stream())
+                  _stream(), pf_ptr, ctypes.c_longlong(pf_bytes))
             if used.value != splits.value:
                 raise KernelError(f"gemm: planned {splits.value} splits, the kernel used {used.value}")
             return stack
@@ -499,7 +507,7 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] =
     scratch = _scratch(a.device)
     _call("gemm_tcgen05", "spy_gemm_tcgen05_ex", _ptr(a), ctypes.c_longlong(K), _ptr(w), ctypes.c_longlong(K), _ptr(out),
           _code(out, "gemm output"), ctypes.c_longlong(n_out), M, N, K, _ptr(scratch), ctypes.c_longlong(scratch.numel()),
-          1 if epilogue == "swiglu" else 0, 0, None, _ptr(status), _stream())
+          1 if epilogue == "swiglu" else 0, 0, None, _ptr(status), _stream(), pf_ptr, ctypes.c_longlong(pf_bytes))
     return out
 
 

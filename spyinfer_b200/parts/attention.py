@@ -77,6 +77,9 @@ class Attention(Mixer):
             mods += self.position.modules()
         return mods
 
+    def linears(self):
+        return [self.qkv, self.o]
+
     def cache_need(self):
         return PagedCacheNeed(self.nkv, self.hd, int(self.window) if self.window is not None else None)
 

@@ -52,6 +52,11 @@ class Part:
     def modules(self) -> List[str]:
         return list(self.kernel_modules)
 
+    def linears(self) -> List:
+        """The part's ``Linear`` products in the order ``forward`` runs them (the model tells each
+        which weight is read next, so that it can ask for it ahead of time)."""
+        return []
+
 
 class Norm(Part):
     def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:

@@ -58,5 +58,8 @@ class LMHead(Part):
     def modules(self):
         return self.linear.modules()
 
+    def linears(self):
+        return [self.linear]
+
     def forward(self, x):
         return self.linear(x, out_dtype=torch.float32)

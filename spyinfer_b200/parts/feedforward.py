@@ -49,6 +49,10 @@ class GatedMLP(FeedForward):
         else:
             self.gate_up = Linear(torch.cat([gate, up], dim=0).contiguous(), self.ctx.dtype)
         self.down = Linear(tensors[p + "down_proj.weight"], self.ctx.dtype)
+        self.gate_up.hint_next = not self.fused       # fused: the down product follows at once
+
+    def linears(self):
+        return [self.gate_up, self.down]
 
     def modules(self):
         return ([] if self.fused else ["swiglu"]) + self.gate_up.modules() + self.down.modules()

@@ -8,6 +8,7 @@ batch it is in.
 """
 from __future__ import annotations
 
+import os
 from typing import List, Optional
 
 import torch
@@ -15,7 +16,23 @@ import torch
 from .. import kernels
 
 
+def _prefetch_cap() -> int:
+    """Most bytes of the following product's weights that a product asks to be brought into L2
+    (``SPYINFER_L2_PREFETCH_MB`` in the environment, 0 turns the hint off)."""
+    try:
+        return max(0, int(float(os.environ.get("SPYINFER_L2_PREFETCH_MB", "16")) * (1 << 20)))
+    except ValueError:
+        return 16 << 20
+
+
 class Linear:
+    #: the weight of the product that runs next in a step (set by the model once all parts are bound):
+    #: a decoding product asks for the start of it to be brought into L2 while the short kernels
+    #: between the two products run
+    next_weight: Optional[torch.Tensor] = None
+    #: False where the next product follows at once (nothing short runs in between, so there is no idle memory to use)
+    hint_next: bool = True
+
     def __init__(self, weight: torch.Tensor, activation_dtype: torch.dtype):
         if weight.dim() != 2:
             raise ValueError(f"a linear weight is [out, in], found shape {tuple(weight.shape)}")
@@ -23,6 +40,7 @@ class Linear:
         self.out_features, self.in_features = weight.shape
         self.fast = (activation_dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
                      and kernels.tensor_core_gemm_takes(self.out_features, self.in_features))
+        self.prefetch_bytes = _prefetch_cap()
 
     def modules(self) -> List[str]:
         return ["gemm_tcgen05"] if self.fast else ["gemm_simt"]
@@ -32,7 +50,9 @@ class Linear:
         and up rows) returns ``silu(gate) * up``.  ``defer=True`` allows the result to come back
         as a stack ``[splits, rows, out]`` of float32 partial products that the consumer sums."""
         if self.fast:
-            return kernels.gemm_tcgen05(x, self.weight, out_dtype=out_dtype or x.dtype, epilogue=epilogue, defer=defer)
+            hint = self.next_weight if self.hint_next and x.shape[0] <= 256 and self.prefetch_bytes > 0 else None
+            return kernels.gemm_tcgen05(x, self.weight, out_dtype=out_dtype or x.dtype, epilogue=epilogue, defer=defer,
+                                        prefetch=hint, prefetch_bytes=self.prefetch_bytes)
         if epilogue is not None:
             raise ValueError("only the tensor-core product has fused epilogues")
         out = torch.empty((x.shape[0], self.out_features), dtype=out_dtype or x.dtype, device=x.device)
