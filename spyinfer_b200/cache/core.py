@@ -44,7 +44,7 @@ def lib() -> ctypes.CDLL:
         L.spy_pool_allocate.argtypes = [ctypes.c_void_p, c_int_p]
         L.spy_pool_free.argtypes = [ctypes.c_void_p, ctypes.c_int]
         L.spy_cache_create.restype = ctypes.c_void_p
-        L.spy_cache_create.argtypes = [ctypes.c_int, c_int_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int]
+        L.spy_cache_create.argtypes = [ctypes.c_int, c_int_p, c_int_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int]
         L.spy_cache_destroy.argtypes = [ctypes.c_void_p]
         L.spy_cache_destroy.restype = None
         for name in ("spy_cache_width", "spy_cache_min_free_pages", "spy_cache_num_free_slots", "spy_cache_num_live", "spy_cache_check"):

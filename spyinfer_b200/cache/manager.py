@@ -65,10 +65,15 @@ class _PagedGroup:
 
 class CacheManager:
     def __init__(self, needs: Sequence, page_size: int, num_pages: int, max_num_seqs: int, max_model_len: int,
-                 dtype: torch.dtype = torch.bfloat16, device=None, cache_of: Optional[Sequence[Optional[int]]] = None):
+                 dtype: torch.dtype = torch.bfloat16, device=None, cache_of: Optional[Sequence[Optional[int]]] = None,
+                 max_step_tokens: Optional[int] = None):
         """``needs[i]`` is the cache need of run-order entry ``i`` (None for an entry that keeps
         nothing); ``cache_of[i]`` names the earlier entry whose cache entry ``i`` reads instead
-        of owning one.  ``num_pages`` is the size of every group's pool."""
+        of owning one.  ``num_pages`` is the size of the pool of a group that keeps every key.
+        With ``max_step_tokens`` (the most tokens one step brings) a windowed group gets only the
+        pages its requests can hold at once: each at most its window, the tokens of one step
+        (their pages are taken before the step and the ones behind the window given back after
+        it) and two pages of rounding; without it, ``num_pages`` as well."""
         if page_size <= 0 or max_num_seqs <= 0 or max_model_len <= 0:
             raise ValueError("page_size, max_num_seqs and max_model_len must be positive")
         self.page_size, self.num_pages, self.max_num_seqs, self.max_model_len = page_size, num_pages, max_num_seqs, max_model_len
@@ -113,17 +118,19 @@ class CacheManager:
         # the bookkeeping (pools, block tables, slots, requests) lives in the C++ engine core
         self._lib = core.lib()
         windows = (ctypes.c_int * max(1, len(self.groups)))(*[(-1 if g.need.window is None else int(g.need.window)) for g in self.groups])
-        self._h = self._lib.spy_cache_create(len(self.groups), windows, page_size, num_pages, max_num_seqs, max_model_len)
+        self.group_pages = [self.pages_of_group(g.need.window, page_size, num_pages, max_num_seqs, max_step_tokens) for g in self.groups]
+        sizes = (ctypes.c_int * max(1, len(self.groups)))(*self.group_pages)
+        self._h = self._lib.spy_cache_create(len(self.groups), windows, sizes, page_size, num_pages, max_num_seqs, max_model_len)
         if not self._h:
             raise ValueError(core.build.last_error("engine_core"))
         for gi, g in enumerate(self.groups):
             g.tables = np.ctypeslib.as_array(self._lib.spy_cache_tables(self._h, gi), shape=(max_num_seqs, self.width))
         if device is not None:
-            for g in self.groups:
+            for g, pool_pages in zip(self.groups, self.group_pages):
                 n = g.need
-                # one page more than the pool hands out: the spare page (id num_pages) takes the
-                # writes of the padding rows of a fixed-size (captured) decode batch
-                g.pages = torch.zeros((len(g.entries), num_pages + 1, 2, n.num_kv_heads, page_size, n.head_dim), dtype=dtype, device=device)
+                # one page more than the pool hands out: the spare page (the id after the pool's last) takes
+                # the writes of the padding rows of a fixed-size (captured) decode batch
+                g.pages = torch.zeros((len(g.entries), pool_pages + 1, 2, n.num_kv_heads, page_size, n.head_dim), dtype=dtype, device=device)
         for i, v in enumerate(self._views):
             if v.kind == "paged" and self.groups[v.group].pages is not None:
                 v.pages = self.groups[v.group].pages[self._entry_slot_in_group[i]]
@@ -159,10 +166,27 @@ class CacheManager:
 
     # ---- sizes -------------------------------------------------------------------------
     @staticmethod
+    def pages_of_group(window: Optional[int], page_size: int, num_pages: int, max_num_seqs: int, max_step_tokens: Optional[int]) -> int:
+        """The pool size of a group with this window (None: every key is kept)."""
+        if window is None or max_step_tokens is None:
+            return num_pages
+        per_request = (int(window) + int(max_step_tokens) + page_size - 1) // page_size + 2
+        return max(1, min(num_pages, max_num_seqs * per_request))
+
+    @staticmethod
     def bytes_per_page(needs: Sequence, page_size: int, dtype: torch.dtype) -> int:
-        """Device bytes that one more page in every group costs."""
+        """Device bytes that one more page costs in every group that keeps every key (windowed
+        groups are bounded by their window, see ``pages_of_group``; with only such groups, in every group)."""
         elt = torch.empty((), dtype=dtype).element_size()
-        return sum(2 * n.num_kv_heads * page_size * n.head_dim * elt for n in needs if isinstance(n, PagedCacheNeed))
+        paged = [n for n in needs if isinstance(n, PagedCacheNeed)]
+        full = [n for n in paged if n.window is None] or paged
+        return sum(2 * n.num_kv_heads * page_size * n.head_dim * elt for n in full)
+
+    def most_tokens_alone(self) -> int:
+        """The most tokens of ONE request that the pools can hold (beyond ``max_model_len`` if only
+        windowed groups exist: their pages come back as the window passes)."""
+        full = [p for g, p in zip(self.groups, self.group_pages) if g.need.window is None]
+        return min(full) * self.page_size if full else max(self.max_model_len, self.num_pages * self.page_size)
 
     def pages_for(self, length: int) -> int:
         return (length + self.page_size - 1) // self.page_size
@@ -254,10 +278,9 @@ class CacheManager:
             raise KeyError(rid)
         core.check(rc)
 
-    @property
-    def spare_page(self) -> int:
-        """Id of the page that no request ever holds (see the pages tensor's allocation)."""
-        return self.num_pages
+    def spare_page(self, group: int = 0) -> int:
+        """Id of the page of ``group`` that no request ever holds (see the pages tensor's allocation)."""
+        return self.group_pages[group]
 
     def block_table(self, rid, group: int = 0) -> np.ndarray:
         return self.groups[group].tables[self.slot(rid)]

@@ -1,7 +1,8 @@
 """The data that describes a model to the engine: parts, layers, and the order they run in.
 
-A model is a list of layers; a layer is a block arrangement of four parts (a norm before
-the mixer, the mixer, a norm before the feed-forward, the feed-forward); each part is a
+A model is a list of layers; a layer is a block arrangement over named parts (for the usual
+pre-norm block: a norm before the mixer, the mixer, a norm before the feed-forward, the
+feed-forward; an arrangement may name others, or fewer); each part is a
 ``PartSpec``: the registry key of its kind plus its sizes and constants.  The order in
 which layers run is a list of ``RunEntry`` and may name a layer twice, or let an entry
 read the cache that an earlier entry wrote.  Nothing here knows a model by name: an
@@ -26,15 +27,34 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: the arrangement (a key of the block registry), its four parts and the
-    prefix of its tensors' names in the checkpoint."""
+    """One layer: the arrangement (a key of the block registry), its parts by the role they play
+    in it, and the prefix of its tensors' names in the checkpoint.
+
+    The four roles of the usual block have fields of their own; an arrangement that needs other
+    parts (norms after the mixer and the feed-forward, a second feed-forward, ...) names them in
+    ``more``, and one that needs fewer leaves fields at None.  Which roles are required is the
+    arrangement's statement (``Block.required`` / ``Block.optional``), checked when the layer is
+    built.  The role ``mixer``, if present, is the part that owns the layer's cache."""
 
     block: str
-    mixer_norm: PartSpec
-    mixer: PartSpec
-    ffn_norm: PartSpec
-    feed_forward: PartSpec
-    weight_prefix: str
+    mixer_norm: Optional[PartSpec] = None
+    mixer: Optional[PartSpec] = None
+    ffn_norm: Optional[PartSpec] = None
+    feed_forward: Optional[PartSpec] = None
+    weight_prefix: str = ""
+    more: Dict[str, PartSpec] = field(default_factory=dict)
+
+    def roles(self) -> Dict[str, PartSpec]:
+        """role -> part, in the order the parts' tensors are declared."""
+        out = {r: getattr(self, r) for r in ("mixer_norm", "mixer", "ffn_norm", "feed_forward") if getattr(self, r) is not None}
+        for r, p in self.more.items():
+            if r in out:
+                raise ValueError(f"layer role {r!r} is given twice")
+            out[r] = p
+        return out
+
+    def __hash__(self):
+        return hash((self.block, self.weight_prefix, tuple(self.roles().items())))
 
 
 @dataclass(frozen=True)

@@ -181,9 +181,17 @@ int spy_pool_allocate(void* h, int* page)
 int spy_pool_free(void* h, int page) { return static_cast<PagePool*>(h)->release(page); }
 
 // ---- the cache's bookkeeping --------------------------------------------------------------------
-// windows[g]: the window of group g in tokens, or -1.  Every group's pool has num_pages pages.
-void* spy_cache_create(int num_groups, const int* windows, int page_size, int num_pages, int max_num_seqs, int max_model_len)
+// windows[g]: the window of group g in tokens, or -1.  group_pages[g]: the pages of group g's pool
+// (null: num_pages for every group); a windowed group, whose requests give pages back as the window
+// passes them, can do with fewer than a group that keeps every key.  num_pages is the size of the
+// largest pool.
+void* spy_cache_create(int num_groups, const int* windows, const int* group_pages, int page_size, int num_pages, int max_num_seqs, int max_model_len)
 {
+    for (int g = 0; group_pages != nullptr && g < num_groups; ++g)
+        if (group_pages[g] <= 0 || group_pages[g] > num_pages) {
+            fail(BAD_VALUE, "group %d: %d pages, expected 1..%d", g, group_pages[g], num_pages);
+            return nullptr;
+        }
     if (num_groups < 0 || page_size <= 0 || num_pages <= 0 || max_num_seqs <= 0 || max_model_len <= 0) {
         fail(BAD_VALUE, "page_size, num_pages, max_num_seqs and max_model_len must be positive");
         return nullptr;
@@ -194,7 +202,7 @@ void* spy_cache_create(int num_groups, const int* windows, int page_size, int nu
     c->max_num_seqs = max_num_seqs;
     c->max_model_len = max_model_len;
     c->width = (max_model_len + page_size - 1) / page_size;
-    for (int g = 0; g < num_groups; ++g) c->groups.emplace_back(windows[g], num_pages, max_num_seqs, c->width);
+    for (int g = 0; g < num_groups; ++g) c->groups.emplace_back(windows[g], group_pages ? group_pages[g] : num_pages, max_num_seqs, c->width);
     for (int s = max_num_seqs - 1; s >= 0; --s) c->free_slots.push_back(s);   // slot 0 is handed out first
     return c;
 }
@@ -329,7 +337,8 @@ int spy_cache_check(void* h)
     if ((int)c->requests.size() + (int)c->free_slots.size() != c->max_num_seqs) return fail(BROKEN, "state slots are lost or held twice");
     for (size_t gi = 0; gi < c->groups.size(); ++gi) {
         const Group& g = c->groups[gi];
-        std::vector<uint8_t> seen((size_t)c->num_pages, 0);   // 1: held, 2: free
+        const int pool_pages = g.pool.size();
+        std::vector<uint8_t> seen((size_t)pool_pages, 0);   // 1: held, 2: free
         int held = 0;
         for (int s = 0; s < c->max_num_seqs; ++s) {
             const int32_t* row = g.tables.data() + (size_t)s * c->width;
@@ -337,19 +346,19 @@ int spy_cache_check(void* h)
                 const int p = row[lp];
                 if (p < 0) continue;
                 if (live_slot[(size_t)s] != 1) return fail(BROKEN, "group %zu: slot %d has no request but still names pages", gi, s);
-                if (p >= c->num_pages) return fail(BROKEN, "group %zu: slot %d names page %d, which is not of the pool", gi, s, p);
+                if (p >= pool_pages) return fail(BROKEN, "group %zu: slot %d names page %d, which is not of the pool", gi, s, p);
                 if (seen[(size_t)p]) return fail(BROKEN, "group %zu: page %d is held twice", gi, p);
                 seen[(size_t)p] = 1;
                 ++held;
             }
         }
         for (int p : g.pool.free_list) {
-            if (p < 0 || p >= c->num_pages) return fail(BROKEN, "group %zu: the free list names page %d", gi, p);
+            if (p < 0 || p >= pool_pages) return fail(BROKEN, "group %zu: the free list names page %d", gi, p);
             if (seen[(size_t)p] == 2) return fail(BROKEN, "group %zu: page %d is on the free list twice", gi, p);
             if (seen[(size_t)p] == 1) return fail(BROKEN, "group %zu: page %d is both free and held", gi, p);
             seen[(size_t)p] = 2;
         }
-        if (held + g.pool.num_free() != c->num_pages) return fail(BROKEN, "group %zu: %d pages are lost", gi, c->num_pages - held - g.pool.num_free());
+        if (held + g.pool.num_free() != pool_pages) return fail(BROKEN, "group %zu: %d pages are lost", gi, pool_pages - held - g.pool.num_free());
     }
     return OK;
 }

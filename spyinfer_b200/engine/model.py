@@ -15,21 +15,22 @@ import torch
 from ..config.spec import ModelSpec
 from ..csrc import build
 from ..parts import BuildContext, build_block, build_part
-from ..weights.loader import WeightDecl, load_checkpoint
+from ..weights.loader import LazyTensors, WeightDecl, open_checkpoint
 from ..weights.random_init import random_tensor
 
 
 class _Layer:
+    """A layer's parts by role, built from the spec, and the block arrangement over them."""
+
     def __init__(self, spec, ctx):
         self.prefix = spec.weight_prefix
-        self.mixer_norm = build_part(spec.mixer_norm, ctx)
-        self.mixer = build_part(spec.mixer, ctx)
-        self.ffn_norm = build_part(spec.ffn_norm, ctx)
-        self.feed_forward = build_part(spec.feed_forward, ctx)
-        self.block = build_block(spec.block, self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward)
+        self.by_role = {role: build_part(part, ctx) for role, part in spec.roles().items()}
+        self.block = build_block(spec.block, self.by_role)
+        self.mixer = self.by_role.get("mixer")          # the part that owns the layer's cache, if the layer has one
+        self.feed_forward = self.by_role.get("feed_forward")
 
     def parts(self):
-        return [self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward]
+        return list(self.by_role.values())
 
 
 def _prefixed(part, prefix: str) -> List[WeightDecl]:
@@ -59,8 +60,12 @@ class Model:
     def ignorable_tensors(self) -> List[str]:
         return list(getattr(self.head, "ignorable", []))
 
-    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
-        """``tensors``: every declared tensor by its full name, on the device."""
+    def bind(self, tensors) -> None:
+        """``tensors``: every declared tensor by its full name, on the device: a dictionary, or a
+        ``LazyTensors`` that makes each tensor when its part is bound.  The parts are bound one
+        after the other and each gets only its own tensors, so with the latter the model never
+        holds a part's stored tensors and the fused layouts made from them for more than one
+        part at a time."""
         def sub(part, prefix):
             return {d.name: tensors[prefix + d.name] for d in part.weight_decls()}
 
@@ -78,19 +83,24 @@ class Model:
         build.ensure_built(self.kernel_modules())
 
     def load(self, model_dir: str) -> None:
-        tensors = load_checkpoint(model_dir, self.weight_decls(), self.ctx.device, self.ignorable_tensors())
-        if self.ctx.dtype == torch.bfloat16:
-            wide = [n for n, t in tensors.items() if t.dim() == 2 and t.dtype == torch.float32]
-            if wide:
-                # a tensor stored in 32-bit stays so, and a 32-bit matrix cannot go to the bfloat16 tensor-core product
-                warnings.warn(f"{model_dir}: {len(wide)} matrices are stored in 32-bit (or 16-bit float, which is widened), the first being "
-                              f"{wide[0]!r}; they stay 32-bit and are multiplied by the CUDA-core kernel, which is far slower than "
-                              "the bfloat16 tensor-core one. Store the checkpoint in bfloat16 for speed.", stacklevel=2)
-        self.bind(tensors)
+        tensors = open_checkpoint(model_dir, self.weight_decls(), self.ctx.device, self.ignorable_tensors())
+        try:
+            if self.ctx.dtype == torch.bfloat16:
+                shapes = {d.name: d.shape for d in self.weight_decls()}
+                wide = [n for n, t in tensors.stored_dtypes.items() if len(shapes[n]) == 2 and t in (torch.float32, torch.float16)]
+                if wide:
+                    # a tensor stored in 32-bit stays so, and a 32-bit matrix cannot go to the bfloat16 tensor-core product
+                    warnings.warn(f"{model_dir}: {len(wide)} matrices are stored in 32-bit (or 16-bit float, which is widened), the first being "
+                                  f"{wide[0]!r}; they stay 32-bit and are multiplied by the CUDA-core kernel, which is far slower than "
+                                  "the bfloat16 tensor-core one. Store the checkpoint in bfloat16 for speed.", stacklevel=2)
+            self.bind(tensors)
+        finally:
+            tensors.close()
 
     def init_random(self, seed: int, std: float = 0.02, norm_std: float = 0.05) -> None:
-        """Seeded random weights made on the device, tensor by tensor (no host copy)."""
-        self.bind({d.name: random_tensor(d, seed, std, norm_std, self.ctx.device) for d in self.weight_decls()})
+        """Seeded random weights made on the device, tensor by tensor as the parts are bound (no host copy)."""
+        decls = {d.name: d for d in self.weight_decls()}
+        self.bind(LazyTensors(list(decls), lambda name: random_tensor(decls[name], seed, std, norm_std, self.ctx.device)))
 
     def kernel_modules(self) -> List[str]:
         mods: List[str] = []
@@ -99,12 +109,12 @@ class Model:
         return list(dict.fromkeys(mods))
 
     def graph_safe(self) -> bool:
-        return all(l.mixer.graph_safe for l in self.layers)
+        return all(l.mixer is None or l.mixer.graph_safe for l in self.layers)
 
     # ---- cache needs -------------------------------------------------------------------------
     def cache_needs(self):
         """Per run-order entry: its mixer's need, and the entry whose cache it reads instead."""
-        needs = [self.layers[e.layer].mixer.cache_need() for e in self.spec.run_order]
+        needs = [self.layers[e.layer].mixer.cache_need() if self.layers[e.layer].mixer is not None else None for e in self.spec.run_order]
         return needs, [e.cache_of for e in self.spec.run_order]
 
     # ---- one step ------------------------------------------------------------------------------

@@ -37,7 +37,8 @@ class ModelRunner:
             if num_pages is None:
                 num_pages = self._pages_from_free_memory(needs)
             cache = CacheManager(needs, config.kvcache_block_size, num_pages, config.max_num_seqs, config.max_model_len,
-                                 dtype=model.ctx.dtype, device=self.device, cache_of=cache_of)
+                                 dtype=model.ctx.dtype, device=self.device, cache_of=cache_of,
+                                 max_step_tokens=max(config.max_num_batched_tokens, config.max_num_seqs))
         self.cache = cache
         self.stager = BatchStager(self.device, max(config.max_num_batched_tokens, config.max_num_seqs), config.max_num_seqs, cache.width, max(1, cache.num_groups()))
         self.vocab_size = model.spec.vocab_size
@@ -55,13 +56,22 @@ class ModelRunner:
         self.step_events: Optional[list] = None
 
     def _pages_from_free_memory(self, needs) -> int:
-        per_page = CacheManager.bytes_per_page(needs, self.config.kvcache_block_size, self.model.ctx.dtype)
+        """The pool size that the free device memory allows: windowed groups take what their windows
+        need (``CacheManager.pages_of_group``), the rest goes to the groups that keep every key."""
+        from ..config.spec import PagedCacheNeed
+        cfg = self.config
+        page, step = cfg.kvcache_block_size, max(cfg.max_num_batched_tokens, cfg.max_num_seqs)
+        per_page = CacheManager.bytes_per_page(needs, page, self.model.ctx.dtype)
         if per_page == 0:
             return 1
+        paged = [n for n in needs if isinstance(n, PagedCacheNeed)]
+        windowed = [n for n in paged if n.window is not None] if any(n.window is None for n in paged) else []
+        fixed = sum(CacheManager.pages_of_group(n.window, page, 1 << 30, cfg.max_num_seqs, step) * CacheManager.bytes_per_page([n], page, self.model.ctx.dtype)
+                    for n in windowed)
         free, total = torch.cuda.mem_get_info(self.device)
-        budget = free - int(total * (1.0 - self.config.gpu_memory_utilization)) - (2 << 30)  # room for activations
+        budget = free - int(total * (1.0 - cfg.gpu_memory_utilization)) - (2 << 30) - fixed  # room for activations
         pages = budget // per_page
-        most = self.config.max_num_seqs * ((self.config.max_model_len + self.config.kvcache_block_size - 1) // self.config.kvcache_block_size)
+        most = cfg.max_num_seqs * ((cfg.max_model_len + page - 1) // page)
         if pages <= 0:
             raise StepError("no device memory is left for the cache after the weights; lower gpu_memory_utilization's complement or the model size")
         return int(min(pages, most))
@@ -109,7 +119,7 @@ class ModelRunner:
         for g in range(cache.num_groups()):
             t = np.full((bucket, cache.width), -1, np.int32)
             cache.gather_block_tables(rids, g, out=t)
-            t[S:, 0] = cache.spare_page
+            t[S:, 0] = cache.spare_page(g)
             tables.append(t)
         ar = np.arange(bucket + 1, dtype=np.int32)
         return self.stager.stage(token_ids, positions, ar[:bucket], ar, ctx_len, slots, ar[:bucket], tables, bucket, bucket)

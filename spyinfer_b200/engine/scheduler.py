@@ -61,16 +61,16 @@ class Scheduler:
 
     def most_tokens_alone(self) -> int:
         """The most tokens of one request that the pool can hold when the request is alone."""
-        return self.cache.num_pages * self.cache.page_size
+        return self.cache.most_tokens_alone()
 
     def check_fits(self, seq: Sequence, max_new_tokens: int) -> None:
         """Refuses a request that could never run to its end even alone in the pool."""
         if len(seq) >= self.config.max_model_len:
             raise RequestTooLarge(f"a prompt of {len(seq)} tokens leaves no room to generate within max_model_len {self.config.max_model_len}")
         final = min(len(seq) + max_new_tokens, self.config.max_model_len)
-        if self.cache.pages_for(final) > self.cache.num_pages:
+        if final > self.cache.most_tokens_alone():
             raise RequestTooLarge(f"{final} tokens need {self.cache.pages_for(final)} pages of {self.cache.page_size}; the pool has "
-                                  f"{self.cache.num_pages}")
+                                  f"{self.cache.most_tokens_alone() // self.cache.page_size}")
 
     def add_sequence(self, seq: Sequence) -> None:
         seq.status = SequenceStatus.WAITING

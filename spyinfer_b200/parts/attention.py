@@ -139,4 +139,4 @@ class Attention(Mixer):
         else:
             kernels.attention_mma(q, self.nh, self.hd, out, cache.pages, cache.block_table, batch.positions, batch.q_start,
                                   batch.num_seqs, self.scale, window=self.window, status=batch.status)
-        return self.o(out, defer=True)
+        return self.o(out, defer=self.defer_output)

@@ -10,8 +10,9 @@ parts the model has.
 * ``Mixer``: ``forward(x, batch, cache)``; declares what it keeps between steps through
   ``cache_need()`` (pages of keys and values, a fixed-size state per request, or nothing).
 * ``FeedForward``: ``forward(x)``.
-* ``Block``: the arrangement of two norms, a mixer and a feed-forward around the residual
-  stream: ``forward(hidden, delta, batch, cache) -> (hidden, delta)``.
+* ``Block``: the arrangement of a layer's parts around the residual stream (for the usual
+  pre-norm block two norms, a mixer and a feed-forward; an arrangement states the roles it
+  needs): ``forward(hidden, delta, batch, cache) -> (hidden, delta)``.
 """
 from __future__ import annotations
 
@@ -84,6 +85,12 @@ class Mixer(Part):
     #: batch's content), so that a decode step can be captured in a CUDA graph
     graph_safe: bool = False
 
+    #: True: ``forward`` may hand its result over as a stack ``[splits, rows, size]`` of float32 partial
+    #: products (its last product then skips its own reduction), which ``Norm.forward_add`` adds to the
+    #: residual.  A block arrangement that does anything else with the result sets this to False on
+    #: the part and always gets ``[rows, size]``.
+    defer_output: bool = True
+
     def cache_need(self):
         """A ``PagedCacheNeed``, a ``StateCacheNeed`` or None."""
         return None
@@ -93,15 +100,30 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    defer_output: bool = True     # as ``Mixer.defer_output``
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
 
 
 class Block:
-    kind: str = ""
+    """An arrangement of a layer's parts.  ``required`` and ``optional`` name the roles it takes
+    (``LayerSpec.roles()``); the parts arrive as ``self.parts[role]`` and as attributes of the
+    same names (None for an optional role that the layer does not have)."""
 
-    def __init__(self, mixer_norm: Norm, mixer: Mixer, ffn_norm: Norm, feed_forward: FeedForward):
-        self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward = mixer_norm, mixer, ffn_norm, feed_forward
+    kind: str = ""
+    required: Sequence[str] = ("mixer_norm", "mixer", "ffn_norm", "feed_forward")
+    optional: Sequence[str] = ()
+
+    def __init__(self, parts: Dict[str, Part]):
+        missing = [r for r in self.required if r not in parts]
+        unknown = [r for r in parts if r not in self.required and r not in self.optional]
+        if missing or unknown:
+            raise ValueError(f"block arrangement {self.kind!r} takes the roles {list(self.required)} (optional {list(self.optional)}): "
+                             f"missing {missing}, unknown {unknown}")
+        self.parts = dict(parts)
+        for role in list(self.required) + list(self.optional):
+            setattr(self, role, parts.get(role))
 
     def forward(self, hidden: torch.Tensor, delta: Optional[torch.Tensor], batch, cache):
         """``hidden`` is the 32-bit residual stream; ``delta`` the previous block's output

@@ -21,10 +21,11 @@ def register_block(kind: str):
     return wrap
 
 
-def build_block(kind: str, mixer_norm, mixer, ffn_norm, feed_forward) -> Block:
+def build_block(kind: str, parts) -> Block:
+    """``parts``: role -> built part (``LayerSpec.roles()`` with every ``PartSpec`` built)."""
     if kind not in _BLOCKS:
         raise KeyError(f"unknown block arrangement {kind!r}; registered: {', '.join(sorted(_BLOCKS))}")
-    return _BLOCKS[kind](mixer_norm, mixer, ffn_norm, feed_forward)
+    return _BLOCKS[kind](dict(parts))
 
 
 @register_block("pre_norm")

@@ -59,7 +59,7 @@ class GatedMLP(FeedForward):
 
     def forward(self, x):
         if self.fused:
-            return self.down(self.gate_up(x, epilogue="swiglu"), defer=True)
+            return self.down(self.gate_up(x, epilogue="swiglu"), defer=self.defer_output)
         gu = self.gate_up(x)
         z = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
         kernels.swiglu(gu, z)

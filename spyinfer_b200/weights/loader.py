@@ -12,8 +12,10 @@ integer tables become int32.
 """
 from __future__ import annotations
 
+import weakref
+from collections.abc import Mapping
 from dataclasses import dataclass
-from typing import Dict, Iterable, List, Sequence, Tuple
+from typing import Callable, Dict, Iterable, List, Optional, Sequence, Tuple
 
 import torch
 
@@ -56,14 +58,58 @@ def _store(t: torch.Tensor, decl: WeightDecl) -> torch.Tensor:
     return t
 
 
-def load_checkpoint(model_dir: str, decls: Iterable[WeightDecl], device, ignorable: Sequence[str] = ()) -> Dict[str, torch.Tensor]:
-    """``ignorable`` names tensors that may be present without being used (the separate head
+class LazyTensors(Mapping):
+    """``name -> tensor`` whose tensors are made when they are asked for (read from the checkpoint and
+    copied to the device, or drawn at random) and not kept: a model that binds its parts one after the
+    other, each turning what it gets into the layout it computes with, then never holds the whole
+    checkpoint beside the model.  A tensor that is asked for again while the first one is still in
+    use (a tied head and its embedding table) is the same object, not a second copy."""
+
+    def __init__(self, names: Iterable[str], make: Callable[[str], torch.Tensor], on_close: Optional[Callable[[], None]] = None):
+        self._names = list(names)
+        self._known = set(self._names)
+        self._make = make
+        self._alive = weakref.WeakValueDictionary()
+        self._on_close = on_close
+
+    def __getitem__(self, name: str) -> torch.Tensor:
+        if name not in self._known:
+            raise KeyError(name)
+        t = self._alive.get(name)
+        if t is None:
+            t = self._make(name)
+            self._alive[name] = t
+        return t
+
+    def __iter__(self):
+        return iter(self._names)
+
+    def __len__(self):
+        return len(self._names)
+
+    def close(self) -> None:
+        if self._on_close is not None:
+            self._on_close()
+            self._on_close = None
+
+
+def open_checkpoint(model_dir: str, decls: Iterable[WeightDecl], device, ignorable: Sequence[str] = ()) -> LazyTensors:
+    """Checks the folder against the declarations (ONE ``WeightError`` that lists every missing,
+    unexpected and wrong tensor) and returns its tensors as a ``LazyTensors``: each is read and
+    copied to ``device`` when it is asked for.  ``stored_dtypes`` of the result tells how each
+    tensor is stored.  Close it when the model is bound.
+    ``ignorable`` names tensors that may be present without being used (the separate head
     of a checkpoint whose configuration ties it to the embedding)."""
     decls = list(decls)
     try:
         files = [SafetensorsFile(p) for p in shard_paths(model_dir)]
     except SafetensorsError as e:
         raise WeightError(str(e), [], [], []) from None
+
+    def close():
+        for f in files:
+            f.close()
+
     where: Dict[str, SafetensorsFile] = {}
     for f in files:
         for name in f.names():
@@ -81,13 +127,20 @@ def load_checkpoint(model_dir: str, decls: Iterable[WeightDecl], device, ignorab
         if is_int != d.integer:
             wrong.append(f"{d.name}: expected {'an integer' if d.integer else 'a floating-point'} tensor, found {f.dtype(d.name)} in {f.path}")
     unexpected = sorted(n for n in where if n not in wanted and n not in set(ignorable))
+    if missing or unexpected or wrong:
+        close()
+        raise WeightError(model_dir, missing, unexpected, wrong)
+    by_name = {d.name: d for d in decls}
+    out = LazyTensors([d.name for d in decls], lambda n: _store(where[n].tensor(n), by_name[n]).to(device).contiguous(), close)
+    out.stored_dtypes = {d.name: where[d.name].dtype(d.name) for d in decls}
+    return out
+
+
+def load_checkpoint(model_dir: str, decls: Iterable[WeightDecl], device, ignorable: Sequence[str] = ()) -> Dict[str, torch.Tensor]:
+    """Every declared tensor on ``device`` (see ``open_checkpoint`` for the checks and for a way
+    that does not hold them all at once)."""
+    lazy = open_checkpoint(model_dir, decls, device, ignorable)
     try:
-        if missing or unexpected or wrong:
-            raise WeightError(model_dir, missing, unexpected, wrong)
-        out = {}
-        for d in decls:
-            out[d.name] = _store(where[d.name].tensor(d.name), d).to(device).contiguous()
-        return out
+        return {name: lazy[name] for name in lazy}
     finally:
-        for f in files:
-            f.close()
+        lazy.close()

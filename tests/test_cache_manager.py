@@ -196,3 +196,34 @@ def test_a_step_that_cannot_be_assembled_takes_nothing():
         m.check_invariants()
     m.assemble(["a", "old"], [[1] * 8, [2]], [[], [0]], vocab_size=10)              # 2 + 1 pages: fits
     assert m.num_free_pages() == free_pages - 3
+
+
+def test_a_windowed_group_gets_the_pages_its_windows_need_not_the_whole_pool():
+    """Two groups: one keeps every key (the pool's 200 pages), one has a window of 16 tokens.  With
+    steps of at most 8 tokens and 3 live requests the windowed group's pool is 3 x (ceil(24 / 4) + 2) =
+    24 pages.  Three requests run far past the window in steps of up to 8 tokens without the small
+    pool ever running out, and every page comes back."""
+    rng = random.Random(2)
+    m = CacheManager([FULL, PagedCacheNeed(2, 16, 16)], 4, 200, 3, 256, device=None, max_step_tokens=8)
+    assert m.group_pages == [200, 24] and m.spare_page(0) == 200 and m.spare_page(1) == 24
+    assert m.most_tokens_alone() == 800
+    lengths = {r: 0 for r in "abc"}
+    for r in lengths:
+        m.add_request(r)
+    for _ in range(120):
+        r = rng.choice("abc")
+        n = rng.randint(1, 8)
+        if lengths[r] + n > 256:
+            continue
+        m.reserve(r, lengths[r] + n)
+        lengths[r] += n
+        m.commit(r, lengths[r])
+        m.check_invariants()
+        held = sum(int((m.block_table(q, 1) >= 0).sum()) for q in lengths)
+        assert held <= 24 and m.num_free_pages(1) == 24 - held
+    assert max(lengths.values()) > 100
+    for r in lengths:
+        m.free_request(r)
+    assert m.num_free_pages(0) == 200 and m.num_free_pages(1) == 24
+    # without the step bound every group gets the whole pool, as before
+    assert CacheManager([FULL, PagedCacheNeed(2, 16, 16)], 4, 200, 3, 256, device=None).group_pages == [200, 200]

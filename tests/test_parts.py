@@ -345,7 +345,7 @@ def test_embedding_head_and_block_parts(dtype):
     w = {}
     for i, part in enumerate((norm1, norm2, attn, ffn)):
         w.update(bound(part, std=0.15, seed=10 + i))
-    block = build_block("pre_norm", norm1, attn, norm2, ffn)
+    block = build_block("pre_norm", {"mixer_norm": norm1, "mixer": attn, "ffn_norm": norm2, "feed_forward": ffn})
     n = 13
     cache = CacheManager([attn.cache_need()], 4, 16, 2, 64, dtype=dtype, device=torch.device(DEV))
     batch = one_step_batch(cache, [n], torch.device(DEV))
@@ -468,4 +468,89 @@ def test_toy_routed_feed_forward_and_toy_position_encoding():
     runner.finish("w")
     cut = torch.cat([runner.step([StepEntry("c", tokens[a:b], range(b - a))]).cpu() for a, b in [(0, 10), (10, 12), (12, 13), (13, 27)]])
     torch.testing.assert_close(cut, want, rtol=1e-4, atol=2e-5)
+    runner.check_status()
+
+
+def register_toy_blocks():
+    """Two arrangements that the engine does not have, with other roles than the usual four: norms
+    after the mixer and after the feed-forward as well ("sandwich": six parts), and a layer that is
+    a mixer alone ("mixer_only": two parts, no feed-forward)."""
+    from spyinfer_b200.parts import Block, register_block
+
+    @register_block("toy_sandwich")
+    class Sandwich(Block):
+        required = ("mixer_norm", "mixer", "post_mixer_norm", "ffn_norm", "feed_forward", "post_ffn_norm")
+
+        def __init__(self, parts):
+            super().__init__(parts)
+            self.mixer.defer_output = self.feed_forward.defer_output = False     # their results are normed, not added
+
+        def forward(self, hidden, delta, batch, cache):
+            x = self.mixer_norm.forward_add(hidden, delta)
+            a = self.post_mixer_norm.forward(self.mixer.forward(x, batch, cache), out_dtype=torch.float32)
+            x = self.ffn_norm.forward_add(hidden, a)
+            return hidden, self.post_ffn_norm.forward(self.feed_forward.forward(x), out_dtype=torch.float32)
+
+    @register_block("toy_mixer_only")
+    class MixerOnly(Block):
+        required = ("mixer_norm", "mixer")
+
+        def forward(self, hidden, delta, batch, cache):
+            x = self.mixer_norm.forward_add(hidden, delta)
+            return hidden, self.mixer.forward(x, batch, cache)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_block_arrangements_with_other_roles_are_registered_built_and_stepped(dtype):
+    """A layer with six parts and a layer with two, arranged by blocks defined here: the layer
+    description carries the further roles, the model builds, declares the weights of and binds
+    whatever parts a layer has, and a layer without a feed-forward or with two more norms steps
+    through the engine, whole and cut, as the plain statement of the same arrangement does."""
+    from spyinfer_b200.config import EngineConfig, LayerSpec, ModelSpec, PartSpec, RunEntry
+    from spyinfer_b200.engine import Model, ModelRunner, StepEntry
+    from spyinfer_b200.weights import random_tensors
+    register_toy_blocks()
+    H, V, nh, nkv, hd, eps = 64, 131, 2, 1, 64, 1e-5
+    norm = lambda name: PartSpec("rms_norm", {"size": H, "eps": eps, "weight": name})
+    attn = PartSpec("attention", {"hidden_size": H, "num_heads": nh, "num_kv_heads": nkv, "head_dim": hd, "qk_norm_eps": eps,
+                                  "position": PartSpec("rotary_half", {"theta": 1e4, "rotary_dim": hd}), "window": None, "scale": None, "prefix": "self_attn."})
+    ffn = PartSpec("gated_mlp", {"hidden_size": H, "intermediate_size": 96, "activation": "silu", "prefix": "mlp."})
+    layers = [LayerSpec("toy_sandwich", mixer_norm=norm("input_layernorm.weight"), mixer=attn, ffn_norm=norm("pre_feedforward_layernorm.weight"),
+                        feed_forward=ffn, weight_prefix="model.layers.0.",
+                        more={"post_mixer_norm": norm("post_attention_layernorm.weight"), "post_ffn_norm": norm("post_feedforward_layernorm.weight")}),
+              LayerSpec("toy_mixer_only", mixer_norm=norm("input_layernorm.weight"), mixer=attn, weight_prefix="model.layers.1.")]
+    spec = ModelSpec(architecture="toy", hidden_size=H, vocab_size=V,
+                     embedding=PartSpec("token_embedding", {"vocab_size": V, "hidden_size": H, "weight": "model.embed_tokens.weight"}),
+                     layers=layers, run_order=[RunEntry(0), RunEntry(1)], final_norm=norm("model.norm.weight"),
+                     head=PartSpec("lm_head", {"vocab_size": V, "hidden_size": H, "tied": False, "weight": "lm_head.weight",
+                                               "tied_to": "model.embed_tokens.weight"}), max_position=256)
+    with pytest.raises(ValueError, match="missing.*post_ffn_norm"):
+        Model(ModelSpec(**{**spec.__dict__, "layers": [LayerSpec("toy_sandwich", norm("a"), attn, norm("b"), ffn, "model.layers.0.",
+                                                                 more={"post_mixer_norm": norm("c")})], "run_order": [RunEntry(0)]}),
+              torch.float32, DEV, 64)
+    tdtype = torch.float32 if dtype == "float32" else torch.bfloat16
+    cfg = EngineConfig(dtype=dtype, max_num_seqs=2, max_model_len=64, kvcache_block_size=16, num_kvcache_blocks=8, max_num_batched_tokens=64)
+    model = Model(spec, tdtype, cfg.device, cfg.max_model_len)
+    names = {d.name for d in model.weight_decls()}
+    assert "model.layers.0.post_feedforward_layernorm.weight" in names and "model.layers.1.mlp.down_proj.weight" not in names
+    w = dict(random_tensors(model.weight_decls(), seed=9, std=0.08, norm_std=0.1))
+    model.bind({k: v.to(DEV) for k, v in w.items()})
+    runner = ModelRunner(model, cfg)
+    tokens = np.random.default_rng(1).integers(0, V, 23).tolist()
+    cfgd = {"num_attention_heads": nh, "num_key_value_heads": nkv, "head_dim": hd, "rms_norm_eps": eps, "rope_theta": 1e4}
+    pos = list(range(len(tokens)))
+    h = plain_model.embed_tokens(w["model.embed_tokens.weight"], tokens)
+    p = "model.layers.0."
+    a = plain_model.attention_mixer(plain_model.rms_norm(h, w[p + "input_layernorm.weight"], eps), w, p, cfgd, pos)
+    h = h + plain_model.rms_norm(a, w[p + "post_attention_layernorm.weight"], eps)
+    f = plain_model.feed_forward(plain_model.rms_norm(h, w[p + "pre_feedforward_layernorm.weight"], eps), w, p)
+    h = h + plain_model.rms_norm(f, w[p + "post_feedforward_layernorm.weight"], eps)
+    p = "model.layers.1."
+    h = h + plain_model.attention_mixer(plain_model.rms_norm(h, w[p + "input_layernorm.weight"], eps), w, p, cfgd, pos)
+    want = plain_model.linear(plain_model.rms_norm(h, w["model.norm.weight"], eps), w["lm_head.weight"])
+    tol = dict(rtol=1e-4, atol=1e-5) if dtype == "float32" else dict(rtol=0.0, atol=0.05 * want.abs().max().item())
+    whole = runner.step([StepEntry("w", tokens, range(len(tokens)))]).cpu()
+    torch.testing.assert_close(whole, want, **tol)
+    cut = torch.cat([runner.step([StepEntry("c", tokens[a:b], range(b - a))]).cpu() for a, b in [(0, 9), (9, 11), (11, 12), (12, 23)]])
+    torch.testing.assert_close(cut, want, **tol)
     runner.check_status()

@@ -150,3 +150,49 @@ def test_random_model_folder_in_shards_reads_back_as_the_single_file_does(tmp_pa
     one = load_checkpoint(str(tmp_path / "one"), decls, "cpu")
     many = load_checkpoint(str(tmp_path / "many"), decls, "cpu")
     assert one.keys() == many.keys() and all(torch.equal(one[k], many[k]) for k in one)
+
+
+def test_tensors_are_made_when_asked_for_and_not_kept(tmp_path):
+    """``open_checkpoint``: a tensor is read when it is asked for; asked for again while the first is
+    still in use it is the same object (a tied head and its table), and once nobody holds it a fresh one."""
+    from spyinfer_b200.config import config_from_json
+    from spyinfer_b200.engine.model import declared_weights
+    from spyinfer_b200.weights import open_checkpoint, write_model_folder
+    from conftest import TINY
+
+    cfg = config_from_json(TINY["a"]["config"])
+    write_model_folder(str(tmp_path), cfg, 1)
+    lazy = open_checkpoint(str(tmp_path), declared_weights(cfg.to_spec()), "cpu")
+    assert "model.embed_tokens.weight" in lazy and "nothing" not in lazy and len(lazy) == len(declared_weights(cfg.to_spec()))
+    assert lazy.stored_dtypes["model.norm.weight"] == torch.bfloat16
+    a = lazy["model.embed_tokens.weight"]
+    assert lazy["model.embed_tokens.weight"] is a
+    ident = id(a)
+    keep = a.clone()
+    del a
+    b = lazy["model.embed_tokens.weight"]
+    assert torch.equal(b, keep)
+    with pytest.raises(KeyError):
+        lazy["nothing"]
+    lazy.close()
+
+
+@pytest.mark.gpu
+def test_loading_never_holds_the_checkpoint_beside_the_model(tmp_path):
+    """Four layers at the 8B layer sizes (1.5 GB): the parts fuse q|k|v and gate|up into layouts of their
+    own at load.  The most device memory in use during the load stays well below twice the model."""
+    from spyinfer_b200 import LLMEngine
+    from spyinfer_b200.config import config_from_json
+    from spyinfer_b200.weights import write_model_folder
+    cfg = config_from_json({"architectures": ["Qwen3ForCausalLM"], "num_hidden_layers": 4, "hidden_size": 4096, "num_attention_heads": 32,
+                            "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 12288, "vocab_size": 1000, "max_position_embeddings": 256})
+    write_model_folder(str(tmp_path), cfg, 2, device="cuda:0")
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    torch.cuda.reset_peak_memory_stats()
+    before = torch.cuda.memory_allocated()
+    engine = LLMEngine(str(tmp_path), dtype="bfloat16", max_num_seqs=2, max_model_len=64, num_kvcache_blocks=8, max_num_batched_tokens=64)
+    held = torch.cuda.memory_allocated() - before
+    peak = torch.cuda.max_memory_allocated() - before
+    assert held > 1.5e9 and peak < 1.4 * held, f"held {held / 1e9:.2f} GB after the load, {peak / 1e9:.2f} GB at its peak"
+    assert len(engine.generate([[1, 2, 3]])[0]) > 0
