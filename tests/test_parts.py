@@ -554,3 +554,57 @@ def test_block_arrangements_with_other_roles_are_registered_built_and_stepped(dt
     cut = torch.cat([runner.step([StepEntry("c", tokens[a:b], range(b - a))]).cpu() for a, b in [(0, 9), (9, 11), (11, 12), (12, 23)]])
     torch.testing.assert_close(cut, want, **tol)
     runner.check_status()
+
+
+def test_a_whole_architecture_from_this_file_generates_through_the_scheduler_and_survives_preemption(tmp_path):
+    """An architecture registered here (its own config.json keys, its own mixer with per-request state
+    beside an attention layer) is written as a model folder, read back by name, and generates through
+    ``LLMEngine``: with room, and in a pool so small that requests are preempted and recomputed, where
+    the state slot of a recomputed request must start from zero again; launching decode steps ahead
+    changes nothing.  No file of the framework knows this architecture."""
+    import json
+    from dataclasses import dataclass
+
+    from spyinfer_b200 import LLMEngine, SamplingParams
+    from spyinfer_b200.config import ArchitectureConfig, ConfigError, load_model_config, register_architecture
+    from spyinfer_b200.weights import write_model_folder
+    register_toy_parts()
+
+    @register_architecture("ToyDecayForCausalLM", model_type="toy_decay")
+    @dataclass
+    class ToyConfig(ArchitectureConfig):
+        decay_layers: int = 2
+
+        @classmethod
+        def from_json(cls, data):
+            if data.get("decay_layers") != 2:
+                raise ConfigError("toy: decay_layers must be 2")
+            return cls(decay_layers=2)
+
+        def to_json(self):
+            return {"architectures": [self.architecture], "model_type": "toy_decay", "decay_layers": self.decay_layers}
+
+        def to_spec(self):
+            return toy_spec()
+
+    write_model_folder(str(tmp_path), ToyConfig(), seed=6, std=0.1, norm_std=0.1)
+    assert isinstance(load_model_config(str(tmp_path)), ToyConfig)
+    rng = np.random.default_rng(4)
+    prompts = [rng.integers(0, 97, n).tolist() for n in (17, 9, 30, 5)]
+    sp = SamplingParams(max_new_tokens=20, ignore_eos=True)
+    opts = dict(dtype="float32", max_num_seqs=3, max_model_len=128, kvcache_block_size=8, max_num_batched_tokens=24)
+    roomy = LLMEngine(str(tmp_path), num_kvcache_blocks=48, **opts)
+    want = roomy.generate(prompts, sp)
+    from safetensors.torch import load_file
+    w = load_file(str(tmp_path / "model.safetensors"))
+    for p, o in zip(prompts, want):                                         # greedy tokens of the plain statement of this architecture
+        seq = list(p)
+        for tok in o[:4]:
+            logits = plain_toy_logits(w, seq)[-1]
+            assert logits[tok] >= logits.max() - 1e-4
+            seq.append(tok)
+    for ahead in (True, False):
+        tight = LLMEngine(str(tmp_path), num_kvcache_blocks=9, lookahead_decode=ahead, **opts)       # 72 tokens of cache for requests of up to 50
+        assert tight.generate(prompts, sp) == want
+        assert tight.scheduler.num_preemptions > 0, "the pool was meant to be too small"
+        tight.runner.cache.check_invariants()
