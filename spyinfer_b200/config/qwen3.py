@@ -16,9 +16,11 @@ list is absent, ``max_window_layers`` (layers ``0 .. max_window_layers - 1`` see
 the layers from ``max_window_layers`` on have the window).  ``use_sliding_window`` with
 neither is refused: it would not say which layers are meant.  Where both are given the list
 counts.  The reference reads none of these keys (every layer of its model sees all keys),
-so their meaning here is this engine's statement, pinned by its own tests only.  Keys that
-would change the result and are not implemented are refused: ``rope_scaling``,
-``attention_bias``.  A key that is not read at all and is not known to be without effect on
+so their meaning here is this engine's statement, pinned by its own tests only.  ``attention_bias`` true gives the q, k and v projections bias
+tensors (``self_attn.{q,k,v}_proj.bias``: the three the reference's model has slots for and
+never binds, src/models/qwen3.hpp:39, 143-157; a checkpoint with further bias tensors is
+refused by name at load).  Keys that would change the result and are not implemented are
+refused: ``rope_scaling`` of any kind but the default.  A key that is not read at all and is not known to be without effect on
 the logits (``_NO_EFFECT``) is named in a warning, never dropped silently.
 
 The layer structure itself (pre-norm blocks of grouped-query attention with per-head q/k
@@ -36,7 +38,7 @@ from .spec import LayerSpec, ModelSpec, PartSpec, RunEntry
 
 # keys that checkpoints carry and that do not change what a forward pass computes
 _NO_EFFECT = {"architectures", "torch_dtype", "dtype", "transformers_version", "use_cache", "attention_dropout", "initializer_range",
-              "pad_token_id", "attention_bias", "rope_scaling", "rope_parameters", "_name_or_path"}
+              "pad_token_id", "rope_scaling", "rope_parameters", "_name_or_path"}
 
 _REQUIRED_INTS = ("hidden_size", "intermediate_size", "num_hidden_layers", "num_attention_heads",
                   "num_key_value_heads", "vocab_size")
@@ -64,6 +66,7 @@ class Qwen3Config(ArchitectureConfig):
     sliding_window: Optional[int] = None
     layer_types: Optional[List[str]] = None
     max_window_layers: Optional[int] = None
+    attention_bias: bool = False
     extra: Dict[str, Any] = field(default_factory=dict)
 
     @classmethod
@@ -97,8 +100,8 @@ class Qwen3Config(ArchitectureConfig):
         for key in ("bos_token_id", "eos_token_id"):
             if isinstance(data.get(key), list):
                 data[key] = data[key][0] if data[key] else None
-        if data.get("attention_bias", False):
-            raise ConfigError("Qwen3 config.json: attention_bias=true is not implemented")
+        if not isinstance(data.get("attention_bias", False), bool):
+            raise ConfigError(f"Qwen3 config.json: attention_bias must be true or false, found {data['attention_bias']!r}")
         nh, nkv = data["num_attention_heads"], data["num_key_value_heads"]
         if nh % nkv != 0:
             raise ConfigError(f"Qwen3 config.json: num_attention_heads {nh} is not a multiple of num_key_value_heads {nkv}")
@@ -146,6 +149,7 @@ class Qwen3Config(ArchitectureConfig):
             use_sliding_window=use_window, sliding_window=window if use_window else None,
             layer_types=list(layer_types) if (use_window and layer_types is not None) else None,
             max_window_layers=first_windowed if (use_window and layer_types is None) else None,
+            attention_bias=bool(data.get("attention_bias", False)),
             extra={k: v for k, v in data.items() if k not in known and k not in ("architectures", "rope_parameters")},
         )
 
@@ -176,7 +180,7 @@ class Qwen3Config(ArchitectureConfig):
                 mixer=PartSpec("attention", {
                     "hidden_size": H, "num_heads": self.num_attention_heads, "num_kv_heads": self.num_key_value_heads,
                     "head_dim": self.head_dim, "qk_norm_eps": self.rms_norm_eps, "position": position,
-                    "window": self.layer_window(i), "scale": None, "prefix": "self_attn.",
+                    "window": self.layer_window(i), "scale": None, "prefix": "self_attn.", "qkv_bias": self.attention_bias,
                 }),
                 ffn_norm=PartSpec("rms_norm", {"size": H, "eps": self.rms_norm_eps, "weight": "post_attention_layernorm.weight"}),
                 feed_forward=PartSpec("gated_mlp", {"hidden_size": H, "intermediate_size": self.intermediate_size,

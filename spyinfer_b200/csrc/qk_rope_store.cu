@@ -10,10 +10,13 @@
 //   v    copied to the page of its position
 //
 // Norm (optional): x * (1/sqrt(mean(x^2) + eps)) * w over head_dim, 32-bit.
-// Rotation (optional): pairs (j, j + rot_half) for j < rot_half, angles from a table of
-// (cos, sin) [positions, rot_half] built in 32-bit by spy_build_rope_table; elements from
-// 2*rot_half on pass through.  Formula: src/backends/cpu/cpu_operator.cpp:397-408,
-// table: src/utils/constant_table.hpp:28-41.
+// Rotation (optional): pair j of a head, j < rot_half, is rotated by the angle of table entry
+// (position, j); the table of (cos, sin) [positions, rot_half] is built in 32-bit by
+// spy_build_rope_table; elements from 2*rot_half on pass through.  Which two elements form pair
+// j is the pairing rule: 0 ("half") (j, j + rot_half), the reference's (formula:
+// src/backends/cpu/cpu_operator.cpp:397-408, table: src/utils/constant_table.hpp:28-41);
+// 1 ("interleaved") (2j, 2j + 1), the other rule in use (the reference's doc/op.md:58-95
+// describes it, its code does not use it).
 //
 // Pages of one cache: [num_pages][2 (K, V)][nkv][page_size][hd].  A token at position p of
 // sequence s lies in page block_table[s, p / page_size] at slot p % page_size.
@@ -50,7 +53,7 @@ __global__ void qk_rope_store_kernel(const TS* src, int src_splits, long long sr
                                      int nh, int nkv, int hd, const TW* __restrict__ q_w, const TW* __restrict__ k_w, float eps,
                                      const float2* __restrict__ cos_sin, int rot_half, int table_rows, const int* __restrict__ positions,
                                      const int* __restrict__ seq_of_token, const int* __restrict__ block_table, int table_width, TC* pages,
-                                     int page_size, int num_pages, int store, int* status)
+                                     int page_size, int num_pages, int store, int pairing, int* status)
 {
     extern __shared__ float head_buf[];  // WARPS_PER_BLOCK * hd
     pdl_enter();
@@ -110,10 +113,12 @@ __global__ void qk_rope_store_kernel(const TS* src, int src_splits, long long sr
     for (int d = lane; d < hd; d += 32) {
         float v = buf[d];
         if (rotate && d < 2 * rot_half) {
-            const int j = d < rot_half ? d : d - rot_half;
+            // pair j = (a, b): a' = a cos - b sin, b' = a sin + b cos
+            const bool first = pairing == 0 ? d < rot_half : (d & 1) == 0;
+            const int j = pairing == 0 ? (first ? d : d - rot_half) : d >> 1;
             const float2 cs = cos_sin[(size_t)pos * rot_half + j];
-            const float lo = buf[j], hi = buf[j + rot_half];
-            v = d < rot_half ? lo * cs.x - hi * cs.y : lo * cs.y + hi * cs.x;
+            const float lo = buf[pairing == 0 ? j : 2 * j], hi = buf[pairing == 0 ? j + rot_half : 2 * j + 1];
+            v = first ? lo * cs.x - hi * cs.y : lo * cs.y + hi * cs.x;
         }
         if (kind == 0) q_dst[d] = from_f32<TQ>(v);
         else dst_page[d] = from_f32<TC>(v);
@@ -354,7 +359,7 @@ template <typename TS, typename TQ, typename TC, typename TW>
 static int launch(const void* src, int src_splits, long long src_split_stride, void* q_out, long long q_out_stride, int tokens, int nh, int nkv,
                   int hd, const void* q_w, const void* k_w, float eps, const float* cos_sin, int rot_half, int table_rows, const int* positions,
                   const int* seq_of_token, const int* block_table, int table_width, void* pages, int page_size, int num_pages, int store,
-                  int* status, cudaStream_t stream)
+                  int pairing, int* status, cudaStream_t stream)
 {
     const int heads = store ? nh + 2 * nkv : nh;
     const long long items = (long long)tokens * heads;
@@ -365,7 +370,7 @@ static int launch(const void* src, int src_splits, long long src_split_stride, v
     spy_launch(qk_rope_store_kernel<TS, TQ, TC, TW>, dim3((int)blocks), dim3(WARPS_PER_BLOCK * 32), smem, stream,
         (const TS*)src, src_splits, src_split_stride, (TQ*)q_out, q_out_stride, tokens, nh, nkv, hd, (const TW*)q_w, (const TW*)k_w, eps,
         (const float2*)cos_sin, rot_half, table_rows, positions, seq_of_token, block_table, table_width, (TC*)pages, page_size, num_pages, store,
-        status);
+        pairing, status);
     SPY_CHECK_LAUNCH("qk_rope_store");
     return 0;
 }
@@ -375,13 +380,15 @@ static int launch(const void* src, int src_splits, long long src_split_stride, v
 // be src itself (same dtype, one split, stride (nh + 2 nkv) hd).
 // q_w / k_w: null for no norm (both or neither).  cos_sin: null for no rotation.
 // store == 0: only the q heads are processed (a layer that reads another layer's cache).
+// pairing: 0 pairs (j, j + rot_half), 1 pairs (2j, 2j + 1).
 extern "C" int spy_qk_rope_store(const void* src, int src_dtype, int src_splits, long long src_split_stride, void* q_out, int q_dtype,
                                  long long q_out_stride, int tokens, int nh, int nkv, int hd, const void* q_w, const void* k_w, int w_dtype,
                                  float eps, const float* cos_sin, int rot_half, int table_rows, const int* positions, const int* seq_of_token,
                                  const int* block_table, int table_width, void* pages, int cache_dtype, int page_size, int num_pages, int store,
-                                 int* status, cudaStream_t stream)
+                                 int pairing, int* status, cudaStream_t stream)
 {
     if (tokens <= 0) return 0;
+    if (pairing != 0 && pairing != 1) SPY_FAIL("qk_rope_store: unknown pairing rule %d (0: halves, 1: interleaved)", pairing);
     if (nh <= 0 || nkv <= 0 || hd <= 0) SPY_FAIL("qk_rope_store: heads %d/%d and head_dim %d must be positive", nh, nkv, hd);
     if (src_splits <= 0) SPY_FAIL("qk_rope_store: src_splits %d must be positive", src_splits);
     if (q_out_stride < (long long)nh * hd) SPY_FAIL("qk_rope_store: q_out rows of %lld elements cannot hold %d heads of %d", q_out_stride, nh, hd);
@@ -392,7 +399,7 @@ extern "C" int spy_qk_rope_store(const void* src, int src_dtype, int src_splits,
     const bool plain_bf16 = src_dtype == SPY_BF16 && src_splits == 1;
     const bool float_stack = src_dtype == SPY_F32 && src_split_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0 && q_out != src;
     if ((plain_bf16 || float_stack) && q_dtype == SPY_BF16 && (!store || cache_dtype == SPY_BF16) && hd == 128 &&
-        (cos_sin == nullptr || rot_half == 64) && q_out_stride % 8 == 0 &&
+        (cos_sin == nullptr || (rot_half == 64 && pairing == 0)) && q_out_stride % 8 == 0 &&
         ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(pages)) & 15) == 0) {
         const int heads = store ? nh + 2 * nkv : nh;
         const long long items = (long long)tokens * heads;
@@ -427,7 +434,7 @@ extern "C" int spy_qk_rope_store(const void* src, int src_dtype, int src_splits,
                 SPY_DISPATCH_DTYPE(w_dtype, TW, {
                     return launch<TS, TQ, TC, TW>(src, src_splits, src_split_stride, q_out, q_out_stride, tokens, nh, nkv, hd, q_w, k_w, eps,
                                                   cos_sin, rot_half, table_rows, positions, seq_of_token, block_table, table_width, pages,
-                                                  page_size, num_pages, store, status, stream);
+                                                  page_size, num_pages, store, pairing, status, stream);
                 })
             })
         })

@@ -143,13 +143,17 @@ def build_rope_table(inv_freq: torch.Tensor, rows: int) -> torch.Tensor:
 def qk_rope_store(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, q_weight: Optional[torch.Tensor],
                   k_weight: Optional[torch.Tensor], eps: float, rope_table: Optional[torch.Tensor], positions: torch.Tensor,
                   seq_of_token: torch.Tensor, block_table: Optional[torch.Tensor], pages: Optional[torch.Tensor], store: bool = True,
-                  status: Optional[torch.Tensor] = None, q_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                  status: Optional[torch.Tensor] = None, q_out: Optional[torch.Tensor] = None, pairing: str = "half") -> torch.Tensor:
     """Per-head RMSNorm (if weights are given) and rotation (if a table is given) of the q and k
     heads of ``qkv [T, (nh + 2 nkv) hd]``, or of a stack ``[splits, T, ...]`` of float32 partial
     products that is summed on the way.  q goes to ``q_out [T, nh hd]`` (default: in place,
     which a stack does not allow).  With ``store`` the k heads (normed, rotated) and the v heads
     go to ``pages [num_pages, 2, nkv, page_size, hd]`` through ``block_table [S, width]``.
+    ``pairing``: which elements the angle ``j`` of the table rotates: ``"half"`` ``(j, j + r)``,
+    ``"interleaved"`` ``(2j, 2j + 1)``.
     Returns the tensor that holds q (rows may be wider than ``nh hd``)."""
+    if pairing not in ("half", "interleaved"):
+        raise KernelError(f"qk_rope_store: unknown pairing rule {pairing!r}")
     width = (num_heads + 2 * num_kv_heads) * head_dim
     if qkv.dim() == 3:
         _check(qkv, "qkv partial products", torch.float32, 3)
@@ -200,7 +204,7 @@ def qk_rope_store(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim
           _code(q_out, "q output"), ctypes.c_longlong(q_out.shape[1]), T, num_heads, num_kv_heads, head_dim, _ptr(q_weight), _ptr(k_weight),
           w_code, ctypes.c_float(eps), _ptr(rope_table), rot_half, table_rows, _ptr(positions), _ptr(seq_of_token),
           _ptr(block_table if store else None), table_width, _ptr(pages if store else None), cache_code, page_size, num_pages,
-          int(bool(store)), _ptr(status), _stream())
+          int(bool(store)), 0 if pairing == "half" else 1, _ptr(status), _stream())
     return q_out
 
 
@@ -388,6 +392,16 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     if two_i % 2 != 0 or tuple(out.shape) != (T, two_i // 2):
         raise KernelError(f"swiglu: input {tuple(gate_up.shape)} and output {tuple(out.shape)} do not fit")
     _call("swiglu", "spy_swiglu", _ptr(gate_up), _ptr(out), _code(gate_up, "swiglu input"), T, two_i // 2, _stream())
+    return out
+
+
+def add_bias(out: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """``out[t, c] += bias[c]`` in place (32-bit sum); out [T, C] float32 or bfloat16, bias [C]."""
+    _check(out, "bias target", ndim=2)
+    _check(bias, "bias", ndim=1)
+    if bias.shape[0] != out.shape[1]:
+        raise KernelError(f"add_bias: a bias of {bias.shape[0]} does not fit rows of {out.shape[1]}")
+    _call("swiglu", "spy_add_bias", _ptr(out), _code(out, "bias target"), _ptr(bias), _code(bias, "bias"), out.shape[0], out.shape[1], _stream())
     return out
 
 

@@ -26,7 +26,8 @@ from .registry import build_part, register_part
 class Attention(Mixer):
     """params: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``, ``qk_norm_eps``
     (None: no q/k norm), ``position`` (a PartSpec or None), ``window`` (None: all keys),
-    ``scale`` (None: 1/sqrt(head_dim)), ``prefix``."""
+    ``scale`` (None: 1/sqrt(head_dim)), ``prefix``, ``qkv_bias`` and ``o_bias`` (default false: the
+    projections have bias tensors ``{q,k,v}_proj.bias`` / ``o_proj.bias``)."""
 
     graph_safe = True
 
@@ -44,6 +45,7 @@ class Attention(Mixer):
             raise ValueError(f"attention: window {self.window} must be positive")
         self.scale = float(params["scale"]) if params.get("scale") is not None else 1.0 / math.sqrt(float(self.hd))
         self.prefix = params.get("prefix", "")
+        self.qkv_bias, self.o_bias = bool(params.get("qkv_bias", False)), bool(params.get("o_bias", False))
         pos = params.get("position")
         self.position = build_part(pos, ctx) if pos is not None else None
         self.qkv = self.o = self.q_norm = self.k_norm = self.rope_table = None
@@ -57,6 +59,10 @@ class Attention(Mixer):
         if self.qk_norm_eps is not None:
             decls += [WeightDecl(p + "q_norm.weight", (hd,), init="one_plus_normal"),
                       WeightDecl(p + "k_norm.weight", (hd,), init="one_plus_normal")]
+        if self.qkv_bias:
+            decls += [WeightDecl(p + "q_proj.bias", (nh * hd,)), WeightDecl(p + "k_proj.bias", (nkv * hd,)), WeightDecl(p + "v_proj.bias", (nkv * hd,))]
+        if self.o_bias:
+            decls += [WeightDecl(p + "o_proj.bias", (H,))]
         return decls
 
     def bind(self, tensors):
@@ -64,8 +70,11 @@ class Attention(Mixer):
         qkv = [tensors[p + n] for n in ("q_proj.weight", "k_proj.weight", "v_proj.weight")]
         if len({t.dtype for t in qkv}) > 1:
             qkv = [t.float() for t in qkv]
-        self.qkv = Linear(torch.cat(qkv, dim=0).contiguous(), self.ctx.dtype)
-        self.o = Linear(tensors[p + "o_proj.weight"], self.ctx.dtype)
+        bias = None
+        if self.qkv_bias:
+            bias = torch.cat([tensors[p + n].float() for n in ("q_proj.bias", "k_proj.bias", "v_proj.bias")]).contiguous()
+        self.qkv = Linear(torch.cat(qkv, dim=0).contiguous(), self.ctx.dtype, bias=bias)
+        self.o = Linear(tensors[p + "o_proj.weight"], self.ctx.dtype, bias=tensors[p + "o_proj.bias"] if self.o_bias else None)
         if self.qk_norm_eps is not None:
             self.q_norm, self.k_norm = tensors[p + "q_norm.weight"], tensors[p + "k_norm.weight"]
             if self.q_norm.dtype != self.k_norm.dtype:
@@ -115,7 +124,8 @@ class Attention(Mixer):
             q = torch.empty((x.shape[0], self.nh * self.hd), dtype=x.dtype, device=x.device)
         q = kernels.qk_rope_store(qkv, self.nh, self.nkv, self.hd, self.q_norm, self.k_norm, float(self.qk_norm_eps or 0.0),
                                   self.rope_table, batch.positions, batch.seq_of_token, cache.block_table, cache.pages,
-                                  store=cache.writes, status=batch.status, q_out=q)
+                                  store=cache.writes, status=batch.status, q_out=q,
+                                  pairing=self.position.pairing if self.position is not None else "half")
         out = torch.empty((x.shape[0], self.nh * self.hd), dtype=x.dtype, device=x.device)
         decoding = batch.num_tokens == batch.num_seqs         # every request brings one token
         if not self.fast:

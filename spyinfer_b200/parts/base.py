@@ -73,9 +73,14 @@ class Norm(Part):
 
 
 class PositionEncoding(Part):
+    #: which two elements of a head the table's angle ``j`` rotates: "half" ``(j, j + r)`` or
+    #: "interleaved" ``(2j, 2j + 1)``
+    pairing: str = "half"
+
     def rotation_table(self) -> Optional[torch.Tensor]:
-        """For encodings that rotate pairs ``(j, j + r)`` of each head: float32 ``[positions, r, 2]``
-        of (cos, sin), which the fused q/k kernel applies; None for no rotation."""
+        """For encodings that rotate pairs of each head's elements: float32 ``[positions, r, 2]``
+        of (cos, sin) per position and pair, which the fused q/k kernel applies by the part's
+        ``pairing`` rule; None for no rotation."""
         return None
 
 

@@ -1,4 +1,4 @@
-"""``y = x @ W^T`` for weights stored ``[out, in]``, as every projection of the model is.
+"""``y = x @ W^T (+ b)`` for weights stored ``[out, in]``, as every projection of the model is.
 
 The kernel is chosen by storage types and shape: bfloat16 activations with bfloat16 weights
 go to the tcgen05 tensor-core kernel when it takes the shape, everything else (the float32
@@ -33,22 +33,34 @@ class Linear:
     #: False where the next product follows at once (nothing short runs in between, so there is no idle memory to use)
     hint_next: bool = True
 
-    def __init__(self, weight: torch.Tensor, activation_dtype: torch.dtype):
+    def __init__(self, weight: torch.Tensor, activation_dtype: torch.dtype, bias: Optional[torch.Tensor] = None):
+        """``bias`` ``[out]`` (optional) is added by a pass of its own after the product; such a product
+        always hands over a summed result (``defer`` is ignored) and takes no fused epilogue."""
         if weight.dim() != 2:
             raise ValueError(f"a linear weight is [out, in], found shape {tuple(weight.shape)}")
-        self.weight = weight
+        if bias is not None and tuple(bias.shape) != (weight.shape[0],):
+            raise ValueError(f"a bias of shape {tuple(bias.shape)} does not fit a weight of shape {tuple(weight.shape)}")
+        self.weight, self.bias = weight, bias
         self.out_features, self.in_features = weight.shape
         self.fast = (activation_dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
                      and kernels.tensor_core_gemm_takes(self.out_features, self.in_features))
         self.prefetch_bytes = _prefetch_cap()
 
     def modules(self) -> List[str]:
-        return ["gemm_tcgen05"] if self.fast else ["gemm_simt"]
+        return (["gemm_tcgen05"] if self.fast else ["gemm_simt"]) + (["swiglu"] if self.bias is not None else [])
 
     def __call__(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None, epilogue: Optional[str] = None, defer: bool = False) -> torch.Tensor:
         """``epilogue="swiglu"`` (tensor-core kernel only; the weight's rows must alternate gate
         and up rows) returns ``silu(gate) * up``.  ``defer=True`` allows the result to come back
         as a stack ``[splits, rows, out]`` of float32 partial products that the consumer sums."""
+        if self.bias is not None:
+            if epilogue is not None:
+                raise ValueError("a product with a bias takes no fused epilogue")
+            defer = False
+        y = self._product(x, out_dtype, epilogue, defer)
+        return kernels.add_bias(y, self.bias) if self.bias is not None else y
+
+    def _product(self, x, out_dtype, epilogue, defer):
         if self.fast:
             hint = self.next_weight if self.hint_next and x.shape[0] <= 256 and self.prefetch_bytes > 0 else None
             return kernels.gemm_tcgen05(x, self.weight, out_dtype=out_dtype or x.dtype, epilogue=epilogue, defer=defer,

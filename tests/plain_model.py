@@ -109,13 +109,22 @@ def attention_mixer(x, w, prefix, cfg, positions, window=None):
 
     src/models/qwen3.hpp:136-213 in that order: three linears (138-158), RMSNorm over
     head_dim with one shared weight and the model's eps on q and k, not v (161-180),
-    RoPE on q and k (183-194), attention (197-205), o_proj (207-213).
+    RoPE on q and k (183-194), attention (197-205), o_proj (207-213).  The reference's model has
+    bias slots for q, k and v that it never binds (:39, 143, 150, 157); where the weights hold
+    ``{q,k,v}_proj.bias`` they are added to the projections (``y = x W^T + b``,
+    src/backends/cpu/cpu_operator.cpp:150-186).
     """
     T = x.shape[0]
     nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
-    q = linear(x, w[prefix + "self_attn.q_proj.weight"]).reshape(T, nh, hd)
-    k = linear(x, w[prefix + "self_attn.k_proj.weight"]).reshape(T, nkv, hd)
-    v = linear(x, w[prefix + "self_attn.v_proj.weight"]).reshape(T, nkv, hd)
+
+    def projected(name):
+        y = linear(x, w[prefix + f"self_attn.{name}_proj.weight"])
+        b = w.get(prefix + f"self_attn.{name}_proj.bias")
+        return y if b is None else y + b.to(y.dtype)
+
+    q = projected("q").reshape(T, nh, hd)
+    k = projected("k").reshape(T, nkv, hd)
+    v = projected("v").reshape(T, nkv, hd)
     q = rms_norm(q, w[prefix + "self_attn.q_norm.weight"], cfg["rms_norm_eps"])
     k = rms_norm(k, w[prefix + "self_attn.k_norm.weight"], cfg["rms_norm_eps"])
     cos, sin = rotary_angles(positions, hd, cfg["rope_theta"], compute=x.dtype)
@@ -256,6 +265,10 @@ def random_weights(cfg, seed: int, std: float = 0.02, norm_std: float = 0.05):
         w[p + "self_attn.o_proj.weight"] = lin(H, nh * hd)
         w[p + "self_attn.q_norm.weight"] = norm(hd)
         w[p + "self_attn.k_norm.weight"] = norm(hd)
+        if cfg.get("attention_bias", False):
+            w[p + "self_attn.q_proj.bias"] = lin(nh * hd) * 10.0
+            w[p + "self_attn.k_proj.bias"] = lin(nkv * hd) * 10.0
+            w[p + "self_attn.v_proj.bias"] = lin(nkv * hd) * 10.0
         w[p + "post_attention_layernorm.weight"] = norm(H)
         w[p + "mlp.gate_proj.weight"] = lin(I, H)
         w[p + "mlp.up_proj.weight"] = lin(I, H)

@@ -62,7 +62,7 @@ def test_missing_keys_are_named(key):
 
 
 @pytest.mark.parametrize("patch", [{"num_key_value_heads": 3}, {"hidden_act": "gelu"}, {"rope_scaling": {"type": "yarn"}},
-                                   {"attention_bias": True}, {"head_dim": 15}, {"vocab_size": -1},
+                                   {"attention_bias": "yes"}, {"head_dim": 15}, {"vocab_size": -1},
                                    {"use_sliding_window": True, "sliding_window": None},
                                    {"use_sliding_window": True, "sliding_window": 8},
                                    {"use_sliding_window": True, "sliding_window": 8, "max_window_layers": 3},
@@ -115,6 +115,15 @@ def test_keys_that_are_not_read_are_named_in_a_warning():
             config_from_json(TINY[name]["config"])
         config_from_json(dict(TINY["a"]["config"], torch_dtype="bfloat16", use_cache=True, attention_dropout=0.0, transformers_version="x",
                               sliding_window=None, max_window_layers=28, use_sliding_window=False))
+
+
+def test_attention_bias_gives_the_q_k_v_projections_bias_tensors():
+    from spyinfer_b200.engine.model import declared_weights
+    spec = config_from_json(TINY["e"]["config"]).to_spec()
+    names = {d.name: d.shape for d in declared_weights(spec)}
+    assert names["model.layers.1.self_attn.q_proj.bias"] == (5 * 16,) and names["model.layers.0.self_attn.v_proj.bias"] == (1 * 16,)
+    assert "model.layers.0.self_attn.o_proj.bias" not in names
+    assert not any(n.endswith(".bias") for n in {d.name for d in declared_weights(config_from_json(TINY["a"]["config"]).to_spec())})
 
 
 def test_config_round_trips_through_json(tmp_path):

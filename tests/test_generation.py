@@ -35,7 +35,7 @@ def check_greedy(weights, cfg, prompt, out, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["a", "b", "c", "d"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d", "e"])
 def test_greedy_generation_matches_plain(name, dtype, tiny_models):
     from spyinfer_b200 import SamplingParams
     folder, cfg, weights = tiny_models[name]

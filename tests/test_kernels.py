@@ -11,6 +11,31 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
+@pytest.fixture(autouse=True)
+def guard_zones(guarded_allocations):
+    """Every device buffer of these tests lies between guard zones, checked after each test."""
+    yield guarded_allocations
+
+
+def test_guard_zones_see_a_write_outside_a_buffer(guard_zones):
+    """The checker itself: a buffer made under the fixture is usable, aligned and surrounded, and a
+    byte written one place past its end, or one before its start, is found."""
+    a = torch.empty(3, 5, device=DEV, dtype=torch.bfloat16)
+    b = torch.full((7,), 2.0, device=DEV)
+    c = torch.zeros(4, 4, device=DEV, dtype=torch.int32)
+    assert a.data_ptr() % 256 == 0 and a.is_contiguous() and float(b.sum()) == 14.0 and int(c.abs().sum()) == 0
+    assert guard_zones.check() >= 3
+    raw, nbytes = guard_zones.held[0]
+    raw[guard_zones.ZONE + nbytes] = 0
+    with pytest.raises(AssertionError, match="past the end"):
+        guard_zones.check()
+    raw[guard_zones.ZONE + nbytes] = guard_zones.PATTERN
+    raw[guard_zones.ZONE - 1] = 0
+    with pytest.raises(AssertionError, match="before the start"):
+        guard_zones.check()
+    raw[guard_zones.ZONE - 1] = guard_zones.PATTERN
+
+
 def tol(dtype):
     return dict(rtol=2e-2, atol=2e-2) if dtype == torch.bfloat16 else dict(rtol=2e-5, atol=2e-5)
 
@@ -173,8 +198,9 @@ def test_attention_generic_finds_one_far_key():
 
 @pytest.mark.parametrize("adtype,cdtype,wdtype", [(torch.float32, torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16, torch.bfloat16),
                                                   (torch.float32, torch.float32, torch.bfloat16)])
+@pytest.mark.parametrize("pairing", ["half", "interleaved"])
 @pytest.mark.parametrize("nh,nkv,hd,rot,page_size", [(4, 2, 16, 16, 4), (3, 3, 48, 32, 8), (8, 2, 128, 128, 16), (2, 1, 80, 80, 5), (5, 1, 128, 64, 16)])
-def test_qk_norm_rope_store(adtype, cdtype, wdtype, nh, nkv, hd, rot, page_size):
+def test_qk_norm_rope_store(adtype, cdtype, wdtype, nh, nkv, hd, rot, page_size, pairing):
     from spyinfer_b200 import kernels
     torch.manual_seed(nh * hd)
     S, lens = 3, [9, 1, 30]
@@ -198,12 +224,16 @@ def test_qk_norm_rope_store(adtype, cdtype, wdtype, nh, nkv, hd, rot, page_size)
     seq_of = torch.tensor([s for s, _ in toks], dtype=torch.int32, device=DEV)
     before = qkv.clone().float()
     status = torch.zeros(2, dtype=torch.int32, device=DEV)
-    kernels.qk_rope_store(qkv, nh, nkv, hd, qw, kw, eps, table, positions, seq_of, bt, pages, store=True, status=status)
+    kernels.qk_rope_store(qkv, nh, nkv, hd, qw, kw, eps, table, positions, seq_of, bt, pages, store=True, status=status, pairing=pairing)
     assert status[0].item() == 0
 
     def norm_rope(x, w):                                    # x [T, heads, hd] float32
         x = x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * w.float()
         c, s = torch.cos(pos_f[positions.long()])[:, None, :], torch.sin(pos_f[positions.long()])[:, None, :]
+        if pairing == "interleaved":                        # angle j turns the pair (2j, 2j + 1)
+            lo, hi, rest = x[..., 0:rot:2], x[..., 1:rot:2], x[..., rot:]
+            turned = torch.stack([lo * c - hi * s, lo * s + hi * c], dim=-1).flatten(-2)
+            return torch.cat([turned, rest], dim=-1)
         lo, hi, rest = x[..., :rot // 2], x[..., rot // 2:rot], x[..., rot:]
         return torch.cat([lo * c - hi * s, lo * s + hi * c, rest], dim=-1)
 
@@ -224,7 +254,7 @@ def test_qk_norm_rope_store(adtype, cdtype, wdtype, nh, nkv, hd, rot, page_size)
     # store=False touches no page and still norms and rotates q
     qkv2 = before.to(adtype)
     pages2 = torch.zeros_like(pages)
-    kernels.qk_rope_store(qkv2, nh, nkv, hd, qw, kw, eps, table, positions, seq_of, None, None, store=False)
+    kernels.qk_rope_store(qkv2, nh, nkv, hd, qw, kw, eps, table, positions, seq_of, None, None, store=False, pairing=pairing)
     assert torch.equal(qkv2[:, :nh * hd], qkv[:, :nh * hd]) and pages2.abs().sum() == 0
     # a block-table entry that is no page is reported and skipped
     bad = bt.clone()

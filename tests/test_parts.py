@@ -608,3 +608,65 @@ def test_a_whole_architecture_from_this_file_generates_through_the_scheduler_and
         assert tight.generate(prompts, sp) == want
         assert tight.scheduler.num_preemptions > 0, "the pool was meant to be too small"
         tight.runner.cache.check_invariants()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_interleaved_pairs_and_scaled_frequencies_are_parameters_of_the_rotary_part(dtype):
+    """``rotary_interleaved`` (angle j turns the pair (2j, 2j + 1)) with ``frequency_scale`` 4 on one layer and
+    ``rotary_half`` with explicit ``inverse_frequencies`` on the other, at head size 128, where the
+    bfloat16 path has a kernel of its own for the usual rule and must not take it for the other one."""
+    from spyinfer_b200.config import EngineConfig, LayerSpec, ModelSpec, PartSpec, RunEntry
+    from spyinfer_b200.engine import Model, ModelRunner, StepEntry
+    from spyinfer_b200.weights import random_tensors
+    H, V, nh, nkv, hd, I, eps, theta = 128, 211, 2, 1, 128, 96, 1e-6, 5000.0
+    given = [0.5 / (j + 1) for j in range(hd // 2)]
+    norm = lambda name: PartSpec("rms_norm", {"size": H, "eps": eps, "weight": name})
+    attn = lambda pos: PartSpec("attention", {"hidden_size": H, "num_heads": nh, "num_kv_heads": nkv, "head_dim": hd, "qk_norm_eps": eps,
+                                              "position": pos, "window": None, "scale": None, "prefix": "self_attn."})
+    ffn = PartSpec("gated_mlp", {"hidden_size": H, "intermediate_size": I, "activation": "silu", "prefix": "mlp."})
+    layers = [LayerSpec("pre_norm", norm("input_layernorm.weight"), attn(PartSpec("rotary_interleaved", {"theta": theta, "rotary_dim": hd, "frequency_scale": 4.0})),
+                        norm("post_attention_layernorm.weight"), ffn, "model.layers.0."),
+              LayerSpec("pre_norm", norm("input_layernorm.weight"), attn(PartSpec("rotary_half", {"theta": theta, "rotary_dim": hd, "inverse_frequencies": given})),
+                        norm("post_attention_layernorm.weight"), ffn, "model.layers.1.")]
+    spec = ModelSpec(architecture="toy3", hidden_size=H, vocab_size=V,
+                     embedding=PartSpec("token_embedding", {"vocab_size": V, "hidden_size": H, "weight": "model.embed_tokens.weight"}),
+                     layers=layers, run_order=[RunEntry(0), RunEntry(1)], final_norm=norm("model.norm.weight"),
+                     head=PartSpec("lm_head", {"vocab_size": V, "hidden_size": H, "tied": True, "weight": "lm_head.weight",
+                                               "tied_to": "model.embed_tokens.weight"}), max_position=128)
+    cfg = EngineConfig(dtype=dtype, max_num_seqs=2, max_model_len=64, kvcache_block_size=16, num_kvcache_blocks=8, max_num_batched_tokens=64)
+    model = Model(spec, torch.float32 if dtype == "float32" else torch.bfloat16, cfg.device, cfg.max_model_len)
+    w = dict(random_tensors(model.weight_decls(), seed=12, std=0.08, norm_std=0.1))
+    model.bind({k: v.to(DEV) for k, v in w.items()})
+    runner = ModelRunner(model, cfg)
+    tokens = np.random.default_rng(2).integers(0, V, 29).tolist()
+    T, pos = len(tokens), torch.arange(len(tokens), dtype=torch.float32)
+
+    def turn(x, angle, interleaved):                        # x [T, heads, hd]
+        c, s = torch.cos(angle)[:, None, :], torch.sin(angle)[:, None, :]
+        if interleaved:
+            lo, hi = x[..., 0::2], x[..., 1::2]
+            return torch.stack([lo * c - hi * s, lo * s + hi * c], dim=-1).flatten(-2)
+        return plain_model.rotate_half(x, torch.cos(angle), torch.sin(angle))
+
+    h = plain_model.embed_tokens(w["model.embed_tokens.weight"], tokens)
+    for layer in range(2):
+        p = f"model.layers.{layer}."
+        n = plain_model.rms_norm(h, w[p + "input_layernorm.weight"], eps)
+        if layer == 0:
+            inv = torch.pow(torch.tensor(theta), -torch.arange(hd // 2, dtype=torch.float32) / (hd // 2)) / 4.0
+        else:
+            inv = torch.tensor(given, dtype=torch.float32)
+        angle = pos[:, None] * inv[None, :]
+        q = turn(plain_model.rms_norm(plain_model.linear(n, w[p + "self_attn.q_proj.weight"]).reshape(T, nh, hd), w[p + "self_attn.q_norm.weight"], eps), angle, layer == 0)
+        k = turn(plain_model.rms_norm(plain_model.linear(n, w[p + "self_attn.k_proj.weight"]).reshape(T, nkv, hd), w[p + "self_attn.k_norm.weight"], eps), angle, layer == 0)
+        v = plain_model.linear(n, w[p + "self_attn.v_proj.weight"]).reshape(T, nkv, hd)
+        o = plain_model.causal_attention(q, k, v, list(range(T)))
+        h = h + plain_model.linear(o.reshape(T, nh * hd), w[p + "self_attn.o_proj.weight"])
+        h = h + plain_model.feed_forward(plain_model.rms_norm(h, w[p + "post_attention_layernorm.weight"], eps), w, p)
+    want = plain_model.linear(plain_model.rms_norm(h, w["model.norm.weight"], eps), w["model.embed_tokens.weight"])
+    tol = dict(rtol=1e-4, atol=2e-5) if dtype == "float32" else dict(rtol=0.0, atol=0.05 * want.abs().max().item())
+    whole = runner.step([StepEntry("w", tokens, range(T))]).cpu()
+    torch.testing.assert_close(whole, want, **tol)
+    cut = torch.cat([runner.step([StepEntry("c", tokens[a:b], range(b - a))]).cpu() for a, b in [(0, 11), (11, 13), (13, 14), (14, 29)]])
+    torch.testing.assert_close(cut, want, **tol)
+    runner.check_status()

@@ -41,7 +41,7 @@ def requests_of(name):
 
 
 # (model, page size); None: the program's default with the pool from --max-tokens
-CASES = [("a", None), ("b", None), ("c", None), ("d", None), ("a", 4), ("b", 8), ("d", 4)]
+CASES = [("a", None), ("b", None), ("c", None), ("d", None), ("e", None), ("a", 4), ("b", 8), ("d", 4)]
 CASE_IDS = [f"{n}-page{p or 16}" for n, p in CASES]
 
 
