@@ -295,8 +295,9 @@ def attention_mma(q: torch.Tensor, num_heads: int, head_dim: int, out: torch.Ten
 def attention_tc(q: torch.Tensor, num_heads: int, head_dim: int, out: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor,
                  positions: torch.Tensor, q_start: torch.Tensor, num_seqs: int, scale: float, window: Optional[int] = None,
                  status: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Attention of a batch over its pages on tcgen05 (128-row blocks, scores and output in tensor
-    memory, pages brought in by TMA): prompt portions, any mix.  Page sizes 8 .. 128."""
+    """Attention of a batch over its pages on tcgen05 (blocks of two 128-row query tiles that share
+    every key and value tile, scores and output in tensor memory, pages brought in by TMA): prompt
+    portions, any mix.  Page sizes 8 .. 128."""
     _check(q, "attention queries", torch.bfloat16, 2)
     _check(out, "attention output", torch.bfloat16, 2)
     _check(pages, "cache pages", torch.bfloat16, 5)

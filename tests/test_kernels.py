@@ -672,6 +672,34 @@ def test_attention_tc_mixed_batch(nh, nkv, hd, page_size, window):
         torch.testing.assert_close(out[i].view(nh, hd).double(), ref, rtol=2e-2, atol=2e-2)
 
 
+def test_attention_tc_blocks_of_one_query_tile_behind_blocks_of_two():
+    """A mixed step as serving has them: two decoded tokens with long contexts beside a prompt of 1,400 tokens, at
+    the 8B head counts.  There are more work items than SMs, so some blocks take a second item, and for some
+    of them that item is a decoded token's: a block of rows whose second query tile is empty, with many key
+    tiles, behind an item that used both tiles.  The idle half of the block then runs ahead of the working one."""
+    from spyinfer_b200 import kernels
+    torch.manual_seed(5)
+    nh, nkv, hd, page_size = 32, 8, 128, 16
+    lens = [1500, 700, 1400]
+    pages, bt, ks, vs = paged_setup(3, lens, nkv, hd, page_size, torch.bfloat16)
+    toks = [(0, 1499), (1, 699)] + [(2, p) for p in range(1400)]
+    T = len(toks)
+    q = torch.randn(T, (nh + 2 * nkv) * hd, device=DEV).to(torch.bfloat16)
+    positions = torch.tensor([p for _, p in toks], dtype=torch.int32, device=DEV)
+    q_start = torch.tensor([0, 1, 2, T], dtype=torch.int32, device=DEV)
+    scale = 1 / math.sqrt(hd)
+    for _ in range(2):
+        out = torch.full((T, nh * hd), float("nan"), device=DEV, dtype=torch.bfloat16)
+        kernels.attention_tc(q, nh, hd, out, pages, bt, positions, q_start, 3, scale)
+        torch.cuda.synchronize()
+        assert kernels.status_word(DEV)[0].item() == 0
+        assert torch.isfinite(out.float()).all()
+        for i in [0, 1, 2, 3, 65, 66, 129, 130] + list(range(97, T, 97)) + [T - 1]:
+            s_, p_ = toks[i]
+            ref = ref_attention(q[i, :nh * hd].view(nh, hd), ks[s_], vs[s_], p_, scale, None)
+            torch.testing.assert_close(out[i].view(nh, hd).double(), ref, rtol=2e-2, atol=2e-2)
+
+
 def test_attention_tc_refuses_pages_that_are_no_tma_box():
     from spyinfer_b200 import kernels
     pages, bt, ks, vs = paged_setup(1, [20], 1, 64, 5, torch.bfloat16)
