@@ -700,6 +700,66 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const 
 // and publishes an accumulator, in both blocks; the peer's epilogue threads arrive on the
 // leader's accumulator-empty barrier through the cluster's shared window.  Persistent: cluster c
 // walks tiles c, c + clusters, ...; two accumulators (2 x 256 columns) as in the kernel above.
+// How a cluster of the pair kernel walks through its work.  Whole units: unit u is tile
+// u % whole_tiles over K range u / whole_tiles (one range unless K is cut by plan), taken round
+// robin, cluster c the units c, c + clusters, ...  Ahead of them, when the host found that the last
+// round of whole tiles would leave most clusters idle for long, the cluster's share of the TAIL: the K blocks of
+// the last tail_tiles tiles are numbered through, tile after tile, and cluster c takes the numbers
+// [c * tail_share, (c + 1) * tail_share): one or two segments, each a range of K blocks of one
+// tile (tail_share is less than a tile's K blocks, so no segment is a whole tile).  A segment's
+// 32-bit partial tile goes to the workspace, slot (cluster, 0 or 1, block of the pair); the block
+// whose segment is the LAST of a tile to arrive (a counter per tile and block of the pair, which
+// that block also puts back to zero) adds the tile's partial tiles in the order of their K ranges
+// and stores the result.  Nothing waits for anything: no flag is spun on.
+struct PairUnit {
+    int tile, kb0, nkb, range, slot;
+    bool partial;
+};
+struct PairWalk {
+    int unit, clusters, whole_units, whole_tiles, kb_per_split, k_blocks, slot;
+    long long at, end;
+    __device__ PairWalk(int cluster, int clusters_, int num_tiles, int splits, int kb_per_split_, int k_blocks_, int tail_tiles, int tail_share)
+        : unit(cluster), clusters(clusters_), whole_units((num_tiles - tail_tiles) * splits), whole_tiles(num_tiles - tail_tiles),
+          kb_per_split(kb_per_split_), k_blocks(k_blocks_), slot(0)
+    {
+        const long long total = (long long)tail_tiles * k_blocks;
+        at = (long long)cluster * tail_share;
+        if (at > total) at = total;
+        end = at + tail_share < total ? at + tail_share : total;
+    }
+    __device__ bool next(PairUnit& u)
+    {
+        // the tail's segments come FIRST: the sums over their partial tiles (round trips to L2, by the epilogue warps
+        // of whichever block arrives last) then run beside the main loops of the whole tiles that follow, not after
+        // everything else as the kernel's last act
+        if (at < end) {
+            const int t = (int)(at / k_blocks);
+            u.tile = whole_tiles + t;
+            u.range = 0;
+            u.kb0 = (int)(at - (long long)t * k_blocks);
+            const long long left = end - at;
+            u.nkb = left < k_blocks - u.kb0 ? (int)left : k_blocks - u.kb0;
+            u.partial = true;
+            u.slot = slot++;
+            at += u.nkb;
+            return true;
+        }
+        if (unit < whole_units) {
+            u.tile = unit % whole_tiles;
+            u.range = unit / whole_tiles;
+            u.kb0 = u.range * kb_per_split;
+            u.nkb = (k_blocks < u.kb0 + kb_per_split ? k_blocks : u.kb0 + kb_per_split) - u.kb0;
+            u.partial = false;
+            u.slot = 0;
+            unit += clusters;
+            return true;
+        }
+        return false;
+    }
+};
+constexpr int PAIR_TAIL_MAX_TILES = 512;
+__device__ int g_pair_tail_count[2 * PAIR_TAIL_MAX_TILES];   // [tail tile][block of the pair]: segments of the tile that have arrived
+
 constexpr int PAIR_STAGES = 6;
 constexpr int PAIR_X_BYTES = BM * BK * 2;                    // 128 rows of X
 constexpr int PAIR_STAGE_BYTES = 2 * PAIR_X_BYTES;           // and 128 rows of Y
@@ -709,13 +769,12 @@ template <typename TC, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, TC* __restrict__ out,
                          long long ld, int x_rows, int y_rows, int k_blocks, int x_tiles, int num_tiles, int splits, int kb_per_split,
-                         long long split_stride, int* status)
+                         long long split_stride, int tail_tiles, int tail_share, float* __restrict__ workspace, int* status)
 {
     // splits > 1 (few tiles, 512 tokens or so): a work unit is one tile over one range of kb_per_split K blocks; unit u is
     // tile u % num_tiles of range u / num_tiles, and its 32-bit partial tile goes to out + range * split_stride (the
     // caller sums the ranges in order).  With one range a unit is a whole tile.
     constexpr int BN = 256;
-    const int num_units = num_tiles * splits;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* tiles = smem;
@@ -725,6 +784,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
     uint64_t* acc_empty = acc_full + 2;             // [2] the leader's are used: 256 arrivals
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* tail_last = reinterpret_cast<volatile int*>(tmem_slot + 2);   // this block's segment was the last of its tile to arrive
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
@@ -753,9 +813,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
         if (lane == 0) {
             long long g = 0;
             bool ok = true, first = true;
-            for (int unit = cluster; unit < num_units && ok; unit += clusters) {
-                const int tile = unit % num_tiles, kb0 = (unit / num_tiles) * kb_per_split;
-                const int nkb = min(k_blocks, kb0 + kb_per_split) - kb0;
+            PairWalk walk(cluster, clusters, num_tiles, splits, kb_per_split, k_blocks, tail_tiles, tail_share);
+            PairUnit u;
+            while (ok && walk.next(u)) {
+                const int tile = u.tile, kb0 = u.kb0, nkb = u.nkb;
                 const int x0 = (tile % x_tiles) * (2 * BM) + (int)rank * BM, y0 = (tile / x_tiles) * BN + (int)rank * (BN / 2);
                 int kb = 0;
                 if (first) {
@@ -791,9 +852,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
             long long g = 0;
             int i = 0;
             bool ok = true;
-            for (int unit = cluster; unit < num_units && ok; unit += clusters, ++i) {
-                const int kb0 = (unit / num_tiles) * kb_per_split;
-                const int nkb = min(k_blocks, kb0 + kb_per_split) - kb0;
+            PairWalk walk(cluster, clusters, num_tiles, splits, kb_per_split, k_blocks, tail_tiles, tail_share);
+            PairUnit u;
+            for (; ok && walk.next(u); ++i) {
+                const int nkb = u.nkb;
                 const int buf = i & 1;
                 const uint32_t aph = (uint32_t)(i >> 1) & 1;
                 if (i >= 2) ok = mbar_wait(acc_empty + buf, aph ^ 1, abort_flag);   // both blocks' epilogues have read this buffer's last tile
@@ -823,26 +885,93 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
         pdl_wait();   // the output buffer may still be in use by a kernel ahead in the stream
         int i = 0;
         bool ok = true;
-        for (int unit = cluster; unit < num_units && ok; unit += clusters, ++i) {
-            const int tile = unit % num_tiles;
-            TC* unit_out = out + (size_t)(unit / num_tiles) * split_stride;
+        PairWalk walk(cluster, clusters, num_tiles, splits, kb_per_split, k_blocks, tail_tiles, tail_share);
+        PairUnit u;
+        const int whole_tiles = num_tiles - tail_tiles;
+        for (; ok && walk.next(u); ++i) {
+            const int tile = u.tile;
+            TC* unit_out = out + (size_t)u.range * split_stride;
             const int buf = i & 1;
             const uint32_t aph = (uint32_t)(i >> 1) & 1;
             const int x0 = (tile % x_tiles) * (2 * BM) + (int)rank * BM, y0 = (tile / x_tiles) * BN;
             ok = mbar_wait(acc_full + buf, aph, abort_flag);
             if (!ok) break;
             fence_after_sync();
-            const int x = x0 + quarter * 32 + lane;
+            const int row = quarter * 32 + lane;
+            const int x = x0 + row;
+            if (!u.partial) {
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 32) {
+                    uint32_t r[32];
+                    tmem_load<32>(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c), r);
+                    tmem_wait_ld();
+                    store_chunk_normal<TC, EPI>(unit_out, ld, x, y0 + c, x_rows, y_rows, r);
+                }
+                fence_before_sync();
+                if (rank == 0) mbar_arrive(acc_empty + buf);
+                else mbar_arrive_cluster(map_to_rank(smem_u32(acc_empty + buf), 0));
+                continue;
+            }
+            // a segment of a tail tile: the partial tile goes to the workspace, and the accumulator is free again
+            float* mine = workspace + ((size_t)(cluster * 2 + u.slot) * 2 + rank) * STREAM_TILE_FLOATS;
 #pragma unroll 1
             for (int c = 0; c < BN; c += 32) {
                 uint32_t r[32];
                 tmem_load<32>(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c), r);
                 tmem_wait_ld();
-                store_chunk_normal<TC, EPI>(unit_out, ld, x, y0 + c, x_rows, y_rows, r);
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    __stcg(reinterpret_cast<float4*>(mine + partial_index(c, j, row)),
+                           make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3])));
             }
             fence_before_sync();
             if (rank == 0) mbar_arrive(acc_empty + buf);
             else mbar_arrive_cluster(map_to_rank(smem_u32(acc_empty + buf), 0));
+            // which segments make up this tile: clusters c_first .. c_last hold its K blocks, in this order
+            const int tile_rel = tile - whole_tiles;
+            const long long n0 = (long long)tile_rel * k_blocks;
+            const int c_first = (int)(n0 / tail_share), c_last = (int)((n0 + k_blocks - 1) / tail_share);
+            __threadfence();
+            epilogue_barrier();
+            if (row == 0) {
+                const int arrived = atomicAdd(&g_pair_tail_count[tile_rel * 2 + (int)rank], 1);
+                *tail_last = arrived == c_last - c_first ? 1 : 0;
+            }
+            epilogue_barrier();
+            const bool last = *tail_last != 0;
+            epilogue_barrier();   // everybody has read the flag before a later segment's arrival may write it again
+            if (!last) continue;
+            __threadfence();
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                float4 sum[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) sum[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int cl = c_first; cl <= c_last; ++cl) {
+                    const int sl = ((long long)cl * tail_share) / k_blocks == tile_rel ? 0 : 1;   // the cluster's share begins in this tile, or in the one before
+                    const float* theirs = workspace + ((size_t)(cl * 2 + sl) * 2 + rank) * STREAM_TILE_FLOATS;
+                    float4 v[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) v[j] = __ldcg(reinterpret_cast<const float4*>(theirs + partial_index(c, j, row)));
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        sum[j].x += v[j].x;
+                        sum[j].y += v[j].y;
+                        sum[j].z += v[j].z;
+                        sum[j].w += v[j].w;
+                    }
+                }
+                uint32_t r[32];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    r[4 * j] = __float_as_uint(sum[j].x);
+                    r[4 * j + 1] = __float_as_uint(sum[j].y);
+                    r[4 * j + 2] = __float_as_uint(sum[j].z);
+                    r[4 * j + 3] = __float_as_uint(sum[j].w);
+                }
+                store_chunk_normal<TC, EPI>(unit_out, ld, x, y0 + c, x_rows, y_rows, r);
+            }
+            if (row == 0) g_pair_tail_count[tile_rel * 2 + (int)rank] = 0;   // for the next product: nobody else touches it in this one
         }
     }
 
@@ -945,6 +1074,20 @@ bool pair_kernel_enabled()
 {
     const char* e = getenv("SPYINFER_GEMM_PAIRS");   // read at every call: a test may switch it
     return !(e != nullptr && e[0] == '0');
+}
+
+bool tail_sharing_enabled()
+{
+    const char* e = getenv("SPYINFER_GEMM_TAIL");   // read at every call: a test may switch it
+    return !(e != nullptr && e[0] == '0');
+}
+
+// K blocks of one cluster's time that sharing the last round must save to be worth its cost
+// (SPYINFER_GEMM_TAIL_MIN in the environment overrides it: tests use 0 to reach the path at small sizes).
+long long tail_sharing_threshold()
+{
+    const char* e = getenv("SPYINFER_GEMM_TAIL_MIN");
+    return e != nullptr ? atoll(e) : 100;
 }
 
 struct Plan {
@@ -1095,22 +1238,39 @@ extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, 
         if (splits > 1) {
             // ranges of K: 32-bit partial tiles into the scratch, [range][M][N]
             spy_launch_cluster(gemm_tcgen05_pair_kernel<float, 0>, dim3(2 * clusters), dim3(NUM_THREADS), PAIR_SMEM, stream, 2u, mx, my_half, (float*)scratch,
-                               (long long)N, M, N, k_blocks, x_tiles, (int)num_tiles, splits, kb_per_split, split_stride, status);
+                               (long long)N, M, N, k_blocks, x_tiles, (int)num_tiles, splits, kb_per_split, split_stride, 0, 0, (float*)nullptr, status);
             SPY_CHECK_LAUNCH("gemm_tcgen05 (pairs, K ranges)");
             if (!defer_reduce) {
                 if (int rc = reduce_splits(scratch, C, c_dtype, ldc, M, N, splits, stream)) return rc;
             }
             return 0;
         }
+        // The last round of whole tiles.  When it would leave clusters idle for long (a few tiles of a long K left over:
+        // the down projections of the larger models are 160 tiles on 74 clusters, a third round for twelve tiles),
+        // the K blocks of its tiles are shared out over all clusters instead (see PairWalk), through partial tiles in
+        // the scratch.  The sums over the partial tiles and the colder start cost about as much as 100 K blocks of
+        // one cluster, so only what saves more than that is shared (measured: at the 8B sizes, where 54 of 128 tiles
+        // are left over and a tile has 64 or 192 K blocks, whole tiles stay faster).
+        int tail_tiles = 0, tail_share = 0;
+        const long long left = num_tiles % clusters_max;
+        if (tail_sharing_enabled() && num_tiles > clusters_max && left > 0 && left <= PAIR_TAIL_MAX_TILES && scratch != nullptr &&
+            scratch_floats >= (long long)clusters_max * 4 * STREAM_TILE_FLOATS) {
+            const long long share = (left * k_blocks + clusters_max - 1) / clusters_max;
+            const long long saved = k_blocks - share;   // K blocks of a cluster's time that the last round no longer takes
+            if (share >= 8 && share < k_blocks && saved >= tail_sharing_threshold()) {
+                tail_tiles = (int)left;
+                tail_share = (int)share;
+            }
+        }
         if (epilogue == 1)
             spy_launch_cluster(gemm_tcgen05_pair_kernel<bf16, 1>, dim3(2 * clusters), dim3(NUM_THREADS), PAIR_SMEM, stream, 2u, mx, my_half, (bf16*)C, ldc,
-                               M, N, k_blocks, x_tiles, (int)num_tiles, 1, k_blocks, 0LL, status);
+                               M, N, k_blocks, x_tiles, (int)num_tiles, 1, k_blocks, 0LL, tail_tiles, tail_share, scratch, status);
         else if (c_dtype == SPY_F32)
             spy_launch_cluster(gemm_tcgen05_pair_kernel<float, 0>, dim3(2 * clusters), dim3(NUM_THREADS), PAIR_SMEM, stream, 2u, mx, my_half, (float*)C, ldc,
-                               M, N, k_blocks, x_tiles, (int)num_tiles, 1, k_blocks, 0LL, status);
+                               M, N, k_blocks, x_tiles, (int)num_tiles, 1, k_blocks, 0LL, tail_tiles, tail_share, scratch, status);
         else
             spy_launch_cluster(gemm_tcgen05_pair_kernel<bf16, 0>, dim3(2 * clusters), dim3(NUM_THREADS), PAIR_SMEM, stream, 2u, mx, my_half, (bf16*)C, ldc,
-                               M, N, k_blocks, x_tiles, (int)num_tiles, 1, k_blocks, 0LL, status);
+                               M, N, k_blocks, x_tiles, (int)num_tiles, 1, k_blocks, 0LL, tail_tiles, tail_share, scratch, status);
         SPY_CHECK_LAUNCH("gemm_tcgen05 (pairs)");
         return 0;
     }
@@ -1195,6 +1355,8 @@ extern "C" int spy_gemm_tcgen05_reset(cudaStream_t stream)
     void* flags = nullptr;
     SPY_CUDA(cudaGetSymbolAddress(&flags, g_stream_flags));
     SPY_CUDA(cudaMemsetAsync(flags, 0, sizeof(int) * STREAM_MAX_BLOCKS, stream));
+    SPY_CUDA(cudaGetSymbolAddress(&flags, g_pair_tail_count));   // the counters of the pair kernel's tail tiles, for the same reason
+    SPY_CUDA(cudaMemsetAsync(flags, 0, sizeof(int) * 2 * PAIR_TAIL_MAX_TILES, stream));
     return 0;
 }
 

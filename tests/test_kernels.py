@@ -504,6 +504,48 @@ def test_attention_mma_finds_one_far_key(split_keys):
         assert hit == inside, f"window {window}, far key {far}: expected {'a hit' if inside else 'no hit'}"
 
 
+@pytest.mark.parametrize("M,N,K,epilogue,out_dtype", [
+    (2048, 4096, 4096, None, torch.bfloat16),        # 128 tiles of 256 x 256 on 74 clusters: 54 tail tiles (the o projection at 2,048 tokens)
+    (2048, 6144, 4096, None, torch.float32),         # 192 tiles: 44 tail tiles
+    (1500, 5000, 1032, None, torch.bfloat16),        # tails in M, N and K as well: 6 x 20 tiles, 17 K blocks with 8 columns in the last
+    (2048, 5120, 8192, None, torch.bfloat16),        # 160 tiles: 12 tail tiles of 128 K blocks, shared by default (the o projection of the 32B shape)
+    (1200, 6400, 2048, "swiglu", torch.bfloat16),    # 5 x 25 tiles with the SwiGLU epilogue on the summed tile
+])
+def test_gemm_tcgen05_shares_the_last_round_of_tiles(M, N, K, epilogue, out_dtype, monkeypatch):
+    """Many tokens on pairs of blocks: when the last round of 256 x 256 tiles would leave clusters idle,
+    the K blocks of its tiles are shared out over all clusters and the partial tiles are summed by the
+    block that arrives last.  The result is the one of whole tiles (same products, sums in K order),
+    against a 32-bit reference, twice in a row (the arrival counters return to zero by themselves).
+    The threshold that keeps small products on whole tiles is lowered to zero for the test."""
+    from spyinfer_b200 import kernels
+    torch.manual_seed(M + N + K)
+    a = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
+    status = kernels.status_word(DEV)
+    n_out = N // 2 if epilogue else N
+    if epilogue:
+        g, u = a.float() @ w[0::2].float().t(), a.float() @ w[1::2].float().t()
+        ref = (g / (1 + torch.exp(-g))) * u
+    else:
+        ref = a.float() @ w.float().t()
+    outs = []
+    monkeypatch.setenv("SPYINFER_GEMM_TAIL_MIN", "0")
+    for tail in ("1", "1", "0"):
+        monkeypatch.setenv("SPYINFER_GEMM_TAIL", tail)
+        out = torch.full((M, n_out), float("nan"), device=DEV, dtype=out_dtype)
+        kernels.gemm_tcgen05(a, w, out, epilogue=epilogue)
+        torch.cuda.synchronize()
+        assert status[0].item() == 0 and torch.isfinite(out.float()).all()
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1])
+    if out_dtype == torch.float32:
+        torch.testing.assert_close(outs[0], ref, rtol=1e-4, atol=3e-4)
+        torch.testing.assert_close(outs[0], outs[2], rtol=1e-4, atol=2e-4)       # other order of the 32-bit sums over K
+    else:
+        torch.testing.assert_close(outs[0].float(), ref.to(torch.bfloat16).float(), rtol=1.6e-2, atol=4e-3)
+        assert (outs[0].float() - outs[2].float()).abs().max().item() <= 2.0 ** -6 * max(1.0, ref.abs().max().item())
+
+
 @pytest.mark.parametrize("M,I,K", [(3, 100, 64), (16, 328, 200), (40, 1000, 136), (64, 6144, 512), (70, 520, 264), (128, 12288, 1024), (130, 520, 264), (300, 12288, 1024),
                                    (520, 1000, 136), (1100, 2304, 512)])   # 512 rows and more: pairs of blocks on 256 x 256 tiles
 def test_gemm_tcgen05_swiglu_epilogue(M, I, K):
