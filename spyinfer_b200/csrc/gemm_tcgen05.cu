@@ -703,45 +703,58 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const 
 // How a cluster of the pair kernel walks through its work.  Whole units: unit u is tile
 // u % whole_tiles over K range u / whole_tiles (one range unless K is cut by plan), taken round
 // robin, cluster c the units c, c + clusters, ...  Ahead of them, when the host found that the last
-// round of whole tiles would leave most clusters idle for long, the cluster's share of the TAIL: the K blocks of
-// the last tail_tiles tiles are numbered through, tile after tile, and cluster c takes the numbers
-// [c * tail_share, (c + 1) * tail_share): one or two segments, each a range of K blocks of one
-// tile (tail_share is less than a tile's K blocks, so no segment is a whole tile).  A segment's
-// 32-bit partial tile goes to the workspace, slot (cluster, 0 or 1, block of the pair); the block
-// whose segment is the LAST of a tile to arrive (a counter per tile and block of the pair, which
-// that block also puts back to zero) adds the tile's partial tiles in the order of their K ranges
+// round of whole tiles would leave most clusters idle for long, the TAIL: the last tail_tiles tiles are
+// cut along K into segments that all clusters share, in such a way that clusters which work at the same
+// time walk the SAME range of K in different tiles, as they do in a round of whole tiles (neighbours then
+// find each other's operand tiles in L2; clusters that start at scattered K offsets fetch everything from
+// memory, which is slower than leaving clusters idle).  The first tail_p * tail_tiles clusters ("main")
+// take K blocks [0, tail_x) of a tile, cut into tail_p equal slices: cluster c the slice c / tail_tiles
+// of tail tile c % tail_tiles.  The other clusters ("helpers", H of them) take the rest [tail_x, K blocks)
+// of tail tiles h, h + H, h + 2H, ...  The host chooses tail_x so that both kinds end together.  A
+// segment's 32-bit partial tile goes to the workspace, slot (tail tile, segment, block of the pair);
+// the block whose segment is the LAST of a tile to arrive (a counter per tile and block of the pair,
+// which that block also puts back to zero) adds the tile's partial tiles in the order of their K ranges
 // and stores the result.  Nothing waits for anything: no flag is spun on.
 struct PairUnit {
-    int tile, kb0, nkb, range, slot;
+    int tile, kb0, nkb, range, seg;
     bool partial;
 };
 struct PairWalk {
-    int unit, clusters, whole_units, whole_tiles, kb_per_split, k_blocks, slot;
-    long long at, end;
-    __device__ PairWalk(int cluster, int clusters_, int num_tiles, int splits, int kb_per_split_, int k_blocks_, int tail_tiles, int tail_share)
-        : unit(cluster), clusters(clusters_), whole_units((num_tiles - tail_tiles) * splits), whole_tiles(num_tiles - tail_tiles),
-          kb_per_split(kb_per_split_), k_blocks(k_blocks_), slot(0)
+    int unit, clusters, whole_units, whole_tiles, kb_per_split, k_blocks;
+    int tail_tiles, tail_p, tail_x, tail_tile, tail_step, tail_seg, tail_kb0, tail_nkb;
+    __device__ PairWalk(int cluster, int clusters_, int num_tiles, int splits, int kb_per_split_, int k_blocks_, int tail_tiles_, int tail_p_, int tail_x_)
+        : unit(cluster), clusters(clusters_), whole_units((num_tiles - tail_tiles_) * splits), whole_tiles(num_tiles - tail_tiles_),
+          kb_per_split(kb_per_split_), k_blocks(k_blocks_), tail_tiles(tail_tiles_), tail_p(tail_p_), tail_x(tail_x_)
     {
-        const long long total = (long long)tail_tiles * k_blocks;
-        at = (long long)cluster * tail_share;
-        if (at > total) at = total;
-        end = at + tail_share < total ? at + tail_share : total;
+        const int mains = tail_p * tail_tiles;
+        if (cluster < mains) {                 // one slice of [0, tail_x) of one tail tile
+            const int slice = cluster / tail_tiles;
+            tail_tile = cluster % tail_tiles;
+            tail_step = tail_tiles;            // no second segment
+            tail_seg = slice;
+            tail_kb0 = (int)((long long)slice * tail_x / tail_p);
+            tail_nkb = (int)((long long)(slice + 1) * tail_x / tail_p) - tail_kb0;
+        } else {                               // the rest [tail_x, k_blocks) of every (clusters - mains)-th tail tile
+            tail_tile = tail_x < k_blocks ? cluster - mains : tail_tiles;
+            tail_step = clusters - mains;
+            tail_seg = tail_p;
+            tail_kb0 = tail_x;
+            tail_nkb = k_blocks - tail_x;
+        }
     }
     __device__ bool next(PairUnit& u)
     {
         // the tail's segments come FIRST: the sums over their partial tiles (round trips to L2, by the epilogue warps
         // of whichever block arrives last) then run beside the main loops of the whole tiles that follow, not after
         // everything else as the kernel's last act
-        if (at < end) {
-            const int t = (int)(at / k_blocks);
-            u.tile = whole_tiles + t;
+        if (tail_tile < tail_tiles) {
+            u.tile = whole_tiles + tail_tile;
             u.range = 0;
-            u.kb0 = (int)(at - (long long)t * k_blocks);
-            const long long left = end - at;
-            u.nkb = left < k_blocks - u.kb0 ? (int)left : k_blocks - u.kb0;
+            u.kb0 = tail_kb0;
+            u.nkb = tail_nkb;
             u.partial = true;
-            u.slot = slot++;
-            at += u.nkb;
+            u.seg = tail_seg;
+            tail_tile += tail_step;
             return true;
         }
         if (unit < whole_units) {
@@ -750,7 +763,7 @@ struct PairWalk {
             u.kb0 = u.range * kb_per_split;
             u.nkb = (k_blocks < u.kb0 + kb_per_split ? k_blocks : u.kb0 + kb_per_split) - u.kb0;
             u.partial = false;
-            u.slot = 0;
+            u.seg = 0;
             unit += clusters;
             return true;
         }
@@ -769,7 +782,7 @@ template <typename TC, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, TC* __restrict__ out,
                          long long ld, int x_rows, int y_rows, int k_blocks, int x_tiles, int num_tiles, int splits, int kb_per_split,
-                         long long split_stride, int tail_tiles, int tail_share, float* __restrict__ workspace, int* status)
+                         long long split_stride, int tail_tiles, int tail_p, int tail_x, float* __restrict__ workspace, int* status)
 {
     // splits > 1 (few tiles, 512 tokens or so): a work unit is one tile over one range of kb_per_split K blocks; unit u is
     // tile u % num_tiles of range u / num_tiles, and its 32-bit partial tile goes to out + range * split_stride (the
@@ -813,7 +826,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
         if (lane == 0) {
             long long g = 0;
             bool ok = true, first = true;
-            PairWalk walk(cluster, clusters, num_tiles, splits, kb_per_split, k_blocks, tail_tiles, tail_share);
+            PairWalk walk(cluster, clusters, num_tiles, splits, kb_per_split, k_blocks, tail_tiles, tail_p, tail_x);
             PairUnit u;
             while (ok && walk.next(u)) {
                 const int tile = u.tile, kb0 = u.kb0, nkb = u.nkb;
@@ -852,7 +865,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
             long long g = 0;
             int i = 0;
             bool ok = true;
-            PairWalk walk(cluster, clusters, num_tiles, splits, kb_per_split, k_blocks, tail_tiles, tail_share);
+            PairWalk walk(cluster, clusters, num_tiles, splits, kb_per_split, k_blocks, tail_tiles, tail_p, tail_x);
             PairUnit u;
             for (; ok && walk.next(u); ++i) {
                 const int nkb = u.nkb;
@@ -885,7 +898,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
         pdl_wait();   // the output buffer may still be in use by a kernel ahead in the stream
         int i = 0;
         bool ok = true;
-        PairWalk walk(cluster, clusters, num_tiles, splits, kb_per_split, k_blocks, tail_tiles, tail_share);
+        PairWalk walk(cluster, clusters, num_tiles, splits, kb_per_split, k_blocks, tail_tiles, tail_p, tail_x);
         PairUnit u;
         const int whole_tiles = num_tiles - tail_tiles;
         for (; ok && walk.next(u); ++i) {
@@ -913,7 +926,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
                 continue;
             }
             // a segment of a tail tile: the partial tile goes to the workspace, and the accumulator is free again
-            float* mine = workspace + ((size_t)(cluster * 2 + u.slot) * 2 + rank) * STREAM_TILE_FLOATS;
+            const int tile_rel = tile - whole_tiles;
+            const int segments = tail_p + (tail_x < k_blocks ? 1 : 0);   // of every tail tile, in the order of their K ranges
+            float* mine = workspace + (((size_t)tile_rel * (tail_p + 1) + u.seg) * 2 + rank) * STREAM_TILE_FLOATS;
 #pragma unroll 1
             for (int c = 0; c < BN; c += 32) {
                 uint32_t r[32];
@@ -927,15 +942,11 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
             fence_before_sync();
             if (rank == 0) mbar_arrive(acc_empty + buf);
             else mbar_arrive_cluster(map_to_rank(smem_u32(acc_empty + buf), 0));
-            // which segments make up this tile: clusters c_first .. c_last hold its K blocks, in this order
-            const int tile_rel = tile - whole_tiles;
-            const long long n0 = (long long)tile_rel * k_blocks;
-            const int c_first = (int)(n0 / tail_share), c_last = (int)((n0 + k_blocks - 1) / tail_share);
             __threadfence();
             epilogue_barrier();
             if (row == 0) {
                 const int arrived = atomicAdd(&g_pair_tail_count[tile_rel * 2 + (int)rank], 1);
-                *tail_last = arrived == c_last - c_first ? 1 : 0;
+                *tail_last = arrived == segments - 1 ? 1 : 0;
             }
             epilogue_barrier();
             const bool last = *tail_last != 0;
@@ -947,18 +958,27 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
                 float4 sum[8];
 #pragma unroll
                 for (int j = 0; j < 8; ++j) sum[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-                for (int cl = c_first; cl <= c_last; ++cl) {
-                    const int sl = ((long long)cl * tail_share) / k_blocks == tile_rel ? 0 : 1;   // the cluster's share begins in this tile, or in the one before
-                    const float* theirs = workspace + ((size_t)(cl * 2 + sl) * 2 + rank) * STREAM_TILE_FLOATS;
-                    float4 v[8];
+                for (int sg = 0; sg < segments; sg += 2) {   // two segments' loads in flight: the sums are bound by the round trips to L2
+                    const float* first = workspace + (((size_t)tile_rel * (tail_p + 1) + sg) * 2 + rank) * STREAM_TILE_FLOATS;
+                    const bool two = sg + 1 < segments;
+                    const float* second = two ? first + 2 * (size_t)STREAM_TILE_FLOATS : first;
+                    float4 v[8], w[8];
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) v[j] = __ldcg(reinterpret_cast<const float4*>(theirs + partial_index(c, j, row)));
+                    for (int j = 0; j < 8; ++j) v[j] = __ldcg(reinterpret_cast<const float4*>(first + partial_index(c, j, row)));
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) w[j] = __ldcg(reinterpret_cast<const float4*>(second + partial_index(c, j, row)));
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         sum[j].x += v[j].x;
                         sum[j].y += v[j].y;
                         sum[j].z += v[j].z;
                         sum[j].w += v[j].w;
+                        if (two) {
+                            sum[j].x += w[j].x;
+                            sum[j].y += w[j].y;
+                            sum[j].z += w[j].z;
+                            sum[j].w += w[j].w;
+                        }
                     }
                 }
                 uint32_t r[32];
@@ -1082,12 +1102,40 @@ bool tail_sharing_enabled()
     return !(e != nullptr && e[0] == '0');
 }
 
-// K blocks of one cluster's time that sharing the last round must save to be worth its cost
-// (SPYINFER_GEMM_TAIL_MIN in the environment overrides it: tests use 0 to reach the path at small sizes).
+// K blocks of one cluster's time that sharing the last round must save to be used
+// (SPYINFER_GEMM_TAIL_MIN in the environment overrides it: tests use 0 to reach the path at every size).
 long long tail_sharing_threshold()
 {
     const char* e = getenv("SPYINFER_GEMM_TAIL_MIN");
-    return e != nullptr ? atoll(e) : 100;
+    return e != nullptr ? atoll(e) : 8;
+}
+
+// How the left-over tiles of the pair kernel's last round are cut (see PairWalk): p main clusters a tile share K blocks
+// [0, x) in equal slices, the other clusters take [x, k_blocks) of the tiles in turns; x is where both kinds end together,
+// a helper's turn counted with what its hand-over costs beside the K blocks themselves (the accumulator's way to the
+// workspace and the arrival: about TAIL_TURN_COST K blocks of time; with short turns the helpers ended last by far).
+// A segment has at least 8 K blocks.  saved: K blocks of one cluster's time that the last round no longer takes.
+struct TailPlan {
+    int p, x;
+    long long saved;
+};
+constexpr int TAIL_TURN_COST = 16;
+TailPlan plan_tail(int tiles, int clusters, int k_blocks)
+{
+    TailPlan t;
+    t.p = clusters / tiles;
+    while (t.p > 1 && k_blocks / t.p < 8) --t.p;
+    const int helpers = clusters - t.p * tiles;
+    const long long turns = helpers > 0 ? (tiles + helpers - 1) / helpers : 0;
+    t.x = k_blocks;
+    if (helpers > 0) {
+        // x / p = turns * (k_blocks - x + cost)
+        const long long x = (long long)t.p * turns * (k_blocks + TAIL_TURN_COST) / (1 + t.p * turns);
+        if (x < k_blocks && k_blocks - x >= 8 && x / t.p >= 8) t.x = (int)x;
+    }
+    const long long main_time = (t.x + t.p - 1) / t.p, helper_time = t.x < k_blocks ? turns * (k_blocks - t.x + TAIL_TURN_COST) : 0;
+    t.saved = k_blocks - (main_time > helper_time ? main_time : helper_time);
+    return t;
 }
 
 struct Plan {
@@ -1238,39 +1286,38 @@ extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, 
         if (splits > 1) {
             // ranges of K: 32-bit partial tiles into the scratch, [range][M][N]
             spy_launch_cluster(gemm_tcgen05_pair_kernel<float, 0>, dim3(2 * clusters), dim3(NUM_THREADS), PAIR_SMEM, stream, 2u, mx, my_half, (float*)scratch,
-                               (long long)N, M, N, k_blocks, x_tiles, (int)num_tiles, splits, kb_per_split, split_stride, 0, 0, (float*)nullptr, status);
+                               (long long)N, M, N, k_blocks, x_tiles, (int)num_tiles, splits, kb_per_split, split_stride, 0, 1, 0, (float*)nullptr, status);
             SPY_CHECK_LAUNCH("gemm_tcgen05 (pairs, K ranges)");
             if (!defer_reduce) {
                 if (int rc = reduce_splits(scratch, C, c_dtype, ldc, M, N, splits, stream)) return rc;
             }
             return 0;
         }
-        // The last round of whole tiles.  When it would leave clusters idle for long (a few tiles of a long K left over:
-        // the down projections of the larger models are 160 tiles on 74 clusters, a third round for twelve tiles),
-        // the K blocks of its tiles are shared out over all clusters instead (see PairWalk), through partial tiles in
-        // the scratch.  The sums over the partial tiles and the colder start cost about as much as 100 K blocks of
-        // one cluster, so only what saves more than that is shared (measured: at the 8B sizes, where 54 of 128 tiles
-        // are left over and a tile has 64 or 192 K blocks, whole tiles stay faster).
-        int tail_tiles = 0, tail_share = 0;
+        // The last round of whole tiles.  When it would leave clusters idle (the down projections of the larger models
+        // are 160 tiles on 74 clusters, a third round for twelve tiles; at 2,048 tokens of the 8B shape 54 of 128 tiles
+        // are left over), its tiles are cut along K and shared out over all clusters instead (see PairWalk and plan_tail),
+        // through partial tiles in the scratch.  Measured inside whole prompts: 2 to 7 % at the 14B and 32B sizes, nothing
+        // lost at the 8B sizes.  Timed alone the gain is smaller than the idle time it removes: under the power cap the
+        // idle clusters of a last round lend their share of the power to the busy rounds.
+        int tail_tiles = 0, tail_p = 1, tail_x = 0;
         const long long left = num_tiles % clusters_max;
-        if (tail_sharing_enabled() && num_tiles > clusters_max && left > 0 && left <= PAIR_TAIL_MAX_TILES && scratch != nullptr &&
-            scratch_floats >= (long long)clusters_max * 4 * STREAM_TILE_FLOATS) {
-            const long long share = (left * k_blocks + clusters_max - 1) / clusters_max;
-            const long long saved = k_blocks - share;   // K blocks of a cluster's time that the last round no longer takes
-            if (share >= 8 && share < k_blocks && saved >= tail_sharing_threshold()) {
+        if (tail_sharing_enabled() && num_tiles > clusters_max && left > 0 && left <= PAIR_TAIL_MAX_TILES && scratch != nullptr) {
+            const TailPlan tp = plan_tail((int)left, clusters_max, k_blocks);
+            if (tp.saved >= tail_sharing_threshold() && scratch_floats >= left * (tp.p + 1) * 2 * (long long)STREAM_TILE_FLOATS) {
                 tail_tiles = (int)left;
-                tail_share = (int)share;
+                tail_p = tp.p;
+                tail_x = tp.x;
             }
         }
         if (epilogue == 1)
             spy_launch_cluster(gemm_tcgen05_pair_kernel<bf16, 1>, dim3(2 * clusters), dim3(NUM_THREADS), PAIR_SMEM, stream, 2u, mx, my_half, (bf16*)C, ldc,
-                               M, N, k_blocks, x_tiles, (int)num_tiles, 1, k_blocks, 0LL, tail_tiles, tail_share, scratch, status);
+                               M, N, k_blocks, x_tiles, (int)num_tiles, 1, k_blocks, 0LL, tail_tiles, tail_p, tail_x, scratch, status);
         else if (c_dtype == SPY_F32)
             spy_launch_cluster(gemm_tcgen05_pair_kernel<float, 0>, dim3(2 * clusters), dim3(NUM_THREADS), PAIR_SMEM, stream, 2u, mx, my_half, (float*)C, ldc,
-                               M, N, k_blocks, x_tiles, (int)num_tiles, 1, k_blocks, 0LL, tail_tiles, tail_share, scratch, status);
+                               M, N, k_blocks, x_tiles, (int)num_tiles, 1, k_blocks, 0LL, tail_tiles, tail_p, tail_x, scratch, status);
         else
             spy_launch_cluster(gemm_tcgen05_pair_kernel<bf16, 0>, dim3(2 * clusters), dim3(NUM_THREADS), PAIR_SMEM, stream, 2u, mx, my_half, (bf16*)C, ldc,
-                               M, N, k_blocks, x_tiles, (int)num_tiles, 1, k_blocks, 0LL, tail_tiles, tail_share, scratch, status);
+                               M, N, k_blocks, x_tiles, (int)num_tiles, 1, k_blocks, 0LL, tail_tiles, tail_p, tail_x, scratch, status);
         SPY_CHECK_LAUNCH("gemm_tcgen05 (pairs)");
         return 0;
     }

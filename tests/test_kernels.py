@@ -510,6 +510,7 @@ def test_attention_mma_finds_one_far_key(split_keys):
     (1500, 5000, 1032, None, torch.bfloat16),        # tails in M, N and K as well: 6 x 20 tiles, 17 K blocks with 8 columns in the last
     (2048, 5120, 8192, None, torch.bfloat16),        # 160 tiles: 12 tail tiles of 128 K blocks, shared by default (the o projection of the 32B shape)
     (1200, 6400, 2048, "swiglu", torch.bfloat16),    # 5 x 25 tiles with the SwiGLU epilogue on the summed tile
+    (2048, 3328, 2048, None, torch.float32),         # 104 tiles: 30 tail tiles, two main clusters a tile and 14 helpers with three turns each
 ])
 def test_gemm_tcgen05_shares_the_last_round_of_tiles(M, N, K, epilogue, out_dtype, monkeypatch):
     """Many tokens on pairs of blocks: when the last round of 256 x 256 tiles would leave clusters idle,
