@@ -76,7 +76,7 @@ constexpr int SMEM_TOTAL = BAR_OFF + NUM_BARS * 8 + 32 + 1024;   // then slack t
 constexpr int TMEM_COLS = 64;                                    // S^T: 2 x 16 columns; O^T: 16 columns from 32
 
 struct Params {
-    bf16* out;                 // [T, nh * HD]
+    bf16* out;                 // [T, nh * hd]
     const int* block_table;    // [S, table_width]
     const int* positions;      // [T]
     const int* q_start;        // [S + 1]
@@ -84,6 +84,7 @@ struct Params {
     float* part_ml;            // [slots][G][2]  (maximum in the log2 domain, sum)
     int* status;
     int table_width, page_size, num_pages, nh, nkv, G, S, window, blocks, max_keys, mode;
+    int hd;                    // the head size as stored (a multiple of 8, at most HD): the tiles are HD wide, what lies beyond hd is zero
     float scale_log2;
 };
 
@@ -383,8 +384,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
             if (direct) {
 #pragma unroll
                 for (int n = 0; n < GN; ++n)
-                    if (n < p.G && tid < HD)
-                        p.out[((size_t)tok * p.nh + g.kvh * p.G + n) * HD + tid] = __float2bfloat16_rn(sums[n] > 0.f ? __uint_as_float(o[n]) / sums[n] : 0.f);
+                    if (n < p.G && tid < p.hd)
+                        p.out[((size_t)tok * p.nh + g.kvh * p.G + n) * p.hd + tid] = __float2bfloat16_rn(sums[n] > 0.f ? __uint_as_float(o[n]) / sums[n] : 0.f);
             } else {
 #pragma unroll
                 for (int n = 0; n < GN; ++n) {
@@ -447,7 +448,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
                                 }
                             }
                         }
-                        bf16* dst = p.out + ((size_t)tok * p.nh + g.kvh * p.G + n) * HD + col;
+                        bf16* dst = p.out + ((size_t)tok * p.nh + g.kvh * p.G + n) * p.hd + col;
                         const float inv = L > 0.f ? 1.f / L : 0.f;
 #pragma unroll
                         for (int i = 0; i < W; i += 8) {
@@ -458,7 +459,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
                                 const __nv_bfloat162 t2 = __floats2bfloat162_rn(acc[i + 2 * e] * inv, acc[i + 2 * e + 1] * inv);
                                 u[e] = *reinterpret_cast<const uint32_t*>(&t2);
                             }
-                            *reinterpret_cast<uint4*>(dst + i) = v;
+                            if (col + i < p.hd) *reinterpret_cast<uint4*>(dst + i) = v;
                         }
                     }
                 }
@@ -619,7 +620,7 @@ int launch(const CUtensorMap& page_map, const CUtensorMap& q_map, const Params& 
 extern "C" long long spy_attention_decode_scratch_floats(int seqs, int nh, int nkv, int hd)
 {
     if (nkv <= 0 || nh % nkv != 0) return 0;
-    return ((long long)seqs * nkv + sm_count()) * (nh / nkv) * (hd + 2);
+    return ((long long)seqs * nkv + sm_count()) * (nh / nkv) * ((hd <= 64 ? 64 : 128) + 2);
 }
 
 // Attention of a decoding batch over its pages: every sequence brings one token (row
@@ -634,7 +635,8 @@ extern "C" int spy_attention_decode(const void* q, long long q_row_stride, void*
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0) SPY_FAIL("attention_decode: %d query heads do not group over %d key/value heads", nh, nkv);
     const int G = nh / nkv;
     if (G > NCOLS) SPY_FAIL("attention_decode: %d query heads per key/value head exceed %d", G, NCOLS);
-    if (hd != 64 && hd != 128) SPY_FAIL("attention_decode: head_dim %d is not 64 or 128", hd);
+    if (hd < 8 || hd > 128 || hd % 8 != 0) SPY_FAIL("attention_decode: head_dim %d is not a multiple of 8 between 8 and 128", hd);
+    const int hd_tile = hd <= 64 ? 64 : 128;   // the kernel's tile width: the TMA boxes fill what lies beyond hd with zeros
     if (seqs > MAX_SEQS || (long long)seqs * nkv > MAX_PAIRS)
         SPY_FAIL("attention_decode: %d sequences of %d key/value heads exceed %d sequences or %d pairs", seqs, nkv, MAX_SEQS, MAX_PAIRS);
     if (q_row_stride % 8 != 0 || q_row_stride < (long long)nh * hd || (reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(pages) & 15))
@@ -656,9 +658,9 @@ extern "C" int spy_attention_decode(const void* q, long long q_row_stride, void*
 
     Params p;
     p.out = (bf16*)out; p.block_table = block_table; p.positions = positions; p.q_start = q_start; p.status = status;
-    p.part_o = scratch; p.part_ml = scratch + ((size_t)seqs * nkv + sms) * G * hd;
+    p.part_o = scratch; p.part_ml = scratch + ((size_t)seqs * nkv + sms) * G * hd_tile;
     p.table_width = table_width; p.page_size = page_size; p.num_pages = num_pages; p.nh = nh; p.nkv = nkv; p.G = G; p.S = seqs;
-    p.window = window; p.blocks = sms; p.max_keys = (int)max_keys; p.mode = mode; p.scale_log2 = scale * LOG2E;
+    p.window = window; p.hd = hd; p.blocks = sms; p.max_keys = (int)max_keys; p.mode = mode; p.scale_log2 = scale * LOG2E;
 
     // the pages of this cache as one matrix [num_pages * 2 * nkv * page_size rows, hd]; a box is one page's rows x 64 columns
     CUtensorMap page_map, q_map;
@@ -683,6 +685,6 @@ extern "C" int spy_attention_decode(const void* q, long long q_row_stride, void*
         if (r != CUDA_SUCCESS) SPY_FAIL("attention_decode: cuTensorMapEncodeTiled (queries) failed with code %d", (int)r);
     }
     const int gn = G <= 4 ? 4 : (G <= 8 ? 8 : 16);
-    if (hd == 64) return gn == 4 ? launch<64, 4>(page_map, q_map, p, stream) : (gn == 8 ? launch<64, 8>(page_map, q_map, p, stream) : launch<64, 16>(page_map, q_map, p, stream));
+    if (hd_tile == 64) return gn == 4 ? launch<64, 4>(page_map, q_map, p, stream) : (gn == 8 ? launch<64, 8>(page_map, q_map, p, stream) : launch<64, 16>(page_map, q_map, p, stream));
     return gn == 4 ? launch<128, 4>(page_map, q_map, p, stream) : (gn == 8 ? launch<128, 8>(page_map, q_map, p, stream) : launch<128, 16>(page_map, q_map, p, stream));
 }

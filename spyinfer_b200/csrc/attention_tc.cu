@@ -67,12 +67,13 @@ constexpr float RESCALE_THRESHOLD = 8.0f;
 struct Params {
     const bf16* q;
     long long q_stride;
-    bf16* out;                 // [T, nh * HD]
+    bf16* out;                 // [T, nh * hd]
     const int* block_table;    // [S, table_width]
     const int* positions;      // [T]
     const int* q_start;        // [S + 1]
     int* status;
     int table_width, page_size, num_pages, nh, nkv, G, Gp, S, window;
+    int hd;                    // the head size as stored (a multiple of 8, at most HD): the tiles are HD wide, what lies beyond hd is zero
     int x_blocks, items;       // 256-row blocks along the tokens (an upper bound), and x_blocks * nkv work items
     float scale_log2;
 };
@@ -235,8 +236,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
             for (int idx = row; idx < ROWS * CPR; idx += GROUP_THREADS) {
                 const int r = idx / CPR, c = idx % CPR;
                 const int r_tok = it.tok0 + grp * tokens_per_tile + r / p.Gp, r_hg = r % p.Gp;
-                const bool ok = r_tok < it.tok_end && r_hg < p.G;
-                const bf16* src = p.q + (size_t)(ok ? r_tok : 0) * p.q_stride + (size_t)(it.kvh * p.G + (ok ? r_hg : 0)) * HD + c * 8;
+                const bool ok = r_tok < it.tok_end && r_hg < p.G && c * 8 < p.hd;   // rows and columns beyond the data are filled with zeros
+                const bf16* src = p.q + (size_t)(ok ? r_tok : 0) * p.q_stride + (size_t)(it.kvh * p.G + (ok ? r_hg : 0)) * p.hd + (ok ? c * 8 : 0);
                 cp_async16(smem + L::Q_OFF + grp * L::OPERAND_BYTES + tile_offset(r, c), src, ok);
             }
         };
@@ -368,7 +369,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
             // ---- ... and this item's output is read and stored meanwhile: O_g / l
             if (my_tiles > 0) {
                 const float inv = l > 0.f ? 1.f / l : 0.f;
-                bf16* dst = p.out + ((size_t)(row_ok ? tok : 0) * p.nh + head) * HD;
+                bf16* dst = p.out + ((size_t)(row_ok ? tok : 0) * p.nh + head) * p.hd;
 #pragma unroll 1
                 for (int c = 0; c < HD; c += 32) {
                     uint32_t r[32];
@@ -382,7 +383,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
                         v.y = pack_bf16(__uint_as_float(r[8 * q4 + 2]) * inv, __uint_as_float(r[8 * q4 + 3]) * inv);
                         v.z = pack_bf16(__uint_as_float(r[8 * q4 + 4]) * inv, __uint_as_float(r[8 * q4 + 5]) * inv);
                         v.w = pack_bf16(__uint_as_float(r[8 * q4 + 6]) * inv, __uint_as_float(r[8 * q4 + 7]) * inv);
-                        *reinterpret_cast<uint4*>(dst + c + 8 * q4) = v;
+                        if (c + 8 * q4 < p.hd) *reinterpret_cast<uint4*>(dst + c + 8 * q4) = v;
                     }
                 }
             }
@@ -541,7 +542,7 @@ extern "C" int spy_attention_tc(const void* q, long long q_row_stride, void* out
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0) SPY_FAIL("attention_tc: %d query heads do not group over %d key/value heads", nh, nkv);
     const int G = nh / nkv;
     if (G > 16) SPY_FAIL("attention_tc: %d query heads per key/value head exceed 16", G);
-    if (hd != 64 && hd != 128) SPY_FAIL("attention_tc: head_dim %d is not 64 or 128", hd);
+    if (hd < 8 || hd > 128 || hd % 8 != 0) SPY_FAIL("attention_tc: head_dim %d is not a multiple of 8 between 8 and 128", hd);
     if (q_row_stride % 8 != 0 || (reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(pages) & 15) ||
         (reinterpret_cast<uintptr_t>(out) & 15))
         SPY_FAIL("attention_tc: queries, pages and output must be 16-byte aligned with rows a multiple of 8 elements");
@@ -552,10 +553,11 @@ extern "C" int spy_attention_tc(const void* q, long long q_row_stride, void* out
     Params p;
     p.q = (const bf16*)q; p.q_stride = q_row_stride; p.out = (bf16*)out; p.block_table = block_table;
     p.positions = positions; p.q_start = q_start; p.status = status; p.table_width = table_width; p.page_size = page_size;
-    p.num_pages = num_pages; p.nh = nh; p.nkv = nkv; p.G = G; p.Gp = Gp; p.S = seqs; p.window = window; p.scale_log2 = scale * LOG2E;
+    p.num_pages = num_pages; p.nh = nh; p.nkv = nkv; p.G = G; p.Gp = Gp; p.S = seqs; p.window = window; p.hd = hd; p.scale_log2 = scale * LOG2E;
     if (page_size < 8 || page_size > TILE || TILE % page_size != 0)
         SPY_FAIL("attention_tc: page_size %d must be 8, 16, 32, 64 or 128 (one TMA box per page)", page_size);
     // the pages of this cache as one matrix [num_pages * 2 * nkv * page_size rows, hd]; a box is one page's rows x 64 columns
+    // (columns beyond hd are outside the matrix and arrive as zeros: a head size below the tile's 64 or 128 is padded on the way in)
     tc::EncodeTiledFn encode = tc::encode_tiled_fn();
     if (encode == nullptr) SPY_FAIL("attention_tc: cuTensorMapEncodeTiled is not available from the driver");
     CUtensorMap page_map;
@@ -583,7 +585,7 @@ extern "C" int spy_attention_tc(const void* q, long long q_row_stride, void* out
     // last tiles of the one before are worked on)
     const int sms = spy_sm_count();
     dim3 grid((unsigned)(items < sms ? items : sms));
-    if (hd == 64) spy_launch(attention_tc_kernel<64>, grid, dim3(NUM_THREADS), (size_t)Smem<64>::TOTAL, stream, page_map, p);
+    if (hd <= 64) spy_launch(attention_tc_kernel<64>, grid, dim3(NUM_THREADS), (size_t)Smem<64>::TOTAL, stream, page_map, p);
     else spy_launch(attention_tc_kernel<128>, grid, dim3(NUM_THREADS), (size_t)Smem<128>::TOTAL, stream, page_map, p);
     SPY_CHECK_LAUNCH("attention_tc");
     return 0;

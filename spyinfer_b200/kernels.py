@@ -324,11 +324,22 @@ ATTENTION_DECODE_MAX_SEQS = 1024
 ATTENTION_DECODE_MAX_PAIRS = 65536   # sequences x key/value heads
 
 
+ATTENTION_TMA_PAGE_SIZES = (8, 16, 32, 64, 128)   # a page of the cache is one TMA box
+
+
+def attention_tc_takes(num_heads: int, num_kv_heads: int, head_dim: int, dtype: torch.dtype) -> bool:
+    """Whether the tcgen05 attention kernels (prompt portions and decoding) take these sizes: bfloat16, a
+    head size that is a multiple of 8 up to 128 (their tiles are 64 or 128 wide; the TMA boxes fill what
+    lies beyond the head size with zeros), at most 16 query heads per key/value head.  The page size must
+    be one of ``ATTENTION_TMA_PAGE_SIZES`` besides."""
+    return (dtype == torch.bfloat16 and 8 <= head_dim <= 128 and head_dim % 8 == 0 and num_kv_heads > 0 and num_heads % num_kv_heads == 0
+            and num_heads // num_kv_heads <= 16)
+
+
 def attention_decode_takes(num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, dtype: torch.dtype) -> bool:
-    """Whether the persistent tcgen05 decode-attention kernel takes these sizes: bfloat16, head size
-    64 or 128, at most 16 query heads per key/value head, pages of 8 .. 128 tokens (a power of two)."""
-    return (dtype == torch.bfloat16 and head_dim in (64, 128) and num_kv_heads > 0 and num_heads % num_kv_heads == 0
-            and num_heads // num_kv_heads <= 16 and page_size in (8, 16, 32, 64, 128))
+    """Whether the persistent tcgen05 decode-attention kernel takes these sizes: those of
+    ``attention_tc_takes`` and pages of 8 .. 128 tokens (a power of two)."""
+    return attention_tc_takes(num_heads, num_kv_heads, head_dim, dtype) and page_size in ATTENTION_TMA_PAGE_SIZES
 
 
 def attention_decode(q: torch.Tensor, num_heads: int, head_dim: int, out: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor,

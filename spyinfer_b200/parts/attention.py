@@ -49,7 +49,9 @@ class Attention(Mixer):
         pos = params.get("position")
         self.position = build_part(pos, ctx) if pos is not None else None
         self.qkv = self.o = self.q_norm = self.k_norm = self.rope_table = None
-        self.fast = kernels.attention_mma_takes(self.nh, self.nkv, self.hd, ctx.dtype)
+        # which attention kernels take these sizes (the page size, known at the first step, decides between them)
+        self.tc = kernels.attention_tc_takes(self.nh, self.nkv, self.hd, ctx.dtype)        # tcgen05, pages that are one TMA box
+        self.mma = kernels.attention_mma_takes(self.nh, self.nkv, self.hd, ctx.dtype)      # mma.sync, any page size
         self._split_plans = {}
 
     def weight_decls(self):
@@ -81,7 +83,7 @@ class Attention(Mixer):
                 self.q_norm, self.k_norm = self.q_norm.float(), self.k_norm.float()
 
     def modules(self):
-        mods = ["qk_rope_store"] + (["attention_mma", "attention_tc", "attention_decode"] if self.fast else ["attention_generic"]) + self.qkv.modules() + self.o.modules()
+        mods = ["qk_rope_store"] + (["attention_tc", "attention_decode"] if self.tc else []) + (["attention_mma"] if self.mma else ["attention_generic"]) + self.qkv.modules() + self.o.modules()
         if self.position is not None:
             mods += self.position.modules()
         return mods
@@ -128,25 +130,27 @@ class Attention(Mixer):
                                   pairing=self.position.pairing if self.position is not None else "half")
         out = torch.empty((x.shape[0], self.nh * self.hd), dtype=x.dtype, device=x.device)
         decoding = batch.num_tokens == batch.num_seqs         # every request brings one token
-        if not self.fast:
-            kernels.attention_generic(q, self.nh, self.hd, out, cache.pages, cache.block_table, batch.positions, batch.seq_of_token,
-                                      self.scale, window=self.window, status=batch.status)
-        elif decoding and batch.num_seqs <= kernels.ATTENTION_DECODE_MAX_SEQS and batch.num_seqs * self.nkv <= kernels.ATTENTION_DECODE_MAX_PAIRS and kernels.attention_decode_takes(
-                self.nh, self.nkv, self.hd, cache.page_size, x.dtype):
+        boxes = self.tc and cache.page_size in kernels.ATTENTION_TMA_PAGE_SIZES        # a page is one TMA box
+        if (boxes and decoding and batch.num_seqs <= kernels.ATTENTION_DECODE_MAX_SEQS and batch.num_seqs * self.nkv <= kernels.ATTENTION_DECODE_MAX_PAIRS
+                and kernels.attention_decode_takes(self.nh, self.nkv, self.hd, cache.page_size, x.dtype)):
             # memory-bound: one persistent block per SM, the batch's key tiles shared out evenly, pages by TMA
             kernels.attention_decode(q, self.nh, self.hd, out, cache.pages, cache.block_table, batch.positions, batch.q_start,
                                      batch.num_seqs, self.scale, window=self.window, status=batch.status)
-        elif decoding:
+        elif decoding and self.mma:
             # page sizes that are no TMA box, or very many requests: keys split across blocks by a plan per batch size
             split_keys, max_splits = self.split_plan(batch.num_seqs)
             kernels.attention_mma(q, self.nh, self.hd, out, cache.pages, cache.block_table, batch.positions, batch.q_start,
                                   batch.num_seqs, self.scale, window=self.window, split_keys=split_keys, max_splits=max_splits,
                                   status=batch.status)
-        elif cache.page_size in (8, 16, 32, 64, 128):
-            # prompt portions (and whatever decodes beside them): 128-row blocks on tcgen05, a page is one TMA box
+        elif boxes:
+            # prompt portions (and whatever decodes beside them): blocks of 256 query rows on tcgen05
             kernels.attention_tc(q, self.nh, self.hd, out, cache.pages, cache.block_table, batch.positions, batch.q_start,
                                  batch.num_seqs, self.scale, window=self.window, status=batch.status)
-        else:
+        elif self.mma:
             kernels.attention_mma(q, self.nh, self.hd, out, cache.pages, cache.block_table, batch.positions, batch.q_start,
                                   batch.num_seqs, self.scale, window=self.window, status=batch.status)
+        else:
+            # the float32 path, head sizes above 128 or no multiple of 8, more than 16 query heads a key/value head
+            kernels.attention_generic(q, self.nh, self.hd, out, cache.pages, cache.block_table, batch.positions, batch.seq_of_token,
+                                      self.scale, window=self.window, status=batch.status)
         return self.o(out, defer=self.defer_output)

@@ -687,10 +687,12 @@ def test_qk_rope_store_many_tokens_at_once_equal_few_at_a_time(stacked, nh, nkv)
 
 
 @pytest.mark.parametrize("nh,nkv,hd,page_size,window", [(8, 2, 128, 16, None), (10, 2, 64, 16, 150), (4, 4, 128, 8, None), (16, 1, 64, 32, None),
-                                                        (6, 2, 128, 64, 33), (32, 8, 128, 16, None), (2, 1, 64, 128, None)])
+                                                        (6, 2, 128, 64, 33), (32, 8, 128, 16, None), (2, 1, 64, 128, None),
+                                                        (6, 2, 96, 16, None), (4, 1, 80, 8, 100), (8, 4, 24, 16, None), (3, 3, 112, 32, 260), (2, 2, 8, 16, None)])
 def test_attention_tc_mixed_batch(nh, nkv, hd, page_size, window):
     """tcgen05 attention: portions, single tokens, a one-token sequence and a 300-token portion
-    (several 128-row blocks and several key tiles) in one batch; group sizes 1, 3, 4, 5, 16."""
+    (several 128-row blocks and several key tiles) in one batch; group sizes 1, 3, 4, 5, 16; head sizes
+    that fill a tile of 64 or 128 columns and head sizes that are padded to one (8 ... 112)."""
     from spyinfer_b200 import kernels
     torch.manual_seed(nh * hd + 1)
     lens = [1, 70, 333, 129, 40, 700]
@@ -775,11 +777,13 @@ def test_attention_tc_finds_one_far_key_and_survives_large_scores():
 
 @pytest.mark.parametrize("share", ["auto", "split", "whole"])
 @pytest.mark.parametrize("nh,nkv,hd,page_size,window", [(32, 8, 128, 16, None), (10, 2, 64, 16, 300), (8, 8, 128, 8, None), (12, 4, 64, 32, None),
-                                                        (16, 1, 128, 16, 700), (6, 1, 128, 128, None), (8, 2, 128, 64, 130)])
+                                                        (16, 1, 128, 16, 700), (6, 1, 128, 128, None), (8, 2, 128, 64, 130),
+                                                        (12, 4, 96, 16, None), (5, 5, 80, 8, 200), (4, 2, 40, 16, None), (2, 1, 8, 32, None)])
 def test_attention_decode_contexts_from_one_key_to_thousands(nh, nkv, hd, page_size, window, share):
     """Persistent tcgen05 decode attention: one token per sequence, contexts at tile edges (127, 128,
     129 keys) and long ones, so that pairs are written whole by one block, cut over two blocks and over
-    many; group sizes 1, 3, 4, 5, 6 and 16; with and without a window."""
+    many; group sizes 1, 3, 4, 5, 6 and 16; with and without a window; head sizes that fill a tile of 64 or
+    128 columns and head sizes that are padded to one."""
     from spyinfer_b200 import kernels
     torch.manual_seed(nh + hd + 5)
     lens = [1, 17, 127, 128, 129, 700, 1500, 3000]
