@@ -1144,12 +1144,33 @@ struct Plan {
 
 static inline int pair_min_tiles() { return (spy_sm_count() / 2 + 1) / 2; }   // whole 256 x 256 tiles occupy at least half of the clusters (SMs / 2) from here on
 
+// Whether a product of more than 256 tokens runs on pairs of blocks (256 x 256 tiles) or on single blocks (128 x 256).
+// From 512 tokens on: pairs.  Below (a third or fourth 128-token tile that pairs would round up to 512): pairs too
+// when the single blocks would have fewer tiles than SMs (their shared K blocks cost more than the pairs' K ranges;
+// measured at 320 to 448 tokens and the 8B sizes: q‖k‖v 33-40 -> 28-29 us, o 33-36 -> 20, down 54-78 -> 42-44), and
+// otherwise when the pairs' rounds of tiles, the last one counted by what sharing it out leaves of it, are no more
+// than the single blocks' (gate‖up at 320 and 384 tokens: 288 tiles are two rounds of single blocks = 67-69 us,
+// 192 tiles 2.6 rounds of pairs = 79-81 us; at 448 tokens three rounds either way, 88 against 83 us).
+bool pairs_take(int M, int N)
+{
+    if (!pair_kernel_enabled() || M <= 256) return false;
+    if (M >= 512) return true;
+    const int sms = spy_sm_count();
+    const long long y_tiles = (N + 255) / 256;
+    const long long tiles1 = (long long)((M + BM - 1) / BM) * y_tiles, tiles2 = (long long)((M + 2 * BM - 1) / (2 * BM)) * y_tiles;
+    if (tiles1 < sms) return true;
+    const long long clusters = sms / 2;
+    const long long r1 = (tiles1 + sms - 1) / sms;
+    const long long r2 = (tiles2 * 10 - 3 * clusters + 10 * clusters - 1) / (10 * clusters);   // ceil(tiles2 / clusters - 0.3)
+    return r2 <= r1;
+}
+
 Plan make_plan(int M, int N, int K, bool may_split)
 {
     const int k_blocks = (K + BK - 1) / BK;
     Plan best = {1, BM};
-    if (M >= 512 && may_split && pair_kernel_enabled()) {
-        // 512 tokens or so on pairs of blocks: with too few 256 x 256 tiles for the clusters (o and down at the 8B
+    if (pairs_take(M, N) && may_split) {
+        // a few hundred tokens on pairs of blocks: with too few 256 x 256 tiles for the clusters (o and down at the 8B
         // shape: 32), K is cut into two to four ranges, so that tiles x ranges occupy most of the clusters (SMs / 2); the
         // partial tiles are summed by the caller or by the reduce kernel.  At least 16 K blocks a range.
         const long long tiles = (long long)((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
@@ -1250,7 +1271,7 @@ extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, 
     const bool f32_out = splits > 1 || c_dtype == SPY_F32;
     // pairs need enough 256 x 256 tiles to occupy at least half of the clusters; smaller products go to single
     // blocks, which share the K blocks of their 128 x 256 tiles out over all SMs
-    if (!swap && M >= 512 && (splits > 1 || (long long)((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256) >= pair_min_tiles()) && pair_kernel_enabled()) {
+    if (!swap && pairs_take(M, N) && (splits > 1 || (long long)((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256) >= pair_min_tiles())) {
         // many tokens, one pass over K, at least two 256-row tiles: pairs of blocks on 256 x 256 tiles
         CUtensorMap my_half;
         if (make_map(&my_half, W, N, K, ldw, BM)) return 1;

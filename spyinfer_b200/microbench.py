@@ -1,10 +1,11 @@
 """Timings of single kernels at chosen sizes.
 
-    python -m spyinfer_b200.microbench gemm --m 2048 --n 24576 --k 4096 [--out-dtype float32] [--iters 20]
+    python -m spyinfer_b200.microbench gemm --m 2048 --n 24576 --k 4096 [--out-dtype float32] [--iters 20] [--graph] [--defer] [--epilogue swiglu]
     python -m spyinfer_b200.microbench attention --batch 8 --context 8192 [--q-len 1] [--split-keys 576] [--kernel tc|mma|decode] [--iters 10]
 
 Defaults are Qwen3-8B's sizes (32 query heads, 8 key/value heads, head size 128, pages of 16).
-Timing is by CUDA events around ``iters`` launches after a warm-up; the product cycles through
+Timing is by CUDA events around ``iters`` launches after a warm-up (``--graph``: replayed from a CUDA graph, which
+kernels of a few microseconds need: eager launches cost the host more than that); the product cycles through
 enough weight copies to exceed L2, the attention's cache does so by itself at the default sizes.
 """
 from __future__ import annotations
@@ -20,22 +21,44 @@ from . import kernels
 DEV = "cuda:0"
 
 
-def bench_gemm(M: int, N: int, K: int, out_dtype=torch.bfloat16, iters: int = 20) -> dict:
+def bench_gemm(M: int, N: int, K: int, out_dtype=torch.bfloat16, iters: int = 20, graph: bool = False, defer: bool = False,
+               epilogue=None) -> dict:
+    """``defer``: the product may leave split-K parts for its consumer, as the model's parts allow it to
+    (the time is then without the sum over the parts).  ``epilogue="swiglu"``: rows of gate and up alternate."""
     a = torch.randn(M, K, device=DEV).to(torch.bfloat16)
     copies = max(1, int(300e6 // (N * K * 2)) + 1)
     ws = [(torch.randn(N, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16) for _ in range(copies)]
-    out = torch.empty(M, N, device=DEV, dtype=out_dtype)
-    for w in ws[:2]:
-        kernels.gemm_tcgen05(a, w, out)
+    n_out = N // 2 if epilogue else N
+    out = None if defer else torch.empty(M, n_out, device=DEV, dtype=out_dtype)
+
+    def run(i):
+        if defer:
+            kernels.gemm_tcgen05(a, ws[i % copies], out_dtype=out_dtype, defer=True)
+        else:
+            kernels.gemm_tcgen05(a, ws[i % copies], out, epilogue=epilogue)
+
+    for i in range(2):
+        run(i)
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(iters):
-        kernels.gemm_tcgen05(a, ws[i % copies], out)
-    e1.record()
+    if graph:   # the launches replayed from a CUDA graph: device time without the host's launch cost
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(iters):
+                run(i)
+        g.replay()
+        torch.cuda.synchronize()
+        e0.record()
+        g.replay()
+        e1.record()
+    else:
+        e0.record()
+        for i in range(iters):
+            run(i)
+        e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / iters
-    return {"us": ms * 1e3, "tflops": 2.0 * M * N * K / ms / 1e9, "gbs": (N * K * 2 + M * K * 2 + M * N * out.element_size()) / ms / 1e6}
+    return {"us": ms * 1e3, "tflops": 2.0 * M * N * K / ms / 1e9, "gbs": (N * K * 2 + M * K * 2 + M * n_out * (4 if out_dtype == torch.float32 else 2)) / ms / 1e6}
 
 
 def bench_attention(batch: int, context: int, q_len: int = 1, split_keys: int = 0, nh: int = 32, nkv: int = 8, hd: int = 128,
@@ -94,6 +117,9 @@ def main(argv=None) -> int:
     g.add_argument("--k", type=int, required=True)
     g.add_argument("--out-dtype", default="bfloat16", choices=["bfloat16", "float32"])
     g.add_argument("--iters", type=int, default=20)
+    g.add_argument("--graph", action="store_true", help="replay the launches from a CUDA graph (device time without host launch cost)")
+    g.add_argument("--defer", action="store_true", help="split-K parts may stay unsummed, as inside the model")
+    g.add_argument("--epilogue", default=None, choices=["swiglu"])
     a = sub.add_parser("attention")
     a.add_argument("--batch", type=int, required=True)
     a.add_argument("--context", type=int, required=True)
@@ -108,7 +134,7 @@ def main(argv=None) -> int:
     args = ap.parse_args(argv)
     kernels.require_cuda()
     if args.what == "gemm":
-        r = bench_gemm(args.m, args.n, args.k, getattr(torch, args.out_dtype), args.iters)
+        r = bench_gemm(args.m, args.n, args.k, getattr(torch, args.out_dtype), args.iters, graph=args.graph, defer=args.defer, epilogue=args.epilogue)
         print(f"gemm M={args.m} N={args.n} K={args.k}: {r['us']:.1f} us, {r['tflops']:.1f} TFLOP/s, {r['gbs']:.1f} GB/s")
     else:
         r = bench_attention(args.batch, args.context, args.q_len, args.split_keys, page_size=args.page_size, iters=args.iters, kernel=args.kernel, share=args.share, graph=args.graph)
