@@ -415,6 +415,10 @@ def main() -> int:
     total_steps = warmup + args.steps + 8
     pages_per_req = (ctx + page - 1) // page + 1
     num_pages = max_batch * pages_per_req + (args.prefill_tokens + page - 1) // page + 8
+    # one more point when the batch-64 points fit: 256 requests of 1,024 keys (the pool of 64 x the context holds them)
+    large = (256, 1024) if (not args.no_points and 64 in points_batches and 256 * (1024 // page + 2) <= num_pages) else None
+    if large:
+        max_batch = max(max_batch, large[0])
     engine = LLMEngine(model_config=model_config, seed=0, dtype="bfloat16", max_num_seqs=max_batch, max_model_len=max(ctx, args.prefill_tokens) + 16,
                        kvcache_block_size=page, num_kvcache_blocks=num_pages, max_num_batched_tokens=max(args.prefill_tokens, max_batch))
     runner, cache = engine.runner, engine.runner.cache
@@ -551,6 +555,8 @@ def main() -> int:
             point(f"decode_b{b}", b, ctx)
         for b in (1, 8) + points_batches[1:]:
             point(f"decode_b{b}_ctx640", b, 640 + (args.steps + warmup) // 2)
+        if large:
+            point(f"decode_b{large[0]}_ctx{large[1]}", large[0], large[1] + (args.steps + warmup) // 2)
         out["points"] = points
         out["points_detail"] = detail
     if not args.no_kernels:

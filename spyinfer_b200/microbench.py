@@ -2,6 +2,7 @@
 
     python -m spyinfer_b200.microbench gemm --m 2048 --n 24576 --k 4096 [--out-dtype float32] [--iters 20] [--graph] [--defer] [--epilogue swiglu]
     python -m spyinfer_b200.microbench attention --batch 8 --context 8192 [--q-len 1] [--split-keys 576] [--kernel tc|mma|decode] [--iters 10]
+                                                 [--heads 64 --kv-heads 8 --head-dim 128] [--graph]
 
 Defaults are Qwen3-8B's sizes (32 query heads, 8 key/value heads, head size 128, pages of 16).
 Timing is by CUDA events around ``iters`` launches after a warm-up (``--graph``: replayed from a CUDA graph, which
@@ -127,6 +128,9 @@ def main(argv=None) -> int:
     a.add_argument("--split-keys", type=int, default=0, help="mma kernel only: 0: tiles mode; else split mode with this range length")
     a.add_argument("--iters", type=int, default=10)
     a.add_argument("--page-size", type=int, default=16)
+    a.add_argument("--heads", type=int, default=32, help="query heads")
+    a.add_argument("--kv-heads", type=int, default=8)
+    a.add_argument("--head-dim", type=int, default=128)
     a.add_argument("--graph", action="store_true", help="replay the launches from a CUDA graph (device time without host launch cost)")
     a.add_argument("--share", default="auto", choices=["auto", "split", "whole"], help="decode kernel: how the work is dealt out over the blocks")
     a.add_argument("--kernel", default="auto", choices=["auto", "tc", "mma", "decode"],
@@ -137,7 +141,8 @@ def main(argv=None) -> int:
         r = bench_gemm(args.m, args.n, args.k, getattr(torch, args.out_dtype), args.iters, graph=args.graph, defer=args.defer, epilogue=args.epilogue)
         print(f"gemm M={args.m} N={args.n} K={args.k}: {r['us']:.1f} us, {r['tflops']:.1f} TFLOP/s, {r['gbs']:.1f} GB/s")
     else:
-        r = bench_attention(args.batch, args.context, args.q_len, args.split_keys, page_size=args.page_size, iters=args.iters, kernel=args.kernel, share=args.share, graph=args.graph)
+        r = bench_attention(args.batch, args.context, args.q_len, args.split_keys, nh=args.heads, nkv=args.kv_heads, hd=args.head_dim, page_size=args.page_size,
+                            iters=args.iters, kernel=args.kernel, share=args.share, graph=args.graph)
         print(f"attention batch={args.batch} context={args.context} q_len={args.q_len} split_keys={args.split_keys}: {r['us']:.1f} us, "
               f"cache read at {r['kv_gbs']:.1f} GB/s, {r['tflops']:.1f} TFLOP/s")
     return 0
