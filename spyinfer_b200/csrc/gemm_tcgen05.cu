@@ -1074,14 +1074,14 @@ static int launch(const CUtensorMap& mx, const CUtensorMap& my, void* out, long 
 
 namespace {
 
-// The plan of a product: how many ways K is split and how many weight rows a block takes.
-// Many tokens (M > 256): 128 x 256 or 256 x 256 tiles, K never split by plan (the persistent kernel
-// shares K blocks out itself when there are fewer tiles than SMs).
-// Few tokens (up to 256: decoding; the weights sit in the instruction's M slot, two blocks share an
-// SM; 65 to 256 tokens are two to four token tiles of 64 whose blocks start side by side and share
+// The plan of a product: the kernel it runs on (choose_kind), how many ways K is split and how many weight rows a block takes.
+// Pairs and single blocks (many tokens): 256 x 256 or 128 x 256 tiles; K is cut into ranges by plan only for pairs with
+// few tiles (the single-block kernel shares K blocks out itself when there are fewer tiles than SMs).
+// The swapped kernel (few tokens: decoding; the weights sit in the instruction's M slot, two blocks share an
+// SM; 65 tokens and more are two to four token tiles of 64 whose blocks start side by side and share
 // every weight tile through L2, so the plan fills the slots divided by the token tiles; measured on
-// whole decode steps of the 8B shape at 2,048 keys: batch 128 12.46 -> 10.58 ms, batch 256 18.79 ->
-// 18.50 ms against 128 x 256 tiles with shared K blocks):
+// whole decode steps of the 8B shape at 2,048 keys: batch 128 12.46 -> 10.58 ms against 128 x 256 tiles
+// with shared K blocks):
 // the product is bound by reading the weights, so what counts is that all 2 x SMs block
 // slots stream at once and end together.  When 128-row tiles times the splits would not fill
 // the slots, the tile takes fewer rows (a multiple of 4, at least 64: the TMA box shrinks, the
@@ -1138,38 +1138,47 @@ TailPlan plan_tail(int tiles, int clusters, int k_blocks)
     return t;
 }
 
+enum Kind { SWAPPED, SINGLE, PAIRS };   // the kernel a product runs on
 struct Plan {
     int splits, tile_rows;
+    Kind kind;
 };
 
 static inline int pair_min_tiles() { return (spy_sm_count() / 2 + 1) / 2; }   // whole 256 x 256 tiles occupy at least half of the clusters (SMs / 2) from here on
 
-// Whether a product of more than 256 tokens runs on pairs of blocks (256 x 256 tiles) or on single blocks (128 x 256).
-// From 512 tokens on: pairs.  Below (a third or fourth 128-token tile that pairs would round up to 512): pairs too
-// when the single blocks would have fewer tiles than SMs (their shared K blocks cost more than the pairs' K ranges;
-// measured at 320 to 448 tokens and the 8B sizes: q‖k‖v 33-40 -> 28-29 us, o 33-36 -> 20, down 54-78 -> 42-44), and
-// otherwise when the pairs' rounds of tiles, the last one counted by what sharing it out leaves of it, are no more
-// than the single blocks' (gate‖up at 320 and 384 tokens: 288 tiles are two rounds of single blocks = 67-69 us,
-// 192 tiles 2.6 rounds of pairs = 79-81 us; at 448 tokens three rounds either way, 88 against 83 us).
-bool pairs_take(int M, int N)
+// Which kernel a product runs on.  Up to 128 tokens: the swapped kernel (weights in the instruction's M slot, one or
+// two token tiles of 64).  Beyond: pairs of blocks on 256 x 256 tiles where they find enough work (whole tiles for
+// at least half of the clusters, or, where K may be cut into ranges, at least 8 tiles), else the swapped kernel up
+// to 256 tokens and single blocks on 128 x 256 tiles above.  129 to 256 tokens (one row of 256-token tiles; a third and
+// fourth token tile of the swapped kernel would read every weight tile from L2 again: measured at 256 tokens, 8B
+// sizes q‖k‖v 26 -> 21 us, gate‖up 75 -> 51, down 37 -> 29; 14B sizes gate‖up 127 -> 79, down 88 -> 48; at 128 tokens
+// the swapped kernel is still ahead).  257 to 511 tokens (a third or fourth 128-token tile that pairs round up to 512):
+// pairs when the single blocks would have fewer tiles than SMs (their shared K blocks cost more than the pairs' K
+// ranges: at 320 to 448 tokens q‖k‖v 33-40 -> 28-29 us, o 33-36 -> 20, down 54-78 -> 42-44), and otherwise when the
+// pairs' rounds of tiles, the last one counted by what sharing it out leaves of it, are no more than the single
+// blocks' (gate‖up at 320 and 384 tokens: 288 tiles are two rounds of single blocks = 67-69 us, 192 tiles 2.6 rounds
+// of pairs = 79-81 us; at 448 tokens three rounds either way, 88 against 83 us).  From 512 tokens on: pairs.
+Kind choose_kind(int M, int N, bool may_split)
 {
-    if (!pair_kernel_enabled() || M <= 256) return false;
-    if (M >= 512) return true;
+    if (M <= 2 * 64) return SWAPPED;
+    const Kind other = M <= 256 ? SWAPPED : SINGLE;
+    if (!pair_kernel_enabled()) return other;
     const int sms = spy_sm_count();
     const long long y_tiles = (N + 255) / 256;
     const long long tiles1 = (long long)((M + BM - 1) / BM) * y_tiles, tiles2 = (long long)((M + 2 * BM - 1) / (2 * BM)) * y_tiles;
-    if (tiles1 < sms) return true;
+    if (!(tiles2 >= pair_min_tiles() || (may_split && tiles2 >= 8))) return other;
+    if (M <= 256 || M >= 512 || tiles1 < sms) return PAIRS;
     const long long clusters = sms / 2;
     const long long r1 = (tiles1 + sms - 1) / sms;
     const long long r2 = (tiles2 * 10 - 3 * clusters + 10 * clusters - 1) / (10 * clusters);   // ceil(tiles2 / clusters - 0.3)
-    return r2 <= r1;
+    return r2 <= r1 ? PAIRS : SINGLE;
 }
 
 Plan make_plan(int M, int N, int K, bool may_split)
 {
     const int k_blocks = (K + BK - 1) / BK;
-    Plan best = {1, BM};
-    if (pairs_take(M, N) && may_split) {
+    Plan best = {1, BM, choose_kind(M, N, may_split)};
+    if (best.kind == PAIRS && may_split) {
         // a few hundred tokens on pairs of blocks: with too few 256 x 256 tiles for the clusters (o and down at the 8B
         // shape: 32), K is cut into two to four ranges, so that tiles x ranges occupy most of the clusters (SMs / 2); the
         // partial tiles are summed by the caller or by the reduce kernel.  At least 16 K blocks a range.
@@ -1179,10 +1188,11 @@ Plan make_plan(int M, int N, int K, bool may_split)
             if (s > 4) s = 4;
             while (s > 1 && (k_blocks / s < 16 || (k_blocks + (k_blocks + s - 1) / s - 1) / ((k_blocks + s - 1) / s) != s)) --s;
             best.splits = s;
+            if (s == 1) best.kind = M <= 256 ? SWAPPED : SINGLE;   // K is too short for ranges: too few tiles for the clusters
         }
-        return best;
+        if (best.kind == PAIRS) return best;
     }
-    if (M > 256) return best;   // many tokens: the persistent kernels share the work out themselves (stream-K)
+    if (best.kind != SWAPPED) return best;   // many tokens: the persistent kernels share the work out themselves (stream-K)
     const int slots = 2 * spy_sm_count() / ((M + 63) / 64 > 0 ? (M + 63) / 64 : 1);   // 65 to 256 tokens: two to four token tiles share every weight tile
     if ((N + BM - 1) / BM >= slots) return best;   // more 128-row tiles than slots: they spread evenly as they are
     int most = may_split ? (k_blocks / 4 > 0 ? k_blocks / 4 : 1) : 1;
@@ -1256,7 +1266,7 @@ extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, 
     const int splits = plan.splits;
     if (splits_used) *splits_used = splits;
     const int k_blocks = (K + BK - 1) / BK;
-    const bool swap = M <= 256;
+    const bool swap = plan.kind == SWAPPED;
     const int bn = swap ? (M <= 16 ? 16 : (M <= 32 ? 32 : 64)) : 256;
     CUtensorMap mx, my;
     if (swap) {
@@ -1271,7 +1281,7 @@ extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, 
     const bool f32_out = splits > 1 || c_dtype == SPY_F32;
     // pairs need enough 256 x 256 tiles to occupy at least half of the clusters; smaller products go to single
     // blocks, which share the K blocks of their 128 x 256 tiles out over all SMs
-    if (!swap && pairs_take(M, N) && (splits > 1 || (long long)((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256) >= pair_min_tiles())) {
+    if (plan.kind == PAIRS) {
         // many tokens, one pass over K, at least two 256-row tiles: pairs of blocks on 256 x 256 tiles
         CUtensorMap my_half;
         if (make_map(&my_half, W, N, K, ldw, BM)) return 1;
