@@ -1,9 +1,10 @@
 // bfloat16 attention for prompt portions on the 5th-generation tensor cores (tcgen05), keys
 // and values read from the paged cache.
 //
-// One block owns 256 rows = (256 / Gp) consecutive tokens of one sequence x the G query
-// heads of one key/value head (Gp = G rounded up to a power of two), as TWO query tiles of
-// 128 rows, A (the earlier tokens) and B, and walks the keys in tiles of 128.  Every key and
+// One block owns 256 rows = 2 x (128 / G) consecutive tokens of one sequence x the G query
+// heads of one key/value head, as TWO query tiles of 128 rows (a token's G heads in G
+// consecutive rows; the last 128 % G rows of a tile stay empty), A (the earlier tokens) and B,
+// and walks the keys in tiles of 128.  Every key and
 // value tile is brought into shared memory once and used by both query tiles: a block reads
 // half the cache bytes per product that a block of 128 rows would, and it is the traffic from
 // L2 into the SMs (every block of rows re-reads the keys it sees) that bounds this kernel at
@@ -137,7 +138,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
 
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
-    const int tokens_per_block = BLOCK_ROWS / p.Gp, tokens_per_tile = ROWS / p.Gp;
+    const int tokens_per_tile = ROWS / p.Gp, tokens_per_block = 2 * tokens_per_tile;   // a tile's last ROWS % Gp rows stay empty
     if (tid == 0) {
         for (int i = 0; i < K_STAGES; ++i) {
             mbar_init(bar_k + i, 1);
@@ -236,7 +237,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
             for (int idx = row; idx < ROWS * CPR; idx += GROUP_THREADS) {
                 const int r = idx / CPR, c = idx % CPR;
                 const int r_tok = it.tok0 + grp * tokens_per_tile + r / p.Gp, r_hg = r % p.Gp;
-                const bool ok = r_tok < it.tok_end && r_hg < p.G && c * 8 < p.hd;   // rows and columns beyond the data are filled with zeros
+                const bool ok = r / p.Gp < tokens_per_tile && r_tok < it.tok_end && r_hg < p.G && c * 8 < p.hd;   // rows and columns beyond the data are filled with zeros
                 const bf16* src = p.q + (size_t)(ok ? r_tok : 0) * p.q_stride + (size_t)(it.kvh * p.G + (ok ? r_hg : 0)) * p.hd + (ok ? c * 8 : 0);
                 cp_async16(smem + L::Q_OFF + grp * L::OPERAND_BYTES + tile_offset(r, c), src, ok);
             }
@@ -248,7 +249,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
             if (it.n_tiles < 0) break;
             const int my_tiles = grp == 0 ? it.tiles_a : it.tiles_b, tile_first = it.tile_first, tok_end = it.tok_end, kvh = it.kvh;
             const int tok = it.tok0 + grp * tokens_per_tile + row / p.Gp, hg = row % p.Gp;
-            const bool row_ok = tok < tok_end && hg < p.G;
+            const bool row_ok = row / p.Gp < tokens_per_tile && tok < tok_end && hg < p.G;
             const int head = kvh * p.G + hg;
             // the keys this row sees
             const int pos = row_ok ? min(p.positions[tok], it.block_last_pos) : -1;
@@ -548,8 +549,7 @@ extern "C" int spy_attention_tc(const void* q, long long q_row_stride, void* out
         SPY_FAIL("attention_tc: queries, pages and output must be 16-byte aligned with rows a multiple of 8 elements");
     if (page_size <= 0 || num_pages <= 0 || table_width <= 0) SPY_FAIL("attention_tc: page_size, num_pages and table_width must be positive");
     if (window < 0) SPY_FAIL("attention_tc: window %d must be 0 (none) or positive", window);
-    int Gp = 1;
-    while (Gp < G) Gp *= 2;
+    const int Gp = G;   // rows a token takes in a query tile: one per head of the group (128 / G tokens a tile, the remainder of the rows stays empty)
     Params p;
     p.q = (const bf16*)q; p.q_stride = q_row_stride; p.out = (bf16*)out; p.block_table = block_table;
     p.positions = positions; p.q_start = q_start; p.status = status; p.table_width = table_width; p.page_size = page_size;
@@ -575,7 +575,7 @@ extern "C" int spy_attention_tc(const void* q, long long q_row_stride, void* out
         SPY_CUDA(cudaFuncSetAttribute(attention_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<64>::TOTAL));
         SPY_CUDA(cudaFuncSetAttribute(attention_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<128>::TOTAL));
     }
-    const int tokens_per_block = BLOCK_ROWS / Gp;
+    const int tokens_per_block = 2 * (BLOCK_ROWS / 2 / Gp);
     const long long blocks = (tokens + tokens_per_block - 1) / tokens_per_block + seqs;   // an upper bound without a host copy of q_start
     const long long items = blocks * nkv;
     if (items > 0x7fffffffLL) SPY_FAIL("attention_tc: the batch's %lld work items exceed the kernel's range", items);
