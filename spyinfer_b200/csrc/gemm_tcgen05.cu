@@ -1078,10 +1078,11 @@ namespace {
 // Pairs and single blocks (many tokens): 256 x 256 or 128 x 256 tiles; K is cut into ranges by plan only for pairs with
 // few tiles (the single-block kernel shares K blocks out itself when there are fewer tiles than SMs).
 // The swapped kernel (few tokens: decoding; the weights sit in the instruction's M slot, two blocks share an
-// SM; 65 tokens and more are two to four token tiles of 64 whose blocks start side by side and share
-// every weight tile through L2, so the plan fills the slots divided by the token tiles; measured on
-// whole decode steps of the 8B shape at 2,048 keys: batch 128 12.46 -> 10.58 ms against 128 x 256 tiles
-// with shared K blocks):
+// SM; the token tile is 16, 32, 64 or 128 tokens (65 to 128 tokens in ONE tile of 128: against two tiles of
+// 64, which read every weight tile from L2 twice, gate‖up of the 8B shape 53 -> 42 us, down 26 -> 24, of the
+// 14B shape 75 -> 62 and 48 -> 38); more than 128 tokens, where the pairs find too little work, are two token
+// tiles whose blocks start side by side and share every weight tile through L2, so the plan fills the slots
+// divided by the token tiles):
 // the product is bound by reading the weights, so what counts is that all 2 x SMs block
 // slots stream at once and end together.  When 128-row tiles times the splits would not fill
 // the slots, the tile takes fewer rows (a multiple of 4, at least 64: the TMA box shrinks, the
@@ -1139,6 +1140,8 @@ TailPlan plan_tail(int tiles, int clusters, int k_blocks)
 }
 
 enum Kind { SWAPPED, SINGLE, PAIRS };   // the kernel a product runs on
+// The swapped kernel's token tile (the instruction's N): 16, 32, 64 or 128 tokens, the smallest that holds them all.
+static inline int token_tile(int M) { return M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128)); }
 struct Plan {
     int splits, tile_rows;
     Kind kind;
@@ -1193,7 +1196,8 @@ Plan make_plan(int M, int N, int K, bool may_split)
         if (best.kind == PAIRS) return best;
     }
     if (best.kind != SWAPPED) return best;   // many tokens: the persistent kernels share the work out themselves (stream-K)
-    const int slots = 2 * spy_sm_count() / ((M + 63) / 64 > 0 ? (M + 63) / 64 : 1);   // 65 to 256 tokens: two to four token tiles share every weight tile
+    const int token_tiles = (M + token_tile(M) - 1) / token_tile(M);   // more than 128 tokens: two token tiles share every weight tile
+    const int slots = 2 * spy_sm_count() / (token_tiles > 0 ? token_tiles : 1);
     if ((N + BM - 1) / BM >= slots) return best;   // more 128-row tiles than slots: they spread evenly as they are
     int most = may_split ? (k_blocks / 4 > 0 ? k_blocks / 4 : 1) : 1;
     if (most > 16) most = 16;
@@ -1267,7 +1271,7 @@ extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, 
     if (splits_used) *splits_used = splits;
     const int k_blocks = (K + BK - 1) / BK;
     const bool swap = plan.kind == SWAPPED;
-    const int bn = swap ? (M <= 16 ? 16 : (M <= 32 ? 32 : 64)) : 256;
+    const int bn = swap ? token_tile(M) : 256;
     CUtensorMap mx, my;
     if (swap) {
         if (make_map(&mx, W, N, K, ldw, plan.tile_rows) || make_map(&my, A, M, K, lda, bn)) return 1;
@@ -1405,6 +1409,7 @@ extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, 
                        : launch<BN_, bf16, 0>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, plan.tile_rows, status, stream, next_weights, next_bytes)
     if (bn == 16) SPY_LAUNCH(16);
     else if (bn == 32) SPY_LAUNCH(32);
+    else if (bn == 128) SPY_LAUNCH(128);
     else SPY_LAUNCH(64);
 #undef SPY_LAUNCH
     if (rc) return rc;

@@ -57,6 +57,8 @@ class StepBatch:
     host_state_slot: np.ndarray = None
     max_q_len: int = 0
     max_ctx_len: int = 0
+    #: every request of the batch brings exactly one token (a decode step): parts may then take kernels made for that
+    one_token_each: bool = False
     extras: Dict[str, object] = field(default_factory=dict)
 
 
@@ -108,4 +110,5 @@ class BatchStager:
             num_tokens=T, num_seqs=S, token_ids=v[0], positions=v[1], seq_of_token=v[2], logit_rows=v[3], q_start=v[4], ctx_len=v[5],
             state_slot=v[6], block_tables=[v[7 + i].view(S, widths[i]) for i in range(len(tables))], status=self.status,
             host_positions=positions, host_q_start=q_start, host_ctx_len=ctx_len, host_state_slot=state_slot,
-            max_q_len=int(np.max(q_start[1:] - q_start[:-1])) if S else 0, max_ctx_len=int(ctx_len.max()) if S else 0)
+            max_q_len=int(np.max(q_start[1:] - q_start[:-1])) if S else 0, max_ctx_len=int(ctx_len.max()) if S else 0,
+            one_token_each=bool(S > 0 and T == S and int(np.min(q_start[1:] - q_start[:-1])) == 1))

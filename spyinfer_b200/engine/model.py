@@ -109,7 +109,10 @@ class Model:
         return list(dict.fromkeys(mods))
 
     def graph_safe(self) -> bool:
-        return all(l.mixer is None or l.mixer.graph_safe for l in self.layers)
+        """Every part and every block arrangement says that its launches do not depend on a batch's content."""
+        parts = [self.embedding, self.final_norm, self.head] + [p for l in self.layers for p in l.parts()]
+        nested = [p.position for p in parts if getattr(p, "position", None) is not None]
+        return all(p.graph_safe for p in parts + nested) and all(l.block.graph_safe for l in self.layers)
 
     # ---- cache needs -------------------------------------------------------------------------
     def cache_needs(self):

@@ -48,7 +48,7 @@ class ModelRunner:
         self._host_tokens = [None, None]
         self._tokens_copied = [torch.cuda.Event(), torch.cuda.Event()]
         self._read_turn = 0
-        self._graphs = {}          # decode batch size (padded) -> (graph, logits, kernel launches it holds)
+        self._graphs = {}          # padded sizes of a step -> (graph, logits, kernel launches it holds); decode steps: the batch size
         self._use_graphs = bool(config.use_cuda_graphs) and model.graph_safe()
         #: set to a list to have every step append a pair of CUDA events (timing enabled) recorded
         #: before its first and after its last launch: the sum of the pairs' times against the span
@@ -124,46 +124,99 @@ class ModelRunner:
         ar = np.arange(bucket + 1, dtype=np.int32)
         return self.stager.stage(token_ids, positions, ar[:bucket], ar, ctx_len, slots, ar[:bucket], tables, bucket, bucket)
 
+    #: a step of other shapes (prompt portions, mixes) up to this many tokens is padded to one of a few sizes and
+    #: replayed from a graph as well: below it the host takes longer to launch the step's kernels one by one
+    #: than the device takes to run them
+    GRAPH_STEP_TOKENS = 384
+    #: graphs of padded steps kept at a time (the least recently used one goes first)
+    GRAPH_STEP_LIMIT = 24
+
     def _step_graph(self, entries: Sequence[StepEntry], tokens_from: Optional[torch.Tensor] = None) -> torch.Tensor:
         S = len(entries)
         bucket = self._decode_bucket(S)
         batch = self._build_decode_batch(entries, bucket)
         if tokens_from is not None:
             batch.token_ids[:S].copy_(tokens_from[:S])   # behind the staging copy on the stream, ahead of the kernels
-        held = self._graphs.get(bucket)
-        if held is None:
-            # the first step of this size runs eagerly (it also makes every lazy allocation);
-            # the graph is captured from the second on
-            self._graphs[bucket] = "warm"
-            logits = self.model.forward(batch, self.cache)
-        elif held == "warm":
-            torch.cuda.synchronize()
-            before = kernels.launch_count()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                static_logits = self.model.forward(batch, self.cache)
-            self._graphs[bucket] = (graph, static_logits, kernels.launch_count() - before)
-            kernels.count_launches(-(kernels.launch_count() - before))   # captured, not run
-            graph.replay()
-            kernels.count_launches(self._graphs[bucket][2])
-            logits = static_logits
-            self.graph_steps += 1
-        else:
-            graph, static_logits, launches = held
-            graph.replay()
-            kernels.count_launches(launches)
-            logits = static_logits
-            self.graph_steps += 1
+        logits = self._run_through_graph(bucket, batch)
         self.commit(entries)
         self.steps += 1
         self.tokens_run += S
         return logits[:S]
 
+    def _run_through_graph(self, key, batch: StepBatch) -> torch.Tensor:
+        """The forward pass of a batch whose arrays lie at the fixed offsets of its padded sizes ``key``: eagerly the
+        first time (which also makes every lazy allocation), captured the second, replayed from then on."""
+        held = self._graphs.get(key)
+        if held is None:
+            self._graphs[key] = "warm"
+            return self.model.forward(batch, self.cache)
+        if held == "warm":
+            torch.cuda.synchronize()
+            before = kernels.launch_count()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                static_logits = self.model.forward(batch, self.cache)
+            launches = kernels.launch_count() - before
+            self._graphs[key] = (graph, static_logits, launches)
+            kernels.count_launches(-launches)   # captured, not run
+        else:
+            self._graphs[key] = self._graphs.pop(key)   # most recently used last
+        graph, static_logits, launches = self._graphs[key]
+        graph.replay()
+        kernels.count_launches(launches)
+        self.graph_steps += 1
+        return static_logits
+
+    def _padded_sizes(self, entries: Sequence[StepEntry]):
+        """The padded sizes (tokens, requests, wanted rows) under which a small step of any shape is replayed from a
+        graph, or None when it runs eagerly (too many tokens, nothing wanted, no room for the padding)."""
+        T, S, R = sum(len(e.tokens) for e in entries), len(entries), sum(len(e.want) for e in entries)
+        if R == 0 or T > self.GRAPH_STEP_TOKENS:
+            return None
+        Tb = (T + 31) // 32 * 32 if T <= 128 else (T + 63) // 64 * 64
+        need = S + (1 if Tb > T else 0)           # the padding tokens are a request of their own
+        Sb = 1
+        while Sb < need:
+            Sb *= 2
+        Sb = min(Sb, self.config.max_num_seqs)
+        Rb = 1
+        while Rb < R:
+            Rb *= 2
+        Rb = min(Rb, Tb)
+        if Sb < need or Rb < R or Tb > self.stager.max_tokens:
+            return None
+        return Tb, Sb, Rb
+
+    def _build_padded_batch(self, entries: Sequence[StepEntry], Tb: int, Sb: int, Rb: int) -> StepBatch:
+        """The batch laid out for ``Tb`` tokens, ``Sb`` requests and ``Rb`` wanted rows: the entries first; the
+        padding tokens form one more request at position 0 that reads and writes only the cache's spare page, further
+        requests are empty, and the padding rows of the logits repeat the first wanted row."""
+        cache = self.cache
+        rids, tok, pos, seq_of, q_start, ctx, slot, rows, _ = self._fill(entries)
+        T, S, R = len(tok), len(ctx), len(rows)
+        token_ids, positions = np.zeros(Tb, np.int32), np.zeros(Tb, np.int32)
+        seq_of_token = np.full(Tb, S, np.int32)
+        token_ids[:T], positions[:T], seq_of_token[:T] = tok, pos, seq_of
+        starts = np.full(Sb + 1, Tb, np.int32)
+        starts[:S + 1] = q_start
+        ctx_len, slots = np.ones(Sb, np.int32), np.zeros(Sb, np.int32)
+        ctx_len[:S], slots[:S] = ctx, slot
+        logit_rows = np.full(Rb, rows[0], np.int32)
+        logit_rows[:R] = rows
+        tables = []
+        for g in range(cache.num_groups()):
+            t = np.full((Sb, cache.width), -1, np.int32)
+            cache.gather_block_tables(rids, g, out=t)
+            t[S:, 0] = cache.spare_page(g)
+            tables.append(t)
+        return self.stager.stage(token_ids, positions, seq_of_token, starts, ctx_len, slots, logit_rows, tables, Tb, Sb)
+
     def step(self, entries: Sequence[StepEntry], tokens_from: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Runs the entries as one batch.  Returns float32 logits ``[wanted, vocab]`` on the
         device, rows in the order of the entries and of each entry's ``want``; None when
         nothing is wanted.  A batch in which every request brings one token and wants its
-        logits (a decode step) is replayed from a CUDA graph captured for its size; the
+        logits (a decode step) is replayed from a CUDA graph captured for its size, and so is any
+        other batch of up to ``GRAPH_STEP_TOKENS`` tokens, padded to one of a few sizes; the
         returned tensor is then the graph's own output buffer, valid until the next step.
 
         ``tokens_from`` (int32 on the device, one per entry; every entry brings one token): the token
@@ -187,6 +240,20 @@ class ModelRunner:
             if len({e.request for e in entries}) != len(entries):
                 raise StepError("a request appears twice in one step")
             return self._step_graph(entries, tokens_from)
+        sizes = self._padded_sizes(entries) if self._use_graphs and tokens_from is None else None
+        if sizes is not None:
+            if len({e.request for e in entries}) != len(entries):
+                raise StepError("a request appears twice in one step")
+            batch = self._build_padded_batch(entries, *sizes)
+            wanted = sum(len(e.want) for e in entries)
+            logits = self._run_through_graph(("step",) + sizes, batch)[:wanted]
+            mixed = [k for k in self._graphs if isinstance(k, tuple)]
+            if len(mixed) > self.GRAPH_STEP_LIMIT:
+                del self._graphs[mixed[0]]
+            self.commit(entries)
+            self.steps += 1
+            self.tokens_run += sum(len(e.tokens) for e in entries)
+            return logits
         batch = self.build_batch(entries)
         if tokens_from is not None:
             batch.token_ids.copy_(tokens_from[:batch.num_tokens])

@@ -129,7 +129,7 @@ class Attention(Mixer):
                                   store=cache.writes, status=batch.status, q_out=q,
                                   pairing=self.position.pairing if self.position is not None else "half")
         out = torch.empty((x.shape[0], self.nh * self.hd), dtype=x.dtype, device=x.device)
-        decoding = batch.num_tokens == batch.num_seqs         # every request brings one token
+        decoding = batch.one_token_each         # every request brings one token
         boxes = self.tc and cache.page_size in kernels.ATTENTION_TMA_PAGE_SIZES        # a page is one TMA box
         if (boxes and decoding and batch.num_seqs <= kernels.ATTENTION_DECODE_MAX_SEQS and batch.num_seqs * self.nkv <= kernels.ATTENTION_DECODE_MAX_PAIRS
                 and kernels.attention_decode_takes(self.nh, self.nkv, self.hd, cache.page_size, x.dtype)):

@@ -38,6 +38,11 @@ class Part:
     kind: str = ""
     #: kernel modules (``csrc/<name>.cu``) this part launches; built before the first step
     kernel_modules: Sequence[str] = ()
+    #: True when ``forward`` launches the same kernels with the same arguments for every batch of the same sizes
+    #: (tokens, requests, wanted rows): no look at the batch's content on the host, no wait for the device, no
+    #: allocation that outlives the call.  A model whose parts all say so has its small steps captured in CUDA
+    #: graphs and replayed; one part that does not keeps the whole model on launches one by one.
+    graph_safe: bool = False
 
     def __init__(self, params: Dict[str, Any], ctx: BuildContext):
         self.params = params
@@ -85,11 +90,6 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
-    #: True when ``forward`` launches the same kernels with the same arguments for every
-    #: batch of one size whose requests bring one token each (no host-side look at the
-    #: batch's content), so that a decode step can be captured in a CUDA graph
-    graph_safe: bool = False
-
     #: True: ``forward`` may hand its result over as a stack ``[splits, rows, size]`` of float32 partial
     #: products (its last product then skips its own reduction), which ``Norm.forward_add`` adds to the
     #: residual.  A block arrangement that does anything else with the result sets this to False on
@@ -117,6 +117,7 @@ class Block:
     same names (None for an optional role that the layer does not have)."""
 
     kind: str = ""
+    graph_safe: bool = False      # as ``Part.graph_safe``, for the arrangement's own code
     required: Sequence[str] = ("mixer_norm", "mixer", "ffn_norm", "feed_forward")
     optional: Sequence[str] = ()
 

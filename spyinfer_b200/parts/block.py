@@ -30,6 +30,8 @@ def build_block(kind: str, parts) -> Block:
 
 @register_block("pre_norm")
 class PreNormBlock(Block):
+    graph_safe = True
+
     def forward(self, hidden, delta, batch, cache):
         x = self.mixer_norm.forward_add(hidden, delta)
         a = self.mixer.forward(x, batch, cache)

@@ -17,6 +17,7 @@ from .registry import register_part
 
 @register_part("token_embedding")
 class TokenEmbedding(Part):
+    graph_safe = True
     """params: ``vocab_size``, ``hidden_size``, ``weight`` (full tensor name)."""
 
     kernel_modules = ("embedding",)
@@ -39,6 +40,7 @@ class TokenEmbedding(Part):
 
 @register_part("lm_head")
 class LMHead(Part):
+    graph_safe = True
     """params: ``vocab_size``, ``hidden_size``, ``tied``, ``weight`` (full name when untied),
     ``tied_to`` (full name of the embedding table when tied)."""
 

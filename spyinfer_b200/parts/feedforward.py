@@ -19,6 +19,7 @@ from .registry import register_part
 
 @register_part("gated_mlp")
 class GatedMLP(FeedForward):
+    graph_safe = True
     """params: ``hidden_size``, ``intermediate_size``, ``activation`` ("silu"), ``prefix``."""
 
     def __init__(self, params, ctx):

@@ -16,6 +16,7 @@ from .registry import register_part
 
 @register_part("rms_norm")
 class RMSNorm(Norm):
+    graph_safe = True
     """params: ``size``, ``eps``, ``weight`` (the tensor's relative name)."""
 
     kernel_modules = ("rmsnorm",)

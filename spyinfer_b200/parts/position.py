@@ -22,6 +22,7 @@ _TABLES = {}
 
 @register_part("rotary_half")
 class RotaryHalf(PositionEncoding):
+    graph_safe = True
     """params: ``theta``, ``rotary_dim`` (even, at most the head size); optional
     ``frequency_scale`` (default 1) and ``inverse_frequencies`` (a list of ``rotary_dim / 2``
     numbers that replaces ``theta^(-j/r)``)."""
@@ -67,4 +68,5 @@ class RotaryInterleaved(RotaryHalf):
 
 @register_part("no_position")
 class NoPosition(PositionEncoding):
+    graph_safe = True
     pass

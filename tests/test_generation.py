@@ -216,6 +216,51 @@ def test_step_raw_gives_the_plain_logits_and_leaves_the_scheduler_alone(tiny_mod
     check_greedy(weights, cfg, toks[:3], out, "float32")
 
 
+@pytest.mark.parametrize("dtype,name", [("float32", "b"), ("bfloat16", "d"), ("bfloat16", "c")])
+def test_small_steps_of_any_shape_replayed_from_graphs_equal_eager_steps(tiny_models, dtype, name):
+    """Small steps that are no decode steps (a prompt portion beside decoded tokens of others) are padded to a few
+    sizes and replayed from CUDA graphs.  Seven steps of the same padded sizes but different shapes inside (the
+    first runs eagerly, the second is captured, the rest are replays) give what an engine without graphs gives,
+    row for row, and what the plain implementation gives; the padding leaves nothing behind in the cache."""
+    from spyinfer_b200.engine import StepEntry
+    folder, cfg, weights = tiny_models[name]
+    rng = np.random.default_rng(11)
+    V = cfg["vocab_size"]
+    seqs = {r: rng.integers(1, V, size=60).tolist() for r in ("u", "v", "w0", "w1", "w2", "w3", "w4", "w5", "w6")}
+    engines = [engine_for(folder, dtype, max_num_seqs=8, num_kvcache_blocks=64, max_num_batched_tokens=128, use_cuda_graphs=g) for g in (True, False)]
+    free = [e.stats()["free_pages"] for e in engines]
+    outs = [[], []]
+    for i, engine in enumerate(engines):
+        done = {"u": 0, "v": 0}
+        for r, n in (("u", 9), ("v", 30)):                       # two requests under way
+            engine.step_raw([StepEntry(r, seqs[r][:n], [])])
+            done[r] = n
+        for k in range(7):
+            w, n = f"w{k}", 17 + k                                  # a new request's prompt of 17 ... 23 tokens beside two decoded tokens
+            entries = [StepEntry("u", seqs["u"][done["u"]:done["u"] + 1], [0]), StepEntry(w, seqs[w][:n], [n - 1, 0] if k % 2 else [n - 1]),
+                       StepEntry("v", seqs["v"][done["v"]:done["v"] + 1], [0])]
+            outs[i].append(engine.step_raw(entries).copy())
+            done["u"] += 1
+            done["v"] += 1
+            engine.release_raw(w)
+        for r in ("u", "v"):
+            engine.release_raw(r)
+        assert engine.stats()["free_pages"] == free[i]
+    assert engines[0].runner.graph_steps >= 5 and engines[1].runner.graph_steps == 0
+    tol = dict(rtol=2e-4, atol=2e-5) if dtype == "float32" else dict(rtol=3e-2, atol=3e-2)
+    for k, (a, b) in enumerate(zip(*outs)):
+        assert a.shape == b.shape
+        np.testing.assert_allclose(a, b, **(dict(rtol=1e-5, atol=1e-6) if dtype == "float32" else tol), err_msg=f"step {k}")
+    # against the plain implementation: the new request's last row and u's decoded rows
+    ref_u = plain_model.forward_logits(weights, cfg, seqs["u"][:16]).numpy()
+    for k in range(7):
+        n = 17 + k
+        ref_w = plain_model.forward_logits(weights, cfg, seqs[f"w{k}"][:n]).numpy()
+        scale = np.abs(ref_w).max()
+        np.testing.assert_allclose(outs[0][k][0], ref_u[9 + k], rtol=tol["rtol"], atol=tol["atol"] * max(1.0, scale))
+        np.testing.assert_allclose(outs[0][k][1], ref_w[n - 1], rtol=tol["rtol"], atol=tol["atol"] * max(1.0, scale))
+
+
 def SamplingParamsFor(n):
     from spyinfer_b200 import SamplingParams
     return SamplingParams(max_new_tokens=n, ignore_eos=True)

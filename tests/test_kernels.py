@@ -332,11 +332,11 @@ def test_sampling_top_k_draws_only_among_the_largest():
 
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("M,N,K", [(1, 128, 64), (5, 200, 96), (16, 4096, 4096), (17, 1000, 520), (33, 136, 72), (64, 6144, 512),
-                                   (65, 300, 136), (128, 256, 64), (100, 4096, 4096), (128, 6144, 4096), (90, 1187, 1032), (129, 1187, 1032), (300, 512, 4096), (1000, 24, 200), (2048, 1024, 12288), (512, 4096, 4096), (600, 3000, 4096),
+                                   (65, 300, 136), (128, 256, 64), (100, 4096, 4096), (128, 6144, 4096), (90, 1187, 1032), (129, 1187, 1032), (200, 6144, 4096), (256, 4096, 12288), (160, 9000, 520), (300, 512, 4096), (1000, 24, 200), (2048, 1024, 12288), (512, 4096, 4096), (600, 3000, 4096),
                                    (2048, 4096, 512), (1500, 3000, 264), (4100, 2600, 72)])
 def test_gemm_tcgen05(out_dtype, M, N, K):
-    """Tensor-core product at sizes that exercise every tile class (16/32/64 tokens swapped,
-    128 x 256 tiles), tails in M, N and K, split-K, and the persistent kernel with one, two and
+    """Tensor-core product at sizes that exercise every tile class (16/32/64/128 tokens swapped, one and two
+    token tiles; pairs with one row of 256 x 256 tiles, with and without K ranges; 128 x 256 tiles), tails in M, N and K, split-K, and the persistent kernel with one, two and
     several tiles per block."""
     from spyinfer_b200 import kernels
     torch.manual_seed(M * 7 + N)
