@@ -239,14 +239,18 @@ def kernel_rooflines(engine, batches, prompt_tokens, hbm_gbs, bf16_tflops, page)
     sizes = [(f"b{b}", b) for b in batches] + [(f"t{prompt_tokens}", prompt_tokens)]
     for tag, M in sizes[:-1]:
         product(f"lm_head_{tag}", [model.head.linear], M, out_dtype=torch.float32)
-    for tag, M in sizes:
+    def products(tag, M):
         product(f"qkv_{tag}", [l.mixer.qkv for l in layers], M, defer=True)
         product(f"o_{tag}", [l.mixer.o for l in layers], M, defer=True)
         product(f"gate_up_{tag}", [l.feed_forward.gate_up for l in layers], M, epilogue="swiglu")
         product(f"down_{tag}", [l.feed_forward.down for l in layers], M, defer=True)
+
+    for tag, M in sizes[:-1]:
+        products(tag, M)
     r = microbench.bench_attention(1, prompt_tokens, q_len=prompt_tokens, nh=nh, nkv=nkv, hd=hd, page_size=page, kernel="tc", iters=20, graph=True)
     out[f"attention_prompt_t{prompt_tokens}"] = {"us": round(r["us"], 2), "achieved": round(r["tflops"], 1), "unit": "TFLOP/s",
                                                   "frac": round(r["tflops"] / bf16_tflops, 4)}
+    products(*sizes[-1])
     return out
 
 
