@@ -50,6 +50,7 @@ class ModelRunner:
         self._read_turn = 0
         self._graphs = {}          # padded sizes of a step -> (graph, logits, kernel launches it holds); decode steps: the batch size
         self._use_graphs = bool(config.use_cuda_graphs) and model.graph_safe()
+        self._graph_pool = None
         #: set to a list to have every step append a pair of CUDA events (timing enabled) recorded
         #: before its first and after its last launch: the sum of the pairs' times against the span
         #: from the first to the last event is the share of the time the device was at work
@@ -154,7 +155,11 @@ class ModelRunner:
             torch.cuda.synchronize()
             before = kernels.launch_count()
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
+            if self._graph_pool is None:
+                self._graph_pool = torch.cuda.graph_pool_handle()
+            # one memory pool for all step graphs: they never run at the same time, none reads what another wrote, and the
+            # logits each returns stay allocated while the graph is held, so their activations may share the same memory
+            with torch.cuda.graph(graph, pool=self._graph_pool):
                 static_logits = self.model.forward(batch, self.cache)
             launches = kernels.launch_count() - before
             self._graphs[key] = (graph, static_logits, launches)
