@@ -26,6 +26,28 @@ class StepError(RuntimeError):
     pass
 
 
+def padded_step_sizes(tokens: int, requests: int, wanted: int, max_requests: int, max_tokens: int, limit: int):
+    """The sizes (tokens, requests, wanted rows) that a step is padded to before it is replayed from a CUDA graph: tokens
+    to a multiple of 32 (up to 128) or 64, requests to a power of two with room for the request that holds the padding
+    tokens, wanted rows to a power of two that is at least the requests'.  None: the step is not padded (more than ``limit`` tokens, nothing wanted,
+    or no room left for the padding), it runs on launches one by one."""
+    if wanted <= 0 or tokens <= 0 or tokens > limit:
+        return None
+    Tb = (tokens + 31) // 32 * 32 if tokens <= 128 else (tokens + 63) // 64 * 64
+    need = requests + (1 if Tb > tokens else 0)           # the padding tokens are a request of their own
+    Sb = 1
+    while Sb < need:
+        Sb *= 2
+    Sb = min(Sb, max_requests)
+    Rb = 1
+    while Rb < wanted:
+        Rb *= 2
+    Rb = max(min(Rb, Tb), min(Sb, Tb))                    # at least a row a request: fewer distinct sizes, and the extra rows cost next to nothing
+    if Sb < need or Rb < wanted or Tb > max_tokens:
+        return None
+    return Tb, Sb, Rb
+
+
 class ModelRunner:
     def __init__(self, model: Model, config: EngineConfig, cache: Optional[CacheManager] = None):
         kernels.require_cuda()
@@ -175,22 +197,8 @@ class ModelRunner:
     def _padded_sizes(self, entries: Sequence[StepEntry]):
         """The padded sizes (tokens, requests, wanted rows) under which a small step of any shape is replayed from a
         graph, or None when it runs eagerly (too many tokens, nothing wanted, no room for the padding)."""
-        T, S, R = sum(len(e.tokens) for e in entries), len(entries), sum(len(e.want) for e in entries)
-        if R == 0 or T > self.GRAPH_STEP_TOKENS:
-            return None
-        Tb = (T + 31) // 32 * 32 if T <= 128 else (T + 63) // 64 * 64
-        need = S + (1 if Tb > T else 0)           # the padding tokens are a request of their own
-        Sb = 1
-        while Sb < need:
-            Sb *= 2
-        Sb = min(Sb, self.config.max_num_seqs)
-        Rb = 1
-        while Rb < R:
-            Rb *= 2
-        Rb = min(Rb, Tb)
-        if Sb < need or Rb < R or Tb > self.stager.max_tokens:
-            return None
-        return Tb, Sb, Rb
+        return padded_step_sizes(sum(len(e.tokens) for e in entries), len(entries), sum(len(e.want) for e in entries),
+                                 self.config.max_num_seqs, self.stager.max_tokens, self.GRAPH_STEP_TOKENS)
 
     def _build_padded_batch(self, entries: Sequence[StepEntry], Tb: int, Sb: int, Rb: int) -> StepBatch:
         """The batch laid out for ``Tb`` tokens, ``Sb`` requests and ``Rb`` wanted rows: the entries first; the

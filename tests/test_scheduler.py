@@ -263,3 +263,25 @@ def test_random_workloads_in_a_pool_smaller_than_max_model_len(seed):
         else:
             assert s.finish_reason == "max_new_tokens" and s.num_generated == s.sampling.max_new_tokens
     assert cache.num_free_pages() == 6 and cache.num_free_slots() == 3
+
+
+def test_padded_sizes_of_small_steps():
+    """The sizes a small step is padded to for its CUDA graph: few distinct ones, always room for the step and for the
+    request that holds the padding tokens, and no padding where there is no room or nothing to gain."""
+    from spyinfer_b200.engine.runner import padded_step_sizes
+    assert padded_step_sizes(17, 3, 3, 8, 2048, 384) == (32, 4, 4)
+    assert padded_step_sizes(32, 1, 1, 8, 2048, 384) == (32, 1, 1)          # nothing to pad
+    assert padded_step_sizes(40, 5, 1, 8, 2048, 384) == (64, 8, 8)          # wanted rows: at least one a request
+    assert padded_step_sizes(33, 8, 2, 8, 2048, 384) is None                # the padding tokens would need a ninth request
+    assert padded_step_sizes(64, 8, 8, 8, 2048, 384) == (64, 8, 8)
+    assert padded_step_sizes(130, 2, 1, 64, 2048, 384) == (192, 4, 4)
+    assert padded_step_sizes(385, 1, 1, 64, 2048, 384) is None              # large steps run as they are
+    assert padded_step_sizes(100, 1, 0, 64, 2048, 384) is None              # nothing wanted: no logits to return
+    assert padded_step_sizes(300, 1, 1, 64, 256, 384) is None               # beyond the staging buffers
+    seen = set()
+    for t in range(1, 385):
+        for s_ in (1, 2, 3, 5, 9, 17, 33):
+            sizes = padded_step_sizes(t, s_, min(s_, t), 64, 2048, 384)
+            assert sizes is not None and sizes[0] >= t and sizes[1] >= s_ + (1 if sizes[0] > t else 0) and sizes[2] >= min(s_, t)
+            seen.add(sizes)
+    assert len(seen) <= 60
