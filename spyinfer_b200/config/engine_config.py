@@ -28,6 +28,7 @@ class EngineConfig:
     dtype: str = "bfloat16"
     device: str = "cuda:0"
     use_cuda_graphs: bool = True
+    graph_step_tokens: int = 384      # steps of other shapes than decode steps are replayed from CUDA graphs up to this many tokens (0: never)
     lookahead_decode: bool = True     # launch the next decode step before the last one's tokens are read (see LLMEngine.step)
 
     def __post_init__(self):
@@ -42,6 +43,8 @@ class EngineConfig:
             raise ValueError(f"chunk_size must be a positive integer or None, found {self.chunk_size!r}")
         if self.num_kvcache_blocks is not None and self.num_kvcache_blocks <= 0:
             raise ValueError(f"num_kvcache_blocks must be positive, found {self.num_kvcache_blocks!r}")
+        if not isinstance(self.graph_step_tokens, int) or self.graph_step_tokens < 0:
+            raise ValueError(f"graph_step_tokens must be a non-negative integer, found {self.graph_step_tokens!r}")
         if not 0.0 < self.gpu_memory_utilization <= 1.0:
             raise ValueError("gpu_memory_utilization must lie in (0, 1]")
 

@@ -147,10 +147,9 @@ class ModelRunner:
         ar = np.arange(bucket + 1, dtype=np.int32)
         return self.stager.stage(token_ids, positions, ar[:bucket], ar, ctx_len, slots, ar[:bucket], tables, bucket, bucket)
 
-    #: a step of other shapes (prompt portions, mixes) up to this many tokens is padded to one of a few sizes and
-    #: replayed from a graph as well: below it the host takes longer to launch the step's kernels one by one
-    #: than the device takes to run them
-    GRAPH_STEP_TOKENS = 384
+    # A step of other shapes (prompt portions, mixes) of up to ``EngineConfig.graph_step_tokens`` tokens is padded to one of a
+    # few sizes and replayed from a graph as well: below that size the host takes longer to launch the step's kernels one by
+    # one than the device takes to run them (the default, 384, is where the two meet at the 8B shape).
     #: graphs of padded steps kept at a time (the least recently used one goes first)
     GRAPH_STEP_LIMIT = 24
 
@@ -198,7 +197,7 @@ class ModelRunner:
         """The padded sizes (tokens, requests, wanted rows) under which a small step of any shape is replayed from a
         graph, or None when it runs eagerly (too many tokens, nothing wanted, no room for the padding)."""
         return padded_step_sizes(sum(len(e.tokens) for e in entries), len(entries), sum(len(e.want) for e in entries),
-                                 self.config.max_num_seqs, self.stager.max_tokens, self.GRAPH_STEP_TOKENS)
+                                 self.config.max_num_seqs, self.stager.max_tokens, self.config.graph_step_tokens)
 
     def _build_padded_batch(self, entries: Sequence[StepEntry], Tb: int, Sb: int, Rb: int) -> StepBatch:
         """The batch laid out for ``Tb`` tokens, ``Sb`` requests and ``Rb`` wanted rows: the entries first; the
@@ -229,7 +228,7 @@ class ModelRunner:
         device, rows in the order of the entries and of each entry's ``want``; None when
         nothing is wanted.  A batch in which every request brings one token and wants its
         logits (a decode step) is replayed from a CUDA graph captured for its size, and so is any
-        other batch of up to ``GRAPH_STEP_TOKENS`` tokens, padded to one of a few sizes; the
+        other batch of up to ``EngineConfig.graph_step_tokens`` tokens, padded to one of a few sizes; the
         returned tensor is then the graph's own output buffer, valid until the next step.
 
         ``tokens_from`` (int32 on the device, one per entry; every entry brings one token): the token
