@@ -20,7 +20,7 @@ SHAPES = {
     "14b": dict(hidden_size=5120, num_attention_heads=40, num_key_value_heads=8, head_dim=128, intermediate_size=17408),
     "32b": dict(hidden_size=5120, num_attention_heads=64, num_key_value_heads=8, head_dim=128, intermediate_size=25600),
 }
-LENGTHS = [3, 40, 131]
+LENGTHS = [3, 40, 131, 300]   # 131 and 300 tokens: one row of 256-token tiles, and two
 PORTIONS = (7, 2, 19, 3, 2, 33)
 # the same bounds as the tiny models' replay tests
 TOL = {"float32": dict(max_rel=3e-5, rms_rel=1e-5), "bfloat16": dict(max_rel=5e-2, rms_rel=2e-2)}
