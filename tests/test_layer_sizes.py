@@ -127,3 +127,27 @@ def test_eight_layers_at_8b_sizes_in_bfloat16_stay_within_the_bound(tmp_path, ca
         print(f"\n  eight 8B-sized layers in bfloat16: largest error {worst:.4f} of the largest logit, rms error {err_rms:.4f} of the rms logit "
               f"(decoded rows alone: {err[64:].max() / scale:.4f})")
     assert worst <= TOL["bfloat16"]["max_rel"] and err_rms <= TOL["bfloat16"]["rms_rel"]
+
+
+@pytest.mark.parametrize("name,requests", [("8b", 200), ("14b", 100)])
+def test_many_requests_decode_together(name, requests, layer_models):
+    """A hundred and two hundred requests decoding at once in bfloat16 (the products then run on one token tile of 128, or on
+    pairs of blocks with K ranges whose partial sums the next norm and the q/k kernel add up; the decode graph is the padded
+    one of 128 or 256 rows): three new tokens each, every one held against the plain implementation given the same history."""
+    from spyinfer_b200 import LLMEngine, SamplingParams
+    folder, cfg, _, _ = layer_models(name)
+    weights = plain_model.random_weights(cfg, 100 + len(name), 0.02, 0.05)
+    rng = random.Random(requests)
+    prompts = [[rng.randrange(cfg["vocab_size"]) for _ in range(rng.randrange(2, 7))] for _ in range(requests)]
+    engine = LLMEngine(folder, dtype="bfloat16", max_num_seqs=256, max_model_len=64, num_kvcache_blocks=512, max_num_batched_tokens=2048)
+    outs = engine.generate(prompts, SamplingParams(max_new_tokens=3, ignore_eos=True))
+    assert engine.runner.graph_steps >= 1
+    for i, (p, o) in enumerate(zip(prompts, outs)):
+        assert len(o) == 3
+        if i % 5:
+            continue                      # the plain implementation on every fifth request
+        seq = list(p)
+        for k, tok in enumerate(o):
+            logits = plain_model.forward_logits(weights, cfg, seq)[-1]
+            assert logits[tok].item() >= logits.max().item() - 0.05 * logits.abs().max().item(), f"request {i}, token {k}: engine chose {tok}, plain argmax {int(logits.argmax())}"
+            seq.append(tok)
