@@ -29,8 +29,8 @@ class StepError(RuntimeError):
 def padded_step_sizes(tokens: int, requests: int, wanted: int, max_requests: int, max_tokens: int, limit: int):
     """The sizes (tokens, requests, wanted rows) that a step is padded to before it is replayed from a CUDA graph: tokens
     to a multiple of 32 (up to 128) or 64, requests to a power of two with room for the request that holds the padding
-    tokens, wanted rows to a power of two that is at least the requests'.  None: the step is not padded (more than ``limit`` tokens, nothing wanted,
-    or no room left for the padding), it runs on launches one by one."""
+    tokens, wanted rows to a power of two that is at least the requests'.  None: the step is not padded (more than ``limit``
+    tokens, nothing wanted, or no room left for the padding), it runs on launches one by one."""
     if wanted <= 0 or tokens <= 0 or tokens > limit:
         return None
     Tb = (tokens + 31) // 32 * 32 if tokens <= 128 else (tokens + 63) // 64 * 64
