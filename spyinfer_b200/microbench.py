@@ -3,6 +3,7 @@
     python -m spyinfer_b200.microbench gemm --m 2048 --n 24576 --k 4096 [--out-dtype float32] [--iters 20] [--graph] [--defer] [--epilogue swiglu]
     python -m spyinfer_b200.microbench attention --batch 8 --context 8192 [--q-len 1] [--split-keys 576] [--kernel tc|mma|decode] [--iters 10]
                                                  [--heads 64 --kv-heads 8 --head-dim 128] [--graph]
+    python -m spyinfer_b200.microbench rmsnorm --rows 2048 [--size 4096] [--splits 6]
 
 Defaults are Qwen3-8B's sizes (32 query heads, 8 key/value heads, head size 128, pages of 16).
 Timing is by CUDA events around ``iters`` launches after a warm-up (``--graph``: replayed from a CUDA graph, which
@@ -109,6 +110,43 @@ def bench_attention(batch: int, context: int, q_len: int = 1, split_keys: int = 
     return {"us": ms * 1e3, "kv_gbs": kv_bytes / ms / 1e6, "tflops": flops / ms / 1e9}
 
 
+def bench_rmsnorm(rows: int, size: int, splits: int = 0, iters: int = 20, graph: bool = True) -> dict:
+    """The residual norm as a layer runs it: ``h += delta; x = norm(h) * weight`` with a float32 stream ``h``, bfloat16 ``x``
+    and a bfloat16 ``delta`` (``splits == 0``) or ``splits`` stacked float32 partial products.  Several copies of the
+    buffers are cycled so that a launch does not find the last one's in L2."""
+    copies = max(2, int(200e6 // (rows * size * 10)) + 1)
+    hs = [torch.randn(rows, size, device=DEV) for _ in range(copies)]
+    ds = [torch.randn(splits, rows, size, device=DEV) if splits else torch.randn(rows, size, device=DEV).to(torch.bfloat16) for _ in range(copies)]
+    w = torch.ones(size, device=DEV, dtype=torch.bfloat16)
+    out = torch.empty(rows, size, device=DEV, dtype=torch.bfloat16)
+
+    def run(i):
+        kernels.rmsnorm(hs[i % copies], w, 1e-6, out, delta=ds[i % copies], write_back=True)
+
+    run(0)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if graph:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(iters):
+                run(i)
+        g.replay()
+        torch.cuda.synchronize()
+        e0.record()
+        g.replay()
+        e1.record()
+    else:
+        e0.record()
+        for i in range(iters):
+            run(i)
+        e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / iters
+    nbytes = rows * size * (4 + 4 + 2 + (4 * splits if splits else 2))
+    return {"us": ms * 1e3, "gbs": nbytes / ms / 1e6}
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="what", required=True)
@@ -121,6 +159,11 @@ def main(argv=None) -> int:
     g.add_argument("--graph", action="store_true", help="replay the launches from a CUDA graph (device time without host launch cost)")
     g.add_argument("--defer", action="store_true", help="split-K parts may stay unsummed, as inside the model")
     g.add_argument("--epilogue", default=None, choices=["swiglu"])
+    n = sub.add_parser("rmsnorm")
+    n.add_argument("--rows", type=int, required=True)
+    n.add_argument("--size", type=int, default=4096)
+    n.add_argument("--splits", type=int, default=0, help="the delta is a stack of this many float32 partial products (0: one bfloat16 tensor)")
+    n.add_argument("--iters", type=int, default=20)
     a = sub.add_parser("attention")
     a.add_argument("--batch", type=int, required=True)
     a.add_argument("--context", type=int, required=True)
@@ -140,6 +183,9 @@ def main(argv=None) -> int:
     if args.what == "gemm":
         r = bench_gemm(args.m, args.n, args.k, getattr(torch, args.out_dtype), args.iters, graph=args.graph, defer=args.defer, epilogue=args.epilogue)
         print(f"gemm M={args.m} N={args.n} K={args.k}: {r['us']:.1f} us, {r['tflops']:.1f} TFLOP/s, {r['gbs']:.1f} GB/s")
+    elif args.what == "rmsnorm":
+        r = bench_rmsnorm(args.rows, args.size, args.splits, args.iters)
+        print(f"rmsnorm rows={args.rows} size={args.size} splits={args.splits}: {r['us']:.1f} us, {r['gbs']:.1f} GB/s")
     else:
         r = bench_attention(args.batch, args.context, args.q_len, args.split_keys, nh=args.heads, nkv=args.kv_heads, hd=args.head_dim, page_size=args.page_size,
                             iters=args.iters, kernel=args.kernel, share=args.share, graph=args.graph)
