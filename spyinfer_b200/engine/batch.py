@@ -59,6 +59,10 @@ class StepBatch:
     max_ctx_len: int = 0
     #: every request of the batch brings exactly one token (a decode step): parts may then take kernels made for that
     one_token_each: bool = False
+    #: how many requests at the head of the batch bring exactly one token while later ones bring more (0 when the batch is
+    #: not laid out that way): an attention part may run those through its kernel for decoding and the rest through the
+    #: one for prompt portions
+    one_token_head: int = 0
     extras: Dict[str, object] = field(default_factory=dict)
 
 

@@ -115,6 +115,29 @@ class ModelRunner:
         tables = [cache.gather_block_tables(rids, g, width) for g in range(cache.num_groups())]
         return self.stager.stage(token_ids, positions, seq_of_token, q_start, ctx_len, slots, logit_rows, tables, pad_tokens, pad_seqs)
 
+    def _build_mixed_batch(self, entries: Sequence[StepEntry]) -> StepBatch:
+        """The batch of a step that mixes decoded tokens with prompt portions: the requests that bring one token are laid
+        out first (``StepBatch.one_token_head`` says how many), so that attention can read their caches with the kernel made
+        for decoding, which is two to three times faster at it than the kernel for portions; the wanted rows keep the order
+        of ``entries``."""
+        n = len(entries)
+        order = sorted(range(n), key=lambda i: len(entries[i].tokens) != 1)       # stable: one-token requests first
+        head = sum(1 for e in entries if len(e.tokens) == 1)
+        if head == 0 or head == n:
+            return self.build_batch(entries)
+        cache = self.cache
+        laid_out = [entries[i] for i in order]
+        rids, token_ids, positions, seq_of_token, q_start, ctx_len, slots, logit_rows, longest = self._fill(laid_out)
+        # the wanted rows, entry by entry in the caller's order
+        ends = np.cumsum([len(e.want) for e in laid_out])
+        rows_of = {i: logit_rows[end - len(entries[i].want):end] for i, end in zip(order, ends)}
+        logit_rows = np.concatenate([rows_of[i] for i in range(n)]).astype(np.int32) if len(logit_rows) else logit_rows
+        width = max(1, cache.pages_for(longest))
+        tables = [cache.gather_block_tables(rids, g, width) for g in range(cache.num_groups())]
+        batch = self.stager.stage(token_ids, positions, seq_of_token, q_start, ctx_len, slots, logit_rows, tables)
+        batch.one_token_head = head
+        return batch
+
     def commit(self, entries: Sequence[StepEntry]) -> None:
         self.cache.advance([e.request for e in entries], [len(e.tokens) for e in entries])
 
@@ -152,6 +175,9 @@ class ModelRunner:
     # one than the device takes to run them (the default, 384, is where the two meet at the 8B shape).
     #: graphs of padded steps kept at a time (the least recently used one goes first)
     GRAPH_STEP_LIMIT = 24
+    #: a padded step's graph runs every token through the attention kernel for portions; with more one-token requests than
+    #: this beside a portion the step is launched one by one instead, which lets those requests take the decode kernel
+    GRAPH_STEP_ONE_TOKEN_REQUESTS = 16
 
     def _step_graph(self, entries: Sequence[StepEntry], tokens_from: Optional[torch.Tensor] = None) -> torch.Tensor:
         S = len(entries)
@@ -253,6 +279,8 @@ class ModelRunner:
                 raise StepError("a request appears twice in one step")
             return self._step_graph(entries, tokens_from)
         sizes = self._padded_sizes(entries) if self._use_graphs and tokens_from is None else None
+        if sizes is not None and sum(1 for e in entries if len(e.tokens) == 1) > self.GRAPH_STEP_ONE_TOKEN_REQUESTS:
+            sizes = None   # many decoded tokens beside a portion: launched one by one, the decoded tokens on the decode kernel
         if sizes is not None:
             if len({e.request for e in entries}) != len(entries):
                 raise StepError("a request appears twice in one step")
@@ -266,7 +294,7 @@ class ModelRunner:
             self.steps += 1
             self.tokens_run += sum(len(e.tokens) for e in entries)
             return logits
-        batch = self.build_batch(entries)
+        batch = self.build_batch(entries) if tokens_from is not None else self._build_mixed_batch(entries)
         if tokens_from is not None:
             batch.token_ids.copy_(tokens_from[:batch.num_tokens])
         logits = self.model.forward(batch, self.cache)

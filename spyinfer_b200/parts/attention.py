@@ -30,6 +30,8 @@ class Attention(Mixer):
     projections have bias tensors ``{q,k,v}_proj.bias`` / ``o_proj.bias``)."""
 
     graph_safe = True
+    #: from this many one-token requests at the head of a mixed batch on, they get a launch of the decode kernel of their own
+    ONE_TOKEN_HEAD_MIN = 4
 
     def __init__(self, params, ctx):
         super().__init__(params, ctx)
@@ -143,9 +145,17 @@ class Attention(Mixer):
                                   batch.num_seqs, self.scale, window=self.window, split_keys=split_keys, max_splits=max_splits,
                                   status=batch.status)
         elif boxes:
-            # prompt portions (and whatever decodes beside them): blocks of 256 query rows on tcgen05
-            kernels.attention_tc(q, self.nh, self.hd, out, cache.pages, cache.block_table, batch.positions, batch.q_start,
-                                 batch.num_seqs, self.scale, window=self.window, status=batch.status)
+            # prompt portions on blocks of 256 query rows; requests that decode beside them (laid out first in the batch)
+            # go through the decode kernel, which reads a cache two to three times faster for one token than a 256-row block does
+            head = batch.one_token_head
+            if not (self.ONE_TOKEN_HEAD_MIN <= head <= kernels.ATTENTION_DECODE_MAX_SEQS and head * self.nkv <= kernels.ATTENTION_DECODE_MAX_PAIRS
+                    and kernels.attention_decode_takes(self.nh, self.nkv, self.hd, cache.page_size, x.dtype)):
+                head = 0
+            if head:
+                kernels.attention_decode(q, self.nh, self.hd, out, cache.pages, cache.block_table[:head], batch.positions, batch.q_start[:head + 1],
+                                         head, self.scale, window=self.window, status=batch.status)
+            kernels.attention_tc(q, self.nh, self.hd, out, cache.pages, cache.block_table[head:], batch.positions, batch.q_start[head:],
+                                 batch.num_seqs - head, self.scale, window=self.window, status=batch.status)
         elif self.mma:
             kernels.attention_mma(q, self.nh, self.hd, out, cache.pages, cache.block_table, batch.positions, batch.q_start,
                                   batch.num_seqs, self.scale, window=self.window, status=batch.status)

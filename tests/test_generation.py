@@ -295,6 +295,40 @@ def test_random_engine_options_and_request_mixes(tiny_models, seed):
         engine.runner.cache.check_invariants()
 
 
+@pytest.mark.parametrize("name,graphs", [("d", False), ("d", True), ("c", False), ("b", True)])
+def test_decoded_tokens_beside_a_portion_take_the_decode_kernel(tiny_models, name, graphs):
+    """A step that mixes many decoded tokens with prompt portions lays the one-token requests out first and runs their
+    attention through the decode kernel, the portions through the kernel for portions.  The logits come back in the order
+    of the entries as given (a portion first, decoded tokens around a second portion), every row as the plain
+    implementation has it; with graphs on, twenty decoded tokens are too many for a padded graph and take the same path."""
+    from spyinfer_b200.engine import StepEntry
+    folder, cfg, weights = tiny_models[name]
+    rng = np.random.default_rng(23)
+    V = cfg["vocab_size"]
+    n_dec = 20 if graphs else 7
+    engine = engine_for(folder, "bfloat16", max_num_seqs=32, num_kvcache_blocks=256, max_num_batched_tokens=512, use_cuda_graphs=graphs)
+    seqs = {f"r{i}": rng.integers(1, V, size=int(rng.integers(3, 150))).tolist() for i in range(n_dec)}
+    for r, toks in seqs.items():                                     # the requests that will decode: all but their last token
+        assert engine.step_raw([StepEntry(r, toks[:-1], [])]) is None
+    p1, p2 = rng.integers(1, V, size=45).tolist(), rng.integers(1, V, size=133).tolist()
+    engine.step_raw([StepEntry("p2", p2[:100], [])])
+    names = list(seqs)
+    entries = ([StepEntry("p1", p1, [0, 44])] + [StepEntry(r, seqs[r][-1:], [0]) for r in names[:3]] + [StepEntry("p2", p2[100:], [32, 5])]
+               + [StepEntry(r, seqs[r][-1:], [0]) for r in names[3:]])
+    got = engine.step_raw(entries)
+    want = []
+    for e in entries:
+        full = p1 if e.request == "p1" else (p2 if e.request == "p2" else seqs[e.request])
+        ref = plain_model.forward_logits(weights, cfg, full).numpy()
+        start = len(full) - len(e.tokens)
+        want += [ref[start + w] for w in e.want]
+    want = np.stack(want)
+    assert got.shape == want.shape
+    scale = np.abs(want).max()
+    np.testing.assert_allclose(got, want, rtol=3e-2, atol=5e-2 * scale)
+    assert np.sqrt(((got - want) ** 2).mean()) <= 2e-2 * np.sqrt((want ** 2).mean())
+
+
 def SamplingParamsFor(n):
     from spyinfer_b200 import SamplingParams
     return SamplingParams(max_new_tokens=n, ignore_eos=True)
