@@ -73,6 +73,7 @@ class ModelRunner:
         self._graphs = {}          # padded sizes of a step -> (graph, logits, kernel launches it holds); decode steps: the batch size
         self._use_graphs = bool(config.use_cuda_graphs) and model.graph_safe()
         self._graph_pool = None
+        self._capture_stream = None
         #: set to a list to have every step append a pair of CUDA events (timing enabled) recorded
         #: before its first and after its last launch: the sum of the pairs' times against the span
         #: from the first to the last event is the share of the time the device was at work
@@ -199,15 +200,25 @@ class ModelRunner:
             self._graphs[key] = "warm"
             return self.model.forward(batch, self.cache)
         if held == "warm":
-            torch.cuda.synchronize()
             before = kernels.launch_count()
             graph = torch.cuda.CUDAGraph()
             if self._graph_pool is None:
                 self._graph_pool = torch.cuda.graph_pool_handle()
-            # one memory pool for all step graphs: they never run at the same time, none reads what another wrote, and the
-            # logits each returns stay allocated while the graph is held, so their activations may share the same memory
-            with torch.cuda.graph(graph, pool=self._graph_pool):
-                static_logits = self.model.forward(batch, self.cache)
+                self._capture_stream = torch.cuda.Stream(device=self.device)
+            # One memory pool for all step graphs: they never run at the same time, none reads what another wrote, and the
+            # logits each returns stay allocated while the graph is held, so their activations may share the same memory.
+            # Captured on a stream of its own between two joins with the current one.  (torch.cuda.graph() would also
+            # collect garbage and hand all cached device memory back first, after which the next large step allocates anew:
+            # with a large model in memory that cost most of a second at every new size.)
+            current = torch.cuda.current_stream(self.device)
+            self._capture_stream.wait_stream(current)
+            with torch.cuda.stream(self._capture_stream):
+                graph.capture_begin(pool=self._graph_pool)
+                try:
+                    static_logits = self.model.forward(batch, self.cache)
+                finally:
+                    graph.capture_end()
+            current.wait_stream(self._capture_stream)
             launches = kernels.launch_count() - before
             self._graphs[key] = (graph, static_logits, launches)
             kernels.count_launches(-launches)   # captured, not run
