@@ -4,6 +4,7 @@
     python -m spyinfer_b200.microbench attention --batch 8 --context 8192 [--q-len 1] [--split-keys 576] [--kernel tc|mma|decode] [--iters 10]
                                                  [--heads 64 --kv-heads 8 --head-dim 128] [--graph]
     python -m spyinfer_b200.microbench rmsnorm --rows 2048 [--size 4096] [--splits 6]
+    python -m spyinfer_b200.microbench step --batch 8 --context 8192 [--layers 4] [--prompt-tokens 2048]      # one step's kernels on the time axis
 
 Defaults are Qwen3-8B's sizes (32 query heads, 8 key/value heads, head size 128, pages of 16).
 Timing is by CUDA events around ``iters`` launches after a warm-up (``--graph``: replayed from a CUDA graph, which
@@ -147,6 +148,69 @@ def bench_rmsnorm(rows: int, size: int, splits: int = 0, iters: int = 20, graph:
     return {"us": ms * 1e3, "gbs": nbytes / ms / 1e6}
 
 
+def step_timeline(batch: int, context: int, layers: int = 4, shape: dict = None, prompt_tokens: int = 0) -> list:
+    """The kernels of one step of a model with ``layers`` layers of the given layer sizes (default: Qwen3-8B's), as the
+    profiler (CUPTI) saw them on the device: ``(name, start µs, duration µs)`` in the order of their starts.  A decode step
+    of ``batch`` requests holding ``context`` keys each, replayed from its graph; with ``prompt_tokens`` a prompt of that
+    many tokens instead.  With programmatic dependent launch a kernel starts while the one ahead still runs, so what a
+    link of the chain costs is the distance between two kernels' ENDS, which ``print_timeline`` lists."""
+    from torch.profiler import ProfilerActivity, profile
+
+    from .config import config_from_json
+    from .engine import LLMEngine, StepEntry
+
+    cfg = {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "hidden_act": "silu", "num_hidden_layers": layers, "hidden_size": 4096,
+           "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 12288, "vocab_size": 151936,
+           "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "max_position_embeddings": 40960}
+    cfg.update(shape or {})
+    page = 16
+    tokens = max(context + 16, prompt_tokens + 16)
+    engine = LLMEngine(model_config=config_from_json(cfg), seed=0, dtype="bfloat16", max_num_seqs=max(batch, 1), max_model_len=tokens,
+                       kvcache_block_size=page, num_kvcache_blocks=max(batch, 1) * (tokens // page + 2) + 8, max_num_batched_tokens=max(prompt_tokens, batch, 16))
+    runner, cache = engine.runner, engine.runner.cache
+    if prompt_tokens:
+        toks = torch.randint(0, 1000, (prompt_tokens,)).tolist()
+
+        def run(i):
+            runner.step([StepEntry(f"p{i}", toks, [prompt_tokens - 1])])
+            runner.finish(f"p{i}")
+    else:
+        rids = [f"d{i}" for i in range(batch)]
+        for r in rids:
+            cache.add_request(r)
+            cache.reserve(r, context)
+            cache.commit(r, context)
+
+        def run(i):
+            runner.step([StepEntry(r, [5 + i], [0]) for r in rids])
+    for i in range(5):
+        run(i)
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        run(5)
+        torch.cuda.synchronize()
+    events = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA and "mem" not in e.name.lower()]
+    events.sort(key=lambda e: e.time_range.start)
+    t0 = events[0].time_range.start
+    return [(e.name, e.time_range.start - t0, e.time_range.end - e.time_range.start) for e in events]
+
+
+def print_timeline(events: list) -> None:
+    """The second layer's kernels with their starts, durations, ends and the distance of each end from the end before."""
+    def short(name):
+        name = name.replace("(anonymous namespace)::", "").replace("void ", "")
+        return name.split("(")[0][:44]
+    firsts = [i for i, e in enumerate(events) if "rmsnorm" in e[0]]
+    lo, hi = (firsts[2], firsts[4] + 1) if len(firsts) > 4 else (0, len(events))     # two norms a layer: the second layer, and the norm after it
+    prev_end = None
+    print(f"{'kernel':46s} {'start':>9s} {'duration':>9s} {'end':>9s} {'after the end before':>21s}")
+    for name, start, dur in events[lo:hi]:
+        end = start + dur
+        print(f"{short(name):46s} {start:9.1f} {dur:9.1f} {end:9.1f} {'' if prev_end is None else format(end - prev_end, '21.1f')}")
+        prev_end = end
+    print(f"whole step: {events[-1][1] + events[-1][2]:.1f} us, {len(events)} kernels")
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="what", required=True)
@@ -164,6 +228,11 @@ def main(argv=None) -> int:
     n.add_argument("--size", type=int, default=4096)
     n.add_argument("--splits", type=int, default=0, help="the delta is a stack of this many float32 partial products (0: one bfloat16 tensor)")
     n.add_argument("--iters", type=int, default=20)
+    t = sub.add_parser("step", help="the kernels of one step on the device's time axis")
+    t.add_argument("--batch", type=int, default=8)
+    t.add_argument("--context", type=int, default=8192)
+    t.add_argument("--layers", type=int, default=4)
+    t.add_argument("--prompt-tokens", type=int, default=0, help="a prompt of this many tokens instead of a decode step")
     a = sub.add_parser("attention")
     a.add_argument("--batch", type=int, required=True)
     a.add_argument("--context", type=int, required=True)
@@ -183,6 +252,9 @@ def main(argv=None) -> int:
     if args.what == "gemm":
         r = bench_gemm(args.m, args.n, args.k, getattr(torch, args.out_dtype), args.iters, graph=args.graph, defer=args.defer, epilogue=args.epilogue)
         print(f"gemm M={args.m} N={args.n} K={args.k}: {r['us']:.1f} us, {r['tflops']:.1f} TFLOP/s, {r['gbs']:.1f} GB/s")
+    elif args.what == "step":
+        print_timeline(step_timeline(args.batch, args.context, args.layers, prompt_tokens=args.prompt_tokens))
+        return 0
     elif args.what == "rmsnorm":
         r = bench_rmsnorm(args.rows, args.size, args.splits, args.iters)
         print(f"rmsnorm rows={args.rows} size={args.size} splits={args.splits}: {r['us']:.1f} us, {r['gbs']:.1f} GB/s")
