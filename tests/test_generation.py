@@ -295,6 +295,26 @@ def test_random_engine_options_and_request_mixes(tiny_models, seed):
         engine.runner.cache.check_invariants()
 
 
+def test_one_long_request_decoding_beside_a_portion(tiny_models):
+    """A single decoded token whose request holds more than a thousand keys, beside a prompt portion of another request: the
+    decode kernel takes it (one 256-row block would walk its cache alone); logits as the plain implementation has them."""
+    from spyinfer_b200.engine import StepEntry
+    folder, cfg, weights = tiny_models["d"]
+    rng = np.random.default_rng(41)
+    long_one, other = rng.integers(1, cfg["vocab_size"], size=1300).tolist(), rng.integers(1, cfg["vocab_size"], size=500).tolist()
+    engine = LLMEngine_for_long(folder)
+    assert engine.step_raw([StepEntry("long", long_one[:-1], [])]) is None
+    got = engine.step_raw([StepEntry("other", other, [499]), StepEntry("long", long_one[-1:], [0])])
+    ref_long = plain_model.forward_logits(weights, cfg, long_one)[-1].numpy()
+    ref_other = plain_model.forward_logits(weights, cfg, other)[-1].numpy()
+    for row, ref in ((got[0], ref_other), (got[1], ref_long)):
+        np.testing.assert_allclose(row, ref, rtol=3e-2, atol=5e-2 * np.abs(ref).max())
+
+
+def LLMEngine_for_long(folder):
+    return engine_for(folder, "bfloat16", max_num_seqs=4, max_model_len=2048, num_kvcache_blocks=160, max_num_batched_tokens=2048, graph_step_tokens=0)
+
+
 @pytest.mark.parametrize("name,graphs", [("d", False), ("d", True), ("c", False), ("b", True)])
 def test_decoded_tokens_beside_a_portion_take_the_decode_kernel(tiny_models, name, graphs):
     """A step that mixes many decoded tokens with prompt portions lays the one-token requests out first and runs their
