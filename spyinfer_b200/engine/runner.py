@@ -26,13 +26,21 @@ class StepError(RuntimeError):
     pass
 
 
-def padded_step_sizes(tokens: int, requests: int, wanted: int, max_requests: int, max_tokens: int, limit: int):
-    """The sizes (tokens, requests, wanted rows) that a step is padded to before it is replayed from a CUDA graph: tokens
-    to a multiple of 32 (up to 128) or 64, requests to a power of two with room for the request that holds the padding
-    tokens, wanted rows to a power of two that is at least the requests'.  None: the step is not padded (more than ``limit``
-    tokens, nothing wanted, or no room left for the padding), it runs on launches one by one."""
+def padded_step_sizes(tokens: int, requests: int, wanted: int, max_requests: int, max_tokens: int, limit: int, head: int = 0):
+    """The sizes (tokens, requests, wanted rows, one-token requests at the head) that a step is padded to before it is
+    replayed from a CUDA graph: tokens to a multiple of 32 (up to 128) or 64, requests to a power of two with room for the
+    request that holds the padding tokens, wanted rows to a power of two that is at least the requests'; ``head`` (the
+    requests at the head of the batch that bring one token and go through the decode kernel; 0: none do) to a power of two,
+    the padding being one-token requests of their own.  None: the step is not padded (more than ``limit`` tokens, nothing
+    wanted, or no room left for the padding), it runs on launches one by one."""
     if wanted <= 0 or tokens <= 0 or tokens > limit:
         return None
+    Hb = 0
+    if head > 0:
+        Hb = 1
+        while Hb < head:
+            Hb *= 2
+    tokens, requests = tokens + (Hb - head), requests + (Hb - head)
     Tb = (tokens + 31) // 32 * 32 if tokens <= 128 else (tokens + 63) // 64 * 64
     need = requests + (1 if Tb > tokens else 0)           # the padding tokens are a request of their own
     Sb = 1
@@ -45,7 +53,7 @@ def padded_step_sizes(tokens: int, requests: int, wanted: int, max_requests: int
     Rb = max(min(Rb, Tb), min(Sb, Tb))                    # at least a row a request: fewer distinct sizes, and the extra rows cost next to nothing
     if Sb < need or Rb < wanted or Tb > max_tokens:
         return None
-    return Tb, Sb, Rb
+    return Tb, Sb, Rb, Hb
 
 
 class ModelRunner:
@@ -116,23 +124,36 @@ class ModelRunner:
         tables = [cache.gather_block_tables(rids, g, width) for g in range(cache.num_groups())]
         return self.stager.stage(token_ids, positions, seq_of_token, q_start, ctx_len, slots, logit_rows, tables, pad_tokens, pad_seqs)
 
-    def _build_mixed_batch(self, entries: Sequence[StepEntry]) -> StepBatch:
-        """The batch of a step that mixes decoded tokens with prompt portions: the requests that bring one token are laid
-        out first (``StepBatch.one_token_head`` says how many), so that attention can read their caches with the kernel made
-        for decoding, which is two to three times faster at it than the kernel for portions; the wanted rows keep the order
-        of ``entries``."""
+    #: From this many one-token requests beside prompt portions on, their attention runs through the decode kernel (the
+    #: batch says so in ``one_token_head``), which reads a cache two to three times faster for one token than a 256-row
+    #: block of the kernel for portions does ...
+    ONE_TOKEN_HEAD_MIN = 4
+    #: ... or from this many keys of the longest of them on: such a block walks a long cache alone, tile after tile (77 us for
+    #: 8,192 keys where the decode kernel, which shares a pair's tiles out over all blocks, needs 14)
+    ONE_TOKEN_HEAD_KEYS = 1024
+
+    def _lay_out(self, entries: Sequence[StepEntry]):
+        """The arrays of a step that is no decode step, with the requests that bring one token laid out first.  Returns
+        ``(filled, head)``: ``filled`` as ``_fill`` gives it, the wanted rows in the order of ``entries`` as given; ``head``,
+        how many requests at the head bring one token each and should go through the decode kernel (0: none, or not worth a
+        launch of its own)."""
         n = len(entries)
+        ones = sum(1 for e in entries if len(e.tokens) == 1)
+        if ones == 0 or ones == n:
+            return self._fill(entries), 0
         order = sorted(range(n), key=lambda i: len(entries[i].tokens) != 1)       # stable: one-token requests first
-        head = sum(1 for e in entries if len(e.tokens) == 1)
-        if head == 0 or head == n:
-            return self.build_batch(entries)
-        cache = self.cache
         laid_out = [entries[i] for i in order]
         rids, token_ids, positions, seq_of_token, q_start, ctx_len, slots, logit_rows, longest = self._fill(laid_out)
-        # the wanted rows, entry by entry in the caller's order
-        ends = np.cumsum([len(e.want) for e in laid_out])
-        rows_of = {i: logit_rows[end - len(entries[i].want):end] for i, end in zip(order, ends)}
-        logit_rows = np.concatenate([rows_of[i] for i in range(n)]).astype(np.int32) if len(logit_rows) else logit_rows
+        if len(logit_rows):                                                       # the wanted rows, entry by entry in the caller's order
+            ends = np.cumsum([len(e.want) for e in laid_out])
+            rows_of = {i: logit_rows[end - len(entries[i].want):end] for i, end in zip(order, ends)}
+            logit_rows = np.concatenate([rows_of[i] for i in range(n)]).astype(np.int32)
+        head = ones if ones >= self.ONE_TOKEN_HEAD_MIN or int(ctx_len[:ones].max()) >= self.ONE_TOKEN_HEAD_KEYS else 0
+        return (rids, token_ids, positions, seq_of_token, q_start, ctx_len, slots, logit_rows, longest), head
+
+    def _batch_as_laid_out(self, filled, head: int) -> StepBatch:
+        cache = self.cache
+        rids, token_ids, positions, seq_of_token, q_start, ctx_len, slots, logit_rows, longest = filled
         width = max(1, cache.pages_for(longest))
         tables = [cache.gather_block_tables(rids, g, width) for g in range(cache.num_groups())]
         batch = self.stager.stage(token_ids, positions, seq_of_token, q_start, ctx_len, slots, logit_rows, tables)
@@ -176,8 +197,8 @@ class ModelRunner:
     # one than the device takes to run them (the default, 384, is where the two meet at the 8B shape).
     #: graphs of padded steps kept at a time (the least recently used one goes first)
     GRAPH_STEP_LIMIT = 24
-    #: a padded step's graph runs every token through the attention kernel for portions; with more one-token requests than
-    #: this beside a portion the step is launched one by one instead, which lets those requests take the decode kernel
+    #: a padded step's graph is made for a padded number of one-token requests at its head; with more of them than this
+    #: the step is launched one by one instead
     GRAPH_STEP_ONE_TOKEN_REQUESTS = 16
 
     def _step_graph(self, entries: Sequence[StepEntry], tokens_from: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -230,35 +251,39 @@ class ModelRunner:
         self.graph_steps += 1
         return static_logits
 
-    def _padded_sizes(self, entries: Sequence[StepEntry]):
-        """The padded sizes (tokens, requests, wanted rows) under which a small step of any shape is replayed from a
-        graph, or None when it runs eagerly (too many tokens, nothing wanted, no room for the padding)."""
-        return padded_step_sizes(sum(len(e.tokens) for e in entries), len(entries), sum(len(e.want) for e in entries),
-                                 self.config.max_num_seqs, self.stager.max_tokens, self.config.graph_step_tokens)
-
-    def _build_padded_batch(self, entries: Sequence[StepEntry], Tb: int, Sb: int, Rb: int) -> StepBatch:
-        """The batch laid out for ``Tb`` tokens, ``Sb`` requests and ``Rb`` wanted rows: the entries first; the
-        padding tokens form one more request at position 0 that reads and writes only the cache's spare page, further
-        requests are empty, and the padding rows of the logits repeat the first wanted row."""
+    def _padded_batch(self, filled, head: int, Tb: int, Sb: int, Rb: int, Hb: int) -> StepBatch:
+        """The batch laid out for ``Tb`` tokens, ``Sb`` requests, ``Rb`` wanted rows and ``Hb`` one-token requests at the head:
+        the ``head`` real one-token requests, one-token requests of padding up to ``Hb``, the other requests, then one
+        request that holds the padding tokens; further requests are empty.  All padding sits at position 0 and reads and
+        writes only the cache's spare page; the padding rows of the logits repeat the first wanted row."""
         cache = self.cache
-        rids, tok, pos, seq_of, q_start, ctx, slot, rows, _ = self._fill(entries)
-        T, S, R = len(tok), len(ctx), len(rows)
+        rids, tok, pos, seq_of, q_start, ctx, slot, rows, _ = filled
+        T, S, R, extra = len(tok), len(ctx), len(rows), Hb - head
         token_ids, positions = np.zeros(Tb, np.int32), np.zeros(Tb, np.int32)
-        seq_of_token = np.full(Tb, S, np.int32)
-        token_ids[:T], positions[:T], seq_of_token[:T] = tok, pos, seq_of
+        seq_of_token = np.full(Tb, S + extra, np.int32)                          # what is left over belongs to the request of padding tokens
+        token_ids[:head], positions[:head], seq_of_token[:head] = tok[:head], pos[:head], seq_of[:head]
+        seq_of_token[head:Hb] = np.arange(head, Hb, dtype=np.int32)
+        token_ids[Hb:T + extra], positions[Hb:T + extra], seq_of_token[Hb:T + extra] = tok[head:], pos[head:], seq_of[head:] + extra
         starts = np.full(Sb + 1, Tb, np.int32)
-        starts[:S + 1] = q_start
+        starts[:Hb + 1] = np.arange(Hb + 1, dtype=np.int32)
+        starts[Hb:S + extra + 1] = q_start[head:] + extra
         ctx_len, slots = np.ones(Sb, np.int32), np.zeros(Sb, np.int32)
-        ctx_len[:S], slots[:S] = ctx, slot
-        logit_rows = np.full(Rb, rows[0], np.int32)
-        logit_rows[:R] = rows
+        ctx_len[:head], slots[:head] = ctx[:head], slot[:head]
+        ctx_len[Hb:S + extra], slots[Hb:S + extra] = ctx[head:], slot[head:]
+        logit_rows = np.full(Rb, 0, np.int32)
+        logit_rows[:R] = np.where(rows >= head, rows + extra, rows)
+        logit_rows[R:] = logit_rows[0]
         tables = []
         for g in range(cache.num_groups()):
             t = np.full((Sb, cache.width), -1, np.int32)
-            cache.gather_block_tables(rids, g, out=t)
-            t[S:, 0] = cache.spare_page(g)
+            real = cache.gather_block_tables(rids, g, cache.width)
+            t[:head], t[Hb:S + extra] = real[:head], real[head:]
+            t[head:Hb, 0] = cache.spare_page(g)
+            t[S + extra:, 0] = cache.spare_page(g)
             tables.append(t)
-        return self.stager.stage(token_ids, positions, seq_of_token, starts, ctx_len, slots, logit_rows, tables, Tb, Sb)
+        batch = self.stager.stage(token_ids, positions, seq_of_token, starts, ctx_len, slots, logit_rows, tables, Tb, Sb)
+        batch.one_token_head = Hb
+        return batch
 
     def step(self, entries: Sequence[StepEntry], tokens_from: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Runs the entries as one batch.  Returns float32 logits ``[wanted, vocab]`` on the
@@ -289,29 +314,29 @@ class ModelRunner:
             if len({e.request for e in entries}) != len(entries):
                 raise StepError("a request appears twice in one step")
             return self._step_graph(entries, tokens_from)
-        sizes = self._padded_sizes(entries) if self._use_graphs and tokens_from is None else None
-        if sizes is not None and sum(1 for e in entries if len(e.tokens) == 1) > self.GRAPH_STEP_ONE_TOKEN_REQUESTS:
-            sizes = None   # many decoded tokens beside a portion: launched one by one, the decoded tokens on the decode kernel
-        if sizes is not None:
+        if tokens_from is not None:
+            batch = self.build_batch(entries)
+            batch.token_ids.copy_(tokens_from[:batch.num_tokens])
+            logits = self.model.forward(batch, self.cache)
+        else:
             if len({e.request for e in entries}) != len(entries):
                 raise StepError("a request appears twice in one step")
-            batch = self._build_padded_batch(entries, *sizes)
-            wanted = sum(len(e.want) for e in entries)
-            logits = self._run_through_graph(("step",) + sizes, batch)[:wanted]
-            mixed = [k for k in self._graphs if isinstance(k, tuple)]
-            if len(mixed) > self.GRAPH_STEP_LIMIT:
-                del self._graphs[mixed[0]]
-            self.commit(entries)
-            self.steps += 1
-            self.tokens_run += sum(len(e.tokens) for e in entries)
-            return logits
-        batch = self.build_batch(entries) if tokens_from is not None else self._build_mixed_batch(entries)
-        if tokens_from is not None:
-            batch.token_ids.copy_(tokens_from[:batch.num_tokens])
-        logits = self.model.forward(batch, self.cache)
+            filled, head = self._lay_out(entries)
+            wanted = len(filled[7])
+            sizes = None
+            if self._use_graphs and head <= self.GRAPH_STEP_ONE_TOKEN_REQUESTS:
+                sizes = padded_step_sizes(len(filled[1]), len(entries), wanted, self.config.max_num_seqs, self.stager.max_tokens,
+                                          self.config.graph_step_tokens, head)
+            if sizes is not None:
+                logits = self._run_through_graph(("step",) + sizes, self._padded_batch(filled, head, *sizes))[:wanted]
+                mixed = [k for k in self._graphs if isinstance(k, tuple)]
+                if len(mixed) > self.GRAPH_STEP_LIMIT:
+                    del self._graphs[mixed[0]]
+            else:
+                logits = self.model.forward(self._batch_as_laid_out(filled, head), self.cache)
         self.commit(entries)
         self.steps += 1
-        self.tokens_run += batch.num_tokens
+        self.tokens_run += sum(len(e.tokens) for e in entries)
         return logits
 
     def finish(self, request) -> None:

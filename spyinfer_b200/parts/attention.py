@@ -30,11 +30,6 @@ class Attention(Mixer):
     projections have bias tensors ``{q,k,v}_proj.bias`` / ``o_proj.bias``)."""
 
     graph_safe = True
-    #: from this many one-token requests at the head of a mixed batch on, they get a launch of the decode kernel of their own
-    ONE_TOKEN_HEAD_MIN = 4
-    #: or from this many keys of the longest of them on (a 256-row block walks a long cache alone, tile after tile: 77 us for 8,192 keys
-    #: where the decode kernel, which shares a pair's tiles out over all blocks, needs 14)
-    ONE_TOKEN_HEAD_KEYS = 1024
 
     def __init__(self, params, ctx):
         super().__init__(params, ctx)
@@ -150,10 +145,9 @@ class Attention(Mixer):
         elif boxes:
             # prompt portions on blocks of 256 query rows; requests that decode beside them (laid out first in the batch)
             # go through the decode kernel, which reads a cache two to three times faster for one token than a 256-row block does
-            head = batch.one_token_head      # never set in a batch laid out for a graph, so the look at the lengths below is no part of a capture
+            head = batch.one_token_head      # the step function says whether a launch of the decode kernel pays for them
             if not (0 < head <= kernels.ATTENTION_DECODE_MAX_SEQS and head * self.nkv <= kernels.ATTENTION_DECODE_MAX_PAIRS
-                    and kernels.attention_decode_takes(self.nh, self.nkv, self.hd, cache.page_size, x.dtype)
-                    and (head >= self.ONE_TOKEN_HEAD_MIN or int(batch.host_ctx_len[:head].max()) >= self.ONE_TOKEN_HEAD_KEYS)):
+                    and kernels.attention_decode_takes(self.nh, self.nkv, self.hd, cache.page_size, x.dtype)):
                 head = 0
             if head:
                 kernels.attention_decode(q, self.nh, self.hd, out, cache.pages, cache.block_table[:head], batch.positions, batch.q_start[:head + 1],

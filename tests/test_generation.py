@@ -295,6 +295,50 @@ def test_random_engine_options_and_request_mixes(tiny_models, seed):
         engine.runner.cache.check_invariants()
 
 
+@pytest.mark.parametrize("decoders", [[1100], [30, 9, 60, 200, 45]])
+def test_small_steps_with_decode_kernel_requests_replayed_from_graphs(tiny_models, decoders):
+    """Small mixed steps whose one-token requests go through the decode kernel (one request holding more than a thousand keys,
+    or five requests: the graph's head is then padded to eight with one-token requests of padding): six steps of the same
+    padded sizes, each a new request's prompt beside the decoded tokens, give what an engine without graphs gives and what
+    the plain implementation gives, rows in the order of the entries."""
+    from spyinfer_b200.engine import StepEntry
+    folder, cfg, weights = tiny_models["d"]
+    rng = np.random.default_rng(len(decoders))
+    V = cfg["vocab_size"]
+    dec = {f"u{i}": rng.integers(1, V, size=n + 8).tolist() for i, n in enumerate(decoders)}
+    news = [rng.integers(1, V, size=20 + k).tolist() for k in range(6)]
+    outs = []
+    for graphs in (True, False):
+        engine = engine_for(folder, "bfloat16", max_num_seqs=16, max_model_len=2048, num_kvcache_blocks=256, max_num_batched_tokens=2048, use_cuda_graphs=graphs)
+        done = {}
+        for (r, toks), n in zip(dec.items(), decoders):
+            engine.step_raw([StepEntry(r, toks[:n], [])])
+            done[r] = n
+        got = []
+        for k, new in enumerate(news):
+            names = list(dec)
+            entries = ([StepEntry(r, dec[r][done[r]:done[r] + 1], [0]) for r in names[:1]] + [StepEntry(f"w{k}", new, [len(new) - 1])]
+                       + [StepEntry(r, dec[r][done[r]:done[r] + 1], [0]) for r in names[1:]])
+            got.append(engine.step_raw(entries).copy())
+            for r in names:
+                done[r] += 1
+            engine.release_raw(f"w{k}")
+        outs.append(got)
+        if graphs:
+            assert engine.runner.graph_steps >= 4
+            keys = [k for k in engine.runner._graphs if isinstance(k, tuple)]
+            assert keys and all(k[4] == (1 if len(decoders) == 1 else 8) for k in keys), keys
+    for k, (a, b) in enumerate(zip(*outs)):
+        np.testing.assert_allclose(a, b, rtol=3e-2, atol=3e-2, err_msg=f"step {k}")
+    first = list(dec)[0]
+    ref_first = plain_model.forward_logits(weights, cfg, dec[first][:decoders[0] + 6]).numpy()
+    for k, new in enumerate(news):
+        ref_new = plain_model.forward_logits(weights, cfg, new).numpy()
+        scale = max(np.abs(ref_new).max(), np.abs(ref_first).max())
+        np.testing.assert_allclose(outs[0][k][0], ref_first[decoders[0] + k], rtol=3e-2, atol=5e-2 * scale)
+        np.testing.assert_allclose(outs[0][k][1], ref_new[-1], rtol=3e-2, atol=5e-2 * scale)
+
+
 def test_one_long_request_decoding_beside_a_portion(tiny_models):
     """A single decoded token whose request holds more than a thousand keys, beside a prompt portion of another request: the
     decode kernel takes it (one 256-row block would walk its cache alone); logits as the plain implementation has them."""

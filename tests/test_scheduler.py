@@ -269,15 +269,17 @@ def test_padded_sizes_of_small_steps():
     """The sizes a small step is padded to for its CUDA graph: few distinct ones, always room for the step and for the
     request that holds the padding tokens, and no padding where there is no room or nothing to gain."""
     from spyinfer_b200.engine.runner import padded_step_sizes
-    assert padded_step_sizes(17, 3, 3, 8, 2048, 384) == (32, 4, 4)
-    assert padded_step_sizes(32, 1, 1, 8, 2048, 384) == (32, 1, 1)          # nothing to pad
-    assert padded_step_sizes(40, 5, 1, 8, 2048, 384) == (64, 8, 8)          # wanted rows: at least one a request
+    assert padded_step_sizes(17, 3, 3, 8, 2048, 384) == (32, 4, 4, 0)
+    assert padded_step_sizes(32, 1, 1, 8, 2048, 384) == (32, 1, 1, 0)          # nothing to pad
+    assert padded_step_sizes(40, 5, 1, 8, 2048, 384) == (64, 8, 8, 0)          # wanted rows: at least one a request
     assert padded_step_sizes(33, 8, 2, 8, 2048, 384) is None                # the padding tokens would need a ninth request
-    assert padded_step_sizes(64, 8, 8, 8, 2048, 384) == (64, 8, 8)
-    assert padded_step_sizes(130, 2, 1, 64, 2048, 384) == (192, 4, 4)
+    assert padded_step_sizes(64, 8, 8, 8, 2048, 384) == (64, 8, 8, 0)
+    assert padded_step_sizes(130, 2, 1, 64, 2048, 384) == (192, 4, 4, 0)
     assert padded_step_sizes(385, 1, 1, 64, 2048, 384) is None              # large steps run as they are
     assert padded_step_sizes(100, 1, 0, 64, 2048, 384) is None              # nothing wanted: no logits to return
     assert padded_step_sizes(300, 1, 1, 64, 256, 384) is None               # beyond the staging buffers
+    assert padded_step_sizes(100, 4, 4, 64, 2048, 384, head=3) == (128, 8, 8, 4)   # three one-token requests at the head and one of padding
+    assert padded_step_sizes(31, 2, 2, 8, 2048, 384, head=1) == (32, 4, 4, 1)
     seen = set()
     for t in range(1, 385):
         for s_ in (1, 2, 3, 5, 9, 17, 33):
